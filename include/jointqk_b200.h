@@ -1,0 +1,206 @@
+/*
+ * jointqk_b200 -- C ABI of the compress-then-attend key path for NVIDIA B200 (sm_100a).
+ *
+ * The reference (Amir-zsh/JointQK) is pure Python/PyTorch and has no FFI; each entry point
+ * below names the reference function whose work it takes over, by path inside that project.
+ *
+ * Conventions
+ *   - every function returns 0 on success, a negative JQK_E_* code for a rejected argument
+ *     and a positive cudaError_t value when a CUDA call failed; jqk_last_error() returns a
+ *     thread-local human-readable message for the last non-zero return on this thread;
+ *   - every pointer except `tables` (a host struct of device pointers), and where marked
+ *     "host", is a device pointer on the current device; buffers are borrowed for the
+ *     duration of the call (asynchronous on `stream`), nothing is allocated or freed;
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream;
+ *   - the library keeps no mutable global state except what is documented per function.
+ *
+ * Paged storage (new in this build; the reference stores dequantised floats)
+ *   - a page holds JQK_PAGE_TOKENS consecutive keys of one sequence for all kv heads;
+ *   - K pool:  uint32 [n_pages][n_kv_heads][words_per_record][16]; word w of key t of head h
+ *     in page p is k_pool[((p*H + h)*words_per_record + w)*16 + t];
+ *   - V pool:  bf16   [n_pages][n_kv_heads][16][d];
+ *   - page_table: int32 [n_seqs][page_table_stride], logical page -> physical page.
+ */
+#ifndef JOINTQK_B200_H_
+#define JOINTQK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JQK_PAGE_TOKENS 16
+#define JQK_MAX_DIM 128        /* head_dim: multiple of 16, at most 128 */
+#define JQK_MAX_COLS 128       /* coordinates that carry >0 bits, padded to 16 */
+#define JQK_MAX_WORDS 16       /* uint32 words per record */
+#define JQK_MAX_TABLES 208     /* lookups per record (see jqk_head_tables.table_fields) */
+#define JQK_DESC_INTS 32       /* int32 per head in jqk_head_tables.desc */
+#define JQK_MAX_GROUP 4        /* q heads scored together by one thread block */
+
+#define JQK_DTYPE_F32 0
+#define JQK_DTYPE_BF16 1
+#define JQK_DTYPE_F16 2
+
+#define JQK_E_ARG (-1)         /* null pointer, bad size or stride */
+#define JQK_E_LAYOUT (-2)      /* head tables inconsistent with the call */
+#define JQK_E_UNSUPPORTED (-3) /* shape outside what the kernels implement */
+#define JQK_E_WORKSPACE (-4)   /* workspace too small */
+
+/* Bits of the device status word (int32, OR-ed by kernels, never cleared by them). */
+#define JQK_STATUS_BAD_PAGE 1      /* page index outside [0, n_pages) - access skipped */
+#define JQK_STATUS_WAIT_EXPIRED 2  /* a bounded wait on an mbarrier gave up */
+
+/*
+ * Per-head device tables built on the host from a fitted compressor
+ * (reference object: PerCoordCompressor, experiments/stage1/toolkit/per_coord_quantization.py:43-121;
+ * fields derive from its bits_int, forward_map, inverse_map and codebooks_padded).
+ * "Column" c is the c-th coordinate with >0 bits in ascending record bit position.
+ *
+ *   desc          int32 [H][JQK_DESC_INTS]: d, n_cols, n_active, n_words, n_a_words, n_c_words,
+ *                 n_tables, payload_bits, then word_col_begin[0..n_words] at offset 8
+ *   col_meta      int32 [H][128]: width | bitpos << 4 | coord << 16 for column c (width 0 and
+ *                 coord 255 = padding column)
+ *   table_fields  int32 [H][JQK_MAX_TABLES][4]: col | width << 8 | shift << 12, or -1
+ *   fwd_cols      float [H][d][128]: forward_map[i][coord(c)]
+ *   thresholds    float [H][128][16]: code = #{l < 15 : x >= thresholds[c][l]} (+inf padded)
+ *   cb_cols       float [H][128][16]: codebooks_padded[coord(c)][l], 0 beyond the last level
+ *   qproj_cols    float [H][d][128]: inverse_map[coord(c)][i] (query projection)
+ *   inv_rows      float [H][128][d]: inverse_map[coord(c)][i] (reconstruction)
+ *   fwd_limbs     bf16  [H][3][128][d]: three-way bf16 split of fwd_cols, column-major
+ *                 (limb l, column c, dim i), for the tensor-core transform; may be NULL
+ */
+typedef struct jqk_head_tables {
+  int32_t n_heads;
+  int32_t d;
+  int32_t words_per_record; /* K pool stride in words: max n_words over the heads */
+  int32_t reserved;
+  const int32_t* desc;
+  const int32_t* col_meta;
+  const int32_t* table_fields;
+  const float* fwd_cols;
+  const float* thresholds;
+  const float* cb_cols;
+  const float* qproj_cols;
+  const float* inv_rows;
+  const uint16_t* fwd_limbs;
+} jqk_head_tables;
+
+/* Library version: major << 16 | minor. */
+int32_t jqk_version(void);
+
+/* Message for the last non-zero return on the calling thread ("" if none). */
+const char* jqk_last_error(void);
+
+/*
+ * Prefill compression: basis transform, per-coordinate nearest-centroid quantisation and
+ * bit-packing into pages.  Replaces the forward half of PerCoordCompressor.roundtrip
+ * (per_coord_quantization.py:132-157) for all heads of a layer, i.e. the per-head loop of
+ * JointQKPress._quantize_layer (experiments/stage1/toolkit/jointqk_press.py:253-256).
+ *
+ *   keys        [n_seqs][H][*][d] of key_dtype with element strides (seq, head, token); d contiguous
+ *   n_tokens    int32 [n_seqs] keys to compress per sequence in this call
+ *   seq_starts  int32 [n_seqs] position in the sequence of keys[...][0] (NULL = 0); the
+ *               destination of key t is slot (seq_starts+t) % 16 of logical page (seq_starts+t)/16
+ *   max_tokens  largest n_tokens[] value (host), sizes the grid
+ *   status      int32 device word, see JQK_STATUS_*
+ */
+int32_t jqk_compress_paged(const jqk_head_tables* tables, const void* keys, int32_t key_dtype,
+                           int64_t seq_stride, int64_t head_stride, int64_t token_stride,
+                           int32_t n_seqs, const int32_t* n_tokens, const int32_t* seq_starts,
+                           int32_t max_tokens, const int32_t* page_table,
+                           int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool,
+                           int32_t* status, void* stream);
+
+/*
+ * Reconstruction from pages: unpack, centroid lookup, inverse map.  Replaces the second half
+ * of PerCoordCompressor.roundtrip (per_coord_quantization.py:158-164).
+ *   out  float [n_seqs][H][max_tokens][d] (contiguous); rows beyond n_tokens[s] are not written
+ */
+int32_t jqk_decompress_paged(const jqk_head_tables* tables, int32_t n_seqs,
+                             const int32_t* n_tokens, int32_t max_tokens,
+                             const int32_t* page_table, int32_t page_table_stride,
+                             int32_t n_pages, const uint32_t* k_pool, float* out,
+                             int32_t* status, void* stream);
+
+/*
+ * Integer codes in coordinate order (0 for coordinates with 0 bits).  The reference never
+ * returns its argmin indices (per_coord_quantization.py:156-160); this exposes them for
+ * bit-exact parity checks.
+ *   codes  uint8 [n_seqs][H][max_tokens][d]
+ */
+int32_t jqk_unpack_codes(const jqk_head_tables* tables, int32_t n_seqs, const int32_t* n_tokens,
+                         int32_t max_tokens, const int32_t* page_table,
+                         int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                         uint8_t* codes, int32_t* status, void* stream);
+
+/*
+ * Attention logits of queries against packed keys, q . k_hat / sqrt(d), through the same
+ * lookup tables as decode.  Replaces compute_attention_metrics' candidate logits
+ * (experiments/stage1/toolkit/eval.py:21) with GQA grouping as in repeat_kv_states
+ * (experiments/stage1/toolkit/metric_transform.py:21-27).
+ *   q       [n_seqs][n_q_heads][n_queries][d] of q_dtype, contiguous
+ *   scores  float [n_seqs][n_q_heads][n_queries][max_tokens]; entries beyond seq_lens[s] untouched
+ */
+int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q, int32_t q_dtype,
+                        int32_t n_seqs, int32_t n_q_heads, int32_t n_queries,
+                        const int32_t* seq_lens, int32_t max_tokens, const int32_t* page_table,
+                        int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                        float* scores, int32_t* status, void* stream);
+
+/*
+ * Bytes of zero-initialised workspace jqk_decode_attend needs.  The caller zeroes it once;
+ * the kernel leaves its counters at zero when it finishes, so the same buffer can be passed
+ * to the next call on the same stream without clearing.
+ */
+size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
+                                  int32_t max_splits);
+
+/*
+ * One decode step of attention over packed keys and bf16 values for one layer:
+ * out = softmax(q . k_hat / sqrt(d)) @ V.  In the reference this is stock attention over the
+ * reconstructed cache (jointqk_press.py:306-307 swaps it in); the scores follow eval.py:20-21.
+ *   q                bf16 [n_seqs][n_q_heads][d]
+ *   seq_lens         int32 [n_seqs] context length per sequence (0 allowed: output zeros)
+ *   max_seq_len      largest seq_lens[] value (host)
+ *   tokens_per_split keys handled by one thread block (multiple of 32; 0 = choose)
+ *   out              [n_seqs][n_q_heads][d] of out_dtype (JQK_DTYPE_F32 or JQK_DTYPE_BF16)
+ *   workspace        from jqk_decode_workspace_bytes with max_splits >= ceil(max_seq_len/tokens_per_split)
+ */
+int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
+                          int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                          int32_t tokens_per_split, const int32_t* page_table,
+                          int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                          const void* v_pool, void* out, int32_t out_dtype, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream);
+
+/* tokens_per_split that jqk_decode_attend would choose for this shape (host helper). */
+int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
+                                 int32_t max_seq_len);
+
+/*
+ * Calibration moments: accumulates (+=) the per-kv-head sums over tokens
+ *   sq_sum  += sum_g sum_t q_g q_g^T      (pooled over the q heads of the group)
+ *   sk_sum  += sum_t k k^T
+ *   cqk_sum += sum_t mean_g(q_g) k^T
+ * for one layer.  Replaces the einsums of compute_moments_from_tensors
+ * (experiments/stage1/calibration/compute_stats.py:118-123) and of the streaming
+ * accumulators (experiments/stage1/toolkit/moments.py:68,110).
+ *   q  [n_q_heads][n_tokens][d], k [n_kv_heads][n_tokens][d] of dtype (bf16, f16 or f32); tokens are
+ *      d elements apart, heads q_head_stride / k_head_stride elements apart
+ *   sq_sum, sk_sum, cqk_sum  float [n_kv_heads][d][d]; any of them may be NULL to skip it
+ *   workspace / workspace_bytes: scratch from jqk_moments_workspace_bytes (may be 0 bytes)
+ */
+int32_t jqk_moments_accumulate(const void* q, const void* k, int32_t dtype, int64_t n_tokens,
+                               int64_t q_head_stride, int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
+                               float* sk_sum, float* cqk_sum, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+size_t jqk_moments_workspace_bytes(int64_t n_tokens, int32_t n_q_heads, int32_t n_kv_heads,
+                                   int32_t d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JOINTQK_B200_H_ */

@@ -1,0 +1,28 @@
+// Library-wide entry points: version, error text, table validation.
+#include <string.h>
+
+#include "jqk_common.cuh"
+
+namespace jqk {
+
+char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int32_t check_tables(const jqk_head_tables* t) {
+  if (!t) return fail(JQK_E_ARG, "null head tables");
+  if (t->n_heads <= 0 || t->n_heads > 1024) return fail(JQK_E_ARG, "n_heads %d out of range", t->n_heads);
+  if (t->d <= 0 || t->d > JQK_MAX_DIM || t->d % 16) return fail(JQK_E_UNSUPPORTED, "head_dim %d must be a multiple of 16 and at most %d", t->d, JQK_MAX_DIM);
+  if (t->words_per_record <= 0 || t->words_per_record > JQK_MAX_WORDS) return fail(JQK_E_LAYOUT, "words_per_record %d outside 1..%d", t->words_per_record, JQK_MAX_WORDS);
+  if (!t->desc || !t->col_meta || !t->table_fields || !t->fwd_cols || !t->thresholds || !t->cb_cols ||
+      !t->qproj_cols || !t->inv_rows)
+    return fail(JQK_E_ARG, "head tables hold a null pointer");
+  return 0;
+}
+
+}  // namespace jqk
+
+extern "C" int32_t jqk_version(void) { return (0 << 16) | 1; }
+
+extern "C" const char* jqk_last_error(void) { return jqk::error_buffer(); }

@@ -1,0 +1,134 @@
+"""Device tables of one layer's kv heads: what the kernels read besides keys, values and pages.
+
+Built on the host from the same three tensors the reference's batched path consumes --
+``forward_maps (H,d,d)``, ``inverse_maps (H,d,d)`` and ``codebooks (H,d,K)`` with ``+inf`` in
+unused slots (``stack_per_head``, experiments/stage1/toolkit/per_coord_quantization.py:219-233)
+-- and uploaded once.  The per-coordinate bit width is read off the codebook row length.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _native
+from .layout import MAX_TABLES, KeyLayout, decision_thresholds, plan_key_layout
+
+DESC_INTS = 32
+MAX_COLS = 128
+
+
+def split_bf16_limbs(x: torch.Tensor, n_limbs: int = 3) -> torch.Tensor:
+    """Split fp32 ``x`` into ``n_limbs`` bf16 tensors whose sum reproduces ``x`` to ~2^-24.
+
+    Each limb is the round-to-nearest bf16 of the residual left by the previous limbs, so
+    bf16 x bf16 products against bf16 keys are exact in fp32 and only the accumulation order
+    differs from a plain fp32 dot product."""
+    res = x.float().clone()
+    limbs = []
+    for _ in range(n_limbs):
+        l = res.to(torch.bfloat16)
+        limbs.append(l)
+        res = res - l.float()
+    return torch.stack(limbs, 0)
+
+
+class HeadTables:
+    """Stacked tables for ``H`` heads; owns the device tensors and the ctypes struct."""
+
+    def __init__(self, forward_maps: torch.Tensor | None, inverse_maps: torch.Tensor | None,
+                 codebooks: torch.Tensor, device: torch.device | str = "cuda") -> None:
+        cb = codebooks.detach().float().cpu()
+        if cb.dim() != 3:
+            raise ValueError("codebooks must be (H, d, K)")
+        H, d, K = cb.shape
+        eye = torch.eye(d).expand(H, d, d)
+        fwd = eye if forward_maps is None else forward_maps.detach().float().cpu()
+        inv = fwd.transpose(-1, -2) if inverse_maps is None else inverse_maps.detach().float().cpu()
+        if tuple(fwd.shape) != (H, d, d) or tuple(inv.shape) != (H, d, d):
+            raise ValueError(f"maps must be (H, d, d) = ({H}, {d}, {d})")
+        lengths = torch.isfinite(cb).sum(-1)                       # (H, d)
+        if not bool(((lengths & (lengths - 1)) == 0).all()) or int(lengths.min()) < 1:
+            raise ValueError("each codebook row must hold a power-of-two number of finite levels")
+        if int(lengths.max()) > 16:
+            raise ValueError(
+                f"the packed GPU path stores at most 4 bits per coordinate; a codebook row has "
+                f"{int(lengths.max())} levels")
+        bits = torch.log2(lengths.float()).round().long()
+        zero_rows = cb[..., 0][bits == 0]
+        if zero_rows.numel() and float(zero_rows.abs().max()) != 0.0:
+            raise ValueError("a 0-bit coordinate must reconstruct to 0.0")
+
+        self.n_heads, self.d = H, d
+        self.bits = bits.clone()
+        self.layouts: list[KeyLayout] = [plan_key_layout(bits[h].numpy()) for h in range(H)]
+        self.words_per_record = max(l.n_words for l in self.layouts)
+
+        desc = np.zeros((H, DESC_INTS), np.int32)
+        col_meta = np.zeros((H, MAX_COLS), np.int32)
+        col_meta[:] = 255 << 16
+        fields = np.full((H, MAX_TABLES, 4), -1, np.int32)
+        fwd_cols = np.zeros((H, d, MAX_COLS), np.float32)
+        qproj = np.zeros((H, d, MAX_COLS), np.float32)
+        inv_rows = np.zeros((H, MAX_COLS, d), np.float32)
+        thr = np.full((H, MAX_COLS, 16), np.inf, np.float32)
+        cb_cols = np.zeros((H, MAX_COLS, 16), np.float32)
+        cb_np, fwd_np, inv_np = cb.numpy(), fwd.numpy(), inv.numpy()
+        for h, lay in enumerate(self.layouts):
+            desc[h, :8] = lay.descriptor()
+            desc[h, 8:8 + lay.n_words + 1] = lay.word_col_begin
+            n = lay.n_active
+            coords = lay.col_coord[:n]
+            col_meta[h, :n] = lay.col_width[:n] | (lay.col_bitpos[:n] << 4) | (coords << 16)
+            if lay.n_tables:
+                fields[h, :lay.n_tables] = lay.table_fields
+            fwd_cols[h, :, :n] = fwd_np[h][:, coords]
+            qproj[h, :, :n] = inv_np[h][coords, :].T
+            inv_rows[h, :n, :] = inv_np[h][coords, :]
+            rows = np.zeros((n, 16), np.float32)
+            kk = min(K, 16)
+            rows[:, :kk] = np.where(np.isfinite(cb_np[h][coords, :kk]), cb_np[h][coords, :kk], 0.0)
+            cb_cols[h, :n] = rows
+            thr[h, :n, :15] = decision_thresholds(rows, lay.col_width[:n])
+        self.device = torch.device(device)
+        up = lambda a: torch.from_numpy(a).to(self.device)
+        self.desc, self.col_meta, self.table_fields = up(desc), up(col_meta), up(fields)
+        self.fwd_cols, self.qproj_cols, self.inv_rows = up(fwd_cols), up(qproj), up(inv_rows)
+        self.thresholds, self.cb_cols = up(thr), up(cb_cols)
+        # three bf16 limbs of the forward map, [H][3][col][dim] (column-major = K-major B operand)
+        self.fwd_limbs = split_bf16_limbs(torch.from_numpy(fwd_cols).transpose(1, 2).contiguous(), 3) \
+            .permute(1, 0, 2, 3).contiguous().to(self.device)
+        self.struct = _native.JqkHeadTables(
+            n_heads=H, d=d, words_per_record=self.words_per_record, reserved=0,
+            desc=self.desc.data_ptr(), col_meta=self.col_meta.data_ptr(),
+            table_fields=self.table_fields.data_ptr(), fwd_cols=self.fwd_cols.data_ptr(),
+            thresholds=self.thresholds.data_ptr(), cb_cols=self.cb_cols.data_ptr(),
+            qproj_cols=self.qproj_cols.data_ptr(), inv_rows=self.inv_rows.data_ptr(),
+            fwd_limbs=self.fwd_limbs.data_ptr())
+
+    @property
+    def ref(self):
+        return C.byref(self.struct)
+
+    @property
+    def record_bytes(self) -> int:
+        return 4 * self.words_per_record
+
+    @property
+    def payload_bytes_per_key(self) -> float:
+        """Algorithmic code bytes per key and head (sum of bits / 8, averaged over heads)."""
+        return float(np.mean([l.payload_bits for l in self.layouts])) / 8.0
+
+    @classmethod
+    def from_compressors(cls, comps, device="cuda") -> "HeadTables":
+        d = comps[0].d
+        k_max = max(int(c.codebooks_padded.shape[1]) for c in comps)
+        cb = torch.full((len(comps), d, k_max), float("inf"))
+        for h, c in enumerate(comps):
+            cb[h, :, : c.codebooks_padded.shape[1]] = c.codebooks_padded.detach().float().cpu()
+        eye = torch.eye(d)
+        fwd = torch.stack([(c.forward_map if c.forward_map is not None else eye).detach().float().cpu() for c in comps])
+        inv = torch.stack([(c.inverse_map if c.inverse_map is not None else eye).detach().float().cpu() for c in comps])
+        return cls(fwd, inv, cb, device=device)
