@@ -1,0 +1,486 @@
+#!/usr/bin/env python
+"""Benchmark of the compress-then-attend key path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline (one JSON line on stdout): compressed-K decode tokens/s on the single-layer decode
+config -- GQA 32 q / 8 kv heads, head_dim 128, batch 1 per GPU, context 32768, keys packed at
+2.0 bits/coordinate in 16-token pages, bf16 V -- with the HBM roofline of the decode kernel,
+the same metric end to end from host buffers (``e2e``), and the reference algorithm's torch
+CPU path timed on this box (``cpu_baseline``).  ``extra`` carries the other two stages of the
+path on their named shapes: prefill compression (keys/s) and calibration moments
+(token-layers/s), each with its own roofline fraction.
+
+With N > 1 (torchrun, one rank per GPU) every rank serves its own sequence of the same shape
+(the path shards by sequence with no collective on decode); the time is the max over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CTX = 32768
+N_Q_HEADS, N_KV_HEADS, HEAD_DIM = 32, 8, 128
+B_AVG = 2.0
+L2_BYTES = 126 * 2 ** 20
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks() -> tuple[float, float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return float(j["hbm_gbs"]), float(j.get("bf16_tflops_sustained", j.get("bf16_tflops", FALLBACK_BF16_TFLOPS))), "measured"
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks sampling through NVML (read-only)
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[tuple[float, int, int]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [x for x in visible.split(",") if x.strip() != ""]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self) -> None:
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                self.samples.append((time.perf_counter(), mhz, rs))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self) -> None:
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> None:
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(1.0)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-5:]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        mhz = sorted(s[1] for s in inside)
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        reasons = [n for b, n in self.REASONS.items() if bits & b and n != "gpu_idle"]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(inside)}
+
+
+# ----------------------------------------------------------------------------------------------
+# workload: decode, one layer, context 32768, 2.0 bits
+# ----------------------------------------------------------------------------------------------
+def build_decode_workload(device, rank: int, n_copies: int):
+    """Fit the 8 heads on a 4096-key sample of the config's key distribution, compress the full
+    context through the product's own prefill path and build ``n_copies`` distinct caches so
+    that consecutive steps never find their pages in L2."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    keys = torch.stack([spectrum_keys(CTX, config_seed(1, 0, h) + 100 * rank, device=device) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), B_AVG)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(config_seed(1, 0, 0) + 7 + rank)
+    caches = []
+    for c in range(n_copies):
+        cache = paged.PagedKVCache(tables, [CTX])
+        v = torch.randn(1, N_KV_HEADS, CTX, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+        cache.prefill(keys.roll(c * 17, 1).unsqueeze(0), v)
+        caches.append(cache)
+    q = torch.randn(1, N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    paged.check_status(caches[0].status)
+    return tables, comps, caches, q, keys
+
+
+def decode_algorithmic_bytes(tables) -> dict:
+    k_bytes = CTX * N_KV_HEADS * tables.payload_bytes_per_key
+    v_bytes = CTX * N_KV_HEADS * HEAD_DIM * 2
+    basis = N_KV_HEADS * HEAD_DIM * HEAD_DIM * 4
+    small = N_KV_HEADS * 128 * 16 * 4 + N_Q_HEADS * HEAD_DIM * (2 + 4)
+    return {"k_codes": k_bytes, "v": v_bytes, "basis": basis, "tables_q_out": small,
+            "total": k_bytes + v_bytes + basis + small}
+
+
+def timed_loop(fn, steps: int, warmup: int, device, world: int):
+    """W untimed steps, barrier + synchronize, K steps between two CUDA events on the current
+    stream, synchronize + barrier; returns (max-over-ranks ms, host t0, host t1)."""
+    import torch.distributed as dist
+
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    t1 = time.perf_counter()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, t0, t1
+
+
+def prewarm(fn, device, seconds: float = 0.25) -> None:
+    """Untimed spin-up so that the SM clock has left idle before the W warm-up steps."""
+    end = time.perf_counter() + seconds
+    i = 0
+    while time.perf_counter() < end:
+        for _ in range(50):
+            fn(i)
+            i += 1
+        torch.cuda.synchronize(device)
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU side: the reference algorithm's torch path for one decode step (oracle port)
+# ----------------------------------------------------------------------------------------------
+def cpu_decode_setup(comps, keys_cpu: torch.Tensor, ctx: int):
+    """Reconstructed keys (the reference keeps dequantised floats in its cache), V and q on the host."""
+    from oracle import reference_port as orc
+
+    k_hat = torch.stack([orc.roundtrip(keys_cpu[h, :ctx], comps[h].codebooks_padded, comps[h].forward_map,
+                                       comps[h].inverse_map)[0] for h in range(N_KV_HEADS)]).unsqueeze(0)
+    g = torch.Generator().manual_seed(99)
+    v = torch.randn(1, N_KV_HEADS, ctx, HEAD_DIM, generator=g).to(torch.bfloat16)
+    q = torch.randn(1, N_Q_HEADS, HEAD_DIM, generator=g).to(torch.bfloat16)
+    return k_hat, v, q
+
+
+def cpu_decode_steps_per_s(comps, keys_cpu, budget_s: float, steps: int | None = None, warmup: int = 1):
+    """Times ``orc.decode_attention`` (fp32 matmul / softmax / @V on reconstructed keys).  A step is
+    the full context when it fits the time budget, otherwise a leading slice of the context whose
+    time is scaled linearly to the full context (the work is linear in context length)."""
+    from oracle import reference_port as orc
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ctx = CTX
+    k_hat, v, q = cpu_decode_setup(comps, keys_cpu, ctx)
+    t = time.perf_counter()
+    orc.decode_attention(q, k_hat, v)
+    t_full = time.perf_counter() - t
+    n = steps if steps is not None else max(3, min(50, int(budget_s / max(t_full, 1e-6))))
+    if (n + warmup) * t_full > budget_s:
+        ctx = max(1024, int(CTX * budget_s / ((n + warmup) * t_full)) // 16 * 16)
+        k_hat, v = k_hat[:, :, :ctx].contiguous(), v[:, :, :ctx].contiguous()
+    for _ in range(warmup):
+        orc.decode_attention(q, k_hat, v)
+    t = time.perf_counter()
+    for _ in range(n):
+        orc.decode_attention(q, k_hat, v)
+    dt = (time.perf_counter() - t) / n
+    per_full_step = dt * (CTX / ctx)
+    sample = f"{n} decode steps over {ctx} of {CTX} context keys, 32 q / 8 kv heads, fp32 matmul+softmax+@V on reconstructed keys"
+    if ctx != CTX:
+        sample += ", time scaled linearly to the full context"
+    return 1.0 / per_full_step, per_full_step * 1e3, cores, sample
+
+
+def run_reference_arm(args, rank: int, world: int) -> None:
+    """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    keys = torch.stack([spectrum_keys(CTX, config_seed(1, 0, h)) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096], B_AVG)
+    value, ms, cores, sample = cpu_decode_steps_per_s(comps, keys, budget_s=150.0, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+METRIC = "compressed-K decode tokens/s"
+UNIT = "tokens/s (one decode step of one layer per sequence)"
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {
+        "workload": "decode, 1 layer, Llama-3.1-8B attention shape: 32 q / 8 kv heads, head_dim 128, "
+                    "batch 1 per GPU, context 32768, K packed at 2.0 bits/coord in 16-token pages, V bf16",
+        "context": CTX, "n_q_heads": N_Q_HEADS, "n_kv_heads": N_KV_HEADS, "head_dim": HEAD_DIM, "bits_per_coord": B_AVG,
+        "sequences": n_gpus, "sharding": "by sequence, one per GPU, no collective",
+        "l2_policy": "inputs rotate over 8 distinct caches (608 MB > 126 MB L2), so every step reads HBM",
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+# secondary stages on their named shapes (reported under "extra")
+# ----------------------------------------------------------------------------------------------
+def bench_compress(device, hbm_gbs: float, peak_kind: str) -> dict:
+    """Prefill compression, Qwen3-8B-shaped slice: 8 kv heads x 131072 bf16 keys of one layer and
+    one sequence (268 MB in, > L2), 2.5 bits/coord, 8 outlier channels x20."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    T = 131072
+    keys = torch.stack([spectrum_keys(T, config_seed(4, 0, h), 8, 20.0, device=device, dtype=torch.bfloat16)
+                        for h in range(N_KV_HEADS)]).unsqueeze(0)
+    comps, _ = fit_sigma_k_heads(keys[0, :, :4096].float().cpu(), 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    page_table, used = paged.sequential_page_table([T], device)
+    k_pool = paged.alloc_k_pool(tables, used)
+    n_tok = torch.tensor([T], dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    run = lambda: paged.compress_into(tables, keys, n_tok, T, page_table, k_pool, status)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / reps
+    n_keys = T * N_KV_HEADS
+    bytes_per_key = HEAD_DIM * 2 + tables.payload_bytes_per_key
+    gbs = n_keys * bytes_per_key / (ms * 1e-3) / 1e9
+    return {"metric": "keys compressed/s", "value": n_keys / (ms * 1e-3), "ms_per_launch": ms,
+            "workload": "1 layer x 8 kv heads x 131072 bf16 keys, 2.5 bits/coord, 16-token pages",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
+                         "bytes_per_key": bytes_per_key, "peak_kind": peak_kind}}
+
+
+def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict:
+    """Calibration moments: one layer, 32 q / 8 kv heads, 131072 bf16 tokens per launch (1.3 GB in)."""
+    from jointqk_b200.moments import KeyPathMoments
+    from jointqk_b200.synthetic import config_seed, correlated_qk
+
+    T = 131072
+    q, k = correlated_qk(T, N_Q_HEADS, N_KV_HEADS, config_seed(3, 0, 0), device=device)
+    acc = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    run = lambda: acc.update(0, q, k)
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / reps
+    bytes_per_tl = (N_Q_HEADS + N_KV_HEADS) * HEAD_DIM * 2
+    flop_per_tl = (N_Q_HEADS + 2 * N_KV_HEADS) * 2 * HEAD_DIM * HEAD_DIM
+    gbs = T * bytes_per_tl / (ms * 1e-3) / 1e9
+    tf = T * flop_per_tl / (ms * 1e-3) / 1e12
+    return {"metric": "calibration token-layers/s", "value": T / (ms * 1e-3), "ms_per_launch": ms,
+            "workload": "1 layer, 32 q / 8 kv heads, 131072 bf16 tokens, head_dim 128",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
+                         "tensor_tflops": tf, "tensor_frac": tf / tflops, "peak_kind": peak_kind}}
+
+
+# ----------------------------------------------------------------------------------------------
+# main arm
+# ----------------------------------------------------------------------------------------------
+def run_ours(args, rank: int, local_rank: int, world: int) -> None:
+    import torch.distributed as dist
+    from jointqk_b200 import paged
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU implementation")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    hbm_gbs, tflops, peak_kind = measured_peaks()
+    n_copies = 8
+    tables, comps, caches, q, keys = build_decode_workload(device, rank, n_copies)
+    tps = paged.default_split(1, N_Q_HEADS, N_KV_HEADS, CTX)
+    max_splits = -(-CTX // tps)
+    ws = paged.DecodeWorkspace(1, N_Q_HEADS, N_KV_HEADS, max_splits, device)
+    out = torch.empty((1, N_Q_HEADS, HEAD_DIM), dtype=torch.float32, device=device)
+
+    def step(i: int) -> None:
+        c = caches[i % n_copies]
+        paged.decode_attend(tables, q, c.seq_lens, CTX, c.page_table, c.k_pool, c.v_pool, out, ws, c.status, tps)
+
+    # Launch-bound loop: capture n_copies consecutive steps in a CUDA graph and replay it.
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for i in range(n_copies):
+            step(i)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(n_copies):
+                step(i)
+    torch.cuda.synchronize(device)
+    full, rest = divmod(args.steps, n_copies)
+
+    def replay(_i: int) -> None:
+        graph.replay()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    prewarm(replay, device)
+    # W warm-up steps and exactly K timed steps (graph replays of 8 steps plus single launches)
+    def run_steps(n: int, base: int) -> None:
+        f, r = divmod(n, n_copies)
+        for _ in range(f):
+            graph.replay()
+        for i in range(r):
+            step(base + i)
+
+    run_steps(args.warmup, 0)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    run_steps(args.steps, 0)
+    e1.record()
+    torch.cuda.synchronize(device)
+    t1 = time.perf_counter()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sampler.stop()
+    clocks = sampler.summary(t0, t1)
+    paged.check_status(caches[0].status)
+
+    # end to end through the public call with host buffers: H2D of the query, decode, D2H of the result
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty((1, N_Q_HEADS, HEAD_DIM), dtype=torch.float32).pin_memory()
+    q_dev = torch.empty_like(q)
+    e2e_steps = max(20, min(args.steps, 500))
+
+    def e2e_step(i: int) -> None:
+        c = caches[i % n_copies]
+        q_dev.copy_(q_host, non_blocking=True)
+        paged.decode_attend(tables, q_dev, c.seq_lens, CTX, c.page_table, c.k_pool, c.v_pool, out, ws, c.status, tps)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()      # the next token depends on this result
+
+    e2e_ms, _, _ = timed_loop(e2e_step, e2e_steps, max(3, args.warmup), device, world)
+
+    alg = decode_algorithmic_bytes(tables)
+    per_launch_ms = ms / args.steps
+    achieved = alg["total"] / (per_launch_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_launch_ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes, fp32 accumulate",
+        "data": "synthetic", "config": workload_config(world), "clocks": clocks,
+        "e2e": {"value": world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 4,
+                "steps": e2e_steps, "note": "pinned-host query in, result out, stream synchronised every step"},
+        "gpu_launches": args.steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "decode_kernel",
+                     "algorithmic_bytes_per_launch": alg, "tokens_per_split": tps},
+    }
+    if world == 1 and not args.no_extra:
+        del caches[1:]
+        torch.cuda.empty_cache()
+        line["extra"] = {"prefill_compress": bench_compress(device, hbm_gbs, peak_kind),
+                         "calibration_moments": bench_moments(device, hbm_gbs, tflops, peak_kind)}
+    if rank == 0:
+        if world == 1 and not args.no_cpu:
+            v, cms, cores, sample = cpu_decode_steps_per_s(comps, keys.cpu(), budget_s=20.0)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                    "ms_per_step": cms}
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the compress / moments stages")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        if args.steps > 200:
+            args.steps = 200
+        run_reference_arm(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, local_rank, world)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -36,6 +36,20 @@ inline int32_t cuda_fail(cudaError_t e, const char* what) {
     if (e__ != cudaSuccess) return ::jqk::cuda_fail(e__, what); \
   } while (0)
 
+// Raises a kernel's dynamic shared-memory limit the first time it is launched on each device
+// (a plain attribute call, kept out of the steady-state path and of stream captures).
+#define JQK_SMEM_ONCE(kernel, bytes, what)                                                   \
+  do {                                                                                       \
+    static bool done__[64] = {false};                                                        \
+    int dev__ = 0;                                                                           \
+    JQK_CUDA_OK(cudaGetDevice(&dev__), "cudaGetDevice");                                     \
+    if (dev__ < 0 || dev__ >= 64 || !done__[dev__]) {                                        \
+      JQK_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                       (int)(bytes)), what);                                 \
+      if (dev__ >= 0 && dev__ < 64) done__[dev__] = true;                                    \
+    }                                                                                        \
+  } while (0)
+
 // Validates the table struct against the limits the kernels are written for.
 int32_t check_tables(const jqk_head_tables* t);
 

@@ -270,8 +270,7 @@ extern "C" int32_t jqk_compress_paged(const jqk_head_tables* tables, const void*
   cudaStream_t st = (cudaStream_t)stream;
 #define JQK_LAUNCH_COMPRESS(KT)                                                                        \
   do {                                                                                                 \
-    JQK_CUDA_OK(cudaFuncSetAttribute(compress_simt_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                     (int)kTileSmem), "compress smem attribute");                       \
+    JQK_SMEM_ONCE(compress_simt_kernel<KT>, kTileSmem, "compress smem attribute");                      \
     compress_simt_kernel<KT><<<grid, 256, kTileSmem, st>>>(*tables, (const KT*)keys, seq_stride,        \
                                                            head_stride, token_stride, pa, k_pool);     \
   } while (0)
@@ -295,8 +294,7 @@ extern "C" int32_t jqk_decompress_paged(const jqk_head_tables* tables, int32_t n
   if (!out) return fail(JQK_E_ARG, "null out");
   dim3 grid((max_tokens + TILE_T - 1) / TILE_T, tables->n_heads, n_seqs);
   PagedArgs pa{n_tokens, nullptr, page_table, page_table_stride, n_pages, max_tokens, status};
-  JQK_CUDA_OK(cudaFuncSetAttribute(decompress_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)kTileSmem), "decompress smem attribute");
+  JQK_SMEM_ONCE(decompress_simt_kernel, kTileSmem, "decompress smem attribute");
   decompress_simt_kernel<<<grid, 256, kTileSmem, (cudaStream_t)stream>>>(*tables, pa, k_pool, out);
   JQK_CUDA_OK(cudaGetLastError(), "decompress launch");
   return 0;

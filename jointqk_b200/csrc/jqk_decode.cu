@@ -468,8 +468,7 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q,
   if (page_table_stride <= 0 || n_pages <= 0) return fail(JQK_E_ARG, "page_table_stride and n_pages must be positive");
   dim3 grid((max_tokens + SCORE_CHUNK - 1) / SCORE_CHUNK, tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads),
             n_seqs * n_queries);
-  JQK_CUDA_OK(cudaFuncSetAttribute(score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ScoreSmem)),
-              "score smem attribute");
+  JQK_SMEM_ONCE(score_kernel, sizeof(ScoreSmem), "score smem attribute");
   score_kernel<<<grid, DEC_THREADS, sizeof(ScoreSmem), (cudaStream_t)stream>>>(
       *tables, q, q_dtype, n_q_heads, n_queries, seq_lens, max_tokens, page_table, page_table_stride, n_pages,
       k_pool, scores, status);
@@ -511,8 +510,7 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
     ws.part_acc = (float*)p;
   }
   dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
-  JQK_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DecodeSmem)),
-              "decode smem attribute");
+  JQK_SMEM_ONCE(decode_kernel, sizeof(DecodeSmem), "decode smem attribute");
   decode_kernel<<<grid, DEC_THREADS, sizeof(DecodeSmem), (cudaStream_t)stream>>>(
       *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
       n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);

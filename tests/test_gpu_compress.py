@@ -1,0 +1,161 @@
+"""GPU parity of prefill compression / reconstruction against the oracle and the reference
+fixtures.  Codes: bit-exact except on coordinates within rounding of a decision boundary
+(mismatch rate <= 1e-5).  Reconstruction: max-abs < 1e-5 * scale on rows whose codes agree."""
+
+import numpy as np
+import pytest
+import torch
+
+import jointqk_b200 as jq
+from jointqk_b200 import paged
+from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+from gpu_util import code_mismatch, oracle_codes_and_recon
+
+pytestmark = pytest.mark.gpu
+MAX_RATE = 1e-5
+
+
+def _t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def _golden_comp(g, which):
+    if which == "a":
+        R = _t(g["R_sym"])
+        return jq.PerCoordCompressor(_t(g["bits_cap4"]), _t(g["ref_stds"]), R, R.T)
+    R = _t(g["basis_b"])
+    return jq.PerCoordCompressor(_t(g["bits_b"]), _t(g["stds_b"]), R, R.T)
+
+
+@pytest.mark.parametrize("which,codes_name,rt_name,dtype", [
+    ("a", "ref_codes_cap4", "ref_roundtrip_cap4", torch.float32),
+    ("a", "ref_codes_cap4_bf16", "ref_roundtrip_cap4_bf16", torch.bfloat16),
+    ("b", "ref_codes_b", "ref_roundtrip_b", torch.float32)])
+def test_codes_and_roundtrip_against_reference_fixture(golden, which, codes_name, rt_name, dtype):
+    g = golden("compressor")
+    comp = _golden_comp(g, which)
+    keys = _t(g["keys"]).to(dtype).cuda()
+    codes = comp.codes(keys)
+    bad, _ = code_mismatch(codes, _t(g[codes_name]))
+    assert bad <= 1, f"{bad} code mismatches on 32768 coordinates"
+    out = comp.roundtrip(keys)
+    assert out.dtype == torch.float32 and out.shape == keys.shape and out.is_cuda
+    ref = _t(g[rt_name])
+    row_ok = (codes.cpu() == _t(g[codes_name])).all(-1)
+    err = (out.cpu() - ref)[row_ok].abs().max().item()
+    assert err < 1e-5 * max(1.0, ref.abs().max().item()), err
+
+
+def test_roundtrip_accepts_cpu_tensors_and_leading_dims(golden):
+    g = golden("compressor")
+    comp = _golden_comp(g, "b")
+    keys = _t(g["keys"]).view(2, 4, 32, 128)
+    out = comp.roundtrip(keys)
+    assert out.device.type == "cpu" and out.shape == keys.shape
+    ref = _t(g["ref_roundtrip_b"]).view(2, 4, 32, 128)
+    assert ((out - ref).abs().amax(-1) > 1e-4).sum() <= 1
+
+
+def test_batched_roundtrip_against_reference_fixture(golden):
+    g = golden("compressor")
+    ca, cb = _golden_comp(g, "a"), _golden_comp(g, "b")
+    fwd, inv, cbs = jq.stack_per_head([ca, cb])
+    keys = _t(g["keys"])
+    kb = torch.stack([keys, keys.flip(0)], 0).unsqueeze(0).cuda()
+    out = jq.batched_roundtrip(kb, fwd, inv, cbs)
+    assert out.shape == kb.shape and out.dtype == kb.dtype
+    ref = _t(g["ref_batched_roundtrip"])
+    assert ((out.cpu() - ref).abs().amax(-1) > 1e-4).sum() <= 2
+    out16 = jq.batched_roundtrip(kb.to(torch.bfloat16), fwd, inv, cbs)
+    assert out16.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("b_avg,dtype,n_out,scale", [(2.0, torch.float32, 4, 15.0), (3.0, torch.float32, 4, 15.0),
+                                                      (2.5, torch.bfloat16, 8, 20.0)])
+def test_parity_config_codes(b_avg, dtype, n_out, scale):
+    """8 heads x 4096 keys of the parity config: codes vs the oracle, mismatch rate reported."""
+    H, N = 8, 4096
+    keys = torch.stack([spectrum_keys(N, config_seed(0, 0, h), n_out, scale) for h in range(H)]).to(dtype)
+    comps, _ = fit_sigma_k_heads(keys.float(), b_avg)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    assert tables.record_bytes == int(b_avg * 16)
+    packed = paged.compress(tables, keys.cuda().unsqueeze(0))
+    codes = paged.unpack_codes(packed)[0].cpu()
+    recon = paged.decompress(packed)[0].cpu()
+    paged.check_status(packed.status)
+    total_bad = 0
+    for h in range(H):
+        ref_codes, ref_out = oracle_codes_and_recon(comps[h], keys[h])
+        bad, _ = code_mismatch(codes[h], ref_codes)
+        total_bad += bad
+        ok = (codes[h].long() == ref_codes).all(-1)
+        err = (recon[h] - ref_out)[ok].abs().max().item()
+        assert err < 1e-5 * max(1.0, ref_out.abs().max().item())
+        assert int(codes[h].max()) <= 15 and (codes[h][:, comps[h].bits_int == 0] == 0).all()
+    rate = total_bad / (H * N * 128)
+    print(f"code mismatch rate b_avg={b_avg} {dtype}: {total_bad}/{H * N * 128} = {rate:.2e}")
+    assert rate <= MAX_RATE
+
+
+def test_ragged_empty_and_append_equivalence():
+    H, d = 2, 128
+    keys = torch.stack([spectrum_keys(300, config_seed(0, 1, h)) for h in range(H)])
+    comps, _ = fit_sigma_k_heads(keys, 3.0)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    kb = torch.stack([keys, keys.flip(1), keys * 0.5]).cuda()                 # 3 sequences
+    lens = [300, 37, 0]
+    packed = paged.compress(tables, kb, lens)
+    codes = paged.unpack_codes(packed).cpu()
+    one = paged.unpack_codes(paged.compress(tables, kb[:1])).cpu()
+    assert torch.equal(codes[0], one[0])
+    two = paged.unpack_codes(paged.compress(tables, kb[1:2, :, :37])).cpu()
+    assert torch.equal(codes[1, :, :37], two[0])
+    assert int(codes[1, :, 37:].abs().sum()) == 0 and int(codes[2].abs().sum()) == 0
+    # empty batch and empty sequences do not launch and do not fail
+    empty = paged.compress(tables, kb[:1, :, :0])
+    assert paged.decompress(empty).shape == (1, H, 0, d)
+    # appending 23 then 277 keys (mid-page boundary) equals one shot of 300
+    cache = paged.PagedKVCache(tables, [300])
+    v = torch.zeros(1, H, 300, d, device="cuda", dtype=torch.bfloat16)
+    cache.prefill(kb[:1, :, :23], v[:, :, :23])
+    cache.prefill(kb[:1, :, 23:], v[:, :, 23:])
+    n_pages_used = packed.page_table[0, : paged.pages_for(300)]
+    assert torch.equal(cache.k_pool[: paged.pages_for(300)], packed.k_pool[n_pages_used.long()])
+    paged.check_status(cache.status)
+
+
+def test_bad_page_index_sets_status_and_is_skipped():
+    keys = spectrum_keys(64, config_seed(0, 2, 0))[None]
+    comps, _ = fit_sigma_k_heads(keys, 2.0)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    packed = paged.compress(tables, keys.cuda().unsqueeze(0))
+    packed.page_table[0, 1] = 10_000                       # outside the pool
+    paged.decompress(packed)
+    with pytest.raises(RuntimeError, match="outside the pool"):
+        paged.check_status(packed.status)
+
+
+def test_small_head_dim_and_identity_map():
+    d = 64
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(100, d, generator=g) * torch.linspace(3, 0.1, d)
+    bits = torch.tensor([4] * 8 + [3] * 12 + [2] * 20 + [1] * 12 + [0] * 12)
+    comp = jq.PerCoordCompressor(bits, torch.linspace(3, 0.1, d))          # no maps: identity
+    from oracle import reference_port as orc
+    ref, ref_codes = orc.roundtrip(x, comp.codebooks_padded, None, None)
+    assert torch.equal(comp.codes(x).long(), ref_codes)
+    assert torch.allclose(comp.roundtrip(x), ref, atol=1e-6)
+
+
+def test_idempotence_at_scale():
+    """Full-size property: re-compressing the reconstruction reproduces the codes."""
+    H, N = 8, 32768
+    keys = torch.stack([spectrum_keys(N, config_seed(4, 0, h), 8, 20.0, device="cuda") for h in range(H)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    p1 = paged.compress(tables, keys.to(torch.bfloat16).unsqueeze(0))
+    c1 = paged.unpack_codes(p1)
+    p2 = paged.compress(tables, paged.decompress(p1))
+    c2 = paged.unpack_codes(p2)
+    rate = float((c1 != c2).float().mean())
+    assert rate <= MAX_RATE, rate

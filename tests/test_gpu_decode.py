@@ -1,0 +1,153 @@
+"""GPU parity of lookup-table scoring and paged decode attention against the oracle.
+
+Scores are compared against the oracle's logits on the reconstruction of the *same codes*
+(so a boundary flip in compression is not counted twice), within 2e-3 by the metric
+max_i |s_i - ref_i| / max(|ref_i|, rms_row(ref)).  Top-1 retention on the parity config's
+queries must equal the oracle's."""
+
+import math
+
+import pytest
+import torch
+
+import jointqk_b200 as jq
+from jointqk_b200 import paged
+from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, retrieval_queries, spectrum_keys
+from gpu_util import recon_from_codes, score_rel_error
+from oracle import reference_port as orc
+
+pytestmark = pytest.mark.gpu
+SCORE_TOL = 2e-3
+OUT_TOL = 2e-3      # attention output, relative to max |out| of the row
+
+
+def _setup(H, N, b_avg, cfg_layer=0, dtype=torch.float32):
+    keys = torch.stack([spectrum_keys(N, config_seed(0, cfg_layer, h)) for h in range(H)]).to(dtype)
+    comps, sig = fit_sigma_k_heads(keys.float(), b_avg)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    return keys, comps, sig, tables
+
+
+def _k_hat_from_packed(packed, comps):
+    codes = paged.unpack_codes(packed).cpu()                      # (S, H, T, d)
+    return torch.stack([torch.stack([recon_from_codes(comps[h], codes[s, h]) for h in range(len(comps))])
+                        for s in range(codes.shape[0])])
+
+
+@pytest.mark.parametrize("b_avg", [2.0, 3.0])
+def test_parity_config_scores_and_top1(b_avg):
+    H, N, NQ = 8, 4096, 256
+    keys, comps, sig, tables = _setup(H, N, b_avg)
+    packed = paged.compress(tables, keys.cuda().unsqueeze(0))
+    q = torch.stack([retrieval_queries(keys[h], sig[h], NQ, config_seed(0, 0, h) + 7)[0] for h in range(H)])
+    qq = q.unsqueeze(0)                                            # (1, H, NQ, d): one q head per kv head
+    s = paged.score(packed, qq.cuda()).cpu()
+    k_hat = _k_hat_from_packed(packed, comps)
+    ref = orc.logits(qq, k_hat)
+    err = score_rel_error(s, ref)
+    print(f"score rel error b_avg={b_avg}: {err:.2e}")
+    assert err < SCORE_TOL
+    # retention: argmax over compressed scores vs argmax over exact scores, GPU vs oracle
+    real = orc.logits(qq, keys.unsqueeze(0))
+    ret_gpu = (s.argmax(-1) == real.argmax(-1)).float().mean().item()
+    ret_ref = orc.attention_metrics(qq, keys.unsqueeze(0), k_hat)["top1_match"]
+    print(f"top-1 retention b_avg={b_avg}: gpu {ret_gpu:.4f} oracle {ret_ref:.4f}")
+    assert torch.equal(s.argmax(-1), ref.argmax(-1))
+    assert ret_gpu == ret_ref
+    m = jq.compute_attention_metrics(qq, keys.unsqueeze(0), packed)
+    assert m["top1_match"] == ret_ref
+
+
+@pytest.mark.parametrize("hq,hkv,dtype", [(8, 2, torch.bfloat16), (2, 2, torch.float32), (16, 2, torch.bfloat16)])
+def test_scores_gqa_groups(hq, hkv, dtype):
+    keys, comps, _, tables = _setup(hkv, 777, 2.0, cfg_layer=3)
+    kb = torch.stack([keys, keys.flip(1)]).cuda()
+    packed = paged.compress(tables, kb, [777, 130])
+    g = torch.Generator().manual_seed(hq)
+    q = torch.randn(2, hq, 3, 128, generator=g).to(dtype)
+    s = paged.score(packed, q.cuda()).cpu()
+    k_hat = _k_hat_from_packed(packed, comps)
+    ref = orc.logits(q.float(), k_hat)
+    assert score_rel_error(s[0], ref[0]) < SCORE_TOL
+    assert score_rel_error(s[1, :, :, :130], ref[1, :, :, :130]) < SCORE_TOL
+    assert float(s[1, :, :, 130:].abs().max()) == 0.0
+
+
+def _decode_case(lens, hq, hkv, b_avg, tokens_per_split=0, out_dtype=torch.float32, shuffle_pages=False):
+    N = max(max(lens), 1)
+    keys, comps, _, tables = _setup(hkv, N, b_avg, cfg_layer=5)
+    S = len(lens)
+    kb = torch.stack([keys.roll(7 * s, 1) for s in range(S)]).cuda()
+    g = torch.Generator().manual_seed(1234 + S)
+    v = torch.randn(S, hkv, N, 128, generator=g).to(torch.bfloat16)
+    q = torch.randn(S, hq, 128, generator=g).to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, [max(n, 1) for n in lens])
+    if shuffle_pages:
+        perm = torch.randperm(cache.n_pages, generator=g).to(torch.int32).cuda()
+        cache.page_table = perm[cache.page_table.long()]
+    cache.prefill(kb, v.cuda(), lens)
+    out = cache.decode(q.cuda(), out_dtype=out_dtype, tokens_per_split=tokens_per_split).float().cpu()
+    paged.check_status(cache.status)
+    packed = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(lens), cache.status)
+    k_hat = _k_hat_from_packed(packed, comps)
+    ref = torch.zeros(S, hq, 128)
+    for s, n in enumerate(lens):
+        if n:
+            ref[s] = orc.decode_attention(q[s:s + 1], k_hat[s:s + 1, :, :n], v[s:s + 1, :, :n])[0]
+    return out, ref
+
+
+@pytest.mark.parametrize("lens,hq,hkv,b_avg,tps", [
+    ([1000, 37, 1, 16], 8, 2, 2.0, 0),
+    ([4096], 32, 8, 2.0, 0),
+    ([4096], 32, 8, 2.0, 256),
+    ([513, 0, 2048], 8, 2, 3.0, 512),
+    ([300, 299], 2, 2, 2.5, 0),
+    ([700], 16, 2, 3.0, 256)])
+def test_decode_matches_oracle(lens, hq, hkv, b_avg, tps):
+    out, ref = _decode_case(lens, hq, hkv, b_avg, tps)
+    scale = ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)
+    err = ((out - ref).abs() / scale).max().item()
+    print(f"decode lens={lens} hq={hq} hkv={hkv} bits={b_avg} tps={tps}: max rel err {err:.2e}")
+    assert err < OUT_TOL
+    for s, n in enumerate(lens):
+        if n == 0:
+            assert float(out[s].abs().max()) == 0.0
+
+
+def test_decode_bf16_output_and_page_permutation_invariance():
+    a, ref = _decode_case([1500, 640], 8, 2, 2.0, 0, out_dtype=torch.bfloat16)
+    b, _ = _decode_case([1500, 640], 8, 2, 2.0, 0, out_dtype=torch.float32, shuffle_pages=True)
+    scale = ref.abs().amax(-1, keepdim=True)
+    assert ((a - ref).abs() / scale).max().item() < 1e-2          # bf16 rounding of the output
+    assert ((b - ref).abs() / scale).max().item() < OUT_TOL
+
+
+def test_decode_split_invariance_at_context_32768():
+    """Full-context property: the result does not depend on how the keys are split over blocks."""
+    H, N = 8, 32768
+    keys = torch.stack([spectrum_keys(N, config_seed(1, 0, h), device="cuda") for h in range(H)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), 2.0)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    v = torch.randn(1, H, N, 128, generator=g, device="cuda").to(torch.bfloat16)
+    q = torch.randn(1, 32, 128, generator=g, device="cuda").to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, [N])
+    cache.prefill(keys.unsqueeze(0), v)
+    outs = [cache.decode(q, tokens_per_split=t) for t in (0, 1024, 4096, 32768)]
+    for o in outs[1:]:
+        assert ((o - outs[0]).abs().max() / outs[0].abs().max()).item() < 1e-4
+    # repeated calls reuse the workspace (counters return to zero)
+    again = cache.decode(q)
+    assert torch.equal(again, outs[0])
+
+
+def test_decode_rejects_bad_arguments():
+    keys, comps, _, tables = _setup(2, 64, 2.0)
+    cache = paged.PagedKVCache(tables, [64])
+    with pytest.raises(ValueError):
+        cache.decode(torch.zeros(1, 3, 128, dtype=torch.bfloat16, device="cuda"))     # 3 q heads over 2 kv heads
+    with pytest.raises(ValueError):
+        cache.decode(torch.zeros(1, 4, 128, dtype=torch.float32, device="cuda"))      # q must be bf16
+    with pytest.raises(ValueError):
+        cache.decode(torch.zeros(1, 4, 128, dtype=torch.bfloat16, device="cuda"), tokens_per_split=100)

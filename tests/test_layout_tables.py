@@ -1,0 +1,134 @@
+"""Record layout, decision thresholds and device tables, checked on the CPU through a NumPy
+model of the kernels' index arithmetic (tests/kernel_model.py) against the oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from jointqk_b200.layout import decision_thresholds, plan_key_layout
+from jointqk_b200.tables import HeadTables, split_bf16_limbs
+from oracle import reference_port as orc
+
+import kernel_model as km
+
+HISTS = [[14, 40, 26, 28, 20], [0, 0, 47, 34, 47], [0, 27, 42, 27, 32], [23, 27, 28, 27, 23],
+         [0, 15, 28, 27, 58], [0, 0, 0, 128, 0], [0, 0, 0, 0, 128], [128, 0, 0, 0, 0], [100, 1, 0, 27, 0],
+         [0, 128, 0, 0, 0], [3, 2, 1, 121, 1]]
+
+
+def _bits(hist, seed=0):
+    b = np.concatenate([np.full(n, w) for w, n in enumerate(hist)])
+    np.random.default_rng(seed).shuffle(b)
+    return b
+
+
+@pytest.mark.parametrize("hist", HISTS)
+def test_layout_invariants(hist):
+    bits = _bits(hist)
+    lay = plan_key_layout(bits)
+    n = lay.n_active
+    assert n == int((bits > 0).sum()) and lay.n_cols % 16 == 0 and lay.n_cols >= max(n, 16)
+    assert sorted(lay.col_coord[:n].tolist()) == np.nonzero(bits > 0)[0].tolist()
+    assert np.array_equal(lay.col_width[:n], bits[lay.col_coord[:n]])
+    # fields never overlap and never straddle a 32-bit word
+    used = np.zeros(32 * lay.n_words, bool)
+    for c in range(n):
+        p, w = int(lay.col_bitpos[c]), int(lay.col_width[c])
+        assert p // 32 == (p + w - 1) // 32
+        assert not used[p:p + w].any()
+        used[p:p + w] = True
+    assert used.sum() == lay.payload_bits
+    assert lay.n_words <= 16 and lay.n_tables <= 208
+    # every column is referenced by exactly one table field
+    refs = [int(f) & 255 for f in lay.table_fields.reshape(-1) if f >= 0]
+    assert sorted(refs) == list(range(n))
+
+
+def test_layout_packs_named_configs_without_waste():
+    for hist, nbytes in (([14, 40, 26, 28, 20], 32), ([0, 27, 42, 27, 32], 40), ([0, 0, 47, 34, 47], 48)):
+        lay = plan_key_layout(_bits(hist))
+        assert lay.record_bytes == nbytes and lay.waste_bits == 0
+
+
+def test_layout_rejects_unsupported():
+    with pytest.raises(ValueError):
+        plan_key_layout(np.full(128, 5))
+    with pytest.raises(ValueError):
+        plan_key_layout(np.full(100, 2))
+
+
+def test_decision_thresholds_reproduce_argmin():
+    from jointqk_b200.codebooks import unit_gaussian_centroids
+
+    rng = np.random.default_rng(1)
+    widths = np.array([1, 2, 3, 4, 4, 2])
+    stds = np.array([1.0, 0.37, 15.2, 1e-3, 3.3, 0.011], np.float32)
+    cb = np.zeros((6, 16), np.float32)
+    for i, w in enumerate(widths):
+        cb[i, : 2 ** w] = unit_gaussian_centroids(int(w)).numpy() * np.float32(stds[i])
+    thr = decision_thresholds(cb, widths)
+    for i, w in enumerate(widths):
+        lv = cb[i, : 2 ** w]
+        xs = [rng.normal(size=50000).astype(np.float32) * stds[i] * 1.5]
+        for t in thr[i, : 2 ** w - 1]:
+            xs.append(np.array([np.nextafter(t, -np.inf), t, np.nextafter(t, np.inf)], np.float32))
+        # |x| stays below 2^20 level gaps: beyond ~2^24 gaps the fp32 distances to several levels
+        # round to the same value and torch's first-index tie rule takes over (documented limit)
+        xs.append(np.array([0.0, -0.0, -1e30, 1e4 * stds[i], -1e4 * stds[i], lv[0], lv[-1]], np.float32))
+        x = np.concatenate(xs)
+        ref = np.abs(x[:, None] - lv[None, :]).argmin(-1)
+        mine = (x[:, None] >= thr[i][None, :]).sum(-1)
+        assert np.array_equal(ref, mine)
+
+
+def test_bf16_limbs_reconstruct_fp32():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(64, 64, generator=g)
+    limbs = split_bf16_limbs(x, 3)
+    err = (limbs.float().sum(0) - x).abs().max().item()
+    assert err <= 2.0 ** -22 * x.abs().max().item()
+
+
+def _tables_from_golden(g):
+    R, Rb = torch.from_numpy(g["R_sym"]), torch.from_numpy(g["basis_b"])
+    fwd, inv = torch.stack([R, Rb]), torch.stack([R.T, Rb.T])
+    cb = torch.stack([torch.from_numpy(g["ref_codebooks_cap4"]), torch.from_numpy(g["ref_codebooks_b"])])
+    return HeadTables(fwd, inv, cb, device="cpu")
+
+
+def test_kernel_model_codes_match_reference(golden):
+    g = golden("compressor")
+    tab = _tables_from_golden(g)
+    keys = g["keys"]
+    for h, name in ((0, "ref_codes_cap4"), (1, "ref_codes_b")):
+        rec = km.compress_model(tab, h, keys)
+        codes = km.unpack_model(tab, h, rec)
+        mism = int((codes != g[name]).sum())
+        assert mism <= 1, mism              # summation order may flip a code on a decision boundary
+        lay = tab.layouts[h]
+        ref_rec = orc.pack_records(g[name], lay.col_coord, lay.col_width, lay.col_bitpos, lay.n_words)
+        assert (rec != ref_rec).sum() <= 1
+
+
+def test_kernel_model_scores_match_reference(golden):
+    g = golden("compressor")
+    tab = _tables_from_golden(g)
+    rng = np.random.default_rng(3)
+    for h, codes_name, rt_name in ((0, "ref_codes_cap4", "ref_roundtrip_cap4"), (1, "ref_codes_b", "ref_roundtrip_b")):
+        lay = tab.layouts[h]
+        rec = orc.pack_records(g[codes_name], lay.col_coord, lay.col_width, lay.col_bitpos, lay.n_words)
+        q = rng.normal(size=(4, 128)).astype(np.float32)
+        s = km.score_model(tab, h, rec, q)
+        ref = (q @ g[rt_name].T) / np.sqrt(128.0)
+        rms = np.sqrt((ref ** 2).mean(-1, keepdims=True))
+        rel = np.abs(s - ref) / np.maximum(np.abs(ref), rms)
+        assert rel.max() < 2e-3, rel.max()
+        assert rel.max() < 1e-3           # the fixed-point tables stay well inside the bar
+        assert np.array_equal(s.argmax(-1), ref.argmax(-1))
+
+
+def test_head_tables_reject_wide_codebooks():
+    cb = torch.full((1, 16, 32), float("inf"))
+    cb[0, :, :32] = torch.arange(32.0)
+    with pytest.raises(ValueError, match="4 bits"):
+        HeadTables(None, None, cb, device="cpu")
