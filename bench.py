@@ -348,7 +348,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     hbm_gbs, tflops, peak_kind = measured_peaks()
     n_copies = 8
     tables, comps, caches, q, keys = build_decode_workload(device, rank, n_copies)
-    tps = paged.default_split(1, N_Q_HEADS, N_KV_HEADS, CTX)
+    tps = args.tokens_per_split or paged.default_split(1, N_Q_HEADS, N_KV_HEADS, CTX)
     max_splits = -(-CTX // tps)
     ws = paged.DecodeWorkspace(1, N_Q_HEADS, N_KV_HEADS, max_splits, device)
     out = torch.empty((1, N_Q_HEADS, HEAD_DIM), dtype=torch.float32, device=device)
@@ -371,16 +371,20 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     full, rest = divmod(args.steps, n_copies)
 
     def replay(_i: int) -> None:
-        graph.replay()
+        if args.no_graph:
+            for i in range(n_copies):
+                step(i)
+        else:
+            graph.replay()
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    prewarm(replay, device)
+    prewarm(replay, device, 0.05 if args.no_graph else 0.25)
     # W warm-up steps and exactly K timed steps (graph replays of 8 steps plus single launches)
     def run_steps(n: int, base: int) -> None:
         f, r = divmod(n, n_copies)
         for _ in range(f):
-            graph.replay()
+            replay(0)
         for i in range(r):
             step(base + i)
 
@@ -458,6 +462,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the compress / moments stages")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
+    ap.add_argument("--tokens-per-split", type=int, default=0, help="override the decode split size (0 = library default)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -1,190 +1,40 @@
 // Scoring of packed keys through shared-memory lookup tables, and paged decode attention.
 //
-// Reference semantics: logits = q . k_hat / sqrt(d) with k_hat = x_hat @ inverse_map
-// (experiments/stage1/toolkit/eval.py:20-21, per_coord_quantization.py:158-164), GQA grouping
-// of metric_transform.py:21-27, then softmax and a product with V in fp32.
+// Reference semantics: logits = q . k_hat / sqrt(d) (experiments/stage1/toolkit/eval.py:20-21)
+// with the GQA grouping of metric_transform.py:21-27, then softmax and a product with V.  The
+// reference runs stock attention over a reconstructed fp16/bf16 cache
+// (experiments/stage1/toolkit/jointqk_press.py:306-307); here no key is ever dequantised.
 //
-// Because k_hat = x_hat @ inverse_map, q . k_hat = q' . x_hat with q' = inverse_map @ q.  The
-// query is projected once per thread block; each lookup (nibble slot or sub-byte field of a
-// record, see layout.py) owns a 16-entry table holding, for the <=4 query heads of the group,
-// the summed contribution q'_c * cb[c][code] of its coordinates.  Entries are 16-bit fixed
-// point with one fp32 scale per query head, 8 bytes per entry, 128 bytes per table, so a
-// warp-wide 8-byte read of one table never has a bank conflict.  No key is ever dequantised.
-#include <math_constants.h>
-
-#include "jqk_common.cuh"
+// Decode kernel, one thread block per (key split, kv head x q-head block, sequence):
+//   * prologue: project the <=4 queries of the group, build the lookup tables (jqk_tables.cuh);
+//   * each warp owns a contiguous run of 32-key tiles.  A lane scores one key: it loads the
+//     record words (word-major pages: coalesced), does one 8-byte table read per lookup and
+//     accumulates four integer sums;
+//   * online softmax per warp with shuffles (running max / sum per query head);
+//   * P.V on the tensor cores: out^T[dims x heads] += V^T[dims x keys] . P^T[keys x heads] with
+//     mma.sync m16n8k16 bf16 (four query heads do not fill a tcgen05 tile; the kernel is bound
+//     by HBM, not by the tensor pipe).  V goes from global memory straight into A fragments:
+//     a lane loads 16-byte pieces of four key rows and pairs keys with byte permutes, so V
+//     never touches shared memory.  P is split into two bf16 terms (hi + lo) to keep fp32-level
+//     weights;
+//   * pages of upcoming tiles are pulled into L2 with cp.async.bulk.prefetch.L2, which needs
+//     no registers or shared memory, so HBM latency is hidden independently of occupancy;
+//   * partial results of the splits are merged by the last block to finish (atomic ticket),
+//     no second launch.
+#include "jqk_tables.cuh"
 
 namespace jqk {
 
-constexpr int DEC_THREADS = 256;
+constexpr int DEC_THREADS = TBL_THREADS;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
-constexpr int TILE_TOK = 32;  // keys per warp step (two pages)
+constexpr int TILE_TOK = 32;        // keys per warp step (two pages)
+constexpr int PREFETCH_TILES = 4;   // how far ahead of the compute the L2 prefetch runs
 constexpr float kLog2e = 1.4426950408889634f;
 
-struct LutView {
-  const uint2* lut;  // [n_tables][16] (int16 x 4 heads)
-  int n_a_words, n_c_words, n_words;
-};
-
-// ---- shared memory carve-up ------------------------------------------------------------
-struct DecodeSmem {
-  uint2 lut[JQK_MAX_TABLES * 16];        // 26,624 B
-  float qraw[JQK_MAX_GROUP][JQK_MAX_DIM];  // 2 KB
-  float qproj[2][JQK_MAX_COLS][JQK_MAX_GROUP];  // two partial sums over halves of the dims
-  float scale[JQK_MAX_GROUP];
-  unsigned int absmax[JQK_MAX_GROUP];
-  float pbuf[DEC_WARPS][TILE_TOK][JQK_MAX_GROUP];
-  float wm[DEC_WARPS][JQK_MAX_GROUP];
-  float wl[DEC_WARPS][JQK_MAX_GROUP];
-  float wacc[DEC_WARPS][JQK_MAX_GROUP][JQK_MAX_DIM];
-  int is_last;
-};
-
-// One table entry in fp32 for the heads of the group.
-__device__ __forceinline__ void table_entry(const int32_t* __restrict__ fields, const float* __restrict__ cb,
-                                            const float (*qp)[JQK_MAX_GROUP], int e, float (&v)[JQK_MAX_GROUP]) {
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) v[h] = 0.f;
-#pragma unroll
-  for (int f = 0; f < 4; ++f) {
-    const int fld = fields[f];
-    if (fld < 0) break;
-    const int col = fld & 255, width = (fld >> 8) & 15, shift = (fld >> 12) & 15;
-    const float c = cb[col * 16 + ((e >> shift) & ((1 << width) - 1))];
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) v[h] = fmaf(qp[col][h], c, v[h]);
-  }
-}
-
-// Projects the group's queries into column space and fills the lookup tables.
-//   q_rows[h] : pointer to the d values of query head h of the group (h < n_group), q_dtype
-template <typename SM>
-__device__ void build_tables(SM& sm, const jqk_head_tables& tb, int head, const HeadDesc& hd,
-                             const void* q_base, int q_dtype, size_t q_head_stride, int n_group) {
-  const int tid = threadIdx.x;
-  const int d = hd.d;
-  for (int e = tid; e < JQK_MAX_GROUP * JQK_MAX_DIM; e += blockDim.x) {
-    const int h = e / JQK_MAX_DIM, i = e % JQK_MAX_DIM;
-    sm.qraw[h][i] = (h < n_group && i < d) ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
-  }
-  if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
-  __syncthreads();
-  {
-    // thread -> (column c, half of the dims); rows of qproj_cols are contiguous in c
-    const int c = tid & 127, half = tid >> 7;
-    const float* P = tb.qproj_cols + (size_t)head * d * 128;
-    float a[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
-    if (half < 2) {
-      const int i_lo = half * (d / 2), i_hi = i_lo + d / 2;
-#pragma unroll 8
-      for (int i = i_lo; i < i_hi; ++i) {
-        const float w = P[(size_t)i * 128 + c];
-#pragma unroll
-        for (int h = 0; h < JQK_MAX_GROUP; ++h) a[h] = fmaf(sm.qraw[h][i], w, a[h]);
-      }
-#pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) sm.qproj[half][c][h] = a[h];
-    }
-  }
-  __syncthreads();
-  if (tid < 128) {
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) sm.qproj[0][tid][h] += sm.qproj[1][tid][h];
-  }
-  __syncthreads();
-  const int32_t* fields = tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4;
-  const float* cb = tb.cb_cols + (size_t)head * 128 * 16;
-  const int n_entries = hd.n_tables * 16;
-  float mx[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
-  for (int e = tid; e < n_entries; e += blockDim.x) {
-    float v[JQK_MAX_GROUP];
-    table_entry(fields + (e >> 4) * 4, cb, sm.qproj[0], e & 15, v);
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) mx[h] = fmaxf(mx[h], fabsf(v[h]));
-  }
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-    const float m = warp_max(mx[h]);
-    if ((tid & 31) == 0) atomicMax(&sm.absmax[h], __float_as_uint(m));  // non-negative floats order as uints
-  }
-  __syncthreads();
-  if (tid < JQK_MAX_GROUP) {
-    const float m = __uint_as_float(sm.absmax[tid]);
-    sm.scale[tid] = (m > 0.f && m < CUDART_INF_F) ? m / 32767.f : 1.f;
-  }
-  __syncthreads();
-  float inv[JQK_MAX_GROUP];
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / sm.scale[h];
-  for (int e = tid; e < n_entries; e += blockDim.x) {
-    float v[JQK_MAX_GROUP];
-    table_entry(fields + (e >> 4) * 4, cb, sm.qproj[0], e & 15, v);
-    int q[JQK_MAX_GROUP];
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h])));
-    uint2 packed;
-    packed.x = (uint32_t)(q[0] & 0xffff) | ((uint32_t)q[1] << 16);
-    packed.y = (uint32_t)(q[2] & 0xffff) | ((uint32_t)q[3] << 16);
-    sm.lut[e] = packed;
-  }
-  __syncthreads();
-}
-
-__device__ __forceinline__ void add_entry(const uint2 e, int (&acc)[JQK_MAX_GROUP]) {
-  acc[0] += (int)(short)(e.x & 0xffffu);
-  acc[1] += ((int)e.x) >> 16;
-  acc[2] += (int)(short)(e.y & 0xffffu);
-  acc[3] += ((int)e.y) >> 16;
-}
-
-// Integer score sums of one record.  `kp` points at word 0 of the key's slot inside its page
-// (words are JQK_PAGE_TOKENS uint32 apart).
-__device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, const LutView& lv,
-                                             int (&acc)[JQK_MAX_GROUP]) {
-  uint32_t ra[JQK_MAX_WORDS], rc[JQK_MAX_WORDS];
-#pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    ra[w] = (w < lv.n_a_words) ? __ldg(kp + w * JQK_PAGE_TOKENS) : 0u;
-    rc[w] = (w < lv.n_c_words) ? __ldg(kp + (lv.n_words - 1 - w) * JQK_PAGE_TOKENS) : 0u;
-  }
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] = 0;
-#pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    if (w < lv.n_a_words) {
-      const uint32_t x = ra[w];
-#pragma unroll
-      for (int k = 0; k < 8; ++k) add_entry(lv.lut[(w * 8 + k) * 16 + ((x >> (4 * k)) & 15u)], acc);
-    }
-  }
-  const uint2* lc = lv.lut + lv.n_a_words * 8 * 16;
-#pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    if (w < lv.n_c_words) {
-      const uint32_t x = rc[w];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t y = x >> (8 * b);
-        add_entry(lc[((w * 12 + b * 3 + 0) * 16) + (y & 7u)], acc);
-        add_entry(lc[((w * 12 + b * 3 + 1) * 16) + ((y >> 3) & 7u)], acc);
-        add_entry(lc[((w * 12 + b * 3 + 2) * 16) + ((y >> 6) & 3u)], acc);
-      }
-    }
-  }
-}
-
 // ---------------------------------------------------------------------------------------
-// Score kernel (evaluation / parity): one block per (token chunk, kv head x q block, seq x query)
+// Score kernel (evaluation / parity): one block per (key chunk, kv head x q block, seq x query)
 // ---------------------------------------------------------------------------------------
 constexpr int SCORE_CHUNK = 2048;
-
-struct ScoreSmem {
-  uint2 lut[JQK_MAX_TABLES * 16];
-  float qraw[JQK_MAX_GROUP][JQK_MAX_DIM];
-  float qproj[2][JQK_MAX_COLS][JQK_MAX_GROUP];
-  float scale[JQK_MAX_GROUP];
-  unsigned int absmax[JQK_MAX_GROUP];
-};
 
 __global__ void __launch_bounds__(DEC_THREADS)
 score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_q_heads, int n_queries,
@@ -192,7 +42,7 @@ score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_
              int pt_stride, int n_pages, const uint32_t* __restrict__ k_pool, float* __restrict__ scores,
              int32_t* status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  ScoreSmem& sm = *reinterpret_cast<ScoreSmem*>(smem_raw);
+  TableSmem& sm = *reinterpret_cast<TableSmem*>(smem_raw);
   const int group = n_q_heads / tb.n_heads;
   const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
   const int head = blockIdx.y / q_blocks, qb = blockIdx.y % q_blocks;
@@ -208,7 +58,6 @@ score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_
   const size_t q_elem0 = (((size_t)seq * n_q_heads + qh0) * n_queries + qi) * d;
   const char* q_ptr = (const char*)q + q_elem0 * (q_dtype == JQK_DTYPE_F32 ? 4 : 2);
   build_tables(sm, tb, head, hd, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
-  LutView lv{sm.lut, hd.n_a_words, hd.n_c_words, hd.n_words};
   const float inv_sqrt_d = 1.0f / sqrtf((float)d);
   for (int tok = t_begin + threadIdx.x; tok < t_end; tok += blockDim.x) {
     const int page = lookup_page(page_table, pt_stride, seq, tok / JQK_PAGE_TOKENS, n_pages, status);
@@ -216,7 +65,7 @@ score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_
     const uint32_t* kp = k_pool + ((size_t)page * tb.n_heads + head) * tb.words_per_record * JQK_PAGE_TOKENS +
                          (tok % JQK_PAGE_TOKENS);
     int acc[JQK_MAX_GROUP];
-    score_record(kp, lv, acc);
+    score_record(kp, sm.lut, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
       if (h < n_group)
@@ -230,140 +79,251 @@ score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_
 // Decode attention
 // ---------------------------------------------------------------------------------------
 struct DecodeWs {
-  float* part_m;     // [n_seqs][n_q_heads][max_splits]
-  float* part_l;     // [n_seqs][n_q_heads][max_splits]
-  float* part_acc;   // [n_seqs][n_q_heads][max_splits][128]
+  float* part_m;           // [n_seqs][n_q_heads][max_splits]
+  float* part_l;           // [n_seqs][n_q_heads][max_splits]
+  float* part_acc;         // [n_seqs][n_q_heads][max_splits][128]
   unsigned int* counters;  // [n_seqs][n_kv_heads * q_blocks]
   int max_splits;
 };
+
+struct DecodeSmem {
+  TableSmem t;
+  __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
+  float wm[DEC_WARPS][JQK_MAX_GROUP];
+  float wl[DEC_WARPS][JQK_MAX_GROUP];
+  int is_last;
+};
+// t.part doubles as the per-warp output staging [DEC_WARPS][JQK_MAX_GROUP][128] after the prologue.
+static_assert(sizeof(float) * 8 * JQK_MAX_COLS * JQK_MAX_GROUP >= sizeof(float) * DEC_WARPS * JQK_MAX_GROUP * JQK_MAX_DIM,
+              "projection scratch too small to stage the warp outputs");
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == JQK_DTYPE_F32) ((float*)out)[idx] = v;
   else ((__nv_bfloat16*)out)[idx] = __float2bfloat16(v);
 }
 
-__global__ void __launch_bounds__(DEC_THREADS)
+__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 32 page ids of a warp's window, validated; -1 beyond the sequence or outside the pool.
+__device__ __forceinline__ int load_page_window(const int32_t* __restrict__ page_table, int pt_stride, int seq,
+                                                int first_lp, int n_seq_pages, int n_pages, int32_t* status) {
+  const int lp = first_lp + (threadIdx.x & 31);
+  if (lp >= n_seq_pages || lp >= pt_stride) return -1;
+  return lookup_page(page_table, pt_stride, seq, lp, n_pages, status);
+}
+
+// NCH = 16-byte pieces of a V row per lane: 2 for head_dim 128, 1 for head_dim 64.
+template <int NCH>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
               const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
               const uint32_t* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status) {
+  constexpr int D = 64 * NCH;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
   const int group = n_q_heads / tb.n_heads;
   const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
   const int head = blockIdx.y / q_blocks, qb = blockIdx.y % q_blocks;
   const int seq = blockIdx.z, split = blockIdx.x;
   const int len = seq_lens[seq];
   const int n_splits = (len + tokens_per_split - 1) / tokens_per_split;
-  const HeadDesc hd = load_desc(tb.desc, head);
-  const int d = hd.d;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
   const int qh0 = head * group + g0;
   if (len <= 0) {  // empty context: defined output (zeros), written by split 0
     if (split == 0)
-      for (int e = tid; e < n_group * d; e += blockDim.x)
-        store_out(out, out_dtype, ((size_t)seq * n_q_heads + qh0 + e / d) * d + e % d, 0.f);
+      for (int e = tid; e < n_group * D; e += DEC_THREADS)
+        store_out(out, out_dtype, ((size_t)seq * n_q_heads + qh0 + e / D) * D + e % D, 0.f);
     return;
   }
   if (split >= n_splits) return;
+  const HeadDesc hd = load_desc(tb.desc, head);
   const int t_begin = split * tokens_per_split;
   const int t_end = min(len, t_begin + tokens_per_split);
+  const int n_seq_pages = (len + JQK_PAGE_TOKENS - 1) / JQK_PAGE_TOKENS;
+  const int wpr = tb.words_per_record;
+  const size_t k_page_words = (size_t)tb.n_heads * wpr * JQK_PAGE_TOKENS;
+  const size_t v_page_elems = (size_t)tb.n_heads * JQK_PAGE_TOKENS * D;
+  const uint32_t* k_head = k_pool + (size_t)head * wpr * JQK_PAGE_TOKENS;
+  const __nv_bfloat16* v_head = v_pool + (size_t)head * JQK_PAGE_TOKENS * D;
 
-  build_tables(sm, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * d, JQK_DTYPE_BF16, (size_t)d, n_group);
-  LutView lv{sm.lut, hd.n_a_words, hd.n_c_words, hd.n_words};
+  // ---- this warp's run of tiles, its page ids, and the first prefetches (before the prologue) ----
+  const int tiles_total = (t_end - t_begin + TILE_TOK - 1) / TILE_TOK;
+  const int tiles_per_warp = (tiles_total + DEC_WARPS - 1) / DEC_WARPS;
+  const int tile_lo = min(tiles_total, warp * tiles_per_warp);
+  const int n_my = min(tiles_total, tile_lo + tiles_per_warp) - tile_lo;
+  const int lp0 = t_begin / JQK_PAGE_TOKENS + 2 * tile_lo;  // first logical page of this warp
+  int pg_cur = load_page_window(page_table, pt_stride, seq, lp0, n_seq_pages, n_pages, status);
+  int pg_next = load_page_window(page_table, pt_stride, seq, lp0 + 32, n_seq_pages, n_pages, status);
+  const uint32_t k_page_bytes = (uint32_t)hd.n_words * JQK_PAGE_TOKENS * 4;
+  {
+    const int n_pre = min(2 * PREFETCH_TILES, 2 * n_my);
+    if (lane < n_pre && pg_cur >= 0) {
+      prefetch_l2(v_head + (size_t)pg_cur * v_page_elems, JQK_PAGE_TOKENS * D * 2);
+      prefetch_l2(k_head + (size_t)pg_cur * k_page_words, k_page_bytes);
+    }
+  }
+
+  build_tables(sm.t, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
   float sc[JQK_MAX_GROUP];
   {
-    const float f = kLog2e / sqrtf((float)d);
+    const float f = kLog2e / sqrtf((float)D);
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.scale[h] * f;
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.scale[h] * f;
   }
+  const uint2* lut = sm.t.lut;
+  const int n_a_words = hd.n_a_words, n_c_words = hd.n_c_words, n_words = hd.n_words;
 
-  float m_run[JQK_MAX_GROUP], l_run[JQK_MAX_GROUP], o[JQK_MAX_GROUP][4];
+  float m_run[JQK_MAX_GROUP], l_run[JQK_MAX_GROUP];
 #pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-    m_run[h] = -CUDART_INF_F; l_run[h] = 0.f;
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) { m_run[h] = -CUDART_INF_F; l_run[h] = 0.f; }
+  float acc[NCH * 4][4];  // tile (piece ch, j): rows = dims ch*64 + 8g + 2j (+1), cols = heads 2c, 2c+1
 #pragma unroll
-    for (int k = 0; k < 4; ++k) o[h][k] = 0.f;
-  }
-  const size_t k_page_words = (size_t)tb.n_heads * tb.words_per_record * JQK_PAGE_TOKENS;
-  const size_t v_page_elems = (size_t)tb.n_heads * JQK_PAGE_TOKENS * d;
-  const bool lane_has_dims = 4 * lane < d;
+  for (int j = 0; j < NCH * 4; ++j)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
 
-  for (int t0 = t_begin + warp * TILE_TOK; t0 < t_end; t0 += DEC_WARPS * TILE_TOK) {
+  for (int r = 0; r < n_my; ++r) {
+    if (r > 0 && (r & 15) == 0) {
+      pg_cur = pg_next;
+      pg_next = load_page_window(page_table, pt_stride, seq, lp0 + 2 * r + 32, n_seq_pages, n_pages, status);
+    }
+    {  // L2 prefetch of the pages PREFETCH_TILES ahead: lanes 0 and 1 take one page each
+      const int rp = r + PREFETCH_TILES;
+      const int src = ((rp >> 4) == (r >> 4)) ? pg_cur : pg_next;
+      const int ppg = __shfl_sync(0xffffffffu, src, ((rp & 15) << 1) | (lane & 1));
+      if (lane < 2 && rp < n_my && ppg >= 0) {
+        prefetch_l2(v_head + (size_t)ppg * v_page_elems, JQK_PAGE_TOKENS * D * 2);
+        prefetch_l2(k_head + (size_t)ppg * k_page_words, k_page_bytes);
+      }
+    }
+    const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
+    const int page_lo = __shfl_sync(0xffffffffu, pg_cur, (r & 15) << 1);
+    const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
+
+    // ---- V rows for the two 16-key blocks of the tile, straight into registers ----
+    uint4 vr[2][4][NCH];  // [block][key 2c, 2c+1, 2c+8, 2c+9][piece]
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      const int pg = kb ? page_hi : page_lo;
+      const bool blk_ok = pg >= 0 && t0 + 16 * kb < t_end;
+      const __nv_bfloat16* vp = v_head + (size_t)(blk_ok ? pg : 0) * v_page_elems + 8 * g;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int slot = 2 * c + (s & 1) + 8 * (s >> 1);
+        const bool ok = blk_ok && t0 + 16 * kb + slot < t_end;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch)
+          vr[kb][s][ch] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + slot * D + 64 * ch)) : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+
+    // ---- score this lane's key ----
     const int tok = t0 + lane;
-    const bool valid = tok < t_end;
-    int page = -1;
-    if (valid) page = lookup_page(page_table, pt_stride, seq, tok / JQK_PAGE_TOKENS, n_pages, status);
+    const int my_page = (lane < 16) ? page_lo : page_hi;
     float s[JQK_MAX_GROUP];
-    if (page >= 0) {
-      const uint32_t* kp = k_pool + (size_t)page * k_page_words +
-                           (size_t)head * tb.words_per_record * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS);
-      int acc[JQK_MAX_GROUP];
-      score_record(kp, lv, acc);
+    if (tok < t_end && my_page >= 0) {
+      int ia[JQK_MAX_GROUP];
+      score_record(k_head + (size_t)my_page * k_page_words + (lane & 15), lut, n_a_words, n_c_words, n_words, ia);
 #pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = (float)acc[h] * sc[h];
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = (float)ia[h] * sc[h];
     } else {
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = -CUDART_INF_F;
     }
-    float p[JQK_MAX_GROUP];
-    bool any = false;
+
+    // ---- online softmax (warp-uniform maxima) ----
+    float alpha[JQK_MAX_GROUP];
+    bool any = false, grew = false;
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      const float tmax = warp_max(s[h]);
-      const float m_new = fmaxf(m_run[h], tmax);
-      if (m_new == -CUDART_INF_F) { p[h] = 0.f; continue; }
-      any = true;
-      const float alpha = exp2f(m_run[h] - m_new);  // exp2(-inf) = 0 on the first tile
-      p[h] = exp2f(s[h] - m_new);
-      l_run[h] = l_run[h] * alpha + warp_sum(p[h]);
+      const float m_new = fmaxf(m_run[h], warp_max(s[h]));
+      alpha[h] = 1.f;
+      float p = 0.f;
+      if (m_new > -CUDART_INF_F) {
+        any = true;
+        if (m_new > m_run[h]) { alpha[h] = exp2f(m_run[h] - m_new); grew = true; }
+        p = exp2f(s[h] - m_new);
+      }
+      const __nv_bfloat16 p_hi = __float2bfloat16(p);
+      const __nv_bfloat16 p_lo = __float2bfloat16(p - __bfloat162float(p_hi));
+      sm.pbuf[warp][0][h][lane] = p_hi;
+      sm.pbuf[warp][1][h][lane] = p_lo;
+      l_run[h] = l_run[h] * alpha[h] + warp_sum(__bfloat162float(p_hi) + __bfloat162float(p_lo));
       m_run[h] = m_new;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) o[h][k] *= alpha;
     }
-    if (!any) continue;  // warp-uniform: every lane sees the same maxima
-    *reinterpret_cast<float4*>(&sm.pbuf[warp][lane][0]) = make_float4(p[0], p[1], p[2], p[3]);
     __syncwarp();
-    const int page_lo = __shfl_sync(0xffffffffu, page, 0);
-    const int page_hi = __shfl_sync(0xffffffffu, page, 16);
-    const int n_here = min(TILE_TOK, t_end - t0);
-#pragma unroll 8
-    for (int t = 0; t < n_here; ++t) {
-      const int pg = (t < 16) ? page_lo : page_hi;
-      if (pg < 0) continue;
-      const float4 pw = *reinterpret_cast<const float4*>(&sm.pbuf[warp][t][0]);
-      if (lane_has_dims) {
-        const __nv_bfloat16* vp = v_pool + (size_t)pg * v_page_elems +
-                                  ((size_t)head * JQK_PAGE_TOKENS + (t & 15)) * d + 4 * lane;
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vp));
-        const float v0 = __uint_as_float(raw.x << 16), v1 = __uint_as_float(raw.x & 0xffff0000u);
-        const float v2 = __uint_as_float(raw.y << 16), v3 = __uint_as_float(raw.y & 0xffff0000u);
-        o[0][0] = fmaf(pw.x, v0, o[0][0]); o[0][1] = fmaf(pw.x, v1, o[0][1]);
-        o[0][2] = fmaf(pw.x, v2, o[0][2]); o[0][3] = fmaf(pw.x, v3, o[0][3]);
-        o[1][0] = fmaf(pw.y, v0, o[1][0]); o[1][1] = fmaf(pw.y, v1, o[1][1]);
-        o[1][2] = fmaf(pw.y, v2, o[1][2]); o[1][3] = fmaf(pw.y, v3, o[1][3]);
-        o[2][0] = fmaf(pw.z, v0, o[2][0]); o[2][1] = fmaf(pw.z, v1, o[2][1]);
-        o[2][2] = fmaf(pw.z, v2, o[2][2]); o[2][3] = fmaf(pw.z, v3, o[2][3]);
-        o[3][0] = fmaf(pw.w, v0, o[3][0]); o[3][1] = fmaf(pw.w, v1, o[3][1]);
-        o[3][2] = fmaf(pw.w, v2, o[3][2]); o[3][3] = fmaf(pw.w, v3, o[3][3]);
+    if (any) {
+      if (grew) {
+        const float a_even = (c & 1) ? alpha[2] : alpha[0];  // head 2c   (c >= 2: heads that do not exist)
+        const float a_odd = (c & 1) ? alpha[3] : alpha[1];   // head 2c+1
+#pragma unroll
+        for (int j = 0; j < NCH * 4; ++j) { acc[j][0] *= a_even; acc[j][1] *= a_odd; acc[j][2] *= a_even; acc[j][3] *= a_odd; }
+      }
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        if (t0 + 16 * kb >= t_end) break;
+        uint32_t b[2][2];  // [hi/lo][k half]
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const uint32_t* prow = reinterpret_cast<const uint32_t*>(&sm.pbuf[warp][t][g & 3][16 * kb]);
+          b[t][0] = (g < JQK_MAX_GROUP) ? prow[c] : 0u;
+          b[t][1] = (g < JQK_MAX_GROUP) ? prow[c + 4] : 0u;
+        }
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const uint32_t ra[4] = {vr[kb][0][ch].x, vr[kb][0][ch].y, vr[kb][0][ch].z, vr[kb][0][ch].w};
+          const uint32_t rb[4] = {vr[kb][1][ch].x, vr[kb][1][ch].y, vr[kb][1][ch].z, vr[kb][1][ch].w};
+          const uint32_t rc2[4] = {vr[kb][2][ch].x, vr[kb][2][ch].y, vr[kb][2][ch].z, vr[kb][2][ch].w};
+          const uint32_t rd[4] = {vr[kb][3][ch].x, vr[kb][3][ch].y, vr[kb][3][ch].z, vr[kb][3][ch].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t a0 = __byte_perm(ra[j], rb[j], 0x5410), a1 = __byte_perm(ra[j], rb[j], 0x7632);
+            const uint32_t a2 = __byte_perm(rc2[j], rd[j], 0x5410), a3 = __byte_perm(rc2[j], rd[j], 0x7632);
+            mma_bf16_16816(acc[ch * 4 + j], a0, a1, a2, a3, b[0][0], b[0][1]);
+            mma_bf16_16816(acc[ch * 4 + j], a0, a1, a2, a3, b[1][0], b[1][1]);
+          }
+        }
       }
     }
-    __syncwarp();
+    __syncwarp();  // pbuf is rewritten by the next tile
   }
 
-  // ---- combine the warps of this block -------------------------------------------------
+  // ---- combine the warps of this block (t.part is free after the prologue) ----------------
+  float* wacc = &sm.t.part[0][0][0];  // [DEC_WARPS][JQK_MAX_GROUP][128]
+  if (lane == 0) {
 #pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-    if (lane == 0) { sm.wm[warp][h] = m_run[h]; sm.wl[warp][h] = l_run[h]; }
-    if (lane_has_dims)
-      *reinterpret_cast<float4*>(&sm.wacc[warp][h][4 * lane]) = make_float4(o[h][0], o[h][1], o[h][2], o[h][3]);
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) { sm.wm[warp][h] = m_run[h]; sm.wl[warp][h] = l_run[h]; }
+  }
+  if (c < 2) {
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int dim = 64 * ch + 8 * g + 2 * j;
+        float* w0 = wacc + ((size_t)warp * JQK_MAX_GROUP + 2 * c) * JQK_MAX_DIM + dim;
+        float* w1 = w0 + JQK_MAX_DIM;
+        w0[0] = acc[ch * 4 + j][0]; w1[0] = acc[ch * 4 + j][1];
+        w0[1] = acc[ch * 4 + j][2]; w1[1] = acc[ch * 4 + j][3];
+      }
   }
   __syncthreads();
   const bool single = (n_splits == 1);
-  for (int e = tid; e < n_group * d; e += blockDim.x) {
-    const int h = e / d, i = e % d;
+  for (int e = tid; e < n_group * D; e += DEC_THREADS) {
+    const int h = e / D, i = e % D;
     float M = -CUDART_INF_F;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm.wm[w][h]);
@@ -373,12 +333,12 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       for (int w = 0; w < DEC_WARPS; ++w) {
         const float f = exp2f(sm.wm[w][h] - M);
         L += sm.wl[w][h] * f;
-        A += sm.wacc[w][h][i] * f;
+        A += wacc[((size_t)w * JQK_MAX_GROUP + h) * JQK_MAX_DIM + i] * f;
       }
     }
     const size_t qrow = (size_t)seq * n_q_heads + qh0 + h;
     if (single) {
-      store_out(out, out_dtype, qrow * d + i, L > 0.f ? A / L : 0.f);
+      store_out(out, out_dtype, qrow * D + i, L > 0.f ? A / L : 0.f);
     } else {
       const size_t pidx = qrow * ws.max_splits + split;
       ws.part_acc[pidx * JQK_MAX_DIM + i] = A;
@@ -387,7 +347,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   }
   if (single) return;
 
-  // ---- last block of this (sequence, head group) merges the splits -----------------------
+  // ---- the last block of this (sequence, head group) to finish merges the splits ------------
   __threadfence();
   __syncthreads();
   unsigned int* counter = ws.counters + (size_t)seq * gridDim.y + blockIdx.y;
@@ -398,8 +358,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   __syncthreads();
   if (!sm.is_last) return;
   __threadfence();
-  for (int e = tid; e < n_group * d; e += blockDim.x) {
-    const int h = e / d, i = e % d;
+  for (int e = tid; e < n_group * D; e += DEC_THREADS) {
+    const int h = e / D, i = e % D;
     const size_t qrow = (size_t)seq * n_q_heads + qh0 + h;
     const size_t p0 = qrow * ws.max_splits;
     float M = -CUDART_INF_F;
@@ -412,7 +372,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         A += __ldcg(ws.part_acc + (p0 + s2) * JQK_MAX_DIM + i) * f;
       }
     }
-    store_out(out, out_dtype, qrow * d + i, L > 0.f ? A / L : 0.f);
+    store_out(out, out_dtype, qrow * D + i, L > 0.f ? A / L : 0.f);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
 }
@@ -440,15 +400,15 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
 
 extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                             int32_t max_seq_len) {
-  if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return TILE_TOK * DEC_WARPS;
+  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level
+  if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return unit;
   const long long items = (long long)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
-  const long long target_blocks = 148LL * 2;  // two resident blocks per SM
+  const long long target_blocks = 148;  // one resident block per SM
   long long splits = target_blocks / items;
   if (splits < 1) splits = 1;
   long long tps = (max_seq_len + splits - 1) / splits;
-  if (items * 4 >= target_blocks && tps > 2048) tps = 2048;  // many sequences: fixed granularity
-  tps = (tps + TILE_TOK - 1) / TILE_TOK * TILE_TOK;
-  if (tps < TILE_TOK * DEC_WARPS) tps = TILE_TOK * DEC_WARPS;
+  if (items * 2 >= target_blocks && tps > 2048) tps = 2048;  // many sequences: fixed granularity
+  tps = (tps + unit - 1) / unit * unit;
   return (int32_t)tps;
 }
 
@@ -468,8 +428,8 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q,
   if (page_table_stride <= 0 || n_pages <= 0) return fail(JQK_E_ARG, "page_table_stride and n_pages must be positive");
   dim3 grid((max_tokens + SCORE_CHUNK - 1) / SCORE_CHUNK, tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads),
             n_seqs * n_queries);
-  JQK_SMEM_ONCE(score_kernel, sizeof(ScoreSmem), "score smem attribute");
-  score_kernel<<<grid, DEC_THREADS, sizeof(ScoreSmem), (cudaStream_t)stream>>>(
+  JQK_SMEM_ONCE(score_kernel, sizeof(TableSmem), "score smem attribute");
+  score_kernel<<<grid, DEC_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
       *tables, q, q_dtype, n_q_heads, n_queries, seq_lens, max_tokens, page_table, page_table_stride, n_pages,
       k_pool, scores, status);
   JQK_CUDA_OK(cudaGetLastError(), "score launch");
@@ -490,9 +450,10 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   if (n_q_heads <= 0 || n_q_heads % tables->n_heads) return fail(JQK_E_ARG, "n_q_heads %d is not a multiple of the %d kv heads", n_q_heads, tables->n_heads);
   if (out_dtype != JQK_DTYPE_F32 && out_dtype != JQK_DTYPE_BF16) return fail(JQK_E_ARG, "out dtype must be f32 or bf16");
   if (n_seqs > 65535) return fail(JQK_E_UNSUPPORTED, "n_seqs %d exceeds 65535", n_seqs);
-  if (tables->d % 4) return fail(JQK_E_UNSUPPORTED, "head_dim must be a multiple of 4");
+  if (tables->d != 128 && tables->d != 64) return fail(JQK_E_UNSUPPORTED, "decode attention is built for head_dim 64 and 128, got %d", tables->d);
   if (max_seq_len > 0 && (!page_table || !k_pool || !v_pool)) return fail(JQK_E_ARG, "null page_table, k_pool or v_pool");
   if (max_seq_len > 0 && (page_table_stride <= 0 || n_pages <= 0)) return fail(JQK_E_ARG, "page_table_stride and n_pages must be positive");
+  if (max_seq_len > 0 && ((uintptr_t)v_pool % 16 || (uintptr_t)k_pool % 16)) return fail(JQK_E_ARG, "k_pool and v_pool must be 16-byte aligned");
   if (tokens_per_split == 0) tokens_per_split = jqk_decode_default_split(n_seqs, n_q_heads, tables->n_heads, max_seq_len);
   if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
@@ -510,10 +471,18 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
     ws.part_acc = (float*)p;
   }
   dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
-  JQK_SMEM_ONCE(decode_kernel, sizeof(DecodeSmem), "decode smem attribute");
-  decode_kernel<<<grid, DEC_THREADS, sizeof(DecodeSmem), (cudaStream_t)stream>>>(
-      *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
-      n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tables->d == 128) {
+    JQK_SMEM_ONCE(decode_kernel<2>, sizeof(DecodeSmem), "decode smem attribute");
+    decode_kernel<2><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
+        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
+        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
+  } else {
+    JQK_SMEM_ONCE(decode_kernel<1>, sizeof(DecodeSmem), "decode smem attribute");
+    decode_kernel<1><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
+        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
+        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
+  }
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
   return 0;
 }

@@ -10,7 +10,7 @@
 namespace jqk {
 
 constexpr int MOM_TOK = 32;      // tokens staged per step
-constexpr int MOM_CHUNK = 4096;  // tokens per thread block
+constexpr int MOM_CHUNK = 512;   // tokens per thread block; short chunks keep the fp32 running sums accurate
 
 // One block: (token chunk, kv head, which matrix).  256 threads, each an 8x8 patch of the
 // d x d output (d <= 128); operands staged in shared memory as fp32.

@@ -1,0 +1,200 @@
+// Query projection and lookup-table construction shared by the score and decode kernels.
+//
+// q . k_hat = q' . x_hat with q' = inverse_map @ q (k_hat = x_hat @ inverse_map,
+// experiments/stage1/toolkit/per_coord_quantization.py:158-164).  Each lookup of a record owns a
+// 16-entry table with, for the <=4 query heads of the group, the summed contribution
+// q'_c * cb[c][code] of its coordinates.  Entries are 16-bit fixed point with one fp32 scale
+// per query head: 8 bytes per entry, 128 bytes per table, so a warp-wide 8-byte read of one
+// table never has a bank conflict.
+#pragma once
+
+#include <math_constants.h>
+
+#include "jqk_common.cuh"
+
+namespace jqk {
+
+constexpr int TBL_THREADS = 256;  // build_tables is written for exactly this block size
+
+struct TableSmem {
+  uint2 lut[JQK_MAX_TABLES * 16];                // 26,624 B: [table][16] x (int16 x 4 heads)
+  float part[8][JQK_MAX_COLS][JQK_MAX_GROUP];    // 16,384 B: projection partial sums
+  float qproj[JQK_MAX_COLS][JQK_MAX_GROUP];      //  2,048 B: projected queries, column space
+  float qraw[JQK_MAX_GROUP][JQK_MAX_DIM];        //  2,048 B
+  float cb[JQK_MAX_COLS * 16];                   //  8,192 B: staged codebooks
+  int32_t fields[JQK_MAX_TABLES * 4];            //  3,328 B: staged table composition
+  float scale[JQK_MAX_GROUP];
+  unsigned int absmax[JQK_MAX_GROUP];
+};
+
+// One table entry in fp32 for the heads of the group (all operands in shared memory).
+__device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&v)[JQK_MAX_GROUP]) {
+#pragma unroll
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) v[h] = 0.f;
+  const int32_t* fields = sm.fields + (e >> 4) * 4;
+  const int idx = e & 15;
+#pragma unroll
+  for (int f = 0; f < 4; ++f) {
+    const int fld = fields[f];
+    if (fld < 0) break;
+    const int col = fld & 255, width = (fld >> 8) & 15, shift = (fld >> 12) & 15;
+    const float c = sm.cb[col * 16 + ((idx >> shift) & ((1 << width) - 1))];
+    const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[col]);
+    v[0] = fmaf(qp.x, c, v[0]); v[1] = fmaf(qp.y, c, v[1]);
+    v[2] = fmaf(qp.z, c, v[2]); v[3] = fmaf(qp.w, c, v[3]);
+  }
+}
+
+// Projects the group's queries into column space and fills the lookup tables.
+//   q_base + h * q_head_stride : the d values of query head h of the group (h < n_group)
+// Every global read is issued before the first barrier so that one memory round trip covers
+// the projection matrix, the codebooks and the table composition.
+__device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_tables& tb, int head,
+                                             const HeadDesc& hd, const void* q_base, int q_dtype,
+                                             size_t q_head_stride, int n_group) {
+  const int tid = threadIdx.x;
+  const int d = hd.d;
+  const int cg = tid & 31, rg = tid >> 5;  // columns 4*cg..4*cg+3, rows rg + 8*r
+  const float4* P4 = reinterpret_cast<const float4*>(tb.qproj_cols + (size_t)head * d * 128);
+  float4 w[JQK_MAX_DIM / 8];
+#pragma unroll
+  for (int r = 0; r < JQK_MAX_DIM / 8; ++r) {
+    const int i = rg + 8 * r;
+    w[r] = (i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int e = tid; e < JQK_MAX_GROUP * JQK_MAX_DIM; e += TBL_THREADS) {
+    const int h = e / JQK_MAX_DIM, i = e % JQK_MAX_DIM;
+    sm.qraw[h][i] = (h < n_group && i < d) ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
+  }
+  {
+    const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
+    float4* dst = reinterpret_cast<float4*>(sm.cb);
+    for (int e = tid; e < hd.n_cols * 4; e += TBL_THREADS) dst[e] = __ldg(cb4 + e);
+    const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
+    int4* fdst = reinterpret_cast<int4*>(sm.fields);
+    for (int e = tid; e < hd.n_tables; e += TBL_THREADS) fdst[e] = __ldg(f4 + e);
+  }
+  if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
+  __syncthreads();
+  {
+    float a[4][JQK_MAX_GROUP];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) a[k][h] = 0.f;
+#pragma unroll
+    for (int r = 0; r < JQK_MAX_DIM / 8; ++r) {
+      const int i = rg + 8 * r;  // beyond d: w[r] is zero and qraw is zero
+      const float q0 = sm.qraw[0][i], q1 = sm.qraw[1][i], q2 = sm.qraw[2][i], q3 = sm.qraw[3][i];
+      const float wk[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        a[k][0] = fmaf(q0, wk[k], a[k][0]); a[k][1] = fmaf(q1, wk[k], a[k][1]);
+        a[k][2] = fmaf(q2, wk[k], a[k][2]); a[k][3] = fmaf(q3, wk[k], a[k][3]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      *reinterpret_cast<float4*>(sm.part[rg][4 * cg + k]) = make_float4(a[k][0], a[k][1], a[k][2], a[k][3]);
+  }
+  __syncthreads();
+  if (tid < JQK_MAX_COLS) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      const float4 p = *reinterpret_cast<const float4*>(sm.part[r][tid]);
+      s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+    }
+    *reinterpret_cast<float4*>(sm.qproj[tid]) = s;
+  }
+  __syncthreads();
+  const int n_entries = hd.n_tables * 16;
+  float mx[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
+  for (int e = tid; e < n_entries; e += TBL_THREADS) {
+    float v[JQK_MAX_GROUP];
+    table_entry(sm, e, v);
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) mx[h] = fmaxf(mx[h], fabsf(v[h]));
+  }
+#pragma unroll
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+    const float m = warp_max(mx[h]);
+    if ((tid & 31) == 0) atomicMax(&sm.absmax[h], __float_as_uint(m));  // non-negative floats order as uints
+  }
+  __syncthreads();
+  if (tid < JQK_MAX_GROUP) {
+    const float m = __uint_as_float(sm.absmax[tid]);
+    sm.scale[tid] = (m > 0.f && m < CUDART_INF_F) ? m / 32767.f : 1.f;
+  }
+  __syncthreads();
+  float inv[JQK_MAX_GROUP];
+#pragma unroll
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / sm.scale[h];
+  for (int e = tid; e < n_entries; e += TBL_THREADS) {
+    float v[JQK_MAX_GROUP];
+    table_entry(sm, e, v);
+    int q[JQK_MAX_GROUP];
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h])));
+    uint2 packed;
+    packed.x = (uint32_t)(q[0] & 0xffff) | ((uint32_t)q[1] << 16);
+    packed.y = (uint32_t)(q[2] & 0xffff) | ((uint32_t)q[3] << 16);
+    sm.lut[e] = packed;
+  }
+  __syncthreads();
+}
+
+// acc[h] += entry[h] for the four 16-bit lanes of one table entry (sign-extending dot products).
+__device__ __forceinline__ void add_entry(const uint2 e, int (&acc)[JQK_MAX_GROUP]) {
+  acc[0] = __dp2a_lo((int)e.x, 0x00000001, acc[0]);
+  acc[1] = __dp2a_lo((int)e.x, 0x00000100, acc[1]);
+  acc[2] = __dp2a_lo((int)e.y, 0x00000001, acc[2]);
+  acc[3] = __dp2a_lo((int)e.y, 0x00000100, acc[3]);
+}
+
+// Integer score sums of one record.  `kp` points at word 0 of the key's slot inside its page
+// (words are JQK_PAGE_TOKENS uint32 apart).  Nibble words are scanned from the start of the
+// record, (3,3,2)-byte words from its end; lookups that fall on the other region hit all-zero
+// tables.
+__device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, const uint2* __restrict__ lut,
+                                             int n_a_words, int n_c_words, int n_words,
+                                             int (&acc)[JQK_MAX_GROUP]) {
+  uint32_t ra[JQK_MAX_WORDS], rc[JQK_MAX_WORDS];
+#pragma unroll
+  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
+    ra[w] = (w < n_a_words) ? __ldg(kp + w * JQK_PAGE_TOKENS) : 0u;
+    rc[w] = (w < n_c_words) ? __ldg(kp + (n_words - 1 - w) * JQK_PAGE_TOKENS) : 0u;
+  }
+#pragma unroll
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] = 0;
+  const char* lb = reinterpret_cast<const char*>(lut);
+#pragma unroll
+  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
+    if (w < n_a_words) {
+      const uint32_t x = ra[w];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t off = (k == 0) ? ((x << 3) & 0x78u) : ((x >> (4 * k - 3)) & 0x78u);
+        add_entry(*reinterpret_cast<const uint2*>(lb + (w * 8 + k) * 128 + off), acc);
+      }
+    }
+  }
+  const char* lc = lb + n_a_words * 8 * 128;
+#pragma unroll
+  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
+    if (w < n_c_words) {
+      const uint32_t x = rc[w];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t o0 = (b == 0) ? ((x << 3) & 0x38u) : ((x >> (8 * b - 3)) & 0x38u);
+        const uint32_t o1 = (x >> (8 * b)) & 0x38u;          // bits 3..5 of the byte, already times 8
+        const uint32_t o2 = (x >> (8 * b + 3)) & 0x18u;      // bits 6..7 of the byte, times 8
+        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 0) * 128 + o0), acc);
+        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 1) * 128 + o1), acc);
+        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 2) * 128 + o2), acc);
+      }
+    }
+  }
+}
+
+}  // namespace jqk

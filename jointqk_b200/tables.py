@@ -93,6 +93,8 @@ class HeadTables:
             cb_cols[h, :n] = rows
             thr[h, :n, :15] = decision_thresholds(rows, lay.col_width[:n])
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         up = lambda a: torch.from_numpy(a).to(self.device)
         self.desc, self.col_meta, self.table_fields = up(desc), up(col_meta), up(fields)
         self.fwd_cols, self.qproj_cols, self.inv_rows = up(fwd_cols), up(qproj), up(inv_rows)
