@@ -136,14 +136,15 @@ int32_t jqk_unpack_codes(const jqk_head_tables* tables, int32_t n_seqs, const in
                          uint8_t* codes, int32_t* status, void* stream);
 
 /*
- * Attention logits of queries against packed keys, q . k_hat / sqrt(d), through the same
- * lookup tables as decode.  Replaces compute_attention_metrics' candidate logits
+ * Attention logits of queries against packed keys, q . k_hat / sqrt(d).  Replaces compute_attention_metrics' candidate logits
  * (experiments/stage1/toolkit/eval.py:21) with GQA grouping as in repeat_kv_states
  * (experiments/stage1/toolkit/metric_transform.py:21-27).
+ *   table_mode 0: fp32 sum over coordinates of q'_c * codebook[c][code] (evaluation, top-1 metrics);
+ *              1: the decode kernel's 16-bit fixed-point lookup tables (what decode attention scores with)
  *   q       [n_seqs][n_q_heads][n_queries][d] of q_dtype, contiguous
  *   scores  float [n_seqs][n_q_heads][n_queries][max_tokens]; entries beyond seq_lens[s] untouched
  */
-int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q, int32_t q_dtype,
+int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_mode, const void* q, int32_t q_dtype,
                         int32_t n_seqs, int32_t n_q_heads, int32_t n_queries,
                         const int32_t* seq_lens, int32_t max_tokens, const int32_t* page_table,
                         int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,

@@ -49,7 +49,7 @@ SIGNATURES = {
         C.POINTER(JqkHeadTables), C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "jqk_score_paged": (C.c_int32, [
-        C.POINTER(JqkHeadTables), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+        C.POINTER(JqkHeadTables), C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
         C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "jqk_decode_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "jqk_decode_default_split": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

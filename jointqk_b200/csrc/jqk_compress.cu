@@ -8,7 +8,16 @@
 //   idx = argmin_l |x_j - cb[j, l]|, first index on ties   (:156-157)
 //   xh  = cb[j, idx]; k_hat = xh @ inverse_map             (:158-164)
 // The argmin is evaluated through exact fp32 decision thresholds prepared on the host.
+#include <stdlib.h>
+
 #include "jqk_common.cuh"
+
+// Tensor-core path (jqk_compress_tc.cu): 0 = launched, 1 = call does not fit it, else an error code.
+int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int32_t key_dtype, int64_t seq_stride,
+                            int64_t head_stride, int64_t token_stride, int32_t n_seqs, const int32_t* n_tokens,
+                            const int32_t* seq_starts, int32_t max_tokens, const int32_t* page_table,
+                            int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, int32_t* status,
+                            cudaStream_t st);
 
 namespace jqk {
 
@@ -265,10 +274,21 @@ extern "C" int32_t jqk_compress_paged(const jqk_head_tables* tables, const void*
   if (n_seqs == 0 || max_tokens == 0) return 0;
   if (!keys) return fail(JQK_E_ARG, "null keys");
   if (token_stride < tables->d) return fail(JQK_E_ARG, "token_stride %lld smaller than d", (long long)token_stride);
+  cudaStream_t st = (cudaStream_t)stream;
+  {
+    // bf16 keys of head_dim 128 go to the tensor-core kernel; everything else (fp32 / fp16 keys,
+    // other head sizes, unaligned strides, fewer than 128 keys) stays on the exact fp32 kernel.
+    static const bool tc_off = getenv("JQK_DISABLE_TENSOR_CORE_COMPRESS") != nullptr;
+    if (!tc_off) {
+      const int32_t r = jqk_compress_tc_try(tables, keys, key_dtype, seq_stride, head_stride, token_stride, n_seqs,
+                                            n_tokens, seq_starts, max_tokens, page_table, page_table_stride, n_pages,
+                                            k_pool, status, st);
+      if (r != 1) return r;
+    }
+  }
   dim3 grid((max_tokens + TILE_T - 1) / TILE_T, tables->n_heads, n_seqs);
   PagedArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, max_tokens, status};
-  cudaStream_t st = (cudaStream_t)stream;
-#define JQK_LAUNCH_COMPRESS(KT)                                                                        \
+#define JQK_LAUNCH_COMPRESS(KT)                                                                       \
   do {                                                                                                 \
     JQK_SMEM_ONCE(compress_simt_kernel<KT>, kTileSmem, "compress smem attribute");                      \
     compress_simt_kernel<KT><<<grid, 256, kTileSmem, st>>>(*tables, (const KT*)keys, seq_stride,        \

@@ -1,0 +1,281 @@
+// Prefill compression on the tensor cores (bf16 keys, head_dim 128).
+//
+// Same result as compress_simt_kernel (jqk_compress.cu); reference semantics
+// experiments/stage1/toolkit/per_coord_quantization.py:132-157.  The basis transform
+// x = k @ forward_map runs as tcgen05.mma with the fp32 map split into three bf16 limbs
+// (F = F0 + F1 + F2 to ~2^-24): bf16 x bf16 products are exact in fp32, the limbs are added
+// smallest first into one fp32 TMEM accumulator, so the transform keeps fp32 accuracy, which
+// the bit-exact code requirement needs (one bf16 or TF32 pass would flip ~1e-3 of the codes).
+//
+// One thread block walks a run of 128-key tiles of one (sequence, head):
+//   warp 0      TMA producer: key tiles [128 keys][128 dims] bf16 into a 3-stage ring (128B swizzle)
+//   warp 1      allocates TMEM, loads the three limb matrices once, issues 24 MMAs per tile
+//               (8 K-steps x 3 limbs, M=128, N=columns, K=16) into one of two accumulators
+//   warps 2..9  epilogue: a thread owns one key (TMEM lane) and half of the record's words; it
+//               reads 16 columns at a time, finds each code by binary search over the exact
+//               fp32 decision thresholds in shared memory, appends the bits and stores finished
+//               words to the page (word-major pages: 64-byte segments per warp store).
+// Every mbarrier wait is bounded in time; on expiry the block flags JQK_STATUS_WAIT_EXPIRED,
+// drains its copies, frees TMEM and returns.
+#include "jqk_common.cuh"
+#include "jqk_sm100.cuh"
+
+namespace jqk {
+
+using namespace sm100;
+
+constexpr int TC_TILE = 128;
+constexpr int TC_STAGES = 3;
+constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
+constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
+constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
+constexpr uint32_t TC_TMEM_COLS = 256;               // two fp32 accumulators of 128 columns
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
+
+struct TcSmem {
+  uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
+  uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
+  float thr[128 * 16];
+  int32_t meta[128];
+  int32_t wcb[JQK_MAX_WORDS + 4];
+  uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], b_full;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+struct TcArgs {
+  const int32_t* n_tokens;
+  const int32_t* seq_starts;
+  const int32_t* page_table;
+  int32_t pt_stride;
+  int32_t n_pages;
+  int32_t tiles_per_block;
+  int32_t* status;
+};
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait: false (and the abort flag) after TC_WAIT_NS or when another role gave up.
+__device__ __forceinline__ bool tc_wait(TcSmem& sm, uint64_t* bar, uint32_t parity, int32_t* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm.abort) return false;
+    if (now_ns() - t0 > TC_WAIT_NS) {
+      sm.abort = 1;
+      if (status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+      return false;
+    }
+  }
+}
+
+// code = #{l : x >= thr[l]} for sorted thresholds, by binary search over 2^width - 1 entries.
+__device__ __forceinline__ uint32_t search_code(float x, const float* __restrict__ thr, int width) {
+  uint32_t code = 0;
+  for (int step = (1 << width) >> 1; step >= 1; step >>= 1)
+    code += (x >= thr[code + step - 1]) ? step : 0;
+  return code;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
+                   jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
+  extern __shared__ uint8_t smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int n_tok = pa.n_tokens[seq];
+  const int n_tiles = (n_tok + TC_TILE - 1) / TC_TILE;
+  const int tile_lo = blockIdx.x * pa.tiles_per_block;
+  const int tile_hi = min(n_tiles, tile_lo + pa.tiles_per_block);
+  if (tile_lo >= tile_hi) return;
+  const HeadDesc hd = load_desc(tb.desc, head);
+
+  // ---- set-up ----
+  for (int e = tid; e < hd.n_cols * 16; e += TC_THREADS) sm.thr[e] = tb.thresholds[(size_t)head * 128 * 16 + e];
+  for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
+  for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&sm.acc_full[a], 1); mbar_init(&sm.acc_empty[a], TC_EPI_WARPS); }
+    mbar_init(&sm.b_full, 1);
+    sm.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&sm.tmem_base, TC_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      tma_prefetch_desc(&key_map);
+      int issued = 0;
+      for (int t = tile_lo; t < tile_hi; ++t, ++issued) {
+        const int s = issued % TC_STAGES;
+        const uint32_t ph = (issued / TC_STAGES) & 1;
+        if (issued >= TC_STAGES && !tc_wait(sm, &sm.empty[s], ph ^ 1, pa.status)) break;
+        mbar_arrive_expect_tx(&sm.full[s], TC_A_BYTES);
+        tma_load_4d(sm.a[s], &key_map, &sm.full[s], 0, t * TC_TILE, head, seq);
+        tma_load_4d(sm.a[s] + TC_A_BYTES / 2, &key_map, &sm.full[s], 64, t * TC_TILE, head, seq);
+      }
+      if (sm.abort) {  // let the copies that were issued land before the block goes away
+        for (int i = max(0, issued - TC_STAGES); i < issued; ++i)
+          tc_wait(sm, &sm.full[i % TC_STAGES], (i / TC_STAGES) & 1, nullptr);
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      tma_prefetch_desc(&limb_map);
+      mbar_arrive_expect_tx(&sm.b_full, TC_B_BYTES);
+      for (int l = 0; l < 3; ++l)
+        for (int kh = 0; kh < 2; ++kh)
+          tma_load_2d(sm.b[l] + kh * (128 * 64 * 2), &limb_map, &sm.b_full, 64 * kh, (head * 3 + l) * 128);
+      const uint32_t idesc = make_idesc_bf16(128, hd.n_cols, false, false);
+      bool ok = tc_wait(sm, &sm.b_full, 0, pa.status);
+      int it = 0;
+      for (int t = tile_lo; ok && t < tile_hi; ++t, ++it) {
+        const int s = it % TC_STAGES, a = it & 1;
+        if (!tc_wait(sm, &sm.full[s], (it / TC_STAGES) & 1, pa.status)) break;
+        if (it >= 2 && !tc_wait(sm, &sm.acc_empty[a], ((it >> 1) & 1) ^ 1, pa.status)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + a * 128;
+        const uint32_t a_base = smem_u32(sm.a[s]);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * (128 * 64 * 2) + (ks & 3) * 32;
+          const uint64_t a_desc = make_smem_desc_sw128(a_base + off, 16, 1024);
+#pragma unroll
+          for (int l = 2; l >= 0; --l) {
+            const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sm.b[l]) + off, 16, 1024);
+            umma_bf16(d_tmem, a_desc, b_desc, idesc, !(ks == 0 && l == 2));
+          }
+        }
+        umma_commit(&sm.empty[s]);     // the key tile may be overwritten
+        umma_commit(&sm.acc_full[a]);  // the accumulator may be read
+      }
+    }
+  } else {
+    // ================= epilogue =================
+    const int ew = warp - 2;
+    const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
+    const int half = ew >> 2;
+    const int w_split = (hd.n_words + 1) >> 1;
+    const int w_lo = half ? w_split : 0, w_hi = half ? hd.n_words : w_split;
+    const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
+    const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
+    const int wpr = tb.words_per_record;
+    int it = 0;
+    for (int t = tile_lo; t < tile_hi; ++t, ++it) {
+      const int a = it & 1;
+      if (!tc_wait(sm, &sm.acc_full[a], (it >> 1) & 1, pa.status)) break;
+      tc_fence_after();
+      const int key = t * TC_TILE + row;
+      const bool valid = key < n_tok;
+      uint32_t* dst = nullptr;
+      if (valid) {
+        const int tok = seq_start + key;
+        const int page = lookup_page(pa.page_table, pa.pt_stride, seq, tok / JQK_PAGE_TOKENS, pa.n_pages, pa.status);
+        if (page >= 0)
+          dst = k_pool + ((size_t)page * tb.n_heads + head) * wpr * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS);
+      }
+      const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
+      int cur_w = w_lo;
+      uint32_t cur = 0;
+      for (int c0 = c_lo & ~15; c0 < c_hi; c0 += 16) {
+        float v[16];
+        tmem_ld16(t_lane + c0, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int c = c0 + i;
+          if (c >= c_lo && c < c_hi) {  // warp-uniform
+            const int m = sm.meta[c];
+            const int bp = (m >> 4) & 1023;
+            const int w = bp >> 5;
+            while (cur_w < w) {  // finished words (and pad words) leave in order
+              if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
+              cur = 0;
+              ++cur_w;
+            }
+            cur |= search_code(v[i], sm.thr + c * 16, m & 15) << (bp & 31);
+          }
+        }
+      }
+      while (cur_w < w_hi) {
+        if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
+        cur = 0;
+        ++cur_w;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty[a]);
+    }
+  }
+
+  // ---- teardown ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TC_TMEM_COLS);
+  }
+}
+
+}  // namespace jqk
+
+using namespace jqk;
+
+// Launches the tensor-core kernel when the call fits it (bf16 keys, head_dim 128, 16-byte aligned
+// strides); returns 1 when the caller should use the fp32 CUDA-core kernel instead.
+int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int32_t key_dtype,
+                            int64_t seq_stride, int64_t head_stride, int64_t token_stride, int32_t n_seqs,
+                            const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
+                            const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
+                            uint32_t* k_pool, int32_t* status, cudaStream_t st) {
+  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs) return 1;
+  if ((uintptr_t)keys % 16 || (token_stride * 2) % 16 || (head_stride * 2) % 16 || (seq_stride * 2) % 16) return 1;
+  if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE) return 1;
+  CUtensorMap key_map, limb_map;
+  char err[256];
+  {
+    // dims innermost first: (dim, key, head, sequence); a stride of one sequence / head may be 0
+    // bytes for a single-entry dimension, which the encoder rejects, so give it the row pitch.
+    const uint64_t row = (uint64_t)token_stride * 2;
+    const uint64_t dims[4] = {128, (uint64_t)max_tokens, (uint64_t)tables->n_heads, (uint64_t)n_seqs};
+    const uint64_t strides[3] = {row, head_stride ? (uint64_t)head_stride * 2 : row * max_tokens,
+                                 seq_stride ? (uint64_t)seq_stride * 2 : row * max_tokens * tables->n_heads};
+    const uint32_t box[4] = {64, TC_TILE, 1, 1};
+    if (!encode_bf16_map(&key_map, keys, 4, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "key tensor map: %s", err);
+  }
+  {
+    const uint64_t dims[2] = {128, (uint64_t)tables->n_heads * 3 * 128};
+    const uint64_t strides[1] = {256};
+    const uint32_t box[2] = {64, 128};
+    if (!encode_bf16_map(&limb_map, tables->fwd_limbs, 2, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "limb tensor map: %s", err);
+  }
+  const int max_tiles = (max_tokens + TC_TILE - 1) / TC_TILE;
+  // about two waves of blocks over 148 SMs, each block a contiguous run of tiles of one head
+  const long long pairs = (long long)n_seqs * tables->n_heads;
+  long long blocks_per_pair = (2 * 148 + pairs - 1) / pairs;
+  if (blocks_per_pair < 1) blocks_per_pair = 1;
+  int tiles_per_block = (int)((max_tiles + blocks_per_pair - 1) / blocks_per_pair);
+  if (tiles_per_block < 4) tiles_per_block = 4;
+  dim3 grid((max_tiles + tiles_per_block - 1) / tiles_per_block, tables->n_heads, n_seqs);
+  TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, status};
+  const size_t smem = sizeof(TcSmem) + 1024;
+  JQK_SMEM_ONCE(compress_tc_kernel, smem, "tensor-core compress smem attribute");
+  compress_tc_kernel<<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
+  JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
+  return 0;
+}

@@ -37,7 +37,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int SCORE_CHUNK = 2048;
 
 __global__ void __launch_bounds__(DEC_THREADS)
-score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_q_heads, int n_queries,
+score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int q_dtype, int n_q_heads, int n_queries,
              const int32_t* __restrict__ seq_lens, int max_tokens, const int32_t* __restrict__ page_table,
              int pt_stride, int n_pages, const uint32_t* __restrict__ k_pool, float* __restrict__ scores,
              int32_t* status) {
@@ -64,13 +64,30 @@ score_kernel(jqk_head_tables tb, const void* __restrict__ q, int q_dtype, int n_
     if (page < 0) continue;
     const uint32_t* kp = k_pool + ((size_t)page * tb.n_heads + head) * tb.words_per_record * JQK_PAGE_TOKENS +
                          (tok % JQK_PAGE_TOKENS);
-    int acc[JQK_MAX_GROUP];
-    score_record(kp, sm.lut, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
+    float sv[JQK_MAX_GROUP];
+    if (table_mode) {  // the decode kernel's fixed-point tables
+      int acc[JQK_MAX_GROUP];
+      score_record(kp, sm.lut, sm.dshift, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) sv[h] = (float)acc[h] * sm.scale[h];
+    } else {           // plain fp32: sum_c q'_c * cb[c][code_c], column after column
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) sv[h] = 0.f;
+      const int32_t* meta = tb.col_meta + (size_t)head * 128;
+      for (int c = 0; c < hd.n_active; ++c) {
+        const int m = __ldg(meta + c);
+        const int bp = (m >> 4) & 1023;
+        const uint32_t word = __ldg(kp + (bp >> 5) * JQK_PAGE_TOKENS);
+        const float x = sm.cb[c * 16 + ((word >> (bp & 31)) & ((1u << (m & 15)) - 1u))];
+        const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[c]);
+        sv[0] = fmaf(qp.x, x, sv[0]); sv[1] = fmaf(qp.y, x, sv[1]);
+        sv[2] = fmaf(qp.z, x, sv[2]); sv[3] = fmaf(qp.w, x, sv[3]);
+      }
+    }
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
       if (h < n_group)
-        scores[(((size_t)seq * n_q_heads + qh0 + h) * n_queries + qi) * max_tokens + tok] =
-            (float)acc[h] * sm.scale[h] * inv_sqrt_d;
+        scores[(((size_t)seq * n_q_heads + qh0 + h) * n_queries + qi) * max_tokens + tok] = sv[h] * inv_sqrt_d;
     }
   }
 }
@@ -237,7 +254,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     float s[JQK_MAX_GROUP];
     if (tok < t_end && my_page >= 0) {
       int ia[JQK_MAX_GROUP];
-      score_record(k_head + (size_t)my_page * k_page_words + (lane & 15), lut, n_a_words, n_c_words, n_words, ia);
+      score_record(k_head + (size_t)my_page * k_page_words + (lane & 15), lut, sm.t.dshift, n_a_words, n_c_words, n_words, ia);
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = (float)ia[h] * sc[h];
     } else {
@@ -412,7 +429,7 @@ extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, i
   return (int32_t)tps;
 }
 
-extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q, int32_t q_dtype,
+extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_mode, const void* q, int32_t q_dtype,
                                    int32_t n_seqs, int32_t n_q_heads, int32_t n_queries,
                                    const int32_t* seq_lens, int32_t max_tokens, const int32_t* page_table,
                                    int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
@@ -424,14 +441,15 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, const void* q,
   if (!q || !seq_lens || !page_table || !k_pool || !scores) return fail(JQK_E_ARG, "null pointer argument");
   if (n_q_heads <= 0 || n_q_heads % tables->n_heads) return fail(JQK_E_ARG, "n_q_heads %d is not a multiple of the %d kv heads", n_q_heads, tables->n_heads);
   if (q_dtype != JQK_DTYPE_F32 && q_dtype != JQK_DTYPE_BF16 && q_dtype != JQK_DTYPE_F16) return fail(JQK_E_ARG, "unknown q dtype %d", q_dtype);
+  if (table_mode != 0 && table_mode != 1) return fail(JQK_E_ARG, "table_mode must be 0 (fp32) or 1 (decode tables)");
   if ((long long)n_seqs * n_queries > 65535) return fail(JQK_E_UNSUPPORTED, "n_seqs * n_queries exceeds 65535");
   if (page_table_stride <= 0 || n_pages <= 0) return fail(JQK_E_ARG, "page_table_stride and n_pages must be positive");
   dim3 grid((max_tokens + SCORE_CHUNK - 1) / SCORE_CHUNK, tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads),
             n_seqs * n_queries);
   JQK_SMEM_ONCE(score_kernel, sizeof(TableSmem), "score smem attribute");
   score_kernel<<<grid, DEC_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
-      *tables, q, q_dtype, n_q_heads, n_queries, seq_lens, max_tokens, page_table, page_table_stride, n_pages,
-      k_pool, scores, status);
+      *tables, table_mode, q, q_dtype, n_q_heads, n_queries, seq_lens, max_tokens, page_table, page_table_stride,
+      n_pages, k_pool, scores, status);
   JQK_CUDA_OK(cudaGetLastError(), "score launch");
   return 0;
 }

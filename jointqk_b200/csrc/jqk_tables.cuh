@@ -6,6 +6,14 @@
 // q'_c * cb[c][code] of its coordinates.  Entries are 16-bit fixed point with one fp32 scale
 // per query head: 8 bytes per entry, 128 bytes per table, so a warp-wide 8-byte read of one
 // table never has a bank conflict.
+//
+// Fixed-point scale.  Tables of later record words belong to lower-variance coordinates, so a
+// single scale would spend most of the 16 bits on a few large tables.  Instead word w (nibble
+// words first, then byte words) is quantised at scale_h / 2^K_w with K non-decreasing in w; the
+// scoring loop shifts its integer sums left by K_w - K_{w-1} before it adds the lookups of word
+// w, which is exact, and the final sum is in units of scale_h / 2^K_last.  K_w is the largest
+// shift that keeps every entry of every later-or-equal word inside 16 bits (capped at
+// TBL_MAX_SHIFT so that the 32-bit sums cannot overflow).
 #pragma once
 
 #include <math_constants.h>
@@ -15,6 +23,8 @@
 namespace jqk {
 
 constexpr int TBL_THREADS = 256;  // build_tables is written for exactly this block size
+constexpr int TBL_MAX_SHIFT = 8;  // 29 words x 12 lookups x 2^15 x 2^8 < 2^31
+constexpr int TBL_WORDS = 2 * JQK_MAX_WORDS;  // nibble words, then byte words
 
 struct TableSmem {
   uint2 lut[JQK_MAX_TABLES * 16];                // 26,624 B: [table][16] x (int16 x 4 heads)
@@ -23,9 +33,17 @@ struct TableSmem {
   float qraw[JQK_MAX_GROUP][JQK_MAX_DIM];        //  2,048 B
   float cb[JQK_MAX_COLS * 16];                   //  8,192 B: staged codebooks
   int32_t fields[JQK_MAX_TABLES * 4];            //  3,328 B: staged table composition
-  float scale[JQK_MAX_GROUP];
+  float scale[JQK_MAX_GROUP];                    // value of one unit of the final integer sum
   unsigned int absmax[JQK_MAX_GROUP];
+  unsigned int wmax[TBL_WORDS][JQK_MAX_GROUP];   // per scan-order word: largest |entry| per head
+  int kshift[TBL_WORDS];                         // K_w
+  int dshift[TBL_WORDS];                         // K_w - K_{w-1}
 };
+
+// Scan-order word of table t: nibble word t/8, or n_a_words + byte word.
+__device__ __forceinline__ int table_word(int t, int n_a_words) {
+  return (t < 8 * n_a_words) ? (t >> 3) : (n_a_words + (t - 8 * n_a_words) / 12);
+}
 
 // One table entry in fp32 for the heads of the group (all operands in shared memory).
 __device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&v)[JQK_MAX_GROUP]) {
@@ -75,6 +93,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     for (int e = tid; e < hd.n_tables; e += TBL_THREADS) fdst[e] = __ldg(f4 + e);
   }
   if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
+  if (tid < TBL_WORDS * JQK_MAX_GROUP) (&sm.wmax[0][0])[tid] = 0u;
   __syncthreads();
   {
     float a[4][JQK_MAX_GROUP];
@@ -109,33 +128,65 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
   }
   __syncthreads();
   const int n_entries = hd.n_tables * 16;
-  float mx[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
+  const int n_scan_words = hd.n_a_words + hd.n_c_words;
+  // pass 1: largest |entry| per (word, head); 16 consecutive threads share a table
   for (int e = tid; e < n_entries; e += TBL_THREADS) {
     float v[JQK_MAX_GROUP];
     table_entry(sm, e, v);
+    const int w = table_word(e >> 4, hd.n_a_words);
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) mx[h] = fmaxf(mx[h], fabsf(v[h]));
-  }
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+      float m = fabsf(v[h]);
 #pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-    const float m = warp_max(mx[h]);
-    if ((tid & 31) == 0) atomicMax(&sm.absmax[h], __float_as_uint(m));  // non-negative floats order as uints
+      for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      if ((tid & 15) == 0) atomicMax(&sm.wmax[w][h], __float_as_uint(m));  // non-negative floats order as uints
+    }
   }
   __syncthreads();
   if (tid < JQK_MAX_GROUP) {
-    const float m = __uint_as_float(sm.absmax[tid]);
-    sm.scale[tid] = (m > 0.f && m < CUDART_INF_F) ? m / 32767.f : 1.f;
+    float m = 0.f;
+    for (int w = 0; w < n_scan_words; ++w) m = fmaxf(m, __uint_as_float(sm.wmax[w][tid]));
+    sm.absmax[tid] = __float_as_uint((m > 0.f && m < CUDART_INF_F) ? m : 0.f);
+  }
+  __syncthreads();
+  if (tid < TBL_WORDS) {
+    // largest shift that keeps word `tid` inside 16 bits for every head
+    int fit = TBL_MAX_SHIFT;
+    if (tid < n_scan_words) {
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+        const float g = __uint_as_float(sm.absmax[h]), m = __uint_as_float(sm.wmax[tid][h]);
+        if (g > 0.f && m > 0.f) fit = min(fit, max(0, (int)floorf(log2f(g / m) - 1e-3f)));
+      }
+    }
+    sm.kshift[tid] = fit;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int k = TBL_MAX_SHIFT;
+    for (int w = n_scan_words - 1; w >= 0; --w) { k = min(k, sm.kshift[w]); sm.kshift[w] = k; }
+    int prev = 0;
+    for (int w = 0; w < n_scan_words; ++w) { sm.dshift[w] = sm.kshift[w] - prev; prev = sm.kshift[w]; }
+    const int k_last = n_scan_words ? prev : 0;
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+      const float m = __uint_as_float(sm.absmax[h]);
+      const float base = (m > 0.f) ? m / 32767.f : 1.f;
+      sm.scale[h] = base / (float)(1 << k_last);
+      sm.absmax[h] = __float_as_uint(base);  // reused below as the per-head base scale
+    }
   }
   __syncthreads();
   float inv[JQK_MAX_GROUP];
 #pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / sm.scale[h];
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / __uint_as_float(sm.absmax[h]);
   for (int e = tid; e < n_entries; e += TBL_THREADS) {
     float v[JQK_MAX_GROUP];
     table_entry(sm, e, v);
+    const float up = (float)(1 << sm.kshift[table_word(e >> 4, hd.n_a_words)]);
     int q[JQK_MAX_GROUP];
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h])));
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h] * up)));
     uint2 packed;
     packed.x = (uint32_t)(q[0] & 0xffff) | ((uint32_t)q[1] << 16);
     packed.y = (uint32_t)(q[2] & 0xffff) | ((uint32_t)q[3] << 16);
@@ -157,8 +208,8 @@ __device__ __forceinline__ void add_entry(const uint2 e, int (&acc)[JQK_MAX_GROU
 // record, (3,3,2)-byte words from its end; lookups that fall on the other region hit all-zero
 // tables.
 __device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, const uint2* __restrict__ lut,
-                                             int n_a_words, int n_c_words, int n_words,
-                                             int (&acc)[JQK_MAX_GROUP]) {
+                                             const int* __restrict__ dshift, int n_a_words, int n_c_words,
+                                             int n_words, int (&acc)[JQK_MAX_GROUP]) {
   uint32_t ra[JQK_MAX_WORDS], rc[JQK_MAX_WORDS];
 #pragma unroll
   for (int w = 0; w < JQK_MAX_WORDS; ++w) {
@@ -172,6 +223,9 @@ __device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, co
   for (int w = 0; w < JQK_MAX_WORDS; ++w) {
     if (w < n_a_words) {
       const uint32_t x = ra[w];
+      const int sh = dshift[w];
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] <<= sh;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const uint32_t off = (k == 0) ? ((x << 3) & 0x78u) : ((x >> (4 * k - 3)) & 0x78u);
@@ -184,6 +238,9 @@ __device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, co
   for (int w = 0; w < JQK_MAX_WORDS; ++w) {
     if (w < n_c_words) {
       const uint32_t x = rc[w];
+      const int sh = dshift[n_a_words + w];
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] <<= sh;
 #pragma unroll
       for (int b = 0; b < 4; ++b) {
         const uint32_t o0 = (b == 0) ? ((x << 3) & 0x38u) : ((x >> (8 * b - 3)) & 0x38u);

@@ -142,8 +142,11 @@ def unpack_codes(packed: PackedKeys) -> torch.Tensor:
     return out
 
 
-def score(packed: PackedKeys, q: torch.Tensor) -> torch.Tensor:
-    """Logits ``q . k_hat / sqrt(d)``: q (n_seqs, Hq, n_queries, d) -> (n_seqs, Hq, n_queries, max_tokens)."""
+def score(packed: PackedKeys, q: torch.Tensor, decode_tables: bool = False) -> torch.Tensor:
+    """Logits ``q . k_hat / sqrt(d)``: q (n_seqs, Hq, n_queries, d) -> (n_seqs, Hq, n_queries, max_tokens).
+
+    ``decode_tables=False`` sums in fp32 (evaluation metrics); ``True`` scores through the 16-bit
+    fixed-point lookup tables exactly as the decode kernel does."""
     t = packed.tables
     if q.dim() != 4 or q.shape[0] != packed.n_seqs or q.shape[3] != t.d:
         raise ValueError(f"q must be ({packed.n_seqs}, Hq, n_queries, {t.d}), got {tuple(q.shape)}")
@@ -153,7 +156,7 @@ def score(packed: PackedKeys, q: torch.Tensor) -> torch.Tensor:
     out = torch.zeros((packed.n_seqs, q.shape[1], q.shape[2], packed.max_tokens), dtype=torch.float32, device=t.device)
     if out.numel():
         _native.check(_native.lib.jqk_score_paged(
-            t.ref, q.data_ptr(), _native.torch_dtype_code(q.dtype), packed.n_seqs, q.shape[1], q.shape[2],
+            t.ref, int(decode_tables), q.data_ptr(), _native.torch_dtype_code(q.dtype), packed.n_seqs, q.shape[1], q.shape[2],
             packed.n_tokens.data_ptr(), packed.max_tokens, packed.page_table.data_ptr(),
             packed.page_table.stride(0), packed.n_pages, packed.k_pool.data_ptr(), out.data_ptr(),
             packed.status.data_ptr(), _stream_ptr(t.device)))

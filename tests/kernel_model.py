@@ -42,7 +42,7 @@ def unpack_model(tab, h, rec):
 
 
 def build_lut_model(tab, h, q):
-    """q (G<=4, d) fp32 -> (lut int16 (n_tables*16, 4), scale (4,)), like build_tables."""
+    """q (G<=4, d) fp32 -> (lut (n_tables*16, 4), scale (4,), per-word shifts), like build_tables."""
     desc = tab.desc[h].numpy()
     n_tables = int(desc[6])
     qp = np.zeros((128, 4), np.float32)
@@ -61,26 +61,48 @@ def build_lut_model(tab, h, q):
                 col, wd, sh = fld & 255, (fld >> 8) & 15, (fld >> 12) & 15
                 v += qp[col] * cb[col, (e >> sh) & ((1 << wd) - 1)]
             ent[t * 16 + e] = v
-    mx = np.abs(ent).max(0) if n_tables else np.zeros(4, np.float32)
-    scale = np.where(mx > 0, mx / np.float32(32767.0), np.float32(1.0)).astype(np.float32)
-    lut = np.clip(np.rint(ent / scale), -32767, 32767).astype(np.int32)
-    return lut, scale
+    naw, ncw = int(desc[4]), int(desc[5])
+    n_scan = naw + ncw
+    word_of = np.array([t // 8 if t < 8 * naw else naw + (t - 8 * naw) // 12 for t in range(n_tables)], np.int64)
+    tmax = np.abs(ent).reshape(n_tables, 16, 4).max(1) if n_tables else np.zeros((0, 4), np.float32)
+    wmax = np.zeros((n_scan, 4), np.float32)
+    for t in range(n_tables):
+        wmax[word_of[t]] = np.maximum(wmax[word_of[t]], tmax[t])
+    gmax = wmax.max(0) if n_scan else np.zeros(4, np.float32)
+    fit = np.full(n_scan, 8, np.int64)
+    for w in range(n_scan):
+        for h in range(4):
+            if gmax[h] > 0 and wmax[w, h] > 0:
+                fit[w] = min(fit[w], max(0, int(np.floor(np.log2(gmax[h] / wmax[w, h]) - 1e-3))))
+    k = 8
+    kshift = np.zeros(n_scan, np.int64)
+    for w in range(n_scan - 1, -1, -1):
+        k = min(k, int(fit[w]))
+        kshift[w] = k
+    base = np.where(gmax > 0, gmax / np.float32(32767.0), np.float32(1.0)).astype(np.float32)
+    up = (2.0 ** kshift[word_of]).astype(np.float32) if n_tables else np.zeros(0, np.float32)
+    lut = np.clip(np.rint(ent / base * np.repeat(up, 16)[:, None]), -32767, 32767).astype(np.int64)
+    scale = base / np.float32(2.0 ** (kshift[-1] if n_scan else 0))
+    dshift = np.diff(np.concatenate([[0], kshift]))
+    return lut, scale, dshift
 
 
 def score_model(tab, h, rec, q):
     """Scores (G, N) = q . k_hat / sqrt(d) from records, like score_record + score_kernel."""
     desc = tab.desc[h].numpy()
     d, n_words, naw, ncw = int(desc[0]), int(desc[3]), int(desc[4]), int(desc[5])
-    lut, scale = build_lut_model(tab, h, q)
+    lut, scale, dshift = build_lut_model(tab, h, q)
     acc = np.zeros((rec.shape[0], 4), np.int64)
     for w in range(naw):
         x = rec[:, w]
+        acc <<= int(dshift[w])
         for k in range(8):
             idx = (x >> np.uint32(4 * k)) & np.uint32(15)
             acc += lut[(w * 8 + k) * 16 + idx]
     base = naw * 8 * 16
     for w in range(ncw):
         x = rec[:, n_words - 1 - w]
+        acc <<= int(dshift[naw + w])
         for b in range(4):
             y = x >> np.uint32(8 * b)
             acc += lut[base + (w * 12 + b * 3 + 0) * 16 + (y & np.uint32(7))]

@@ -159,3 +159,36 @@ def test_idempotence_at_scale():
     c2 = paged.unpack_codes(p2)
     rate = float((c1 != c2).float().mean())
     assert rate <= MAX_RATE, rate
+
+
+def test_tensor_core_path_ragged_bf16_and_append():
+    """bf16 keys take the tcgen05 kernel: ragged batch, tile tails, a mid-page append offset and
+    a strided (non-contiguous) key tensor, all against the oracle's codes."""
+    H = 3
+    base = torch.stack([spectrum_keys(700, config_seed(4, 1, h), 8, 20.0) for h in range(H)])
+    comps, _ = fit_sigma_k_heads(base, 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    keys = torch.stack([base, base.flip(1), base * 0.7, base.roll(5, 1)]).to(torch.bfloat16)      # (4, H, 700, d)
+    lens = [700, 129, 0, 512]
+    # a view with a larger token stride (e.g. keys living inside a fused qkv buffer)
+    wide = torch.zeros(4, H, 700, 256, dtype=torch.bfloat16, device="cuda")
+    wide[..., :128] = keys.cuda()
+    packed = paged.compress(tables, wide[..., :128], lens)
+    paged.check_status(packed.status)
+    codes = paged.unpack_codes(packed).cpu()
+    bad = 0
+    for s, n in enumerate(lens):
+        for h in range(H):
+            ref_codes, _ = oracle_codes_and_recon(comps[h], keys[s, h, :n])
+            bad += int((codes[s, h, :n].long() != ref_codes).sum())
+        assert int(codes[s, :, n:].abs().sum()) == 0
+    assert bad <= 2, bad
+    # append at a mid-page offset: 23 keys through the fp32 kernel, then 677 through the tensor cores
+    cache = paged.PagedKVCache(tables, [700])
+    v = torch.zeros(1, H, 700, 128, device="cuda", dtype=torch.bfloat16)
+    cache.prefill(keys[:1, :, :23].cuda(), v[:, :, :23])
+    cache.prefill(keys[:1, :, 23:].cuda(), v[:, :, 23:])
+    paged.check_status(cache.status)
+    pk = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, [700], cache.status)
+    again = paged.unpack_codes(pk).cpu()
+    assert int((again[0] != codes[0]).sum()) <= 2

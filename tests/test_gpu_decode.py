@@ -41,12 +41,13 @@ def test_parity_config_scores_and_top1(b_avg):
     packed = paged.compress(tables, keys.cuda().unsqueeze(0))
     q = torch.stack([retrieval_queries(keys[h], sig[h], NQ, config_seed(0, 0, h) + 7)[0] for h in range(H)])
     qq = q.unsqueeze(0)                                            # (1, H, NQ, d): one q head per kv head
-    s = paged.score(packed, qq.cuda()).cpu()
+    s = paged.score(packed, qq.cuda()).cpu()                        # fp32 sums
+    s_tab = paged.score(packed, qq.cuda(), decode_tables=True).cpu()  # what the decode kernel scores with
     k_hat = _k_hat_from_packed(packed, comps)
     ref = orc.logits(qq, k_hat)
-    err = score_rel_error(s, ref)
-    print(f"score rel error b_avg={b_avg}: {err:.2e}")
-    assert err < SCORE_TOL
+    err, err_tab = score_rel_error(s, ref), score_rel_error(s_tab, ref)
+    print(f"score rel error b_avg={b_avg}: fp32 {err:.2e}, decode tables {err_tab:.2e}")
+    assert err < 1e-5 and err_tab < SCORE_TOL
     # retention: argmax over compressed scores vs argmax over exact scores, GPU vs oracle
     real = orc.logits(qq, keys.unsqueeze(0))
     ret_gpu = (s.argmax(-1) == real.argmax(-1)).float().mean().item()
@@ -65,12 +66,13 @@ def test_scores_gqa_groups(hq, hkv, dtype):
     packed = paged.compress(tables, kb, [777, 130])
     g = torch.Generator().manual_seed(hq)
     q = torch.randn(2, hq, 3, 128, generator=g).to(dtype)
-    s = paged.score(packed, q.cuda()).cpu()
     k_hat = _k_hat_from_packed(packed, comps)
     ref = orc.logits(q.float(), k_hat)
-    assert score_rel_error(s[0], ref[0]) < SCORE_TOL
-    assert score_rel_error(s[1, :, :, :130], ref[1, :, :, :130]) < SCORE_TOL
-    assert float(s[1, :, :, 130:].abs().max()) == 0.0
+    for tables_mode in (False, True):
+        s = paged.score(packed, q.cuda(), decode_tables=tables_mode).cpu()
+        assert score_rel_error(s[0], ref[0]) < SCORE_TOL
+        assert score_rel_error(s[1, :, :, :130], ref[1, :, :, :130]) < SCORE_TOL
+        assert float(s[1, :, :, 130:].abs().max()) == 0.0
 
 
 def _decode_case(lens, hq, hkv, b_avg, tokens_per_split=0, out_dtype=torch.float32, shuffle_pages=False):
