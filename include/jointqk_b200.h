@@ -191,7 +191,8 @@ int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv
  *   q  [n_q_heads][n_tokens][d], k [n_kv_heads][n_tokens][d] of dtype (bf16, f16 or f32); tokens are
  *      d elements apart, heads q_head_stride / k_head_stride elements apart
  *   sq_sum, sk_sum, cqk_sum  float [n_kv_heads][d][d]; any of them may be NULL to skip it
- *   workspace / workspace_bytes: scratch from jqk_moments_workspace_bytes (may be 0 bytes)
+ *   workspace / workspace_bytes: scratch from jqk_moments_workspace_bytes; its first int32 is a
+ *      device status word (JQK_STATUS_*), OR-ed by the kernel, zeroed by the caller; may be NULL
  */
 int32_t jqk_moments_accumulate(const void* q, const void* k, int32_t dtype, int64_t n_tokens,
                                int64_t q_head_stride, int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,

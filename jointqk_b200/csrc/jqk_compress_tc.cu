@@ -196,19 +196,33 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       for (int c0 = c_lo & ~15; c0 < c_hi; c0 += 16) {
         float v[16];
         tmem_ld16(t_lane + c0, v);
+        // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
+        // their last level); keeping them branch-free lets the loads of all 16 overlap
+        uint32_t code[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float* th = sm.thr + (c0 + i) * 16;
+          uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
+          k += (v[i] >= th[k + 3]) ? 4u : 0u;
+          k += (v[i] >= th[k + 1]) ? 2u : 0u;
+          k += (v[i] >= th[k]) ? 1u : 0u;
+          code[i] = k;
+        }
+        int mt[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) mt[i] = sm.meta[c0 + i];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const int c = c0 + i;
           if (c >= c_lo && c < c_hi) {  // warp-uniform
-            const int m = sm.meta[c];
-            const int bp = (m >> 4) & 1023;
+            const int bp = (mt[i] >> 4) & 1023;
             const int w = bp >> 5;
             while (cur_w < w) {  // finished words (and pad words) leave in order
               if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
               cur = 0;
               ++cur_w;
             }
-            cur |= search_code(v[i], sm.thr + c * 16, m & 15) << (bp & 31);
+            cur |= code[i] << (bp & 31);
           }
         }
       }

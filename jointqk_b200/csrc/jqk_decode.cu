@@ -21,11 +21,14 @@
 //     no registers or shared memory, so HBM latency is hidden independently of occupancy;
 //   * partial results of the splits are merged by the last block to finish (atomic ticket),
 //     no second launch.
+#include <limits.h>
+
 #include "jqk_tables.cuh"
 
 namespace jqk {
 
-constexpr int DEC_THREADS = TBL_THREADS;
+constexpr int SCORE_THREADS = TBL_THREADS;
+constexpr int DEC_THREADS = 384;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int TILE_TOK = 32;        // keys per warp step (two pages)
 constexpr int PREFETCH_TILES = 4;   // how far ahead of the compute the L2 prefetch runs
@@ -36,7 +39,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 // ---------------------------------------------------------------------------------------
 constexpr int SCORE_CHUNK = 2048;
 
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(SCORE_THREADS)
 score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int q_dtype, int n_q_heads, int n_queries,
              const int32_t* __restrict__ seq_lens, int max_tokens, const int32_t* __restrict__ page_table,
              int pt_stride, int n_pages, const uint32_t* __restrict__ k_pool, float* __restrict__ scores,
@@ -67,7 +70,7 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
     float sv[JQK_MAX_GROUP];
     if (table_mode) {  // the decode kernel's fixed-point tables
       int acc[JQK_MAX_GROUP];
-      score_record(kp, sm.lut, sm.dshift, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
+      score_record([kp](int w) { return __ldg(kp + w * JQK_PAGE_TOKENS); }, sm, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) sv[h] = (float)acc[h] * sm.scale[h];
     } else {           // plain fp32: sum_c q'_c * cb[c][code_c], column after column
@@ -105,18 +108,32 @@ struct DecodeWs {
 
 struct DecodeSmem {
   TableSmem t;
+  uint4 vbuf[DEC_WARPS][2][4][2][TILE_TOK];                   // V pieces of one tile per warp, [block][key][piece][lane]
+  uint32_t kbuf[DEC_WARPS][2][JQK_MAX_WORDS][TILE_TOK];       // record words of two tiles per warp, [word][lane]
   __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
 };
-// t.part doubles as the per-warp output staging [DEC_WARPS][JQK_MAX_GROUP][128] after the prologue.
-static_assert(sizeof(float) * 8 * JQK_MAX_COLS * JQK_MAX_GROUP >= sizeof(float) * DEC_WARPS * JQK_MAX_GROUP * JQK_MAX_DIM,
-              "projection scratch too small to stage the warp outputs");
+// vbuf doubles as the per-warp output staging [DEC_WARPS][JQK_MAX_GROUP][128] floats after the last tile.
+static_assert(sizeof(uint4) * 2 * 4 * 2 * TILE_TOK >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM,
+              "a warp's V staging must be able to hold its partial output");
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == JQK_DTYPE_F32) ((float*)out)[idx] = v;
   else ((__nv_bfloat16*)out)[idx] = __float2bfloat16(v);
+}
+
+// 4-byte asynchronous copy global -> shared; every lane stages the words it will read itself.
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_but_two() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
+// 16-byte asynchronous copy that bypasses L1; src_bytes = 0 writes zeros instead of reading.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src), "r"(src_bytes) : "memory");
 }
 
 __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
@@ -201,8 +218,44 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.scale[h] * f;
   }
-  const uint2* lut = sm.t.lut;
   const int n_a_words = hd.n_a_words, n_c_words = hd.n_c_words, n_words = hd.n_words;
+
+  // Stages the record words of tile `r` of this warp (one key per lane) into kbuf[r & 1].
+  auto stage_keys = [&](int r, int pg_lo, int pg_hi) {
+    const int tok = t_begin + (tile_lo + r) * TILE_TOK + lane;
+    const int pg = (lane < 16) ? pg_lo : pg_hi;
+    if (tok < t_end && pg >= 0) {
+      const uint32_t* src = k_head + (size_t)pg * k_page_words + (lane & 15);
+      uint32_t* dst = &sm.kbuf[warp][r & 1][0][lane];
+      for (int w = 0; w < n_words; ++w) cp_async_4(dst + w * TILE_TOK, src + w * JQK_PAGE_TOKENS);
+    }
+    cp_async_commit();  // one group per tile, also when this lane has nothing to copy
+  };
+  // Stages the V pieces this lane turns into MMA fragments for tile `r` (keys 2c, 2c+1, 2c+8, 2c+9
+  // of both 16-key blocks, dims 8g.. and 64+8g..); keys past the end of the split are zero-filled.
+  auto stage_values = [&](int r, int pg_lo, int pg_hi) {
+    const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      const int pg = kb ? pg_hi : pg_lo;
+      const bool blk_ok = pg >= 0 && t0 + 16 * kb < t_end;
+      const __nv_bfloat16* vp = v_head + (size_t)(blk_ok ? pg : 0) * v_page_elems + 8 * g;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int slot = 2 * c + (s & 1) + 8 * (s >> 1);
+        const uint32_t nbytes = (blk_ok && t0 + 16 * kb + slot < t_end) ? 16u : 0u;
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) cp_async_16(&sm.vbuf[warp][kb][s][ch][lane], vp + slot * D + 64 * ch, nbytes);
+      }
+    }
+    cp_async_commit();
+  };
+  // Copy groups are committed in the order K(0), V(0), K(1), V(1), K(2), ...: K(r+1) at the top of
+  // tile r, V(r+1) at its bottom (when the fragments of tile r have been consumed).
+  {
+    const int p0 = __shfl_sync(0xffffffffu, pg_cur, 0), p1 = __shfl_sync(0xffffffffu, pg_cur, 1);
+    if (n_my > 0) { stage_keys(0, p0, p1); stage_values(0, p0, p1); } else { cp_async_commit(); cp_async_commit(); }
+  }
 
   float m_run[JQK_MAX_GROUP], l_run[JQK_MAX_GROUP];
 #pragma unroll
@@ -230,57 +283,48 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
     const int page_lo = __shfl_sync(0xffffffffu, pg_cur, (r & 15) << 1);
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
-
-    // ---- V rows for the two 16-key blocks of the tile, straight into registers ----
-    uint4 vr[2][4][NCH];  // [block][key 2c, 2c+1, 2c+8, 2c+9][piece]
-#pragma unroll
-    for (int kb = 0; kb < 2; ++kb) {
-      const int pg = kb ? page_hi : page_lo;
-      const bool blk_ok = pg >= 0 && t0 + 16 * kb < t_end;
-      const __nv_bfloat16* vp = v_head + (size_t)(blk_ok ? pg : 0) * v_page_elems + 8 * g;
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const int slot = 2 * c + (s & 1) + 8 * (s >> 1);
-        const bool ok = blk_ok && t0 + 16 * kb + slot < t_end;
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch)
-          vr[kb][s][ch] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + slot * D + 64 * ch)) : make_uint4(0u, 0u, 0u, 0u);
-      }
+    {  // record words of the next tile go in flight now and land while this tile is computed
+      const int rn = r + 1;
+      const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
+      const int nlo = __shfl_sync(0xffffffffu, src, (rn & 15) << 1);
+      const int nhi = __shfl_sync(0xffffffffu, src, ((rn & 15) << 1) | 1);
+      if (rn < n_my) stage_keys(rn, nlo, nhi); else cp_async_commit();
     }
 
-    // ---- score this lane's key ----
+    // ---- score this lane's key from the staged record words ----
+    cp_async_wait_but_two();  // K(r) has landed; V(r) and K(r+1) may still be in flight
     const int tok = t0 + lane;
-    const int my_page = (lane < 16) ? page_lo : page_hi;
-    float s[JQK_MAX_GROUP];
-    if (tok < t_end && my_page >= 0) {
-      int ia[JQK_MAX_GROUP];
-      score_record(k_head + (size_t)my_page * k_page_words + (lane & 15), lut, sm.t.dshift, n_a_words, n_c_words, n_words, ia);
+    const bool lane_ok = tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
+    int ia[JQK_MAX_GROUP];
+    {
+      const uint32_t* kw = &sm.kbuf[warp][r & 1][0][lane];
+      score_record([kw](int w) { return kw[w * 32]; }, sm.t, n_a_words, n_c_words, n_words, ia);
+    }
+    if (!lane_ok) {
 #pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = (float)ia[h] * sc[h];
-    } else {
-#pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) s[h] = -CUDART_INF_F;
+      for (int h = 0; h < JQK_MAX_GROUP; ++h) ia[h] = INT_MIN;
     }
 
-    // ---- online softmax (warp-uniform maxima) ----
+    // ---- online softmax: the tile maximum is an integer reduction (scores are scale * integer);
+    //      the sum of the weights stays per lane and is reduced once after the last tile ----
     float alpha[JQK_MAX_GROUP];
     bool any = false, grew = false;
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      const float m_new = fmaxf(m_run[h], warp_max(s[h]));
+      const int imax = __reduce_max_sync(0xffffffffu, ia[h]);
       alpha[h] = 1.f;
       float p = 0.f;
-      if (m_new > -CUDART_INF_F) {
+      if (imax != INT_MIN) {
         any = true;
-        if (m_new > m_run[h]) { alpha[h] = exp2f(m_run[h] - m_new); grew = true; }
-        p = exp2f(s[h] - m_new);
+        const float m_new = fmaxf(m_run[h], (float)imax * sc[h]);
+        if (m_new > m_run[h]) { alpha[h] = exp2f(m_run[h] - m_new); grew = true; m_run[h] = m_new; }
+        if (lane_ok) p = exp2f((float)ia[h] * sc[h] - m_new);
       }
       const __nv_bfloat16 p_hi = __float2bfloat16(p);
       const __nv_bfloat16 p_lo = __float2bfloat16(p - __bfloat162float(p_hi));
       sm.pbuf[warp][0][h][lane] = p_hi;
       sm.pbuf[warp][1][h][lane] = p_lo;
-      l_run[h] = l_run[h] * alpha[h] + warp_sum(__bfloat162float(p_hi) + __bfloat162float(p_lo));
-      m_run[h] = m_new;
+      l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
     __syncwarp();
     if (any) {
@@ -290,6 +334,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
         for (int j = 0; j < NCH * 4; ++j) { acc[j][0] *= a_even; acc[j][1] *= a_odd; acc[j][2] *= a_even; acc[j][3] *= a_odd; }
       }
+      cp_async_wait_but_one();  // V(r) has landed
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         if (t0 + 16 * kb >= t_end) break;
@@ -302,10 +347,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         }
 #pragma unroll
         for (int ch = 0; ch < NCH; ++ch) {
-          const uint32_t ra[4] = {vr[kb][0][ch].x, vr[kb][0][ch].y, vr[kb][0][ch].z, vr[kb][0][ch].w};
-          const uint32_t rb[4] = {vr[kb][1][ch].x, vr[kb][1][ch].y, vr[kb][1][ch].z, vr[kb][1][ch].w};
-          const uint32_t rc2[4] = {vr[kb][2][ch].x, vr[kb][2][ch].y, vr[kb][2][ch].z, vr[kb][2][ch].w};
-          const uint32_t rd[4] = {vr[kb][3][ch].x, vr[kb][3][ch].y, vr[kb][3][ch].z, vr[kb][3][ch].w};
+          const uint4 va = sm.vbuf[warp][kb][0][ch][lane], vb = sm.vbuf[warp][kb][1][ch][lane];
+          const uint4 vc = sm.vbuf[warp][kb][2][ch][lane], vd = sm.vbuf[warp][kb][3][ch][lane];
+          const uint32_t ra[4] = {va.x, va.y, va.z, va.w}, rb[4] = {vb.x, vb.y, vb.z, vb.w};
+          const uint32_t rc2[4] = {vc.x, vc.y, vc.z, vc.w}, rd[4] = {vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint32_t a0 = __byte_perm(ra[j], rb[j], 0x5410), a1 = __byte_perm(ra[j], rb[j], 0x7632);
@@ -316,11 +361,22 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         }
       }
     }
+    {  // the fragments of this tile are in registers or consumed: V of the next tile may overwrite them
+      const int rn = r + 1;
+      const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
+      const int nlo = __shfl_sync(0xffffffffu, src, (rn & 15) << 1);
+      const int nhi = __shfl_sync(0xffffffffu, src, ((rn & 15) << 1) | 1);
+      if (rn < n_my) stage_values(rn, nlo, nhi); else cp_async_commit();
+    }
     __syncwarp();  // pbuf is rewritten by the next tile
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
 
-  // ---- combine the warps of this block (t.part is free after the prologue) ----------------
-  float* wacc = &sm.t.part[0][0][0];  // [DEC_WARPS][JQK_MAX_GROUP][128]
+  // ---- combine the warps of this block (each warp reuses its own V staging) ---------------
+  float* wacc = reinterpret_cast<float*>(&sm.vbuf[0][0][0][0][0]);  // warp w at w * WACC_STRIDE floats
+  constexpr int WACC_STRIDE = (int)(sizeof(uint4) * 2 * 4 * 2 * TILE_TOK / sizeof(float));
+#pragma unroll
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) l_run[h] = warp_sum(l_run[h]);
   if (lane == 0) {
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) { sm.wm[warp][h] = m_run[h]; sm.wl[warp][h] = l_run[h]; }
@@ -331,7 +387,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int dim = 64 * ch + 8 * g + 2 * j;
-        float* w0 = wacc + ((size_t)warp * JQK_MAX_GROUP + 2 * c) * JQK_MAX_DIM + dim;
+        float* w0 = wacc + (size_t)warp * WACC_STRIDE + (2 * c) * JQK_MAX_DIM + dim;
         float* w1 = w0 + JQK_MAX_DIM;
         w0[0] = acc[ch * 4 + j][0]; w1[0] = acc[ch * 4 + j][1];
         w0[1] = acc[ch * 4 + j][2]; w1[1] = acc[ch * 4 + j][3];
@@ -350,7 +406,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       for (int w = 0; w < DEC_WARPS; ++w) {
         const float f = exp2f(sm.wm[w][h] - M);
         L += sm.wl[w][h] * f;
-        A += wacc[((size_t)w * JQK_MAX_GROUP + h) * JQK_MAX_DIM + i] * f;
+        A += wacc[(size_t)w * WACC_STRIDE + h * JQK_MAX_DIM + i] * f;
       }
     }
     const size_t qrow = (size_t)seq * n_q_heads + qh0 + h;
@@ -417,7 +473,7 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
 
 extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                             int32_t max_seq_len) {
-  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level
+  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (384 keys)
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return unit;
   const long long items = (long long)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
   const long long target_blocks = 148;  // one resident block per SM
@@ -447,7 +503,7 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_
   dim3 grid((max_tokens + SCORE_CHUNK - 1) / SCORE_CHUNK, tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads),
             n_seqs * n_queries);
   JQK_SMEM_ONCE(score_kernel, sizeof(TableSmem), "score smem attribute");
-  score_kernel<<<grid, DEC_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
+  score_kernel<<<grid, SCORE_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
       *tables, table_mode, q, q_dtype, n_q_heads, n_queries, seq_lens, max_tokens, page_table, page_table_stride,
       n_pages, k_pool, scores, status);
   JQK_CUDA_OK(cudaGetLastError(), "score launch");

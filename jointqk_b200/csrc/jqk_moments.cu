@@ -5,7 +5,14 @@
 // (experiments/stage1/calibration/compute_stats.py:118-123) and the streaming accumulators of
 // experiments/stage1/toolkit/moments.py:68,110.  All three are X^T Y contractions over tokens:
 //   sq[h] = sum_g Q_g^T Q_g,  sk[h] = K^T K,  cqk[h] = (1/G) sum_g Q_g^T K.
+#include <stdlib.h>
+
 #include "jqk_common.cuh"
+
+// Tensor-core path (jqk_moments_tc.cu): 0 = launched, 1 = call does not fit it, else an error code.
+int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t n_tokens, int64_t q_head_stride,
+                           int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
+                           float* sk_sum, float* cqk_sum, int32_t* status, cudaStream_t st);
 
 namespace jqk {
 
@@ -81,14 +88,14 @@ using namespace jqk;
 
 extern "C" size_t jqk_moments_workspace_bytes(int64_t n_tokens, int32_t n_q_heads, int32_t n_kv_heads, int32_t d) {
   (void)n_tokens; (void)n_q_heads; (void)n_kv_heads; (void)d;
-  return 0;
+  return sizeof(int32_t);  // one status word
 }
 
 extern "C" int32_t jqk_moments_accumulate(const void* q, const void* k, int32_t dtype, int64_t n_tokens,
                                           int64_t q_head_stride, int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
                                           float* sk_sum, float* cqk_sum, void* workspace,
                                           size_t workspace_bytes, void* stream) {
-  (void)workspace; (void)workspace_bytes;
+  int32_t* status = (workspace && workspace_bytes >= sizeof(int32_t)) ? (int32_t*)workspace : nullptr;
   if (n_tokens < 0) return fail(JQK_E_ARG, "negative n_tokens");
   if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads) return fail(JQK_E_ARG, "GQA mismatch: q_heads=%d, kv_heads=%d", n_q_heads, n_kv_heads);
   if (d <= 0 || d > JQK_MAX_DIM || d % 16) return fail(JQK_E_UNSUPPORTED, "head_dim %d must be a multiple of 16 and at most %d", d, JQK_MAX_DIM);
@@ -97,6 +104,15 @@ extern "C" int32_t jqk_moments_accumulate(const void* q, const void* k, int32_t 
     return fail(JQK_E_ARG, "head stride smaller than n_tokens * d");
   if (!k || ((sq_sum || cqk_sum) && !q)) return fail(JQK_E_ARG, "null q or k");
   if (n_kv_heads > 65535) return fail(JQK_E_UNSUPPORTED, "too many kv heads");
+  {
+    // bf16 inputs of head_dim 128 with at most 4 q heads per kv head go to the tensor-core kernel
+    static const bool tc_off = getenv("JQK_DISABLE_TENSOR_CORE_MOMENTS") != nullptr;
+    if (!tc_off) {
+      const int32_t r = jqk_moments_tc_try(q, k, dtype, n_tokens, q_head_stride, k_head_stride, n_q_heads, n_kv_heads, d,
+                                           sq_sum, sk_sum, cqk_sum, status, (cudaStream_t)stream);
+      if (r != 1) return r;
+    }
+  }
   const long long chunks = (n_tokens + MOM_CHUNK - 1) / MOM_CHUNK;
   if (chunks > 0x7fffffffLL) return fail(JQK_E_UNSUPPORTED, "n_tokens too large for one call");
   dim3 grid((unsigned)chunks, n_kv_heads, 3);

@@ -1,0 +1,209 @@
+// Calibration moments on the tensor cores (bf16 inputs, head_dim 128, group size <= 4).
+//
+// Same sums as moments_simt_kernel (jqk_moments.cu); reference:
+// experiments/stage1/calibration/compute_stats.py:118-123.  For one kv head
+//   sq  = sum_g Q_g^T Q_g,   sk = K^T K,   cqk = (1/G) sum_g Q_g^T K
+// are X^T Y contractions over tokens.  A token tile [64 tokens][128 dims] that TMA drops into
+// shared memory with the 128-byte swizzle is, as it stands, an MN-major tcgen05 operand (the
+// 128 dims are the M or N index, tokens are K), so one copy of a tile serves as A and as B:
+// nothing is transposed or staged twice.  Per 16 tokens the block issues 1 + 2G MMAs
+// (M = N = 128, K = 16, bf16 in, fp32 accumulate) into three 128-column TMEM accumulators.
+//
+// A block owns a chunk of 2048 tokens of one kv head; at the end of the chunk four epilogue
+// warps read the accumulators and add them to the outputs with vector reductions
+// (red.global.add.v4.f32).  Short chunks bound the length of each fp32 running sum, which keeps
+// the result as accurate as a blocked CPU summation.
+//
+//   warp 0  TMA producer (G + 1 tiles per stage, 2 stages)     warp 1  TMEM owner + MMA issuer
+//   warps 2..5  epilogue
+// Every mbarrier wait is bounded in time (see tc_wait in jqk_compress_tc.cu for the policy).
+#include <stdlib.h>
+
+#include "jqk_common.cuh"
+#include "jqk_sm100.cuh"
+
+namespace jqk {
+
+using namespace sm100;
+
+constexpr int MT_TOK = 64;             // tokens per tile
+constexpr int MT_STAGES = 2;
+constexpr int MT_CHUNK = 2048;         // default tokens per block
+constexpr int MT_THREADS = 192;
+constexpr uint32_t MT_TILE_BYTES = MT_TOK * 128 * 2;  // one head's tile: two boxes of [64 tokens][64 dims]
+constexpr uint32_t MT_TMEM_COLS = 512;
+constexpr unsigned long long MT_WAIT_NS = 2000000000ull;
+
+struct MtSmem {
+  uint8_t tile[MT_STAGES][JQK_MAX_GROUP + 1][MT_TILE_BYTES];  // [stage][q_0..q_{G-1}, k]
+  uint64_t full[MT_STAGES], empty[MT_STAGES], done;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ bool mt_wait(MtSmem& sm, uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (sm.abort) return false;
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > MT_WAIT_NS) { sm.abort = 1; return false; }
+  }
+}
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(MT_THREADS, 1)
+moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                  long long n_tokens, int chunk, int group, float* __restrict__ sq, float* __restrict__ sk,
+                  float* __restrict__ cqk, int32_t* wait_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  MtSmem& sm = *reinterpret_cast<MtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int head = blockIdx.y;
+  const long long t_begin = (long long)blockIdx.x * chunk;
+  const long long t_end = min(n_tokens, t_begin + chunk);
+  const int n_tiles = (int)((t_end - t_begin + MT_TOK - 1) / MT_TOK);
+  const bool want_q = (sq != nullptr) || (cqk != nullptr);
+
+  if (tid == 0) {
+    for (int s = 0; s < MT_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    mbar_init(&sm.done, 1);
+    sm.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(&sm.tmem_base, MT_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&k_map);
+      if (want_q) tma_prefetch_desc(&q_map);
+      const uint32_t bytes = (want_q ? group + 1 : 1) * MT_TILE_BYTES;
+      int issued = 0;
+      for (int t = 0; t < n_tiles; ++t, ++issued) {
+        const int s = issued % MT_STAGES;
+        if (issued >= MT_STAGES && !mt_wait(sm, &sm.empty[s], ((issued / MT_STAGES) & 1) ^ 1)) break;
+        const int tok = (int)(t_begin + (long long)t * MT_TOK);
+        mbar_arrive_expect_tx(&sm.full[s], bytes);
+        for (int half = 0; half < 2; ++half) {
+          if (want_q)
+            for (int g = 0; g < group; ++g)
+              tma_load_3d(sm.tile[s][g] + half * (MT_TILE_BYTES / 2), &q_map, &sm.full[s], 64 * half, tok, head * group + g);
+          tma_load_3d(sm.tile[s][JQK_MAX_GROUP] + half * (MT_TILE_BYTES / 2), &k_map, &sm.full[s], 64 * half, tok, head);
+        }
+      }
+      if (sm.abort)
+        for (int i = max(0, issued - MT_STAGES); i < issued; ++i) mt_wait(sm, &sm.full[i % MT_STAGES], (i / MT_STAGES) & 1);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(128, 128, true, true);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % MT_STAGES;
+        if (!mt_wait(sm, &sm.full[s], (t / MT_STAGES) & 1)) break;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(sm.tile[s][JQK_MAX_GROUP]);
+#pragma unroll
+        for (int ks = 0; ks < MT_TOK / 16; ++ks) {
+          const bool first = (t == 0 && ks == 0);
+          // 16 tokens further along K is 16 rows of 128 bytes; the second 64-dim block is half a tile away
+          const uint64_t k_desc = make_smem_desc_sw128(k_base + ks * 2048, MT_TILE_BYTES / 2, 1024);
+          if (sk) umma_bf16(tmem + 128, k_desc, k_desc, idesc, !first);
+          if (want_q) {
+            for (int g = 0; g < group; ++g) {
+              const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sm.tile[s][g]) + ks * 2048, MT_TILE_BYTES / 2, 1024);
+              if (sq) umma_bf16(tmem + 0, q_desc, q_desc, idesc, !(first && g == 0));
+              if (cqk) umma_bf16(tmem + 256, q_desc, k_desc, idesc, !(first && g == 0));
+            }
+          }
+        }
+        umma_commit(&sm.empty[s]);
+      }
+      umma_commit(&sm.done);
+    }
+  } else {
+    // epilogue: lane of TMEM = row (dim of the first factor), column = dim of the second factor
+    if (mt_wait(sm, &sm.done, 0) && !sm.abort) {
+      tc_fence_after();
+      const int row = 32 * (warp & 3) + lane;
+      const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+      float* outs[3] = {sq, sk, cqk};
+      const float scale[3] = {1.f, 1.f, 1.f / (float)group};
+#pragma unroll 1
+      for (int m = 0; m < 3; ++m) {
+        if (!outs[m]) continue;
+        float* dst = outs[m] + ((size_t)head * 128 + row) * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+          float v[16];
+          tmem_ld16(t_lane + m * 128 + c0, v);
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            red_add_v4(dst + c0 + i, v[i] * scale[m], v[i + 1] * scale[m], v[i + 2] * scale[m], v[i + 3] * scale[m]);
+        }
+      }
+    }
+  }
+  if (sm.abort && tid == 0 && wait_flag) atomicOr(wait_flag, JQK_STATUS_WAIT_EXPIRED);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, MT_TMEM_COLS);
+  }
+}
+
+}  // namespace jqk
+
+using namespace jqk;
+
+// Launches the tensor-core kernel when the call fits it; returns 1 when the caller should use the
+// CUDA-core kernel (other dtypes, head sizes, group sizes, unaligned strides, key-only calls).
+int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t n_tokens, int64_t q_head_stride,
+                           int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
+                           float* sk_sum, float* cqk_sum, int32_t* status, cudaStream_t st) {
+  const int group = n_q_heads / n_kv_heads;
+  if (dtype != JQK_DTYPE_BF16 || d != 128 || group > JQK_MAX_GROUP || n_tokens < MT_TOK || n_tokens > 0x7fffffffLL) return 1;
+  const bool want_q = sq_sum || cqk_sum;
+  if ((uintptr_t)k % 16 || (k_head_stride * 2) % 16) return 1;
+  if (want_q && (!q || (uintptr_t)q % 16 || (q_head_stride * 2) % 16)) return 1;
+  for (float* o : {sq_sum, sk_sum, cqk_sum})
+    if (o && (uintptr_t)o % 16) return 1;
+  CUtensorMap q_map, k_map;
+  char err[256];
+  const uint32_t box[3] = {64, MT_TOK, 1};
+  {
+    const uint64_t dims[3] = {128, (uint64_t)n_tokens, (uint64_t)n_kv_heads};
+    const uint64_t strides[2] = {256, n_kv_heads > 1 ? (uint64_t)k_head_stride * 2 : 256ull * n_tokens};
+    if (!encode_bf16_map(&k_map, k, 3, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "k tensor map: %s", err);
+  }
+  if (want_q) {
+    const uint64_t dims[3] = {128, (uint64_t)n_tokens, (uint64_t)n_q_heads};
+    const uint64_t strides[2] = {256, n_q_heads > 1 ? (uint64_t)q_head_stride * 2 : 256ull * n_tokens};
+    if (!encode_bf16_map(&q_map, q, 3, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "q tensor map: %s", err);
+  } else {
+    q_map = k_map;
+  }
+  static const int chunk = [] {
+    const char* e = getenv("JQK_MOMENTS_CHUNK");  // tuning knob: tokens per block, a multiple of 64
+    const int v = e ? atoi(e) : 0;
+    return (v >= MT_TOK && v % MT_TOK == 0) ? v : MT_CHUNK;
+  }();
+  dim3 grid((unsigned)((n_tokens + chunk - 1) / chunk), n_kv_heads);
+  const size_t smem = sizeof(MtSmem) + 1024;
+  JQK_SMEM_ONCE(moments_tc_kernel, smem, "tensor-core moments smem attribute");
+  moments_tc_kernel<<<grid, MT_THREADS, smem, st>>>(q_map, k_map, (long long)n_tokens, chunk, group, sq_sum, sk_sum, cqk_sum, status);
+  JQK_CUDA_OK(cudaGetLastError(), "tensor-core moments launch");
+  return 0;
+}

@@ -22,8 +22,8 @@
 
 namespace jqk {
 
-constexpr int TBL_THREADS = 256;  // build_tables is written for exactly this block size
-constexpr int TBL_MAX_SHIFT = 8;  // 29 words x 12 lookups x 2^15 x 2^8 < 2^31
+constexpr int TBL_THREADS = 256;  // threads that take part in the query projection (blocks may be larger)
+constexpr int TBL_MAX_SHIFT = 7;  // 320 lookups x 2^16 x 2^7 < 2^32: the packed sums stay recoverable
 constexpr int TBL_WORDS = 2 * JQK_MAX_WORDS;  // nibble words, then byte words
 
 struct TableSmem {
@@ -38,6 +38,7 @@ struct TableSmem {
   unsigned int wmax[TBL_WORDS][JQK_MAX_GROUP];   // per scan-order word: largest |entry| per head
   int kshift[TBL_WORDS];                         // K_w
   int dshift[TBL_WORDS];                         // K_w - K_{w-1}
+  unsigned int bias;                             // what the +32768 offsets of the low halves add up to
 };
 
 // Scan-order word of table t: nibble word t/8, or n_a_words + byte word.
@@ -70,32 +71,33 @@ __device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&
 __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_tables& tb, int head,
                                              const HeadDesc& hd, const void* q_base, int q_dtype,
                                              size_t q_head_stride, int n_group) {
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
   const int d = hd.d;
-  const int cg = tid & 31, rg = tid >> 5;  // columns 4*cg..4*cg+3, rows rg + 8*r
+  const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
+  const bool projector = tid < TBL_THREADS;
   const float4* P4 = reinterpret_cast<const float4*>(tb.qproj_cols + (size_t)head * d * 128);
   float4 w[JQK_MAX_DIM / 8];
 #pragma unroll
   for (int r = 0; r < JQK_MAX_DIM / 8; ++r) {
     const int i = rg + 8 * r;
-    w[r] = (i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+    w[r] = (projector && i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (int e = tid; e < JQK_MAX_GROUP * JQK_MAX_DIM; e += TBL_THREADS) {
+  for (int e = tid; e < JQK_MAX_GROUP * JQK_MAX_DIM; e += nthr) {
     const int h = e / JQK_MAX_DIM, i = e % JQK_MAX_DIM;
     sm.qraw[h][i] = (h < n_group && i < d) ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
   }
   {
     const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
     float4* dst = reinterpret_cast<float4*>(sm.cb);
-    for (int e = tid; e < hd.n_cols * 4; e += TBL_THREADS) dst[e] = __ldg(cb4 + e);
+    for (int e = tid; e < hd.n_cols * 4; e += nthr) dst[e] = __ldg(cb4 + e);
     const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
     int4* fdst = reinterpret_cast<int4*>(sm.fields);
-    for (int e = tid; e < hd.n_tables; e += TBL_THREADS) fdst[e] = __ldg(f4 + e);
+    for (int e = tid; e < hd.n_tables; e += nthr) fdst[e] = __ldg(f4 + e);
   }
   if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
   if (tid < TBL_WORDS * JQK_MAX_GROUP) (&sm.wmax[0][0])[tid] = 0u;
   __syncthreads();
-  {
+  if (projector) {
     float a[4][JQK_MAX_GROUP];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
@@ -130,7 +132,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
   const int n_entries = hd.n_tables * 16;
   const int n_scan_words = hd.n_a_words + hd.n_c_words;
   // pass 1: largest |entry| per (word, head); 16 consecutive threads share a table
-  for (int e = tid; e < n_entries; e += TBL_THREADS) {
+  for (int e = tid; e < n_entries; e += nthr) {
     float v[JQK_MAX_GROUP];
     table_entry(sm, e, v);
     const int w = table_word(e >> 4, hd.n_a_words);
@@ -168,6 +170,10 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     int prev = 0;
     for (int w = 0; w < n_scan_words; ++w) { sm.dshift[w] = sm.kshift[w] - prev; prev = sm.kshift[w]; }
     const int k_last = n_scan_words ? prev : 0;
+    unsigned int bias = 0u;
+    for (int w = 0; w < n_scan_words; ++w)
+      bias += (unsigned int)((w < hd.n_a_words ? 8 : 12) * 32768) << (k_last - sm.kshift[w]);
+    sm.bias = bias;
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
       const float m = __uint_as_float(sm.absmax[h]);
@@ -180,7 +186,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
   float inv[JQK_MAX_GROUP];
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / __uint_as_float(sm.absmax[h]);
-  for (int e = tid; e < n_entries; e += TBL_THREADS) {
+  for (int e = tid; e < n_entries; e += nthr) {
     float v[JQK_MAX_GROUP];
     table_entry(sm, e, v);
     const float up = (float)(1 << sm.kshift[table_word(e >> 4, hd.n_a_words)]);
@@ -188,70 +194,76 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h] * up)));
     uint2 packed;
-    packed.x = (uint32_t)(q[0] & 0xffff) | ((uint32_t)q[1] << 16);
-    packed.y = (uint32_t)(q[2] & 0xffff) | ((uint32_t)q[3] << 16);
+    // high half: signed value of the odd head; low half: value of the even head plus 32768
+    packed.x = (uint32_t)((q[0] + 32768) & 0xffff) | ((uint32_t)q[1] << 16);
+    packed.y = (uint32_t)((q[2] + 32768) & 0xffff) | ((uint32_t)q[3] << 16);
     sm.lut[e] = packed;
   }
   __syncthreads();
 }
 
-// acc[h] += entry[h] for the four 16-bit lanes of one table entry (sign-extending dot products).
-__device__ __forceinline__ void add_entry(const uint2 e, int (&acc)[JQK_MAX_GROUP]) {
-  acc[0] = __dp2a_lo((int)e.x, 0x00000001, acc[0]);
-  acc[1] = __dp2a_lo((int)e.x, 0x00000100, acc[1]);
-  acc[2] = __dp2a_lo((int)e.y, 0x00000001, acc[2]);
-  acc[3] = __dp2a_lo((int)e.y, 0x00000100, acc[3]);
-}
+// Running sums of one record.  An entry word holds a signed 16-bit value in its high half and an
+// offset (unsigned) one in its low half.  `hi` accumulates floor(word / 65536), which is exactly
+// the high value (one IMAD.HI); `raw` accumulates the whole word modulo 2^32 (one IADD).  The low
+// sum is recovered at the end as raw - 65536 * hi - bias, exact because it stays below 2^32.
+struct ScoreAcc {
+  int hi[2];
+  unsigned int raw[2];
+  __device__ __forceinline__ void clear() { hi[0] = hi[1] = 0; raw[0] = raw[1] = 0u; }
+  __device__ __forceinline__ void shift(int sh) { hi[0] <<= sh; hi[1] <<= sh; raw[0] <<= sh; raw[1] <<= sh; }
+  __device__ __forceinline__ void add(const uint2 e) {
+    asm("mad.hi.s32 %0, %1, 65536, %0;" : "+r"(hi[0]) : "r"(e.x));
+    raw[0] += e.x;
+    asm("mad.hi.s32 %0, %1, 65536, %0;" : "+r"(hi[1]) : "r"(e.y));
+    raw[1] += e.y;
+  }
+  // integer sums of the four heads, in units of scale[h]
+  __device__ __forceinline__ void finish(unsigned int bias, int (&out)[JQK_MAX_GROUP]) const {
+    out[1] = hi[0];
+    out[0] = (int)(raw[0] - ((unsigned int)hi[0] << 16) - bias);
+    out[3] = hi[1];
+    out[2] = (int)(raw[1] - ((unsigned int)hi[1] << 16) - bias);
+  }
+};
 
-// Integer score sums of one record.  `kp` points at word 0 of the key's slot inside its page
-// (words are JQK_PAGE_TOKENS uint32 apart).  Nibble words are scanned from the start of the
-// record, (3,3,2)-byte words from its end; lookups that fall on the other region hit all-zero
-// tables.
-__device__ __forceinline__ void score_record(const uint32_t* __restrict__ kp, const uint2* __restrict__ lut,
-                                             const int* __restrict__ dshift, int n_a_words, int n_c_words,
-                                             int n_words, int (&acc)[JQK_MAX_GROUP]) {
-  uint32_t ra[JQK_MAX_WORDS], rc[JQK_MAX_WORDS];
+// Scores one record.  `word(w)` returns physical word w of the record.  Nibble words are scanned
+// from the start of the record, (3,3,2)-byte words from its end; lookups that fall on the other
+// region hit all-zero tables.  The word loops are not unrolled: the body of one word (8 or 12
+// lookups) is what has to stay in the instruction cache.
+template <typename WordFn>
+__device__ __forceinline__ void score_record(WordFn word, const TableSmem& sm, int n_a_words, int n_c_words,
+                                             int n_words, int (&out)[JQK_MAX_GROUP]) {
+  ScoreAcc acc;
+  acc.clear();
+  const char* lb = reinterpret_cast<const char*>(sm.lut);
+#pragma unroll 1
+  for (int w = 0; w < n_a_words; ++w) {
+    const uint32_t x = word(w);
+    acc.shift(sm.dshift[w]);
+    const char* lw = lb + w * 1024;
 #pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    ra[w] = (w < n_a_words) ? __ldg(kp + w * JQK_PAGE_TOKENS) : 0u;
-    rc[w] = (w < n_c_words) ? __ldg(kp + (n_words - 1 - w) * JQK_PAGE_TOKENS) : 0u;
-  }
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] = 0;
-  const char* lb = reinterpret_cast<const char*>(lut);
-#pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    if (w < n_a_words) {
-      const uint32_t x = ra[w];
-      const int sh = dshift[w];
-#pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] <<= sh;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const uint32_t off = (k == 0) ? ((x << 3) & 0x78u) : ((x >> (4 * k - 3)) & 0x78u);
-        add_entry(*reinterpret_cast<const uint2*>(lb + (w * 8 + k) * 128 + off), acc);
-      }
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t off = (k == 0) ? ((x << 3) & 0x78u) : ((x >> (4 * k - 3)) & 0x78u);
+      acc.add(*reinterpret_cast<const uint2*>(lw + k * 128 + off));
     }
   }
-  const char* lc = lb + n_a_words * 8 * 128;
+  const char* lc = lb + n_a_words * 1024;
+#pragma unroll 1
+  for (int w = 0; w < n_c_words; ++w) {
+    const uint32_t x = word(n_words - 1 - w);
+    acc.shift(sm.dshift[n_a_words + w]);
+    const char* lw = lc + w * 1536;
 #pragma unroll
-  for (int w = 0; w < JQK_MAX_WORDS; ++w) {
-    if (w < n_c_words) {
-      const uint32_t x = rc[w];
-      const int sh = dshift[n_a_words + w];
-#pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) acc[h] <<= sh;
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t o0 = (b == 0) ? ((x << 3) & 0x38u) : ((x >> (8 * b - 3)) & 0x38u);
-        const uint32_t o1 = (x >> (8 * b)) & 0x38u;          // bits 3..5 of the byte, already times 8
-        const uint32_t o2 = (x >> (8 * b + 3)) & 0x18u;      // bits 6..7 of the byte, times 8
-        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 0) * 128 + o0), acc);
-        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 1) * 128 + o1), acc);
-        add_entry(*reinterpret_cast<const uint2*>(lc + (w * 12 + b * 3 + 2) * 128 + o2), acc);
-      }
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t o0 = (b == 0) ? ((x << 3) & 0x38u) : ((x >> (8 * b - 3)) & 0x38u);
+      const uint32_t o1 = (x >> (8 * b)) & 0x38u;      // bits 3..5 of the byte, already times 8
+      const uint32_t o2 = (x >> (8 * b + 3)) & 0x18u;  // bits 6..7 of the byte, times 8
+      acc.add(*reinterpret_cast<const uint2*>(lw + (b * 3 + 0) * 128 + o0));
+      acc.add(*reinterpret_cast<const uint2*>(lw + (b * 3 + 1) * 128 + o1));
+      acc.add(*reinterpret_cast<const uint2*>(lw + (b * 3 + 2) * 128 + o2));
     }
   }
+  acc.finish(sm.bias, out);
 }
 
 }  // namespace jqk

@@ -57,7 +57,28 @@ def accumulate_layer(q: torch.Tensor | None, k: torch.Tensor, sq_sum: torch.Tens
         None if q is None else q.data_ptr(), k.data_ptr(), _native.torch_dtype_code(k.dtype), T,
         0 if q is None else q.stride(0), k.stride(0), n_q, n_kv, d,
         None if sq_sum is None else sq_sum.data_ptr(), None if sk_sum is None else sk_sum.data_ptr(),
-        None if cqk_sum is None else cqk_sum.data_ptr(), None, 0, torch.cuda.current_stream(dev).cuda_stream))
+        None if cqk_sum is None else cqk_sum.data_ptr(), _status_word(dev).data_ptr(), 4,
+        torch.cuda.current_stream(dev).cuda_stream))
+
+
+_STATUS: dict = {}
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    """Per-device status word the moment kernels OR their flags into."""
+    key = (dev.type, dev.index)
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _STATUS[key]
+
+
+def check_status(dev: torch.device | None = None) -> None:
+    """Raise if a moment kernel reported an expired bounded wait (synchronises)."""
+    for key, word in _STATUS.items():
+        if dev is not None and key != (dev.type, dev.index):
+            continue
+        if int(word.item()) & _native.STATUS_WAIT_EXPIRED:
+            raise RuntimeError("jointqk_b200: a bounded device-side wait expired in the moment kernel")
 
 
 def _second_moment_sum(x: torch.Tensor) -> torch.Tensor:
