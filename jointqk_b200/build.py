@@ -45,8 +45,9 @@ def is_stale() -> bool:
     return LIB_PATH.stat().st_mtime < newest
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if needed and return its path."""
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = ()) -> Path:
+    """Compile the library if needed and return its path.  ``defines`` adds -D flags (development
+    builds, e.g. the phase counters of the decode kernel)."""
     if not force and not is_stale():
         return LIB_PATH
     obj_dir = PKG_DIR / "build"
@@ -56,7 +57,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -77,5 +78,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv or any(a.startswith("-D") for a in sys.argv), verbose="-v" in sys.argv,
+                 defines=tuple(a[2:] for a in sys.argv if a.startswith("-D")))
     print(path)

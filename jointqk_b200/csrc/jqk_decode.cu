@@ -156,6 +156,20 @@ __device__ __forceinline__ int load_page_window(const int32_t* __restrict__ page
   return lookup_page(page_table, pt_stride, seq, lp, n_pages, status);
 }
 
+#ifdef JQK_DECODE_PROFILE
+// Development aid: per-phase clock totals of warp 0 of every block (prologue, wait K, score,
+// softmax, wait V, MMA, stage, epilogue).  Not part of the product build.
+__device__ long long g_decode_prof[8];
+#define PROF_MARK(i)                                                        \
+  do {                                                                      \
+    const long long now__ = clock64();                                      \
+    if (tid == 0) atomicAdd((unsigned long long*)&g_decode_prof[i], (unsigned long long)(now__ - prof_t)); \
+    prof_t = now__;                                                         \
+  } while (0)
+#else
+#define PROF_MARK(i) do {} while (0)
+#endif
+
 // NCH = 16-byte pieces of a V row per lane: 2 for head_dim 128, 1 for head_dim 64.
 template <int NCH>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
@@ -211,7 +225,11 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
   }
 
+#ifdef JQK_DECODE_PROFILE
+  long long prof_t = clock64();
+#endif
   build_tables(sm.t, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
+  PROF_MARK(0);
   float sc[JQK_MAX_GROUP];
   {
     const float f = kLog2e / sqrtf((float)D);
@@ -292,7 +310,9 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
 
     // ---- score this lane's key from the staged record words ----
+    PROF_MARK(6);
     cp_async_wait_but_two();  // K(r) has landed; V(r) and K(r+1) may still be in flight
+    PROF_MARK(1);
     const int tok = t0 + lane;
     const bool lane_ok = tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
     int ia[JQK_MAX_GROUP];
@@ -304,6 +324,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) ia[h] = INT_MIN;
     }
+    PROF_MARK(2);
 
     // ---- online softmax: the tile maximum is an integer reduction (scores are scale * integer);
     //      the sum of the weights stays per lane and is reduced once after the last tile ----
@@ -327,6 +348,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
     __syncwarp();
+    PROF_MARK(3);
     if (any) {
       if (grew) {
         const float a_even = (c & 1) ? alpha[2] : alpha[0];  // head 2c   (c >= 2: heads that do not exist)
@@ -335,6 +357,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         for (int j = 0; j < NCH * 4; ++j) { acc[j][0] *= a_even; acc[j][1] *= a_odd; acc[j][2] *= a_even; acc[j][3] *= a_odd; }
       }
       cp_async_wait_but_one();  // V(r) has landed
+      PROF_MARK(4);
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         if (t0 + 16 * kb >= t_end) break;
@@ -361,6 +384,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         }
       }
     }
+    PROF_MARK(5);
     {  // the fragments of this tile are in registers or consumed: V of the next tile may overwrite them
       const int rn = r + 1;
       const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
@@ -371,6 +395,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     __syncwarp();  // pbuf is rewritten by the next tile
   }
   asm volatile("cp.async.wait_all;" ::: "memory");
+  PROF_MARK(6);
 
   // ---- combine the warps of this block (each warp reuses its own V staging) ---------------
   float* wacc = reinterpret_cast<float*>(&sm.vbuf[0][0][0][0][0]);  // warp w at w * WACC_STRIDE floats
@@ -451,6 +476,17 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+#ifdef JQK_DECODE_PROFILE
+extern "C" int32_t jqk_debug_decode_profile(long long* out8, int32_t reset) {
+  if (cudaMemcpyFromSymbol(out8, g_decode_prof, sizeof(long long) * 8) != cudaSuccess) return 1;
+  if (reset) {
+    long long z[8] = {0};
+    if (cudaMemcpyToSymbol(g_decode_prof, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
 
 static int q_blocks_for(int n_q_heads, int n_kv_heads) {
   const int group = n_q_heads / n_kv_heads;
@@ -559,61 +595,4 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   }
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
   return 0;
-}
-
-// ---------------------------------------------------------------------------------------
-// Decode attention for callers that cannot hand over a workspace
-// ---------------------------------------------------------------------------------------
-// The split-key partial results and the per-group tickets live in this fixed array, which every
-// device that loads the library keeps until the process exits.
-static __device__ __align__(256) unsigned char g_decode_scratch[JQK_DECODE_STATIC_SCRATCH_BYTES];
-
-// Device address of g_decode_scratch on the current device.  In host code the array's name is
-// only a handle for the runtime, not an address a kernel could use, so the address is asked for
-// once per device with that device current and remembered; the tickets at the front of the
-// array are zeroed on `st` at that moment (they are zero when the module loads, and every launch
-// leaves them at zero, but an earlier launch that was cut short must not poison this one).
-static int32_t decode_static_scratch(void** out, cudaStream_t st) {
-  static void* addr[64] = {nullptr};
-  int dev = 0;
-  JQK_CUDA_OK(cudaGetDevice(&dev), "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(JQK_E_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
-  if (!addr[dev]) {
-    void* p = nullptr;
-    JQK_CUDA_OK(cudaGetSymbolAddress(&p, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
-    JQK_CUDA_OK(cudaMemsetAsync(p, 0, 65536, st), "clearing the decode tickets");
-    addr[dev] = p;
-  }
-  *out = addr[dev];
-  return 0;
-}
-
-extern "C" int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
-                                            int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
-                                            int32_t tokens_per_split, const int32_t* page_table,
-                                            int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
-                                            const void* v_pool, void* out, int32_t out_dtype, int32_t* status,
-                                            void* stream) {
-  int32_t rc = check_tables(tables);
-  if (rc) return rc;
-  if (n_seqs <= 0 || n_q_heads <= 0 || max_seq_len < 0)
-    return jqk_decode_attend(tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
-                             page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, nullptr, 0, status, stream);
-  if (tokens_per_split == 0) tokens_per_split = jqk_decode_default_split(n_seqs, n_q_heads, tables->n_heads, max_seq_len);
-  if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
-  const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
-  const size_t need = max_splits > 1 ? jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits) : 0;
-  if (need > (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES)
-    return fail(JQK_E_WORKSPACE,
-                "this call needs %zu bytes of split scratch but the built-in array holds %d; use fewer splits "
-                "(larger tokens_per_split), a smaller batch, or jqk_decode_attend with a caller workspace",
-                need, (int)JQK_DECODE_STATIC_SCRATCH_BYTES);
-  if ((size_t)n_seqs * tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads) * sizeof(unsigned int) > 65536)
-    return fail(JQK_E_WORKSPACE, "too many (sequence, head group) pairs for the built-in ticket area");
-  void* scratch = nullptr;
-  rc = decode_static_scratch(&scratch, (cudaStream_t)stream);
-  if (rc) return rc;
-  return jqk_decode_attend(tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
-                           page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, scratch,
-                           (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES, status, stream);
 }

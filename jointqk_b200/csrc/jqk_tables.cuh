@@ -131,18 +131,24 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
   __syncthreads();
   const int n_entries = hd.n_tables * 16;
   const int n_scan_words = hd.n_a_words + hd.n_c_words;
-  // pass 1: largest |entry| per (word, head); 16 consecutive threads share a table
-  for (int e = tid; e < n_entries; e += nthr) {
-    float v[JQK_MAX_GROUP];
-    table_entry(sm, e, v);
-    const int w = table_word(e >> 4, hd.n_a_words);
+  // Largest |entry| per (word, head).  The fields of a table take their codes independently and the
+  // levels are sorted, so the largest |sum| is the sum over fields of |q'_c| * max(|first|, |last| level).
+  for (int t = tid; t < hd.n_tables; t += nthr) {
+    float m[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      float m = fabsf(v[h]);
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-      if ((tid & 15) == 0) atomicMax(&sm.wmax[w][h], __float_as_uint(m));  // non-negative floats order as uints
+    for (int f = 0; f < 4; ++f) {
+      const int fld = sm.fields[t * 4 + f];
+      if (fld < 0) break;
+      const int col = fld & 255, width = (fld >> 8) & 15;
+      const float big = fmaxf(fabsf(sm.cb[col * 16]), fabsf(sm.cb[col * 16 + (1 << width) - 1]));
+      const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[col]);
+      m[0] = fmaf(fabsf(qp.x), big, m[0]); m[1] = fmaf(fabsf(qp.y), big, m[1]);
+      m[2] = fmaf(fabsf(qp.z), big, m[2]); m[3] = fmaf(fabsf(qp.w), big, m[3]);
     }
+    const int w = table_word(t, hd.n_a_words);
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h)
+      atomicMax(&sm.wmax[w][h], __float_as_uint(m[h] * 1.0000005f));  // non-negative floats order as uints
   }
   __syncthreads();
   if (tid < JQK_MAX_GROUP) {
