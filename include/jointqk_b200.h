@@ -176,6 +176,33 @@ int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t 
                           const void* v_pool, void* out, int32_t out_dtype, void* workspace,
                           size_t workspace_bytes, int32_t* status, void* stream);
 
+/*
+ * jqk_decode_attend for callers that must not allocate (no counterpart in the reference, which
+ * leaves all memory to torch).  Some hosts of this library cannot call cudaMalloc on the decode
+ * path at all: a serving engine that has handed every byte of device memory to its own pool at
+ * start-up, a plugin that runs inside another process's memory budget, code that runs while an
+ * allocator lock is held.  For them the split-key scratch is a fixed array inside the library,
+ * JQK_DECODE_STATIC_SCRATCH_BYTES per device, held from the moment the library is loaded on a
+ * device until the process exits.  Inputs and outputs are still the caller's.
+ *
+ *   - a call whose splits need more than the array (see jqk_decode_workspace_bytes) is rejected
+ *     with JQK_E_WORKSPACE and a message that says how much was needed;
+ *   - no cudaMalloc / cudaFree / allocating library routine is called, ever;
+ *   - the first call on a device looks up the array's device address and zeroes its ticket area
+ *     on `stream`; make that first call outside any stream capture;
+ *   - all calls on a device share the one array: two calls that overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it and produce garbage.  Calls that are
+ *     ordered on one stream are safe; each launch leaves the tickets at zero for the next.
+ * Arguments are those of jqk_decode_attend without workspace / workspace_bytes.
+ */
+#define JQK_DECODE_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
+                                 int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                                 int32_t tokens_per_split, const int32_t* page_table,
+                                 int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                                 const void* v_pool, void* out, int32_t out_dtype, int32_t* status,
+                                 void* stream);
+
 /* tokens_per_split that jqk_decode_attend would choose for this shape (host helper). */
 int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                  int32_t max_seq_len);

@@ -596,3 +596,60 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention for callers that cannot hand over a workspace
+// ---------------------------------------------------------------------------------------
+// The split-key partial results and the per-group tickets live in this fixed array, which every
+// device that loads the library keeps until the process exits.
+static __device__ __align__(256) unsigned char g_decode_scratch[JQK_DECODE_STATIC_SCRATCH_BYTES];
+
+// Device address of g_decode_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so the address is asked for
+// once per device with that device current and remembered; the tickets at the front of the
+// array are zeroed on `st` at that moment (they are zero when the module loads, and every launch
+// leaves them at zero, but an earlier launch that was cut short must not poison this one).
+static int32_t decode_static_scratch(void** out, cudaStream_t st) {
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  JQK_CUDA_OK(cudaGetDevice(&dev), "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(JQK_E_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    JQK_CUDA_OK(cudaGetSymbolAddress(&p, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
+    JQK_CUDA_OK(cudaMemsetAsync(p, 0, 65536, st), "clearing the decode tickets");
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return 0;
+}
+
+extern "C" int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
+                                            int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                                            int32_t tokens_per_split, const int32_t* page_table,
+                                            int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                                            const void* v_pool, void* out, int32_t out_dtype, int32_t* status,
+                                            void* stream) {
+  int32_t rc = check_tables(tables);
+  if (rc) return rc;
+  if (n_seqs <= 0 || n_q_heads <= 0 || max_seq_len < 0)
+    return jqk_decode_attend(tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                             page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, nullptr, 0, status, stream);
+  if (tokens_per_split == 0) tokens_per_split = jqk_decode_default_split(n_seqs, n_q_heads, tables->n_heads, max_seq_len);
+  if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
+  const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
+  const size_t need = max_splits > 1 ? jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits) : 0;
+  if (need > (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES)
+    return fail(JQK_E_WORKSPACE,
+                "this call needs %zu bytes of split scratch but the built-in array holds %d; use fewer splits "
+                "(larger tokens_per_split), a smaller batch, or jqk_decode_attend with a caller workspace",
+                need, (int)JQK_DECODE_STATIC_SCRATCH_BYTES);
+  if ((size_t)n_seqs * tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads) * sizeof(unsigned int) > 65536)
+    return fail(JQK_E_WORKSPACE, "too many (sequence, head group) pairs for the built-in ticket area");
+  void* scratch = nullptr;
+  rc = decode_static_scratch(&scratch, (cudaStream_t)stream);
+  if (rc) return rc;
+  return jqk_decode_attend(tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                           page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, scratch,
+                           (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES, status, stream);
+}
