@@ -18,7 +18,10 @@
  *   - a page holds JQK_PAGE_TOKENS consecutive keys of one sequence for all kv heads;
  *   - K pool:  uint32 [n_pages][n_kv_heads][words_per_record][16]; word w of key t of head h
  *     in page p is k_pool[((p*H + h)*words_per_record + w)*16 + t];
- *   - V pool:  bf16   [n_pages][n_kv_heads][16][d];
+ *   - V pool:  bf16   [n_pages][n_kv_heads][d][16], dims-major inside a (page, head) block: the value
+ *     of key slot t, dim i sits at element i*16 + (((t>>3) ^ ((i>>2)&1)) << 3) + (t&7) of the block
+ *     (a 16-dim x 16-key tile is one ldmatrix of the decode kernel; the two 8-key halves of a row
+ *     are swapped on dims 4..7 mod 8 to spread shared-memory banks);
  *   - page_table: int32 [n_seqs][page_table_stride], logical page -> physical page.
  */
 #ifndef JOINTQK_B200_H_

@@ -28,10 +28,9 @@
 namespace jqk {
 
 constexpr int SCORE_THREADS = TBL_THREADS;
-constexpr int DEC_THREADS = 384;
+constexpr int DEC_THREADS = 256;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int TILE_TOK = 32;        // keys per warp step (two pages)
-constexpr int PREFETCH_TILES = 4;   // how far ahead of the compute the L2 prefetch runs
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------
@@ -44,7 +43,7 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
              const int32_t* __restrict__ seq_lens, int max_tokens, const int32_t* __restrict__ page_table,
              int pt_stride, int n_pages, const uint32_t* __restrict__ k_pool, float* __restrict__ scores,
              int32_t* status) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   TableSmem& sm = *reinterpret_cast<TableSmem*>(smem_raw);
   const int group = n_q_heads / tb.n_heads;
   const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
@@ -106,38 +105,68 @@ struct DecodeWs {
   int max_splits;
 };
 
+// Per-warp staging of one tile: the two V pages (dims-major, see the V page layout in the file
+// header) and the two K pages, filled by bulk asynchronous copies that the warp issues itself.
+constexpr int K_STAGE_STRIDE = JQK_MAX_WORDS * JQK_PAGE_TOKENS * 4 + 64;  // +64 B: the two pages hit different banks
+struct alignas(128) TileStage {
+  uint8_t v[2][JQK_PAGE_TOKENS * JQK_MAX_DIM * 2];  // 2 x 4096 B
+  uint8_t k[2][K_STAGE_STRIDE];                     // 2 x 1088 B
+};
+
 struct DecodeSmem {
   TableSmem t;
-  uint4 vbuf[DEC_WARPS][2][4][2][TILE_TOK];                   // V pieces of one tile per warp, [block][key][piece][lane]
-  uint32_t kbuf[DEC_WARPS][2][JQK_MAX_WORDS][TILE_TOK];       // record words of two tiles per warp, [word][lane]
+  TileStage stage[DEC_WARPS][2];
+  uint64_t full[DEC_WARPS][2];
   __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
 };
-// vbuf doubles as the per-warp output staging [DEC_WARPS][JQK_MAX_GROUP][128] floats after the last tile.
-static_assert(sizeof(uint4) * 2 * 4 * 2 * TILE_TOK >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM,
-              "a warp's V staging must be able to hold its partial output");
+// A warp's first stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
+static_assert(sizeof(TileStage) >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM, "stage too small for the partial output");
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == JQK_DTYPE_F32) ((float*)out)[idx] = v;
   else ((__nv_bfloat16*)out)[idx] = __float2bfloat16(v);
 }
 
-// 4-byte asynchronous copy global -> shared; every lane stages the words it will read itself.
-__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Bulk asynchronous copy global -> shared (16-byte aligned, size a multiple of 16), completing on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_but_two() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
-// 16-byte asynchronous copy that bypasses L1; src_bytes = 0 writes zeros instead of reading.
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src), "r"(src_bytes) : "memory");
+__device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait (about two seconds of %globaltimer): a copy that never completes ends in a status
+// bit and a skipped tile, not in a hung device.
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
+  if (bar_try_wait(bar, parity)) return true;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (bar_try_wait(bar, parity)) return true;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;
+  }
 }
 
-__device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -157,8 +186,8 @@ __device__ __forceinline__ int load_page_window(const int32_t* __restrict__ page
 }
 
 #ifdef JQK_DECODE_PROFILE
-// Development aid: per-phase clock totals of warp 0 of every block (prologue, wait K, score,
-// softmax, wait V, MMA, stage, epilogue).  Not part of the product build.
+// Development aid: per-phase clock totals of warp 0 of every block (prologue, wait, score,
+// softmax, -, MMA, issue).  Not part of the product build.
 __device__ long long g_decode_prof[8];
 #define PROF_MARK(i)                                                        \
   do {                                                                      \
@@ -170,16 +199,17 @@ __device__ long long g_decode_prof[8];
 #define PROF_MARK(i) do {} while (0)
 #endif
 
-// NCH = 16-byte pieces of a V row per lane: 2 for head_dim 128, 1 for head_dim 64.
-template <int NCH>
+// D = head_dim (64 or 128).
+template <int D>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
               const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
               const uint32_t* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status) {
-  constexpr int D = 64 * NCH;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int DT = D / 16;                       // 16-dim MMA tiles
+  constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -207,8 +237,9 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const size_t v_page_elems = (size_t)tb.n_heads * JQK_PAGE_TOKENS * D;
   const uint32_t* k_head = k_pool + (size_t)head * wpr * JQK_PAGE_TOKENS;
   const __nv_bfloat16* v_head = v_pool + (size_t)head * JQK_PAGE_TOKENS * D;
+  const uint32_t k_page_bytes = (uint32_t)hd.n_words * JQK_PAGE_TOKENS * 4;
 
-  // ---- this warp's run of tiles, its page ids, and the first prefetches (before the prologue) ----
+  // ---- this warp's run of tiles and its page ids ----
   const int tiles_total = (t_end - t_begin + TILE_TOK - 1) / TILE_TOK;
   const int tiles_per_warp = (tiles_total + DEC_WARPS - 1) / DEC_WARPS;
   const int tile_lo = min(tiles_total, warp * tiles_per_warp);
@@ -216,14 +247,33 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const int lp0 = t_begin / JQK_PAGE_TOKENS + 2 * tile_lo;  // first logical page of this warp
   int pg_cur = load_page_window(page_table, pt_stride, seq, lp0, n_seq_pages, n_pages, status);
   int pg_next = load_page_window(page_table, pt_stride, seq, lp0 + 32, n_seq_pages, n_pages, status);
-  const uint32_t k_page_bytes = (uint32_t)hd.n_words * JQK_PAGE_TOKENS * 4;
-  {
-    const int n_pre = min(2 * PREFETCH_TILES, 2 * n_my);
-    if (lane < n_pre && pg_cur >= 0) {
-      prefetch_l2(v_head + (size_t)pg_cur * v_page_elems, JQK_PAGE_TOKENS * D * 2);
-      prefetch_l2(k_head + (size_t)pg_cur * k_page_words, k_page_bytes);
+
+  if (lane == 0) { bar_init(&sm.full[warp][0], 1); bar_init(&sm.full[warp][1], 1); }
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncwarp();
+
+  // Lane 0 starts the copies of tile `r` (pages pg_lo / pg_hi, -1 = absent) into stage r & 1.  The
+  // stage was last read by this warp two tiles ago, in program order, so no "empty" barrier is needed.
+  auto issue_tile = [&](int r, int pg_lo, int pg_hi) {
+    if (lane == 0) {
+      TileStage& st = sm.stage[warp][r & 1];
+      uint64_t* bar = &sm.full[warp][r & 1];
+      const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
+      const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
+      bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * (V_PAGE_BYTES + k_page_bytes));
+      if (ok0) {
+        bulk_load(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar);
+        bulk_load(st.k[0], k_head + (size_t)pg_lo * k_page_words, k_page_bytes, bar);
+      }
+      if (ok1) {
+        bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
+        bulk_load(st.k[1], k_head + (size_t)pg_hi * k_page_words, k_page_bytes, bar);
+      }
     }
-  }
+  };
+  // the first two tiles go in flight before the prologue, so HBM works while the tables are built
+  if (n_my > 0) issue_tile(0, __shfl_sync(0xffffffffu, pg_cur, 0), __shfl_sync(0xffffffffu, pg_cur, 1));
+  if (n_my > 1) issue_tile(1, __shfl_sync(0xffffffffu, pg_cur, 2), __shfl_sync(0xffffffffu, pg_cur, 3));
 
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
@@ -238,87 +288,39 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   }
   const int n_a_words = hd.n_a_words, n_c_words = hd.n_c_words, n_words = hd.n_words;
 
-  // Stages the record words of tile `r` of this warp (one key per lane) into kbuf[r & 1].
-  auto stage_keys = [&](int r, int pg_lo, int pg_hi) {
-    const int tok = t_begin + (tile_lo + r) * TILE_TOK + lane;
-    const int pg = (lane < 16) ? pg_lo : pg_hi;
-    if (tok < t_end && pg >= 0) {
-      const uint32_t* src = k_head + (size_t)pg * k_page_words + (lane & 15);
-      uint32_t* dst = &sm.kbuf[warp][r & 1][0][lane];
-      for (int w = 0; w < n_words; ++w) cp_async_4(dst + w * TILE_TOK, src + w * JQK_PAGE_TOKENS);
-    }
-    cp_async_commit();  // one group per tile, also when this lane has nothing to copy
-  };
-  // Stages the V pieces this lane turns into MMA fragments for tile `r` (keys 2c, 2c+1, 2c+8, 2c+9
-  // of both 16-key blocks, dims 8g.. and 64+8g..); keys past the end of the split are zero-filled.
-  auto stage_values = [&](int r, int pg_lo, int pg_hi) {
-    const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
-#pragma unroll
-    for (int kb = 0; kb < 2; ++kb) {
-      const int pg = kb ? pg_hi : pg_lo;
-      const bool blk_ok = pg >= 0 && t0 + 16 * kb < t_end;
-      const __nv_bfloat16* vp = v_head + (size_t)(blk_ok ? pg : 0) * v_page_elems + 8 * g;
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        const int slot = 2 * c + (s & 1) + 8 * (s >> 1);
-        const uint32_t nbytes = (blk_ok && t0 + 16 * kb + slot < t_end) ? 16u : 0u;
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) cp_async_16(&sm.vbuf[warp][kb][s][ch][lane], vp + slot * D + 64 * ch, nbytes);
-      }
-    }
-    cp_async_commit();
-  };
-  // Copy groups are committed in the order K(0), V(0), K(1), V(1), K(2), ...: K(r+1) at the top of
-  // tile r, V(r+1) at its bottom (when the fragments of tile r have been consumed).
-  {
-    const int p0 = __shfl_sync(0xffffffffu, pg_cur, 0), p1 = __shfl_sync(0xffffffffu, pg_cur, 1);
-    if (n_my > 0) { stage_keys(0, p0, p1); stage_values(0, p0, p1); } else { cp_async_commit(); cp_async_commit(); }
-  }
-
   float m_run[JQK_MAX_GROUP], l_run[JQK_MAX_GROUP];
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) { m_run[h] = -CUDART_INF_F; l_run[h] = 0.f; }
-  float acc[NCH * 4][4];  // tile (piece ch, j): rows = dims ch*64 + 8g + 2j (+1), cols = heads 2c, 2c+1
+  float acc[DT][4];  // MMA tile j: rows = dims 16j + g (+8), cols = heads 2c, 2c+1
 #pragma unroll
-  for (int j = 0; j < NCH * 4; ++j)
+  for (int j = 0; j < DT; ++j)
 #pragma unroll
     for (int k = 0; k < 4; ++k) acc[j][k] = 0.f;
+  // ldmatrix row address of this lane inside a 16-dim x 16-key block of a V page (32-byte rows; the
+  // two 16-byte halves of a row are swapped on rows 4..7 mod 8 so that eight rows hit eight bank groups)
+  const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+  const uint32_t lm_off = (uint32_t)(lrow * 32 + (((lane >> 4) ^ ((lrow >> 2) & 1)) * 16));
 
   for (int r = 0; r < n_my; ++r) {
     if (r > 0 && (r & 15) == 0) {
       pg_cur = pg_next;
       pg_next = load_page_window(page_table, pt_stride, seq, lp0 + 2 * r + 32, n_seq_pages, n_pages, status);
     }
-    {  // L2 prefetch of the pages PREFETCH_TILES ahead: lanes 0 and 1 take one page each
-      const int rp = r + PREFETCH_TILES;
-      const int src = ((rp >> 4) == (r >> 4)) ? pg_cur : pg_next;
-      const int ppg = __shfl_sync(0xffffffffu, src, ((rp & 15) << 1) | (lane & 1));
-      if (lane < 2 && rp < n_my && ppg >= 0) {
-        prefetch_l2(v_head + (size_t)ppg * v_page_elems, JQK_PAGE_TOKENS * D * 2);
-        prefetch_l2(k_head + (size_t)ppg * k_page_words, k_page_bytes);
-      }
-    }
     const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
     const int page_lo = __shfl_sync(0xffffffffu, pg_cur, (r & 15) << 1);
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
-    {  // record words of the next tile go in flight now and land while this tile is computed
-      const int rn = r + 1;
-      const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
-      const int nlo = __shfl_sync(0xffffffffu, src, (rn & 15) << 1);
-      const int nhi = __shfl_sync(0xffffffffu, src, ((rn & 15) << 1) | 1);
-      if (rn < n_my) stage_keys(rn, nlo, nhi); else cp_async_commit();
-    }
+    TileStage& st = sm.stage[warp][r & 1];
+    const bool landed = bar_wait(&sm.full[warp][r & 1], (r >> 1) & 1);
+    if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+    PROF_MARK(1);
 
     // ---- score this lane's key from the staged record words ----
-    PROF_MARK(6);
-    cp_async_wait_but_two();  // K(r) has landed; V(r) and K(r+1) may still be in flight
-    PROF_MARK(1);
     const int tok = t0 + lane;
-    const bool lane_ok = tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
+    const bool lane_ok = landed && tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
     int ia[JQK_MAX_GROUP];
     {
-      const uint32_t* kw = &sm.kbuf[warp][r & 1][0][lane];
-      score_record([kw](int w) { return kw[w * 32]; }, sm.t, n_a_words, n_c_words, n_words, ia);
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(st.k[lane >> 4]) + (lane & 15);
+      score_record([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, sm.t, n_a_words, n_c_words, n_words, ia);
     }
     if (!lane_ok) {
 #pragma unroll
@@ -347,6 +349,19 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       sm.pbuf[warp][1][h][lane] = p_lo;
       l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
+    // keys past the end of the split inside a page that is present: their V columns may hold
+    // anything (stale or never written), and 0 x NaN must not reach the accumulators
+    if (any && t0 + TILE_TOK > t_end) {
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        const int n_valid = min(JQK_PAGE_TOKENS, max(0, t_end - (t0 + JQK_PAGE_TOKENS * kb)));
+        if (n_valid > 0 && n_valid < JQK_PAGE_TOKENS) {
+          for (int d = lane; d < D; d += 32)
+            for (int t = n_valid; t < JQK_PAGE_TOKENS; ++t)
+              *reinterpret_cast<uint16_t*>(st.v[kb] + d * 32 + (((t >> 3) ^ ((d >> 2) & 1)) * 16) + (t & 7) * 2) = 0;
+        }
+      }
+    }
     __syncwarp();
     PROF_MARK(3);
     if (any) {
@@ -354,52 +369,44 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         const float a_even = (c & 1) ? alpha[2] : alpha[0];  // head 2c   (c >= 2: heads that do not exist)
         const float a_odd = (c & 1) ? alpha[3] : alpha[1];   // head 2c+1
 #pragma unroll
-        for (int j = 0; j < NCH * 4; ++j) { acc[j][0] *= a_even; acc[j][1] *= a_odd; acc[j][2] *= a_even; acc[j][3] *= a_odd; }
+        for (int j = 0; j < DT; ++j) { acc[j][0] *= a_even; acc[j][1] *= a_odd; acc[j][2] *= a_even; acc[j][3] *= a_odd; }
       }
-      cp_async_wait_but_one();  // V(r) has landed
-      PROF_MARK(4);
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
-        if (t0 + 16 * kb >= t_end) break;
-        uint32_t b[2][2];  // [hi/lo][k half]
+        const int pg = kb ? page_hi : page_lo;
+        if (pg < 0 || t0 + JQK_PAGE_TOKENS * kb >= t_end) continue;  // warp-uniform
+        uint32_t b[2][2];  // [hi/lo][key half]: P^T fragment, column n = head g
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-          const uint32_t* prow = reinterpret_cast<const uint32_t*>(&sm.pbuf[warp][t][g & 3][16 * kb]);
+          const uint32_t* prow = reinterpret_cast<const uint32_t*>(&sm.pbuf[warp][t][g & 3][JQK_PAGE_TOKENS * kb]);
           b[t][0] = (g < JQK_MAX_GROUP) ? prow[c] : 0u;
           b[t][1] = (g < JQK_MAX_GROUP) ? prow[c + 4] : 0u;
         }
+        const uint32_t vbase = smem_addr(st.v[kb]) + lm_off;
 #pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) {
-          const uint4 va = sm.vbuf[warp][kb][0][ch][lane], vb = sm.vbuf[warp][kb][1][ch][lane];
-          const uint4 vc = sm.vbuf[warp][kb][2][ch][lane], vd = sm.vbuf[warp][kb][3][ch][lane];
-          const uint32_t ra[4] = {va.x, va.y, va.z, va.w}, rb[4] = {vb.x, vb.y, vb.z, vb.w};
-          const uint32_t rc2[4] = {vc.x, vc.y, vc.z, vc.w}, rd[4] = {vd.x, vd.y, vd.z, vd.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t a0 = __byte_perm(ra[j], rb[j], 0x5410), a1 = __byte_perm(ra[j], rb[j], 0x7632);
-            const uint32_t a2 = __byte_perm(rc2[j], rd[j], 0x5410), a3 = __byte_perm(rc2[j], rd[j], 0x7632);
-            mma_bf16_16816(acc[ch * 4 + j], a0, a1, a2, a3, b[0][0], b[0][1]);
-            mma_bf16_16816(acc[ch * 4 + j], a0, a1, a2, a3, b[1][0], b[1][1]);
-          }
+        for (int j = 0; j < DT; ++j) {
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4(vbase + j * 512, a0, a1, a2, a3);
+          mma_bf16_16816(acc[j], a0, a1, a2, a3, b[0][0], b[0][1]);
+          mma_bf16_16816(acc[j], a0, a1, a2, a3, b[1][0], b[1][1]);
         }
       }
     }
+    __syncwarp();  // every lane is done with this stage and with pbuf
     PROF_MARK(5);
-    {  // the fragments of this tile are in registers or consumed: V of the next tile may overwrite them
-      const int rn = r + 1;
+    {  // refill this stage with the tile two ahead
+      const int rn = r + 2;
       const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
       const int nlo = __shfl_sync(0xffffffffu, src, (rn & 15) << 1);
       const int nhi = __shfl_sync(0xffffffffu, src, ((rn & 15) << 1) | 1);
-      if (rn < n_my) stage_values(rn, nlo, nhi); else cp_async_commit();
+      if (rn < n_my) issue_tile(rn, nlo, nhi);
     }
-    __syncwarp();  // pbuf is rewritten by the next tile
+    PROF_MARK(6);
   }
-  asm volatile("cp.async.wait_all;" ::: "memory");
-  PROF_MARK(6);
 
-  // ---- combine the warps of this block (each warp reuses its own V staging) ---------------
-  float* wacc = reinterpret_cast<float*>(&sm.vbuf[0][0][0][0][0]);  // warp w at w * WACC_STRIDE floats
-  constexpr int WACC_STRIDE = (int)(sizeof(uint4) * 2 * 4 * 2 * TILE_TOK / sizeof(float));
+  // ---- combine the warps of this block (each warp reuses its own first stage) ---------------
+  float* wacc = reinterpret_cast<float*>(&sm.stage[0][0]);  // warp w at w * WACC_STRIDE floats
+  constexpr int WACC_STRIDE = (int)(2 * sizeof(TileStage) / sizeof(float));
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) l_run[h] = warp_sum(l_run[h]);
   if (lane == 0) {
@@ -408,15 +415,12 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   }
   if (c < 2) {
 #pragma unroll
-    for (int ch = 0; ch < NCH; ++ch)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int dim = 64 * ch + 8 * g + 2 * j;
-        float* w0 = wacc + (size_t)warp * WACC_STRIDE + (2 * c) * JQK_MAX_DIM + dim;
-        float* w1 = w0 + JQK_MAX_DIM;
-        w0[0] = acc[ch * 4 + j][0]; w1[0] = acc[ch * 4 + j][1];
-        w0[1] = acc[ch * 4 + j][2]; w1[1] = acc[ch * 4 + j][3];
-      }
+    for (int j = 0; j < DT; ++j) {
+      float* w0 = wacc + (size_t)warp * WACC_STRIDE + (2 * c) * JQK_MAX_DIM + 16 * j + g;
+      float* w1 = w0 + JQK_MAX_DIM;
+      w0[0] = acc[j][0]; w1[0] = acc[j][1];
+      w0[8] = acc[j][2]; w1[8] = acc[j][3];
+    }
   }
   __syncthreads();
   const bool single = (n_splits == 1);
@@ -509,7 +513,7 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
 
 extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                             int32_t max_seq_len) {
-  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (384 keys)
+  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (256 keys)
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return unit;
   const long long items = (long long)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
   const long long target_blocks = 148;  // one resident block per SM
@@ -583,13 +587,13 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
   cudaStream_t st = (cudaStream_t)stream;
   if (tables->d == 128) {
-    JQK_SMEM_ONCE(decode_kernel<2>, sizeof(DecodeSmem), "decode smem attribute");
-    decode_kernel<2><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
+    JQK_SMEM_ONCE(decode_kernel<128>, sizeof(DecodeSmem), "decode smem attribute");
+    decode_kernel<128><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
         *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
         n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
   } else {
-    JQK_SMEM_ONCE(decode_kernel<1>, sizeof(DecodeSmem), "decode smem attribute");
-    decode_kernel<1><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
+    JQK_SMEM_ONCE(decode_kernel<64>, sizeof(DecodeSmem), "decode smem attribute");
+    decode_kernel<64><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
         *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
         n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
   }

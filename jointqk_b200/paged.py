@@ -62,8 +62,28 @@ def alloc_k_pool(tables: HeadTables, n_pages: int) -> torch.Tensor:
 
 
 def alloc_v_pool(tables: HeadTables, n_pages: int) -> torch.Tensor:
-    return torch.zeros((n_pages, tables.n_heads, PAGE_TOKENS, tables.d), dtype=torch.bfloat16,
+    """bf16 value pool, (n_pages, H, d * 16): a (page, head) block is dims-major, see ``v_slot_offsets``."""
+    return torch.zeros((n_pages, tables.n_heads, tables.d * PAGE_TOKENS), dtype=torch.bfloat16,
                        device=tables.device)
+
+
+_V_OFFSETS: dict = {}
+
+
+def v_slot_offsets(d: int, device) -> torch.Tensor:
+    """int64 (16, d): element offset of (slot, dim) inside a (page, head) block of the V pool.
+
+    The block is stored dims-major -- 32 bytes (16 keys) per dim -- because that is the operand
+    layout of the decode kernel's tensor-core product: a 16-dim x 16-key tile is one ldmatrix.
+    The two 16-byte halves of a row are swapped on dims 4..7 (mod 8) so that the eight rows an
+    ldmatrix phase touches fall into eight different shared-memory bank groups."""
+    key = (d, str(device))
+    if key not in _V_OFFSETS:
+        slot = torch.arange(PAGE_TOKENS).view(PAGE_TOKENS, 1)
+        dim = torch.arange(d).view(1, d)
+        off = dim * PAGE_TOKENS + ((((slot >> 3) ^ ((dim >> 2) & 1)) << 3) + (slot & 7))
+        _V_OFFSETS[key] = off.to(device)
+    return _V_OFFSETS[key]
 
 
 def sequential_page_table(lengths: list[int], device, first_page: int = 0) -> tuple[torch.Tensor, int]:
@@ -234,7 +254,8 @@ class PagedKVCache:
                 continue
             pos = torch.arange(self.lengths[s], self.lengths[s] + n, device=dev)
             pages = self.page_table[s, pos // PAGE_TOKENS].long()
-            self.v_pool[pages, :, pos % PAGE_TOKENS, :] = values[s, :, :n, :].to(torch.bfloat16).transpose(0, 1)
+            offs = v_slot_offsets(d, dev)[pos % PAGE_TOKENS]                     # (n, d)
+            self.v_pool[pages[:, None], :, offs] = values[s, :, :n, :].to(torch.bfloat16).permute(1, 2, 0)
             self.lengths[s] += n
         self.seq_lens[: len(self.lengths)] = torch.tensor(self.lengths, dtype=torch.int32, device=dev)
 
