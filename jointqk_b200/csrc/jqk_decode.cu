@@ -28,7 +28,7 @@
 namespace jqk {
 
 constexpr int SCORE_THREADS = TBL_THREADS;
-constexpr int DEC_THREADS = 256;
+constexpr int DEC_THREADS = 384;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int TILE_TOK = 32;        // keys per warp step (two pages)
 constexpr float kLog2e = 1.4426950408889634f;
@@ -109,20 +109,21 @@ struct DecodeWs {
 // header) and the two K pages, filled by bulk asynchronous copies that the warp issues itself.
 constexpr int K_STAGE_STRIDE = JQK_MAX_WORDS * JQK_PAGE_TOKENS * 4 + 64;  // +64 B: the two pages hit different banks
 struct alignas(128) TileStage {
-  uint8_t v[2][JQK_PAGE_TOKENS * JQK_MAX_DIM * 2];  // 2 x 4096 B
-  uint8_t k[2][K_STAGE_STRIDE];                     // 2 x 1088 B
+  uint8_t v[2][JQK_PAGE_TOKENS * JQK_MAX_DIM * 2];  // the two V pages of the current tile, 2 x 4096 B
+  uint8_t k[2][2][K_STAGE_STRIDE];                  // the K pages of two tiles (double buffer), 4 x 1088 B
 };
 
 struct DecodeSmem {
   TableSmem t;
-  TileStage stage[DEC_WARPS][2];
-  uint64_t full[DEC_WARPS][2];
+  TileStage stage[DEC_WARPS];
+  uint64_t kfull[DEC_WARPS][2];
+  uint64_t vfull[DEC_WARPS];
   __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
 };
-// A warp's first stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
+// A warp's stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
 static_assert(sizeof(TileStage) >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM, "stage too small for the partial output");
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
@@ -248,32 +249,41 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   int pg_cur = load_page_window(page_table, pt_stride, seq, lp0, n_seq_pages, n_pages, status);
   int pg_next = load_page_window(page_table, pt_stride, seq, lp0 + 32, n_seq_pages, n_pages, status);
 
-  if (lane == 0) { bar_init(&sm.full[warp][0], 1); bar_init(&sm.full[warp][1], 1); }
+  if (lane == 0) { bar_init(&sm.kfull[warp][0], 1); bar_init(&sm.kfull[warp][1], 1); bar_init(&sm.vfull[warp], 1); }
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncwarp();
 
-  // Lane 0 starts the copies of tile `r` (pages pg_lo / pg_hi, -1 = absent) into stage r & 1.  The
-  // stage was last read by this warp two tiles ago, in program order, so no "empty" barrier is needed.
-  auto issue_tile = [&](int r, int pg_lo, int pg_hi) {
+  // Lane 0 starts the copies of a tile (pages pg_lo / pg_hi, -1 = absent).  K pages of tile r go to
+  // K buffer r & 1, V pages to the single V buffer.  Buffers are refilled by the warp that read
+  // them, in program order after its last read, so no "empty" barriers are needed.
+  TileStage& st = sm.stage[warp];
+  auto issue_keys = [&](int r, int pg_lo, int pg_hi) {
     if (lane == 0) {
-      TileStage& st = sm.stage[warp][r & 1];
-      uint64_t* bar = &sm.full[warp][r & 1];
+      uint64_t* bar = &sm.kfull[warp][r & 1];
       const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
       const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
-      bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * (V_PAGE_BYTES + k_page_bytes));
-      if (ok0) {
-        bulk_load(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar);
-        bulk_load(st.k[0], k_head + (size_t)pg_lo * k_page_words, k_page_bytes, bar);
-      }
-      if (ok1) {
-        bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
-        bulk_load(st.k[1], k_head + (size_t)pg_hi * k_page_words, k_page_bytes, bar);
-      }
+      bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * k_page_bytes);
+      if (ok0) bulk_load(st.k[r & 1][0], k_head + (size_t)pg_lo * k_page_words, k_page_bytes, bar);
+      if (ok1) bulk_load(st.k[r & 1][1], k_head + (size_t)pg_hi * k_page_words, k_page_bytes, bar);
     }
   };
-  // the first two tiles go in flight before the prologue, so HBM works while the tables are built
-  if (n_my > 0) issue_tile(0, __shfl_sync(0xffffffffu, pg_cur, 0), __shfl_sync(0xffffffffu, pg_cur, 1));
-  if (n_my > 1) issue_tile(1, __shfl_sync(0xffffffffu, pg_cur, 2), __shfl_sync(0xffffffffu, pg_cur, 3));
+  auto issue_values = [&](int r, int pg_lo, int pg_hi) {
+    if (lane == 0) {
+      uint64_t* bar = &sm.vfull[warp];
+      const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
+      const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
+      bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * V_PAGE_BYTES);
+      if (ok0) bulk_load(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar);
+      if (ok1) bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
+    }
+  };
+  // the first copies go in flight before the prologue, so HBM works while the tables are built
+  {
+    const int p0 = __shfl_sync(0xffffffffu, pg_cur, 0), p1 = __shfl_sync(0xffffffffu, pg_cur, 1);
+    const int p2 = __shfl_sync(0xffffffffu, pg_cur, 2), p3 = __shfl_sync(0xffffffffu, pg_cur, 3);
+    if (n_my > 0) { issue_keys(0, p0, p1); issue_values(0, p0, p1); }
+    if (n_my > 1) issue_keys(1, p2, p3);
+  }
 
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
@@ -309,9 +319,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
     const int page_lo = __shfl_sync(0xffffffffu, pg_cur, (r & 15) << 1);
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
-    TileStage& st = sm.stage[warp][r & 1];
-    const bool landed = bar_wait(&sm.full[warp][r & 1], (r >> 1) & 1);
-    if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+    bool landed = bar_wait(&sm.kfull[warp][r & 1], (r >> 1) & 1);
     PROF_MARK(1);
 
     // ---- score this lane's key from the staged record words ----
@@ -319,7 +327,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const bool lane_ok = landed && tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
     int ia[JQK_MAX_GROUP];
     {
-      const uint32_t* kw = reinterpret_cast<const uint32_t*>(st.k[lane >> 4]) + (lane & 15);
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(st.k[r & 1][lane >> 4]) + (lane & 15);
       score_record([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, sm.t, n_a_words, n_c_words, n_words, ia);
     }
     if (!lane_ok) {
@@ -349,6 +357,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       sm.pbuf[warp][1][h][lane] = p_lo;
       l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
+    landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
+    if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
     if (any && t0 + TILE_TOK > t_end) {
@@ -364,7 +374,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     __syncwarp();
     PROF_MARK(3);
-    if (any) {
+    if (any && landed) {
       if (grew) {
         const float a_even = (c & 1) ? alpha[2] : alpha[0];  // head 2c   (c >= 2: heads that do not exist)
         const float a_odd = (c & 1) ? alpha[3] : alpha[1];   // head 2c+1
@@ -394,19 +404,20 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     __syncwarp();  // every lane is done with this stage and with pbuf
     PROF_MARK(5);
-    {  // refill this stage with the tile two ahead
-      const int rn = r + 2;
-      const int src = ((rn >> 4) == (r >> 4)) ? pg_cur : pg_next;
-      const int nlo = __shfl_sync(0xffffffffu, src, (rn & 15) << 1);
-      const int nhi = __shfl_sync(0xffffffffu, src, ((rn & 15) << 1) | 1);
-      if (rn < n_my) issue_tile(rn, nlo, nhi);
+    {  // V of the next tile and K of the tile after it take the buffers this tile has just released
+      const int r1 = r + 1, r2 = r + 2;
+      const int s1 = ((r1 >> 4) == (r >> 4)) ? pg_cur : pg_next, s2 = ((r2 >> 4) == (r >> 4)) ? pg_cur : pg_next;
+      const int v_lo = __shfl_sync(0xffffffffu, s1, (r1 & 15) << 1), v_hi = __shfl_sync(0xffffffffu, s1, ((r1 & 15) << 1) | 1);
+      const int k_lo = __shfl_sync(0xffffffffu, s2, (r2 & 15) << 1), k_hi = __shfl_sync(0xffffffffu, s2, ((r2 & 15) << 1) | 1);
+      if (r1 < n_my) issue_values(r1, v_lo, v_hi);
+      if (r2 < n_my) issue_keys(r2, k_lo, k_hi);
     }
     PROF_MARK(6);
   }
 
   // ---- combine the warps of this block (each warp reuses its own first stage) ---------------
-  float* wacc = reinterpret_cast<float*>(&sm.stage[0][0]);  // warp w at w * WACC_STRIDE floats
-  constexpr int WACC_STRIDE = (int)(2 * sizeof(TileStage) / sizeof(float));
+  float* wacc = reinterpret_cast<float*>(&sm.stage[0]);  // warp w at w * WACC_STRIDE floats
+  constexpr int WACC_STRIDE = (int)(sizeof(TileStage) / sizeof(float));
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) l_run[h] = warp_sum(l_run[h]);
   if (lane == 0) {
@@ -513,7 +524,7 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
 
 extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                             int32_t max_seq_len) {
-  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (256 keys)
+  const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (384 keys)
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return unit;
   const long long items = (long long)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
   const long long target_blocks = 148;  // one resident block per SM

@@ -151,41 +151,44 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
       atomicMax(&sm.wmax[w][h], __float_as_uint(m[h] * 1.0000005f));  // non-negative floats order as uints
   }
   __syncthreads();
-  if (tid < JQK_MAX_GROUP) {
-    float m = 0.f;
-    for (int w = 0; w < n_scan_words; ++w) m = fmaxf(m, __uint_as_float(sm.wmax[w][tid]));
-    sm.absmax[tid] = __float_as_uint((m > 0.f && m < CUDART_INF_F) ? m : 0.f);
-  }
-  __syncthreads();
-  if (tid < TBL_WORDS) {
-    // largest shift that keeps word `tid` inside 16 bits for every head
+  if (tid < 32) {
+    // warp 0 derives the per-word shifts with shuffles: lane w owns scan word w (n_scan_words <= 32)
+    const int lane = tid;
+    float wm[JQK_MAX_GROUP], gm[JQK_MAX_GROUP];
     int fit = TBL_MAX_SHIFT;
-    if (tid < n_scan_words) {
-#pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-        const float g = __uint_as_float(sm.absmax[h]), m = __uint_as_float(sm.wmax[tid][h]);
-        if (g > 0.f && m > 0.f) fit = min(fit, max(0, (int)floorf(log2f(g / m) - 1e-3f)));
-      }
-    }
-    sm.kshift[tid] = fit;
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int k = TBL_MAX_SHIFT;
-    for (int w = n_scan_words - 1; w >= 0; --w) { k = min(k, sm.kshift[w]); sm.kshift[w] = k; }
-    int prev = 0;
-    for (int w = 0; w < n_scan_words; ++w) { sm.dshift[w] = sm.kshift[w] - prev; prev = sm.kshift[w]; }
-    const int k_last = n_scan_words ? prev : 0;
-    unsigned int bias = 0u;
-    for (int w = 0; w < n_scan_words; ++w)
-      bias += (unsigned int)((w < hd.n_a_words ? 8 : 12) * 32768) << (k_last - sm.kshift[w]);
-    sm.bias = bias;
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      const float m = __uint_as_float(sm.absmax[h]);
-      const float base = (m > 0.f) ? m / 32767.f : 1.f;
-      sm.scale[h] = base / (float)(1 << k_last);
-      sm.absmax[h] = __float_as_uint(base);  // reused below as the per-head base scale
+      wm[h] = (lane < n_scan_words) ? __uint_as_float(sm.wmax[lane][h]) : 0.f;
+      gm[h] = warp_max(wm[h]);
+      if (!(gm[h] < CUDART_INF_F)) gm[h] = 0.f;
+      // largest shift that keeps this word inside 16 bits for head h
+      if (gm[h] > 0.f && wm[h] > 0.f) fit = min(fit, max(0, (int)floorf(log2f(gm[h] / wm[h]) - 1e-3f)));
+    }
+    // K_w = min over later-or-equal words (suffix minimum): non-decreasing along the scan
+    int k = (lane < n_scan_words) ? fit : TBL_MAX_SHIFT;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int other = __shfl_down_sync(0xffffffffu, k, o);
+      if (lane + o < 32) k = min(k, other);
+    }
+    const int prev = __shfl_up_sync(0xffffffffu, k, 1);
+    const int k_last = __shfl_sync(0xffffffffu, k, max(n_scan_words - 1, 0));
+    unsigned int term = 0u;
+    if (lane < n_scan_words) {
+      sm.kshift[lane] = k;
+      sm.dshift[lane] = k - (lane ? prev : 0);
+      term = (unsigned int)((lane < hd.n_a_words ? 8 : 12) * 32768) << (k_last - k);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) term += __shfl_xor_sync(0xffffffffu, term, o);
+    if (lane == 0) sm.bias = term;
+    if (lane < JQK_MAX_GROUP) {
+      float base = 1.f;
+#pragma unroll
+      for (int h = 0; h < JQK_MAX_GROUP; ++h)
+        if (h == lane) base = (gm[h] > 0.f) ? gm[h] / 32767.f : 1.f;
+      sm.scale[lane] = base / (float)(1 << (n_scan_words ? k_last : 0));
+      sm.absmax[lane] = __float_as_uint(base);  // the per-head base scale, read by the quantising pass
     }
   }
   __syncthreads();
