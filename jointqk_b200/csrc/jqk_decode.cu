@@ -28,6 +28,7 @@
 namespace jqk {
 
 constexpr int SCORE_THREADS = TBL_THREADS;
+constexpr int TBL_BUILD_THREADS = 512;
 constexpr int DEC_THREADS = 384;
 constexpr int DEC_WARPS = DEC_THREADS / 32;
 constexpr int TILE_TOK = 32;        // keys per warp step (two pages)
@@ -69,7 +70,7 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
     float sv[JQK_MAX_GROUP];
     if (table_mode) {  // the decode kernel's fixed-point tables
       int acc[JQK_MAX_GROUP];
-      score_record([kp](int w) { return __ldg(kp + w * JQK_PAGE_TOKENS); }, sm, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
+      score_record([kp](int w) { return __ldg(kp + w * JQK_PAGE_TOKENS); }, TableView{sm.lut, sm.dshift, sm.bias}, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) sv[h] = (float)acc[h] * sm.scale[h];
     } else {           // plain fp32: sum_c q'_c * cb[c][code_c], column after column
@@ -98,6 +99,7 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
 // Decode attention
 // ---------------------------------------------------------------------------------------
 struct DecodeWs {
+  TableRecord* tables;     // [n_seqs][n_kv_heads * q_blocks]
   float* part_m;           // [n_seqs][n_q_heads][max_splits]
   float* part_l;           // [n_seqs][n_q_heads][max_splits]
   float* part_acc;         // [n_seqs][n_q_heads][max_splits][128]
@@ -114,8 +116,9 @@ struct alignas(128) TileStage {
 };
 
 struct DecodeSmem {
-  TableSmem t;
+  TableRecord t;   // this block's copy of the finished tables
   TileStage stage[DEC_WARPS];
+  uint64_t tfull;
   uint64_t kfull[DEC_WARPS][2];
   uint64_t vfull[DEC_WARPS];
   __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
@@ -199,6 +202,27 @@ __device__ long long g_decode_prof[8];
 #else
 #define PROF_MARK(i) do {} while (0)
 #endif
+
+// Builds the lookup tables of every (sequence, kv head, q-head block) once per decode step; the
+// decode blocks of all key splits of that group then only copy them.  One block per group.
+__global__ void __launch_bounds__(TBL_BUILD_THREADS)
+decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads, TableRecord* __restrict__ recs) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  TableSmem& sm = *reinterpret_cast<TableSmem*>(smem_raw);
+  const int group = n_q_heads / tb.n_heads;
+  const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
+  const int head = blockIdx.x / q_blocks, qb = blockIdx.x % q_blocks, seq = blockIdx.y;
+  const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
+  const HeadDesc hd = load_desc(tb.desc, head);
+  build_tables(sm, tb, head, hd, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d, JQK_DTYPE_BF16, (size_t)hd.d, n_group);
+  TableRecord* rec = recs + (size_t)seq * gridDim.x + blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(sm.lut);
+  uint4* dst = reinterpret_cast<uint4*>(rec->lut);
+  for (int e = threadIdx.x; e < hd.n_tables * 8; e += blockDim.x) dst[e] = src[e];
+  if (threadIdx.x < TBL_WORDS) rec->dshift[threadIdx.x] = sm.dshift[threadIdx.x];
+  if (threadIdx.x < JQK_MAX_GROUP) rec->scale[threadIdx.x] = sm.scale[threadIdx.x];
+  if (threadIdx.x == 0) rec->bias = sm.bias;
+}
 
 // D = head_dim (64 or 128).
 template <int D>
@@ -288,13 +312,27 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
 #endif
-  build_tables(sm.t, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
+  // ---- the finished tables of this (sequence, head group) come from the table kernel ----
+  if (tid == 0) {
+    const TableRecord* rec = ws.tables + (size_t)seq * gridDim.y + blockIdx.y;
+    const uint32_t lut_bytes = (uint32_t)hd.n_tables * 128u;
+    bar_init(&sm.tfull, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bar_expect_tx(&sm.tfull, lut_bytes + TABLE_RECORD_META_BYTES);
+    if (lut_bytes) bulk_load(sm.t.lut, rec->lut, lut_bytes, &sm.tfull);
+    bulk_load(sm.t.dshift, rec->dshift, TABLE_RECORD_META_BYTES, &sm.tfull);
+  }
+  __syncthreads();
+  if (!bar_wait(&sm.tfull, 0) && tid == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
   PROF_MARK(0);
   float sc[JQK_MAX_GROUP];
   {
     const float f = kLog2e / sqrtf((float)D);
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.scale[h] * f;
+  }
+  const TableView tview{sm.t.lut, sm.t.dshift, sm.t.bias};
+  {
   }
   const int n_a_words = hd.n_a_words, n_c_words = hd.n_c_words, n_words = hd.n_words;
 
@@ -328,7 +366,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     int ia[JQK_MAX_GROUP];
     {
       const uint32_t* kw = reinterpret_cast<const uint32_t*>(st.k[r & 1][lane >> 4]) + (lane & 15);
-      score_record([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, sm.t, n_a_words, n_c_words, n_words, ia);
+      score_record([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, tview, n_a_words, n_c_words, n_words, ia);
     }
     if (!lane_ok) {
 #pragma unroll
@@ -516,9 +554,11 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
                                              int32_t max_splits) {
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_splits <= 0) return 0;
   const size_t rows = (size_t)n_seqs * n_q_heads * max_splits;
-  size_t b = align_up((size_t)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads) * sizeof(unsigned int), 256);
+  const size_t groups = (size_t)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
+  size_t b = align_up(groups * sizeof(unsigned int), 256);
   b += align_up(rows * sizeof(float), 256) * 2;
   b += align_up(rows * JQK_MAX_DIM * sizeof(float), 256);
+  b += align_up(groups * sizeof(TableRecord), 256);
   return b;
 }
 
@@ -583,8 +623,8 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
   const int qbl = q_blocks_for(n_q_heads, tables->n_heads);
-  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, max_splits};
-  if (max_splits > 1) {
+  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits};
+  {
     const size_t need = jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits);
     if (!workspace || workspace_bytes < need) return fail(JQK_E_WORKSPACE, "decode workspace needs %zu bytes, got %zu", need, workspace_bytes);
     if ((uintptr_t)workspace % 16) return fail(JQK_E_ARG, "workspace must be 16-byte aligned");
@@ -593,7 +633,14 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
     ws.counters = (unsigned int*)p; p += align_up((size_t)n_seqs * tables->n_heads * qbl * sizeof(unsigned int), 256);
     ws.part_m = (float*)p; p += align_up(rows * sizeof(float), 256);
     ws.part_l = (float*)p; p += align_up(rows * sizeof(float), 256);
-    ws.part_acc = (float*)p;
+    ws.part_acc = (float*)p; p += align_up(rows * JQK_MAX_DIM * sizeof(float), 256);
+    ws.tables = (TableRecord*)p;
+  }
+  if (max_seq_len > 0) {
+    JQK_SMEM_ONCE(decode_tables_kernel, sizeof(TableSmem), "decode tables smem attribute");
+    decode_tables_kernel<<<dim3(tables->n_heads * qbl, n_seqs), TBL_BUILD_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
+        *tables, (const __nv_bfloat16*)q, n_q_heads, ws.tables);
+    JQK_CUDA_OK(cudaGetLastError(), "decode tables launch");
   }
   dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
   cudaStream_t st = (cudaStream_t)stream;
@@ -653,7 +700,7 @@ extern "C" int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const
   if (tokens_per_split == 0) tokens_per_split = jqk_decode_default_split(n_seqs, n_q_heads, tables->n_heads, max_seq_len);
   if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
-  const size_t need = max_splits > 1 ? jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits) : 0;
+  const size_t need = jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits);
   if (need > (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES)
     return fail(JQK_E_WORKSPACE,
                 "this call needs %zu bytes of split scratch but the built-in array holds %d; use fewer splits "

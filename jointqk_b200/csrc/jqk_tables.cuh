@@ -17,6 +17,7 @@
 #pragma once
 
 #include <math_constants.h>
+#include <stddef.h>
 
 #include "jqk_common.cuh"
 
@@ -239,8 +240,27 @@ struct ScoreAcc {
 // from the start of the record, (3,3,2)-byte words from its end; lookups that fall on the other
 // region hit all-zero tables.  The word loops are not unrolled: the body of one word (8 or 12
 // lookups) is what has to stay in the instruction cache.
+// What the scoring loop reads, wherever it lives (the builder's TableSmem or a copy of the record).
+struct TableView {
+  const uint2* lut;
+  const int* dshift;
+  unsigned int bias;
+};
+
+// Finished tables of one (sequence, kv head, q-head block) in global memory: written by the table
+// kernel, copied into shared memory by every decode block of that group.
+struct TableRecord {
+  uint2 lut[JQK_MAX_TABLES * 16];
+  int dshift[TBL_WORDS];
+  float scale[JQK_MAX_GROUP];
+  unsigned int bias;
+  unsigned int pad[27];
+};
+static_assert(sizeof(TableRecord) % 16 == 0 && offsetof(TableRecord, dshift) % 16 == 0, "bulk copies need 16-byte pieces");
+constexpr uint32_t TABLE_RECORD_META_BYTES = sizeof(TableRecord) - offsetof(TableRecord, dshift);  // 256
+
 template <typename WordFn>
-__device__ __forceinline__ void score_record(WordFn word, const TableSmem& sm, int n_a_words, int n_c_words,
+__device__ __forceinline__ void score_record(WordFn word, const TableView& sm, int n_a_words, int n_c_words,
                                              int n_words, int (&out)[JQK_MAX_GROUP]) {
   ScoreAcc acc;
   acc.clear();
