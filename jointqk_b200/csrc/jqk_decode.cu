@@ -116,7 +116,10 @@ struct alignas(128) TileStage {
 };
 
 struct DecodeSmem {
-  TableRecord t;   // this block's copy of the finished tables
+  union {            // the tables this block scores with:
+    TableRecord rec;   //   a copy of the table kernel's record, or
+    TableSmem build;   //   tables built by the block itself (few blocks: latency matters more than repeated work)
+  } t;
   TileStage stage[DEC_WARPS];
   uint64_t tfull;
   uint64_t kfull[DEC_WARPS][2];
@@ -225,7 +228,7 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
 }
 
 // D = head_dim (64 or 128).
-template <int D>
+template <int D, bool BUILD_IN_BLOCK>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
@@ -312,27 +315,35 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
 #endif
-  // ---- the finished tables of this (sequence, head group) come from the table kernel ----
-  if (tid == 0) {
-    const TableRecord* rec = ws.tables + (size_t)seq * gridDim.y + blockIdx.y;
-    const uint32_t lut_bytes = (uint32_t)hd.n_tables * 128u;
-    bar_init(&sm.tfull, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    bar_expect_tx(&sm.tfull, lut_bytes + TABLE_RECORD_META_BYTES);
-    if (lut_bytes) bulk_load(sm.t.lut, rec->lut, lut_bytes, &sm.tfull);
-    bulk_load(sm.t.dshift, rec->dshift, TABLE_RECORD_META_BYTES, &sm.tfull);
-  }
-  __syncthreads();
-  if (!bar_wait(&sm.tfull, 0) && tid == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
-  PROF_MARK(0);
   float sc[JQK_MAX_GROUP];
+  TableView tview;
+  if constexpr (BUILD_IN_BLOCK) {
+    build_tables(sm.t.build, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
+    tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias};
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];
+  } else {
+    // the finished tables of this (sequence, head group) come from the table kernel
+    if (tid == 0) {
+      const TableRecord* rec = ws.tables + (size_t)seq * gridDim.y + blockIdx.y;
+      const uint32_t lut_bytes = (uint32_t)hd.n_tables * 128u;
+      bar_init(&sm.tfull, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      bar_expect_tx(&sm.tfull, lut_bytes + TABLE_RECORD_META_BYTES);
+      if (lut_bytes) bulk_load(sm.t.rec.lut, rec->lut, lut_bytes, &sm.tfull);
+      bulk_load(sm.t.rec.dshift, rec->dshift, TABLE_RECORD_META_BYTES, &sm.tfull);
+    }
+    __syncthreads();
+    if (!bar_wait(&sm.tfull, 0) && tid == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+    tview = TableView{sm.t.rec.lut, sm.t.rec.dshift, sm.t.rec.bias};
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.rec.scale[h];
+  }
+  PROF_MARK(0);
   {
     const float f = kLog2e / sqrtf((float)D);
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.scale[h] * f;
-  }
-  const TableView tview{sm.t.lut, sm.t.dshift, sm.t.bias};
-  {
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] *= f;
   }
   const int n_a_words = hd.n_a_words, n_c_words = hd.n_c_words, n_words = hd.n_words;
 
@@ -636,25 +647,27 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
     ws.part_acc = (float*)p; p += align_up(rows * JQK_MAX_DIM * sizeof(float), 256);
     ws.tables = (TableRecord*)p;
   }
-  if (max_seq_len > 0) {
+  dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
+  cudaStream_t st = (cudaStream_t)stream;
+  // One wave of blocks or less: every block builds its own tables (no second launch on the
+  // critical path).  More: a table kernel builds them once per group and the blocks copy them.
+  const bool in_block = (long long)max_splits * tables->n_heads * qbl * n_seqs <= 148;
+  if (max_seq_len > 0 && !in_block) {
     JQK_SMEM_ONCE(decode_tables_kernel, sizeof(TableSmem), "decode tables smem attribute");
-    decode_tables_kernel<<<dim3(tables->n_heads * qbl, n_seqs), TBL_BUILD_THREADS, sizeof(TableSmem), (cudaStream_t)stream>>>(
+    decode_tables_kernel<<<dim3(tables->n_heads * qbl, n_seqs), TBL_BUILD_THREADS, sizeof(TableSmem), st>>>(
         *tables, (const __nv_bfloat16*)q, n_q_heads, ws.tables);
     JQK_CUDA_OK(cudaGetLastError(), "decode tables launch");
   }
-  dim3 grid(max_splits, tables->n_heads * qbl, n_seqs);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (tables->d == 128) {
-    JQK_SMEM_ONCE(decode_kernel<128>, sizeof(DecodeSmem), "decode smem attribute");
-    decode_kernel<128><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
-        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
-        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
-  } else {
-    JQK_SMEM_ONCE(decode_kernel<64>, sizeof(DecodeSmem), "decode smem attribute");
-    decode_kernel<64><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(
-        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,
-        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);
-  }
+#define JQK_LAUNCH_DECODE(DIM, INB)                                                                              \
+  do {                                                                                                           \
+    JQK_SMEM_ONCE((decode_kernel<DIM, INB>), sizeof(DecodeSmem), "decode smem attribute");                       \
+    decode_kernel<DIM, INB><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(                                      \
+        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,  \
+        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);                              \
+  } while (0)
+  if (tables->d == 128) { if (in_block) JQK_LAUNCH_DECODE(128, true); else JQK_LAUNCH_DECODE(128, false); }
+  else { if (in_block) JQK_LAUNCH_DECODE(64, true); else JQK_LAUNCH_DECODE(64, false); }
+#undef JQK_LAUNCH_DECODE
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
   return 0;
 }
