@@ -73,6 +73,9 @@ extern "C" {
  *   inv_rows      float [H][128][d]: inverse_map[coord(c)][i] (reconstruction)
  *   fwd_limbs     bf16  [H][3][128][d]: three-way bf16 split of fwd_cols, column-major
  *                 (limb l, column c, dim i), for the tensor-core transform; may be NULL
+ *   bucket_pre    uint8 [H][128][128], bucket_aff float [H][128][2]: coarse-to-exact quantiser of the
+ *                 tensor-core kernel: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes
+ *                 2^23), code = pre[c][cell] + (x >= thresholds[c][pre[c][cell]]); both NULL = not used
  */
 typedef struct jqk_head_tables {
   int32_t n_heads;
@@ -88,6 +91,8 @@ typedef struct jqk_head_tables {
   const float* qproj_cols;
   const float* inv_rows;
   const uint16_t* fwd_limbs;
+  const uint8_t* bucket_pre;
+  const float* bucket_aff;
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */

@@ -31,6 +31,8 @@ class JqkHeadTables(C.Structure):
         ("qproj_cols", C.c_void_p),
         ("inv_rows", C.c_void_p),
         ("fwd_limbs", C.c_void_p),
+        ("bucket_pre", C.c_void_p),
+        ("bucket_aff", C.c_void_p),
     ]
 
 

@@ -11,10 +11,11 @@
 //   warp 0      TMA producer: key tiles [128 keys][128 dims] bf16 into a 3-stage ring (128B swizzle)
 //   warp 1      allocates TMEM, loads the three limb matrices once, issues 24 MMAs per tile
 //               (8 K-steps x 3 limbs, M=128, N=columns, K=16) into one of two accumulators
-//   warps 2..9  epilogue: a thread owns one key (TMEM lane) and half of the record's words; it
-//               reads 16 columns at a time, finds each code by binary search over the exact
-//               fp32 decision thresholds in shared memory, appends the bits and stores finished
-//               words to the page (word-major pages: 64-byte segments per warp store).
+//   warps 2..17 epilogue: a thread owns one key (TMEM lane) and a quarter of the record's words; it
+//               reads 16 columns at a time, finds each code (a cell lookup plus one comparison with
+//               the exact fp32 decision threshold, or a binary search over the thresholds when the
+//               cell tables do not apply), appends the bits and stores finished words to the page
+//               (word-major pages: 64-byte segments per warp store).
 // Every mbarrier wait is bounded in time; on expiry the block flags JQK_STATUS_WAIT_EXPIRED,
 // drains its copies, frees TMEM and returns.
 #include "jqk_common.cuh"
@@ -26,7 +27,7 @@ using namespace sm100;
 
 constexpr int TC_TILE = 128;
 constexpr int TC_STAGES = 3;
-constexpr int TC_EPI_WARPS = 8;
+constexpr int TC_EPI_WARPS = 16;  // four per TMEM lane quarter, each taking a quarter of the record's words
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
 constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
@@ -37,6 +38,8 @@ struct TcSmem {
   uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
   float thr[128 * 16];
+  uint8_t pre[128 * 128];   // coarse-to-exact quantiser: lower bound of the code per cell
+  float2 aff[128];          // cell = low 7 bits of clamp(x * aff.x + aff.y)
   int32_t meta[128];
   int32_t wcb[JQK_MAX_WORDS + 4];
   uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], b_full;
@@ -85,6 +88,7 @@ __device__ __forceinline__ uint32_t search_code(float x, const float* __restrict
   return code;
 }
 
+template <bool USE_BUCKETS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
                    jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
@@ -102,6 +106,12 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   // ---- set-up ----
   for (int e = tid; e < hd.n_cols * 16; e += TC_THREADS) sm.thr[e] = tb.thresholds[(size_t)head * 128 * 16 + e];
   for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
+  if constexpr (USE_BUCKETS) {
+    const uint4* src = reinterpret_cast<const uint4*>(tb.bucket_pre + (size_t)head * 128 * 128);
+    uint4* dst = reinterpret_cast<uint4*>(sm.pre);
+    for (int e = tid; e < hd.n_cols * 8; e += TC_THREADS) dst[e] = src[e];
+    for (int e = tid; e < 128; e += TC_THREADS) sm.aff[e] = reinterpret_cast<const float2*>(tb.bucket_aff)[(size_t)head * 128 + e];
+  }
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -170,9 +180,8 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     // ================= epilogue =================
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
-    const int half = ew >> 2;
-    const int w_split = (hd.n_words + 1) >> 1;
-    const int w_lo = half ? w_split : 0, w_hi = half ? hd.n_words : w_split;
+    const int part = ew >> 2;
+    const int w_lo = (hd.n_words * part) >> 2, w_hi = (hd.n_words * (part + 1)) >> 2;
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
     const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
     const int wpr = tb.words_per_record;
@@ -196,17 +205,30 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       for (int c0 = c_lo & ~15; c0 < c_hi; c0 += 16) {
         float v[16];
         tmem_ld16(t_lane + c0, v);
-        // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
-        // their last level); keeping them branch-free lets the loads of all 16 overlap
         uint32_t code[16];
+        if constexpr (USE_BUCKETS) {
+          // one fused multiply-add finds the cell, a byte table gives a lower bound of the code that
+          // is at most one short, one exact comparison settles it
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float* th = sm.thr + (c0 + i) * 16;
-          uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
-          k += (v[i] >= th[k + 3]) ? 4u : 0u;
-          k += (v[i] >= th[k + 1]) ? 2u : 0u;
-          k += (v[i] >= th[k]) ? 1u : 0u;
-          code[i] = k;
+          for (int i = 0; i < 16; ++i) {
+            const float2 af = sm.aff[c0 + i];
+            float y = fmaf(v[i], af.x, af.y);
+            y = fminf(fmaxf(y, 8388608.f), 8388608.f + 127.f);
+            const uint32_t k = sm.pre[(c0 + i) * 128 + (__float_as_uint(y) & 127u)];
+            code[i] = k + ((v[i] >= sm.thr[(c0 + i) * 16 + k]) ? 1u : 0u);
+          }
+        } else {
+          // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
+          // their last level); keeping them branch-free lets the loads of all 16 overlap
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float* th = sm.thr + (c0 + i) * 16;
+            uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
+            k += (v[i] >= th[k + 3]) ? 4u : 0u;
+            k += (v[i] >= th[k + 1]) ? 2u : 0u;
+            k += (v[i] >= th[k]) ? 1u : 0u;
+            code[i] = k;
+          }
         }
         int mt[16];
 #pragma unroll
@@ -288,8 +310,13 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
   dim3 grid((max_tiles + tiles_per_block - 1) / tiles_per_block, tables->n_heads, n_seqs);
   TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, status};
   const size_t smem = sizeof(TcSmem) + 1024;
-  JQK_SMEM_ONCE(compress_tc_kernel, smem, "tensor-core compress smem attribute");
-  compress_tc_kernel<<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
+  if (tables->bucket_pre && tables->bucket_aff) {
+    JQK_SMEM_ONCE(compress_tc_kernel<true>, smem, "tensor-core compress smem attribute");
+    compress_tc_kernel<true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
+  } else {
+    JQK_SMEM_ONCE(compress_tc_kernel<false>, smem, "tensor-core compress smem attribute");
+    compress_tc_kernel<false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
+  }
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
   return 0;
 }

@@ -216,3 +216,50 @@ def decision_thresholds(codebook_rows: np.ndarray, widths: np.ndarray) -> np.nda
         hi = np.where(pred, mid, hi)
         lo = np.where(pred, lo, mid)
     return np.where(valid, from_ord(hi), np.float32(np.inf)).astype(np.float32)
+
+
+BUCKETS = 128
+
+
+def bucket_tables(thresholds: np.ndarray, widths: np.ndarray):
+    """Coarse-to-exact quantiser tables for the tensor-core compress kernel.
+
+    The kernel maps a transformed value to one of ``BUCKETS`` equal cells with a single fused
+    multiply-add, ``y = x * inv_step + off`` (``off`` carries the 2**23 bias that leaves the cell
+    index in the low mantissa bits), reads ``pre[cell]`` -- a lower bound of the code that is at most
+    one short -- and settles the code with one exact comparison, ``code = pre + (x >= thr[pre])``.
+    The comparison is against the exact fp32 decision threshold, so the result equals the full
+    threshold count whenever the lower bound is valid; validity needs neighbouring thresholds to be
+    at least three cells apart (one cell of slack on either side absorbs any rounding difference
+    between this host arithmetic and the device FMA).  Returns ``(pre uint8 (n, BUCKETS), aff float32
+    (n, 2), ok)``; ``ok`` is False if some column's thresholds are too close for the scheme.
+    """
+    thr = np.asarray(thresholds, dtype=np.float32)
+    widths = np.asarray(widths).astype(np.int64).reshape(-1)
+    n = thr.shape[0]
+    pre = np.zeros((n, BUCKETS), np.uint8)
+    aff = np.zeros((n, 2), np.float32)
+    aff[:, 1] = np.float32(2.0 ** 23)
+    ok = True
+    cells = np.arange(BUCKETS)
+    for c in range(n):
+        n_thr = (1 << int(widths[c])) - 1
+        if n_thr <= 1:
+            continue                      # one threshold (or none): cell 0 for every x, pre = 0
+        t = thr[c, :n_thr].astype(np.float64)
+        span = t[-1] - t[0]
+        if not np.isfinite(span) or span <= 0:
+            ok = False
+            continue
+        step = span / (BUCKETS - 8)
+        inv_step = np.float32(1.0 / step)
+        off = np.float32(-(t[0] - 4.0 * step) * float(inv_step) + 2.0 ** 23)
+        y = np.float32(thr[c, :n_thr].astype(np.float64) * float(inv_step) + float(off))   # ~ device fmaf
+        y = np.minimum(np.maximum(y, np.float32(2.0 ** 23)), np.float32(2.0 ** 23 + BUCKETS - 1))
+        cell = y.view(np.uint32).astype(np.int64) & (BUCKETS - 1)
+        if np.any(np.diff(cell) < 3):
+            ok = False
+            continue
+        pre[c] = (cell[None, :] <= (cells[:, None] - 2)).sum(-1).astype(np.uint8)
+        aff[c] = (inv_step, off)
+    return pre, aff, ok

@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import _native
-from .layout import MAX_TABLES, KeyLayout, decision_thresholds, plan_key_layout
+from .layout import BUCKETS, MAX_TABLES, KeyLayout, bucket_tables, decision_thresholds, plan_key_layout
 
 DESC_INTS = 32
 MAX_COLS = 128
@@ -75,6 +75,10 @@ class HeadTables:
         inv_rows = np.zeros((H, MAX_COLS, d), np.float32)
         thr = np.full((H, MAX_COLS, 16), np.inf, np.float32)
         cb_cols = np.zeros((H, MAX_COLS, 16), np.float32)
+        b_pre = np.zeros((H, MAX_COLS, BUCKETS), np.uint8)
+        b_aff = np.zeros((H, MAX_COLS, 2), np.float32)
+        b_aff[..., 1] = np.float32(2.0 ** 23)
+        buckets_ok = True
         cb_np, fwd_np, inv_np = cb.numpy(), fwd.numpy(), inv.numpy()
         for h, lay in enumerate(self.layouts):
             desc[h, :8] = lay.descriptor()
@@ -92,6 +96,8 @@ class HeadTables:
             rows[:, :kk] = np.where(np.isfinite(cb_np[h][coords, :kk]), cb_np[h][coords, :kk], 0.0)
             cb_cols[h, :n] = rows
             thr[h, :n, :15] = decision_thresholds(rows, lay.col_width[:n])
+            b_pre[h, :n], b_aff[h, :n], ok = bucket_tables(thr[h, :n, :15], lay.col_width[:n])
+            buckets_ok = buckets_ok and ok
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -99,6 +105,9 @@ class HeadTables:
         self.desc, self.col_meta, self.table_fields = up(desc), up(col_meta), up(fields)
         self.fwd_cols, self.qproj_cols, self.inv_rows = up(fwd_cols), up(qproj), up(inv_rows)
         self.thresholds, self.cb_cols = up(thr), up(cb_cols)
+        # coarse-to-exact quantiser tables; absent when some column's thresholds are too close for them
+        self.bucket_pre = up(b_pre) if buckets_ok else None
+        self.bucket_aff = up(b_aff) if buckets_ok else None
         # three bf16 limbs of the forward map, [H][3][col][dim] (column-major = K-major B operand)
         self.fwd_limbs = split_bf16_limbs(torch.from_numpy(fwd_cols).transpose(1, 2).contiguous(), 3) \
             .permute(1, 0, 2, 3).contiguous().to(self.device)
@@ -108,7 +117,9 @@ class HeadTables:
             table_fields=self.table_fields.data_ptr(), fwd_cols=self.fwd_cols.data_ptr(),
             thresholds=self.thresholds.data_ptr(), cb_cols=self.cb_cols.data_ptr(),
             qproj_cols=self.qproj_cols.data_ptr(), inv_rows=self.inv_rows.data_ptr(),
-            fwd_limbs=self.fwd_limbs.data_ptr())
+            fwd_limbs=self.fwd_limbs.data_ptr(),
+            bucket_pre=None if self.bucket_pre is None else self.bucket_pre.data_ptr(),
+            bucket_aff=None if self.bucket_aff is None else self.bucket_aff.data_ptr())
 
     @property
     def ref(self):

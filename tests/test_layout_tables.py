@@ -132,3 +132,44 @@ def test_head_tables_reject_wide_codebooks():
     cb[0, :, :32] = torch.arange(32.0)
     with pytest.raises(ValueError, match="4 bits"):
         HeadTables(None, None, cb, device="cpu")
+
+
+def test_bucket_quantiser_tables_are_exact():
+    """The coarse-to-exact quantiser of the tensor-core kernel (one FMA -> cell -> lower bound -> one
+    exact comparison) must reproduce the full threshold count for every input, whether the device
+    fuses the multiply-add or not."""
+    from jointqk_b200.codebooks import unit_gaussian_centroids
+    from jointqk_b200.layout import BUCKETS, bucket_tables
+
+    rng = np.random.default_rng(0)
+    widths = np.array([1, 2, 3, 4, 4, 3, 2, 4])
+    stds = np.array([1, 0.3, 12.0, 0.01, 3.3, 1e-3, 7.0, 150.0], np.float32)
+    cb = np.zeros((8, 16), np.float32)
+    for i, w in enumerate(widths):
+        cb[i, : 2 ** w] = unit_gaussian_centroids(int(w)).numpy() * stds[i]
+    thr = decision_thresholds(cb, widths)
+    thr16 = np.full((8, 16), np.inf, np.float32)
+    thr16[:, :15] = thr
+    pre, aff, ok = bucket_tables(thr, widths)
+    assert ok and pre.max() <= 15
+    for i, w in enumerate(widths):
+        xs = [rng.normal(size=100000).astype(np.float32) * stds[i] * 1.7]
+        for t in thr[i, : 2 ** w - 1]:
+            xs.append(np.array([np.nextafter(t, -np.inf), t, np.nextafter(t, np.inf)], np.float32))
+        xs.append(np.array([0, 1e30, -1e30, np.nan], np.float32))
+        x = np.concatenate(xs)
+        ref = (x[:, None] >= thr[i][None, :]).sum(-1)
+        for fused in (True, False):
+            with np.errstate(invalid="ignore", over="ignore"):
+                if fused:
+                    y = np.float32(x.astype(np.float64) * float(aff[i, 0]) + float(aff[i, 1]))
+                else:
+                    y = np.float32(np.float32(x * aff[i, 0]) + aff[i, 1])
+            y = np.fmin(np.fmax(y, np.float32(2 ** 23)), np.float32(2 ** 23 + BUCKETS - 1))
+            cell = y.view(np.uint32) & (BUCKETS - 1)
+            p = pre[i][cell].astype(np.int64)
+            assert np.array_equal(p + (x >= thr16[i][p]), ref)
+    # thresholds closer than three cells: the scheme must report that it does not apply
+    tight = np.full((1, 15), np.inf, np.float32)
+    tight[0, :3] = [0.0, 1e-6, 1.0]
+    assert bucket_tables(tight, np.array([2]))[2] is False
