@@ -464,6 +464,8 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
     ap.add_argument("--tokens-per-split", type=int, default=0, help="override the decode split size (0 = library default)")
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments"],
+                    help="profiling aid: run only one of the secondary stages and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -472,6 +474,13 @@ def main() -> None:
         if args.steps > 200:
             args.steps = 200
         run_reference_arm(args, rank, world)
+        return
+    if args.stage != "all":
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
+        hbm, tf, kind = measured_peaks()
+        res = bench_compress(dev, hbm, kind) if args.stage == "compress" else bench_moments(dev, hbm, tf, kind)
+        print(json.dumps(res), flush=True)
         return
     if world > 1:
         import torch.distributed as dist

@@ -69,8 +69,10 @@ __device__ __forceinline__ bool tc_wait(TcSmem& sm, uint64_t* bar, uint32_t pari
   const unsigned long long t0 = now_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 256; ++i)
+    for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
+      __nanosleep(40);  // waiting roles must not eat the issue slots of the working warps
+    }
     if (sm.abort) return false;
     if (now_ns() - t0 > TC_WAIT_NS) {
       sm.abort = 1;
@@ -88,12 +90,22 @@ __device__ __forceinline__ uint32_t search_code(float x, const float* __restrict
   return code;
 }
 
+#ifdef JQK_COMPRESS_PROFILE
+// Development aid: clock totals of the MMA thread (wait full, wait acc_empty, issue) and of epilogue
+// warp 2 (wait acc_full, tmem load, quantise+pack, other).  Not part of the product build.
+__device__ long long g_tc_prof[8];
+#define TCP_MARK(i) do { const long long n__ = clock64(); atomicAdd((unsigned long long*)&g_tc_prof[i], (unsigned long long)(n__ - tp)); tp = n__; } while (0)
+#else
+#define TCP_MARK(i) do {} while (0)
+#endif
+
 template <bool USE_BUCKETS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
                    jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
   extern __shared__ uint8_t smem_raw[];
-  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // align by pointer arithmetic on the __shared__ array (an integer round trip would turn every access into a generic load)
+  TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y, seq = blockIdx.z;
   const int n_tok = pa.n_tokens[seq];
@@ -155,10 +167,15 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       const uint32_t idesc = make_idesc_bf16(128, hd.n_cols, false, false);
       bool ok = tc_wait(sm, &sm.b_full, 0, pa.status);
       int it = 0;
+#ifdef JQK_COMPRESS_PROFILE
+      long long tp = clock64();
+#endif
       for (int t = tile_lo; ok && t < tile_hi; ++t, ++it) {
         const int s = it % TC_STAGES, a = it & 1;
         if (!tc_wait(sm, &sm.full[s], (it / TC_STAGES) & 1, pa.status)) break;
+        TCP_MARK(0);
         if (it >= 2 && !tc_wait(sm, &sm.acc_empty[a], ((it >> 1) & 1) ^ 1, pa.status)) break;
+        TCP_MARK(1);
         tc_fence_after();
         const uint32_t d_tmem = tmem + a * 128;
         const uint32_t a_base = smem_u32(sm.a[s]);
@@ -174,6 +191,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         }
         umma_commit(&sm.empty[s]);     // the key tile may be overwritten
         umma_commit(&sm.acc_full[a]);  // the accumulator may be read
+        TCP_MARK(2);
       }
     }
   } else {
@@ -181,14 +199,37 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
     const int part = ew >> 2;
-    const int w_lo = (hd.n_words * part) >> 2, w_hi = (hd.n_words * (part + 1)) >> 2;
+    // word ranges of the four parts, cut where the column counts are closest to even (low-bit
+    // words hold up to four times as many columns as 4-bit words)
+    int w_lo = 0, w_hi = hd.n_words;
+    {
+      int cut[5];
+      cut[0] = 0; cut[4] = hd.n_words;
+#pragma unroll
+      for (int q = 1; q < 4; ++q) {
+        const int target = (hd.n_active * q + 2) >> 2;
+        int w = cut[q - 1];
+        while (w < hd.n_words && sm.wcb[w] < target) ++w;
+        if (w > cut[q - 1] && w < hd.n_words && target - sm.wcb[w - 1] < sm.wcb[w] - target) --w;
+        cut[q] = max(w, cut[q - 1]);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) if (q == part) { w_lo = cut[q]; w_hi = cut[q + 1]; }
+    }
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
     const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
     const int wpr = tb.words_per_record;
     int it = 0;
+#ifdef JQK_COMPRESS_PROFILE
+    long long tp = clock64();
+    const bool prof_on = (warp == 2 && lane == 0);
+#undef TCP_MARK
+#define TCP_MARK(i) do { const long long n__ = clock64(); if (prof_on) atomicAdd((unsigned long long*)&g_tc_prof[i], (unsigned long long)(n__ - tp)); tp = n__; } while (0)
+#endif
     for (int t = tile_lo; t < tile_hi; ++t, ++it) {
       const int a = it & 1;
       if (!tc_wait(sm, &sm.acc_full[a], (it >> 1) & 1, pa.status)) break;
+      TCP_MARK(3);
       tc_fence_after();
       const int key = t * TC_TILE + row;
       const bool valid = key < n_tok;
@@ -205,6 +246,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       for (int c0 = c_lo & ~15; c0 < c_hi; c0 += 16) {
         float v[16];
         tmem_ld16(t_lane + c0, v);
+        TCP_MARK(4);
         uint32_t code[16];
         if constexpr (USE_BUCKETS) {
           // one fused multiply-add finds the cell, a byte table gives a lower bound of the code that
@@ -247,6 +289,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
             cur |= code[i] << (bp & 31);
           }
         }
+        TCP_MARK(5);
       }
       while (cur_w < w_hi) {
         if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
@@ -256,6 +299,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[a]);
+      TCP_MARK(6);
     }
   }
 
@@ -271,6 +315,17 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 }  // namespace jqk
 
 using namespace jqk;
+
+#ifdef JQK_COMPRESS_PROFILE
+extern "C" int32_t jqk_debug_compress_profile(long long* out8, int32_t reset) {
+  if (cudaMemcpyFromSymbol(out8, g_tc_prof, sizeof(long long) * 8) != cudaSuccess) return 1;
+  if (reset) {
+    long long z[8] = {0};
+    if (cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
 
 // Launches the tensor-core kernel when the call fits it (bf16 keys, head_dim 128, 16-byte aligned
 // strides); returns 1 when the caller should use the fp32 CUDA-core kernel instead.

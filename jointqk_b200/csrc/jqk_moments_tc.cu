@@ -65,7 +65,7 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                   long long n_tokens, int chunk, int group, float* __restrict__ sq, float* __restrict__ sk,
                   float* __restrict__ cqk, int32_t* wait_flag) {
   extern __shared__ uint8_t smem_raw[];
-  MtSmem& sm = *reinterpret_cast<MtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  MtSmem& sm = *reinterpret_cast<MtSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
   const long long t_begin = (long long)blockIdx.x * chunk;
