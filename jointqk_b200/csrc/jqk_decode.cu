@@ -23,6 +23,20 @@
 //     no second launch.
 #include <limits.h>
 
+#ifdef JQK_DECODE_PROFILE
+// Development aid: per-phase clock totals of thread 0 of every block.  Slots 0-6: table build or
+// copy, wait for K, score, softmax, wait for V, MMA, copy issue; slots 8-14: the phases of the
+// in-block table build.  Not part of the product build.
+__device__ long long g_decode_prof[16];
+#define JQK_TABLES_MARK_INIT long long bt_t__ = clock64();
+#define JQK_TABLES_MARK(i)                                                  \
+  do {                                                                      \
+    const long long now__ = clock64();                                      \
+    if (threadIdx.x == 0) atomicAdd((unsigned long long*)&g_decode_prof[8 + (i)], (unsigned long long)(now__ - bt_t__)); \
+    bt_t__ = now__;                                                         \
+  } while (0)
+#endif
+
 #include "jqk_tables.cuh"
 
 namespace jqk {
@@ -60,7 +74,7 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
   const int qh0 = head * group + g0;
   const size_t q_elem0 = (((size_t)seq * n_q_heads + qh0) * n_queries + qi) * d;
   const char* q_ptr = (const char*)q + q_elem0 * (q_dtype == JQK_DTYPE_F32 ? 4 : 2);
-  build_tables(sm, tb, head, hd, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
+  build_tables(sm, tb, head, hd, q_ptr, q_dtype, (size_t)n_queries * d, n_group, [] {});
   const float inv_sqrt_d = 1.0f / sqrtf((float)d);
   for (int tok = t_begin + threadIdx.x; tok < t_end; tok += blockDim.x) {
     const int page = lookup_page(page_table, pt_stride, seq, tok / JQK_PAGE_TOKENS, n_pages, status);
@@ -193,9 +207,6 @@ __device__ __forceinline__ int load_page_window(const int32_t* __restrict__ page
 }
 
 #ifdef JQK_DECODE_PROFILE
-// Development aid: per-phase clock totals of warp 0 of every block (prologue, wait, score,
-// softmax, -, MMA, issue).  Not part of the product build.
-__device__ long long g_decode_prof[8];
 #define PROF_MARK(i)                                                        \
   do {                                                                      \
     const long long now__ = clock64();                                      \
@@ -217,7 +228,7 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   const int head = blockIdx.x / q_blocks, qb = blockIdx.x % q_blocks, seq = blockIdx.y;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
   const HeadDesc hd = load_desc(tb.desc, head);
-  build_tables(sm, tb, head, hd, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d, JQK_DTYPE_BF16, (size_t)hd.d, n_group);
+  build_tables(sm, tb, head, hd, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d, JQK_DTYPE_BF16, (size_t)hd.d, n_group, [] {});
   TableRecord* rec = recs + (size_t)seq * gridDim.x + blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(sm.lut);
   uint4* dst = reinterpret_cast<uint4*>(rec->lut);
@@ -304,13 +315,15 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       if (ok1) bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
     }
   };
-  // the first copies go in flight before the prologue, so HBM works while the tables are built
-  {
+  // The first copies go in flight before the tables exist, so HBM works during the prologue.  A
+  // block that builds its own tables starts them right behind the table build's own small reads.
+  auto first_copies = [&]() {
     const int p0 = __shfl_sync(0xffffffffu, pg_cur, 0), p1 = __shfl_sync(0xffffffffu, pg_cur, 1);
     const int p2 = __shfl_sync(0xffffffffu, pg_cur, 2), p3 = __shfl_sync(0xffffffffu, pg_cur, 3);
     if (n_my > 0) { issue_keys(0, p0, p1); issue_values(0, p0, p1); }
     if (n_my > 1) issue_keys(1, p2, p3);
-  }
+  };
+  if constexpr (!BUILD_IN_BLOCK) first_copies();
 
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
@@ -318,7 +331,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
-    build_tables(sm.t.build, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
+    build_tables(sm.t.build, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group, first_copies);
     tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias};
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];
@@ -507,6 +520,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       if (i == 0) { ws.part_m[pidx] = M; ws.part_l[pidx] = L; }
     }
   }
+  PROF_MARK(7);
   if (single) return;
 
   // ---- the last block of this (sequence, head group) to finish merges the splits ------------
@@ -520,32 +534,91 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   __syncthreads();
   if (!sm.is_last) return;
   __threadfence();
-  for (int e = tid; e < n_group * D; e += DEC_THREADS) {
-    const int h = e / D, i = e % D;
-    const size_t qrow = (size_t)seq * n_q_heads + qh0 + h;
-    const size_t p0 = qrow * ws.max_splits;
-    float M = -CUDART_INF_F;
-    for (int s2 = 0; s2 < n_splits; ++s2) M = fmaxf(M, __ldcg(ws.part_m + p0 + s2));
-    float L = 0.f, A = 0.f;
-    if (M > -CUDART_INF_F) {
-      for (int s2 = 0; s2 < n_splits; ++s2) {
-        const float f = exp2f(__ldcg(ws.part_m + p0 + s2) - M);
-        L += __ldcg(ws.part_l + p0 + s2) * f;
-        A += __ldcg(ws.part_acc + (p0 + s2) * JQK_MAX_DIM + i) * f;
+  // A thread owns four output dims of one head and every third split: it first puts its partial
+  // rows in flight (MERGE_BATCH independent 16-byte loads), then one warp per head turns the
+  // splits' (max, sum) pairs into one weight per split, so a single memory round trip covers both.
+  // (The stages are free: every warp is past the block-level combine.)
+  constexpr int MERGE_GROUPS = DEC_THREADS / 128, MERGE_BATCH = 6;
+  constexpr int F4 = D / 4;
+  float* fac = reinterpret_cast<float*>(&sm.stage[0]);  // [n_splits][JQK_MAX_GROUP]
+  float4* red = reinterpret_cast<float4*>(fac + (size_t)n_splits * JQK_MAX_GROUP);  // [MERGE_GROUPS][128]
+  const int sg = tid >> 7, col = tid & 127;
+  const int mh = col / F4, mi = col % F4;
+  const bool m_active = mh < n_group;
+  const float4* pa = reinterpret_cast<const float4*>(
+      ws.part_acc + ((size_t)seq * n_q_heads + qh0 + (m_active ? mh : 0)) * ws.max_splits * JQK_MAX_DIM) + mi;
+  float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int base = 0; base < n_splits; base += MERGE_GROUPS * MERGE_BATCH) {
+    float4 raw[MERGE_BATCH];
+#pragma unroll
+    for (int j = 0; j < MERGE_BATCH; ++j) {
+      const int s2 = base + sg + MERGE_GROUPS * j;
+      raw[j] = (m_active && s2 < n_splits) ? __ldcg(pa + (size_t)s2 * (JQK_MAX_DIM / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (base == 0) {
+      if (warp < n_group) {
+        const size_t p0 = ((size_t)seq * n_q_heads + qh0 + warp) * ws.max_splits;
+        const float m0 = (lane < n_splits) ? __ldcg(ws.part_m + p0 + lane) : -CUDART_INF_F;
+        const float l0 = (lane < n_splits) ? __ldcg(ws.part_l + p0 + lane) : 0.f;
+        float M = m0;
+        for (int s2 = lane + 32; s2 < n_splits; s2 += 32) M = fmaxf(M, __ldcg(ws.part_m + p0 + s2));
+        M = warp_max(M);
+        const bool any = M > -CUDART_INF_F;
+        float L = 0.f;
+        if (lane < n_splits) {
+          const float f = any ? exp2f(m0 - M) : 0.f;
+          fac[lane * JQK_MAX_GROUP + warp] = f;
+          L = l0 * f;
+        }
+        for (int s2 = lane + 32; s2 < n_splits; s2 += 32) {
+          const float f = any ? exp2f(__ldcg(ws.part_m + p0 + s2) - M) : 0.f;
+          fac[s2 * JQK_MAX_GROUP + warp] = f;
+          L += __ldcg(ws.part_l + p0 + s2) * f;
+        }
+        L = warp_sum(L);
+        if (lane == 0) sm.wl[0][warp] = L;
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < MERGE_BATCH; ++j) {
+      const int s2 = base + sg + MERGE_GROUPS * j;
+      if (m_active && s2 < n_splits) {
+        const float f = fac[s2 * JQK_MAX_GROUP + mh];
+        sum.x = fmaf(raw[j].x, f, sum.x); sum.y = fmaf(raw[j].y, f, sum.y);
+        sum.z = fmaf(raw[j].z, f, sum.z); sum.w = fmaf(raw[j].w, f, sum.w);
       }
     }
-    store_out(out, out_dtype, qrow * D + i, L > 0.f ? A / L : 0.f);
+  }
+  red[sg * 128 + col] = sum;
+  __syncthreads();
+  if (sg == 0 && m_active) {
+    float4 a4 = red[col];
+#pragma unroll
+    for (int k = 1; k < MERGE_GROUPS; ++k) {
+      const float4 o = red[k * 128 + col];
+      a4.x += o.x; a4.y += o.y; a4.z += o.z; a4.w += o.w;
+    }
+    const float L = sm.wl[0][mh];
+    const size_t o0 = ((size_t)seq * n_q_heads + qh0 + mh) * D + 4 * mi;
+    store_out(out, out_dtype, o0 + 0, L > 0.f ? a4.x / L : 0.f);
+    store_out(out, out_dtype, o0 + 1, L > 0.f ? a4.y / L : 0.f);
+    store_out(out, out_dtype, o0 + 2, L > 0.f ? a4.z / L : 0.f);
+    store_out(out, out_dtype, o0 + 3, L > 0.f ? a4.w / L : 0.f);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
+#ifdef JQK_DECODE_PROFILE
+  if (tid == 0) atomicAdd((unsigned long long*)&g_decode_prof[15], (unsigned long long)(clock64() - prof_t));
+#endif
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 #ifdef JQK_DECODE_PROFILE
-extern "C" int32_t jqk_debug_decode_profile(long long* out8, int32_t reset) {
-  if (cudaMemcpyFromSymbol(out8, g_decode_prof, sizeof(long long) * 8) != cudaSuccess) return 1;
+extern "C" int32_t jqk_debug_decode_profile(long long* out16, int32_t reset) {
+  if (cudaMemcpyFromSymbol(out16, g_decode_prof, sizeof(long long) * 16) != cudaSuccess) return 1;
   if (reset) {
-    long long z[8] = {0};
+    long long z[16] = {0};
     if (cudaMemcpyToSymbol(g_decode_prof, z, sizeof(z)) != cudaSuccess) return 1;
   }
   return 0;

@@ -27,6 +27,11 @@ constexpr int TBL_THREADS = 256;  // threads that take part in the query project
 constexpr int TBL_MAX_SHIFT = 7;  // 320 lookups x 2^16 x 2^7 < 2^32: the packed sums stay recoverable
 constexpr int TBL_WORDS = 2 * JQK_MAX_WORDS;  // nibble words, then byte words
 
+#ifndef JQK_TABLES_MARK  // hooks for a development build that times the phases of build_tables
+#define JQK_TABLES_MARK_INIT
+#define JQK_TABLES_MARK(i) do {} while (0)
+#endif
+
 struct TableSmem {
   uint2 lut[JQK_MAX_TABLES * 16];                // 26,624 B: [table][16] x (int16 x 4 heads)
   float part[8][JQK_MAX_COLS][JQK_MAX_GROUP];    // 16,384 B: projection partial sums
@@ -67,12 +72,16 @@ __device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&
 
 // Projects the group's queries into column space and fills the lookup tables.
 //   q_base + h * q_head_stride : the d values of query head h of the group (h < n_group)
-// Every global read is issued before the first barrier so that one memory round trip covers
-// the projection matrix, the codebooks and the table composition.
+// Every global read is issued into registers before anything waits on one, so a single memory
+// round trip covers the projection matrix, the queries, the codebooks and the table composition.
+// `after_loads()` runs right behind those reads: a caller that has bulk traffic of its own to start
+// puts it there, so that the small reads the table build waits on are not queued behind it.
+template <typename AfterLoads>
 __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_tables& tb, int head,
                                              const HeadDesc& hd, const void* q_base, int q_dtype,
-                                             size_t q_head_stride, int n_group) {
+                                             size_t q_head_stride, int n_group, AfterLoads after_loads) {
   const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
+  JQK_TABLES_MARK_INIT
   const int d = hd.d;
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
   const bool projector = tid < TBL_THREADS;
@@ -83,21 +92,35 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     const int i = rg + 8 * r;
     w[r] = (projector && i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  for (int e = tid; e < JQK_MAX_GROUP * JQK_MAX_DIM; e += nthr) {
+  // nthr >= 256: two query values, two codebook quads and one table composition per thread
+  static_assert(JQK_MAX_GROUP * JQK_MAX_DIM <= 2 * TBL_THREADS && JQK_MAX_COLS * 4 <= 2 * TBL_THREADS &&
+                JQK_MAX_TABLES <= TBL_THREADS, "staging assumes at most two items per thread");
+  const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
+  const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
+  float qv[2];
+  float4 cv[2];
+  int4 fv = make_int4(-1, -1, -1, -1);
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int e = tid + u * nthr;
     const int h = e / JQK_MAX_DIM, i = e % JQK_MAX_DIM;
-    sm.qraw[h][i] = (h < n_group && i < d) ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
+    qv[u] = (e < JQK_MAX_GROUP * JQK_MAX_DIM && h < n_group && i < d)
+                ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
+    cv[u] = (e < hd.n_cols * 4) ? __ldg(cb4 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  {
-    const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
-    float4* dst = reinterpret_cast<float4*>(sm.cb);
-    for (int e = tid; e < hd.n_cols * 4; e += nthr) dst[e] = __ldg(cb4 + e);
-    const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
-    int4* fdst = reinterpret_cast<int4*>(sm.fields);
-    for (int e = tid; e < hd.n_tables; e += nthr) fdst[e] = __ldg(f4 + e);
+  if (tid < hd.n_tables) fv = __ldg(f4 + tid);
+  after_loads();
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int e = tid + u * nthr;
+    if (e < JQK_MAX_GROUP * JQK_MAX_DIM) (&sm.qraw[0][0])[e] = qv[u];
+    if (e < hd.n_cols * 4) reinterpret_cast<float4*>(sm.cb)[e] = cv[u];
   }
+  if (tid < hd.n_tables) reinterpret_cast<int4*>(sm.fields)[tid] = fv;
   if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
   if (tid < TBL_WORDS * JQK_MAX_GROUP) (&sm.wmax[0][0])[tid] = 0u;
   __syncthreads();
+  JQK_TABLES_MARK(0);
   if (projector) {
     float a[4][JQK_MAX_GROUP];
 #pragma unroll
@@ -120,6 +143,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
       *reinterpret_cast<float4*>(sm.part[rg][4 * cg + k]) = make_float4(a[k][0], a[k][1], a[k][2], a[k][3]);
   }
   __syncthreads();
+  JQK_TABLES_MARK(1);
   if (tid < JQK_MAX_COLS) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -130,6 +154,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     *reinterpret_cast<float4*>(sm.qproj[tid]) = s;
   }
   __syncthreads();
+  JQK_TABLES_MARK(2);
   const int n_entries = hd.n_tables * 16;
   const int n_scan_words = hd.n_a_words + hd.n_c_words;
   // Largest |entry| per (word, head).  The fields of a table take their codes independently and the
@@ -152,6 +177,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
       atomicMax(&sm.wmax[w][h], __float_as_uint(m[h] * 1.0000005f));  // non-negative floats order as uints
   }
   __syncthreads();
+  JQK_TABLES_MARK(3);
   if (tid < 32) {
     // warp 0 derives the per-word shifts with shuffles: lane w owns scan word w (n_scan_words <= 32)
     const int lane = tid;
@@ -162,8 +188,9 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
       wm[h] = (lane < n_scan_words) ? __uint_as_float(sm.wmax[lane][h]) : 0.f;
       gm[h] = warp_max(wm[h]);
       if (!(gm[h] < CUDART_INF_F)) gm[h] = 0.f;
-      // largest shift that keeps this word inside 16 bits for head h
-      if (gm[h] > 0.f && wm[h] > 0.f) fit = min(fit, max(0, (int)floorf(log2f(gm[h] / wm[h]) - 1e-3f)));
+      // largest shift that keeps this word inside 16 bits for head h: floor(log2(gm / wm)), which for
+      // positive floats is the difference of their bit patterns shifted down by the mantissa width
+      if (gm[h] > 0.f && wm[h] > 0.f) fit = min(fit, max(0, (__float_as_int(gm[h]) - __float_as_int(wm[h])) >> 23));
     }
     // K_w = min over later-or-equal words (suffix minimum): non-decreasing along the scan
     int k = (lane < n_scan_words) ? fit : TBL_MAX_SHIFT;
@@ -193,6 +220,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     }
   }
   __syncthreads();
+  JQK_TABLES_MARK(4);
   float inv[JQK_MAX_GROUP];
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / __uint_as_float(sm.absmax[h]);
@@ -210,6 +238,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     sm.lut[e] = packed;
   }
   __syncthreads();
+  JQK_TABLES_MARK(5);
 }
 
 // Running sums of one record.  An entry word holds a signed 16-bit value in its high half and an

@@ -69,12 +69,12 @@ def build_lut_model(tab, h, q):
     for t in range(n_tables):
         wmax[word_of[t]] = np.maximum(wmax[word_of[t]], tmax[t])
     gmax = wmax.max(0) if n_scan else np.zeros(4, np.float32)
-    fit = np.full(n_scan, 8, np.int64)
+    fit = np.full(n_scan, 7, np.int64)
     for w in range(n_scan):
         for h in range(4):
             if gmax[h] > 0 and wmax[w, h] > 0:
-                fit[w] = min(fit[w], max(0, int(np.floor(np.log2(gmax[h] / wmax[w, h]) - 1e-3))))
-    k = 8
+                fit[w] = min(fit[w], max(0, (int(np.float32(gmax[h]).view(np.int32)) - int(np.float32(wmax[w, h]).view(np.int32))) >> 23))
+    k = 7
     kshift = np.zeros(n_scan, np.int64)
     for w in range(n_scan - 1, -1, -1):
         k = min(k, int(fit[w]))
