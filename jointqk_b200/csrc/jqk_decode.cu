@@ -400,26 +400,33 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 
     // ---- online softmax: the tile maximum is an integer reduction (scores are scale * integer);
     //      the sum of the weights stays per lane and is reduced once after the last tile ----
+    // Written without branches so that the four heads' dependent chains (reduction, conversion,
+    // two exponentials, bf16 split) interleave instead of running one after the other.
     float alpha[JQK_MAX_GROUP];
+    int imax[JQK_MAX_GROUP];
+#pragma unroll
+    for (int h = 0; h < JQK_MAX_GROUP; ++h) imax[h] = __reduce_max_sync(0xffffffffu, ia[h]);
     bool any = false, grew = false;
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      const int imax = __reduce_max_sync(0xffffffffu, ia[h]);
-      alpha[h] = 1.f;
-      float p = 0.f;
-      if (imax != INT_MIN) {
-        any = true;
-        const float m_new = fmaxf(m_run[h], (float)imax * sc[h]);
-        if (m_new > m_run[h]) { alpha[h] = exp2f(m_run[h] - m_new); grew = true; m_run[h] = m_new; }
-        if (lane_ok) p = exp2f((float)ia[h] * sc[h] - m_new);
-      }
+      const bool some = imax[h] != INT_MIN;
+      const float m_tile = some ? (float)imax[h] * sc[h] : -CUDART_INF_F;
+      const float m_new = fmaxf(m_run[h], m_tile);
+      const bool up = m_new > m_run[h];
+      alpha[h] = up ? exp2f(m_run[h] - m_new) : 1.f;  // first valid tile: exp2(-inf) = 0
+      const float p = lane_ok ? exp2f((float)ia[h] * sc[h] - m_new) : 0.f;
+      any |= some;
+      grew |= up;
+      m_run[h] = m_new;
       const __nv_bfloat16 p_hi = __float2bfloat16(p);
       const __nv_bfloat16 p_lo = __float2bfloat16(p - __bfloat162float(p_hi));
       sm.pbuf[warp][0][h][lane] = p_hi;
       sm.pbuf[warp][1][h][lane] = p_lo;
       l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
+    PROF_MARK(3);
     landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
+    PROF_MARK(4);
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
@@ -435,7 +442,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       }
     }
     __syncwarp();
-    PROF_MARK(3);
     if (any && landed) {
       if (grew) {
         const float a_even = (c & 1) ? alpha[2] : alpha[0];  // head 2c   (c >= 2: heads that do not exist)
@@ -447,20 +453,16 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       for (int kb = 0; kb < 2; ++kb) {
         const int pg = kb ? page_hi : page_lo;
         if (pg < 0 || t0 + JQK_PAGE_TOKENS * kb >= t_end) continue;  // warp-uniform
-        uint32_t b[2][2];  // [hi/lo][key half]: P^T fragment, column n = head g
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const uint32_t* prow = reinterpret_cast<const uint32_t*>(&sm.pbuf[warp][t][g & 3][JQK_PAGE_TOKENS * kb]);
-          b[t][0] = (g < JQK_MAX_GROUP) ? prow[c] : 0u;
-          b[t][1] = (g < JQK_MAX_GROUP) ? prow[c + 4] : 0u;
-        }
+        // P^T fragment, column n = g: columns 0..3 carry the high bf16 terms of the four heads and
+        // columns 4..7 (padding otherwise) the low terms, so one MMA per 16 dims covers both
+        const uint32_t* prow = reinterpret_cast<const uint32_t*>(&sm.pbuf[warp][g >> 2][g & 3][JQK_PAGE_TOKENS * kb]);
+        const uint32_t b0 = prow[c], b1 = prow[c + 4];
         const uint32_t vbase = smem_addr(st.v[kb]) + lm_off;
 #pragma unroll
         for (int j = 0; j < DT; ++j) {
           uint32_t a0, a1, a2, a3;
           ldmatrix_x4(vbase + j * 512, a0, a1, a2, a3);
-          mma_bf16_16816(acc[j], a0, a1, a2, a3, b[0][0], b[0][1]);
-          mma_bf16_16816(acc[j], a0, a1, a2, a3, b[1][0], b[1][1]);
+          mma_bf16_16816(acc[j], a0, a1, a2, a3, b0, b1);
         }
       }
     }
@@ -486,6 +488,11 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) { sm.wm[warp][h] = m_run[h]; sm.wl[warp][h] = l_run[h]; }
   }
+  // lanes c and c + 2 hold the high-term and low-term sums of the same heads
+#pragma unroll
+  for (int j = 0; j < DT; ++j)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[j][k] += __shfl_down_sync(0xffffffffu, acc[j][k], 2);
   if (c < 2) {
 #pragma unroll
     for (int j = 0; j < DT; ++j) {
