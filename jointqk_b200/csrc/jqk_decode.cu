@@ -74,7 +74,10 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
   const int qh0 = head * group + g0;
   const size_t q_elem0 = (((size_t)seq * n_q_heads + qh0) * n_queries + qi) * d;
   const char* q_ptr = (const char*)q + q_elem0 * (q_dtype == JQK_DTYPE_F32 ? 4 : 2);
-  build_tables(sm, tb, head, hd, q_ptr, q_dtype, (size_t)n_queries * d, n_group, [] {});
+  {
+    const TableLoads ld = issue_table_loads(tb, head, d, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
+    build_tables(sm, hd, ld);
+  }
   const float inv_sqrt_d = 1.0f / sqrtf((float)d);
   for (int tok = t_begin + threadIdx.x; tok < t_end; tok += blockDim.x) {
     const int page = lookup_page(page_table, pt_stride, seq, tok / JQK_PAGE_TOKENS, n_pages, status);
@@ -228,7 +231,11 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   const int head = blockIdx.x / q_blocks, qb = blockIdx.x % q_blocks, seq = blockIdx.y;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
   const HeadDesc hd = load_desc(tb.desc, head);
-  build_tables(sm, tb, head, hd, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d, JQK_DTYPE_BF16, (size_t)hd.d, n_group, [] {});
+  {
+    const TableLoads ld = issue_table_loads(tb, head, hd.d, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d,
+                                            JQK_DTYPE_BF16, (size_t)hd.d, n_group);
+    build_tables(sm, hd, ld);
+  }
   TableRecord* rec = recs + (size_t)seq * gridDim.x + blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(sm.lut);
   uint4* dst = reinterpret_cast<uint4*>(rec->lut);
@@ -267,6 +274,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     return;
   }
   if (split >= n_splits) return;
+  // the table build's reads go out first: nothing a block does later is queued ahead of them
+  TableLoads tloads;
+  if constexpr (BUILD_IN_BLOCK)
+    tloads = issue_table_loads(tb, head, D, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
   const HeadDesc hd = load_desc(tb.desc, head);
   const int t_begin = split * tokens_per_split;
   const int t_end = min(len, t_begin + tokens_per_split);
@@ -315,15 +326,13 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       if (ok1) bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
     }
   };
-  // The first copies go in flight before the tables exist, so HBM works during the prologue.  A
-  // block that builds its own tables starts them right behind the table build's own small reads.
-  auto first_copies = [&]() {
+  // the first copies go in flight before the tables exist, so HBM works during the prologue
+  {
     const int p0 = __shfl_sync(0xffffffffu, pg_cur, 0), p1 = __shfl_sync(0xffffffffu, pg_cur, 1);
     const int p2 = __shfl_sync(0xffffffffu, pg_cur, 2), p3 = __shfl_sync(0xffffffffu, pg_cur, 3);
     if (n_my > 0) { issue_keys(0, p0, p1); issue_values(0, p0, p1); }
     if (n_my > 1) issue_keys(1, p2, p3);
-  };
-  if constexpr (!BUILD_IN_BLOCK) first_copies();
+  }
 
 #ifdef JQK_DECODE_PROFILE
   long long prof_t = clock64();
@@ -331,7 +340,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
-    build_tables(sm.t.build, tb, head, hd, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group, first_copies);
+    build_tables(sm.t.build, hd, tloads);
     tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias};
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];

@@ -70,53 +70,61 @@ __device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&
   }
 }
 
-// Projects the group's queries into column space and fills the lookup tables.
+// The global reads of the table build, issued into registers as early as the caller can: one
+// memory round trip covers the projection matrix, the queries, the codebooks and the table
+// composition, and it overlaps whatever the caller does before it needs the tables.
+struct TableLoads {
+  float4 w[JQK_MAX_DIM / 8];
+  float qv[2];
+  float4 cv[2];
+  int4 fv;
+};
+
 //   q_base + h * q_head_stride : the d values of query head h of the group (h < n_group)
-// Every global read is issued into registers before anything waits on one, so a single memory
-// round trip covers the projection matrix, the queries, the codebooks and the table composition.
-// `after_loads()` runs right behind those reads: a caller that has bulk traffic of its own to start
-// puts it there, so that the small reads the table build waits on are not queued behind it.
-template <typename AfterLoads>
-__device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_tables& tb, int head,
-                                             const HeadDesc& hd, const void* q_base, int q_dtype,
-                                             size_t q_head_stride, int n_group, AfterLoads after_loads) {
-  const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
-  JQK_TABLES_MARK_INIT
-  const int d = hd.d;
+// Needs blockDim.x >= TBL_THREADS.  Codebooks and table composition are read at their full
+// per-head extent (both arrays are allocated at it), so the head descriptor is not needed yet.
+__device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& tb, int head, int d, const void* q_base,
+                                                        int q_dtype, size_t q_head_stride, int n_group) {
+  static_assert(JQK_MAX_GROUP * JQK_MAX_DIM <= 2 * TBL_THREADS && JQK_MAX_COLS * 4 <= 2 * TBL_THREADS &&
+                JQK_MAX_TABLES <= TBL_THREADS, "staging assumes at most two items per thread");
+  const int tid = threadIdx.x, nthr = blockDim.x;
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
   const bool projector = tid < TBL_THREADS;
   const float4* P4 = reinterpret_cast<const float4*>(tb.qproj_cols + (size_t)head * d * 128);
-  float4 w[JQK_MAX_DIM / 8];
+  const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
+  const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
+  TableLoads ld;
 #pragma unroll
   for (int r = 0; r < JQK_MAX_DIM / 8; ++r) {
     const int i = rg + 8 * r;
-    w[r] = (projector && i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ld.w[r] = (projector && i < d) ? __ldg(P4 + (size_t)i * 32 + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  // nthr >= 256: two query values, two codebook quads and one table composition per thread
-  static_assert(JQK_MAX_GROUP * JQK_MAX_DIM <= 2 * TBL_THREADS && JQK_MAX_COLS * 4 <= 2 * TBL_THREADS &&
-                JQK_MAX_TABLES <= TBL_THREADS, "staging assumes at most two items per thread");
-  const float4* cb4 = reinterpret_cast<const float4*>(tb.cb_cols + (size_t)head * 128 * 16);
-  const int4* f4 = reinterpret_cast<const int4*>(tb.table_fields + (size_t)head * JQK_MAX_TABLES * 4);
-  float qv[2];
-  float4 cv[2];
-  int4 fv = make_int4(-1, -1, -1, -1);
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int e = tid + u * nthr;
     const int h = e / JQK_MAX_DIM, i = e % JQK_MAX_DIM;
-    qv[u] = (e < JQK_MAX_GROUP * JQK_MAX_DIM && h < n_group && i < d)
-                ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
-    cv[u] = (e < hd.n_cols * 4) ? __ldg(cb4 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ld.qv[u] = (e < JQK_MAX_GROUP * JQK_MAX_DIM && h < n_group && i < d)
+                   ? load_as_f32(q_base, q_dtype, (size_t)h * q_head_stride + i) : 0.f;
+    ld.cv[u] = (e < JQK_MAX_COLS * 4) ? __ldg(cb4 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  if (tid < hd.n_tables) fv = __ldg(f4 + tid);
-  after_loads();
+  ld.fv = (tid < JQK_MAX_TABLES) ? __ldg(f4 + tid) : make_int4(-1, -1, -1, -1);
+  return ld;
+}
+
+// Projects the group's queries into column space and fills the lookup tables from the reads that
+// issue_table_loads() started.
+__device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld) {
+  const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
+  JQK_TABLES_MARK_INIT
+  const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
+  const bool projector = tid < TBL_THREADS;
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int e = tid + u * nthr;
-    if (e < JQK_MAX_GROUP * JQK_MAX_DIM) (&sm.qraw[0][0])[e] = qv[u];
-    if (e < hd.n_cols * 4) reinterpret_cast<float4*>(sm.cb)[e] = cv[u];
+    if (e < JQK_MAX_GROUP * JQK_MAX_DIM) (&sm.qraw[0][0])[e] = ld.qv[u];
+    if (e < JQK_MAX_COLS * 4) reinterpret_cast<float4*>(sm.cb)[e] = ld.cv[u];
   }
-  if (tid < hd.n_tables) reinterpret_cast<int4*>(sm.fields)[tid] = fv;
+  if (tid < JQK_MAX_TABLES) reinterpret_cast<int4*>(sm.fields)[tid] = ld.fv;
   if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
   if (tid < TBL_WORDS * JQK_MAX_GROUP) (&sm.wmax[0][0])[tid] = 0u;
   __syncthreads();
@@ -131,7 +139,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const jqk_head_table
     for (int r = 0; r < JQK_MAX_DIM / 8; ++r) {
       const int i = rg + 8 * r;  // beyond d: w[r] is zero and qraw is zero
       const float q0 = sm.qraw[0][i], q1 = sm.qraw[1][i], q2 = sm.qraw[2][i], q3 = sm.qraw[3][i];
-      const float wk[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+      const float wk[4] = {ld.w[r].x, ld.w[r].y, ld.w[r].z, ld.w[r].w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         a[k][0] = fmaf(q0, wk[k], a[k][0]); a[k][1] = fmaf(q1, wk[k], a[k][1]);
