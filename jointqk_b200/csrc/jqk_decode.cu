@@ -22,6 +22,7 @@
 //   * partial results of the splits are merged by the last block to finish (atomic ticket),
 //     no second launch.
 #include <limits.h>
+#include <stdlib.h>
 
 #ifdef JQK_DECODE_PROFILE
 // Development aid: per-phase clock totals of thread 0 of every block.  Slots 0-6: table build or
@@ -263,6 +264,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
   const int head = blockIdx.y / q_blocks, qb = blockIdx.y % q_blocks;
   const int seq = blockIdx.z, split = blockIdx.x;
+  // Launched as a programmatic dependent: everything up to here overlaps the tail of the previous
+  // kernel on the stream; nothing in memory is read or written before that kernel has completed.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int len = seq_lens[seq];
   const int n_splits = (len + tokens_per_split - 1) / tokens_per_split;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
@@ -747,12 +752,26 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
         *tables, (const __nv_bfloat16*)q, n_q_heads, ws.tables);
     JQK_CUDA_OK(cudaGetLastError(), "decode tables launch");
   }
+  // Programmatic dependent launch: the blocks may become resident while the previous kernel on the
+  // stream drains; they wait for it to complete (griddepcontrol.wait) before they touch memory.
+  static const bool use_pdl = getenv("JQK_DISABLE_PDL") == nullptr;
+  cudaLaunchAttribute pdl_attr[1];
+  pdl_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(DEC_THREADS);
+  cfg.dynamicSmemBytes = sizeof(DecodeSmem);
+  cfg.stream = st;
+  cfg.attrs = pdl_attr;
+  cfg.numAttrs = use_pdl ? 1 : 0;
 #define JQK_LAUNCH_DECODE(DIM, INB)                                                                              \
   do {                                                                                                           \
     JQK_SMEM_ONCE((decode_kernel<DIM, INB>), sizeof(DecodeSmem), "decode smem attribute");                       \
-    decode_kernel<DIM, INB><<<grid, DEC_THREADS, sizeof(DecodeSmem), st>>>(                                      \
-        *tables, (const __nv_bfloat16*)q, n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride,  \
-        n_pages, k_pool, (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status);                              \
+    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB>, *tables, (const __nv_bfloat16*)q, n_q_heads,   \
+                                   seq_lens, tokens_per_split, page_table, page_table_stride, n_pages, k_pool,   \
+                                   (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status),                    \
+                "decode launch");                                                                                \
   } while (0)
   if (tables->d == 128) { if (in_block) JQK_LAUNCH_DECODE(128, true); else JQK_LAUNCH_DECODE(128, false); }
   else { if (in_block) JQK_LAUNCH_DECODE(64, true); else JQK_LAUNCH_DECODE(64, false); }
