@@ -18,6 +18,8 @@
 //               (word-major pages: 64-byte segments per warp store).
 // Every mbarrier wait is bounded in time; on expiry the block flags JQK_STATUS_WAIT_EXPIRED,
 // drains its copies, frees TMEM and returns.
+#include <math_constants.h>
+
 #include "jqk_common.cuh"
 #include "jqk_sm100.cuh"
 
@@ -32,17 +34,22 @@ constexpr int TC_EPI_WARPS = 16;  // four per TMEM lane quarter, each taking a q
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
 constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
-constexpr uint32_t TC_TMEM_COLS = 256;               // two fp32 accumulators of 128 columns
+constexpr uint32_t TC_TMEM_COLS = 512;               // two fp32 accumulators of 128 columns; the rest is only
+                                                     // there so that a 16-column read may start at any column
+constexpr int TC_COL_PAD = 128 + CH;                 // per-column tables cover a read that starts at column 127
+constexpr int TC_PART_WORDS = 4;                     // words a part's registers hold (more: generic path)
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
 
 struct TcSmem {
   uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
-  float thr[128 * 16];
-  uint8_t pre[128 * 128];   // coarse-to-exact quantiser: lower bound of the code per cell
-  float2 aff[128];          // cell = low 7 bits of clamp(x * aff.x + aff.y)
+  float thr[TC_COL_PAD * 16];
+  uint8_t pre[TC_COL_PAD * 128];  // coarse-to-exact quantiser: lower bound of the code per cell
+  float2 aff[TC_COL_PAD];         // cell = round(127 * saturate(x * aff.x + aff.y))
+  uint4 mult[TC_COL_PAD];         // 1 << bit position in word j of the column's part (one of four is non-zero)
   int32_t meta[128];
   int32_t wcb[JQK_MAX_WORDS + 4];
+  int32_t cut[5];                 // word ranges of the four parts
   uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], b_full;
   uint32_t tmem_base;
   volatile int abort;
@@ -100,6 +107,49 @@ __device__ long long g_tc_prof[8];
 #define TCP_MARK(i) do {} while (0)
 #endif
 
+// Codes of 16 consecutive columns (first column c0, any alignment) of one key, added at their bit
+// positions into the registers of the part's words.  Branch-free, so the 16 dependent chains
+// (cell, lower bound, exact comparison) overlap.  TAIL: only the first n_here columns belong to
+// the part.  The cell tables give code 0 for columns past the head's last column.
+template <bool USE_BUCKETS, bool TAIL>
+__device__ __forceinline__ void quant_chunk(const TcSmem& sm, const float (&v)[CH], int c0, int n_here,
+                                            uint32_t (&cur)[TC_PART_WORDS]) {
+  uint32_t code[CH];
+  if constexpr (USE_BUCKETS) {
+    // two fused multiply-adds find the cell (the first one saturates to [0, 1], which is the clamp),
+    // a byte table gives a lower bound of the code that is at most one short, one exact comparison
+    // with the fp32 decision threshold settles it
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const float2 af = sm.aff[c0 + i];
+      const float y = __saturatef(fmaf(v[i], af.x, af.y));
+      const uint32_t cell = __float_as_uint(fmaf(y, 127.f, 8388608.f)) - 0x4B000000u;
+      const uint32_t k = sm.pre[(c0 + i) * 128 + cell];
+      code[i] = k + ((v[i] >= sm.thr[(c0 + i) * 16 + k]) ? 1u : 0u);
+    }
+  } else {
+    // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
+    // their last level)
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const float* th = sm.thr + (c0 + i) * 16;
+      uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
+      k += (v[i] >= th[k + 3]) ? 4u : 0u;
+      k += (v[i] >= th[k + 1]) ? 2u : 0u;
+      k += (v[i] >= th[k]) ? 1u : 0u;
+      code[i] = k;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    if (!TAIL || i < n_here) {  // warp-uniform
+      const uint4 m = sm.mult[c0 + i];
+      cur[0] += code[i] * m.x; cur[1] += code[i] * m.y;
+      cur[2] += code[i] * m.z; cur[3] += code[i] * m.w;
+    }
+  }
+}
+
 template <bool USE_BUCKETS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
@@ -117,13 +167,24 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   const HeadDesc hd = load_desc(tb.desc, head);
 
   // ---- set-up ----
-  for (int e = tid; e < hd.n_cols * 16; e += TC_THREADS) sm.thr[e] = tb.thresholds[(size_t)head * 128 * 16 + e];
+  // per-column tables; columns past n_cols (reachable by the last 16-column read of a part) quantise to code 0
+  for (int e = tid; e < TC_COL_PAD * 16; e += TC_THREADS)
+    sm.thr[e] = (e < hd.n_cols * 16) ? tb.thresholds[(size_t)head * 128 * 16 + e] : CUDART_INF_F;
   for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
-  if constexpr (USE_BUCKETS) {
+  {
     const uint4* src = reinterpret_cast<const uint4*>(tb.bucket_pre + (size_t)head * 128 * 128);
     uint4* dst = reinterpret_cast<uint4*>(sm.pre);
-    for (int e = tid; e < hd.n_cols * 8; e += TC_THREADS) dst[e] = src[e];
-    for (int e = tid; e < 128; e += TC_THREADS) sm.aff[e] = reinterpret_cast<const float2*>(tb.bucket_aff)[(size_t)head * 128 + e];
+    for (int e = tid; e < TC_COL_PAD * 8; e += TC_THREADS)
+      dst[e] = (USE_BUCKETS && e < hd.n_cols * 8) ? src[e] : make_uint4(0u, 0u, 0u, 0u);
+    for (int e = tid; e < TC_COL_PAD; e += TC_THREADS) {
+      float2 af = make_float2(0.f, 0.f);
+      if (USE_BUCKETS && e < hd.n_cols) {
+        // host form: cell = clamp(round(x * inv_step + off), 0, 127) with 2^23 folded into off
+        const float2 h2 = reinterpret_cast<const float2*>(tb.bucket_aff)[(size_t)head * 128 + e];
+        af = make_float2(h2.x * (1.f / 127.f), (h2.y - 8388608.f) * (1.f / 127.f));
+      }
+      sm.aff[e] = af;
+    }
   }
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
@@ -202,8 +263,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int part = ew >> 2;
     // word ranges of the four parts, cut where the column counts are closest to even (low-bit
     // words hold up to four times as many columns as 4-bit words)
-    int w_lo = 0, w_hi = hd.n_words;
-    {
+    if (ew == 0 && lane == 0) {
       int cut[5];
       cut[0] = 0; cut[4] = hd.n_words;
 #pragma unroll
@@ -215,8 +275,29 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         cut[q] = max(w, cut[q - 1]);
       }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) if (q == part) { w_lo = cut[q]; w_hi = cut[q + 1]; }
+      for (int q = 0; q < 5; ++q) sm.cut[q] = cut[q];
     }
+    asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+    {  // bit position of every column as a multiplier for the word registers of its part
+      const int et = tid - 64;
+      if (et < TC_COL_PAD) {
+        uint4 m = make_uint4(0u, 0u, 0u, 0u);
+        if (et < hd.n_active) {
+          const int bp = (sm.meta[et] >> 4) & 1023;
+          const int w = bp >> 5;
+          int p = 0;
+          while (p < 3 && w >= sm.cut[p + 1]) ++p;
+          const int j = w - sm.cut[p];
+          const uint32_t one = 1u << (bp & 31);
+          m.x = (j == 0) ? one : 0u; m.y = (j == 1) ? one : 0u;
+          m.z = (j == 2) ? one : 0u; m.w = (j == 3) ? one : 0u;
+        }
+        sm.mult[et] = m;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
+    const int w_lo = sm.cut[part], w_hi = sm.cut[part + 1];
+    const bool in_regs = (w_hi - w_lo) <= TC_PART_WORDS;  // otherwise: the generic word-by-word path
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
     const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
     const int wpr = tb.words_per_record;
@@ -242,61 +323,46 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
           dst = k_pool + ((size_t)page * tb.n_heads + head) * wpr * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS);
       }
       const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
-      int cur_w = w_lo;
-      uint32_t cur = 0;
-      for (int c0 = c_lo & ~(CH - 1); c0 < c_hi; c0 += CH) {
-        float v[CH];
-        static_assert(CH == 16, "a 32-column load per thread measured slower: 0.44 ms against 0.29 ms for 1M keys");
-        tmem_ld16(t_lane + c0, v);
-        TCP_MARK(4);
-        uint32_t code[CH];
-        if constexpr (USE_BUCKETS) {
-          // one fused multiply-add finds the cell, a byte table gives a lower bound of the code that
-          // is at most one short, one exact comparison settles it
-#pragma unroll
-          for (int i = 0; i < CH; ++i) {
-            const float2 af = sm.aff[c0 + i];
-            float y = fmaf(v[i], af.x, af.y);
-            y = fminf(fmaxf(y, 8388608.f), 8388608.f + 127.f);
-            const uint32_t k = sm.pre[(c0 + i) * 128 + (__float_as_uint(y) & 127u)];
-            code[i] = k + ((v[i] >= sm.thr[(c0 + i) * 16 + k]) ? 1u : 0u);
-          }
-        } else {
-          // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
-          // their last level); keeping them branch-free lets the loads of all 16 overlap
-#pragma unroll
-          for (int i = 0; i < CH; ++i) {
-            const float* th = sm.thr + (c0 + i) * 16;
-            uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
-            k += (v[i] >= th[k + 3]) ? 4u : 0u;
-            k += (v[i] >= th[k + 1]) ? 2u : 0u;
-            k += (v[i] >= th[k]) ? 1u : 0u;
-            code[i] = k;
-          }
+      if (in_regs) {
+        uint32_t cur[TC_PART_WORDS] = {0u, 0u, 0u, 0u};
+        for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
+          float v[CH];
+          tmem_ld16(t_lane + c0, v);
+          TCP_MARK(4);
+          if (c0 + CH <= c_hi) quant_chunk<USE_BUCKETS, false>(sm, v, c0, CH, cur);
+          else quant_chunk<USE_BUCKETS, true>(sm, v, c0, c_hi - c0, cur);
+          TCP_MARK(5);
         }
-        int mt[CH];
+        if (dst) {
 #pragma unroll
-        for (int i = 0; i < CH; ++i) mt[i] = sm.meta[c0 + i];
-#pragma unroll
-        for (int i = 0; i < CH; ++i) {
-          const int c = c0 + i;
-          if (c >= c_lo && c < c_hi) {  // warp-uniform
-            const int bp = (mt[i] >> 4) & 1023;
-            const int w = bp >> 5;
-            while (cur_w < w) {  // finished words (and pad words) leave in order
+          for (int j = 0; j < TC_PART_WORDS; ++j)
+            if (w_lo + j < w_hi) dst[(w_lo + j) * JQK_PAGE_TOKENS] = cur[j];
+        }
+      } else {
+        int cur_w = w_lo;
+        uint32_t cur = 0;
+        for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
+          float v[CH];
+          tmem_ld16(t_lane + c0, v);
+          for (int i = 0; i < CH && c0 + i < c_hi; ++i) {
+            const int m = sm.meta[c0 + i];
+            const int bp = (m >> 4) & 1023;
+            while (cur_w < (bp >> 5)) {  // finished words (and pad words) leave in order
               if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
               cur = 0;
               ++cur_w;
             }
-            cur |= code[i] << (bp & 31);
+            float x = v[0];  // v[i] without dynamic register indexing
+#pragma unroll
+            for (int u = 1; u < CH; ++u) x = (u == i) ? v[u] : x;
+            cur |= search_code(x, sm.thr + (c0 + i) * 16, m & 15) << (bp & 31);
           }
         }
-        TCP_MARK(5);
-      }
-      while (cur_w < w_hi) {
-        if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
-        cur = 0;
-        ++cur_w;
+        while (cur_w < w_hi) {
+          if (dst) dst[cur_w * JQK_PAGE_TOKENS] = cur;
+          cur = 0;
+          ++cur_w;
+        }
       }
       tc_fence_before();
       __syncwarp();
