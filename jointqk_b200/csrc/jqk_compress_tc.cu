@@ -110,8 +110,8 @@ __device__ long long g_tc_prof[8];
 // Codes of 16 consecutive columns (first column c0, any alignment) of one key, added at their bit
 // positions into the registers of the part's words.  Branch-free, so the 16 dependent chains
 // (cell, lower bound, exact comparison) overlap.  TAIL: only the first n_here columns belong to
-// the part.  The cell tables give code 0 for columns past the head's last column.
-template <bool USE_BUCKETS, bool TAIL>
+// the part; J: words of the part.  The cell tables give code 0 for columns past the head's last column.
+template <bool USE_BUCKETS, bool TAIL, int J>
 __device__ __forceinline__ void quant_chunk(const TcSmem& sm, const float (&v)[CH], int c0, int n_here,
                                             uint32_t (&cur)[TC_PART_WORDS]) {
   uint32_t code[CH];
@@ -144,8 +144,10 @@ __device__ __forceinline__ void quant_chunk(const TcSmem& sm, const float (&v)[C
   for (int i = 0; i < CH; ++i) {
     if (!TAIL || i < n_here) {  // warp-uniform
       const uint4 m = sm.mult[c0 + i];
-      cur[0] += code[i] * m.x; cur[1] += code[i] * m.y;
-      cur[2] += code[i] * m.z; cur[3] += code[i] * m.w;
+      cur[0] += code[i] * m.x;
+      if constexpr (J > 1) cur[1] += code[i] * m.y;
+      if constexpr (J > 2) cur[2] += code[i] * m.z;
+      if constexpr (J > 3) cur[3] += code[i] * m.w;
     }
   }
 }
@@ -158,6 +160,9 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   // align by pointer arithmetic on the __shared__ array (an integer round trip would turn every access into a generic load)
   TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef JQK_COMPRESS_PROFILE
+  const long long t_block0 = clock64();
+#endif
   const int head = blockIdx.y, seq = blockIdx.z;
   const int n_tok = pa.n_tokens[seq];
   const int n_tiles = (n_tok + TC_TILE - 1) / TC_TILE;
@@ -297,7 +302,8 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
     const int w_lo = sm.cut[part], w_hi = sm.cut[part + 1];
-    const bool in_regs = (w_hi - w_lo) <= TC_PART_WORDS;  // otherwise: the generic word-by-word path
+    const int n_part_words = w_hi - w_lo;
+    const bool in_regs = n_part_words <= TC_PART_WORDS;  // otherwise: the generic word-by-word path
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
     const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
     const int wpr = tb.words_per_record;
@@ -325,12 +331,29 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
       if (in_regs) {
         uint32_t cur[TC_PART_WORDS] = {0u, 0u, 0u, 0u};
-        for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
-          float v[CH];
-          tmem_ld16(t_lane + c0, v);
+        // the TMEM read of the next 16 columns is in flight while these are quantised
+        float v[2][CH];
+        tmem_ld16_nowait(t_lane + c_lo, v[0]);
+        int buf = 0;
+        for (int c0 = c_lo; c0 < c_hi; c0 += CH, buf ^= 1) {
+          if (buf == 0) tmem_ld_wait(v[0]); else tmem_ld_wait(v[1]);
+          if (c0 + CH < c_hi) {
+            if (buf == 0) tmem_ld16_nowait(t_lane + c0 + CH, v[1]); else tmem_ld16_nowait(t_lane + c0 + CH, v[0]);
+          }
           TCP_MARK(4);
-          if (c0 + CH <= c_hi) quant_chunk<USE_BUCKETS, false>(sm, v, c0, CH, cur);
-          else quant_chunk<USE_BUCKETS, true>(sm, v, c0, c_hi - c0, cur);
+          const int n_here = c_hi - c0;
+#define JQK_QUANT(JW)                                                                         \
+          do {                                                                                \
+            if (buf == 0) {                                                                   \
+              if (n_here >= CH) quant_chunk<USE_BUCKETS, false, JW>(sm, v[0], c0, CH, cur);   \
+              else quant_chunk<USE_BUCKETS, true, JW>(sm, v[0], c0, n_here, cur);             \
+            } else {                                                                          \
+              if (n_here >= CH) quant_chunk<USE_BUCKETS, false, JW>(sm, v[1], c0, CH, cur);   \
+              else quant_chunk<USE_BUCKETS, true, JW>(sm, v[1], c0, n_here, cur);             \
+            }                                                                                 \
+          } while (0)
+          if (n_part_words <= 2) JQK_QUANT(2); else JQK_QUANT(4);
+#undef JQK_QUANT
           TCP_MARK(5);
         }
         if (dst) {
@@ -374,6 +397,9 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
+#ifdef JQK_COMPRESS_PROFILE
+  if (tid == 64) atomicAdd((unsigned long long*)&g_tc_prof[7], (unsigned long long)(clock64() - t_block0));
+#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, TC_TMEM_COLS);
@@ -424,9 +450,10 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
     if (!encode_bf16_map(&limb_map, tables->fwd_limbs, 2, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "limb tensor map: %s", err);
   }
   const int max_tiles = (max_tokens + TC_TILE - 1) / TC_TILE;
-  // about two waves of blocks over 148 SMs, each block a contiguous run of tiles of one head
+  // at most one wave of blocks over 148 SMs (a block's set-up loads 120 KB of tables), each block a
+  // contiguous run of tiles of one head
   const long long pairs = (long long)n_seqs * tables->n_heads;
-  long long blocks_per_pair = (2 * 148 + pairs - 1) / pairs;
+  long long blocks_per_pair = 148 / pairs;
   if (blocks_per_pair < 1) blocks_per_pair = 1;
   int tiles_per_block = (int)((max_tiles + blocks_per_pair - 1) / blocks_per_pair);
   if (tiles_per_block < 4) tiles_per_block = 4;
