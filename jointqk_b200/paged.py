@@ -236,6 +236,7 @@ class PagedKVCache:
         self.seq_lens = torch.zeros(max(1, len(max_lengths)), dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ws: DecodeWorkspace | None = None
+        self._host_step: dict | None = None
 
     def prefill(self, keys: torch.Tensor, values: torch.Tensor, lengths: list[int] | None = None) -> None:
         """keys/values (n_seqs, H, S, d).  Appends ``lengths[s]`` tokens to every sequence."""
@@ -269,3 +270,59 @@ class PagedKVCache:
         out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
         return decode_attend(self.tables, q, self.seq_lens, max_len, self.page_table, self.k_pool, self.v_pool,
                              out, self._ws, self.status, tps)
+
+    def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0) -> torch.Tensor:
+        """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
+        pinned host tensor that the next call overwrites.
+
+        The copy of the query to the device, the decode launch and the copy of the result back are
+        captured once as a CUDA graph (per batch shape, context length and split); every call stages
+        the query in pinned memory, replays the graph and waits for it, so the host pays one graph
+        launch and one synchronisation per step instead of three enqueues.  The cache must not grow
+        between capture and replay: a call after ``prefill`` captures again."""
+        if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3:
+            raise ValueError("q_host must be a bf16 (n_seqs, n_q_heads, d) tensor in host memory")
+        dev = self.tables.device
+        n_seqs, n_q_heads, d = q_host.shape
+        hs = self._host_step
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split))
+        if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
+            max_len = max(self.lengths) if self.lengths else 0
+            tps = tokens_per_split or default_split(n_seqs, n_q_heads, self.tables.n_heads, max(max_len, 1))
+            max_splits = max(1, -(-max_len // tps))
+            if self._ws is None or self._ws.max_splits < max_splits:
+                self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
+            hs = {"key": key, "lengths": list(self.lengths),
+                  "q_pin": torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16).pin_memory(),
+                  "out_pin": torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
+                  "q_dev": torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
+                  "out_dev": torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32, device=dev),
+                  "stream": torch.cuda.Stream(dev)}
+
+            def enqueue() -> None:
+                hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
+                decode_attend(self.tables, hs["q_dev"], self.seq_lens, max_len, self.page_table, self.k_pool,
+                              self.v_pool, hs["out_dev"], self._ws, self.status, tps)
+                hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
+
+            hs["q_pin"].copy_(q_host)
+            with torch.cuda.stream(hs["stream"]):
+                enqueue()                      # first call outside capture: one-time set-up of the library
+                hs["stream"].synchronize()
+                hs["graph"] = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(hs["graph"], stream=hs["stream"]):
+                    enqueue()
+            self._host_step = hs
+        if q_host.data_ptr() != hs["q_pin"].data_ptr():
+            hs["q_pin"].copy_(q_host)
+        hs["graph"].replay()
+        torch.cuda.current_stream(dev).synchronize()   # the graph is launched on the current stream
+        return hs["out_pin"]
+
+    def host_query_buffer(self, n_seqs: int, n_q_heads: int) -> torch.Tensor | None:
+        """The pinned query buffer of ``decode_host`` once a graph exists for this shape: writing the
+        query straight into it saves ``decode_host`` its host-to-host copy."""
+        hs = self._host_step
+        if hs is None or hs["q_pin"].shape[:2] != (n_seqs, n_q_heads):
+            return None
+        return hs["q_pin"]

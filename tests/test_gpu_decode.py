@@ -125,6 +125,24 @@ def test_decode_bf16_output_and_page_permutation_invariance():
     assert ((b - ref).abs() / scale).max().item() < OUT_TOL
 
 
+def test_decode_from_host_buffers_equals_device_call():
+    """PagedKVCache.decode_host (graph of H2D copy, decode, D2H copy) returns what decode() returns,
+    also when replayed with a new query and after the cache has grown."""
+    keys, comps, sig, tables = _setup(2, 2048, 2.0)
+    g = torch.Generator().manual_seed(5)
+    v = torch.randn(1, 2, 2048, 128, generator=g).to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, [2048])
+    cache.prefill(keys[:, :1500].unsqueeze(0).cuda(), v[:, :, :1500].cuda())
+    for rep in range(3):
+        q = torch.randn(1, 8, 128, generator=g).to(torch.bfloat16)
+        if rep == 2:
+            cache.prefill(keys[:, 1500:1501].unsqueeze(0).cuda(), v[:, :, 1500:1501].cuda())   # append one token
+        got = cache.decode_host(q).clone()
+        want = cache.decode(q.cuda()).cpu()
+        assert torch.equal(got, want)
+    paged.check_status(cache.status)
+
+
 def test_decode_split_invariance_at_context_32768():
     """Full-context property: the result does not depend on how the keys are split over blocks."""
     H, N = 8, 32768
