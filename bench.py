@@ -337,6 +337,11 @@ def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict
 # ----------------------------------------------------------------------------------------------
 # main arm
 # ----------------------------------------------------------------------------------------------
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch of the headline workload,
+# from the ncu capture summarised in profiles/decode_kernel_ctx32768_2bit.md (76.20 MB + 1.46 MB)
+DECODE_DRAM_TRAFFIC_BYTES = 77.66e6
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     import torch.distributed as dist
     from jointqk_b200 import paged
@@ -436,7 +441,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                 "steps": e2e_steps, "note": "host query in, pinned-host result out through PagedKVCache.decode_host (graph of H2D copy, decode, D2H copy), synchronised every step"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "decode_kernel",
+                     "traffic": DECODE_DRAM_TRAFFIC_BYTES, "peak_kind": peak_kind, "kernel": "decode_kernel",
                      "algorithmic_bytes_per_launch": alg, "tokens_per_split": tps},
     }
     if world == 1 and not args.no_extra:
