@@ -5,22 +5,27 @@
 // reference runs stock attention over a reconstructed fp16/bf16 cache
 // (experiments/stage1/toolkit/jointqk_press.py:306-307); here no key is ever dequantised.
 //
-// Decode kernel, one thread block per (key split, kv head x q-head block, sequence):
-//   * prologue: project the <=4 queries of the group, build the lookup tables (jqk_tables.cuh);
-//   * each warp owns a contiguous run of 32-key tiles.  A lane scores one key: it loads the
-//     record words (word-major pages: coalesced), does one 8-byte table read per lookup and
-//     accumulates four integer sums;
-//   * online softmax per warp with shuffles (running max / sum per query head);
-//   * P.V on the tensor cores: out^T[dims x heads] += V^T[dims x keys] . P^T[keys x heads] with
-//     mma.sync m16n8k16 bf16 (four query heads do not fill a tcgen05 tile; the kernel is bound
-//     by HBM, not by the tensor pipe).  V goes from global memory straight into A fragments:
-//     a lane loads 16-byte pieces of four key rows and pairs keys with byte permutes, so V
-//     never touches shared memory.  P is split into two bf16 terms (hi + lo) to keep fp32-level
-//     weights;
-//   * pages of upcoming tiles are pulled into L2 with cp.async.bulk.prefetch.L2, which needs
-//     no registers or shared memory, so HBM latency is hidden independently of occupancy;
-//   * partial results of the splits are merged by the last block to finish (atomic ticket),
-//     no second launch.
+// Decode kernel, one thread block per (key split, kv head x q-head block, sequence), one block per SM:
+//   * prologue: project the <=4 queries of the group and build the lookup tables (jqk_tables.cuh),
+//     or copy the tables a table kernel built once per group when the grid is larger than one
+//     wave.  The global reads of the build are the first thing a block issues; the pages of its
+//     first tiles are in flight while the tables are built;
+//   * each warp owns a contiguous run of 32-key tiles and stages their pages itself: lane 0 issues
+//     cp.async.bulk copies (K: two tiles deep, V: one) that complete on the warp's own mbarriers.
+//     A lane scores one key: per record word one shared-memory read of the word, then one 8-byte
+//     table read per lookup (16-entry tables of 128 bytes: no bank conflicts), accumulated as
+//     packed 16-bit integer sums;
+//   * online softmax per warp, branch-free (integer tile maximum by one warp reduction per head;
+//     the sum of the weights stays per lane until the end); P is split into two bf16 terms
+//     (hi + lo) so that the weights keep fp32-level accuracy;
+//   * P.V on the tensor cores as out^T[dims x heads] += V^T[dims x keys] . P^T[keys x heads] with
+//     mma.sync m16n8k16 (four query heads do not fill a tcgen05 tile): columns 0..3 carry the hi
+//     terms of the four heads and 4..7 the lo terms.  V pages are stored dims-major and swizzled
+//     in HBM (see the V layout in include/jointqk_b200.h), so one ldmatrix.x4 yields the A
+//     fragment of 16 dims x 16 keys;
+//   * the partial results of the splits are merged by the last block of the group to finish
+//     (atomic ticket), with one memory round trip, no second launch.
+// Every wait on a copy is bounded; an expired wait sets JQK_STATUS_WAIT_EXPIRED and skips the tile.
 #include <limits.h>
 #include <stdlib.h>
 
