@@ -152,6 +152,10 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
   }
   __syncthreads();
   JQK_TABLES_MARK(1);
+  // column c: projected queries, and the bound |q'_c| * max |level| (levels are sorted and padded
+  // with zeros, so the largest magnitude of a row is its largest |level|).  The bounds reuse the
+  // raw-query staging, which the projection is done with.
+  float4* colb = reinterpret_cast<float4*>(&sm.qraw[0][0]);  // [JQK_MAX_COLS]
   if (tid < JQK_MAX_COLS) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -160,35 +164,41 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
     }
     *reinterpret_cast<float4*>(sm.qproj[tid]) = s;
+    float big = 0.f;
+#pragma unroll
+    for (int l4 = 0; l4 < 4; ++l4) {
+      const float4 lv = *reinterpret_cast<const float4*>(sm.cb + tid * 16 + 4 * l4);
+      big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
+    }
+    colb[tid] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
   }
   __syncthreads();
   JQK_TABLES_MARK(2);
   const int n_entries = hd.n_tables * 16;
   const int n_scan_words = hd.n_a_words + hd.n_c_words;
-  // Largest |entry| per (word, head).  The fields of a table take their codes independently and the
-  // levels are sorted, so the largest |sum| is the sum over fields of |q'_c| * max(|first|, |last| level).
-  for (int t = tid; t < hd.n_tables; t += nthr) {
-    float m[JQK_MAX_GROUP] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int f = 0; f < 4; ++f) {
-      const int fld = sm.fields[t * 4 + f];
-      if (fld < 0) break;
-      const int col = fld & 255, width = (fld >> 8) & 15;
-      const float big = fmaxf(fabsf(sm.cb[col * 16]), fabsf(sm.cb[col * 16 + (1 << width) - 1]));
-      const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[col]);
-      m[0] = fmaf(fabsf(qp.x), big, m[0]); m[1] = fmaf(fabsf(qp.y), big, m[1]);
-      m[2] = fmaf(fabsf(qp.z), big, m[2]); m[3] = fmaf(fabsf(qp.w), big, m[3]);
-    }
-    const int w = table_word(t, hd.n_a_words);
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h)
-      atomicMax(&sm.wmax[w][h], __float_as_uint(m[h] * 1.0000005f));  // non-negative floats order as uints
-  }
-  __syncthreads();
-  JQK_TABLES_MARK(3);
   if (tid < 32) {
-    // warp 0 derives the per-word shifts with shuffles: lane w owns scan word w (n_scan_words <= 32)
+    // Warp 0 alone: bound on |entry| per (word, head), then the per-word shifts.  The fields of a
+    // table take their codes independently, so the largest |sum| is the sum of its columns' bounds.
     const int lane = tid;
+    for (int t = lane; t < hd.n_tables; t += 32) {
+      const int4 f4 = *reinterpret_cast<const int4*>(sm.fields + t * 4);
+      const int fl[4] = {f4.x, f4.y, f4.z, f4.w};
+      float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        if (fl[f] >= 0) {
+          const float4 cbd = colb[fl[f] & 255];
+          m.x += cbd.x; m.y += cbd.y; m.z += cbd.z; m.w += cbd.w;
+        }
+      }
+      const int w = table_word(t, hd.n_a_words);
+      atomicMax(&sm.wmax[w][0], __float_as_uint(m.x));  // non-negative floats order as uints
+      atomicMax(&sm.wmax[w][1], __float_as_uint(m.y));
+      atomicMax(&sm.wmax[w][2], __float_as_uint(m.z));
+      atomicMax(&sm.wmax[w][3], __float_as_uint(m.w));
+    }
+    __syncwarp();
+    // lane w owns scan word w (n_scan_words <= 32)
     float wm[JQK_MAX_GROUP], gm[JQK_MAX_GROUP];
     int fit = TBL_MAX_SHIFT;
 #pragma unroll
@@ -219,10 +229,12 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     for (int o = 16; o > 0; o >>= 1) term += __shfl_xor_sync(0xffffffffu, term, o);
     if (lane == 0) sm.bias = term;
     if (lane < JQK_MAX_GROUP) {
+      // One unit at shift 0.  The bound on |entry| maps to 32750, not 32767: the quantising pass
+      // rounds with a magic-number add that must never leave the signed 16-bit range.
       float base = 1.f;
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h)
-        if (h == lane) base = (gm[h] > 0.f) ? gm[h] / 32767.f : 1.f;
+        if (h == lane) base = (gm[h] > 0.f) ? gm[h] / 32750.f : 1.f;
       sm.scale[lane] = base / (float)(1 << (n_scan_words ? k_last : 0));
       sm.absmax[lane] = __float_as_uint(base);  // the per-head base scale, read by the quantising pass
     }
@@ -236,13 +248,14 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     float v[JQK_MAX_GROUP];
     table_entry(sm, e, v);
     const float up = (float)(1 << sm.kshift[table_word(e >> 4, hd.n_a_words)]);
-    int q[JQK_MAX_GROUP];
-#pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) q[h] = max(-32767, min(32767, __float2int_rn(v[h] * inv[h] * up)));
-    uint2 packed;
+    // round to nearest by adding 1.5 * 2^23: the low 16 bits of the sum are the two's complement
+    // value (even heads: plus 32768, the offset of the low halves)
+    const uint32_t q0 = __float_as_uint(fmaf(v[0], inv[0] * up, 12582912.f + 32768.f));
+    const uint32_t q1 = __float_as_uint(fmaf(v[1], inv[1] * up, 12582912.f));
+    const uint32_t q2 = __float_as_uint(fmaf(v[2], inv[2] * up, 12582912.f + 32768.f));
+    const uint32_t q3 = __float_as_uint(fmaf(v[3], inv[3] * up, 12582912.f));
     // high half: signed value of the odd head; low half: value of the even head plus 32768
-    packed.x = (uint32_t)((q[0] + 32768) & 0xffff) | ((uint32_t)q[1] << 16);
-    packed.y = (uint32_t)((q[2] + 32768) & 0xffff) | ((uint32_t)q[3] << 16);
+    const uint2 packed = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
     sm.lut[e] = packed;
   }
   __syncthreads();

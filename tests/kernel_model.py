@@ -79,7 +79,7 @@ def build_lut_model(tab, h, q):
     for w in range(n_scan - 1, -1, -1):
         k = min(k, int(fit[w]))
         kshift[w] = k
-    base = np.where(gmax > 0, gmax / np.float32(32767.0), np.float32(1.0)).astype(np.float32)
+    base = np.where(gmax > 0, gmax / np.float32(32750.0), np.float32(1.0)).astype(np.float32)
     up = (2.0 ** kshift[word_of]).astype(np.float32) if n_tables else np.zeros(0, np.float32)
     lut = np.clip(np.rint(ent / base * np.repeat(up, 16)[:, None]), -32767, 32767).astype(np.int64)
     scale = base / np.float32(2.0 ** (kshift[-1] if n_scan else 0))
