@@ -438,7 +438,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "data": "synthetic", "config": workload_config(world), "clocks": clocks,
         "e2e": {"value": world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": e2e_out[0].numel() * 4,
-                "steps": e2e_steps, "note": "host query in, pinned-host result out through PagedKVCache.decode_host (graph of H2D copy, decode, D2H copy), synchronised every step"},
+                "steps": e2e_steps, "note": "host query in, pinned-host result out through PagedKVCache.decode_host (replayed graph of H2D copy, decode, D2H copy; stream wait per step)"},
         "gpu_launches": args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": DECODE_DRAM_TRAFFIC_BYTES, "peak_kind": peak_kind, "kernel": "decode_kernel",

@@ -185,6 +185,25 @@ int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t 
                           size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
+ * jqk_decode_attend from host memory, one call per decode step (no counterpart in the reference,
+ * whose attention inputs are device tensors of the model): copies the query from `q_host` to the
+ * device, runs the step, copies the result to `out_host` and waits for it, all on `stream`.
+ *   q_host     bf16 [n_seqs][n_q_heads][d] anywhere in host memory
+ *   q_pinned   page-locked host staging of the same size (the query is copied there first, so the
+ *              transfer is asynchronous); may equal q_host if that is page-locked already
+ *   q_dev      device staging for the query, same size
+ *   out_dev    device staging for the result, [n_seqs][n_q_heads][d] of out_dtype
+ *   out_host   page-locked host memory of the same size; valid when the call returns
+ * Everything else as in jqk_decode_attend.  h2d / d2h bytes per call: the sizes of q and out.
+ */
+int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const void* q_host, void* q_pinned, void* q_dev,
+                               int32_t n_seqs, int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                               int32_t tokens_per_split, const int32_t* page_table, int32_t page_table_stride,
+                               int32_t n_pages, const uint32_t* k_pool, const void* v_pool, void* out_dev,
+                               void* out_host, int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                               int32_t* status, void* stream);
+
+/*
  * jqk_decode_attend for callers that must not allocate (no counterpart in the reference, which
  * leaves all memory to torch).  Some hosts of this library cannot call cudaMalloc on the decode
  * path at all: a serving engine that has handed every byte of device memory to its own pool at

@@ -63,6 +63,10 @@ SIGNATURES = {
         C.POINTER(JqkHeadTables), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
         C.c_void_p]),
+    "jqk_decode_attend_host": (C.c_int32, [
+        C.POINTER(JqkHeadTables), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+        C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+        C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     "jqk_moments_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32]),
     "jqk_moments_accumulate": (C.c_int32, [
         C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,

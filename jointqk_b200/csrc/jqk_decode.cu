@@ -28,6 +28,7 @@
 // Every wait on a copy is bounded; an expired wait sets JQK_STATUS_WAIT_EXPIRED and skips the tile.
 #include <limits.h>
 #include <stdlib.h>
+#include <string.h>
 
 #ifdef JQK_DECODE_PROFILE
 // Development aid: per-phase clock totals of thread 0 of every block.  Slots 0-6: table build or
@@ -782,6 +783,31 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   else { if (in_block) JQK_LAUNCH_DECODE(64, true); else JQK_LAUNCH_DECODE(64, false); }
 #undef JQK_LAUNCH_DECODE
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
+  return 0;
+}
+
+extern "C" int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const void* q_host, void* q_pinned,
+                                          void* q_dev, int32_t n_seqs, int32_t n_q_heads, const int32_t* seq_lens,
+                                          int32_t max_seq_len, int32_t tokens_per_split, const int32_t* page_table,
+                                          int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                                          const void* v_pool, void* out_dev, void* out_host, int32_t out_dtype,
+                                          void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  int32_t rc = check_tables(tables);
+  if (rc) return rc;
+  if (n_seqs <= 0 || n_q_heads <= 0) return fail(JQK_E_ARG, "n_seqs and n_q_heads must be positive");
+  if (!q_host || !q_pinned || !q_dev || !out_dev || !out_host) return fail(JQK_E_ARG, "null host or staging buffer");
+  if (out_dtype != JQK_DTYPE_F32 && out_dtype != JQK_DTYPE_BF16) return fail(JQK_E_ARG, "out dtype must be f32 or bf16");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t n = (size_t)n_seqs * n_q_heads * tables->d;
+  const size_t q_bytes = n * 2, out_bytes = n * (out_dtype == JQK_DTYPE_F32 ? 4 : 2);
+  if (q_pinned != q_host) memcpy(q_pinned, q_host, q_bytes);
+  JQK_CUDA_OK(cudaMemcpyAsync(q_dev, q_pinned, q_bytes, cudaMemcpyHostToDevice, st), "query copy to the device");
+  rc = jqk_decode_attend(tables, q_dev, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                         page_table_stride, n_pages, k_pool, v_pool, out_dev, out_dtype, workspace, workspace_bytes,
+                         status, stream);
+  if (rc) return rc;
+  JQK_CUDA_OK(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, st), "result copy to the host");
+  JQK_CUDA_OK(cudaStreamSynchronize(st), "waiting for the decode step");
   return 0;
 }
 

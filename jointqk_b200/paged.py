@@ -237,6 +237,7 @@ class PagedKVCache:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ws: DecodeWorkspace | None = None
         self._host_step: dict | None = None
+        self._host_call: dict | None = None
 
     def prefill(self, keys: torch.Tensor, values: torch.Tensor, lengths: list[int] | None = None) -> None:
         """keys/values (n_seqs, H, S, d).  Appends ``lengths[s]`` tokens to every sequence."""
@@ -271,7 +272,7 @@ class PagedKVCache:
         return decode_attend(self.tables, q, self.seq_lens, max_len, self.page_table, self.k_pool, self.v_pool,
                              out, self._ws, self.status, tps)
 
-    def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0) -> torch.Tensor:
+    def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0, use_graph: bool = True) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
         pinned host tensor that the next call overwrites.
 
@@ -279,9 +280,12 @@ class PagedKVCache:
         captured once as a CUDA graph (per batch shape, context length and split); every call stages
         the query in pinned memory, replays the graph and waits for it, so the host pays one graph
         launch and one synchronisation per step instead of three enqueues.  The cache must not grow
-        between capture and replay: a call after ``prefill`` captures again."""
-        if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3:
-            raise ValueError("q_host must be a bf16 (n_seqs, n_q_heads, d) tensor in host memory")
+        between capture and replay: a call after ``prefill`` captures again.  ``use_graph=False`` makes
+        one call of ``jqk_decode_attend_host`` instead (no capture; three enqueues and a wait)."""
+        if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3 or not q_host.is_contiguous():
+            raise ValueError("q_host must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor in host memory")
+        if not use_graph:
+            return self._decode_host_call(q_host, tokens_per_split)
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_step
@@ -319,10 +323,35 @@ class PagedKVCache:
         torch.cuda.current_stream(dev).synchronize()   # the graph is launched on the current stream
         return hs["out_pin"]
 
-    def host_query_buffer(self, n_seqs: int, n_q_heads: int) -> torch.Tensor | None:
-        """The pinned query buffer of ``decode_host`` once a graph exists for this shape: writing the
-        query straight into it saves ``decode_host`` its host-to-host copy."""
-        hs = self._host_step
-        if hs is None or hs["q_pin"].shape[:2] != (n_seqs, n_q_heads):
-            return None
-        return hs["q_pin"]
+    def _decode_host_call(self, q_host: torch.Tensor, tokens_per_split: int = 0) -> torch.Tensor:
+        """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
+        pinned host tensor that the next call overwrites.
+
+        One call of ``jqk_decode_attend_host``: the query is staged in pinned memory and copied to
+        the device, the step runs, the result is copied back and the stream is synchronised, so the
+        host pays one foreign-function call per step.  The staging buffers are kept per batch shape."""
+        dev = self.tables.device
+        n_seqs, n_q_heads, d = q_host.shape
+        hs = self._host_call
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split))
+        if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
+            max_len = max(self.lengths) if self.lengths else 0
+            tps = tokens_per_split or default_split(n_seqs, n_q_heads, self.tables.n_heads, max(max_len, 1))
+            max_splits = max(1, -(-max_len // tps))
+            if self._ws is None or self._ws.max_splits < max_splits:
+                self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
+            keep = hs if hs is not None and hs["key"] == key else None
+            hs = {"key": key, "lengths": list(self.lengths), "max_len": max_len, "tps": tps,
+                  "q_pin": keep["q_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16).pin_memory(),
+                  "out_pin": keep["out_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
+                  "q_dev": keep["q_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
+                  "out_dev": keep["out_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32, device=dev)}
+            hs["args"] = (self.tables.ref, hs["q_pin"].data_ptr(), hs["q_dev"].data_ptr(), n_seqs, n_q_heads,
+                          self.seq_lens.data_ptr(), int(max_len), int(tps), self.page_table.data_ptr(),
+                          self.page_table.stride(0), int(self.k_pool.shape[0]), self.k_pool.data_ptr(),
+                          self.v_pool.data_ptr(), hs["out_dev"].data_ptr(), hs["out_pin"].data_ptr(),
+                          _native.DTYPE_F32, self._ws.buf.data_ptr(), self._ws.buf.numel(), self.status.data_ptr())
+            self._host_call = hs
+        a = hs["args"]
+        _native.check(_native.lib.jqk_decode_attend_host(a[0], q_host.data_ptr(), *a[1:], _stream_ptr(dev)))
+        return hs["out_pin"]

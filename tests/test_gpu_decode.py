@@ -126,8 +126,9 @@ def test_decode_bf16_output_and_page_permutation_invariance():
 
 
 def test_decode_from_host_buffers_equals_device_call():
-    """PagedKVCache.decode_host (graph of H2D copy, decode, D2H copy) returns what decode() returns,
-    also when replayed with a new query and after the cache has grown."""
+    """PagedKVCache.decode_host (a replayed graph of H2D copy, decode, D2H copy, or one call of
+    jqk_decode_attend_host) returns what decode() returns, also with a new query and after the cache
+    has grown."""
     keys, comps, sig, tables = _setup(2, 2048, 2.0)
     g = torch.Generator().manual_seed(5)
     v = torch.randn(1, 2, 2048, 128, generator=g).to(torch.bfloat16)
@@ -137,9 +138,9 @@ def test_decode_from_host_buffers_equals_device_call():
         q = torch.randn(1, 8, 128, generator=g).to(torch.bfloat16)
         if rep == 2:
             cache.prefill(keys[:, 1500:1501].unsqueeze(0).cuda(), v[:, :, 1500:1501].cuda())   # append one token
-        got = cache.decode_host(q).clone()
         want = cache.decode(q.cuda()).cpu()
-        assert torch.equal(got, want)
+        assert torch.equal(cache.decode_host(q).clone(), want)                    # replayed graph
+        assert torch.equal(cache.decode_host(q, use_graph=False).clone(), want)   # jqk_decode_attend_host
     paged.check_status(cache.status)
 
 
