@@ -7,7 +7,7 @@ Headline (one JSON line on stdout): compressed-K decode tokens/s on the single-l
 config -- GQA 32 q / 8 kv heads, head_dim 128, batch 1 per GPU, context 32768, keys packed at
 2.0 bits/coordinate in 16-token pages, bf16 V -- with the HBM roofline of the decode kernel,
 the same metric end to end from host buffers (``e2e``), and the reference algorithm's torch
-CPU path timed on this box (``cpu_baseline``).  ``extra`` carries the other two stages of the
+CPU path timed on this box (``cpu_baseline``).  ``extra`` carries decode at batch and the other two stages of the
 path on their named shapes: prefill compression (keys/s) and calibration moments
 (token-layers/s), each with its own roofline fraction.
 
@@ -304,6 +304,58 @@ def bench_compress(device, hbm_gbs: float, peak_kind: str) -> dict:
                          "bytes_per_key": bytes_per_key, "peak_kind": peak_kind}}
 
 
+def bench_decode_batch(device, hbm_gbs: float, peak_kind: str) -> dict:
+    """Decode at batch: one layer of one rank's share of the 64-sequence config (8 ragged sequences
+    assigned by longest-processing-time, lengths U{4096..65536}), 32 q / 8 kv heads, at 3.0 and at
+    2.0 bits per coordinate.  The pools hold random codes and values: the kernel's work does not
+    depend on their content, and two caches alternate so that every step reads HBM."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, lpt_shards, spectrum_keys, uniform_lengths
+
+    lens_all = uniform_lengths(64, 4096, 65536, config_seed(2, 0, 0))
+    shard = [lens_all[i] for i in lpt_shards(lens_all, 8)[0]]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(config_seed(2, 0, 0) + 1)
+    q = torch.randn(len(shard), N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    out = {"workload": "1 layer, 8 sequences of %d..%d keys (%d in total), 32 q / 8 kv heads, 16-token pages"
+                       % (min(shard), max(shard), sum(shard)), "lengths": shard}
+    for b_avg in (3.0, 2.0):
+        keys = torch.stack([spectrum_keys(4096, config_seed(2, 0, h)) for h in range(N_KV_HEADS)])
+        comps, _ = fit_sigma_k_heads(keys, b_avg)
+        tables = jq.HeadTables.from_compressors(comps, device=device)
+        caches = []
+        for _ in range(2):
+            cache = paged.PagedKVCache(tables, shard)
+            cache.k_pool.random_(0, 2 ** 31 - 1, generator=gen)
+            cache.v_pool.normal_(generator=gen)
+            cache.lengths = list(shard)
+            cache.seq_lens[:] = torch.tensor(shard, dtype=torch.int32, device=device)
+            caches.append(cache)
+        for c in caches:
+            c.decode(q)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 40
+        e0.record()
+        for i in range(reps):
+            caches[i % 2].decode(q)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms = e0.elapsed_time(e1) / reps
+        paged.check_status(caches[0].status)
+        nbytes = sum(shard) * N_KV_HEADS * (tables.record_bytes + HEAD_DIM * 2)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["%.1f bits" % b_avg] = {
+            "ms_per_layer_step": ms, "tokens_per_split": paged.split_for_lengths(shard, N_Q_HEADS, N_KV_HEADS),
+            "layer_steps_x_sequences_per_s": len(shard) / (ms * 1e-3),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
+                         "algorithmic_bytes_per_launch": nbytes, "peak_kind": peak_kind}}
+        del caches
+        torch.cuda.empty_cache()
+    return out
+
+
 def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict:
     """Calibration moments: one layer, 32 q / 8 kv heads, 131072 bf16 tokens per launch (1.3 GB in)."""
     from jointqk_b200.moments import KeyPathMoments
@@ -448,7 +500,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         del caches[1:]
         torch.cuda.empty_cache()
         line["extra"] = {"prefill_compress": bench_compress(device, hbm_gbs, peak_kind),
-                         "calibration_moments": bench_moments(device, hbm_gbs, tflops, peak_kind)}
+                         "calibration_moments": bench_moments(device, hbm_gbs, tflops, peak_kind),
+                         "decode_batch": bench_decode_batch(device, hbm_gbs, peak_kind)}
     if rank == 0:
         if world == 1 and not args.no_cpu:
             v, cms, cores, sample = cpu_decode_steps_per_s(comps, keys.cpu(), budget_s=20.0)
@@ -467,7 +520,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
     ap.add_argument("--tokens-per-split", type=int, default=0, help="override the decode split size (0 = library default)")
-    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments"],
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch"],
                     help="profiling aid: run only one of the secondary stages and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -482,7 +535,8 @@ def main() -> None:
         dev = torch.device("cuda", local_rank)
         torch.cuda.set_device(dev)
         hbm, tf, kind = measured_peaks()
-        res = bench_compress(dev, hbm, kind) if args.stage == "compress" else bench_moments(dev, hbm, tf, kind)
+        res = (bench_compress(dev, hbm, kind) if args.stage == "compress" else
+               bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else bench_moments(dev, hbm, tf, kind))
         print(json.dumps(res), flush=True)
         return
     if world > 1:

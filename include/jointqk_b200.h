@@ -230,9 +230,16 @@ int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const void* q, i
                                  const void* v_pool, void* out, int32_t out_dtype, int32_t* status,
                                  void* stream);
 
-/* tokens_per_split that jqk_decode_attend would choose for this shape (host helper). */
+/* tokens_per_split that jqk_decode_attend would choose for this shape (host helper): every
+ * sequence is taken to be max_seq_len long. */
 int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
                                  int32_t max_seq_len);
+
+/* The same choice for a batch whose context lengths the host knows (host_seq_lens is HOST memory,
+ * int32 [n_seqs]): the block count is fitted to whole waves of one block per SM.  Pass the result
+ * as tokens_per_split. */
+int32_t jqk_decode_split_for_lengths(const int32_t* host_seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                                     int32_t n_kv_heads);
 
 /*
  * Calibration moments: accumulates (+=) the per-kv-head sums over tokens

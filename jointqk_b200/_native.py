@@ -55,6 +55,7 @@ SIGNATURES = {
         C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "jqk_decode_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "jqk_decode_default_split": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "jqk_decode_split_for_lengths": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32]),
     "jqk_decode_attend": (C.c_int32, [
         C.POINTER(JqkHeadTables), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,

@@ -673,18 +673,51 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
   return b;
 }
 
-extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
-                                            int32_t max_seq_len) {
+constexpr int MAX_SPLITS = 4096;  // the merge keeps one weight per split and head in shared memory
+
+// Split size for a batch whose context lengths the host knows (host_lens == nullptr: all sequences
+// at max_seq_len).  Blocks of `tps` keys run in waves of 148 (one block per SM); a block costs its
+// keys plus a fixed share (table build or copy, block combine, merge) of about 1200 keys' worth of
+// main-loop time.  The split that minimises waves x (tps + fixed) wins: for one short batch that is
+// the smallest split that still fits one wave, for large batches a few thousand keys per block
+// with the block count just under a multiple of 148.
+static int32_t choose_split(const int32_t* host_lens, int n_seqs, int n_q_heads, int n_kv_heads, int max_seq_len) {
   const int unit = TILE_TOK * DEC_WARPS;  // one tile per warp: keeps the warps of a block level (384 keys)
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_seq_len <= 0) return unit;
-  const long long items = (long long)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
-  const long long target_blocks = 148;  // one resident block per SM
-  long long splits = target_blocks / items;
-  if (splits < 1) splits = 1;
-  long long tps = (max_seq_len + splits - 1) / splits;
-  if (items * 2 >= target_blocks && tps > 2048) tps = 2048;  // many sequences: fixed granularity
-  tps = (tps + unit - 1) / unit * unit;
-  return (int32_t)tps;
+  const long long groups = (long long)n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
+  const long long fixed = 1200, slots = 148;
+  long long best_cost = -1;
+  int best = unit;
+  const int max_units = (max_seq_len + unit - 1) / unit;
+  for (int u = 1; u <= max_units; ++u) {
+    const long long tps = (long long)u * unit;
+    if ((max_seq_len + tps - 1) / tps > MAX_SPLITS) continue;
+    long long blocks = 0;
+    if (host_lens) {
+      for (int s2 = 0; s2 < n_seqs; ++s2) blocks += (host_lens[s2] > 0) ? (host_lens[s2] + tps - 1) / tps : 0;
+    } else {
+      blocks = (long long)n_seqs * ((max_seq_len + tps - 1) / tps);
+    }
+    blocks *= groups;
+    if (blocks <= 0) continue;
+    const long long waves = (blocks + slots - 1) / slots;
+    const long long cost = waves * (tps + fixed);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = (int)tps; }
+  }
+  return best;
+}
+
+extern "C" int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
+                                            int32_t max_seq_len) {
+  return choose_split(nullptr, n_seqs, n_q_heads, n_kv_heads, max_seq_len);
+}
+
+extern "C" int32_t jqk_decode_split_for_lengths(const int32_t* host_seq_lens, int32_t n_seqs, int32_t n_q_heads,
+                                                int32_t n_kv_heads) {
+  if (!host_seq_lens || n_seqs <= 0) return TILE_TOK * DEC_WARPS;
+  int max_len = 0;
+  for (int s2 = 0; s2 < n_seqs; ++s2) max_len = host_seq_lens[s2] > max_len ? host_seq_lens[s2] : max_len;
+  return choose_split(host_seq_lens, n_seqs, n_q_heads, n_kv_heads, max_len);
 }
 
 extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_mode, const void* q, int32_t q_dtype,
@@ -733,6 +766,7 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   if (tokens_per_split == 0) tokens_per_split = jqk_decode_default_split(n_seqs, n_q_heads, tables->n_heads, max_seq_len);
   if (tokens_per_split < 0 || tokens_per_split % TILE_TOK) return fail(JQK_E_ARG, "tokens_per_split %d must be a positive multiple of %d", tokens_per_split, TILE_TOK);
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
+  if (max_splits > MAX_SPLITS) return fail(JQK_E_UNSUPPORTED, "%d key splits exceed %d: use a larger tokens_per_split", max_splits, MAX_SPLITS);
   const int qbl = q_blocks_for(n_q_heads, tables->n_heads);
   DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits};
   {

@@ -196,6 +196,14 @@ def default_split(n_seqs: int, n_q_heads: int, n_kv_heads: int, max_seq_len: int
     return int(_native.lib.jqk_decode_default_split(n_seqs, n_q_heads, n_kv_heads, max_seq_len))
 
 
+def split_for_lengths(lengths: list[int], n_q_heads: int, n_kv_heads: int) -> int:
+    """Keys per thread block for a batch with these context lengths (fits the block count to waves)."""
+    import ctypes
+
+    arr = (ctypes.c_int32 * max(1, len(lengths)))(*[int(n) for n in lengths])
+    return int(_native.lib.jqk_decode_split_for_lengths(arr, len(lengths), n_q_heads, n_kv_heads))
+
+
 def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int,
                   page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                   out: torch.Tensor, workspace: DecodeWorkspace | None, status: torch.Tensor,
@@ -264,7 +272,7 @@ class PagedKVCache:
     def decode(self, q: torch.Tensor, out_dtype: torch.dtype = torch.float32, tokens_per_split: int = 0) -> torch.Tensor:
         n_seqs, n_q_heads, _ = q.shape
         max_len = max(self.lengths) if self.lengths else 0
-        tps = tokens_per_split or default_split(n_seqs, n_q_heads, self.tables.n_heads, max(max_len, 1))
+        tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
         max_splits = max(1, -(-max_len // tps))
         if self._ws is None or self._ws.max_splits < max_splits:
             self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, self.tables.device)
@@ -292,7 +300,7 @@ class PagedKVCache:
         key = (n_seqs, n_q_heads, d, int(tokens_per_split))
         if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
             max_len = max(self.lengths) if self.lengths else 0
-            tps = tokens_per_split or default_split(n_seqs, n_q_heads, self.tables.n_heads, max(max_len, 1))
+            tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
             max_splits = max(1, -(-max_len // tps))
             if self._ws is None or self._ws.max_splits < max_splits:
                 self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
@@ -336,7 +344,7 @@ class PagedKVCache:
         key = (n_seqs, n_q_heads, d, int(tokens_per_split))
         if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
             max_len = max(self.lengths) if self.lengths else 0
-            tps = tokens_per_split or default_split(n_seqs, n_q_heads, self.tables.n_heads, max(max_len, 1))
+            tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
             max_splits = max(1, -(-max_len // tps))
             if self._ws is None or self._ws.max_splits < max_splits:
                 self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
