@@ -35,3 +35,19 @@ def test_version_and_argument_errors_without_gpu():
     assert rc == -1 and b"null head tables" in _native.lib.jqk_last_error()
     assert _native.lib.jqk_decode_workspace_bytes(1, 32, 8, 37) > 37 * 32 * 128 * 4
     assert _native.lib.jqk_decode_default_split(1, 32, 8, 32768) % 32 == 0
+
+
+def test_decode_split_fits_waves_of_148_blocks():
+    """Host-only helpers: the split is a multiple of 384 keys (one 32-key tile per warp), keeps one
+    short batch inside a single wave of 148 blocks, and gives large batches blocks of several
+    thousand keys with the block count at or under a multiple of 148."""
+    from jointqk_b200 import paged
+
+    tps = paged.default_split(1, 32, 8, 32768)
+    assert tps % 384 == 0 and 8 * -(-32768 // tps) <= 148 and tps == paged.split_for_lengths([32768], 32, 8)
+    lens = [64850, 48381, 47953, 40224, 35138, 25021, 21352, 6227]
+    tps = paged.split_for_lengths(lens, 32, 8)
+    blocks = 8 * sum(-(-n // tps) for n in lens)
+    assert tps % 384 == 0 and 4096 <= tps <= 16384 and blocks % 148 > 148 // 2 or blocks % 148 == 0
+    assert paged.split_for_lengths([0, 0], 8, 8) == 384 and paged.split_for_lengths([100], 8, 8) == 384
+    assert -(-1_000_000 // paged.default_split(1, 32, 8, 1_000_000)) <= 4096   # the merge's split limit
