@@ -551,16 +551,18 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   if (single) return;
 
   // ---- the last block of this (sequence, head group) to finish merges the splits ------------
-  __threadfence();
+  // Ticket with release/acquire at gpu scope: the barrier orders this block's partial results
+  // before thread 0's atomic, whose release makes them visible to whoever takes a later ticket, and
+  // whose acquire (for the last block) makes the other blocks' results visible to the loads below.
   __syncthreads();
   unsigned int* counter = ws.counters + (size_t)seq * gridDim.y + blockIdx.y;
   if (tid == 0) {
-    const unsigned int prev = atomicAdd(counter, 1u);
+    unsigned int prev;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(counter) : "memory");
     sm.is_last = (prev == (unsigned int)(n_splits - 1));
   }
   __syncthreads();
   if (!sm.is_last) return;
-  __threadfence();
   // A thread owns four output dims of one head and every third split: it first puts its partial
   // rows in flight (MERGE_BATCH independent 16-byte loads), then one warp per head turns the
   // splits' (max, sum) pairs into one weight per split, so a single memory round trip covers both.
