@@ -195,11 +195,24 @@ int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t 
   } else {
     q_map = k_map;
   }
-  static const int chunk = [] {
+  static const int env_chunk = [] {
     const char* e = getenv("JQK_MOMENTS_CHUNK");  // tuning knob: tokens per block, a multiple of 64
     const int v = e ? atoi(e) : 0;
-    return (v >= MT_TOK && v % MT_TOK == 0) ? v : MT_CHUNK;
+    return (v >= MT_TOK && v % MT_TOK == 0) ? v : 0;
   }();
+  // One block per SM is resident (160 KB of operand stages), so blocks run in waves of 148.  The
+  // chunk is the largest one not above MT_CHUNK (the bound on the length of an fp32 running sum)
+  // whose block count fills whole waves: 131072 tokens x 8 heads -> 1792 tokens, 592 blocks, 4 waves.
+  int chunk = env_chunk ? env_chunk : MT_CHUNK;
+  if (!env_chunk) {
+    for (int waves = 1; waves <= 4096; ++waves) {
+      const long long per_head = (148LL * waves) / n_kv_heads;
+      if (per_head <= 0) continue;
+      long long c = (n_tokens + per_head - 1) / per_head;
+      c = (c + MT_TOK - 1) / MT_TOK * MT_TOK;
+      if (c <= MT_CHUNK) { chunk = (int)(c < MT_TOK ? MT_TOK : c); break; }
+    }
+  }
   dim3 grid((unsigned)((n_tokens + chunk - 1) / chunk), n_kv_heads);
   const size_t smem = sizeof(MtSmem) + 1024;
   JQK_SMEM_ONCE(moments_tc_kernel, smem, "tensor-core moments smem attribute");
