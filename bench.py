@@ -390,7 +390,7 @@ def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict
 # main arm
 # ----------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch of the headline workload,
-# from the ncu capture summarised in profiles/decode_kernel_ctx32768_2bit.md (76.20 MB + 1.46 MB)
+# from one ncu capture of that launch (76.20 MB + 1.46 MB)
 DECODE_DRAM_TRAFFIC_BYTES = 77.66e6
 
 

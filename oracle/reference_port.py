@@ -6,8 +6,8 @@ CPU baseline / reference arm.  It is written with the same torch CPU operations 
 reference (fp32 ``@``, ``argmin`` over ``|x - codebook|``, ``einsum``) so that its results and
 its running time are those of the reference's own CPU path.
 
-Pinned against the reference itself: ``tests/golden/make_golden.py`` imports
-``/root/reference`` in the build container and stores reference outputs as fixtures;
+Pinned against the reference itself: ``tests/golden/make_golden.py`` imports a checkout of
+the reference (given on ``PYTHONPATH``) and stores reference outputs as fixtures;
 ``tests/test_oracle_golden.py`` checks every function here against them.
 
 Reference locations (paths inside Amir-zsh/JointQK):

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference implementation.
 
-Run in the build container, where the reference checkout is mounted read-only:
+Run where a checkout of the reference is available, from the root of this repository:
 
-    PYTHONPATH=/root/reference:/root/repo python tests/golden/make_golden.py
+    PYTHONPATH=<reference checkout>:. python tests/golden/make_golden.py
 
 Every array saved under a name starting with ``ref_`` is an output of the reference's own
 functions (Amir-zsh/JointQK, experiments/stage1/...); the other arrays are the seeded inputs
