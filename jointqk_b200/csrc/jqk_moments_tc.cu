@@ -9,13 +9,13 @@
 // nothing is transposed or staged twice.  Per 16 tokens the block issues 1 + 2G MMAs
 // (M = N = 128, K = 16, bf16 in, fp32 accumulate) into three 128-column TMEM accumulators.
 //
-// A block owns a chunk of 2048 tokens of one kv head; at the end of the chunk four epilogue
-// warps read the accumulators and add them to the outputs with vector reductions
-// (red.global.add.v4.f32).  Short chunks bound the length of each fp32 running sum, which keeps
+// A block owns a chunk of at most 2048 tokens of one kv head; at the end of the chunk the epilogue
+// warps read the accumulators and add them to the outputs with reductions that a warp issues
+// over 32 consecutive floats (red.global.add.f32).  Short chunks bound the length of each fp32 running sum, which keeps
 // the result as accurate as a blocked CPU summation.
 //
 //   warp 0  TMA producer (G + 1 tiles per stage, 2 stages)     warp 1  TMEM owner + MMA issuer
-//   warps 2..5  epilogue
+//   warps 2..5  epilogue (TMEM lane quarter = warp & 3)
 // Every mbarrier wait is bounded in time (see tc_wait in jqk_compress_tc.cu for the policy).
 #include <stdlib.h>
 
@@ -29,7 +29,8 @@ using namespace sm100;
 constexpr int MT_TOK = 64;             // tokens per tile
 constexpr int MT_STAGES = 2;
 constexpr int MT_CHUNK = 2048;         // default tokens per block
-constexpr int MT_THREADS = 192;
+constexpr int MT_EPI_WARPS = 4;          // one per TMEM lane quarter (eight, two per quarter, measured no faster)
+constexpr int MT_THREADS = 64 + 32 * MT_EPI_WARPS;
 constexpr uint32_t MT_TILE_BYTES = MT_TOK * 128 * 2;  // one head's tile: two boxes of [64 tokens][64 dims]
 constexpr uint32_t MT_TMEM_COLS = 512;
 constexpr unsigned long long MT_WAIT_NS = 2000000000ull;
@@ -54,10 +55,6 @@ __device__ __forceinline__ bool mt_wait(MtSmem& sm, uint64_t* bar, uint32_t pari
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
     if (t1 - t0 > MT_WAIT_NS) { sm.abort = 1; return false; }
   }
-}
-
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 __global__ void __launch_bounds__(MT_THREADS, 1)
@@ -124,7 +121,7 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             for (int g = 0; g < group; ++g) {
               const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sm.tile[s][g]) + ks * 2048, MT_TILE_BYTES / 2, 1024);
               if (sq) umma_bf16(tmem + 0, q_desc, q_desc, idesc, !(first && g == 0));
-              if (cqk) umma_bf16(tmem + 256, q_desc, k_desc, idesc, !(first && g == 0));
+              if (cqk) umma_bf16(tmem + 256, k_desc, q_desc, idesc, !(first && g == 0));  // transposed: lane = k dim
             }
           }
         }
@@ -133,24 +130,28 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       umma_commit(&sm.done);
     }
   } else {
-    // epilogue: lane of TMEM = row (dim of the first factor), column = dim of the second factor
+    // Epilogue.  A thread owns TMEM lane r.  For the two symmetric matrices entry (r, c) is also entry
+    // (c, r); the cross moment is accumulated transposed (lane = k dim, column = q dim).  Either way
+    // the thread adds its value for column c to out[c][r], so the 32 lanes of a warp hit 32
+    // consecutive floats: one 128-byte reduction per instruction instead of 32 scattered ones.
     if (mt_wait(sm, &sm.done, 0) && !sm.abort) {
       tc_fence_after();
       const int row = 32 * (warp & 3) + lane;
+      const int col_lo = ((warp - 2) >> 2) * (128 / (MT_EPI_WARPS / 4));
       const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
       float* outs[3] = {sq, sk, cqk};
       const float scale[3] = {1.f, 1.f, 1.f / (float)group};
 #pragma unroll 1
       for (int m = 0; m < 3; ++m) {
         if (!outs[m]) continue;
-        float* dst = outs[m] + ((size_t)head * 128 + row) * 128;
+        float* dst = outs[m] + (size_t)head * 128 * 128 + row;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 16) {
+        for (int c0 = col_lo; c0 < col_lo + 128 / (MT_EPI_WARPS / 4); c0 += 16) {
           float v[16];
           tmem_ld16(t_lane + m * 128 + c0, v);
 #pragma unroll
-          for (int i = 0; i < 16; i += 4)
-            red_add_v4(dst + c0 + i, v[i] * scale[m], v[i + 1] * scale[m], v[i + 2] * scale[m], v[i + 3] * scale[m]);
+          for (int i = 0; i < 16; ++i)
+            asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)(c0 + i) * 128), "f"(v[i] * scale[m]) : "memory");
         }
       }
     }
