@@ -40,11 +40,10 @@ struct TableSmem {
   float cb[JQK_MAX_COLS * 16];                   //  8,192 B: staged codebooks
   int32_t fields[JQK_MAX_TABLES * 4];            //  3,328 B: staged table composition
   float scale[JQK_MAX_GROUP];                    // value of one unit of the final integer sum
-  unsigned int absmax[JQK_MAX_GROUP];
-  unsigned int wmax[TBL_WORDS][JQK_MAX_GROUP];   // per scan-order word: largest |entry| per head
-  int kshift[TBL_WORDS];                         // K_w
+  float wmax[TBL_WORDS][JQK_MAX_GROUP];          // per scan-order word: bound on |entry| per head
   int dshift[TBL_WORDS];                         // K_w - K_{w-1}
   unsigned int bias;                             // what the +32768 offsets of the low halves add up to
+  int wcb[JQK_MAX_WORDS + 4];                    // first column of every physical record word
 };
 
 // Scan-order word of table t: nibble word t/8, or n_a_words + byte word.
@@ -52,22 +51,28 @@ __device__ __forceinline__ int table_word(int t, int n_a_words) {
   return (t < 8 * n_a_words) ? (t >> 3) : (n_a_words + (t - 8 * n_a_words) / 12);
 }
 
-// One table entry in fp32 for the heads of the group (all operands in shared memory).
+// One table entry in fp32 for the heads of the group (all operands in shared memory).  The four
+// possible fields are evaluated side by side (an absent field contributes zero), so their
+// dependent shared-memory reads overlap.
 __device__ __forceinline__ void table_entry(const TableSmem& sm, int e, float (&v)[JQK_MAX_GROUP]) {
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) v[h] = 0.f;
-  const int32_t* fields = sm.fields + (e >> 4) * 4;
+  const int4 f4 = *reinterpret_cast<const int4*>(sm.fields + (e >> 4) * 4);
+  const int fl[4] = {f4.x, f4.y, f4.z, f4.w};
   const int idx = e & 15;
+  float c[4];
+  float4 qp[4];
 #pragma unroll
   for (int f = 0; f < 4; ++f) {
-    const int fld = fields[f];
-    if (fld < 0) break;
+    const bool on = fl[f] >= 0;
+    const int fld = on ? fl[f] : 0;
     const int col = fld & 255, width = (fld >> 8) & 15, shift = (fld >> 12) & 15;
-    const float c = sm.cb[col * 16 + ((idx >> shift) & ((1 << width) - 1))];
-    const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[col]);
-    v[0] = fmaf(qp.x, c, v[0]); v[1] = fmaf(qp.y, c, v[1]);
-    v[2] = fmaf(qp.z, c, v[2]); v[3] = fmaf(qp.w, c, v[3]);
+    const float lv = sm.cb[col * 16 + ((idx >> shift) & ((1 << width) - 1))];
+    c[f] = on ? lv : 0.f;
+    qp[f] = *reinterpret_cast<const float4*>(sm.qproj[col]);
   }
+  v[0] = fmaf(qp[3].x, c[3], fmaf(qp[2].x, c[2], fmaf(qp[1].x, c[1], qp[0].x * c[0])));
+  v[1] = fmaf(qp[3].y, c[3], fmaf(qp[2].y, c[2], fmaf(qp[1].y, c[1], qp[0].y * c[0])));
+  v[2] = fmaf(qp[3].z, c[3], fmaf(qp[2].z, c[2], fmaf(qp[1].z, c[1], qp[0].z * c[0])));
+  v[3] = fmaf(qp[3].w, c[3], fmaf(qp[2].w, c[2], fmaf(qp[1].w, c[1], qp[0].w * c[0])));
 }
 
 // The global reads of the table build, issued into registers as early as the caller can: one
@@ -78,6 +83,7 @@ struct TableLoads {
   float qv[2];
   float4 cv[2];
   int4 fv;
+  int wv;  // word_col_begin[tid] of the head descriptor (tid <= JQK_MAX_WORDS)
 };
 
 //   q_base + h * q_head_stride : the d values of query head h of the group (h < n_group)
@@ -108,15 +114,20 @@ __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& t
     ld.cv[u] = (e < JQK_MAX_COLS * 4) ? __ldg(cb4 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   ld.fv = (tid < JQK_MAX_TABLES) ? __ldg(f4 + tid) : make_int4(-1, -1, -1, -1);
+  ld.wv = (tid <= JQK_MAX_WORDS) ? __ldg(tb.desc + (size_t)head * JQK_DESC_INTS + 8 + tid) : 0;
   return ld;
 }
 
 // Projects the group's queries into column space and fills the lookup tables from the reads that
-// issue_table_loads() started.
+// issue_table_loads() started.  After the block-wide projection every warp owns whole record
+// words: it sums the partial projections of its word's columns and bounds that word's tables by
+// itself, so only the word maxima cross warps (one barrier); every warp then derives all shifts
+// and the entries are quantised by all threads.
 __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld) {
   const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
   JQK_TABLES_MARK_INIT
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
+  const int lane = tid & 31, warp = tid >> 5, n_warps = nthr >> 5;
   const bool projector = tid < TBL_THREADS;
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
@@ -125,8 +136,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     if (e < JQK_MAX_COLS * 4) reinterpret_cast<float4*>(sm.cb)[e] = ld.cv[u];
   }
   if (tid < JQK_MAX_TABLES) reinterpret_cast<int4*>(sm.fields)[tid] = ld.fv;
-  if (tid < JQK_MAX_GROUP) sm.absmax[tid] = 0u;
-  if (tid < TBL_WORDS * JQK_MAX_GROUP) (&sm.wmax[0][0])[tid] = 0u;
+  if (tid <= JQK_MAX_WORDS) sm.wcb[tid] = ld.wv;
   __syncthreads();
   JQK_TABLES_MARK(0);
   if (projector) {
@@ -152,38 +162,40 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
   }
   __syncthreads();
   JQK_TABLES_MARK(1);
-  // column c: projected queries, and the bound |q'_c| * max |level| (levels are sorted and padded
-  // with zeros, so the largest magnitude of a row is its largest |level|).  The bounds reuse the
-  // raw-query staging, which the projection is done with.
+  const int n_a_words = hd.n_a_words, n_scan_words = hd.n_a_words + hd.n_c_words;
+  // column bounds |q'_c| * max |level| reuse the raw-query staging, which the projection is done with
   float4* colb = reinterpret_cast<float4*>(&sm.qraw[0][0]);  // [JQK_MAX_COLS]
-  if (tid < JQK_MAX_COLS) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  // ---- per warp and scan word: projected queries of the word's columns, bound of its tables ----
+  for (int sw = warp; sw < n_scan_words; sw += n_warps) {
+    const int pw = (sw < n_a_words) ? sw : hd.n_words - 1 - (sw - n_a_words);  // physical word
+    const int c_first = sm.wcb[pw], n_c = sm.wcb[pw + 1] - c_first;            // <= 32 columns
+    if (lane < n_c) {
+      const int c = c_first + lane;
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const float4 p = *reinterpret_cast<const float4*>(sm.part[r][tid]);
-      s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
-    }
-    *reinterpret_cast<float4*>(sm.qproj[tid]) = s;
-    float big = 0.f;
+      for (int r = 0; r < 8; ++r) {
+        const float4 p = *reinterpret_cast<const float4*>(sm.part[r][c]);
+        s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+      }
+      *reinterpret_cast<float4*>(sm.qproj[c]) = s;
+      // levels are sorted and padded with zeros: the largest magnitude of a row is its largest |level|
+      float big = 0.f;
 #pragma unroll
-    for (int l4 = 0; l4 < 4; ++l4) {
-      const float4 lv = *reinterpret_cast<const float4*>(sm.cb + tid * 16 + 4 * l4);
-      big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
+      for (int l4 = 0; l4 < 4; ++l4) {
+        const float4 lv = *reinterpret_cast<const float4*>(sm.cb + c * 16 + 4 * l4);
+        big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
+      }
+      colb[c] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
     }
-    colb[tid] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
-  }
-  __syncthreads();
-  JQK_TABLES_MARK(2);
-  const int n_entries = hd.n_tables * 16;
-  const int n_scan_words = hd.n_a_words + hd.n_c_words;
-  if (tid < 32) {
-    // Warp 0 alone: bound on |entry| per (word, head), then the per-word shifts.  The fields of a
-    // table take their codes independently, so the largest |sum| is the sum of its columns' bounds.
-    const int lane = tid;
-    for (int t = lane; t < hd.n_tables; t += 32) {
-      const int4 f4 = *reinterpret_cast<const int4*>(sm.fields + t * 4);
+    __syncwarp();
+    // The fields of a table take their codes independently, so the largest |entry| of a table is at
+    // most the sum of its columns' bounds; lane k owns table k of the word.
+    const int t_first = (sw < n_a_words) ? 8 * sw : 8 * n_a_words + 12 * (sw - n_a_words);
+    const int n_t = (sw < n_a_words) ? 8 : 12;
+    float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lane < n_t) {
+      const int4 f4 = *reinterpret_cast<const int4*>(sm.fields + (t_first + lane) * 4);
       const int fl[4] = {f4.x, f4.y, f4.z, f4.w};
-      float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int f = 0; f < 4; ++f) {
         if (fl[f] >= 0) {
@@ -191,75 +203,73 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
           m.x += cbd.x; m.y += cbd.y; m.z += cbd.z; m.w += cbd.w;
         }
       }
-      const int w = table_word(t, hd.n_a_words);
-      atomicMax(&sm.wmax[w][0], __float_as_uint(m.x));  // non-negative floats order as uints
-      atomicMax(&sm.wmax[w][1], __float_as_uint(m.y));
-      atomicMax(&sm.wmax[w][2], __float_as_uint(m.z));
-      atomicMax(&sm.wmax[w][3], __float_as_uint(m.w));
     }
-    __syncwarp();
-    // lane w owns scan word w (n_scan_words <= 32)
-    float wm[JQK_MAX_GROUP], gm[JQK_MAX_GROUP];
-    int fit = TBL_MAX_SHIFT;
+    m.x = warp_max(m.x); m.y = warp_max(m.y); m.z = warp_max(m.z); m.w = warp_max(m.w);
+    if (lane == 0) *reinterpret_cast<float4*>(sm.wmax[sw]) = make_float4(m.x, m.y, m.z, m.w);
+  }
+  __syncthreads();
+  JQK_TABLES_MARK(2);
+  // ---- every warp derives the per-word shifts from the word maxima (lane w owns scan word w) ----
+  float wm[JQK_MAX_GROUP], gm[JQK_MAX_GROUP];
+  int fit = TBL_MAX_SHIFT;
 #pragma unroll
-    for (int h = 0; h < JQK_MAX_GROUP; ++h) {
-      wm[h] = (lane < n_scan_words) ? __uint_as_float(sm.wmax[lane][h]) : 0.f;
-      gm[h] = warp_max(wm[h]);
-      if (!(gm[h] < CUDART_INF_F)) gm[h] = 0.f;
-      // largest shift that keeps this word inside 16 bits for head h: floor(log2(gm / wm)), which for
-      // positive floats is the difference of their bit patterns shifted down by the mantissa width
-      if (gm[h] > 0.f && wm[h] > 0.f) fit = min(fit, max(0, (__float_as_int(gm[h]) - __float_as_int(wm[h])) >> 23));
-    }
-    // K_w = min over later-or-equal words (suffix minimum): non-decreasing along the scan
-    int k = (lane < n_scan_words) ? fit : TBL_MAX_SHIFT;
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+    wm[h] = (lane < n_scan_words) ? sm.wmax[lane][h] : 0.f;
+    gm[h] = warp_max(wm[h]);
+    if (!(gm[h] < CUDART_INF_F)) gm[h] = 0.f;
+    // largest shift that keeps this word inside 16 bits for head h: floor(log2(gm / wm)), which for
+    // positive floats is the difference of their bit patterns shifted down by the mantissa width
+    if (gm[h] > 0.f && wm[h] > 0.f) fit = min(fit, max(0, (__float_as_int(gm[h]) - __float_as_int(wm[h])) >> 23));
+  }
+  // K_w = min over later-or-equal words (suffix minimum): non-decreasing along the scan
+  int kw = (lane < n_scan_words) ? fit : TBL_MAX_SHIFT;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int other = __shfl_down_sync(0xffffffffu, k, o);
-      if (lane + o < 32) k = min(k, other);
-    }
-    const int prev = __shfl_up_sync(0xffffffffu, k, 1);
-    const int k_last = __shfl_sync(0xffffffffu, k, max(n_scan_words - 1, 0));
+  for (int o = 1; o < 32; o <<= 1) {
+    const int other = __shfl_down_sync(0xffffffffu, kw, o);
+    if (lane + o < 32) kw = min(kw, other);
+  }
+  const int k_last = __shfl_sync(0xffffffffu, kw, max(n_scan_words - 1, 0));
+  if (warp == 0) {
+    const int prev = __shfl_up_sync(0xffffffffu, kw, 1);
     unsigned int term = 0u;
     if (lane < n_scan_words) {
-      sm.kshift[lane] = k;
-      sm.dshift[lane] = k - (lane ? prev : 0);
-      term = (unsigned int)((lane < hd.n_a_words ? 8 : 12) * 32768) << (k_last - k);
+      sm.dshift[lane] = kw - (lane ? prev : 0);
+      term = (unsigned int)((lane < n_a_words ? 8 : 12) * 32768) << (k_last - kw);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) term += __shfl_xor_sync(0xffffffffu, term, o);
     if (lane == 0) sm.bias = term;
-    if (lane < JQK_MAX_GROUP) {
-      // One unit at shift 0.  The bound on |entry| maps to 32750, not 32767: the quantising pass
-      // rounds with a magic-number add that must never leave the signed 16-bit range.
-      float base = 1.f;
+  }
+  // One unit at shift 0.  The bound on |entry| maps to 32750, not 32767: the quantising pass rounds
+  // with a magic-number add that must never leave the signed 16-bit range.
+  float inv[JQK_MAX_GROUP];
 #pragma unroll
-      for (int h = 0; h < JQK_MAX_GROUP; ++h)
-        if (h == lane) base = (gm[h] > 0.f) ? gm[h] / 32750.f : 1.f;
-      sm.scale[lane] = base / (float)(1 << (n_scan_words ? k_last : 0));
-      sm.absmax[lane] = __float_as_uint(base);  // the per-head base scale, read by the quantising pass
+  for (int h = 0; h < JQK_MAX_GROUP; ++h) {
+    const float base = (gm[h] > 0.f) ? gm[h] * (1.f / 32750.f) : 1.f;
+    inv[h] = __frcp_rn(base);
+    if (tid == h) sm.scale[h] = base * __int_as_float((127 - (n_scan_words ? k_last : 0)) << 23);  // base / 2^k_last
+  }
+  // ---- all threads: quantise the entries (every warp knows every word's shift) ----
+  const int n_entries = hd.n_tables * 16;
+  for (int e0 = warp * 32; e0 < n_entries; e0 += nthr) {
+    const int e = e0 + lane;  // n_entries is a multiple of 16: the second half-warp may be past the end
+    const int sw = table_word(min(e, n_entries - 1) >> 4, n_a_words);
+    const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, sw));
+    if (e < n_entries) {
+      float v[JQK_MAX_GROUP];
+      table_entry(sm, e, v);
+      // round to nearest by adding 1.5 * 2^23: the low 16 bits of the sum are the two's complement
+      // value (even heads: plus 32768, the offset of the low halves)
+      const uint32_t q0 = __float_as_uint(fmaf(v[0], inv[0] * up, 12582912.f + 32768.f));
+      const uint32_t q1 = __float_as_uint(fmaf(v[1], inv[1] * up, 12582912.f));
+      const uint32_t q2 = __float_as_uint(fmaf(v[2], inv[2] * up, 12582912.f + 32768.f));
+      const uint32_t q3 = __float_as_uint(fmaf(v[3], inv[3] * up, 12582912.f));
+      // high half: signed value of the odd head; low half: value of the even head plus 32768
+      sm.lut[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
     }
   }
   __syncthreads();
-  JQK_TABLES_MARK(4);
-  float inv[JQK_MAX_GROUP];
-#pragma unroll
-  for (int h = 0; h < JQK_MAX_GROUP; ++h) inv[h] = 1.f / __uint_as_float(sm.absmax[h]);
-  for (int e = tid; e < n_entries; e += nthr) {
-    float v[JQK_MAX_GROUP];
-    table_entry(sm, e, v);
-    const float up = (float)(1 << sm.kshift[table_word(e >> 4, hd.n_a_words)]);
-    // round to nearest by adding 1.5 * 2^23: the low 16 bits of the sum are the two's complement
-    // value (even heads: plus 32768, the offset of the low halves)
-    const uint32_t q0 = __float_as_uint(fmaf(v[0], inv[0] * up, 12582912.f + 32768.f));
-    const uint32_t q1 = __float_as_uint(fmaf(v[1], inv[1] * up, 12582912.f));
-    const uint32_t q2 = __float_as_uint(fmaf(v[2], inv[2] * up, 12582912.f + 32768.f));
-    const uint32_t q3 = __float_as_uint(fmaf(v[3], inv[3] * up, 12582912.f));
-    // high half: signed value of the odd head; low half: value of the even head plus 32768
-    const uint2 packed = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
-    sm.lut[e] = packed;
-  }
-  __syncthreads();
-  JQK_TABLES_MARK(5);
+  JQK_TABLES_MARK(3);
 }
 
 // Running sums of one record.  An entry word holds a signed 16-bit value in its high half and an
