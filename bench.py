@@ -390,8 +390,8 @@ def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict
 # main arm
 # ----------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch of the headline workload,
-# from one ncu capture of that launch (76.20 MB + 1.46 MB)
-DECODE_DRAM_TRAFFIC_BYTES = 77.66e6
+# from one ncu capture of that launch (76.20 MB + 1.38 MB)
+DECODE_DRAM_TRAFFIC_BYTES = 77.58e6
 
 
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
