@@ -168,6 +168,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
 }
+// The same for data that is read once per launch (K and V pages): marked evict-first in L2, so the
+// stream does not push out what every launch reuses (the per-head tables and projection matrices).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_load_stream(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
 }
@@ -317,14 +328,15 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // K buffer r & 1, V pages to the single V buffer.  Buffers are refilled by the warp that read
   // them, in program order after its last read, so no "empty" barriers are needed.
   TileStage& st = sm.stage[warp];
+  const uint64_t stream_policy = l2_evict_first_policy();
   auto issue_keys = [&](int r, int pg_lo, int pg_hi) {
     if (lane == 0) {
       uint64_t* bar = &sm.kfull[warp][r & 1];
       const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
       const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
       bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * k_page_bytes);
-      if (ok0) bulk_load(st.k[r & 1][0], k_head + (size_t)pg_lo * k_page_words, k_page_bytes, bar);
-      if (ok1) bulk_load(st.k[r & 1][1], k_head + (size_t)pg_hi * k_page_words, k_page_bytes, bar);
+      if (ok0) bulk_load_stream(st.k[r & 1][0], k_head + (size_t)pg_lo * k_page_words, k_page_bytes, bar, stream_policy);
+      if (ok1) bulk_load_stream(st.k[r & 1][1], k_head + (size_t)pg_hi * k_page_words, k_page_bytes, bar, stream_policy);
     }
   };
   auto issue_values = [&](int r, int pg_lo, int pg_hi) {
@@ -333,8 +345,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
       const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
       bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * V_PAGE_BYTES);
-      if (ok0) bulk_load(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar);
-      if (ok1) bulk_load(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar);
+      if (ok0) bulk_load_stream(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
+      if (ok1) bulk_load_stream(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
     }
   };
   // the first copies go in flight before the tables exist, so HBM works during the prologue
