@@ -30,7 +30,8 @@ using namespace sm100;
 constexpr int TC_TILE = 128;
 constexpr int TC_STAGES = 3;
 constexpr int CH = 16;  // accumulator columns an epilogue thread handles per TMEM load
-constexpr int TC_EPI_WARPS = 16;  // four per TMEM lane quarter, each taking a quarter of the record's words
+constexpr int TC_PARTS = 4;        // parts of the record's words; one epilogue warp per TMEM lane quarter and part (five measured no faster)
+constexpr int TC_EPI_WARPS = 4 * TC_PARTS;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
 constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
@@ -49,7 +50,7 @@ struct TcSmem {
   uint4 mult[TC_COL_PAD];         // 1 << bit position in word j of the column's part (one of four is non-zero)
   int32_t meta[128];
   int32_t wcb[JQK_MAX_WORDS + 4];
-  int32_t cut[5];                 // word ranges of the four parts
+  int32_t cut[TC_PARTS + 1];      // word ranges of the parts
   uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], b_full;
   uint32_t tmem_base;
   volatile int abort;
@@ -266,21 +267,21 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
     const int part = ew >> 2;
-    // word ranges of the four parts, cut where the column counts are closest to even (low-bit
+    // word ranges of the parts, cut where the column counts are closest to even (low-bit
     // words hold up to four times as many columns as 4-bit words)
     if (ew == 0 && lane == 0) {
-      int cut[5];
-      cut[0] = 0; cut[4] = hd.n_words;
+      int cut[TC_PARTS + 1];
+      cut[0] = 0; cut[TC_PARTS] = hd.n_words;
 #pragma unroll
-      for (int q = 1; q < 4; ++q) {
-        const int target = (hd.n_active * q + 2) >> 2;
+      for (int q = 1; q < TC_PARTS; ++q) {
+        const int target = (hd.n_active * q + TC_PARTS / 2) / TC_PARTS;
         int w = cut[q - 1];
         while (w < hd.n_words && sm.wcb[w] < target) ++w;
         if (w > cut[q - 1] && w < hd.n_words && target - sm.wcb[w - 1] < sm.wcb[w] - target) --w;
         cut[q] = max(w, cut[q - 1]);
       }
 #pragma unroll
-      for (int q = 0; q < 5; ++q) sm.cut[q] = cut[q];
+      for (int q = 0; q <= TC_PARTS; ++q) sm.cut[q] = cut[q];
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
     {  // bit position of every column as a multiplier for the word registers of its part
@@ -291,7 +292,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
           const int bp = (sm.meta[et] >> 4) & 1023;
           const int w = bp >> 5;
           int p = 0;
-          while (p < 3 && w >= sm.cut[p + 1]) ++p;
+          while (p < TC_PARTS - 1 && w >= sm.cut[p + 1]) ++p;
           const int j = w - sm.cut[p];
           const uint32_t one = 1u << (bp & 31);
           m.x = (j == 0) ? one : 0u; m.y = (j == 1) ? one : 0u;
