@@ -332,29 +332,18 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
       if (in_regs) {
         uint32_t cur[TC_PART_WORDS] = {0u, 0u, 0u, 0u};
-        // the TMEM read of the next 16 columns is in flight while these are quantised
-        float v[2][CH];
-        tmem_ld16_nowait(t_lane + c_lo, v[0]);
-        int buf = 0;
-        for (int c0 = c_lo; c0 < c_hi; c0 += CH, buf ^= 1) {
-          if (buf == 0) tmem_ld_wait(v[0]); else tmem_ld_wait(v[1]);
-          if (c0 + CH < c_hi) {
-            if (buf == 0) tmem_ld16_nowait(t_lane + c0 + CH, v[1]); else tmem_ld16_nowait(t_lane + c0 + CH, v[0]);
-          }
+        for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
+          float v[CH];
+          tmem_ld16(t_lane + c0, v);
           TCP_MARK(4);
           const int n_here = c_hi - c0;
-#define JQK_QUANT(JW)                                                                         \
-          do {                                                                                \
-            if (buf == 0) {                                                                   \
-              if (n_here >= CH) quant_chunk<USE_BUCKETS, false, JW>(sm, v[0], c0, CH, cur);   \
-              else quant_chunk<USE_BUCKETS, true, JW>(sm, v[0], c0, n_here, cur);             \
-            } else {                                                                          \
-              if (n_here >= CH) quant_chunk<USE_BUCKETS, false, JW>(sm, v[1], c0, CH, cur);   \
-              else quant_chunk<USE_BUCKETS, true, JW>(sm, v[1], c0, n_here, cur);             \
-            }                                                                                 \
-          } while (0)
-          if (n_part_words <= 2) JQK_QUANT(2); else JQK_QUANT(4);
-#undef JQK_QUANT
+          if (n_part_words <= 2) {
+            if (n_here >= CH) quant_chunk<USE_BUCKETS, false, 2>(sm, v, c0, CH, cur);
+            else quant_chunk<USE_BUCKETS, true, 2>(sm, v, c0, n_here, cur);
+          } else {
+            if (n_here >= CH) quant_chunk<USE_BUCKETS, false, 4>(sm, v, c0, CH, cur);
+            else quant_chunk<USE_BUCKETS, true, 4>(sm, v, c0, n_here, cur);
+          }
           TCP_MARK(5);
         }
         if (dst) {
