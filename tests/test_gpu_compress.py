@@ -71,7 +71,8 @@ def test_batched_roundtrip_against_reference_fixture(golden):
 
 
 @pytest.mark.parametrize("b_avg,dtype,n_out,scale", [(2.0, torch.float32, 4, 15.0), (3.0, torch.float32, 4, 15.0),
-                                                      (2.5, torch.bfloat16, 8, 20.0)])
+                                                      (2.5, torch.bfloat16, 8, 20.0), (1.0, torch.bfloat16, 4, 15.0),
+                                                      (4.0, torch.bfloat16, 4, 15.0), (4.0, torch.float32, 4, 15.0)])
 def test_parity_config_codes(b_avg, dtype, n_out, scale):
     """8 heads x 4096 keys of the parity config: codes vs the oracle, mismatch rate reported."""
     H, N = 8, 4096

@@ -105,7 +105,10 @@ def _decode_case(lens, hq, hkv, b_avg, tokens_per_split=0, out_dtype=torch.float
     ([4096], 32, 8, 2.0, 256),
     ([513, 0, 2048], 8, 2, 3.0, 512),
     ([300, 299], 2, 2, 2.5, 0),
-    ([700], 16, 2, 3.0, 256)])
+    ([700], 16, 2, 3.0, 256),
+    ([1500, 900], 8, 2, 1.0, 0),          # the smallest budget: most coordinates carry no bits
+    ([1500, 900], 8, 2, 4.0, 0),          # the largest: 64-byte records, 16-level tables throughout
+    ([6000, 5000], 32, 8, 2.0, 128)])     # 696 blocks: more than one wave, tables come from the table kernel
 def test_decode_matches_oracle(lens, hq, hkv, b_avg, tps):
     out, ref = _decode_case(lens, hq, hkv, b_avg, tps)
     scale = ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)
