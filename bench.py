@@ -230,6 +230,45 @@ def cpu_decode_steps_per_s(comps, keys_cpu, budget_s: float, steps: int | None =
     return 1.0 / per_full_step, per_full_step * 1e3, cores, sample
 
 
+def cpu_stage_baselines() -> dict:
+    """The reference's torch CPU path for the two secondary stages on bounded samples of their bench
+    shapes, all host threads (about five seconds each): the per-head ``roundtrip`` loop on 8 heads x
+    16384 bf16 keys at 2.5 bits, and the moment sums of 32 q / 8 kv heads x 8192 bf16 tokens."""
+    from jointqk_b200.synthetic import config_seed, correlated_qk, fit_sigma_k_heads, spectrum_keys
+    from oracle import reference_port as orc
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    out = {}
+    T = 16384
+    keys = torch.stack([spectrum_keys(T, config_seed(4, 0, h), 8, 20.0, dtype=torch.bfloat16) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].float(), 2.5)
+    run = lambda: [orc.roundtrip(keys[h], comps[h].codebooks_padded, comps[h].forward_map, comps[h].inverse_map)
+                   for h in range(N_KV_HEADS)]
+    run()
+    t = time.perf_counter()
+    reps = 0
+    while reps < 3 or (time.perf_counter() - t < 4.0 and reps < 50):
+        run()
+        reps += 1
+    dt = (time.perf_counter() - t) / reps
+    out["prefill_compress"] = {"value": N_KV_HEADS * T / dt, "unit": "keys compressed/s", "cores": cores, "kind": "port",
+                               "sample": f"{reps} passes of the per-head roundtrip (transform, argmin, gather, inverse) over 8 heads x {T} bf16 keys, 2.5 bits/coord"}
+    T = 8192
+    q, k = correlated_qk(T, N_Q_HEADS, N_KV_HEADS, config_seed(3, 0, 0))
+    q, k = q.unsqueeze(0), k.unsqueeze(0)
+    orc.moment_sums(q, k)
+    t = time.perf_counter()
+    reps = 0
+    while reps < 3 or (time.perf_counter() - t < 4.0 and reps < 50):
+        orc.moment_sums(q, k)
+        reps += 1
+    dt = (time.perf_counter() - t) / reps
+    out["calibration_moments"] = {"value": T / dt, "unit": "calibration token-layers/s", "cores": cores, "kind": "port",
+                                  "sample": f"{reps} passes of the three fp32 einsum sums over 32 q / 8 kv heads x {T} bf16 tokens"}
+    return out
+
+
 def run_reference_arm(args, rank: int, world: int) -> None:
     """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
     if rank != 0:
@@ -507,6 +546,9 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             v, cms, cores, sample = cpu_decode_steps_per_s(comps, keys.cpu(), budget_s=20.0)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                     "ms_per_step": cms}
+            if "extra" in line:
+                for stage, base in cpu_stage_baselines().items():
+                    line["extra"][stage]["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
 
 
