@@ -128,6 +128,28 @@ def test_decode_bf16_output_and_page_permutation_invariance():
     assert ((b - ref).abs() / scale).max().item() < OUT_TOL
 
 
+def test_decode_head_dim_64_matches_oracle():
+    """The decode kernel's second head size: 64 dims, 8 q / 2 kv heads, two ragged sequences."""
+    d, hkv, hq, lens = 64, 2, 8, [1100, 333]
+    N = max(lens)
+    keys = torch.stack([spectrum_keys(N, config_seed(0, 7, h), d=d) for h in range(hkv)])
+    comps, _ = fit_sigma_k_heads(keys, 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    g = torch.Generator().manual_seed(77)
+    v = torch.randn(len(lens), hkv, N, d, generator=g).to(torch.bfloat16)
+    q = torch.randn(len(lens), hq, d, generator=g).to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, lens)
+    cache.prefill(torch.stack([keys.roll(5 * s, 1) for s in range(len(lens))]).cuda(), v.cuda(), lens)
+    out = cache.decode(q.cuda()).cpu()
+    paged.check_status(cache.status)
+    packed = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(lens), cache.status)
+    k_hat = _k_hat_from_packed(packed, comps)
+    for s, n in enumerate(lens):
+        ref = orc.decode_attention(q[s:s + 1], k_hat[s:s + 1, :, :n], v[s:s + 1, :, :n])[0]
+        err = ((out[s] - ref).abs() / ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)).max().item()
+        assert err < OUT_TOL, err
+
+
 def test_decode_from_host_buffers_equals_device_call():
     """PagedKVCache.decode_host (a replayed graph of H2D copy, decode, D2H copy, or one call of
     jqk_decode_attend_host) returns what decode() returns, also with a new query and after the cache
