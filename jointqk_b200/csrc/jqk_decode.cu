@@ -161,6 +161,15 @@ __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, 
   else ((__nv_bfloat16*)out)[idx] = __float2bfloat16(v);
 }
 
+// 2^x for x <= 0 (or -inf): one MUFU instruction, results below the normal range flush to zero.
+// Two ulps of error are far inside what the softmax weights need (they are rounded to two bf16
+// terms afterwards).
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // Bulk asynchronous copy global -> shared (16-byte aligned, size a multiple of 16), completing on `bar`.
@@ -445,8 +454,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       const float m_tile = some ? (float)imax[h] * sc[h] : -CUDART_INF_F;
       const float m_new = fmaxf(m_run[h], m_tile);
       const bool up = m_new > m_run[h];
-      alpha[h] = up ? exp2f(m_run[h] - m_new) : 1.f;  // first valid tile: exp2(-inf) = 0
-      const float p = lane_ok ? exp2f((float)ia[h] * sc[h] - m_new) : 0.f;
+      alpha[h] = up ? exp2_fast(m_run[h] - m_new) : 1.f;  // first valid tile: exp2(-inf) = 0
+      const float p = lane_ok ? exp2_fast((float)ia[h] * sc[h] - m_new) : 0.f;
       any |= some;
       grew |= up;
       m_run[h] = m_new;
