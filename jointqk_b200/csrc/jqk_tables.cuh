@@ -325,7 +325,7 @@ __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, i
   ScoreAcc acc;
   acc.clear();
   const char* lb = reinterpret_cast<const char*>(sm.lut);
-#pragma unroll 1
+#pragma unroll 4
   for (int w = 0; w < n_a_words; ++w) {
     const uint32_t x = word(w);
     acc.shift(sm.dshift[w]);
@@ -337,7 +337,7 @@ __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, i
     }
   }
   const char* lc = lb + n_a_words * 1024;
-#pragma unroll 1
+#pragma unroll 2
   for (int w = 0; w < n_c_words; ++w) {
     const uint32_t x = word(n_words - 1 - w);
     acc.shift(sm.dshift[n_a_words + w]);
