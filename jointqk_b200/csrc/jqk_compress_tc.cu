@@ -20,6 +20,8 @@
 // drains its copies, frees TMEM and returns.
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "jqk_common.cuh"
 #include "jqk_sm100.cuh"
 
@@ -38,23 +40,51 @@ constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
 constexpr uint32_t TC_TMEM_COLS = 512;               // two fp32 accumulators of 128 columns; the rest is only
                                                      // there so that a 16-column read may start at any column
 constexpr int TC_COL_PAD = 128 + CH;                 // per-column tables cover a read that starts at column 127
-constexpr int TC_PART_WORDS = 4;                     // words a part's registers hold (more: generic path)
+constexpr int TC_MAX_UNITS = JQK_MAX_WORDS;          // a unit is one record word, or two neighbouring ones
+constexpr int TC_MAX_SLOTS = 20;                     // 16-column reads of all units (more: generic path)
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
+
+// Classes of a 16-column read.  The general class takes any column; the others skip the cell and
+// threshold lookups for columns whose one or three thresholds fit the constant row itself.
+enum : int {
+  TC_CLS_GENERAL = 0,  // row = cell scale, cell offset, multiplier of the first word, of the second word
+  TC_CLS_ODD1 = 1,     // odd columns are 1-bit (or unused): row = threshold, -, multipliers; even columns general
+  TC_CLS_ALL1 = 2,     // every column 1-bit (or unused): row = threshold, -, multipliers
+  TC_CLS_ALL2 = 3,     // every column 2-bit (or unused), one word: row = three thresholds, multiplier
+};
+
+// How the epilogue warps share a head's record: units (one record word, or two neighbouring ones) are
+// dealt to the parts, and each unit is quantised in 16-column reads ("slots").
+struct TcPlan {
+  // reads of each part in the order they run: x = first column | slot << 8,
+  // y = first word of the unit | words << 8 | first read of the unit << 16 | last read << 17 | class << 18
+  int2 step[TC_PARTS][TC_MAX_SLOTS];
+  int32_t n_steps[TC_PARTS];
+  int32_t n_slots;                  // n_slots > TC_MAX_SLOTS: the generic path runs
+  int32_t slot_step[TC_MAX_SLOTS];  // part * 32 + position in the part's list
+  int32_t cut[TC_PARTS + 1];        // word ranges of the parts (generic path)
+};
 
 struct TcSmem {
   uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
   float thr[TC_COL_PAD * 16];
   uint8_t pre[TC_COL_PAD * 128];  // coarse-to-exact quantiser: lower bound of the code per cell
-  float2 aff[TC_COL_PAD];         // cell = round(127 * saturate(x * aff.x + aff.y))
-  uint4 mult[TC_COL_PAD];         // 1 << bit position in word j of the column's part (one of four is non-zero)
+  // one row per column of every 16-column read: x = cell scale, y = cell offset (cell = round(127 *
+  // saturate(v * x + y))), z / w = 1 << bit position when the column's code belongs to the first /
+  // second word of the unit that issues the read (both 0 for columns the read merely passes over)
+  float2 crow_a[TC_MAX_SLOTS * CH];  // x, y of the row
+  uint2 crow_m[TC_MAX_SLOTS * CH];   // z, w of the row
+  TcPlan plan;
   int32_t meta[128];
   int32_t wcb[JQK_MAX_WORDS + 4];
-  int32_t cut[TC_PARTS + 1];      // word ranges of the parts
   uint64_t full[TC_STAGES], empty[TC_STAGES], acc_full[2], acc_empty[2], b_full;
   uint32_t tmem_base;
   volatile int abort;
 };
+
+static_assert(TC_MAX_UNITS * sizeof(int4) <= sizeof(TcSmem::crow_a), "the planner's scratch lies in the row table");
+static_assert(sizeof(TcSmem) + 1024 <= 232448, "shared memory of the tensor-core compress kernel");
 
 struct TcArgs {
   const int32_t* n_tokens;
@@ -63,7 +93,40 @@ struct TcArgs {
   int32_t pt_stride;
   int32_t n_pages;
   int32_t tiles_per_block;
+  int32_t max_tiles;   // tile slots per sequence: the block's run is a range of sequence * max_tiles + tile
+  int32_t n_seqs;
   int32_t* status;
+};
+
+// A block's run of key tiles: slots [f, f_hi) of the head's tile list, slot = sequence * max_tiles +
+// tile.  Slots past a sequence's last key are passed over, the same way by every role.
+struct TileWalk {
+  int f, f_hi, seq, t, max_tiles, n_tok;
+  const int32_t* n_tokens;
+  __device__ TileWalk(int f_lo, int f_hi_, int max_tiles_, const int32_t* n_tokens_)
+      : f(f_lo), f_hi(f_hi_), max_tiles(max_tiles_), n_tokens(n_tokens_) {
+    seq = f / max_tiles;
+    t = f - seq * max_tiles;
+    n_tok = (f < f_hi) ? n_tokens[seq] : 0;
+  }
+  // moves to the next slot that holds keys; false at the end of the run
+  __device__ bool valid() {
+    while (f < f_hi && t * TC_TILE >= n_tok) {
+      f += max_tiles - t;
+      t = 0;
+      ++seq;
+      if (f < f_hi) n_tok = n_tokens[seq];
+    }
+    return f < f_hi;
+  }
+  __device__ void advance() {
+    ++f;
+    if (++t == max_tiles) {
+      t = 0;
+      ++seq;
+      if (f < f_hi) n_tok = n_tokens[seq];
+    }
+  }
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -108,49 +171,199 @@ __device__ long long g_tc_prof[8];
 #define TCP_MARK(i) do {} while (0)
 #endif
 
-// Codes of 16 consecutive columns (first column c0, any alignment) of one key, added at their bit
-// positions into the registers of the part's words.  Branch-free, so the 16 dependent chains
-// (cell, lower bound, exact comparison) overlap.  TAIL: only the first n_here columns belong to
-// the part; J: words of the part.  The cell tables give code 0 for columns past the head's last column.
-template <bool USE_BUCKETS, bool TAIL, int J>
-__device__ __forceinline__ void quant_chunk(const TcSmem& sm, const float (&v)[CH], int c0, int n_here,
-                                            uint32_t (&cur)[TC_PART_WORDS]) {
-  uint32_t code[CH];
-  if constexpr (USE_BUCKETS) {
-    // two fused multiply-adds find the cell (the first one saturates to [0, 1], which is the clamp),
-    // a byte table gives a lower bound of the code that is at most one short, one exact comparison
-    // with the fp32 decision threshold settles it
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const float2 af = sm.aff[c0 + i];
-      const float y = __saturatef(fmaf(v[i], af.x, af.y));
-      const uint32_t cell = __float_as_uint(fmaf(y, 127.f, 8388608.f)) - 0x4B000000u;
-      const uint32_t k = sm.pre[(c0 + i) * 128 + cell];
-      code[i] = k + ((v[i] >= sm.thr[(c0 + i) * 16 + k]) ? 1u : 0u);
+// Run by one thread.  `wcb[w]` is the first column of record word w (n_words + 1 entries, shared
+// memory), `units` a scratch of TC_MAX_UNITS int4.
+__device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta, int n_words, int n_active, int4* units) {
+  // Units: every record word on its own, or together with its neighbour where that saves a
+  // 16-column read (two 4-bit words hold 16 columns) or one of the two has no column.
+  int n_units = 0, n_slots = 0;
+  for (int w = 0; w < n_words;) {
+    const int ca = wcb[w + 1] - wcb[w];
+    int nw = 1;
+    if (w + 1 < n_words) {
+      const int cb = wcb[w + 2] - wcb[w + 1];
+      if (ca == 0 || cb == 0 || (ca + cb + CH - 1) / CH < (ca + CH - 1) / CH + (cb + CH - 1) / CH) nw = 2;
     }
-  } else {
-    // 16 independent four-step searches (rows are +inf padded, so narrower codes never pass
-    // their last level)
+    // (a unit without columns still writes its zero words: one read that places nothing)
+    const int reads = max(1, (wcb[w + nw] - wcb[w] + CH - 1) / CH);
+    units[n_units] = make_int4(w | (nw << 8), wcb[w], reads, n_slots);
+    n_slots += reads;
+    ++n_units;
+    w += nw;
+  }
+  pl.n_slots = n_slots;
+  // units to parts: largest first, each to the part with the least work so far
+  int load[TC_PARTS];
 #pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const float* th = sm.thr + (c0 + i) * 16;
-      uint32_t k = (v[i] >= th[7]) ? 8u : 0u;
-      k += (v[i] >= th[k + 3]) ? 4u : 0u;
-      k += (v[i] >= th[k + 1]) ? 2u : 0u;
-      k += (v[i] >= th[k]) ? 1u : 0u;
-      code[i] = k;
+  for (int q = 0; q < TC_PARTS; ++q) { load[q] = 0; pl.n_steps[q] = 0; }
+  uint32_t taken = 0;
+  for (int k = 0; k < n_units && n_slots <= TC_MAX_SLOTS; ++k) {
+    int best = -1, best_reads = -1;
+    for (int u = 0; u < n_units; ++u)
+      if (!((taken >> u) & 1u) && units[u].z > best_reads) { best = u; best_reads = units[u].z; }
+    taken |= 1u << best;
+    int q_min = 0;
+#pragma unroll
+    for (int q = 1; q < TC_PARTS; ++q)
+      if (load[q] < load[q_min]) q_min = q;
+#pragma unroll
+    for (int q = 0; q < TC_PARTS; ++q)
+      if (q == q_min) load[q] += best_reads * CH + 4;
+    const int4 un = units[best];
+    int pos = pl.n_steps[q_min];
+    const int c_end = wcb[(un.x & 255) + (un.x >> 8)];
+    for (int r = 0; r < un.z; ++r) {
+      // class of the read from the widths of its columns (columns past the unit count as unused)
+      bool all1 = true, all2 = true, odd1 = true;
+      for (int i = 0; i < CH; ++i) {
+        const int col = un.y + r * CH + i;
+        const int width = (col < c_end) ? (meta[col] & 15) : 0;
+        all1 = all1 && (width == 0 || width == 1);
+        all2 = all2 && (width == 0 || width == 2);
+        if (i & 1) odd1 = odd1 && (width == 0 || width == 1);
+      }
+      const bool one_word = (un.x >> 8) == 1;
+      const int cls = (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
+                    : odd1 ? TC_CLS_ODD1 : TC_CLS_GENERAL;
+      pl.slot_step[un.w + r] = q_min * 32 + pos;
+      pl.step[q_min][pos++] = make_int2((un.y + r * CH) | ((un.w + r) << 8),
+                                        un.x | ((r == 0) << 16) | ((r == un.z - 1) << 17) | (cls << 18));
     }
+    pl.n_steps[q_min] = pos;
+  }
+  // generic path: word ranges cut where the column counts are closest to even
+  int cut[TC_PARTS + 1];
+  cut[0] = 0; cut[TC_PARTS] = n_words;
+#pragma unroll
+  for (int q = 1; q < TC_PARTS; ++q) {
+    const int target = (n_active * q + TC_PARTS / 2) / TC_PARTS;
+    int w = cut[q - 1];
+    while (w < n_words && wcb[w] < target) ++w;
+    if (w > cut[q - 1] && w < n_words && target - wcb[w - 1] < wcb[w] - target) --w;
+    cut[q] = max(w, cut[q - 1]);
   }
 #pragma unroll
-  for (int i = 0; i < CH; ++i) {
-    if (!TAIL || i < n_here) {  // warp-uniform
-      const uint4 m = sm.mult[c0 + i];
-      cur[0] += code[i] * m.x;
-      if constexpr (J > 1) cur[1] += code[i] * m.y;
-      if constexpr (J > 2) cur[2] += code[i] * m.z;
-      if constexpr (J > 3) cur[3] += code[i] * m.w;
-    }
+  for (int q = 0; q <= TC_PARTS; ++q) pl.cut[q] = cut[q];
+}
+
+// Constant row e (slot e / 16, column e % 16 of the read) of a planned head; see the classes above
+// quant16.  `thr`: the head's decision thresholds, 16 per column (+inf padded).
+template <bool USE_BUCKETS>
+__device__ __forceinline__ float4 tc_const_row(const TcPlan& pl, const int32_t* wcb, const int32_t* meta,
+                                               const float* thr, const float* bucket_aff_head, int e) {
+  const int ss = pl.slot_step[e >> 4];
+  const int2 st = pl.step[ss >> 5][ss & 31];
+  const int w_first = st.y & 255, nw = (st.y >> 8) & 255, cls = (st.y >> 18) & 3;
+  const int col = (st.x & 255) + (e & 15);
+  const bool mine = col < wcb[w_first + nw];  // the column belongs to the unit that issues the read
+  uint32_t m_lo = 0u, m_hi = 0u;
+  if (mine) {
+    const int bp = (meta[col] >> 4) & 1023;
+    if ((bp >> 5) == w_first) m_lo = 1u << (bp & 31);
+    else m_hi = 1u << (bp & 31);
   }
+  if (cls == TC_CLS_ALL2)
+    return mine ? make_float4(thr[col * 16], thr[col * 16 + 1], thr[col * 16 + 2], __uint_as_float(m_lo))
+                : make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, 0.f);
+  if (cls == TC_CLS_ALL1 || (cls == TC_CLS_ODD1 && (e & 1)))
+    return make_float4(mine ? thr[col * 16] : CUDART_INF_F, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
+  float4 cr = make_float4(0.f, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
+  if (USE_BUCKETS && mine) {
+    // host form: cell = clamp(round(x * inv_step + off), 0, 127) with 2^23 folded into off
+    const float2 h2 = reinterpret_cast<const float2*>(bucket_aff_head)[col];
+    cr.x = h2.x * (1.f / 127.f);
+    cr.y = (h2.y - 8388608.f) * (1.f / 127.f);
+  }
+  return cr;
+}
+
+// Shared-space loads at a register address plus a compile-time offset (the address register of the
+// cell read is a float's bit pattern, so these cannot go through C++ pointers).
+template <int OFF>
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+  uint32_t r;
+  asm("ld.shared.u8 %0, [%1+%2];" : "=r"(r) : "r"(addr), "n"(OFF));
+  return r;
+}
+template <int OFF>
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float r;
+  asm("ld.shared.f32 %0, [%1+%2];" : "=f"(r) : "r"(addr), "n"(OFF));
+  return r;
+}
+
+// f(integral_constant<int, I>) for I = 0 .. N-1, unrolled at compile time.
+template <int I, int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  if constexpr (I < N) {
+    f(std::integral_constant<int, I>{});
+    static_for<I + 1, N>(f);
+  }
+}
+
+// Codes of 16 consecutive columns of one key, added at their bit positions into the one or two word
+// registers of the unit.  Written stage by stage over all 16 columns (cells, lower bounds, thresholds,
+// comparison, placement) so that the three dependent shared-memory reads of a column overlap with
+// those of the other fifteen.  `ra` / `rm`: the read's constant rows; `pre_base`: a float whose bit
+// pattern is the shared-memory address of the first column's cell row; `thr_base`: address of its
+// threshold row.  The cell index is formed in the subnormal range, where a float's bit pattern is its
+// integer value: fma(y, 127 * 2^-149, pre_base) has the bit pattern pre_base + round(127 y), the
+// address of the cell.
+template <bool USE_BUCKETS, int CLS, int J>
+__device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uint2* __restrict__ rm,
+                                        const float (&v)[CH], float pre_base, uint32_t thr_base, uint32_t& lo,
+                                        uint32_t& hi) {
+  constexpr bool all2 = CLS == TC_CLS_ALL2, all1 = CLS == TC_CLS_ALL1;
+  uint32_t k[CH];
+  float t[CH];
+  static_for<0, CH>([&](auto ic) {
+    constexpr int I = decltype(ic)::value;
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    const float2 a = ra[I];
+    if constexpr (all2) {
+      k[I] = ((v[I] >= a.x) ? 1u : 0u) + ((v[I] >= a.y) ? 1u : 0u);
+    } else if constexpr (direct) {
+      k[I] = (v[I] >= a.x) ? 1u : 0u;
+    } else if constexpr (USE_BUCKETS) {
+      const float y = __saturatef(fmaf(v[I], a.x, a.y));
+      k[I] = __float_as_uint(fmaf(y, __uint_as_float(127u), pre_base));  // address of the cell
+    } else {
+      k[I] = (v[I] >= lds_f32<I * 64 + 28>(thr_base)) ? 8u : 0u;
+    }
+  });
+  static_for<0, CH>([&](auto ic) {
+    constexpr int I = decltype(ic)::value;
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    if constexpr (!direct) {
+      if constexpr (USE_BUCKETS) k[I] = lds_u8<I * 128>(k[I]);  // lower bound of the code, at most one short
+      else k[I] += (v[I] >= lds_f32<I * 64 + 12>(thr_base + 4u * k[I])) ? 4u : 0u;
+    }
+  });
+  if constexpr (!USE_BUCKETS) {
+    static_for<0, CH>([&](auto ic) {
+      constexpr int I = decltype(ic)::value;
+      constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+      if constexpr (!direct) k[I] += (v[I] >= lds_f32<I * 64 + 4>(thr_base + 4u * k[I])) ? 2u : 0u;
+    });
+  }
+  static_for<0, CH>([&](auto ic) {
+    constexpr int I = decltype(ic)::value;
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    if constexpr (!direct) t[I] = lds_f32<I * 64>(thr_base + 4u * k[I]);  // exact fp32 decision threshold
+  });
+  static_for<0, CH>([&](auto ic) {
+    constexpr int I = decltype(ic)::value;
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    const uint2 m = rm[I];
+    if constexpr (all2) {
+      k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
+      lo += k[I] * m.y;
+    } else {
+      if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+      lo += k[I] * m.x;
+      if constexpr (J > 1) hi += k[I] * m.y;
+    }
+  });
 }
 
 template <bool USE_BUCKETS>
@@ -164,12 +377,10 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 #ifdef JQK_COMPRESS_PROFILE
   const long long t_block0 = clock64();
 #endif
-  const int head = blockIdx.y, seq = blockIdx.z;
-  const int n_tok = pa.n_tokens[seq];
-  const int n_tiles = (n_tok + TC_TILE - 1) / TC_TILE;
-  const int tile_lo = blockIdx.x * pa.tiles_per_block;
-  const int tile_hi = min(n_tiles, tile_lo + pa.tiles_per_block);
-  if (tile_lo >= tile_hi) return;
+  const int head = blockIdx.y;
+  const int f_lo = blockIdx.x * pa.tiles_per_block;
+  const int f_hi = min(pa.n_seqs * pa.max_tiles, f_lo + pa.tiles_per_block);
+  if (f_lo >= f_hi) return;
   const HeadDesc hd = load_desc(tb.desc, head);
 
   // ---- set-up ----
@@ -182,15 +393,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     uint4* dst = reinterpret_cast<uint4*>(sm.pre);
     for (int e = tid; e < TC_COL_PAD * 8; e += TC_THREADS)
       dst[e] = (USE_BUCKETS && e < hd.n_cols * 8) ? src[e] : make_uint4(0u, 0u, 0u, 0u);
-    for (int e = tid; e < TC_COL_PAD; e += TC_THREADS) {
-      float2 af = make_float2(0.f, 0.f);
-      if (USE_BUCKETS && e < hd.n_cols) {
-        // host form: cell = clamp(round(x * inv_step + off), 0, 127) with 2^23 folded into off
-        const float2 h2 = reinterpret_cast<const float2*>(tb.bucket_aff)[(size_t)head * 128 + e];
-        af = make_float2(h2.x * (1.f / 127.f), (h2.y - 8388608.f) * (1.f / 127.f));
-      }
-      sm.aff[e] = af;
-    }
   }
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
@@ -211,13 +413,13 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     if (lane == 0) {
       tma_prefetch_desc(&key_map);
       int issued = 0;
-      for (int t = tile_lo; t < tile_hi; ++t, ++issued) {
+      for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); w.valid(); w.advance(), ++issued) {
         const int s = issued % TC_STAGES;
         const uint32_t ph = (issued / TC_STAGES) & 1;
         if (issued >= TC_STAGES && !tc_wait(sm, &sm.empty[s], ph ^ 1, pa.status)) break;
         mbar_arrive_expect_tx(&sm.full[s], TC_A_BYTES);
-        tma_load_4d(sm.a[s], &key_map, &sm.full[s], 0, t * TC_TILE, head, seq);
-        tma_load_4d(sm.a[s] + TC_A_BYTES / 2, &key_map, &sm.full[s], 64, t * TC_TILE, head, seq);
+        tma_load_4d(sm.a[s], &key_map, &sm.full[s], 0, w.t * TC_TILE, head, w.seq);
+        tma_load_4d(sm.a[s] + TC_A_BYTES / 2, &key_map, &sm.full[s], 64, w.t * TC_TILE, head, w.seq);
       }
       if (sm.abort) {  // let the copies that were issued land before the block goes away
         for (int i = max(0, issued - TC_STAGES); i < issued; ++i)
@@ -238,7 +440,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 #ifdef JQK_COMPRESS_PROFILE
       long long tp = clock64();
 #endif
-      for (int t = tile_lo; ok && t < tile_hi; ++t, ++it) {
+      for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); ok && w.valid(); w.advance(), ++it) {
         const int s = it % TC_STAGES, a = it & 1;
         if (!tc_wait(sm, &sm.full[s], (it / TC_STAGES) & 1, pa.status)) break;
         TCP_MARK(0);
@@ -267,46 +469,23 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
     const int part = ew >> 2;
-    // word ranges of the parts, cut where the column counts are closest to even (low-bit
-    // words hold up to four times as many columns as 4-bit words)
-    if (ew == 0 && lane == 0) {
-      int cut[TC_PARTS + 1];
-      cut[0] = 0; cut[TC_PARTS] = hd.n_words;
-#pragma unroll
-      for (int q = 1; q < TC_PARTS; ++q) {
-        const int target = (hd.n_active * q + TC_PARTS / 2) / TC_PARTS;
-        int w = cut[q - 1];
-        while (w < hd.n_words && sm.wcb[w] < target) ++w;
-        if (w > cut[q - 1] && w < hd.n_words && target - sm.wcb[w - 1] < sm.wcb[w] - target) --w;
-        cut[q] = max(w, cut[q - 1]);
-      }
-#pragma unroll
-      for (int q = 0; q <= TC_PARTS; ++q) sm.cut[q] = cut[q];
-    }
+    if (ew == 0 && lane == 0) tc_make_plan(sm.plan, sm.wcb, sm.meta, hd.n_words, hd.n_active, reinterpret_cast<int4*>(sm.crow_a));
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
-    {  // bit position of every column as a multiplier for the word registers of its part
+    const bool planned = sm.plan.n_slots <= TC_MAX_SLOTS;
+    if (planned) {  // constant rows of every read
       const int et = tid - 64;
-      if (et < TC_COL_PAD) {
-        uint4 m = make_uint4(0u, 0u, 0u, 0u);
-        if (et < hd.n_active) {
-          const int bp = (sm.meta[et] >> 4) & 1023;
-          const int w = bp >> 5;
-          int p = 0;
-          while (p < TC_PARTS - 1 && w >= sm.cut[p + 1]) ++p;
-          const int j = w - sm.cut[p];
-          const uint32_t one = 1u << (bp & 31);
-          m.x = (j == 0) ? one : 0u; m.y = (j == 1) ? one : 0u;
-          m.z = (j == 2) ? one : 0u; m.w = (j == 3) ? one : 0u;
-        }
-        sm.mult[et] = m;
+      if (et < sm.plan.n_slots * CH)
+      {
+        const float4 cr = tc_const_row<USE_BUCKETS>(sm.plan, sm.wcb, sm.meta, sm.thr, tb.bucket_aff + (size_t)head * 256, et);
+        sm.crow_a[et] = make_float2(cr.x, cr.y);
+        sm.crow_m[et] = make_uint2(__float_as_uint(cr.z), __float_as_uint(cr.w));
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
-    const int w_lo = sm.cut[part], w_hi = sm.cut[part + 1];
-    const int n_part_words = w_hi - w_lo;
-    const bool in_regs = n_part_words <= TC_PART_WORDS;  // otherwise: the generic word-by-word path
+    const int w_lo = sm.plan.cut[part], w_hi = sm.plan.cut[part + 1];
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
-    const int seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
+    const int my_steps = sm.plan.n_steps[part];
+    const uint32_t pre_addr = smem_u32(sm.pre), thr_addr = smem_u32(sm.thr);
     const int wpr = tb.words_per_record;
     int it = 0;
 #ifdef JQK_COMPRESS_PROFILE
@@ -315,13 +494,18 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 #undef TCP_MARK
 #define TCP_MARK(i) do { const long long n__ = clock64(); if (prof_on) atomicAdd((unsigned long long*)&g_tc_prof[i], (unsigned long long)(n__ - tp)); tp = n__; } while (0)
 #endif
-    for (int t = tile_lo; t < tile_hi; ++t, ++it) {
-      const int a = it & 1;
+    int seq_of_start = -1, seq_start = 0;
+    for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); w.valid(); w.advance(), ++it) {
+      const int a = it & 1, seq = w.seq;
+      if (seq != seq_of_start) {
+        seq_start = pa.seq_starts ? pa.seq_starts[seq] : 0;
+        seq_of_start = seq;
+      }
       if (!tc_wait(sm, &sm.acc_full[a], (it >> 1) & 1, pa.status)) break;
       TCP_MARK(3);
       tc_fence_after();
-      const int key = t * TC_TILE + row;
-      const bool valid = key < n_tok;
+      const int key = w.t * TC_TILE + row;
+      const bool valid = key < w.n_tok;
       uint32_t* dst = nullptr;
       if (valid) {
         const int tok = seq_start + key;
@@ -330,26 +514,38 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
           dst = k_pool + ((size_t)page * tb.n_heads + head) * wpr * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS);
       }
       const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
-      if (in_regs) {
-        uint32_t cur[TC_PART_WORDS] = {0u, 0u, 0u, 0u};
-        for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
-          float v[CH];
-          tmem_ld16(t_lane + c0, v);
+      if (planned) {
+        // one read ahead: the next 16 columns are on their way while these are quantised
+        float v[CH];
+        uint32_t lo = 0u, hi = 0u;
+#pragma unroll 1
+        for (int s = 0; s < my_steps; ++s) {
+          const int2 cur = sm.plan.step[part][s];
+          tmem_ld16(t_lane + (cur.x & 255), v);
           TCP_MARK(4);
-          const int n_here = c_hi - c0;
-          if (n_part_words <= 2) {
-            if (n_here >= CH) quant_chunk<USE_BUCKETS, false, 2>(sm, v, c0, CH, cur);
-            else quant_chunk<USE_BUCKETS, true, 2>(sm, v, c0, n_here, cur);
-          } else {
-            if (n_here >= CH) quant_chunk<USE_BUCKETS, false, 4>(sm, v, c0, CH, cur);
-            else quant_chunk<USE_BUCKETS, true, 4>(sm, v, c0, n_here, cur);
+          const int c0 = cur.x & 255;
+          const float2* ra = sm.crow_a + (cur.x >> 8) * CH;
+          const uint2* rm = sm.crow_m + (cur.x >> 8) * CH;
+          const float pre_base = __uint_as_float(pre_addr + (uint32_t)c0 * 128u);
+          const uint32_t thr_base = thr_addr + (uint32_t)c0 * 64u;
+          if (cur.y & (1 << 16)) lo = hi = 0u;
+          const bool two = (cur.y & 0xff00) == 0x200;
+          switch ((cur.y >> 18) & 3) {  // warp-uniform
+            case TC_CLS_ALL2: quant16<USE_BUCKETS, TC_CLS_ALL2, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
+            case TC_CLS_ALL1: quant16<USE_BUCKETS, TC_CLS_ALL1, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
+            case TC_CLS_ODD1:
+              if (two) quant16<USE_BUCKETS, TC_CLS_ODD1, 2>(ra, rm, v, pre_base, thr_base, lo, hi);
+              else quant16<USE_BUCKETS, TC_CLS_ODD1, 1>(ra, rm, v, pre_base, thr_base, lo, hi);
+              break;
+            default:
+              if (two) quant16<USE_BUCKETS, TC_CLS_GENERAL, 2>(ra, rm, v, pre_base, thr_base, lo, hi);
+              else quant16<USE_BUCKETS, TC_CLS_GENERAL, 1>(ra, rm, v, pre_base, thr_base, lo, hi);
           }
           TCP_MARK(5);
-        }
-        if (dst) {
-#pragma unroll
-          for (int j = 0; j < TC_PART_WORDS; ++j)
-            if (w_lo + j < w_hi) dst[(w_lo + j) * JQK_PAGE_TOKENS] = cur[j];
+          if ((cur.y & (1 << 17)) && dst) {
+            dst[(cur.y & 255) * JQK_PAGE_TOKENS] = lo;
+            if (two) dst[((cur.y & 255) + 1) * JQK_PAGE_TOKENS] = hi;
+          }
         }
       } else {
         int cur_w = w_lo;
@@ -440,17 +636,19 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
     if (!encode_bf16_map(&limb_map, tables->fwd_limbs, 2, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "limb tensor map: %s", err);
   }
   const int max_tiles = (max_tokens + TC_TILE - 1) / TC_TILE;
-  // at most one wave of blocks over 148 SMs (a block's set-up loads 120 KB of tables), each block a
-  // contiguous run of tiles of one head
-  const long long pairs = (long long)n_seqs * tables->n_heads;
-  long long blocks_per_pair = 148 / pairs;
-  if (blocks_per_pair < 1) blocks_per_pair = 1;
-  int tiles_per_block = (int)((max_tiles + blocks_per_pair - 1) / blocks_per_pair);
+  // At most one wave of blocks over 148 SMs (a block's set-up loads 120 KB of tables): the tile
+  // slots of a head, all sequences one after the other, are cut into equal runs.
+  long long blocks_per_head = 148 / tables->n_heads;
+  if (blocks_per_head < 1) blocks_per_head = 1;
+  const long long slots = (long long)n_seqs * max_tiles;
+  if (slots > 0x7fffffffll) return 1;
+  int tiles_per_block = (int)((slots + blocks_per_head - 1) / blocks_per_head);
   if (tiles_per_block < 4) tiles_per_block = 4;
-  dim3 grid((max_tiles + tiles_per_block - 1) / tiles_per_block, tables->n_heads, n_seqs);
-  TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, status};
+  dim3 grid((unsigned)((slots + tiles_per_block - 1) / tiles_per_block), tables->n_heads, 1);
+  TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, max_tiles, n_seqs, status};
   const size_t smem = sizeof(TcSmem) + 1024;
-  if (tables->bucket_pre && tables->bucket_aff) {
+  const bool buckets = tables->bucket_pre && tables->bucket_aff;
+  if (buckets) {
     JQK_SMEM_ONCE(compress_tc_kernel<true>, smem, "tensor-core compress smem attribute");
     compress_tc_kernel<true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
   } else {
