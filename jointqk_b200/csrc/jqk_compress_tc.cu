@@ -7,15 +7,18 @@
 // smallest first into one fp32 TMEM accumulator, so the transform keeps fp32 accuracy, which
 // the bit-exact code requirement needs (one bf16 or TF32 pass would flip ~1e-3 of the codes).
 //
-// One thread block walks a run of 128-key tiles of one (sequence, head):
+// One thread block walks a run of 128-key tiles of one head (the head's tiles of all sequences form
+// one list, cut into equal runs, so that a batch fills every SM whatever its shape):
 //   warp 0      TMA producer: key tiles [128 keys][128 dims] bf16 into a 3-stage ring (128B swizzle)
 //   warp 1      allocates TMEM, loads the three limb matrices once, issues 24 MMAs per tile
 //               (8 K-steps x 3 limbs, M=128, N=columns, K=16) into one of two accumulators
-//   warps 2..17 epilogue: a thread owns one key (TMEM lane) and a quarter of the record's words; it
-//               reads 16 columns at a time, finds each code (a cell lookup plus one comparison with
-//               the exact fp32 decision threshold, or a binary search over the thresholds when the
-//               cell tables do not apply), appends the bits and stores finished words to the page
-//               (word-major pages: 64-byte segments per warp store).
+//   warps 2..17 epilogue: a thread owns one key (TMEM lane); the record's words are dealt to the four
+//               warps of a lane quarter as units of one or two words, and a unit is quantised in
+//               16-column reads.  A column's code is a cell lookup plus one comparison with the exact
+//               fp32 decision threshold (a binary search over the thresholds when the cell tables do
+//               not apply; plain comparisons for 1- and 2-bit columns); its bit position and cell
+//               scale come from a constant row per column of each read.  Finished words go to the
+//               page (word-major pages: 64-byte segments per warp store).
 // Every mbarrier wait is bounded in time; on expiry the block flags JQK_STATUS_WAIT_EXPIRED,
 // drains its copies, frees TMEM and returns.
 #include <math_constants.h>
@@ -32,7 +35,7 @@ using namespace sm100;
 constexpr int TC_TILE = 128;
 constexpr int TC_STAGES = 3;
 constexpr int CH = 16;  // accumulator columns an epilogue thread handles per TMEM load
-constexpr int TC_PARTS = 4;        // parts of the record's words; one epilogue warp per TMEM lane quarter and part (five measured no faster)
+constexpr int TC_PARTS = 4;        // parts of the record's words; one epilogue warp per TMEM lane quarter and part (three and five measured no faster)
 constexpr int TC_EPI_WARPS = 4 * TC_PARTS;
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
@@ -316,20 +319,25 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
   constexpr bool all2 = CLS == TC_CLS_ALL2, all1 = CLS == TC_CLS_ALL1;
   uint32_t k[CH];
   float t[CH];
-  static_for<0, CH>([&](auto ic) {
-    constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
-    const float2 a = ra[I];
-    if constexpr (all2) {
-      k[I] = ((v[I] >= a.x) ? 1u : 0u) + ((v[I] >= a.y) ? 1u : 0u);
-    } else if constexpr (direct) {
-      k[I] = (v[I] >= a.x) ? 1u : 0u;
-    } else if constexpr (USE_BUCKETS) {
-      const float y = __saturatef(fmaf(v[I], a.x, a.y));
-      k[I] = __float_as_uint(fmaf(y, __uint_as_float(127u), pre_base));  // address of the cell
-    } else {
-      k[I] = (v[I] >= lds_f32<I * 64 + 28>(thr_base)) ? 8u : 0u;
-    }
+  // (rows of two neighbouring columns come in one 16-byte read)
+  static_for<0, CH / 2>([&](auto pc) {
+    constexpr int P = decltype(pc)::value;
+    const float4 a2 = reinterpret_cast<const float4*>(ra)[P];
+    static_for<0, 2>([&](auto hc) {
+      constexpr int I = 2 * P + decltype(hc)::value;
+      [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+      const float2 a = (I & 1) ? make_float2(a2.z, a2.w) : make_float2(a2.x, a2.y);
+      if constexpr (all2) {
+        k[I] = ((v[I] >= a.x) ? 1u : 0u) + ((v[I] >= a.y) ? 1u : 0u);
+      } else if constexpr (direct) {
+        k[I] = (v[I] >= a.x) ? 1u : 0u;
+      } else if constexpr (USE_BUCKETS) {
+        const float y = __saturatef(fmaf(v[I], a.x, a.y));
+        k[I] = __float_as_uint(fmaf(y, __uint_as_float(127u), pre_base));  // address of the cell
+      } else {
+        k[I] = (v[I] >= lds_f32<I * 64 + 28>(thr_base)) ? 8u : 0u;
+      }
+    });
   });
   static_for<0, CH>([&](auto ic) {
     constexpr int I = decltype(ic)::value;
@@ -351,18 +359,22 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
     [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
     if constexpr (!direct) t[I] = lds_f32<I * 64>(thr_base + 4u * k[I]);  // exact fp32 decision threshold
   });
-  static_for<0, CH>([&](auto ic) {
-    constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
-    const uint2 m = rm[I];
-    if constexpr (all2) {
-      k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
-      lo += k[I] * m.y;
-    } else {
-      if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
-      lo += k[I] * m.x;
-      if constexpr (J > 1) hi += k[I] * m.y;
-    }
+  static_for<0, CH / 2>([&](auto pc) {
+    constexpr int P = decltype(pc)::value;
+    const uint4 m2 = reinterpret_cast<const uint4*>(rm)[P];
+    static_for<0, 2>([&](auto hc) {
+      constexpr int I = 2 * P + decltype(hc)::value;
+      [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+      const uint2 m = (I & 1) ? make_uint2(m2.z, m2.w) : make_uint2(m2.x, m2.y);
+      if constexpr (all2) {
+        k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
+        lo += k[I] * m.y;
+      } else {
+        if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+        lo += k[I] * m.x;
+        if constexpr (J > 1) hi += k[I] * m.y;
+      }
+    });
   });
 }
 
@@ -515,7 +527,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       }
       const uint32_t t_lane = tmem + a * 128 + ((uint32_t)(32 * (warp & 3)) << 16);
       if (planned) {
-        // one read ahead: the next 16 columns are on their way while these are quantised
+        // (blocking reads: a second register buffer for a read ahead costs more than its wait)
         float v[CH];
         uint32_t lo = 0u, hi = 0u;
 #pragma unroll 1
