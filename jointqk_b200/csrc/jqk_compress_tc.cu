@@ -54,7 +54,11 @@ enum : int {
   TC_CLS_ODD1 = 1,     // odd columns are 1-bit (or unused): row = threshold, -, multipliers; even columns general
   TC_CLS_ALL1 = 2,     // every column 1-bit (or unused): row = threshold, -, multipliers
   TC_CLS_ALL2 = 3,     // every column 2-bit (or unused), one word: row = three thresholds, multiplier
+  TC_CLS_REG4 = 4,     // sixteen 4-bit columns filling two words in order: general, multipliers known at compile time
+  TC_CLS_REG31 = 5,    // eight (3-bit, 1-bit) pairs filling one word in order: as TC_CLS_ODD1, multipliers known at compile time
 };
+// The multiplier half of a row is 8 bytes (first word, second word; for TC_CLS_ALL2 third threshold,
+// multiplier) when the unit has two words or the class is TC_CLS_ALL2, else 4 bytes (first word).
 
 // How the epilogue warps share a head's record: units (one record word, or two neighbouring ones) are
 // dealt to the parts, and each unit is quantised in 16-column reads ("slots").
@@ -226,7 +230,17 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
         if (i & 1) odd1 = odd1 && (width == 0 || width == 1);
       }
       const bool one_word = (un.x >> 8) == 1;
-      const int cls = (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
+      bool reg4 = !one_word && un.y + r * CH + CH <= c_end;
+      for (int i = 0; reg4 && i < CH; ++i) {
+        const int mt = meta[un.y + r * CH + i];
+        reg4 = (mt & 15) == 4 && ((mt >> 4) & 1023) == 32 * (un.x & 255) + 4 * i;
+      }
+      bool reg31 = one_word && un.y + r * CH + CH <= c_end;
+      for (int i = 0; reg31 && i < CH; ++i) {
+        const int mt = meta[un.y + r * CH + i];
+        reg31 = (mt & 15) == ((i & 1) ? 1 : 3) && ((mt >> 4) & 1023) == 32 * (un.x & 255) + 4 * (i / 2) + 3 * (i & 1);
+      }
+      const int cls = reg4 ? TC_CLS_REG4 : reg31 ? TC_CLS_REG31 : (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
                     : odd1 ? TC_CLS_ODD1 : TC_CLS_GENERAL;
       pl.slot_step[un.w + r] = q_min * 32 + pos;
       pl.step[q_min][pos++] = make_int2((un.y + r * CH) | ((un.w + r) << 8),
@@ -256,7 +270,7 @@ __device__ __forceinline__ float4 tc_const_row(const TcPlan& pl, const int32_t* 
                                                const float* thr, const float* bucket_aff_head, int e) {
   const int ss = pl.slot_step[e >> 4];
   const int2 st = pl.step[ss >> 5][ss & 31];
-  const int w_first = st.y & 255, nw = (st.y >> 8) & 255, cls = (st.y >> 18) & 3;
+  const int w_first = st.y & 255, nw = (st.y >> 8) & 255, cls = (st.y >> 18) & 7;
   const int col = (st.x & 255) + (e & 15);
   const bool mine = col < wcb[w_first + nw];  // the column belongs to the unit that issues the read
   uint32_t m_lo = 0u, m_hi = 0u;
@@ -268,7 +282,7 @@ __device__ __forceinline__ float4 tc_const_row(const TcPlan& pl, const int32_t* 
   if (cls == TC_CLS_ALL2)
     return mine ? make_float4(thr[col * 16], thr[col * 16 + 1], thr[col * 16 + 2], __uint_as_float(m_lo))
                 : make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, 0.f);
-  if (cls == TC_CLS_ALL1 || (cls == TC_CLS_ODD1 && (e & 1)))
+  if (cls == TC_CLS_ALL1 || ((cls == TC_CLS_ODD1 || cls == TC_CLS_REG31) && (e & 1)))
     return make_float4(mine ? thr[col * 16] : CUDART_INF_F, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
   float4 cr = make_float4(0.f, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
   if (USE_BUCKETS && mine) {
@@ -325,7 +339,7 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
     const float4 a2 = reinterpret_cast<const float4*>(ra)[P];
     static_for<0, 2>([&](auto hc) {
       constexpr int I = 2 * P + decltype(hc)::value;
-      [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+      [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
       const float2 a = (I & 1) ? make_float2(a2.z, a2.w) : make_float2(a2.x, a2.y);
       if constexpr (all2) {
         k[I] = ((v[I] >= a.x) ? 1u : 0u) + ((v[I] >= a.y) ? 1u : 0u);
@@ -341,7 +355,7 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
   });
   static_for<0, CH>([&](auto ic) {
     constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
     if constexpr (!direct) {
       if constexpr (USE_BUCKETS) k[I] = lds_u8<I * 128>(k[I]);  // lower bound of the code, at most one short
       else k[I] += (v[I] >= lds_f32<I * 64 + 12>(thr_base + 4u * k[I])) ? 4u : 0u;
@@ -350,32 +364,58 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
   if constexpr (!USE_BUCKETS) {
     static_for<0, CH>([&](auto ic) {
       constexpr int I = decltype(ic)::value;
-      constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+      constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
       if constexpr (!direct) k[I] += (v[I] >= lds_f32<I * 64 + 4>(thr_base + 4u * k[I])) ? 2u : 0u;
     });
   }
   static_for<0, CH>([&](auto ic) {
     constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+    [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
     if constexpr (!direct) t[I] = lds_f32<I * 64>(thr_base + 4u * k[I]);  // exact fp32 decision threshold
   });
-  static_for<0, CH / 2>([&](auto pc) {
-    constexpr int P = decltype(pc)::value;
-    const uint4 m2 = reinterpret_cast<const uint4*>(rm)[P];
-    static_for<0, 2>([&](auto hc) {
-      constexpr int I = 2 * P + decltype(hc)::value;
-      [[maybe_unused]] constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
-      const uint2 m = (I & 1) ? make_uint2(m2.z, m2.w) : make_uint2(m2.x, m2.y);
-      if constexpr (all2) {
-        k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
-        lo += k[I] * m.y;
-      } else {
-        if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
-        lo += k[I] * m.x;
-        if constexpr (J > 1) hi += k[I] * m.y;
-      }
+  if constexpr (CLS == TC_CLS_REG31) {
+    static_for<0, CH>([&](auto ic) {
+      constexpr int I = decltype(ic)::value;
+      if constexpr (!(I & 1)) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+      lo += k[I] * (1u << (4 * (I / 2) + 3 * (I & 1)));
     });
-  });
+  } else if constexpr (CLS == TC_CLS_REG4) {
+    static_for<0, CH>([&](auto ic) {
+      constexpr int I = decltype(ic)::value;
+      k[I] += (v[I] >= t[I]) ? 1u : 0u;
+      if constexpr (I < 8) lo += k[I] * (1u << (4 * I));
+      else hi += k[I] * (1u << (4 * (I - 8)));
+    });
+  } else if constexpr (J > 1 || all2) {
+    static_for<0, CH / 2>([&](auto pc) {
+      constexpr int P = decltype(pc)::value;
+      const uint4 m2 = reinterpret_cast<const uint4*>(rm)[P];
+      static_for<0, 2>([&](auto hc) {
+        constexpr int I = 2 * P + decltype(hc)::value;
+        [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
+        const uint2 m = (I & 1) ? make_uint2(m2.z, m2.w) : make_uint2(m2.x, m2.y);
+        if constexpr (all2) {
+          k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
+          lo += k[I] * m.y;
+        } else {
+          if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+          lo += k[I] * m.x;
+          hi += k[I] * m.y;
+        }
+      });
+    });
+  } else {
+    static_for<0, CH / 4>([&](auto qc) {
+      constexpr int Q = decltype(qc)::value;
+      const uint4 m4 = reinterpret_cast<const uint4*>(rm)[Q];  // four columns' first-word multipliers
+      static_for<0, 4>([&](auto hc) {
+        constexpr int H = decltype(hc)::value, I = 4 * Q + H;
+        [[maybe_unused]] constexpr bool direct = all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
+        if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+        lo += k[I] * (H == 0 ? m4.x : H == 1 ? m4.y : H == 2 ? m4.z : m4.w);
+      });
+    });
+  }
 }
 
 template <bool USE_BUCKETS>
@@ -490,7 +530,11 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       {
         const float4 cr = tc_const_row<USE_BUCKETS>(sm.plan, sm.wcb, sm.meta, sm.thr, tb.bucket_aff + (size_t)head * 256, et);
         sm.crow_a[et] = make_float2(cr.x, cr.y);
-        sm.crow_m[et] = make_uint2(__float_as_uint(cr.z), __float_as_uint(cr.w));
+        const int2 st = sm.plan.step[sm.plan.slot_step[et >> 4] >> 5][sm.plan.slot_step[et >> 4] & 31];
+        if (((st.y >> 8) & 255) > 1 || ((st.y >> 18) & 7) == TC_CLS_ALL2)
+          sm.crow_m[et] = make_uint2(__float_as_uint(cr.z), __float_as_uint(cr.w));
+        else
+          reinterpret_cast<uint32_t*>(sm.crow_m + (et & ~15))[et & 15] = __float_as_uint(cr.z);
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
@@ -542,7 +586,9 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
           const uint32_t thr_base = thr_addr + (uint32_t)c0 * 64u;
           if (cur.y & (1 << 16)) lo = hi = 0u;
           const bool two = (cur.y & 0xff00) == 0x200;
-          switch ((cur.y >> 18) & 3) {  // warp-uniform
+          switch ((cur.y >> 18) & 7) {  // warp-uniform
+            case TC_CLS_REG4: quant16<USE_BUCKETS, TC_CLS_REG4, 2>(ra, rm, v, pre_base, thr_base, lo, hi); break;
+            case TC_CLS_REG31: quant16<USE_BUCKETS, TC_CLS_REG31, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
             case TC_CLS_ALL2: quant16<USE_BUCKETS, TC_CLS_ALL2, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
             case TC_CLS_ALL1: quant16<USE_BUCKETS, TC_CLS_ALL1, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
             case TC_CLS_ODD1:
