@@ -193,3 +193,43 @@ def test_tensor_core_path_ragged_bf16_and_append():
     pk = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, [700], cache.status)
     again = paged.unpack_codes(pk).cpu()
     assert int((again[0] != codes[0]).sum()) <= 2
+
+
+@pytest.mark.parametrize("hist", [
+    (0, 128, 0, 0, 0),       # every column 1-bit: four words of 32 columns
+    (0, 0, 128, 0, 0),       # every column 2-bit
+    (0, 64, 0, 64, 0),       # (3,1) pairs only
+    (0, 0, 0, 0, 128),       # every column 4-bit: sixteen words
+    (10, 33, 21, 30, 34),    # odd counts: slots and bytes of every kind, words shared by two regions
+    (100, 9, 7, 7, 5),       # few active columns, a record of two words
+    (0, 2, 43, 42, 41),      # (3,3,2) bytes
+])
+def test_tensor_core_path_allocations(hist):
+    """Allocations that reach each way the tensor-core kernel quantises a 16-column read (general
+    lookups, plain comparisons for 1- and 2-bit columns, regular 4-bit and (3,1) words, units of one
+    and two words): bf16 keys, two ragged sequences, codes against the oracle."""
+    H, N, d = 2, 1500, 128
+    gen = torch.Generator().manual_seed(1234 + sum(i * c for i, c in enumerate(hist)))
+    comps, keys = [], []
+    for h in range(H):
+        bits = torch.cat([torch.full((c,), b, dtype=torch.long) for b, c in enumerate(hist)])
+        bits = bits[torch.randperm(d, generator=gen)]
+        R = jq.generate_rotation_matrix(d, seed=77 + h)
+        stds = torch.exp(torch.randn(d, generator=gen))
+        x = torch.randn(N, d, generator=gen) * stds
+        keys.append((x @ R.T).to(torch.bfloat16))
+        comps.append(jq.PerCoordCompressor(bits, stds, R, R.T))
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    kb = torch.stack([torch.stack(keys), torch.stack(keys).flip(1)])              # (2, H, N, d)
+    lens = [N, 700]
+    packed = paged.compress(tables, kb.cuda(), lens)
+    paged.check_status(packed.status)
+    codes = paged.unpack_codes(packed).cpu()
+    bad = total = 0
+    for s, n in enumerate(lens):
+        for h in range(H):
+            ref_codes, _ = oracle_codes_and_recon(comps[h], kb[s, h, :n])
+            bad += int((codes[s, h, :n].long() != ref_codes).sum())
+            total += n * d
+    print(f"code mismatch rate hist={hist}: {bad}/{total}")
+    assert bad <= max(2, int(MAX_RATE * total)), bad
