@@ -99,8 +99,7 @@ struct TcArgs {
   const int32_t* page_table;
   int32_t pt_stride;
   int32_t n_pages;
-  int32_t blocks_base;  // blocks per head; the first blocks_extra heads have one more
-  int32_t blocks_extra;
+  int32_t tiles_per_block;
   int32_t max_tiles;   // tile slots per sequence: the block's run is a range of sequence * max_tiles + tile
   int32_t n_seqs;
   int32_t* status;
@@ -430,17 +429,9 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 #ifdef JQK_COMPRESS_PROFILE
   const long long t_block0 = clock64();
 #endif
-  // the grid's blocks in order: blocks_base + 1 for each of the first blocks_extra heads, blocks_base for the others
-  int head, idx, n_blk;
-  {
-    const int b = blockIdx.x, wide = pa.blocks_extra * (pa.blocks_base + 1);
-    if (b < wide) { head = b / (pa.blocks_base + 1); idx = b - head * (pa.blocks_base + 1); n_blk = pa.blocks_base + 1; }
-    else { head = pa.blocks_extra + (b - wide) / pa.blocks_base; idx = (b - wide) % pa.blocks_base; n_blk = pa.blocks_base; }
-  }
-  const int n_slots_head = pa.n_seqs * pa.max_tiles;
-  const int tiles_per_block = max(4, (n_slots_head + n_blk - 1) / n_blk);
-  const int f_lo = idx * tiles_per_block;
-  const int f_hi = min(n_slots_head, f_lo + tiles_per_block);
+  const int head = blockIdx.y;
+  const int f_lo = blockIdx.x * pa.tiles_per_block;
+  const int f_hi = min(pa.n_seqs * pa.max_tiles, f_lo + pa.tiles_per_block);
   if (f_lo >= f_hi) return;
   const HeadDesc hd = load_desc(tb.desc, head);
 
@@ -703,17 +694,16 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
     if (!encode_bf16_map(&limb_map, tables->fwd_limbs, 2, dims, strides, box, err, sizeof(err))) return fail(JQK_E_ARG, "limb tensor map: %s", err);
   }
   const int max_tiles = (max_tokens + TC_TILE - 1) / TC_TILE;
-  // One wave of 148 blocks (a block's set-up loads 120 KB of tables): the tile slots of a head, all
-  // sequences one after the other, are cut into equal runs; 148 / heads blocks per head, and one
-  // more for the first 148 % heads heads.
+  // At most one wave of blocks over 148 SMs (a block's set-up loads 120 KB of tables): the tile
+  // slots of a head, all sequences one after the other, are cut into equal runs.
+  long long blocks_per_head = 148 / tables->n_heads;
+  if (blocks_per_head < 1) blocks_per_head = 1;
   const long long slots = (long long)n_seqs * max_tiles;
   if (slots > 0x7fffffffll) return 1;
-  int blocks_base = 148 / tables->n_heads, blocks_extra = 148 % tables->n_heads;
-  if (blocks_base < 1) { blocks_base = 1; blocks_extra = 0; }
-  const long long useful = (slots + 3) / 4;  // a block takes at least four slots
-  if (useful <= blocks_base) { blocks_base = (int)(useful < 1 ? 1 : useful); blocks_extra = 0; }
-  dim3 grid((unsigned)(blocks_base * tables->n_heads + blocks_extra), 1, 1);
-  TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, blocks_base, blocks_extra, max_tiles, n_seqs, status};
+  int tiles_per_block = (int)((slots + blocks_per_head - 1) / blocks_per_head);
+  if (tiles_per_block < 4) tiles_per_block = 4;
+  dim3 grid((unsigned)((slots + tiles_per_block - 1) / tiles_per_block), tables->n_heads, 1);
+  TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, max_tiles, n_seqs, status};
   const size_t smem = sizeof(TcSmem) + 1024;
   const bool buckets = tables->bucket_pre && tables->bucket_aff;
   if (buckets) {
