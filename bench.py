@@ -552,6 +552,65 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps(line), flush=True)
 
 
+def run_batch64(args, rank: int, local_rank: int, world: int) -> None:
+    """Opt-in workload (``--workload batch64``): the 64-sequence decode config.  One step = 32 layer-steps
+    over the rank's share of 64 sequences with context lengths U{4096..65536}, K packed at 3.0 bits,
+    bf16 V.  Sequences are dealt to the ranks by longest-processing-time; there is no collective on the
+    step.  Two caches alternate between layer-steps, so every launch reads HBM.  Strong scaling: the
+    64 sequences are fixed, ``value`` = 64 sequences x steps / max-over-ranks time."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, lpt_shards, spectrum_keys, uniform_lengths
+
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    hbm_gbs, _, peak_kind = measured_peaks()
+    n_layers, b_avg = 32, 3.0
+    lens_all = uniform_lengths(64, 4096, 65536, config_seed(2, 0, 0))
+    shard = [lens_all[i] for i in lpt_shards(lens_all, world)[rank]]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(config_seed(2, 0, 0) + 1 + rank)
+    q = torch.randn(len(shard), N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    keys = torch.stack([spectrum_keys(4096, config_seed(2, 0, h)) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys, b_avg)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    caches = []
+    for _ in range(2):
+        cache = paged.PagedKVCache(tables, shard)
+        cache.k_pool.random_(0, 2 ** 31 - 1, generator=gen)
+        cache.v_pool.normal_(generator=gen)
+        cache.lengths = list(shard)
+        cache.seq_lens[:] = torch.tensor(shard, dtype=torch.int32, device=device)
+        caches.append(cache)
+
+    def step(_i: int) -> None:
+        for layer in range(n_layers):
+            caches[layer % 2].decode(q)
+
+    steps, warmup = min(args.steps, 20), max(3, min(args.warmup, 5))
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms, t0, t1 = timed_loop(step, steps, warmup, device, world)
+    sampler.stop()
+    paged.check_status(caches[0].status)
+    per_step_ms = ms / steps
+    bytes_per_step = sum(lens_all) * N_KV_HEADS * (tables.record_bytes + HEAD_DIM * 2) * n_layers
+    gbs = bytes_per_step / (per_step_ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": 64 * steps / (ms * 1e-3), "unit": "tokens/s (one 32-layer decode step per sequence)",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": "decode, 32 layers, 64 sequences with context U{4096..65536} (%d keys in all), 32 q / 8 kv heads, "
+                                   "head_dim 128, K packed at 3.0 bits/coord in 16-token pages, V bf16" % sum(lens_all),
+                       "sharding": "by sequence, longest-processing-time over %d rank(s), no collective" % world,
+                       "rank0_lengths": shard, "l2_policy": "two caches alternate between layer-steps"},
+            "clocks": sampler.summary(t0, t1), "gpu_launches": steps * n_layers,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs * world, "unit": "GB/s",
+                         "frac": gbs / (hbm_gbs * world), "peak_kind": peak_kind, "kernel": "decode_kernel",
+                         "algorithmic_bytes_per_step": bytes_per_step}}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -562,6 +621,9 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
     ap.add_argument("--tokens-per-split", type=int, default=0, help="override the decode split size (0 = library default)")
+    ap.add_argument("--workload", default="headline", choices=["headline", "batch64"],
+                    help="headline: the single-layer context-32768 step (default, what the JSON contract names); "
+                         "batch64: the 32-layer, 64-sequence decode config sharded by sequence over the ranks")
     ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch"],
                     help="profiling aid: run only one of the secondary stages and print its JSON")
     args = ap.parse_args()
@@ -588,7 +650,10 @@ def main() -> None:
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, local_rank, world)
+        if args.workload == "batch64":
+            run_batch64(args, rank, local_rank, world)
+        else:
+            run_ours(args, rank, local_rank, world)
     finally:
         if world > 1:
             import torch.distributed as dist
