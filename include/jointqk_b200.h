@@ -54,6 +54,9 @@ extern "C" {
 /* Bits of the device status word (int32, OR-ed by kernels, never cleared by them). */
 #define JQK_STATUS_BAD_PAGE 1      /* page index outside [0, n_pages) - access skipped */
 #define JQK_STATUS_WAIT_EXPIRED 2  /* a bounded wait on an mbarrier gave up */
+#define JQK_STATUS_BAD_LENGTH 4    /* a length reaches past what the call was sized for (a context longer
+                                      than max_seq_len, a token range past the page-table row): the
+                                      excess is ignored */
 
 /*
  * Per-head device tables built on the host from a fitted compressor
@@ -120,6 +123,22 @@ int32_t jqk_compress_paged(const jqk_head_tables* tables, const void* keys, int3
                            int32_t max_tokens, const int32_t* page_table,
                            int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool,
                            int32_t* status, void* stream);
+
+/*
+ * Values into pages: transposes rows [token][dim] into the V pool's (page, head) blocks (layout at the
+ * top of this file), converting to bf16.  The reference leaves values in the HF cache and appends the
+ * newest token each step (experiments/stage1/toolkit/jointqk_press.py:298-307); this is that append
+ * for the paged pool, used by prefill and by every decode step.
+ *   values      [n_seqs][n_kv_heads][*][d] of dtype with element strides (seq, head, token); d contiguous
+ *   n_tokens, seq_starts, max_tokens, page_table: as in jqk_compress_paged; slots outside
+ *               [seq_starts, seq_starts + n_tokens) of a page keep their contents
+ *   v_pool      bf16 [n_pages][n_kv_heads][d][16]
+ */
+int32_t jqk_store_values_paged(const void* values, int32_t dtype, int64_t seq_stride, int64_t head_stride,
+                               int64_t token_stride, int32_t n_seqs, int32_t n_kv_heads, int32_t d,
+                               const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
+                               const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
+                               void* v_pool, int32_t* status, void* stream);
 
 /*
  * Reconstruction from pages: unpack, centroid lookup, inverse map.  Replaces the second half
@@ -230,6 +249,14 @@ int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const void* q, i
                                  const void* v_pool, void* out, int32_t out_dtype, int32_t* status,
                                  void* stream);
 
+/*
+ * Self-test of the library's bounded device-side wait (no counterpart in the reference): one warp
+ * waits, with the same routine every kernel here uses, on an mbarrier that nothing completes.
+ * After `limit_us` microseconds the wait gives up, the kernel ORs JQK_STATUS_WAIT_EXPIRED into
+ * `status` (device int32) and returns normally; the context stays usable.  limit_us in 1..100000.
+ */
+int32_t jqk_selftest_bounded_wait(int32_t limit_us, int32_t* status, void* stream);
+
 /* tokens_per_split that jqk_decode_attend would choose for this shape (host helper): every
  * sequence is taken to be max_seq_len long. */
 int32_t jqk_decode_default_split(int32_t n_seqs, int32_t n_q_heads, int32_t n_kv_heads,
@@ -252,12 +279,20 @@ int32_t jqk_decode_split_for_lengths(const int32_t* host_seq_lens, int32_t n_seq
  *   q  [n_q_heads][n_tokens][d], k [n_kv_heads][n_tokens][d] of dtype (bf16, f16 or f32); tokens are
  *      d elements apart, heads q_head_stride / k_head_stride elements apart
  *   sq_sum, sk_sum, cqk_sum  float [n_kv_heads][d][d]; any of them may be NULL to skip it
+ *   q_sum, k_sum  float [n_kv_heads][d]: first moments from the same pass, += sum_g sum_t q_g and
+ *      += sum_t k (compute_stats.py:125-126; the value moments sv_sum / sum_v of :124,127 come from a
+ *      call with the values as `k`); NULL to skip
+ *   max_chain_tokens  bound on the length of one fp32 running sum inside the tensor core (0 = the
+ *      default, 2048 tokens).  The tensor core truncates when it accumulates, so the relative error of
+ *      a sum grows with the chain (about 2e-5 at 2048 tokens, 4e-6 at 512); shorter chains are more
+ *      accurate and somewhat slower (more, smaller blocks)
  *   workspace / workspace_bytes: scratch from jqk_moments_workspace_bytes; its first int32 is a
  *      device status word (JQK_STATUS_*), OR-ed by the kernel, zeroed by the caller; may be NULL
  */
 int32_t jqk_moments_accumulate(const void* q, const void* k, int32_t dtype, int64_t n_tokens,
                                int64_t q_head_stride, int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
-                               float* sk_sum, float* cqk_sum, void* workspace,
+                               float* sk_sum, float* cqk_sum, float* q_sum, float* k_sum,
+                               int32_t max_chain_tokens, void* workspace,
                                size_t workspace_bytes, void* stream);
 
 size_t jqk_moments_workspace_bytes(int64_t n_tokens, int32_t n_q_heads, int32_t n_kv_heads,

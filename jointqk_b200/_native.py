@@ -71,11 +71,16 @@ SIGNATURES = {
     "jqk_moments_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32]),
     "jqk_moments_accumulate": (C.c_int32, [
         C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
-        C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+        C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+        C.c_size_t, C.c_void_p]),
+    "jqk_store_values_paged": (C.c_int32, [
+        C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+        C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "jqk_selftest_bounded_wait": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p]),
 }
 
 DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
-STATUS_BAD_PAGE, STATUS_WAIT_EXPIRED = 1, 2
+STATUS_BAD_PAGE, STATUS_WAIT_EXPIRED, STATUS_BAD_LENGTH = 1, 2, 4
 
 
 def _load() -> C.CDLL:

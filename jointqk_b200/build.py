@@ -52,6 +52,18 @@ def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] =
         return LIB_PATH
     obj_dir = PKG_DIR / "build"
     obj_dir.mkdir(exist_ok=True)
+    # one builder at a time: several ranks importing the package on a stale tree must not compile
+    # into the same object files at once
+    import fcntl
+
+    with open(obj_dir / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and not is_stale():
+            return LIB_PATH
+        return _build_locked(obj_dir, verbose, defines)
+
+
+def _build_locked(obj_dir: Path, verbose: bool, defines: tuple[str, ...]) -> Path:
     nvcc = _nvcc()
     objs = []
     procs = []
@@ -69,11 +81,13 @@ def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] =
             print(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
-    link = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+    tmp = LIB_PATH.with_suffix(".so.tmp")
+    link = [nvcc, "-shared", "-o", str(tmp), *objs, "-gencode", "arch=compute_100a,code=sm_100a",
             "-Xcompiler", "-fPIC", "--cudart", "shared"]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
+    tmp.replace(LIB_PATH)          # readers never see a half-written library
     return LIB_PATH
 
 

@@ -19,7 +19,7 @@ from __future__ import annotations
 import torch
 
 from . import paged
-from .allocation import allocate_bits_for_budget
+from .allocation import allocate_bits_for_budget, round_bits_to_integer, water_fill
 from .basis import eigvec_desc, jointqk_basis
 from .codebooks import unit_gaussian_centroids
 from .tables import HeadTables
@@ -61,6 +61,12 @@ class PerCoordCompressor:
         self.inverse_map = inverse_map.float() if inverse_map is not None else None
         self._build_codebooks()
         self._tables: HeadTables | None = None
+        self.allocation = "given"          # how bits_per_coord was obtained (set by fit / the builders)
+
+    @property
+    def packable(self) -> bool:
+        """True when every coordinate carries at most 4 bits, i.e. the packed GPU format can store it."""
+        return int(self.bits_int.max()) <= 4 if self.bits_int.numel() else True
 
     def _build_codebooks(self) -> None:
         """(d, K_max) table: row j = unit Gaussian centroids(b_j) * float(std_j), +inf padded;
@@ -95,6 +101,12 @@ class PerCoordCompressor:
     # -- device tables -------------------------------------------------------------------
     def head_tables(self, device: torch.device | None = None) -> HeadTables:
         dev = _cuda_device(device)
+        if not self.packable:
+            raise ValueError(
+                f"this compressor gives a coordinate {int(self.bits_int.max())} bits; the packed GPU format stores "
+                "0..4 bits per coordinate.  Fit it with max_bits=4 (PerCoordCompressor.fit(..., max_bits=4) or "
+                "build_method_compressor(..., max_bits=4)); that is a different allocation from the reference's "
+                "cap of 8 and costs retrieval quality where outlier channels want more than 4 bits")
         if self._tables is None or self._tables.device != dev:
             self._tables = HeadTables.from_compressors([self], device=dev)
         return self._tables
@@ -102,14 +114,26 @@ class PerCoordCompressor:
     # -- fit -----------------------------------------------------------------------------
     @classmethod
     def fit(cls, sigma_q: torch.Tensor | None, sigma_k: torch.Tensor, b_avg: float, max_bits: int = 4,
-            basis: str = "r_sym", eps: float = 1e-4) -> "PerCoordCompressor":
+            basis: str = "r_sym", eps: float = 1e-4, allocation: str = "capped_tail") -> "PerCoordCompressor":
         """Fit one head from second moments.
 
         ``basis="r_sym"``: joint Q-K eigenbasis, water-fill on ``diag(R^T Sq R) * diag(R^T Sk R)``
         (per_coord_quantization.py:307-316,362).  ``basis="sigma_k"``: eigenbasis of Sigma_K and
         water-fill on its variances alone (no query statistics), as the reference's V-side
-        compressor does.  ``max_bits`` is the cap of the production tail (:367-379; the
-        reference hard-codes 8, the packed format here stores at most 4)."""
+        compressor does.  ``max_bits`` is the cap on bits per coordinate (the reference hard-codes 8,
+        :367; the packed format here stores at most 4).  There are two legitimate ways to honour a
+        cap and they give different integer allocations; ``allocation`` picks one and the fitted
+        object records it in ``.allocation``:
+
+        * ``"capped_tail"`` (default): the production tail -- uncapped water-fill, largest-remainder
+          rounding, clamp at the cap, hand the removed bits to the least-served coordinates
+          (:360-379 with the cap as a parameter);
+        * ``"water_fill_max"``: the cap goes into the continuous water-fill itself
+          (``water_fill(max_bits=cap)``, metric_transform.py:156-213), then the same rounding.
+
+        With outlier channels a cap of 4 costs retrieval quality whichever way it is applied (the
+        outliers want 6-8 bits); ``max_bits=8`` gives the reference's allocation, which the host
+        objects accept but the packed GPU format cannot store."""
         sk = sigma_k.detach().float().cpu()
         d = sk.shape[-1]
         if basis == "r_sym":
@@ -124,8 +148,17 @@ class PerCoordCompressor:
         else:
             raise ValueError(f"Unknown basis '{basis}'")
         var_k = (R.transpose(-1, -2) @ sk @ R).diagonal(dim1=-2, dim2=-1).clamp_min(1e-30)
-        bits = allocate_bits_for_budget((weights * var_k).unsqueeze(0), float(b_avg) * d, int(max_bits)).squeeze(0)
-        return cls(bits, torch.sqrt(var_k.float()), forward_map=R.float(), inverse_map=R.transpose(-1, -2).float())
+        scores = (weights * var_k).unsqueeze(0)
+        if allocation == "capped_tail":
+            bits = allocate_bits_for_budget(scores, float(b_avg) * d, int(max_bits)).squeeze(0)
+        elif allocation == "water_fill_max":
+            cont = water_fill(scores.clamp_min(1e-30), total_bits=float(b_avg) * d, max_bits=float(max_bits))
+            bits = round_bits_to_integer(cont, total_bits=int(float(b_avg) * d)).squeeze(0).clamp_max(int(max_bits))
+        else:
+            raise ValueError(f"Unknown allocation '{allocation}'")
+        comp = cls(bits, torch.sqrt(var_k.float()), forward_map=R.float(), inverse_map=R.transpose(-1, -2).float())
+        comp.allocation = f"{allocation}(max_bits={int(max_bits)})"
+        return comp
 
     # -- compress / decompress / roundtrip ------------------------------------------------
     @torch.no_grad()
@@ -211,9 +244,14 @@ def build_method_compressor(method: str, sigma_q_for_head: torch.Tensor, sigma_k
                             max_bits: int = 8) -> PerCoordCompressor | None:
     """Reference signature (:261-274) for the method on this path, ``r_sym_waterfill``.
 
-    ``max_bits`` defaults to the reference's hard-coded 8; pass 4 for allocations that the
-    packed GPU format can store.  Other method ids belong to ablations outside this build
-    and raise ``ValueError`` like an unknown method does in the reference."""
+    ``max_bits`` defaults to the reference's hard-coded 8 (:367), so the object built here has the
+    reference's bits, standard deviations and codebooks.  The packed GPU format stores at most 4
+    bits per coordinate: a compressor whose allocation goes above that (``.packable`` is False)
+    raises ``ValueError`` on its first ``compress`` / ``roundtrip``, with a message that says to
+    pass ``max_bits=4``.  That is a different allocation with a quality cost where outlier
+    channels want more than 4 bits, so it is never substituted silently.  Other method ids belong
+    to ablations outside this build and raise ``ValueError`` like an unknown method does in the
+    reference."""
     if method == "v3":
         return None
     if method != "r_sym_waterfill":
@@ -224,4 +262,6 @@ def build_method_compressor(method: str, sigma_q_for_head: torch.Tensor, sigma_k
     var_k = (R.transpose(-1, -2) @ sigma_k_for_head.float() @ R).diagonal(dim1=-2, dim2=-1).clamp_min(1e-30)
     weights = (R.transpose(-1, -2) @ sigma_q_for_head.float() @ R).diagonal(dim1=-2, dim2=-1).clamp_min(1e-30)
     bits = allocate_bits_for_budget((weights * var_k).unsqueeze(0), float(b_avg) * head_dim, int(max_bits)).squeeze(0)
-    return PerCoordCompressor(bits, torch.sqrt(var_k.float()), forward_map=R, inverse_map=R.transpose(-1, -2))
+    comp = PerCoordCompressor(bits, torch.sqrt(var_k.float()), forward_map=R, inverse_map=R.transpose(-1, -2))
+    comp.allocation = f"capped_tail(max_bits={int(max_bits)})"
+    return comp

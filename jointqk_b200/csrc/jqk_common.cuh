@@ -79,10 +79,16 @@ __device__ __forceinline__ float load_as_f32(const void* base, int dtype, size_t
   return __half2float(((const __half*)base)[idx]);
 }
 
-// Physical page of logical page `lp` of sequence `s`, or -1 (and a status bit) if the table
-// holds an index outside the pool.  The caller skips the access when -1 is returned.
+// Physical page of logical page `lp` of sequence `s`, or -1 and a status bit: JQK_STATUS_BAD_LENGTH
+// when `lp` lies outside the sequence's page-table row (a length or start the caller did not size
+// the table for; the next row is never read), JQK_STATUS_BAD_PAGE when the table holds an index
+// outside the pool.  The caller skips the access when -1 is returned.
 __device__ __forceinline__ int lookup_page(const int32_t* page_table, int pt_stride, int s, int lp,
                                            int n_pages, int32_t* status) {
+  if ((unsigned)lp >= (unsigned)pt_stride) {
+    if (status) atomicOr(status, JQK_STATUS_BAD_LENGTH);
+    return -1;
+  }
   int p = page_table[(size_t)s * pt_stride + lp];
   if ((unsigned)p >= (unsigned)n_pages) {
     if (status) atomicOr(status, JQK_STATUS_BAD_PAGE);

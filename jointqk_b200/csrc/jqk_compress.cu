@@ -75,6 +75,17 @@ __device__ __forceinline__ void tile_gemm(const float* a_s, const float* __restr
   __syncthreads();
 }
 
+// Tokens of sequence `seq` this call handles: n_tokens[seq], cut to the max_tokens the call (its grid
+// and its output rows) was sized for, with JQK_STATUS_BAD_LENGTH when it had to be cut.
+__device__ __forceinline__ int call_tokens(const PagedArgs& pa, int seq) {
+  int n = pa.n_tokens[seq];
+  if (n > pa.max_tokens) {
+    n = pa.max_tokens;
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && pa.status) atomicOr(pa.status, JQK_STATUS_BAD_LENGTH);
+  }
+  return n;
+}
+
 template <typename KT>
 __global__ void __launch_bounds__(256)
 compress_simt_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t seq_stride,
@@ -85,7 +96,7 @@ compress_simt_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t se
   float* ws = smem + TILE_T * XS_STRIDE;   // [WS_ROWS][128]
   const int head = blockIdx.y, seq = blockIdx.z;
   const int t0 = blockIdx.x * TILE_T;
-  const int n_tok = pa.n_tokens[seq];
+  const int n_tok = call_tokens(pa, seq);
   if (t0 >= n_tok) return;
   const HeadDesc hd = load_desc(tb.desc, head);
   const int d = hd.d;
@@ -152,7 +163,7 @@ decompress_simt_kernel(jqk_head_tables tb, PagedArgs pa, const uint32_t* __restr
   float* ws = smem + TILE_T * XS_STRIDE;
   const int head = blockIdx.y, seq = blockIdx.z;
   const int t0 = blockIdx.x * TILE_T;
-  const int n_tok = pa.n_tokens[seq];
+  const int n_tok = call_tokens(pa, seq);
   if (t0 >= n_tok) return;
   const HeadDesc hd = load_desc(tb.desc, head);
   const int d = hd.d, tid = threadIdx.x;
@@ -221,7 +232,7 @@ unpack_codes_kernel(jqk_head_tables tb, PagedArgs pa, const uint32_t* __restrict
                     uint8_t* __restrict__ codes) {
   const int head = blockIdx.y, seq = blockIdx.z;
   const int t0 = blockIdx.x * TILE_T;
-  const int n_tok = pa.n_tokens[seq];
+  const int n_tok = call_tokens(pa, seq);
   if (t0 >= n_tok) return;
   const HeadDesc hd = load_desc(tb.desc, head);
   const int d = hd.d, tid = threadIdx.x;

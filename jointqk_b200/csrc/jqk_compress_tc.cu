@@ -136,29 +136,14 @@ struct TileWalk {
   }
 };
 
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
 // Bounded wait: false (and the abort flag) after TC_WAIT_NS or when another role gave up.
 __device__ __forceinline__ bool tc_wait(TcSmem& sm, uint64_t* bar, uint32_t parity, int32_t* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = now_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
-      __nanosleep(40);  // waiting roles must not eat the issue slots of the working warps
-    }
-    if (sm.abort) return false;
-    if (now_ns() - t0 > TC_WAIT_NS) {
-      sm.abort = 1;
-      if (status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
-      return false;
-    }
+  if (mbar_wait_timed<40>(bar, parity, TC_WAIT_NS, &sm.abort)) return true;
+  if (!sm.abort) {
+    sm.abort = 1;
+    if (status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
   }
+  return false;
 }
 
 // code = #{l : x >= thr[l]} for sorted thresholds, by binary search over 2^width - 1 entries.
@@ -169,14 +154,6 @@ __device__ __forceinline__ uint32_t search_code(float x, const float* __restrict
   return code;
 }
 
-#ifdef JQK_COMPRESS_PROFILE
-// Development aid: clock totals of the MMA thread (wait full, wait acc_empty, issue) and of epilogue
-// warp 2 (wait acc_full, tmem load, quantise+pack, other).  Not part of the product build.
-__device__ long long g_tc_prof[8];
-#define TCP_MARK(i) do { const long long n__ = clock64(); atomicAdd((unsigned long long*)&g_tc_prof[i], (unsigned long long)(n__ - tp)); tp = n__; } while (0)
-#else
-#define TCP_MARK(i) do {} while (0)
-#endif
 
 // Run by one thread.  `wcb[w]` is the first column of record word w (n_words + 1 entries, shared
 // memory), `units` a scratch of TC_MAX_UNITS int4.
@@ -426,9 +403,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   // align by pointer arithmetic on the __shared__ array (an integer round trip would turn every access into a generic load)
   TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef JQK_COMPRESS_PROFILE
-  const long long t_block0 = clock64();
-#endif
   const int head = blockIdx.y;
   const int f_lo = blockIdx.x * pa.tiles_per_block;
   const int f_hi = min(pa.n_seqs * pa.max_tiles, f_lo + pa.tiles_per_block);
@@ -489,15 +463,10 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       const uint32_t idesc = make_idesc_bf16(128, hd.n_cols, false, false);
       bool ok = tc_wait(sm, &sm.b_full, 0, pa.status);
       int it = 0;
-#ifdef JQK_COMPRESS_PROFILE
-      long long tp = clock64();
-#endif
       for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); ok && w.valid(); w.advance(), ++it) {
         const int s = it % TC_STAGES, a = it & 1;
         if (!tc_wait(sm, &sm.full[s], (it / TC_STAGES) & 1, pa.status)) break;
-        TCP_MARK(0);
         if (it >= 2 && !tc_wait(sm, &sm.acc_empty[a], ((it >> 1) & 1) ^ 1, pa.status)) break;
-        TCP_MARK(1);
         tc_fence_after();
         const uint32_t d_tmem = tmem + a * 128;
         const uint32_t a_base = smem_u32(sm.a[s]);
@@ -513,7 +482,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         }
         umma_commit(&sm.empty[s]);     // the key tile may be overwritten
         umma_commit(&sm.acc_full[a]);  // the accumulator may be read
-        TCP_MARK(2);
       }
     }
   } else {
@@ -544,12 +512,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const uint32_t pre_addr = smem_u32(sm.pre), thr_addr = smem_u32(sm.thr);
     const int wpr = tb.words_per_record;
     int it = 0;
-#ifdef JQK_COMPRESS_PROFILE
-    long long tp = clock64();
-    const bool prof_on = (warp == 2 && lane == 0);
-#undef TCP_MARK
-#define TCP_MARK(i) do { const long long n__ = clock64(); if (prof_on) atomicAdd((unsigned long long*)&g_tc_prof[i], (unsigned long long)(n__ - tp)); tp = n__; } while (0)
-#endif
     int seq_of_start = -1, seq_start = 0;
     for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); w.valid(); w.advance(), ++it) {
       const int a = it & 1, seq = w.seq;
@@ -558,7 +520,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         seq_of_start = seq;
       }
       if (!tc_wait(sm, &sm.acc_full[a], (it >> 1) & 1, pa.status)) break;
-      TCP_MARK(3);
       tc_fence_after();
       const int key = w.t * TC_TILE + row;
       const bool valid = key < w.n_tok;
@@ -578,7 +539,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         for (int s = 0; s < my_steps; ++s) {
           const int2 cur = sm.plan.step[part][s];
           tmem_ld16(t_lane + (cur.x & 255), v);
-          TCP_MARK(4);
           const int c0 = cur.x & 255;
           const float2* ra = sm.crow_a + (cur.x >> 8) * CH;
           const uint2* rm = sm.crow_m + (cur.x >> 8) * CH;
@@ -599,7 +559,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
               if (two) quant16<USE_BUCKETS, TC_CLS_GENERAL, 2>(ra, rm, v, pre_base, thr_base, lo, hi);
               else quant16<USE_BUCKETS, TC_CLS_GENERAL, 1>(ra, rm, v, pre_base, thr_base, lo, hi);
           }
-          TCP_MARK(5);
           if ((cur.y & (1 << 17)) && dst) {
             dst[(cur.y & 255) * JQK_PAGE_TOKENS] = lo;
             if (two) dst[((cur.y & 255) + 1) * JQK_PAGE_TOKENS] = hi;
@@ -634,16 +593,12 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.acc_empty[a]);
-      TCP_MARK(6);
     }
   }
 
   // ---- teardown ----
   tc_fence_before();
   __syncthreads();
-#ifdef JQK_COMPRESS_PROFILE
-  if (tid == 64) atomicAdd((unsigned long long*)&g_tc_prof[7], (unsigned long long)(clock64() - t_block0));
-#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, TC_TMEM_COLS);
@@ -654,16 +609,6 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 
 using namespace jqk;
 
-#ifdef JQK_COMPRESS_PROFILE
-extern "C" int32_t jqk_debug_compress_profile(long long* out8, int32_t reset) {
-  if (cudaMemcpyFromSymbol(out8, g_tc_prof, sizeof(long long) * 8) != cudaSuccess) return 1;
-  if (reset) {
-    long long z[8] = {0};
-    if (cudaMemcpyToSymbol(g_tc_prof, z, sizeof(z)) != cudaSuccess) return 1;
-  }
-  return 0;
-}
-#endif
 
 // Launches the tensor-core kernel when the call fits it (bf16 keys, head_dim 128, 16-byte aligned
 // strides); returns 1 when the caller should use the fp32 CUDA-core kernel instead.

@@ -27,23 +27,12 @@
 //     (atomic ticket), with one memory round trip, no second launch.
 // Every wait on a copy is bounded; an expired wait sets JQK_STATUS_WAIT_EXPIRED and skips the tile.
 #include <limits.h>
-#include <stdlib.h>
 #include <string.h>
 
-#ifdef JQK_DECODE_PROFILE
-// Development aid: per-phase clock totals of thread 0 of every block.  Slots 0-6: table build or
-// copy, wait for K, score, softmax, wait for V, MMA, copy issue; slots 8-14: the phases of the
-// in-block table build.  Not part of the product build.
-__device__ long long g_decode_prof[16];
-#define JQK_TABLES_MARK_INIT long long bt_t__ = clock64();
-#define JQK_TABLES_MARK(i)                                                  \
-  do {                                                                      \
-    const long long now__ = clock64();                                      \
-    if (threadIdx.x == 0) atomicAdd((unsigned long long*)&g_decode_prof[8 + (i)], (unsigned long long)(now__ - bt_t__)); \
-    bt_t__ = now__;                                                         \
-  } while (0)
-#endif
+#include <atomic>
+#include <mutex>
 
+#include "jqk_sm100.cuh"
 #include "jqk_tables.cuh"
 
 namespace jqk {
@@ -194,25 +183,11 @@ __device__ __forceinline__ void bar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void bar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool bar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait (about two seconds of %globaltimer): a copy that never completes ends in a status
-// bit and a skipped tile, not in a hung device.
-__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity) {
-  if (bar_try_wait(bar, parity)) return true;
-  unsigned long long t0, t1;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (bar_try_wait(bar, parity)) return true;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) return false;
-  }
+// Bounded wait (two seconds of %globaltimer by default): a copy that never completes ends in a
+// status bit and a skipped tile, not in a hung device.
+constexpr unsigned long long DEC_WAIT_NS = 2000000000ull;
+__device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, unsigned long long limit_ns = DEC_WAIT_NS) {
+  return sm100::mbar_wait_timed<0>(bar, parity, limit_ns);
 }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -236,16 +211,6 @@ __device__ __forceinline__ int load_page_window(const int32_t* __restrict__ page
   return lookup_page(page_table, pt_stride, seq, lp, n_pages, status);
 }
 
-#ifdef JQK_DECODE_PROFILE
-#define PROF_MARK(i)                                                        \
-  do {                                                                      \
-    const long long now__ = clock64();                                      \
-    if (tid == 0) atomicAdd((unsigned long long*)&g_decode_prof[i], (unsigned long long)(now__ - prof_t)); \
-    prof_t = now__;                                                         \
-  } while (0)
-#else
-#define PROF_MARK(i) do {} while (0)
-#endif
 
 // Builds the lookup tables of every (sequence, kv head, q-head block) once per decode step; the
 // decode blocks of all key splits of that group then only copy them.  One block per group.
@@ -294,7 +259,17 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // kernel on the stream; nothing in memory is read or written before that kernel has completed.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int len = seq_lens[seq];
+  // A context longer than the call was sized for (max_seq_len on the host side fixed the grid and
+  // the workspace) is cut to what the grid covers and flagged; otherwise the ticket below would
+  // never see its last block.
+  int len = seq_lens[seq];
+  {
+    const long long cap = (long long)gridDim.x * tokens_per_split;
+    if (len > cap) {
+      len = (int)cap;
+      if (threadIdx.x == 0 && split == 0 && status) atomicOr(status, JQK_STATUS_BAD_LENGTH);
+    }
+  }
   const int n_splits = (len + tokens_per_split - 1) / tokens_per_split;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
   const int qh0 = head * group + g0;
@@ -366,9 +341,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if (n_my > 1) issue_keys(1, p2, p3);
   }
 
-#ifdef JQK_DECODE_PROFILE
-  long long prof_t = clock64();
-#endif
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
@@ -393,7 +365,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.rec.scale[h];
   }
-  PROF_MARK(0);
   {
     const float f = kLog2e / sqrtf((float)D);
 #pragma unroll
@@ -423,7 +394,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const int page_lo = __shfl_sync(0xffffffffu, pg_cur, (r & 15) << 1);
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
     bool landed = bar_wait(&sm.kfull[warp][r & 1], (r >> 1) & 1);
-    PROF_MARK(1);
 
     // ---- score this lane's key from the staged record words ----
     const int tok = t0 + lane;
@@ -437,7 +407,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) ia[h] = INT_MIN;
     }
-    PROF_MARK(2);
 
     // ---- online softmax: the tile maximum is an integer reduction (scores are scale * integer);
     //      the sum of the weights stays per lane and is reduced once after the last tile ----
@@ -465,9 +434,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       sm.pbuf[warp][1][h][lane] = p_lo;
       l_run[h] = l_run[h] * alpha[h] + (__bfloat162float(p_hi) + __bfloat162float(p_lo));
     }
-    PROF_MARK(3);
     landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
-    PROF_MARK(4);
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
@@ -508,7 +475,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       }
     }
     __syncwarp();  // every lane is done with this stage and with pbuf
-    PROF_MARK(5);
     {  // V of the next tile and K of the tile after it take the buffers this tile has just released
       const int r1 = r + 1, r2 = r + 2;
       const int s1 = ((r1 >> 4) == (r >> 4)) ? pg_cur : pg_next, s2 = ((r2 >> 4) == (r >> 4)) ? pg_cur : pg_next;
@@ -517,7 +483,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       if (r1 < n_my) issue_values(r1, v_lo, v_hi);
       if (r2 < n_my) issue_keys(r2, k_lo, k_hi);
     }
-    PROF_MARK(6);
   }
 
   // ---- combine the warps of this block (each warp reuses its own first stage) ---------------
@@ -568,7 +533,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       if (i == 0) { ws.part_m[pidx] = M; ws.part_l[pidx] = L; }
     }
   }
-  PROF_MARK(7);
   if (single) return;
 
   // ---- the last block of this (sequence, head group) to finish merges the splits ------------
@@ -657,23 +621,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     store_out(out, out_dtype, o0 + 3, L > 0.f ? a4.w / L : 0.f);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
-#ifdef JQK_DECODE_PROFILE
-  if (tid == 0) atomicAdd((unsigned long long*)&g_decode_prof[15], (unsigned long long)(clock64() - prof_t));
-#endif
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-#ifdef JQK_DECODE_PROFILE
-extern "C" int32_t jqk_debug_decode_profile(long long* out16, int32_t reset) {
-  if (cudaMemcpyFromSymbol(out16, g_decode_prof, sizeof(long long) * 16) != cudaSuccess) return 1;
-  if (reset) {
-    long long z[16] = {0};
-    if (cudaMemcpyToSymbol(g_decode_prof, z, sizeof(z)) != cudaSuccess) return 1;
-  }
-  return 0;
-}
-#endif
 
 static int q_blocks_for(int n_q_heads, int n_kv_heads) {
   const int group = n_q_heads / n_kv_heads;
@@ -817,7 +768,6 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   }
   // Programmatic dependent launch: the blocks may become resident while the previous kernel on the
   // stream drains; they wait for it to complete (griddepcontrol.wait) before they touch memory.
-  static const bool use_pdl = getenv("JQK_DISABLE_PDL") == nullptr;
   cudaLaunchAttribute pdl_attr[1];
   pdl_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -827,7 +777,7 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   cfg.dynamicSmemBytes = sizeof(DecodeSmem);
   cfg.stream = st;
   cfg.attrs = pdl_attr;
-  cfg.numAttrs = use_pdl ? 1 : 0;
+  cfg.numAttrs = 1;
 #define JQK_LAUNCH_DECODE(DIM, INB)                                                                              \
   do {                                                                                                           \
     JQK_SMEM_ONCE((decode_kernel<DIM, INB>), sizeof(DecodeSmem), "decode smem attribute");                       \
@@ -877,21 +827,32 @@ static __device__ __align__(256) unsigned char g_decode_scratch[JQK_DECODE_STATI
 
 // Device address of g_decode_scratch on the current device.  In host code the array's name is
 // only a handle for the runtime, not an address a kernel could use, so the address is asked for
-// once per device with that device current and remembered; the tickets at the front of the
-// array are zeroed on `st` at that moment (they are zero when the module loads, and every launch
-// leaves them at zero, but an earlier launch that was cut short must not poison this one).
+// once per device, with that device current, and remembered.  At that moment the ticket area at the
+// front of the array is also zeroed on `st`.  That is belt and braces: the array is zero when the
+// module loads, and every launch that runs to its end leaves the tickets at zero (a context longer
+// than the grid covers is clamped in the kernel, so the last block always turns up).  Only a
+// launch that the driver aborts half-way can leave a ticket behind, and after that the context
+// is unusable anyway.
+// Host threads: the look-up is serialised by a mutex, so two threads that make the first call on a
+// device at the same time get the same address and one clear; what they then launch on different
+// streams still shares the one array and races on the GPU like any other overlapping pair of calls.
 static int32_t decode_static_scratch(void** out, cudaStream_t st) {
-  static void* addr[64] = {nullptr};
+  static std::atomic<void*> addr[64];
+  static std::mutex first_call;
   int dev = 0;
   JQK_CUDA_OK(cudaGetDevice(&dev), "cudaGetDevice");
   if (dev < 0 || dev >= 64) return fail(JQK_E_UNSUPPORTED, "device ordinal %d outside 0..63", dev);
-  if (!addr[dev]) {
-    void* p = nullptr;
-    JQK_CUDA_OK(cudaGetSymbolAddress(&p, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
-    JQK_CUDA_OK(cudaMemsetAsync(p, 0, 65536, st), "clearing the decode tickets");
-    addr[dev] = p;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (!p) {
+    std::lock_guard<std::mutex> guard(first_call);
+    p = addr[dev].load(std::memory_order_acquire);
+    if (!p) {
+      JQK_CUDA_OK(cudaGetSymbolAddress(&p, g_decode_scratch), "cudaGetSymbolAddress(decode scratch)");
+      JQK_CUDA_OK(cudaMemsetAsync(p, 0, 65536, st), "clearing the decode tickets");
+      addr[dev].store(p, std::memory_order_release);
+    }
   }
-  *out = addr[dev];
+  *out = p;
   return 0;
 }
 
@@ -923,4 +884,30 @@ extern "C" int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const
   return jqk_decode_attend(tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
                            page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, scratch,
                            (size_t)JQK_DECODE_STATIC_SCRATCH_BYTES, status, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded wait
+// ---------------------------------------------------------------------------------------
+namespace jqk {
+// One warp waits on an mbarrier that nothing will ever complete, with the library's wait routine
+// and a short limit.  The wait gives up, the status bit is set, the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns, int32_t* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    bar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const bool done = bar_wait(&bar, 0, limit_ns);
+  if (!done && threadIdx.x == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+}
+}  // namespace jqk
+
+extern "C" int32_t jqk_selftest_bounded_wait(int32_t limit_us, int32_t* status, void* stream) {
+  if (!status) return fail(JQK_E_ARG, "null status word");
+  if (limit_us <= 0 || limit_us > 100000) return fail(JQK_E_ARG, "limit_us %d outside 1..100000", limit_us);
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_us * 1000ull, status);
+  JQK_CUDA_OK(cudaGetLastError(), "bounded-wait self-test launch");
+  return 0;
 }

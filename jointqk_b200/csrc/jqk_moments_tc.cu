@@ -17,8 +17,6 @@
 //   warp 0  TMA producer (G + 1 tiles per stage, 2 stages)     warp 1  TMEM owner + MMA issuer
 //   warps 2..5  epilogue (TMEM lane quarter = warp & 3)
 // Every mbarrier wait is bounded in time (see tc_wait in jqk_compress_tc.cu for the policy).
-#include <stdlib.h>
-
 #include "jqk_common.cuh"
 #include "jqk_sm100.cuh"
 
@@ -37,30 +35,22 @@ constexpr unsigned long long MT_WAIT_NS = 2000000000ull;
 
 struct MtSmem {
   uint8_t tile[MT_STAGES][JQK_MAX_GROUP + 1][MT_TILE_BYTES];  // [stage][q_0..q_{G-1}, k]
+  uint8_t ones[2048];  // bf16 1.0 throughout: 16 tokens x 16 columns of ones as an MN-major operand (any swizzle)
   uint64_t full[MT_STAGES], empty[MT_STAGES], done;
   uint32_t tmem_base;
   volatile int abort;
 };
 
 __device__ __forceinline__ bool mt_wait(MtSmem& sm, uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (sm.abort) return false;
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > MT_WAIT_NS) { sm.abort = 1; return false; }
-  }
+  if (mbar_wait_timed<0>(bar, parity, MT_WAIT_NS, &sm.abort)) return true;
+  sm.abort = 1;
+  return false;
 }
 
 __global__ void __launch_bounds__(MT_THREADS, 1)
 moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   long long n_tokens, int chunk, int group, float* __restrict__ sq, float* __restrict__ sk,
-                  float* __restrict__ cqk, int32_t* wait_flag) {
+                  float* __restrict__ cqk, float* __restrict__ q_sum, float* __restrict__ k_sum, int32_t* wait_flag) {
   extern __shared__ uint8_t smem_raw[];
   MtSmem& sm = *reinterpret_cast<MtSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -68,8 +58,12 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   const long long t_begin = (long long)blockIdx.x * chunk;
   const long long t_end = min(n_tokens, t_begin + chunk);
   const int n_tiles = (int)((t_end - t_begin + MT_TOK - 1) / MT_TOK);
-  const bool want_q = (sq != nullptr) || (cqk != nullptr);
+  const bool want_q = (sq != nullptr) || (cqk != nullptr) || (q_sum != nullptr);
 
+  // the all-ones operand of the first-moment products (written before the barrier below; the MMA
+  // reads it through the async proxy, hence the fence)
+  for (int e = tid; e < 2048 / 4; e += MT_THREADS) reinterpret_cast<uint32_t*>(sm.ones)[e] = 0x3F803F80u;
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (tid == 0) {
     for (int s = 0; s < MT_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     mbar_init(&sm.done, 1);
@@ -106,6 +100,11 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(128, 128, true, true);
+      // First moments ride on the same operands: X^T [128 dims x 16 tokens] times a [16 tokens x 16]
+      // block of ones leaves sum_t x_t in each of 16 accumulator columns (columns 384.. for the key,
+      // 400.. for the queries of the group, pooled).  No second pass over the inputs.
+      const uint32_t idesc_sum = make_idesc_bf16(128, 16, true, true);
+      const uint64_t ones_desc = make_smem_desc_sw128(smem_u32(sm.ones), 16, 1024);
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % MT_STAGES;
         if (!mt_wait(sm, &sm.full[s], (t / MT_STAGES) & 1)) break;
@@ -117,11 +116,13 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
           // 16 tokens further along K is 16 rows of 128 bytes; the second 64-dim block is half a tile away
           const uint64_t k_desc = make_smem_desc_sw128(k_base + ks * 2048, MT_TILE_BYTES / 2, 1024);
           if (sk) umma_bf16(tmem + 128, k_desc, k_desc, idesc, !first);
+          if (k_sum) umma_bf16(tmem + 384, k_desc, ones_desc, idesc_sum, !first);
           if (want_q) {
             for (int g = 0; g < group; ++g) {
               const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sm.tile[s][g]) + ks * 2048, MT_TILE_BYTES / 2, 1024);
               if (sq) umma_bf16(tmem + 0, q_desc, q_desc, idesc, !(first && g == 0));
               if (cqk) umma_bf16(tmem + 256, k_desc, q_desc, idesc, !(first && g == 0));  // transposed: lane = k dim
+              if (q_sum) umma_bf16(tmem + 400, q_desc, ones_desc, idesc_sum, !(first && g == 0));
             }
           }
         }
@@ -154,6 +155,16 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)(c0 + i) * 128), "f"(v[i] * scale[m]) : "memory");
         }
       }
+      if (warp - 2 < 4) {  // first moments: lane = dim, every one of the 16 columns holds the same sum
+        float* firsts[2] = {k_sum, q_sum};
+#pragma unroll 1
+        for (int m = 0; m < 2; ++m) {
+          if (!firsts[m]) continue;
+          float v[16];
+          tmem_ld16(t_lane + 384 + 16 * m, v);
+          asm volatile("red.global.add.f32 [%0], %1;" ::"l"(firsts[m] + (size_t)head * 128 + row), "f"(v[0]) : "memory");
+        }
+      }
     }
   }
   if (sm.abort && tid == 0 && wait_flag) atomicOr(wait_flag, JQK_STATUS_WAIT_EXPIRED);
@@ -173,14 +184,16 @@ using namespace jqk;
 // CUDA-core kernel (other dtypes, head sizes, group sizes, unaligned strides, key-only calls).
 int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t n_tokens, int64_t q_head_stride,
                            int64_t k_head_stride, int32_t n_q_heads, int32_t n_kv_heads, int32_t d, float* sq_sum,
-                           float* sk_sum, float* cqk_sum, int32_t* status, cudaStream_t st) {
+                           float* sk_sum, float* cqk_sum, float* q_sum, float* k_sum, int32_t max_chain_tokens,
+                           int32_t* status, cudaStream_t st) {
   const int group = n_q_heads / n_kv_heads;
   if (dtype != JQK_DTYPE_BF16 || d != 128 || group > JQK_MAX_GROUP || n_tokens < MT_TOK || n_tokens > 0x7fffffffLL) return 1;
-  const bool want_q = sq_sum || cqk_sum;
+  const bool want_q = sq_sum || cqk_sum || q_sum;
   if ((uintptr_t)k % 16 || (k_head_stride * 2) % 16) return 1;
   if (want_q && (!q || (uintptr_t)q % 16 || (q_head_stride * 2) % 16)) return 1;
   for (float* o : {sq_sum, sk_sum, cqk_sum})
     if (o && (uintptr_t)o % 16) return 1;
+  if (!sq_sum && !sk_sum && !cqk_sum) return 1;  // first moments alone: not worth a tensor-core launch
   CUtensorMap q_map, k_map;
   char err[256];
   const uint32_t box[3] = {64, MT_TOK, 1};
@@ -196,28 +209,25 @@ int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t 
   } else {
     q_map = k_map;
   }
-  static const int env_chunk = [] {
-    const char* e = getenv("JQK_MOMENTS_CHUNK");  // tuning knob: tokens per block, a multiple of 64
-    const int v = e ? atoi(e) : 0;
-    return (v >= MT_TOK && v % MT_TOK == 0) ? v : 0;
-  }();
   // One block per SM is resident (160 KB of operand stages), so blocks run in waves of 148.  The
-  // chunk is the largest one not above MT_CHUNK (the bound on the length of an fp32 running sum)
-  // whose block count fills whole waves: 131072 tokens x 8 heads -> 1792 tokens, 592 blocks, 4 waves.
-  int chunk = env_chunk ? env_chunk : MT_CHUNK;
-  if (!env_chunk) {
-    for (int waves = 1; waves <= 4096; ++waves) {
-      const long long per_head = (148LL * waves) / n_kv_heads;
-      if (per_head <= 0) continue;
-      long long c = (n_tokens + per_head - 1) / per_head;
-      c = (c + MT_TOK - 1) / MT_TOK * MT_TOK;
-      if (c <= MT_CHUNK) { chunk = (int)(c < MT_TOK ? MT_TOK : c); break; }
-    }
+  // chunk is the largest one not above the chain bound (the length of an fp32 running sum in tensor
+  // memory: MT_CHUNK unless the caller asks for less) whose block count fills whole waves:
+  // 131072 tokens x 8 heads -> 1792 tokens, 592 blocks, 4 waves.
+  int cap = MT_CHUNK;
+  if (max_chain_tokens > 0 && max_chain_tokens < MT_CHUNK) cap = max(MT_TOK, max_chain_tokens / MT_TOK * MT_TOK);
+  int chunk = cap;
+  for (long long waves = 1; waves <= 65536; ++waves) {
+    const long long per_head = (148LL * waves) / n_kv_heads;
+    if (per_head <= 0) continue;
+    long long c = (n_tokens + per_head - 1) / per_head;
+    c = (c + MT_TOK - 1) / MT_TOK * MT_TOK;
+    if (c <= cap) { chunk = (int)(c < MT_TOK ? MT_TOK : c); break; }
   }
   dim3 grid((unsigned)((n_tokens + chunk - 1) / chunk), n_kv_heads);
   const size_t smem = sizeof(MtSmem) + 1024;
   JQK_SMEM_ONCE(moments_tc_kernel, smem, "tensor-core moments smem attribute");
-  moments_tc_kernel<<<grid, MT_THREADS, smem, st>>>(q_map, k_map, (long long)n_tokens, chunk, group, sq_sum, sk_sum, cqk_sum, status);
+  moments_tc_kernel<<<grid, MT_THREADS, smem, st>>>(q_map, k_map, (long long)n_tokens, chunk, group, sq_sum, sk_sum, cqk_sum,
+                                                       q_sum, k_sum, status);
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core moments launch");
   return 0;
 }

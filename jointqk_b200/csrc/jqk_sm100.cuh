@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
 
 namespace jqk {
 namespace sm100 {
@@ -37,14 +38,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity to complete.  Gives up after `max_polls` polls
-// (each try_wait itself blocks for a hardware-defined time slice) and returns false, so a
-// protocol error ends in a status code instead of a hung device.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t max_polls = 4000000u) {
-  for (uint32_t i = 0; i < max_polls; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// The one wait policy of the library.  Polls the phase with the given parity until it completes
+// (true) or `limit_ns` nanoseconds of %globaltimer have passed (false), so a copy or an MMA that
+// never completes ends in a status bit and a kernel that returns, not in a hung device.  NAP_NS > 0
+// sleeps between polls (roles that wait must not eat the issue slots of the working warps);
+// `abort`, when given, is a block-wide flag another role sets when it gave up: the wait then ends
+// early with false.
+template <int NAP_NS>
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, unsigned long long limit_ns,
+                                                volatile int* abort = nullptr) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if (NAP_NS > 0) __nanosleep(NAP_NS);
+    }
+    if (abort && *abort) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
-  return false;
 }
 
 // ---- TMA ---------------------------------------------------------------------------------

@@ -27,11 +27,6 @@ constexpr int TBL_THREADS = 256;  // threads that take part in the query project
 constexpr int TBL_MAX_SHIFT = 7;  // 320 lookups x 2^16 x 2^7 < 2^32: the packed sums stay recoverable
 constexpr int TBL_WORDS = 2 * JQK_MAX_WORDS;  // nibble words, then byte words
 
-#ifndef JQK_TABLES_MARK  // hooks for a development build that times the phases of build_tables
-#define JQK_TABLES_MARK_INIT
-#define JQK_TABLES_MARK(i) do {} while (0)
-#endif
-
 struct TableSmem {
   uint2 lut[JQK_MAX_TABLES * 16];                // 26,624 B: [table][16] x (int16 x 4 heads)
   float part[8][JQK_MAX_COLS][JQK_MAX_GROUP];    // 16,384 B: projection partial sums
@@ -125,7 +120,6 @@ __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& t
 // and the entries are quantised by all threads.
 __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld) {
   const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
-  JQK_TABLES_MARK_INIT
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
   const int lane = tid & 31, warp = tid >> 5, n_warps = nthr >> 5;
   const bool projector = tid < TBL_THREADS;
@@ -138,7 +132,6 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
   if (tid < JQK_MAX_TABLES) reinterpret_cast<int4*>(sm.fields)[tid] = ld.fv;
   if (tid <= JQK_MAX_WORDS) sm.wcb[tid] = ld.wv;
   __syncthreads();
-  JQK_TABLES_MARK(0);
   if (projector) {
     float a[4][JQK_MAX_GROUP];
 #pragma unroll
@@ -161,7 +154,6 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       *reinterpret_cast<float4*>(sm.part[rg][4 * cg + k]) = make_float4(a[k][0], a[k][1], a[k][2], a[k][3]);
   }
   __syncthreads();
-  JQK_TABLES_MARK(1);
   const int n_a_words = hd.n_a_words, n_scan_words = hd.n_a_words + hd.n_c_words;
   // column bounds |q'_c| * max |level| reuse the raw-query staging, which the projection is done with
   float4* colb = reinterpret_cast<float4*>(&sm.qraw[0][0]);  // [JQK_MAX_COLS]
@@ -208,7 +200,6 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     if (lane == 0) *reinterpret_cast<float4*>(sm.wmax[sw]) = make_float4(m.x, m.y, m.z, m.w);
   }
   __syncthreads();
-  JQK_TABLES_MARK(2);
   // ---- every warp derives the per-word shifts from the word maxima (lane w owns scan word w) ----
   float wm[JQK_MAX_GROUP], gm[JQK_MAX_GROUP];
   int fit = TBL_MAX_SHIFT;
@@ -269,7 +260,6 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     }
   }
   __syncthreads();
-  JQK_TABLES_MARK(3);
 }
 
 // Running sums of one record.  An entry word holds a signed 16-bit value in its high half and an

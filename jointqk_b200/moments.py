@@ -41,8 +41,13 @@ def _as_kernel_input(x: torch.Tensor, dev: torch.device) -> torch.Tensor:
 
 
 def accumulate_layer(q: torch.Tensor | None, k: torch.Tensor, sq_sum: torch.Tensor | None,
-                     sk_sum: torch.Tensor | None, cqk_sum: torch.Tensor | None) -> None:
-    """``+=`` the sums of one layer.  q (Hq, T, d) or None, k (Hkv, T, d); outputs fp32 (Hkv, d, d)."""
+                     sk_sum: torch.Tensor | None, cqk_sum: torch.Tensor | None,
+                     q_sum: torch.Tensor | None = None, k_sum: torch.Tensor | None = None,
+                     max_chain_tokens: int = 0) -> None:
+    """``+=`` the sums of one layer in one pass over the inputs.  q (Hq, T, d) or None, k (Hkv, T, d);
+    second moments fp32 (Hkv, d, d); first moments ``q_sum`` (pooled over the group) and ``k_sum``
+    fp32 (Hkv, d).  ``max_chain_tokens`` bounds the length of an fp32 running sum inside the tensor
+    core (0 = library default); shorter is more accurate and slower."""
     dev = k.device
     n_kv, T, d = k.shape
     n_q = q.shape[0] if q is not None else n_kv
@@ -53,12 +58,15 @@ def accumulate_layer(q: torch.Tensor | None, k: torch.Tensor, sq_sum: torch.Tens
     for o in (sq_sum, sk_sum, cqk_sum):
         if o is not None and (o.dtype != torch.float32 or not o.is_contiguous() or tuple(o.shape) != (n_kv, d, d)):
             raise ValueError(f"moment outputs must be contiguous fp32 ({n_kv}, {d}, {d})")
+    for o in (q_sum, k_sum):
+        if o is not None and (o.dtype != torch.float32 or not o.is_contiguous() or tuple(o.shape) != (n_kv, d)):
+            raise ValueError(f"first-moment outputs must be contiguous fp32 ({n_kv}, {d})")
+    p = lambda t: None if t is None else t.data_ptr()
     _native.check(_native.lib.jqk_moments_accumulate(
-        None if q is None else q.data_ptr(), k.data_ptr(), _native.torch_dtype_code(k.dtype), T,
+        p(q), k.data_ptr(), _native.torch_dtype_code(k.dtype), T,
         0 if q is None else q.stride(0), k.stride(0), n_q, n_kv, d,
-        None if sq_sum is None else sq_sum.data_ptr(), None if sk_sum is None else sk_sum.data_ptr(),
-        None if cqk_sum is None else cqk_sum.data_ptr(), _status_word(dev).data_ptr(), 4,
-        torch.cuda.current_stream(dev).cuda_stream))
+        p(sq_sum), p(sk_sum), p(cqk_sum), p(q_sum), p(k_sum), int(max_chain_tokens),
+        _status_word(dev).data_ptr(), 4, torch.cuda.current_stream(dev).cuda_stream))
 
 
 _STATUS: dict = {}
@@ -81,16 +89,18 @@ def check_status(dev: torch.device | None = None) -> None:
             raise RuntimeError("jointqk_b200: a bounded device-side wait expired in the moment kernel")
 
 
-def _second_moment_sum(x: torch.Tensor) -> torch.Tensor:
-    """sum_t x x^T per head for x (..., H, T, d) -> fp32 (..., H, d, d) on x's CUDA device."""
+def _moment_sums(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(sum_t x x^T, sum_t x) per head for x (..., H, T, d) -> fp32 (..., H, d, d), (..., H, d) on
+    x's CUDA device, both from one pass of the kernel."""
     lead = x.shape[:-3]
     H, T, d = x.shape[-3:]
     flat = x.reshape(-1, H, T, d)
     out = torch.zeros((flat.shape[0], H, d, d), dtype=torch.float32, device=x.device)
+    first = torch.zeros((flat.shape[0], H, d), dtype=torch.float32, device=x.device)
     for i in range(flat.shape[0]):
         xi = _as_kernel_input(flat[i], x.device)
-        accumulate_layer(None, xi, None, out[i], None)
-    return out.reshape(lead + (H, d, d))
+        accumulate_layer(None, xi, None, out[i], None, None, first[i])
+    return out.reshape(lead + (H, d, d)), first.reshape(lead + (H, d))
 
 
 def compute_query_moments(query_tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -98,8 +108,9 @@ def compute_query_moments(query_tensor: torch.Tensor) -> tuple[torch.Tensor, tor
     src = query_tensor.device
     q = query_tensor.to(_dev(query_tensor))
     n = q.shape[2]
-    mean = q.float().mean(dim=2)
-    second = _second_moment_sum(q) / n
+    outer, first = _moment_sums(q)
+    check_status(q.device)
+    mean, second = first / n, outer / n
     cov = second - torch.einsum("lhd,lhe->lhde", mean, mean)
     return mean.to(src), cov.to(src), second.to(src)
 
@@ -112,8 +123,7 @@ class QueryMomentsAccumulator:
 
     def update(self, query_tensor: torch.Tensor) -> None:
         q = query_tensor.to(_dev(query_tensor))
-        q_sum = q.float().sum(dim=2)
-        q_outer = _second_moment_sum(q)
+        q_outer, q_sum = _moment_sums(q)
         if self.sum_q is None:
             self.sum_q, self.sum_outer = q_sum, q_outer
         else:
@@ -124,6 +134,7 @@ class QueryMomentsAccumulator:
     def finalize(self) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         if self.sum_q is None or self.sum_outer is None or self.total_count == 0:
             raise RuntimeError("No query statistics were accumulated.")
+        check_status(self.sum_q.device)
         mean = self.sum_q / self.total_count
         second = self.sum_outer / self.total_count
         cov = second - torch.einsum("lhd,lhe->lhde", mean, mean)
@@ -153,6 +164,7 @@ class CrossMomentsAccumulator:
     def finalize(self) -> torch.Tensor:
         if self.sum_qk is None or self.total_count == 0:
             raise RuntimeError("No cross-moment statistics were accumulated.")
+        check_status(self.sum_qk.device)
         return self.sum_qk / self.total_count
 
 
@@ -167,6 +179,7 @@ def compute_grouped_query_second_moment(future_queries: torch.Tensor, num_kv_hea
         qb = _as_kernel_input(future_queries[b], dev)
         kb = qb[:: n_q // num_kv_heads]                      # any (Hkv, T, d) tensor; only sq is requested
         accumulate_layer(qb, kb if kb.stride(-2) == dim else kb.contiguous(), sq, None, None)
+    check_status(dev)
     return (sq / (bsz * (n_q // num_kv_heads) * T)).to(future_queries.device)
 
 
@@ -178,7 +191,8 @@ def compute_moments_from_tensors(q_post: torch.Tensor, k_post: torch.Tensor, v: 
 
     q_post (L, Hq, T_full, d); k_post, v (L, Hkv, T_full, d).  Returns CPU fp32 tensors under
     the reference's keys (``sq_sum``, ``sk_sum``, ``cqk_sum``, ``sv_sum``, ``sum_q``, ``sum_k``,
-    ``sum_v``) plus shape metadata.  ``gpu_budget_bytes`` is accepted for signature
+    ``sum_v``) plus shape metadata.  Second and first moments of a layer come from one pass of the
+    kernel over q and k (and one over v).  ``gpu_budget_bytes`` is accepted for signature
     compatibility; the kernel reads the 16-bit inputs directly, so nothing is promoted."""
     n_layers, n_kv, _, d = (int(x) for x in k_post.shape)
     n_q = int(q_post.shape[1])
@@ -202,13 +216,11 @@ def compute_moments_from_tensors(q_post: torch.Tensor, k_post: torch.Tensor, v: 
         kl = _as_kernel_input(k_post[l, :, :tokens, :], dev)
         if ql.dtype != kl.dtype:
             ql, kl = ql.float(), kl.float()
-        accumulate_layer(ql, kl, sq[l], sk[l], cqk[l])
-        sum_q[l] = ql.float().view(n_kv, group, tokens, d).sum(dim=(1, 2))
-        sum_k[l] = kl.float().sum(dim=1)
+        accumulate_layer(ql, kl, sq[l], sk[l], cqk[l], sum_q[l], sum_k[l])
         if v is not None:
             vl = _as_kernel_input(v[l, :, :tokens, :], dev)
-            accumulate_layer(None, vl, None, sv[l], None)
-            sum_v[l] = vl.float().sum(dim=1)
+            accumulate_layer(None, vl, None, sv[l], None, None, sum_v[l])
+    check_status(dev)
     return {
         "tokens": tokens, "n_layers": n_layers, "n_kv_heads": n_kv, "n_q_heads": n_q, "group": group,
         "head_dim": d, "sq_sum": sq.cpu(), "sk_sum": sk.cpu(), "cqk_sum": cqk.cpu(), "sv_sum": sv.cpu(),
@@ -217,20 +229,38 @@ def compute_moments_from_tensors(q_post: torch.Tensor, k_post: torch.Tensor, v: 
 
 
 class KeyPathMoments:
-    """Streaming Sigma_Q / Sigma_K / C_QK sums for all layers, sharded over ranks by tokens."""
+    """Streaming sums for all layers, sharded over ranks by tokens: Sigma_Q / Sigma_K / C_QK and the
+    first moments of q and k; with ``with_values=True`` also the second and first moments of V
+    (compute_stats.py:124,127), which the V-side compressor is fitted from.
 
-    def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, device) -> None:
+    ``sums`` is one fp32 block ``[L][3 or 4][Hkv][d][d]`` (sq, sk, cqk, then sv) and ``firsts`` one
+    block ``[L][2 or 3][Hkv][d]`` (sum_q pooled over the group, sum_k, then sum_v), so that one
+    all-reduce per block covers a rank's whole contribution."""
+
+    def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, device,
+                 with_values: bool = False, max_chain_tokens: int = 0) -> None:
         if n_q_heads % n_kv_heads != 0:
             raise ValueError(f"GQA mismatch: q_heads={n_q_heads}, kv_heads={n_kv_heads}")
         self.n_layers, self.n_q_heads, self.n_kv_heads, self.d = n_layers, n_q_heads, n_kv_heads, head_dim
         self.group = n_q_heads // n_kv_heads
-        # one block so that a single all-reduce covers everything: [L][3][Hkv][d][d]
-        self.sums = torch.zeros((n_layers, 3, n_kv_heads, head_dim, head_dim), dtype=torch.float32, device=device)
+        self.with_values = bool(with_values)
+        self.max_chain_tokens = int(max_chain_tokens)
+        n_mat = 4 if with_values else 3
+        self.sums = torch.zeros((n_layers, n_mat, n_kv_heads, head_dim, head_dim), dtype=torch.float32, device=device)
+        self.firsts = torch.zeros((n_layers, n_mat - 1, n_kv_heads, head_dim), dtype=torch.float32, device=device)
         self.tokens = torch.zeros(n_layers, dtype=torch.float64, device=device)
 
-    def update(self, layer: int, q: torch.Tensor, k: torch.Tensor) -> None:
-        """q (Hq, T, d), k (Hkv, T, d) of one layer's chunk of tokens."""
-        accumulate_layer(q, k, self.sums[layer, 0], self.sums[layer, 1], self.sums[layer, 2])
+    def update(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor | None = None) -> None:
+        """q (Hq, T, d), k (Hkv, T, d) and, when values are tracked, v (Hkv, T, d) of one layer's
+        chunk of tokens."""
+        if self.sums.device.type != "cuda":
+            raise RuntimeError("jointqk_b200: the moment kernels have no CPU implementation")
+        accumulate_layer(q, k, self.sums[layer, 0], self.sums[layer, 1], self.sums[layer, 2],
+                         self.firsts[layer, 0], self.firsts[layer, 1], self.max_chain_tokens)
+        if self.with_values:
+            if v is None:
+                raise ValueError("this accumulator tracks values: pass v")
+            accumulate_layer(None, v, None, self.sums[layer, 3], None, None, self.firsts[layer, 2], self.max_chain_tokens)
         self.tokens[layer] += k.shape[1]
 
     def all_reduce(self, group=None) -> None:
@@ -239,15 +269,64 @@ class KeyPathMoments:
 
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
             dist.all_reduce(self.sums, op=dist.ReduceOp.SUM, group=group)
+            dist.all_reduce(self.firsts, op=dist.ReduceOp.SUM, group=group)
             dist.all_reduce(self.tokens, op=dist.ReduceOp.SUM, group=group)
 
     def finalize(self) -> dict[str, torch.Tensor]:
-        tok = self.tokens.clamp_min(1).float().view(-1, 1, 1, 1)
+        """Divide once (compute_stats.py:235-244 / analyze_bases.py:264-279): second moments, means
+        and covariances per (layer, kv head)."""
+        if self.sums.device.type == "cuda":
+            check_status(self.sums.device)
         if float(self.tokens.min()) <= 0:
             raise RuntimeError("no calibration tokens accumulated")
-        return {
-            "sigma_q": self.sums[:, 0] / (self.group * tok),
-            "sigma_k": self.sums[:, 1] / tok,
-            "cqk": self.sums[:, 2] / tok,
+        tok = self.tokens.clamp_min(1).float()
+        t4, t3 = tok.view(-1, 1, 1, 1), tok.view(-1, 1, 1)
+        outer = lambda m: torch.einsum("lhd,lhe->lhde", m, m)
+        out = {
+            "sigma_q": self.sums[:, 0] / (self.group * t4),
+            "sigma_k": self.sums[:, 1] / t4,
+            "cqk": self.sums[:, 2] / t4,
+            "mu_q": self.firsts[:, 0] / (self.group * t3),
+            "mu_k": self.firsts[:, 1] / t3,
             "total_tokens": self.tokens.clone(),
         }
+        out["cov_q"] = out["sigma_q"] - outer(out["mu_q"])
+        out["cov_k"] = out["sigma_k"] - outer(out["mu_k"])
+        if self.with_values:
+            out["sigma_v"] = self.sums[:, 3] / t4
+            out["mu_v"] = self.firsts[:, 2] / t3
+            out["cov_v"] = out["sigma_v"] - outer(out["mu_v"])
+        return out
+
+    def calibration_artifacts(self, eps: float = 1e-4, source: str = "jointqk_b200") -> tuple[dict, dict | None]:
+        """The two dictionaries the reference writes with ``torch.save`` as ``cca_stats_*.pt`` and
+        ``v_stats_*.pt`` (scripts/build_calibration_artifacts_from_pool.py:108-127,148-163), on the
+        CPU, so that its press (jointqk_press.py:124-233) can load a calibration made here.  The
+        CCA-only fields the press constructor touches but ``r_sym_waterfill`` never reads are the
+        same placeholders the reference writes.  The second dictionary is None when values were not
+        tracked."""
+        import time
+
+        from .basis import jointqk_basis
+
+        fin = {k: v.float().cpu() for k, v in self.finalize().items()}
+        L, H, d = self.n_layers, self.n_kv_heads, self.d
+        if len({int(t) for t in self.tokens.tolist()}) != 1:
+            raise RuntimeError("layers saw different token counts")
+        total = int(self.tokens[0].item())
+        eye = torch.eye(d, dtype=torch.float32).expand(L, H, d, d).contiguous()
+        zeros_diag = torch.zeros(L, H, d, dtype=torch.float32)
+        cca = {
+            "sigma_q": fin["sigma_q"], "sigma_k": fin["sigma_k"],
+            "R_sym": jointqk_basis(fin["sigma_q"], fin["sigma_k"], eps=float(eps)).float(),
+            "cqk": torch.zeros_like(fin["sigma_q"]), "rho": zeros_diag, "P_K": eye, "P_K_inv": eye, "P_Q": eye,
+            "mq_eigvals": zeros_diag, "mq_eigvecs": eye, "V_h": eye,
+            "n_layers": L, "n_kv_heads": H, "head_dim": d, "total_prefill_tokens": total,
+            "calibration_source": source, "calibration_date": time.strftime("%Y-%m-%d"),
+        }
+        v_art = None
+        if self.with_values:
+            v_art = {"cov_v": fin["cov_v"], "mu_v": fin["mu_v"], "sigma_v": fin["sigma_v"],
+                     "metadata": {"n_layers": L, "n_kv_heads": H, "head_dim": d, "n_examples": None,
+                                  "total_token_count": total, "prefill_only": True, "bundle": source, "version": 2}}
+        return cca, v_art

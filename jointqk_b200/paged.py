@@ -99,12 +99,32 @@ def sequential_page_table(lengths: list[int], device, first_page: int = 0) -> tu
 
 
 def check_status(status: torch.Tensor) -> None:
-    """Raise if a kernel flagged a bad page index or an expired wait (synchronises)."""
+    """Raise if a kernel flagged a bad page index, an over-long length or an expired wait
+    (synchronises)."""
     v = int(status.item())
     if v & _native.STATUS_BAD_PAGE:
         raise RuntimeError("jointqk_b200: page table holds an index outside the pool")
+    if v & _native.STATUS_BAD_LENGTH:
+        raise RuntimeError("jointqk_b200: a sequence length reaches past what the call was sized for")
     if v & _native.STATUS_WAIT_EXPIRED:
         raise RuntimeError("jointqk_b200: a bounded device-side wait expired")
+
+
+def store_values_into(values: torch.Tensor, n_tokens: torch.Tensor, max_tokens: int, page_table: torch.Tensor,
+                      v_pool: torch.Tensor, status: torch.Tensor, seq_starts: torch.Tensor | None = None) -> None:
+    """values (n_seqs, H, S, d) with d contiguous -> bf16 V pages (one kernel pass, no torch indexing)."""
+    if values.dim() != 4 or values.stride(3) != 1:
+        values = values.contiguous()
+    if values.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+        values = values.float()
+    n_seqs, H, _, d = values.shape
+    if v_pool.dtype != torch.bfloat16 or v_pool.shape[1] != H or v_pool.shape[2] != d * PAGE_TOKENS:
+        raise ValueError(f"v_pool must be bf16 (n_pages, {H}, {d * PAGE_TOKENS})")
+    _native.check(_native.lib.jqk_store_values_paged(
+        values.data_ptr(), _native.torch_dtype_code(values.dtype), values.stride(0), values.stride(1),
+        values.stride(2), n_seqs, H, d, n_tokens.data_ptr(), _ptr(seq_starts), int(max_tokens),
+        page_table.data_ptr(), page_table.stride(0), int(v_pool.shape[0]), v_pool.data_ptr(),
+        status.data_ptr(), _stream_ptr(v_pool.device)))
 
 
 def compress_into(tables: HeadTables, keys: torch.Tensor, n_tokens: torch.Tensor, max_tokens: int,
@@ -188,7 +208,7 @@ class DecodeWorkspace:
 
     def __init__(self, n_seqs: int, n_q_heads: int, n_kv_heads: int, max_splits: int, device) -> None:
         nbytes = int(_native.lib.jqk_decode_workspace_bytes(n_seqs, n_q_heads, n_kv_heads, max_splits))
-        self.max_splits = max_splits
+        self.max_splits, self.n_seqs, self.n_q_heads = max_splits, n_seqs, n_q_heads
         self.buf = torch.zeros(max(nbytes, 16), dtype=torch.uint8, device=device)
 
 
@@ -224,61 +244,177 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
     return out
 
 
+class PagePool:
+    """Physical pages of one layer (packed K and bf16 V side by side, one index space) with a free
+    list.  ``take`` hands out pages; when the list runs dry the pool grows: larger tensors are
+    allocated, the old contents copied over and the old tensors dropped, so page indices stay valid
+    and only the base pointers change (``generation`` counts the moves)."""
+
+    def __init__(self, tables: HeadTables, n_pages: int, growth: float = 1.5) -> None:
+        self.tables = tables
+        self.growth = float(growth)
+        n_pages = max(1, int(n_pages))
+        self.k_pool = alloc_k_pool(tables, n_pages)
+        self.v_pool = alloc_v_pool(tables, n_pages)
+        self._free = list(range(n_pages - 1, -1, -1))   # pop() hands out ascending indices
+        self.generation = 0
+
+    @property
+    def n_pages(self) -> int:
+        return int(self.k_pool.shape[0])
+
+    @property
+    def n_free(self) -> int:
+        return len(self._free)
+
+    def grow(self, n_pages: int) -> None:
+        old = self.n_pages
+        if n_pages <= old:
+            return
+        k_new, v_new = alloc_k_pool(self.tables, n_pages), alloc_v_pool(self.tables, n_pages)
+        k_new[:old].copy_(self.k_pool)
+        v_new[:old].copy_(self.v_pool)
+        self.k_pool, self.v_pool = k_new, v_new
+        self._free = list(range(n_pages - 1, old - 1, -1)) + self._free
+        self.generation += 1
+
+    def take(self, n: int) -> list[int]:
+        if n > len(self._free):
+            self.grow(max(int(self.n_pages * self.growth) + 1, self.n_pages + n - len(self._free)))
+        return [self._free.pop() for _ in range(n)]
+
+    def give_back(self, pages: list[int]) -> None:
+        self._free.extend(sorted((int(p) for p in pages), reverse=True))
+
+
 class PagedKVCache:
     """Packed-K / bf16-V paged cache of one layer for a batch of sequences.
 
-    ``prefill`` compresses keys into pages and scatters values; ``decode`` runs the fused
-    attention kernel.  Pages are assigned sequentially at construction from the maximum
-    lengths given, which is all the synthetic workloads need.
+    ``prefill`` (and ``append``, the same call for the newest tokens of a generate loop;
+    jointqk_press.py:298-304 compresses only those each step) allocates pages on demand from a
+    ``PagePool``, compresses the keys into them and stores the values with one kernel pass each;
+    ``decode`` runs the fused attention kernel; ``release`` returns a sequence's pages to the pool.
+    ``max_lengths`` reserves pages up front (sequence after sequence, which is all the fixed-size
+    workloads need); with ``n_seqs`` alone the cache starts empty and grows, and so does the pool.
     """
 
-    def __init__(self, tables: HeadTables, max_lengths: list[int]) -> None:
+    def __init__(self, tables: HeadTables, max_lengths: list[int] | None = None, *, n_seqs: int | None = None,
+                 pool: PagePool | None = None, initial_pages: int = 0) -> None:
         self.tables = tables
         dev = tables.device
-        self.page_table, used = sequential_page_table(max_lengths, dev)
-        self.n_pages = max(1, used)
-        self.k_pool = alloc_k_pool(tables, self.n_pages)
-        self.v_pool = alloc_v_pool(tables, self.n_pages)
-        self.lengths = [0] * len(max_lengths)
-        self.capacity = [pages_for(n) * PAGE_TOKENS for n in max_lengths]
-        self.seq_lens = torch.zeros(max(1, len(max_lengths)), dtype=torch.int32, device=dev)
+        if max_lengths is None:
+            if n_seqs is None:
+                raise ValueError("give max_lengths (reserve) or n_seqs (grow on demand)")
+            max_lengths = [0] * int(n_seqs)
+        n = len(max_lengths)
+        counts = [pages_for(x) for x in max_lengths]
+        self.pool = pool if pool is not None else PagePool(tables, max(1, sum(counts), int(initial_pages)))
+        self._pages: list[list[int]] = [self.pool.take(c) for c in counts]
+        width = max(1, max(counts) if counts else 1)
+        table = torch.zeros((max(1, n), width), dtype=torch.int32)
+        for s, pg in enumerate(self._pages):
+            table[s, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+        self.page_table = table.to(dev)
+        self.lengths = [0] * n
+        self.seq_lens = torch.zeros(max(1, n), dtype=torch.int32, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._ws: DecodeWorkspace | None = None
         self._host_step: dict | None = None
         self._host_call: dict | None = None
 
+    # the pools belong to the PagePool (they move when it grows)
+    @property
+    def k_pool(self) -> torch.Tensor:
+        return self.pool.k_pool
+
+    @property
+    def v_pool(self) -> torch.Tensor:
+        return self.pool.v_pool
+
+    @property
+    def n_pages(self) -> int:
+        return self.pool.n_pages
+
+    @property
+    def capacity(self) -> list[int]:
+        return [len(pg) * PAGE_TOKENS for pg in self._pages]
+
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        """Make sure sequence ``seq`` owns pages for ``n_tokens`` tokens in all."""
+        need = pages_for(n_tokens) - len(self._pages[seq])
+        if need <= 0:
+            return
+        have = len(self._pages[seq])
+        new = self.pool.take(need)
+        self._pages[seq].extend(new)
+        if have + need > self.page_table.shape[1]:        # widen the table (amortised doubling)
+            width = max(have + need, 2 * self.page_table.shape[1])
+            wider = torch.zeros((self.page_table.shape[0], width), dtype=torch.int32, device=self.page_table.device)
+            wider[:, : self.page_table.shape[1]] = self.page_table
+            self.page_table = wider
+            self._host_step = self._host_call = None
+        self.page_table[seq, have:have + need] = torch.tensor(new, dtype=torch.int32, device=self.page_table.device)
+
+    def release(self, seq: int) -> None:
+        """Forget sequence ``seq`` and return its pages to the pool."""
+        self.pool.give_back(self._pages[seq])
+        self._pages[seq] = []
+        self.lengths[seq] = 0
+        self.seq_lens[seq] = 0
+
     def prefill(self, keys: torch.Tensor, values: torch.Tensor, lengths: list[int] | None = None) -> None:
-        """keys/values (n_seqs, H, S, d).  Appends ``lengths[s]`` tokens to every sequence."""
+        """keys/values (n_seqs, H, S, d).  Appends ``lengths[s]`` tokens to every sequence: one
+        compress launch for the keys, one store launch for the values."""
         n_seqs, H, S, d = keys.shape
         lengths = [S] * n_seqs if lengths is None else [int(x) for x in lengths]
         dev = self.tables.device
         for s, n in enumerate(lengths):
-            if self.lengths[s] + n > self.capacity[s]:
-                raise ValueError(f"sequence {s}: {self.lengths[s]} + {n} tokens exceed its {self.capacity[s]} slots")
-        starts = torch.tensor(self.lengths, dtype=torch.int32, device=dev)
+            self.reserve(s, self.lengths[s] + n)
+        starts = torch.tensor(self.lengths[:n_seqs], dtype=torch.int32, device=dev)
         n_tok = torch.tensor(lengths, dtype=torch.int32, device=dev)
         if max(lengths) > 0:
             compress_into(self.tables, keys, n_tok, max(lengths), self.page_table, self.k_pool, self.status, starts)
-        for s, n in enumerate(lengths):                      # value scatter: plain torch indexing
-            if n == 0:
-                continue
-            pos = torch.arange(self.lengths[s], self.lengths[s] + n, device=dev)
-            pages = self.page_table[s, pos // PAGE_TOKENS].long()
-            offs = v_slot_offsets(d, dev)[pos % PAGE_TOKENS]                     # (n, d)
-            self.v_pool[pages[:, None], :, offs] = values[s, :, :n, :].to(torch.bfloat16).permute(1, 2, 0)
+            store_values_into(values.to(dev), n_tok, max(lengths), self.page_table, self.v_pool, self.status, starts)
+        for s, n in enumerate(lengths):
             self.lengths[s] += n
         self.seq_lens[: len(self.lengths)] = torch.tensor(self.lengths, dtype=torch.int32, device=dev)
+
+    def append(self, keys: torch.Tensor, values: torch.Tensor) -> None:
+        """One new token for every sequence of the cache: keys/values (n_seqs, H, 1, d).  The step of
+        a generate loop: nothing is copied from the host (the current lengths on the device are the
+        destinations, and they are advanced on the device), pages are taken from the pool only when a
+        sequence crosses a page boundary."""
+        n = len(self.lengths)
+        if keys.shape[0] != n or keys.shape[2] != 1:
+            return self.prefill(keys, values)
+        for s in range(n):
+            self.reserve(s, self.lengths[s] + 1)
+        if getattr(self, "_ones", None) is None or self._ones.numel() != n:
+            self._ones = torch.ones(n, dtype=torch.int32, device=self.tables.device)
+        compress_into(self.tables, keys, self._ones, 1, self.page_table, self.k_pool, self.status, self.seq_lens)
+        store_values_into(values, self._ones, 1, self.page_table, self.v_pool, self.status, self.seq_lens)
+        self.seq_lens[:n] += 1
+        for s in range(n):
+            self.lengths[s] += 1
+
+    def _workspace(self, n_seqs: int, n_q_heads: int, max_splits: int) -> DecodeWorkspace:
+        ws = self._ws
+        if ws is None or ws.max_splits < max_splits or ws.n_seqs < n_seqs or ws.n_q_heads < n_q_heads:
+            ws = self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, self.tables.device)
+        return ws
 
     def decode(self, q: torch.Tensor, out_dtype: torch.dtype = torch.float32, tokens_per_split: int = 0) -> torch.Tensor:
         n_seqs, n_q_heads, _ = q.shape
         max_len = max(self.lengths) if self.lengths else 0
         tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
-        max_splits = max(1, -(-max_len // tps))
-        if self._ws is None or self._ws.max_splits < max_splits:
-            self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, self.tables.device)
+        ws = self._workspace(n_seqs, n_q_heads, max(1, -(-max_len // tps)))
         out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
         return decode_attend(self.tables, q, self.seq_lens, max_len, self.page_table, self.k_pool, self.v_pool,
-                             out, self._ws, self.status, tps)
+                             out, ws, self.status, tps)
+
+    def _host_state_stale(self, hs: dict | None, key: tuple) -> bool:
+        return (hs is None or hs["key"] != key or hs["lengths"] != self.lengths
+                or hs["generation"] != self.pool.generation or hs["table_ptr"] != self.page_table.data_ptr())
 
     def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0, use_graph: bool = True) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
@@ -288,8 +424,10 @@ class PagedKVCache:
         captured once as a CUDA graph (per batch shape, context length and split); every call stages
         the query in pinned memory, replays the graph and waits for it, so the host pays one graph
         launch and one synchronisation per step instead of three enqueues.  The cache must not grow
-        between capture and replay: a call after ``prefill`` captures again.  ``use_graph=False`` makes
-        one call of ``jqk_decode_attend_host`` instead (no capture; three enqueues and a wait)."""
+        between capture and replay: a call after ``prefill`` captures again.  The captured graph keeps
+        its own reference to the split workspace it was recorded with, so a later ``decode`` that needs
+        a larger workspace does not pull that memory from under it.  ``use_graph=False`` makes one
+        call of ``jqk_decode_attend_host`` instead (no capture; three enqueues and a wait)."""
         if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3 or not q_host.is_contiguous():
             raise ValueError("q_host must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor in host memory")
         if not use_graph:
@@ -298,13 +436,13 @@ class PagedKVCache:
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_step
         key = (n_seqs, n_q_heads, d, int(tokens_per_split))
-        if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
+        if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
-            max_splits = max(1, -(-max_len // tps))
-            if self._ws is None or self._ws.max_splits < max_splits:
-                self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
-            hs = {"key": key, "lengths": list(self.lengths),
+            hs = {"key": key, "lengths": list(self.lengths), "generation": self.pool.generation,
+                  "table_ptr": self.page_table.data_ptr(),
+                  "ws": self._workspace(n_seqs, n_q_heads, max(1, -(-max_len // tps))),
+                  "pools": (self.k_pool, self.v_pool, self.page_table),
                   "q_pin": torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16).pin_memory(),
                   "out_pin": torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
                   "q_dev": torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
@@ -313,8 +451,8 @@ class PagedKVCache:
 
             def enqueue() -> None:
                 hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
-                decode_attend(self.tables, hs["q_dev"], self.seq_lens, max_len, self.page_table, self.k_pool,
-                              self.v_pool, hs["out_dev"], self._ws, self.status, tps)
+                decode_attend(self.tables, hs["q_dev"], self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
+                              hs["pools"][1], hs["out_dev"], hs["ws"], self.status, tps)
                 hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
 
             hs["q_pin"].copy_(q_host)
@@ -337,19 +475,20 @@ class PagedKVCache:
 
         One call of ``jqk_decode_attend_host``: the query is staged in pinned memory and copied to
         the device, the step runs, the result is copied back and the stream is synchronised, so the
-        host pays one foreign-function call per step.  The staging buffers are kept per batch shape."""
+        host pays one foreign-function call per step.  The staging buffers are kept per batch shape,
+        together with the workspace and pools whose addresses the cached argument list holds."""
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_call
         key = (n_seqs, n_q_heads, d, int(tokens_per_split))
-        if hs is None or hs["key"] != key or hs["lengths"] != self.lengths:
+        if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
-            max_splits = max(1, -(-max_len // tps))
-            if self._ws is None or self._ws.max_splits < max_splits:
-                self._ws = DecodeWorkspace(n_seqs, n_q_heads, self.tables.n_heads, max_splits, dev)
+            ws = self._workspace(n_seqs, n_q_heads, max(1, -(-max_len // tps)))
             keep = hs if hs is not None and hs["key"] == key else None
-            hs = {"key": key, "lengths": list(self.lengths), "max_len": max_len, "tps": tps,
+            hs = {"key": key, "lengths": list(self.lengths), "max_len": max_len, "tps": tps, "ws": ws,
+                  "generation": self.pool.generation, "table_ptr": self.page_table.data_ptr(),
+                  "pools": (self.k_pool, self.v_pool, self.page_table),
                   "q_pin": keep["q_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16).pin_memory(),
                   "out_pin": keep["out_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
                   "q_dev": keep["q_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
@@ -358,7 +497,7 @@ class PagedKVCache:
                           self.seq_lens.data_ptr(), int(max_len), int(tps), self.page_table.data_ptr(),
                           self.page_table.stride(0), int(self.k_pool.shape[0]), self.k_pool.data_ptr(),
                           self.v_pool.data_ptr(), hs["out_dev"].data_ptr(), hs["out_pin"].data_ptr(),
-                          _native.DTYPE_F32, self._ws.buf.data_ptr(), self._ws.buf.numel(), self.status.data_ptr())
+                          _native.DTYPE_F32, ws.buf.data_ptr(), ws.buf.numel(), self.status.data_ptr())
             self._host_call = hs
         a = hs["args"]
         _native.check(_native.lib.jqk_decode_attend_host(a[0], q_host.data_ptr(), *a[1:], _stream_ptr(dev)))

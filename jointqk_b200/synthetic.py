@@ -13,7 +13,6 @@ import math
 import torch
 
 from .codebooks import generate_rotation_matrix
-from .compressor import PerCoordCompressor
 
 HEAD_DIM = 128
 
@@ -56,6 +55,8 @@ def second_moment(x: torch.Tensor) -> torch.Tensor:
 def fit_sigma_k_heads(keys: torch.Tensor, b_avg: float, max_bits: int = 4, eps: float = 1e-4):
     """keys (H, N, d) -> (compressors, sigma_k (H, d, d)): Sigma_K eigenbasis and water-fill on its
     variances, the fit the parity config prescribes."""
+    from .compressor import PerCoordCompressor   # binds the CUDA library; the generators above do not
+
     sig = torch.stack([second_moment(keys[h].float()) for h in range(keys.shape[0])])
     comps = [PerCoordCompressor.fit(None, sig[h], b_avg, max_bits=max_bits, basis="sigma_k", eps=eps)
              for h in range(keys.shape[0])]

@@ -83,6 +83,116 @@ def test_calibration_shape_against_fp64(tokens):
             assert e_gpu <= 6e-5
 
 
+def test_first_moments_and_values_from_the_same_pass():
+    """sum_q (pooled over the group), sum_k and the value moments come out of the contraction kernel
+    itself: tensor-core path (bf16, 4096 tokens) and CUDA-core path (fp32, 50 tokens)."""
+    for tokens, dtype in ((4096 + 64, torch.bfloat16), (50, torch.float32)):
+        q, k = correlated_qk(tokens, 32, 8, seed=41, device="cuda", dtype=dtype)
+        v = (k * 0.5 + 0.25).to(dtype)                      # a non-zero mean
+        acc = KeyPathMoments(1, 32, 8, 128, device="cuda", with_values=True)
+        acc.update(0, q, k, v)
+        qd, kd, vd = q.double(), k.double(), v.double()
+        want = {"sum_q": qd.view(8, 4, tokens, 128).sum((1, 2)), "sum_k": kd.sum(1), "sum_v": vd.sum(1),
+                "sv": torch.einsum("hsd,hse->hde", vd, vd)}
+        scale = {"sum_q": qd.abs().view(8, 4, tokens, 128).sum((1, 2)), "sum_k": kd.abs().sum(1), "sum_v": vd.abs().sum(1)}
+        got = {"sum_q": acc.firsts[0, 0], "sum_k": acc.firsts[0, 1], "sum_v": acc.firsts[0, 2], "sv": acc.sums[0, 3]}
+        for name in ("sum_q", "sum_k", "sum_v"):
+            err = float(((got[name].double() - want[name]).abs() / scale[name]).max())
+            print(f"{name} tokens={tokens}: max error / sum|x| = {err:.2e}")
+            assert err <= 3e-5
+        assert _fro(got["sv"], want["sv"]) <= 6e-5
+        fin = acc.finalize()
+        mu_v = want["sum_v"] / tokens
+        cov_v = want["sv"] / tokens - torch.einsum("hd,he->hde", mu_v, mu_v)
+        assert _fro(fin["cov_v"][0], cov_v) <= 2e-4 and _fro(fin["mu_v"][0], mu_v) <= 1e-4
+
+
+def test_calibration_artifacts_follow_the_reference_schema():
+    """The dictionaries written for the reference's press hold the keys its loader reads, on the CPU,
+    with R_sym equal to the joint eigenbasis of the pooled moments."""
+    q, k = correlated_qk(2048, 8, 2, seed=43, device="cuda")
+    acc = KeyPathMoments(2, 8, 2, 128, device="cuda", with_values=True)
+    for layer in range(2):
+        acc.update(layer, q, k, k)
+    cca, vst = acc.calibration_artifacts(eps=1e-4, source="unit test")
+    for name in ("sigma_q", "sigma_k", "R_sym", "cqk", "rho", "P_K", "P_K_inv", "P_Q", "mq_eigvals", "mq_eigvecs", "V_h"):
+        assert cca[name].device.type == "cpu" and cca[name].dtype == torch.float32
+    assert tuple(cca["R_sym"].shape) == (2, 2, 128, 128) and cca["total_prefill_tokens"] == 2048
+    assert (cca["n_layers"], cca["n_kv_heads"], cca["head_dim"]) == (2, 2, 128)
+    R = jq.jointqk_basis(cca["sigma_q"], cca["sigma_k"], 1e-4)
+    assert torch.equal(R, cca["R_sym"])
+    assert set(vst) == {"cov_v", "mu_v", "sigma_v", "metadata"} and vst["metadata"]["version"] == 2
+    torch.testing.assert_close(vst["cov_v"] + torch.einsum("lhd,lhe->lhde", vst["mu_v"], vst["mu_v"]), vst["sigma_v"],
+                               rtol=1e-5, atol=1e-6)
+    # the K-side builder consumes them the way the reference's press does (jointqk_press.py:152-174)
+    comp = jq.build_method_compressor("r_sym_waterfill", cca["sigma_q"][0, 1], cca["sigma_k"][0, 1], b_avg=2.0,
+                                      head_dim=128, R_sym=cca["R_sym"][0, 1], max_bits=4)
+    assert comp.packable and int(comp.bits_int.sum()) == 256
+
+
+def test_shorter_chains_are_more_accurate():
+    """max_chain_tokens bounds the length of a running sum in tensor memory: 512-token chains bring
+    the tensor-core sums to within 1e-5 of an fp64 sum (2048-token chains: about 2e-5)."""
+    tokens = 65536
+    q, k = correlated_qk(tokens, 32, 8, seed=31, device="cuda")
+    kd = k.double()
+    exact = torch.einsum("hsd,hse->hde", kd, kd).cpu()
+    errs = {}
+    for chain in (0, 512):
+        acc = KeyPathMoments(1, 32, 8, 128, device="cuda", max_chain_tokens=chain)
+        acc.update(0, q, k)
+        errs[chain] = _fro(acc.sums[0, 1].cpu(), exact)
+    print(f"sk_sum relative error: default chains {errs[0]:.2e}, 512-token chains {errs[512]:.2e}")
+    assert errs[512] <= 1e-5 and errs[512] < errs[0]
+
+
+def _nccl_worker(rank, world, port, out):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        T = 8192
+        q, k = correlated_qk(T, 32, 8, seed=77, device="cuda")
+        acc = KeyPathMoments(1, 32, 8, 128, device="cuda")
+        lo, hi = rank * T // world, (rank + 1) * T // world
+        acc.update(0, q[:, lo:hi], k[:, lo:hi])                      # this rank's token shard
+        acc.all_reduce()
+        fin = acc.finalize()
+        ref = orc.normalise_moments(orc.moment_sums(q[None].cpu(), k[None].cpu()), group=4, tokens=T)
+        ok = all(_fro(fin[n][0].cpu(), ref[n][0]) <= 1e-4 for n in ("sigma_q", "sigma_k", "cqk"))
+        out[rank] = bool(ok and float(fin["total_tokens"][0]) == float(T))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_token_sharded_moments_over_nccl():
+    """Two ranks, each the kernel on its token shard, one NCCL all-reduce, compared with the oracle
+    on the full token set."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        out = mgr.dict()
+        procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, out)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(300)
+            assert p.exitcode == 0
+        assert dict(out) == {0: True, 1: True}
+
+
 def test_linearity_and_finalize():
     q, k = correlated_qk(3000, 8, 2, seed=5, device="cuda")
     whole = KeyPathMoments(2, 8, 2, 128, device="cuda")

@@ -2,6 +2,7 @@
 single-rank result, and the sequence / head partitions cover the work exactly once."""
 
 import os
+import socket
 
 import pytest
 import torch
@@ -24,12 +25,16 @@ def _worker(rank, world, port, out):
         lo, hi = rank * 256, (rank + 1) * 256
         part = orc.moment_sums(q[None, :, lo:hi], k[None, :, lo:hi])     # this rank's token shard
         acc.sums[0, 0], acc.sums[0, 1], acc.sums[0, 2] = part["sq_sum"][0], part["sk_sum"][0], part["cqk_sum"][0]
+        acc.firsts[0, 0] = q[:, lo:hi].reshape(2, 2, hi - lo, 32).sum((1, 2))
+        acc.firsts[0, 1] = k[:, lo:hi].sum(1)
         acc.tokens[0] = hi - lo
         acc.all_reduce()
         fin = acc.finalize()
         full = orc.normalise_moments(orc.moment_sums(q[None], k[None]), group=2, tokens=512)
         ok = all(torch.allclose(fin[n][0], full[n][0], rtol=1e-5, atol=1e-5) for n in ("sigma_q", "sigma_k", "cqk"))
         ok = ok and float(fin["total_tokens"][0]) == 512.0
+        ok = ok and torch.allclose(fin["mu_k"][0], k.mean(1), rtol=1e-5, atol=1e-6)
+        ok = ok and torch.allclose(fin["mu_q"][0], q.reshape(2, 2, 512, 32).mean((1, 2)), rtol=1e-5, atol=1e-6)
         out[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -39,7 +44,9 @@ def test_token_sharded_moments_allreduce():
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         out = mgr.dict()
-        port = 29500 + os.getpid() % 2000
+        with socket.socket() as sock:                     # a port the kernel says is free right now
+            sock.bind(("127.0.0.1", 0))
+            port = sock.getsockname()[1]
         procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
         for p in procs:
             p.start()
@@ -47,6 +54,28 @@ def test_token_sharded_moments_allreduce():
             p.join(120)
             assert p.exitcode == 0
         assert dict(out) == {0: True, 1: True}
+
+
+def test_moment_status_word_is_read_on_finalize():
+    """An expired wait in the moment kernel reaches the caller: every finalize reads the status word."""
+    from jointqk_b200 import _native, moments
+
+    key = ("cpu", None)
+    moments._STATUS[key] = torch.tensor([_native.STATUS_WAIT_EXPIRED], dtype=torch.int32)
+    try:
+        with pytest.raises(RuntimeError, match="wait expired"):
+            moments.check_status()
+        acc = moments.QueryMomentsAccumulator()
+        acc.sum_q, acc.sum_outer, acc.total_count = torch.zeros(1, 1, 4), torch.zeros(1, 1, 4, 4), 3
+        with pytest.raises(RuntimeError, match="wait expired"):
+            acc.finalize()
+        cross = moments.CrossMomentsAccumulator()
+        cross.sum_qk, cross.total_count = torch.zeros(1, 4, 4), 3
+        with pytest.raises(RuntimeError, match="wait expired"):
+            cross.finalize()
+    finally:
+        del moments._STATUS[key]
+    assert moments.check_status() is None
 
 
 def test_lpt_partition_covers_everything_once():
