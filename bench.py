@@ -269,14 +269,43 @@ def cpu_stage_baselines() -> dict:
     return out
 
 
+class _HostFit:
+    """What the CPU legs need of a fitted head: codebooks and the two maps (plain tensors)."""
+
+    def __init__(self, codebooks_padded, forward_map, inverse_map):
+        self.codebooks_padded, self.forward_map, self.inverse_map = codebooks_padded, forward_map, inverse_map
+
+
+def host_fit_sigma_k(keys: torch.Tensor, b_avg: float, max_bits: int = 4, eps: float = 1e-4) -> list[_HostFit]:
+    """The parity config's fit (Sigma_K eigenbasis, water-fill on its variances, capped tail, Lloyd-Max
+    codebooks) from the host-side modules alone.  The reference arm uses this so that it never loads
+    the CUDA library."""
+    from jointqk_b200.allocation import allocate_bits_for_budget
+    from jointqk_b200.basis import eigvec_desc
+    from jointqk_b200.codebooks import unit_gaussian_centroids
+    from jointqk_b200.synthetic import second_moment
+    from oracle import reference_port as orc
+
+    unit = {b: unit_gaussian_centroids(b) for b in range(1, max_bits + 1)}
+    out = []
+    for h in range(keys.shape[0]):
+        sig = second_moment(keys[h].float())
+        R = eigvec_desc(sig, eps).float()
+        var = (R.T @ sig @ R).diagonal().clamp_min(1e-30)
+        bits = allocate_bits_for_budget(var.unsqueeze(0), float(b_avg) * keys.shape[-1], max_bits).squeeze(0)
+        out.append(_HostFit(orc.codebooks_padded(bits, var.sqrt(), unit), R, R.T.contiguous()))
+    return out
+
+
 def run_reference_arm(args, rank: int, world: int) -> None:
-    """The reference's CPU implementation of the path on this box's host cores (rank 0 only)."""
+    """The reference's CPU implementation of the path on this box's host cores (rank 0 only).  Nothing
+    here imports a module that binds the CUDA library."""
     if rank != 0:
         return
-    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+    from jointqk_b200.synthetic import config_seed, spectrum_keys
 
     keys = torch.stack([spectrum_keys(CTX, config_seed(1, 0, h)) for h in range(N_KV_HEADS)])
-    comps, _ = fit_sigma_k_heads(keys[:, :4096], B_AVG)
+    comps = host_fit_sigma_k(keys[:, :4096], B_AVG)
     value, ms, cores, sample = cpu_decode_steps_per_s(comps, keys, budget_s=150.0, steps=args.steps, warmup=args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
@@ -425,6 +454,277 @@ def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict
                          "tensor_tflops": tf, "tensor_frac": tf / tflops, "peak_kind": peak_kind}}
 
 
+
+# ----------------------------------------------------------------------------------------------
+# the three partitioned workloads, run at every N (reported under "extra.scale")
+# ----------------------------------------------------------------------------------------------
+def region_ms(fn, reps: int, device, world: int) -> float:
+    """barrier + synchronize, `reps` calls of fn between two CUDA events, synchronize + barrier;
+    the max over ranks of the event time, in ms."""
+    import torch.distributed as dist
+
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        dist.barrier()
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def scale_decode_batch64(device, rank: int, world: int, hbm_gbs: float, peak_kind: str) -> dict:
+    """The 64-sequence decode config, strong scaling: 32 layer-steps over the rank's share of 64
+    sequences (context U{4096..65536}, K at 3.0 bits, bf16 V), sequences dealt by longest-processing-
+    time, no collective; two caches alternate between layer-steps so every launch reads HBM."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, lpt_shards, spectrum_keys, uniform_lengths
+
+    n_layers, b_avg = 32, 3.0
+    lens_all = uniform_lengths(64, 4096, 65536, config_seed(2, 0, 0))
+    shards = lpt_shards(lens_all, world)
+    shard = [lens_all[i] for i in shards[rank]]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(config_seed(2, 0, 0) + 1 + rank)
+    q = torch.randn(len(shard), N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    keys = torch.stack([spectrum_keys(4096, config_seed(2, 0, h)) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys, b_avg)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    caches = []
+    for _ in range(2):
+        cache = paged.PagedKVCache(tables, shard)
+        cache.k_pool.random_(0, 2 ** 31 - 1, generator=gen)
+        cache.v_pool.normal_(generator=gen)
+        cache.lengths = list(shard)
+        cache.seq_lens[:] = torch.tensor(shard, dtype=torch.int32, device=device)
+        caches.append(cache)
+
+    def step(_i: int) -> None:
+        for layer in range(n_layers):
+            caches[layer % 2].decode(q)
+
+    step(0)
+    reps = max(2, math.ceil(50.0 / (45.0 / world)))                     # >= 50 ms timed
+    ms = region_ms(step, reps, device, world) / reps
+    paged.check_status(caches[0].status)
+    bytes_per_step = sum(lens_all) * N_KV_HEADS * (tables.record_bytes + HEAD_DIM * 2) * n_layers
+    gbs = bytes_per_step / (ms * 1e-3) / 1e9
+    loads = [sum(lens_all[i] for i in sh) for sh in shards]
+    del caches
+    torch.cuda.empty_cache()
+    return {"workload": "decode, 32 layers, 64 sequences, context U{4096..65536} (%d keys), 3.0 bits K, bf16 V" % sum(lens_all),
+            "sharding": "sequences by longest-processing-time over %d rank(s), no collective" % world, "scaling": "strong",
+            "value": 64 / (ms * 1e-3), "unit": "tokens/s (one 32-layer decode step per sequence)", "ms_per_step": ms,
+            "timed_steps": reps, "rank_imbalance": max(loads) / (sum(loads) / world),
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs * world, "unit": "GB/s",
+                         "frac": gbs / (hbm_gbs * world), "peak_kind": peak_kind, "algorithmic_bytes_per_step": bytes_per_step}}
+
+
+def scale_calibration(device, rank: int, world: int, hbm_gbs: float, tflops: float, peak_kind: str) -> dict:
+    """The calibration config, strong scaling: 2 097 152 tokens x 32 layers of bf16 q (32 heads) / k (8
+    heads), tokens split evenly over the ranks, streamed as 65536-token chunks from a pool of 8
+    distinct chunks (5.4 GB, generation untimed), then one NCCL all-reduce of the [32][3][8][128][128]
+    fp32 block (50.3 MB) plus first moments and counts.  Kernels and collective are timed apart.  A
+    small separate case checks the sharded sums against a single-rank pass."""
+    import torch.distributed as dist
+    from jointqk_b200.moments import KeyPathMoments
+    from jointqk_b200.synthetic import config_seed, correlated_qk
+
+    n_layers, total, chunk = 32, 2097152, 65536
+    per_rank = total // world
+    n_chunks = per_rank // chunk
+    pool = [correlated_qk(chunk, N_Q_HEADS, N_KV_HEADS, config_seed(3, 0, c) + 50 * rank, device=device) for c in range(8)]
+    acc = KeyPathMoments(n_layers, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+
+    def kernels(_i: int) -> None:
+        for layer in range(n_layers):
+            for c in range(n_chunks):
+                q, k = pool[(layer + c) % 8]
+                acc.update(layer, q, k)
+
+    for layer in range(2):                                               # warm-up: a few chunks
+        for c in range(4):
+            acc.update(layer, *pool[c])
+    acc.all_reduce()
+    acc.sums.zero_()
+    acc.firsts.zero_()
+    acc.tokens.zero_()
+    k_ms = region_ms(kernels, 1, device, world)
+    c_ms = region_ms(lambda _i: acc.all_reduce(), 1, device, world)
+    acc.finalize()
+    # parity of the sharded path on a distinct small case: every rank a token slice, all-reduce, and
+    # rank 0's own pass over all tokens
+    T = 8192 * max(1, world)
+    qs, ks = correlated_qk(T, N_Q_HEADS, N_KV_HEADS, config_seed(3, 1, 0), device=device)
+    part = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    lo, hi = rank * T // world, (rank + 1) * T // world
+    part.update(0, qs[:, lo:hi], ks[:, lo:hi])
+    part.all_reduce()
+    whole = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    whole.update(0, qs, ks)
+    err = float((part.sums.double() - whole.sums.double()).norm() / whole.sums.double().norm())
+    same_tokens = float(part.tokens[0]) == float(T)
+    tl = total * n_layers
+    bytes_tl = (N_Q_HEADS + N_KV_HEADS) * HEAD_DIM * 2
+    flop_tl = (N_Q_HEADS + 2 * N_KV_HEADS) * 2 * HEAD_DIM * HEAD_DIM
+    step_ms = k_ms + c_ms
+    gbs, tf = tl * bytes_tl / (k_ms * 1e-3) / 1e9, tl * flop_tl / (k_ms * 1e-3) / 1e12
+    payload = acc.sums.numel() * 4
+    del pool
+    torch.cuda.empty_cache()
+    return {"workload": "calibration moments, 2097152 tokens x 32 layers, 32 q / 8 kv heads, bf16, 65536-token chunks from a pool of 8",
+            "sharding": "tokens split evenly over %d rank(s), one all-reduce of the sums" % world, "scaling": "strong",
+            "value": tl / (step_ms * 1e-3), "unit": "calibration token-layers/s", "ms_kernels": k_ms, "ms_allreduce": c_ms,
+            "allreduce_share": c_ms / step_ms, "allreduce_bytes": payload,
+            "allreduce_busbw_gbs": (payload * 2 * (world - 1) / world / (c_ms * 1e-3) / 1e9) if world > 1 else None,
+            "sharded_vs_single_pass_rel_err": err, "sharded_token_count_ok": same_tokens,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs * world, "unit": "GB/s", "frac": gbs / (hbm_gbs * world),
+                         "tensor_tflops": tf, "tensor_frac": tf / (tflops * world), "peak_kind": peak_kind,
+                         "note": "kernel time only; the all-reduce is reported beside it"}}
+
+
+def scale_prefill_compress(device, rank: int, world: int, hbm_gbs: float, peak_kind: str) -> dict:
+    """The prefill-compression config, strong scaling: 36 layers x (4 sequences x 8 kv heads) x 131072 bf16
+    keys, 2.5 bits.  The 32 (sequence, head) units of a layer are dealt to the ranks by kv head (rank r
+    takes the heads h with h % N == r, all four sequences), layers iterate locally, no collective."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    T, B, n_layers = 131072, 4, 36
+    if world > N_KV_HEADS:
+        return {"skipped": "more ranks than kv heads"}
+    heads = [h for h in range(N_KV_HEADS) if h % world == rank]
+    keys = torch.stack([torch.stack([spectrum_keys(T, config_seed(4, b, h), 8, 20.0, device=device, dtype=torch.bfloat16)
+                                     for h in heads]) for b in range(B)])
+    comps, _ = fit_sigma_k_heads(keys[0, :, :4096].float().cpu(), 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    page_table, used = paged.sequential_page_table([T] * B, device)
+    k_pool = paged.alloc_k_pool(tables, used)
+    n_tok = torch.tensor([T] * B, dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def step(_i: int) -> None:
+        for _layer in range(n_layers):
+            paged.compress_into(tables, keys, n_tok, T, page_table, k_pool, status)
+
+    step(0)
+    reps = max(2, math.ceil(50.0 / (17.0 / world)))
+    ms = region_ms(step, reps, device, world) / reps
+    paged.check_status(status)
+    n_keys = T * N_KV_HEADS * B * n_layers
+    bytes_per_key = HEAD_DIM * 2 + tables.payload_bytes_per_key
+    gbs = n_keys * bytes_per_key / (ms * 1e-3) / 1e9
+    del keys, k_pool
+    torch.cuda.empty_cache()
+    return {"workload": "prefill compression, 36 layers x 4 sequences x 8 kv heads x 131072 bf16 keys, 2.5 bits/coord",
+            "sharding": "(sequence, kv head) units by head over %d rank(s): %d units per rank, no collective" % (world, len(heads) * B),
+            "scaling": "strong", "value": n_keys / (ms * 1e-3), "unit": "keys compressed/s", "ms_per_step": ms, "timed_steps": reps,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs * world, "unit": "GB/s", "frac": gbs / (hbm_gbs * world),
+                         "bytes_per_key": bytes_per_key, "peak_kind": peak_kind}}
+
+
+def bench_generate_loop(device, tables, cache, hbm_gbs: float) -> dict:
+    """The decode step as a generate loop on the headline shape: every step appends one new token per
+    sequence (compress it into the tail page, store its value, advance the length on the device) and
+    then attends over the whole context.  Timed end to end over 256 steps, launches included."""
+    from jointqk_b200 import paged
+
+    steps, H = 256, N_KV_HEADS
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4242)
+    new_k = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device)
+    new_v = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    q = torch.randn(1, N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    for t in range(8):                                                   # warm-up (also reserves the next page)
+        cache.append(new_k[:, :, t:t + 1], new_v[:, :, t:t + 1])
+        cache.decode(q)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(8, 8 + steps):
+        cache.append(new_k[:, :, t:t + 1], new_v[:, :, t:t + 1])
+        out = cache.decode(q)
+    e1.record()
+    torch.cuda.synchronize(device)
+    wall = time.perf_counter() - t0
+    paged.check_status(cache.status)
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": "generate loop on the headline shape: append 1 token (K compress + V store + length), then decode, context %d -> %d"
+                        % (cache.lengths[0] - steps, cache.lengths[0]),
+            "value": 1.0 / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "wall_ms_per_step": wall / steps * 1e3,
+            "launches_per_step": 4, "steps": steps}
+
+
+def bench_isolated_launch(step, device, alg_bytes: float, hbm_gbs: float) -> dict:
+    """One decode step at a time: launch, wait for it, launch the next.  Nothing of the next step can
+    overlap the tail of this one, unlike the back-to-back replay of the headline; both are real uses
+    (a step that waits for its result, a pipeline of independent steps)."""
+    times = []
+    for i in range(40):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        e0.record()
+        step(i)
+        e1.record()
+        torch.cuda.synchronize(device)
+        times.append(e0.elapsed_time(e1))
+    times = sorted(times[8:])
+    ms = times[len(times) // 2]
+    return {"ms_per_step": ms, "frac_of_hbm": alg_bytes / (ms * 1e-3) / 1e9 / hbm_gbs,
+            "note": "median of 32 single launches, each synchronised before and after (event overhead of ~2 us included)"}
+
+
+def bench_value_store(device, hbm_gbs: float, peak_kind: str) -> dict:
+    """Values of one layer of the prefill config into pages: 4 sequences x 8 kv heads x 131072 bf16 rows,
+    one pass of the store kernel (256 B read + 256 B written per row)."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    T, B = 131072, 4
+    keys = torch.stack([spectrum_keys(4096, config_seed(4, 0, h)) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys, 2.5)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7)
+    v = torch.randn(B, N_KV_HEADS, T, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    page_table, used = paged.sequential_page_table([T] * B, device)
+    v_pool = paged.alloc_v_pool(tables, used)
+    n_tok = torch.tensor([T] * B, dtype=torch.int32, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    run = lambda _i: paged.store_values_into(v, n_tok, T, page_table, v_pool, status)
+    for i in range(3):
+        run(i)
+    ms = region_ms(run, 10, device, 1) / 10
+    rows = T * N_KV_HEADS * B
+    gbs = rows * 512 / (ms * 1e-3) / 1e9
+    return {"metric": "value rows stored/s", "value": rows / (ms * 1e-3), "ms_per_launch": ms,
+            "workload": "1 layer x 4 sequences x 8 kv heads x 131072 bf16 value rows into 16-token pages",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
+                         "bytes_per_row": 512, "peak_kind": peak_kind}}
+
+
+def run_scale_blocks(device, rank: int, world: int) -> dict:
+    hbm_gbs, tflops, peak_kind = measured_peaks()
+    out = {}
+    for name, fn in (("decode_batch64", lambda: scale_decode_batch64(device, rank, world, hbm_gbs, peak_kind)),
+                     ("calibration", lambda: scale_calibration(device, rank, world, hbm_gbs, tflops, peak_kind)),
+                     ("prefill_compress", lambda: scale_prefill_compress(device, rank, world, hbm_gbs, peak_kind))):
+        out[name] = fn()
+    return out
+
 # ----------------------------------------------------------------------------------------------
 # main arm
 # ----------------------------------------------------------------------------------------------
@@ -485,23 +785,31 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             step(base + i)
 
     run_steps(args.warmup, 0)
-    torch.cuda.synchronize(device)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # R repeats of the K-step region, each bracketed by barrier + synchronize and timed with CUDA events
+    # (max over ranks); the reported step time is the median region.  One region of K steps is short
+    # (K x ~20 us), so a single one would mostly measure jitter.
+    region_list = []
     t0 = time.perf_counter()
-    e0.record()
-    run_steps(args.steps, 0)
-    e1.record()
-    torch.cuda.synchronize(device)
+    for _rep in range(max(1, args.repeats)):
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run_steps(args.steps, 0)
+        e1.record()
+        torch.cuda.synchronize(device)
+        r_ms = e0.elapsed_time(e1)
+        if world > 1:
+            dist.barrier()
+            t = torch.tensor([r_ms], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            r_ms = float(t.item())
+        region_list.append(r_ms)
     t1 = time.perf_counter()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        dist.barrier()
-        t = torch.tensor([ms], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ordered = sorted(region_list)
+    ms = ordered[len(ordered) // 2]
     sampler.stop()
     clocks = sampler.summary(t0, t1)
     paged.check_status(caches[0].status)
@@ -531,16 +839,29 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": e2e_out[0].numel() * 4,
                 "steps": e2e_steps, "note": "host query in, pinned-host result out through PagedKVCache.decode_host (replayed graph of H2D copy, decode, D2H copy; stream wait per step)"},
         "gpu_launches": args.steps,
+        "repeats": {"regions": len(region_list), "steps_per_region": args.steps, "ms_per_step_median": per_launch_ms,
+                    "ms_per_step_min": ordered[0] / args.steps, "ms_per_step_max": ordered[-1] / args.steps},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
                      "traffic": DECODE_DRAM_TRAFFIC_BYTES, "peak_kind": peak_kind, "kernel": "decode_kernel",
                      "algorithmic_bytes_per_launch": alg, "tokens_per_split": tps},
     }
-    if world == 1 and not args.no_extra:
+    if not args.no_extra:
+        extra = {}
+        if world == 1:
+            extra["isolated_launch"] = bench_isolated_launch(step, device, alg["total"], hbm_gbs)
+            extra["generate_loop"] = bench_generate_loop(device, tables, caches[0], hbm_gbs)
         del caches[1:]
         torch.cuda.empty_cache()
-        line["extra"] = {"prefill_compress": bench_compress(device, hbm_gbs, peak_kind),
-                         "calibration_moments": bench_moments(device, hbm_gbs, tflops, peak_kind),
-                         "decode_batch": bench_decode_batch(device, hbm_gbs, peak_kind)}
+        if world == 1:
+            extra["prefill_compress"] = bench_compress(device, hbm_gbs, peak_kind)
+            extra["prefill_values"] = bench_value_store(device, hbm_gbs, peak_kind)
+            extra["calibration_moments"] = bench_moments(device, hbm_gbs, tflops, peak_kind)
+            extra["decode_batch"] = bench_decode_batch(device, hbm_gbs, peak_kind)
+        del caches[:]
+        torch.cuda.empty_cache()
+        # the partitioned workloads run at every N: sequences, tokens and (sequence, head) units over the ranks
+        extra["scale"] = run_scale_blocks(device, rank, world)
+        line["extra"] = extra
     if rank == 0:
         if world == 1 and not args.no_cpu:
             v, cms, cores, sample = cpu_decode_steps_per_s(comps, keys.cpu(), budget_s=20.0)
@@ -548,7 +869,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                                     "ms_per_step": cms}
             if "extra" in line:
                 for stage, base in cpu_stage_baselines().items():
-                    line["extra"][stage]["cpu_baseline"] = base
+                    if stage in line["extra"]:
+                        line["extra"][stage]["cpu_baseline"] = base
         print(json.dumps(line), flush=True)
 
 
@@ -616,6 +938,7 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--repeats", type=int, default=10, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the compress / moments stages")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
@@ -624,8 +947,8 @@ def main() -> None:
     ap.add_argument("--workload", default="headline", choices=["headline", "batch64"],
                     help="headline: the single-layer context-32768 step (default, what the JSON contract names); "
                          "batch64: the 32-layer, 64-sequence decode config sharded by sequence over the ranks")
-    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch"],
-                    help="profiling aid: run only one of the secondary stages and print its JSON")
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "scale"],
+                    help="run only one of the secondary stages (or the three partitioned workloads) and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -635,12 +958,13 @@ def main() -> None:
             args.steps = 200
         run_reference_arm(args, rank, world)
         return
-    if args.stage != "all":
+    if args.stage not in ("all", "scale"):
         dev = torch.device("cuda", local_rank)
         torch.cuda.set_device(dev)
         hbm, tf, kind = measured_peaks()
         res = (bench_compress(dev, hbm, kind) if args.stage == "compress" else
-               bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else bench_moments(dev, hbm, tf, kind))
+               bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else
+               bench_value_store(dev, hbm, kind) if args.stage == "values" else bench_moments(dev, hbm, tf, kind))
         print(json.dumps(res), flush=True)
         return
     if world > 1:
@@ -650,7 +974,13 @@ def main() -> None:
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        if args.workload == "batch64":
+        if args.stage == "scale":
+            dev = torch.device("cuda", local_rank)
+            torch.cuda.set_device(dev)
+            res = run_scale_blocks(dev, rank, world)
+            if rank == 0:
+                print(json.dumps(res), flush=True)
+        elif args.workload == "batch64":
             run_batch64(args, rank, local_rank, world)
         else:
             run_ours(args, rank, local_rank, world)

@@ -76,6 +76,10 @@ extern "C" {
  *   inv_rows      float [H][128][d]: inverse_map[coord(c)][i] (reconstruction)
  *   fwd_limbs     bf16  [H][3][128][d]: three-way bf16 split of fwd_cols, column-major
  *                 (limb l, column c, dim i), for the tensor-core transform; may be NULL
+ *   center        float [H][d] or NULL: a mean that is subtracted from every input row before the
+ *                 transform and added back after reconstruction (the reference's CenteredCompressor,
+ *                 experiments/stage1/toolkit/v_compressor_adapter.py:46-72, used on the value side);
+ *                 the tensor-core compress kernel is not used for centred tables
  *   bucket_pre    uint8 [H][128][128], bucket_aff float [H][128][2]: coarse-to-exact quantiser of the
  *                 tensor-core kernel: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes
  *                 2^23), code = pre[c][cell] + (x >= thresholds[c][pre[c][cell]]); both NULL = not used
@@ -96,6 +100,7 @@ typedef struct jqk_head_tables {
   const uint16_t* fwd_limbs;
   const uint8_t* bucket_pre;
   const float* bucket_aff;
+  const float* center;
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */
@@ -143,10 +148,12 @@ int32_t jqk_store_values_paged(const void* values, int32_t dtype, int64_t seq_st
 /*
  * Reconstruction from pages: unpack, centroid lookup, inverse map.  Replaces the second half
  * of PerCoordCompressor.roundtrip (per_coord_quantization.py:158-164).
+ *   seq_starts  int32 [n_seqs] position in the sequence of the first key to reconstruct (NULL = 0);
+ *               row t of the output is key seq_starts + t
  *   out  float [n_seqs][H][max_tokens][d] (contiguous); rows beyond n_tokens[s] are not written
  */
 int32_t jqk_decompress_paged(const jqk_head_tables* tables, int32_t n_seqs,
-                             const int32_t* n_tokens, int32_t max_tokens,
+                             const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
                              const int32_t* page_table, int32_t page_table_stride,
                              int32_t n_pages, const uint32_t* k_pool, float* out,
                              int32_t* status, void* stream);

@@ -19,7 +19,7 @@ __all__ = [
     "HeadTables", "PackedKeys", "PagedKVCache",
     "QueryMomentsAccumulator", "CrossMomentsAccumulator", "KeyPathMoments",
     "compute_moments_from_tensors", "compute_query_moments", "compute_grouped_query_second_moment",
-    "compute_attention_metrics",
+    "compute_attention_metrics", "CenteredCompressor", "build_v_compressor", "V_METHOD_NAMES", "PagePool", "JointQKPressB200",
 ]
 
 _LAZY = {
@@ -28,7 +28,8 @@ _LAZY = {
     "PagedKVCache": "paged", "QueryMomentsAccumulator": "moments", "CrossMomentsAccumulator": "moments",
     "KeyPathMoments": "moments", "compute_moments_from_tensors": "moments",
     "compute_query_moments": "moments", "compute_grouped_query_second_moment": "moments",
-    "compute_attention_metrics": "eval",
+    "compute_attention_metrics": "eval", "CenteredCompressor": "v_compressor", "build_v_compressor": "v_compressor",
+    "V_METHOD_NAMES": "v_compressor", "PagePool": "paged", "JointQKPressB200": "press",
 }
 
 

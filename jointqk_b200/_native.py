@@ -33,6 +33,7 @@ class JqkHeadTables(C.Structure):
         ("fwd_limbs", C.c_void_p),
         ("bucket_pre", C.c_void_p),
         ("bucket_aff", C.c_void_p),
+        ("center", C.c_void_p),
     ]
 
 
@@ -45,7 +46,7 @@ SIGNATURES = {
         C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
         C.c_void_p]),
     "jqk_decompress_paged": (C.c_int32, [
-        C.POINTER(JqkHeadTables), C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
+        C.POINTER(JqkHeadTables), C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "jqk_unpack_codes": (C.c_int32, [
         C.POINTER(JqkHeadTables), C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,

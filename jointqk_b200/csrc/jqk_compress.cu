@@ -103,10 +103,14 @@ compress_simt_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t se
   const int tid = threadIdx.x;
 
   const KT* kbase = keys + (size_t)seq * seq_stride + (size_t)head * head_stride;
+  const float* center = tb.center ? tb.center + (size_t)head * d : nullptr;
   for (int e = tid; e < TILE_T * d; e += blockDim.x) {
     int t = e / d, i = e - t * d;
     float v = 0.f;
-    if (t0 + t < n_tok) v = to_f32<KT>(kbase[(size_t)(t0 + t) * token_stride + i]);
+    if (t0 + t < n_tok) {
+      v = to_f32<KT>(kbase[(size_t)(t0 + t) * token_stride + i]);
+      if (center) v -= center[i];   // fp32, as the reference's `states - mu` (v_compressor_adapter.py:70)
+    }
     xs[t * XS_STRIDE + i] = v;
   }
   float acc[4][8];
@@ -221,9 +225,10 @@ decompress_simt_kernel(jqk_head_tables tb, PagedArgs pa, const uint32_t* __restr
     const int t = 4 * ty + r;
     if (t0 + t >= n_tok) continue;
     float* o = out + (((size_t)seq * tb.n_heads + head) * pa.max_tokens + t0 + t) * d;
+    const float* center = tb.center ? tb.center + (size_t)head * d : nullptr;
 #pragma unroll
     for (int m = 0; m < 8; ++m)
-      if (tx + 16 * m < d) o[tx + 16 * m] = acc[r][m];
+      if (tx + 16 * m < d) o[tx + 16 * m] = center ? acc[r][m] + center[tx + 16 * m] : acc[r][m];
   }
 }
 
@@ -315,7 +320,7 @@ extern "C" int32_t jqk_compress_paged(const jqk_head_tables* tables, const void*
 }
 
 extern "C" int32_t jqk_decompress_paged(const jqk_head_tables* tables, int32_t n_seqs,
-                                        const int32_t* n_tokens, int32_t max_tokens,
+                                        const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
                                         const int32_t* page_table, int32_t page_table_stride,
                                         int32_t n_pages, const uint32_t* k_pool, float* out,
                                         int32_t* status, void* stream) {
@@ -324,7 +329,7 @@ extern "C" int32_t jqk_decompress_paged(const jqk_head_tables* tables, int32_t n
   if (n_seqs == 0 || max_tokens == 0) return 0;
   if (!out) return fail(JQK_E_ARG, "null out");
   dim3 grid((max_tokens + TILE_T - 1) / TILE_T, tables->n_heads, n_seqs);
-  PagedArgs pa{n_tokens, nullptr, page_table, page_table_stride, n_pages, max_tokens, status};
+  PagedArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, max_tokens, status};
   JQK_SMEM_ONCE(decompress_simt_kernel, kTileSmem, "decompress smem attribute");
   decompress_simt_kernel<<<grid, 256, kTileSmem, (cudaStream_t)stream>>>(*tables, pa, k_pool, out);
   JQK_CUDA_OK(cudaGetLastError(), "decompress launch");

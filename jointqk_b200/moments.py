@@ -248,7 +248,16 @@ class KeyPathMoments:
         n_mat = 4 if with_values else 3
         self.sums = torch.zeros((n_layers, n_mat, n_kv_heads, head_dim, head_dim), dtype=torch.float32, device=device)
         self.firsts = torch.zeros((n_layers, n_mat - 1, n_kv_heads, head_dim), dtype=torch.float32, device=device)
-        self.tokens = torch.zeros(n_layers, dtype=torch.float64, device=device)
+        self._tokens = torch.zeros(n_layers, dtype=torch.float64, device=device)
+        self._pending = [0] * n_layers       # token counts not yet added on the device (no launch per update)
+
+    @property
+    def tokens(self) -> torch.Tensor:
+        """Tokens seen per layer, fp64 on the accumulator's device."""
+        if any(self._pending):
+            self._tokens += torch.tensor(self._pending, dtype=torch.float64).to(self._tokens.device)
+            self._pending = [0] * self.n_layers
+        return self._tokens
 
     def update(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor | None = None) -> None:
         """q (Hq, T, d), k (Hkv, T, d) and, when values are tracked, v (Hkv, T, d) of one layer's
@@ -261,7 +270,7 @@ class KeyPathMoments:
             if v is None:
                 raise ValueError("this accumulator tracks values: pass v")
             accumulate_layer(None, v, None, self.sums[layer, 3], None, None, self.firsts[layer, 2], self.max_chain_tokens)
-        self.tokens[layer] += k.shape[1]
+        self._pending[layer] += int(k.shape[1])
 
     def all_reduce(self, group=None) -> None:
         """Sum the partial sums and token counts over the ranks of ``group``."""

@@ -164,7 +164,7 @@ def decompress(packed: PackedKeys) -> torch.Tensor:
     out = torch.zeros((packed.n_seqs, t.n_heads, packed.max_tokens, t.d), dtype=torch.float32, device=t.device)
     if packed.n_seqs and packed.max_tokens:
         _native.check(_native.lib.jqk_decompress_paged(
-            t.ref, packed.n_seqs, packed.n_tokens.data_ptr(), packed.max_tokens,
+            t.ref, packed.n_seqs, packed.n_tokens.data_ptr(), None, packed.max_tokens,
             packed.page_table.data_ptr(), packed.page_table.stride(0), packed.n_pages,
             packed.k_pool.data_ptr(), out.data_ptr(), packed.status.data_ptr(), _stream_ptr(t.device)))
     return out

@@ -39,7 +39,8 @@ class HeadTables:
     """Stacked tables for ``H`` heads; owns the device tensors and the ctypes struct."""
 
     def __init__(self, forward_maps: torch.Tensor | None, inverse_maps: torch.Tensor | None,
-                 codebooks: torch.Tensor, device: torch.device | str = "cuda") -> None:
+                 codebooks: torch.Tensor, device: torch.device | str = "cuda",
+                 center: torch.Tensor | None = None) -> None:
         cb = codebooks.detach().float().cpu()
         if cb.dim() != 3:
             raise ValueError("codebooks must be (H, d, K)")
@@ -111,6 +112,11 @@ class HeadTables:
         # three bf16 limbs of the forward map, [H][3][col][dim] (column-major = K-major B operand)
         self.fwd_limbs = split_bf16_limbs(torch.from_numpy(fwd_cols).transpose(1, 2).contiguous(), 3) \
             .permute(1, 0, 2, 3).contiguous().to(self.device)
+        # optional per-head mean, subtracted before the transform and added back after reconstruction
+        self.center = None
+        if center is not None:
+            c = center.detach().float().cpu().reshape(H, d).contiguous()
+            self.center = c.to(self.device)
         self.struct = _native.JqkHeadTables(
             n_heads=H, d=d, words_per_record=self.words_per_record, reserved=0,
             desc=self.desc.data_ptr(), col_meta=self.col_meta.data_ptr(),
@@ -119,7 +125,8 @@ class HeadTables:
             qproj_cols=self.qproj_cols.data_ptr(), inv_rows=self.inv_rows.data_ptr(),
             fwd_limbs=self.fwd_limbs.data_ptr(),
             bucket_pre=None if self.bucket_pre is None else self.bucket_pre.data_ptr(),
-            bucket_aff=None if self.bucket_aff is None else self.bucket_aff.data_ptr())
+            bucket_aff=None if self.bucket_aff is None else self.bucket_aff.data_ptr(),
+            center=None if self.center is None else self.center.data_ptr())
 
     @property
     def ref(self):
@@ -135,7 +142,7 @@ class HeadTables:
         return float(np.mean([l.payload_bits for l in self.layouts])) / 8.0
 
     @classmethod
-    def from_compressors(cls, comps, device="cuda") -> "HeadTables":
+    def from_compressors(cls, comps, device="cuda", center: torch.Tensor | None = None) -> "HeadTables":
         d = comps[0].d
         k_max = max(int(c.codebooks_padded.shape[1]) for c in comps)
         cb = torch.full((len(comps), d, k_max), float("inf"))
@@ -144,4 +151,4 @@ class HeadTables:
         eye = torch.eye(d)
         fwd = torch.stack([(c.forward_map if c.forward_map is not None else eye).detach().float().cpu() for c in comps])
         inv = torch.stack([(c.inverse_map if c.inverse_map is not None else eye).detach().float().cpu() for c in comps])
-        return cls(fwd, inv, cb, device=device)
+        return cls(fwd, inv, cb, device=device, center=center)

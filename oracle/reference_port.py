@@ -96,6 +96,16 @@ def batched_roundtrip(states: torch.Tensor, forward_maps: torch.Tensor, inverse_
     return rec.to(states.dtype)
 
 
+@torch.no_grad()
+def centred_roundtrip(states: torch.Tensor, mu: torch.Tensor, cb: torch.Tensor, forward_map: torch.Tensor,
+                      inverse_map: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The value side's mean-centring wrapper (v_compressor_adapter.py:64-72): subtract ``mu``,
+    run the inner ``roundtrip``, add ``mu`` back.  Also returns the codes."""
+    centred = states - mu
+    recon, codes = roundtrip(centred, cb, forward_map, inverse_map)
+    return recon + mu, codes
+
+
 # ---- scoring / attention -----------------------------------------------------------------
 def repeat_kv(keys: torch.Tensor, n_q_heads: int) -> torch.Tensor:
     """GQA expansion: kv head h serves q heads h*g .. h*g+g-1 (metric_transform.py:21-27)."""

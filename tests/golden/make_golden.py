@@ -37,6 +37,28 @@ from experiments.stage1.toolkit.quantization import generate_rotation_matrix as 
 from jointqk_b200.synthetic import config_seed, retrieval_queries, second_moment, spectrum_keys  # noqa: E402
 
 
+def _import_v_adapter():
+    """The reference's V-side module imports TurboQuant's value compressor at module level
+    (experiments/stage1/toolkit/v_compressor_adapter.py:43), a third-party package that is not part
+    of the reference checkout.  The methods used here (v_eigen_uniform, v_eigen_waterfill, v_random
+    and the mean-centring wrapper) never touch it, so a placeholder module satisfies the import."""
+    import types
+
+    if "turboquant_pytorch.compressors_v3" not in sys.modules:
+        pkg, mod = types.ModuleType("turboquant_pytorch"), types.ModuleType("turboquant_pytorch.compressors_v3")
+
+        class MSECompressor:  # never constructed by the methods exercised here
+            def __init__(self, *a, **k):
+                raise RuntimeError("TurboQuant is not available")
+
+        mod.MSECompressor = MSECompressor
+        pkg.compressors_v3 = mod
+        sys.modules["turboquant_pytorch"], sys.modules["turboquant_pytorch.compressors_v3"] = pkg, mod
+    from experiments.stage1.toolkit import v_compressor_adapter
+
+    return v_compressor_adapter
+
+
 def save(name: str, **arrays) -> None:
     out = {k: (v.detach().cpu().numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in arrays.items()}
     np.savez_compressed(HERE / f"{name}.npz", **out)
@@ -147,6 +169,31 @@ def main() -> None:
          ref_cross=cross.finalize(), ref_qacc_mean=mean, ref_qacc_cov=cov, ref_qacc_second=second,
          ref_qm_mean=m2[0], ref_qm_cov=m2[1], ref_qm_second=m2[2],
          ref_grouped_second=ref_grouped(qm.float(), 2))
+
+    # 7. V-side compressors: eigenbasis of the centred covariance, uniform / water-fill bits, mean centring
+    va = _import_v_adapter()
+    g = torch.Generator().manual_seed(11)
+    U = ref_rot(128, seed=config_seed(5, 0, 0))
+    lam = torch.exp(-torch.arange(128, dtype=torch.float32) / 40.0)
+    mu_v = 0.3 * torch.randn(128, generator=g)
+    vals = (torch.randn(4096, 128, generator=g) * lam.sqrt()) @ U.T + mu_v
+    sigma_v = second_moment(vals)
+    mean_v = vals.double().mean(0).float()
+    cov_v = sigma_v - torch.outer(mean_v, mean_v)
+    v256, v256_bf16 = vals[:256], vals[:256].to(torch.bfloat16)
+    out = {"values": v256, "cov_v": cov_v, "mu_v": mean_v}
+    for method, bits in (("v_eigen_uniform", 3), ("v_eigen_waterfill", 3), ("v_eigen_waterfill", 2), ("v_random", 2)):
+        comp = va.build_v_compressor(method, cov_v_for_head=cov_v, head_dim=128, bits=bits, seed=42, mu_v_for_head=mean_v)
+        tag = f"{method}_{bits}"
+        out[f"ref_bits_{tag}"] = comp.inner.bits_int
+        out[f"ref_stds_{tag}"] = comp.inner.stds
+        out[f"ref_forward_{tag}"] = comp.inner.forward_map
+        out[f"ref_codebooks_{tag}"] = comp.inner.codebooks_padded
+        out[f"ref_roundtrip_{tag}"] = comp.roundtrip(v256)
+        out[f"ref_roundtrip_bf16_{tag}"] = comp.roundtrip(v256_bf16)
+    plain = va.build_v_compressor("v_eigen_uniform", cov_v_for_head=cov_v, head_dim=128, bits=3, seed=42)
+    out["ref_roundtrip_uncentred_v_eigen_uniform_3"] = plain.roundtrip(v256)
+    save("v_compressor", **out)
 
 
 if __name__ == "__main__":

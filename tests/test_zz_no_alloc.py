@@ -50,18 +50,18 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
     ref = cache.decode(q, tokens_per_split=256)                   # caller-owned workspace, 12 splits
     warm = torch.empty_like(ref)
     _native.check(_call_static(tables, cache, q, lens, 256, warm))   # first call on the device: address look-up
+    outs = [torch.full_like(ref, float("nan")) for _ in range(2)]    # torch allocates before the measurement
     torch.cuda.synchronize()
     free_before = torch.cuda.mem_get_info()[0]
-    for call in range(2):
-        out = torch.full_like(ref, float("nan"))
+    for out in outs:                                                  # two calls in a row through the C ABI
         _native.check(_call_static(tables, cache, q, lens, 256, out))
-        torch.cuda.synchronize()
-        paged.check_status(cache.status)
+    torch.cuda.synchronize()
+    # the entry point took nothing from the device: the driver reports the same free memory
+    assert torch.cuda.mem_get_info()[0] == free_before
+    paged.check_status(cache.status)
+    for call, out in enumerate(outs):
         # same kernel, same split sizes, same merge order: the results are identical
         assert torch.equal(out, ref), f"call {call}: max diff {(out - ref).abs().max().item():.3e}"
-    # `out` comes from torch's cache (the block `warm` sized); the entry point itself took nothing
-    # from the device: the free memory the driver reports is what it was before the two calls
-    assert torch.cuda.mem_get_info()[0] == free_before
     # a different query through the same scratch right after
     q2 = q.flip(1).contiguous()
     ref2 = cache.decode(q2, tokens_per_split=512)
