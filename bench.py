@@ -431,24 +431,23 @@ def bench_moments(device, hbm_gbs: float, tflops: float, peak_kind: str) -> dict
 
     T = 131072
     q, k = correlated_qk(T, N_Q_HEADS, N_KV_HEADS, config_seed(3, 0, 0), device=device)
-    acc = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
-    run = lambda: acc.update(0, q, k)
-    for _ in range(2):
-        run()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 3
-    e0.record()
-    for _ in range(reps):
-        run()
-    e1.record()
-    torch.cuda.synchronize(device)
-    ms = e0.elapsed_time(e1) / reps
+
+    def time_variant(**kw) -> float:
+        acc = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device, **kw)
+        run = lambda _i: acc.update(0, q, k)
+        for i in range(2):
+            run(i)
+        return region_ms(run, 5, device, 1) / 5
+
+    ms = time_variant(first_moments=False)                 # the three second moments (the named config)
+    ms_first = time_variant(first_moments=True)            # plus sum_q / sum_k from the same pass
+    ms_chain512 = time_variant(first_moments=False, max_chain_tokens=512)   # 512-token accumulation chains
     bytes_per_tl = (N_Q_HEADS + N_KV_HEADS) * HEAD_DIM * 2
     flop_per_tl = (N_Q_HEADS + 2 * N_KV_HEADS) * 2 * HEAD_DIM * HEAD_DIM
     gbs = T * bytes_per_tl / (ms * 1e-3) / 1e9
     tf = T * flop_per_tl / (ms * 1e-3) / 1e12
     return {"metric": "calibration token-layers/s", "value": T / (ms * 1e-3), "ms_per_launch": ms,
+            "ms_per_launch_with_first_moments": ms_first, "ms_per_launch_chains_of_512_tokens": ms_chain512,
             "workload": "1 layer, 32 q / 8 kv heads, 131072 bf16 tokens, head_dim 128",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
                          "tensor_tflops": tf, "tensor_frac": tf / tflops, "peak_kind": peak_kind}}
@@ -544,7 +543,7 @@ def scale_calibration(device, rank: int, world: int, hbm_gbs: float, tflops: flo
     per_rank = total // world
     n_chunks = per_rank // chunk
     pool = [correlated_qk(chunk, N_Q_HEADS, N_KV_HEADS, config_seed(3, 0, c) + 50 * rank, device=device) for c in range(8)]
-    acc = KeyPathMoments(n_layers, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    acc = KeyPathMoments(n_layers, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device, first_moments=False)
 
     def kernels(_i: int) -> None:
         for layer in range(n_layers):
@@ -566,11 +565,11 @@ def scale_calibration(device, rank: int, world: int, hbm_gbs: float, tflops: flo
     # rank 0's own pass over all tokens
     T = 8192 * max(1, world)
     qs, ks = correlated_qk(T, N_Q_HEADS, N_KV_HEADS, config_seed(3, 1, 0), device=device)
-    part = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    part = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device, first_moments=False)
     lo, hi = rank * T // world, (rank + 1) * T // world
     part.update(0, qs[:, lo:hi], ks[:, lo:hi])
     part.all_reduce()
-    whole = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device)
+    whole = KeyPathMoments(1, N_Q_HEADS, N_KV_HEADS, HEAD_DIM, device, first_moments=False)
     whole.update(0, qs, ks)
     err = float((part.sums.double() - whole.sums.double()).norm() / whole.sums.double().norm())
     same_tokens = float(part.tokens[0]) == float(T)

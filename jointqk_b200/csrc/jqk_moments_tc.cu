@@ -42,11 +42,17 @@ struct MtSmem {
 };
 
 __device__ __forceinline__ bool mt_wait(MtSmem& sm, uint64_t* bar, uint32_t parity) {
-  if (mbar_wait_timed<0>(bar, parity, MT_WAIT_NS, &sm.abort)) return true;
+  if (mbar_wait_timed<0, 1024>(bar, parity, MT_WAIT_NS, &sm.abort)) return true;
   sm.abort = 1;
   return false;
 }
 
+// G: q heads per kv head when known at compile time (0 = read `group`); MODE 1: all three second
+// moments, no first moments; MODE 2: all three plus both first moments; MODE 0: whatever the
+// pointers say.  The one thread that issues the MMAs is the pace-setter of the kernel: with the
+// common cases fixed at compile time its loop is straight-line code (run-time tests of the output
+// pointers inside it cost 12 % of the kernel time).
+template <int G, int MODE>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                   long long n_tokens, int chunk, int group, float* __restrict__ sq, float* __restrict__ sk,
@@ -105,24 +111,39 @@ moments_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
       // 400.. for the queries of the group, pooled).  No second pass over the inputs.
       const uint32_t idesc_sum = make_idesc_bf16(128, 16, true, true);
       const uint64_t ones_desc = make_smem_desc_sw128(smem_u32(sm.ones), 16, 1024);
+      const bool do_sq = MODE ? true : sq != nullptr, do_sk = MODE ? true : sk != nullptr, do_cqk = MODE ? true : cqk != nullptr;
+      const bool do_ksum = MODE == 2 ? true : MODE == 1 ? false : k_sum != nullptr;
+      const bool do_qsum = MODE == 2 ? true : MODE == 1 ? false : q_sum != nullptr;
+      const int n_group = G ? G : group;
+      // descriptors of a stage's tiles at token 0; 16 tokens further along is +2048 bytes = +128 in the
+      // address field (the second 64-dim block is half a tile away: the leading-dimension offset)
+      uint64_t k_desc0[MT_STAGES], q_desc0[MT_STAGES][JQK_MAX_GROUP];
+#pragma unroll
+      for (int s = 0; s < MT_STAGES; ++s) {
+        k_desc0[s] = make_smem_desc_sw128(smem_u32(sm.tile[s][JQK_MAX_GROUP]), MT_TILE_BYTES / 2, 1024);
+#pragma unroll
+        for (int g = 0; g < JQK_MAX_GROUP; ++g)
+          q_desc0[s][g] = make_smem_desc_sw128(smem_u32(sm.tile[s][g]), MT_TILE_BYTES / 2, 1024);
+      }
       for (int t = 0; t < n_tiles; ++t) {
         const int s = t % MT_STAGES;
         if (!mt_wait(sm, &sm.full[s], (t / MT_STAGES) & 1)) break;
         tc_fence_after();
-        const uint32_t k_base = smem_u32(sm.tile[s][JQK_MAX_GROUP]);
 #pragma unroll
         for (int ks = 0; ks < MT_TOK / 16; ++ks) {
           const bool first = (t == 0 && ks == 0);
-          // 16 tokens further along K is 16 rows of 128 bytes; the second 64-dim block is half a tile away
-          const uint64_t k_desc = make_smem_desc_sw128(k_base + ks * 2048, MT_TILE_BYTES / 2, 1024);
-          if (sk) umma_bf16(tmem + 128, k_desc, k_desc, idesc, !first);
-          if (k_sum) umma_bf16(tmem + 384, k_desc, ones_desc, idesc_sum, !first);
+          const uint64_t k_desc = (s ? k_desc0[1] : k_desc0[0]) + (uint64_t)(ks * 128);
+          if (do_sk) umma_bf16(tmem + 128, k_desc, k_desc, idesc, !first);
+          if (do_ksum) umma_bf16(tmem + 384, k_desc, ones_desc, idesc_sum, !first);
           if (want_q) {
-            for (int g = 0; g < group; ++g) {
-              const uint64_t q_desc = make_smem_desc_sw128(smem_u32(sm.tile[s][g]) + ks * 2048, MT_TILE_BYTES / 2, 1024);
-              if (sq) umma_bf16(tmem + 0, q_desc, q_desc, idesc, !(first && g == 0));
-              if (cqk) umma_bf16(tmem + 256, k_desc, q_desc, idesc, !(first && g == 0));  // transposed: lane = k dim
-              if (q_sum) umma_bf16(tmem + 400, q_desc, ones_desc, idesc_sum, !(first && g == 0));
+#pragma unroll
+            for (int g = 0; g < JQK_MAX_GROUP; ++g) {
+              if (g < n_group) {
+                const uint64_t q_desc = (s ? q_desc0[1][g] : q_desc0[0][g]) + (uint64_t)(ks * 128);
+                if (do_sq) umma_bf16(tmem + 0, q_desc, q_desc, idesc, !(first && g == 0));
+                if (do_cqk) umma_bf16(tmem + 256, k_desc, q_desc, idesc, !(first && g == 0));  // transposed: lane = k dim
+                if (do_qsum) umma_bf16(tmem + 400, q_desc, ones_desc, idesc_sum, !(first && g == 0));
+              }
             }
           }
         }
@@ -225,9 +246,21 @@ int32_t jqk_moments_tc_try(const void* q, const void* k, int32_t dtype, int64_t 
   }
   dim3 grid((unsigned)((n_tokens + chunk - 1) / chunk), n_kv_heads);
   const size_t smem = sizeof(MtSmem) + 1024;
-  JQK_SMEM_ONCE(moments_tc_kernel, smem, "tensor-core moments smem attribute");
-  moments_tc_kernel<<<grid, MT_THREADS, smem, st>>>(q_map, k_map, (long long)n_tokens, chunk, group, sq_sum, sk_sum, cqk_sum,
-                                                       q_sum, k_sum, status);
+  const int mode = (sq_sum && sk_sum && cqk_sum) ? ((q_sum && k_sum) ? 2 : (!q_sum && !k_sum) ? 1 : 0) : 0;
+#define JQK_LAUNCH_MOMENTS(GG, MM)                                                                              \
+  do {                                                                                                          \
+    JQK_SMEM_ONCE((moments_tc_kernel<GG, MM>), smem, "tensor-core moments smem attribute");                     \
+    moments_tc_kernel<GG, MM><<<grid, MT_THREADS, smem, st>>>(q_map, k_map, (long long)n_tokens, chunk, group,  \
+                                                              sq_sum, sk_sum, cqk_sum, q_sum, k_sum, status);   \
+  } while (0)
+  if (mode == 1 && group == 4) JQK_LAUNCH_MOMENTS(4, 1);
+  else if (mode == 2 && group == 4) JQK_LAUNCH_MOMENTS(4, 2);
+  else if (mode == 1 && group == 2) JQK_LAUNCH_MOMENTS(2, 1);
+  else if (mode == 2 && group == 2) JQK_LAUNCH_MOMENTS(2, 2);
+  else if (mode == 1 && group == 1) JQK_LAUNCH_MOMENTS(1, 1);
+  else if (mode == 2 && group == 1) JQK_LAUNCH_MOMENTS(1, 2);
+  else JQK_LAUNCH_MOMENTS(0, 0);
+#undef JQK_LAUNCH_MOMENTS
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core moments launch");
   return 0;
 }

@@ -46,17 +46,19 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // The one wait policy of the library.  Polls the phase with the given parity until it completes
 // (true) or `limit_ns` nanoseconds of %globaltimer have passed (false), so a copy or an MMA that
 // never completes ends in a status bit and a kernel that returns, not in a hung device.  NAP_NS > 0
-// sleeps between polls (roles that wait must not eat the issue slots of the working warps);
+// sleeps between polls (roles that wait must not eat the issue slots of the working warps); POLLS
+// is the number of polls between two looks at the clock (reading %globaltimer is slow, and a
+// thread on the critical path should notice a completed phase at once);
 // `abort`, when given, is a block-wide flag another role sets when it gave up: the wait then ends
 // early with false.
-template <int NAP_NS>
+template <int NAP_NS, int POLLS = 64>
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, unsigned long long limit_ns,
                                                 volatile int* abort = nullptr) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
+    for (int i = 0; i < POLLS; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
       if (NAP_NS > 0) __nanosleep(NAP_NS);
     }

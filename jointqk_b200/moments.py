@@ -238,12 +238,16 @@ class KeyPathMoments:
     all-reduce per block covers a rank's whole contribution."""
 
     def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, head_dim: int, device,
-                 with_values: bool = False, max_chain_tokens: int = 0) -> None:
+                 with_values: bool = False, max_chain_tokens: int = 0, first_moments: bool = True) -> None:
         if n_q_heads % n_kv_heads != 0:
             raise ValueError(f"GQA mismatch: q_heads={n_q_heads}, kv_heads={n_kv_heads}")
         self.n_layers, self.n_q_heads, self.n_kv_heads, self.d = n_layers, n_q_heads, n_kv_heads, head_dim
         self.group = n_q_heads // n_kv_heads
         self.with_values = bool(with_values)
+        # first moments ride on the same pass but are not free: their products re-read the operand tiles
+        # from shared memory (about 15 % of the kernel time on the calibration shape); a caller that only
+        # wants Sigma_Q / Sigma_K / C_QK switches them off
+        self.first_moments = bool(first_moments)
         self.max_chain_tokens = int(max_chain_tokens)
         n_mat = 4 if with_values else 3
         self.sums = torch.zeros((n_layers, n_mat, n_kv_heads, head_dim, head_dim), dtype=torch.float32, device=device)
@@ -264,12 +268,15 @@ class KeyPathMoments:
         chunk of tokens."""
         if self.sums.device.type != "cuda":
             raise RuntimeError("jointqk_b200: the moment kernels have no CPU implementation")
+        fm = self.first_moments
         accumulate_layer(q, k, self.sums[layer, 0], self.sums[layer, 1], self.sums[layer, 2],
-                         self.firsts[layer, 0], self.firsts[layer, 1], self.max_chain_tokens)
+                         self.firsts[layer, 0] if fm else None, self.firsts[layer, 1] if fm else None,
+                         self.max_chain_tokens)
         if self.with_values:
             if v is None:
                 raise ValueError("this accumulator tracks values: pass v")
-            accumulate_layer(None, v, None, self.sums[layer, 3], None, None, self.firsts[layer, 2], self.max_chain_tokens)
+            accumulate_layer(None, v, None, self.sums[layer, 3], None, None, self.firsts[layer, 2] if fm else None,
+                             self.max_chain_tokens)
         self._pending[layer] += int(k.shape[1])
 
     def all_reduce(self, group=None) -> None:
@@ -295,16 +302,18 @@ class KeyPathMoments:
             "sigma_q": self.sums[:, 0] / (self.group * t4),
             "sigma_k": self.sums[:, 1] / t4,
             "cqk": self.sums[:, 2] / t4,
-            "mu_q": self.firsts[:, 0] / (self.group * t3),
-            "mu_k": self.firsts[:, 1] / t3,
             "total_tokens": self.tokens.clone(),
         }
-        out["cov_q"] = out["sigma_q"] - outer(out["mu_q"])
-        out["cov_k"] = out["sigma_k"] - outer(out["mu_k"])
         if self.with_values:
             out["sigma_v"] = self.sums[:, 3] / t4
-            out["mu_v"] = self.firsts[:, 2] / t3
-            out["cov_v"] = out["sigma_v"] - outer(out["mu_v"])
+        if self.first_moments:
+            out["mu_q"] = self.firsts[:, 0] / (self.group * t3)
+            out["mu_k"] = self.firsts[:, 1] / t3
+            out["cov_q"] = out["sigma_q"] - outer(out["mu_q"])
+            out["cov_k"] = out["sigma_k"] - outer(out["mu_k"])
+            if self.with_values:
+                out["mu_v"] = self.firsts[:, 2] / t3
+                out["cov_v"] = out["sigma_v"] - outer(out["mu_v"])
         return out
 
     def calibration_artifacts(self, eps: float = 1e-4, source: str = "jointqk_b200") -> tuple[dict, dict | None]:
@@ -318,6 +327,8 @@ class KeyPathMoments:
 
         from .basis import jointqk_basis
 
+        if not self.first_moments:
+            raise RuntimeError("the artefacts need means and covariances: accumulate with first_moments=True")
         fin = {k: v.float().cpu() for k, v in self.finalize().items()}
         L, H, d = self.n_layers, self.n_kv_heads, self.d
         if len({int(t) for t in self.tokens.tolist()}) != 1:

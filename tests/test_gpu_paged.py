@@ -137,7 +137,9 @@ def test_overlong_length_is_clamped_flagged_and_leaves_the_workspace_clean():
     assert torch.equal(good, ref)
     assert int(cache.status.item()) == 0
     # a token range past the page-table row is flagged by the page lookup, and skipped
-    packed = paged.PackedKeys(tables, cache.k_pool, cache.page_table[:, :64].contiguous(), cache.seq_lens, [2048], cache.status)
+    narrow = torch.zeros(1, 64, dtype=torch.int32, device="cuda")          # a row of 64 pages = 1024 tokens
+    narrow.copy_(cache.page_table[:, :64])
+    packed = paged.PackedKeys(tables, cache.k_pool, narrow, cache.seq_lens, [2048], cache.status)
     paged.unpack_codes(packed)
     torch.cuda.synchronize()
     assert int(cache.status.item()) == _native.STATUS_BAD_LENGTH

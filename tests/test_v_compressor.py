@@ -21,16 +21,29 @@ def _build(g, method, bits, centred=True):
                                  mu_v_for_head=_t(g["mu_v"]) if centred else None)
 
 
+def _from_fixture(g, method, bits, centred=True):
+    """The compressor the reference built, from its stored bits / stds / basis: an eigendecomposition
+    redone on another host may differ in the last bits, which moves codes that sit on a decision
+    boundary, so the GPU comparison must not depend on refitting."""
+    tag = f"{method}_{bits}"
+    fwd = _t(g[f"ref_forward_{tag}"])
+    inner = jq.PerCoordCompressor(_t(g[f"ref_bits_{tag}"]), _t(g[f"ref_stds_{tag}"]), forward_map=fwd,
+                                  inverse_map=fwd.transpose(-1, -2))
+    assert torch.equal(inner.codebooks_padded, _t(g[f"ref_codebooks_{tag}"]))
+    return jq.CenteredCompressor(inner, _t(g["mu_v"])) if centred else inner
+
+
 @pytest.mark.parametrize("method,bits", CASES)
 def test_fit_equals_reference_and_oracle_centring_is_pinned(golden, method, bits):
     g = golden("v_compressor")
     tag = f"{method}_{bits}"
     comp = _build(g, method, bits)
     assert torch.equal(comp.inner.bits_int, _t(g[f"ref_bits_{tag}"]))
-    assert torch.equal(comp.inner.stds, _t(g[f"ref_stds_{tag}"]))
-    assert torch.equal(comp.inner.forward_map, _t(g[f"ref_forward_{tag}"]))
-    assert torch.equal(comp.inner.codebooks_padded, _t(g[f"ref_codebooks_{tag}"]))
+    torch.testing.assert_close(comp.inner.stds, _t(g[f"ref_stds_{tag}"]), rtol=1e-4, atol=1e-7)
+    fwd = _t(g[f"ref_forward_{tag}"])
+    assert float((comp.inner.forward_map * fwd).sum(0).abs().min()) > 0.999       # same basis up to column sign
     assert int(comp.inner.bits_int.sum()) == bits * 128
+    comp = _from_fixture(g, method, bits)
     for dtype, name in ((torch.float32, "ref_roundtrip_"), (torch.bfloat16, "ref_roundtrip_bf16_")):
         out, _ = orc.centred_roundtrip(_t(g["values"]).to(dtype), comp.mu, comp.inner.codebooks_padded,
                                        comp.inner.forward_map, comp.inner.inverse_map)
@@ -54,7 +67,7 @@ def test_builder_errors_follow_the_reference():
 def test_cuda_roundtrip_matches_the_reference(golden, method, bits, dtype):
     g = golden("v_compressor")
     tag = f"{method}_{bits}"
-    comp = _build(g, method, bits)
+    comp = _from_fixture(g, method, bits)
     vals = _t(g["values"]).to(dtype)
     ref = _t(g[("ref_roundtrip_" if dtype == torch.float32 else "ref_roundtrip_bf16_") + tag])
     _, ref_codes = orc.centred_roundtrip(vals, comp.mu, comp.inner.codebooks_padded, comp.inner.forward_map,
@@ -76,7 +89,7 @@ def test_cuda_roundtrip_matches_the_reference(golden, method, bits, dtype):
 @pytest.mark.gpu
 def test_uncentred_value_compressor_and_mean_handling(golden):
     g = golden("v_compressor")
-    plain = _build(g, "v_eigen_uniform", 3, centred=False)
+    plain = _from_fixture(g, "v_eigen_uniform", 3, centred=False)
     out = plain.roundtrip(_t(g["values"]).cuda()).cpu()
     ref = _t(g["ref_roundtrip_uncentred_v_eigen_uniform_3"])
     close = (out - ref).abs().amax(-1) < 1e-5 * float(ref.abs().max())
