@@ -685,6 +685,49 @@ def bench_isolated_launch(step, device, alg_bytes: float, hbm_gbs: float) -> dic
             "note": "median of 32 single launches, each synchronised before and after (event overhead of ~2 us included)"}
 
 
+def bench_decode_packed_values(device, hbm_gbs: float, peak_kind: str) -> dict:
+    """The headline decode shape with the values stored as packed codes too: K at 2.0 bits, V at 3.0
+    bits (eigenbasis of Cov[V], water-fill, mean-centred), 80 bytes per key and head instead of 288.
+    The pools hold random codes (the kernel's work does not depend on their content); 8 caches rotate."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, second_moment, spectrum_keys
+
+    keys = torch.stack([spectrum_keys(4096, config_seed(1, 0, h)) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys, B_AVG)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    vals = torch.stack([spectrum_keys(4096, config_seed(1, 1, h), n_outliers=0) for h in range(N_KV_HEADS)]) + 0.1
+    v_comps = []
+    for h in range(N_KV_HEADS):
+        mu = vals[h].double().mean(0).float()
+        v_comps.append(jq.build_v_compressor("v_eigen_waterfill", cov_v_for_head=second_moment(vals[h]) - torch.outer(mu, mu),
+                                             head_dim=HEAD_DIM, bits=3, mu_v_for_head=mu, max_bits=4))
+    v_tables = jq.HeadTables.from_compressors([c.inner for c in v_comps], device=device, center=torch.stack([c.mu for c in v_comps]))
+    gen = torch.Generator(device=device)
+    gen.manual_seed(5)
+    q = torch.randn(1, N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    caches = []
+    for _ in range(8):
+        c = paged.PagedKVCache(tables, [CTX], v_tables=v_tables)
+        c.k_pool.random_(0, 2 ** 31 - 1, generator=gen)
+        c.v_pool.random_(0, 2 ** 31 - 1, generator=gen)
+        c.lengths = [CTX]
+        c.seq_lens[:] = CTX
+        caches.append(c)
+    run = lambda i: caches[i % 8].decode(q)
+    for i in range(16):
+        run(i)
+    ms = region_ms(run, 200, device, 1) / 200
+    paged.check_status(caches[0].status)
+    nbytes = CTX * N_KV_HEADS * (tables.payload_bytes_per_key + v_tables.payload_bytes_per_key) + 2 * N_KV_HEADS * HEAD_DIM * HEAD_DIM * 4
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": "decode, 1 layer, 32 q / 8 kv heads, context 32768, K 2.0 bits and V 3.0 bits packed (80 B per key and head)",
+            "value": 1.0 / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "cache_bytes_per_step": nbytes,
+            "cache_bytes_vs_bf16_values": nbytes / (CTX * N_KV_HEADS * (tables.payload_bytes_per_key + 2 * HEAD_DIM)),
+            "roofline": {"bound": "shared memory (dequantisation), not hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": gbs / hbm_gbs, "peak_kind": peak_kind}}
+
+
 def bench_value_store(device, hbm_gbs: float, peak_kind: str) -> dict:
     """Values of one layer of the prefill config into pages: 4 sequences x 8 kv heads x 131072 bf16 rows,
     one pass of the store kernel (256 B read + 256 B written per row)."""
@@ -856,6 +899,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             extra["prefill_values"] = bench_value_store(device, hbm_gbs, peak_kind)
             extra["calibration_moments"] = bench_moments(device, hbm_gbs, tflops, peak_kind)
             extra["decode_batch"] = bench_decode_batch(device, hbm_gbs, peak_kind)
+            extra["decode_packed_values"] = bench_decode_packed_values(device, hbm_gbs, peak_kind)
         del caches[:]
         torch.cuda.empty_cache()
         # the partitioned workloads run at every N: sequences, tokens and (sequence, head) units over the ranks
@@ -946,7 +990,7 @@ def main() -> None:
     ap.add_argument("--workload", default="headline", choices=["headline", "batch64"],
                     help="headline: the single-layer context-32768 step (default, what the JSON contract names); "
                          "batch64: the 32-layer, 64-sequence decode config sharded by sequence over the ranks")
-    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "scale"],
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "packed_values", "scale"],
                     help="run only one of the secondary stages (or the three partitioned workloads) and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -963,7 +1007,8 @@ def main() -> None:
         hbm, tf, kind = measured_peaks()
         res = (bench_compress(dev, hbm, kind) if args.stage == "compress" else
                bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else
-               bench_value_store(dev, hbm, kind) if args.stage == "values" else bench_moments(dev, hbm, tf, kind))
+               bench_value_store(dev, hbm, kind) if args.stage == "values" else
+               bench_decode_packed_values(dev, hbm, kind) if args.stage == "packed_values" else bench_moments(dev, hbm, tf, kind))
         print(json.dumps(res), flush=True)
         return
     if world > 1:

@@ -211,6 +211,26 @@ int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t 
                           size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
+ * jqk_decode_attend over packed values: the value pool holds codes of a second per-coordinate
+ * compressor (`v_tables`, optionally centred) in the same paged record format as the keys, written
+ * by jqk_compress_paged with those tables.  The kernel dequantises a tile of values into shared
+ * memory (bf16 centroids), accumulates softmax-weighted sums in the value basis and applies the
+ * value side's inverse map and mean once per query head at the end:
+ * out = (sum_t p_t x_hat_t) @ inverse_map_v + mu_v.  In the reference the same result comes from stock
+ * attention over values reconstructed by the V-side compressor
+ * (experiments/stage1/toolkit/v_compressor_adapter.py:46-72,165-226; jointqk_press.py:262-266).
+ *   v_code_pool  uint32 [n_pages][n_kv_heads][v_tables->words_per_record][16]
+ * Everything else as in jqk_decode_attend (same workspace size).
+ */
+int32_t jqk_decode_attend_packed_values(const jqk_head_tables* tables, const jqk_head_tables* v_tables,
+                                        const void* q, int32_t n_seqs, int32_t n_q_heads,
+                                        const int32_t* seq_lens, int32_t max_seq_len, int32_t tokens_per_split,
+                                        const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
+                                        const uint32_t* k_pool, const uint32_t* v_code_pool, void* out,
+                                        int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                                        int32_t* status, void* stream);
+
+/*
  * jqk_decode_attend from host memory, one call per decode step (no counterpart in the reference,
  * whose attention inputs are device tensors of the model): copies the query from `q_host` to the
  * device, runs the step, copies the result to `out_host` and waits for it, all on `stream`.

@@ -122,28 +122,55 @@ struct DecodeWs {
 
 // Per-warp staging of one tile: the two V pages (dims-major, see the V page layout in the file
 // header) and the two K pages, filled by bulk asynchronous copies that the warp issues itself.
+// With packed values (VQ) the copies bring the two pages of V codes into `vq` and the warp
+// dequantises them into `v`, in the same dims-major layout (rows are then columns of the value
+// basis), so the tensor-core product reads either kind the same way.
 constexpr int K_STAGE_STRIDE = JQK_MAX_WORDS * JQK_PAGE_TOKENS * 4 + 64;  // +64 B: the two pages hit different banks
-struct alignas(128) TileStage {
-  uint8_t v[2][JQK_PAGE_TOKENS * JQK_MAX_DIM * 2];  // the two V pages of the current tile, 2 x 4096 B
-  uint8_t k[2][2][K_STAGE_STRIDE];                  // the K pages of two tiles (double buffer), 4 x 1088 B
+constexpr int V_PAGE_SMEM = JQK_PAGE_TOKENS * JQK_MAX_DIM * 2;            // 4096
+template <bool VQ> struct TileStageT;
+template <> struct alignas(128) TileStageT<false> {
+  uint8_t v[2][V_PAGE_SMEM];         // the two V pages of the current tile, 2 x 4096 B
+  uint8_t k[2][2][K_STAGE_STRIDE];   // the K pages of two tiles (double buffer), 4 x 1088 B
+};
+template <> struct alignas(128) TileStageT<true> {
+  uint8_t v[2][V_PAGE_SMEM + 64];    // dequantised values of the current tile (+64 B: a lane-per-key store
+                                     // of one column touches both pages, which must not share banks)
+  uint8_t k[2][2][K_STAGE_STRIDE];
+  uint8_t vq[2][K_STAGE_STRIDE];     // the two pages of V codes of the current tile
 };
 
-struct DecodeSmem {
+template <bool VQ> struct DecodeSmemT;
+template <> struct DecodeSmemT<false> {
   union {            // the tables this block scores with:
     TableRecord rec;   //   a copy of the table kernel's record, or
     TableSmem build;   //   tables built by the block itself (few blocks: latency matters more than repeated work)
   } t;
-  TileStage stage[DEC_WARPS];
+  TileStageT<false> stage[DEC_WARPS];
   uint64_t tfull;
   uint64_t kfull[DEC_WARPS][2];
   uint64_t vfull[DEC_WARPS];
-  __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
+  alignas(16) __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];  // P hi / lo per warp
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
 };
+template <> struct DecodeSmemT<true> {
+  struct { TableRecord rec; } t;     // the key tables always come from the table kernel
+  TileStageT<true> stage[DEC_WARPS];
+  uint64_t tfull;
+  uint64_t kfull[DEC_WARPS][2];
+  uint64_t vfull[DEC_WARPS];
+  alignas(16) __nv_bfloat16 pbuf[DEC_WARPS][2][JQK_MAX_GROUP][TILE_TOK];
+  float wm[DEC_WARPS][JQK_MAX_GROUP];
+  float wl[DEC_WARPS][JQK_MAX_GROUP];
+  int is_last;
+  int32_t vmeta[JQK_MAX_COLS];                    // value columns: width | bit position << 4
+  __nv_bfloat16 vcb[JQK_MAX_COLS * 16];           // value codebooks, bf16 (what the tensor-core product multiplies)
+};
 // A warp's stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
-static_assert(sizeof(TileStage) >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM, "stage too small for the partial output");
+static_assert(sizeof(TileStageT<false>) >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM, "stage too small for the partial output");
+static_assert(sizeof(DecodeSmemT<true>) <= 232448 && sizeof(DecodeSmemT<false>) <= 232448, "decode shared memory");
+static_assert(offsetof(DecodeSmemT<true>, pbuf) % 16 == 0, "the packed-value epilogue writes float4 into pbuf");
 
 __device__ __forceinline__ void store_out(void* out, int out_dtype, size_t idx, float v) {
   if (out_dtype == JQK_DTYPE_F32) ((float*)out)[idx] = v;
@@ -237,18 +264,49 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   if (threadIdx.x == 0) rec->bias = sm.bias;
 }
 
-// D = head_dim (64 or 128).
-template <int D, bool BUILD_IN_BLOCK>
+// What the kernel needs of the value-side tables when values are stored as packed codes.
+struct ValueSide {
+  const int32_t* desc;      // [H][JQK_DESC_INTS]
+  const int32_t* col_meta;  // [H][128]
+  const float* cb_cols;     // [H][128][16]
+  const float* inv_rows;    // [H][128][d]
+  const float* center;      // [H][d] or null
+  int n_heads, wpr;
+};
+
+// (sum_t p_t x_hat_t) / L in the value basis -> attention output: one 128 x d product per query head
+// with the value side's inverse map, plus the mean the values were centred with.  `yb`: shared,
+// [JQK_MAX_GROUP][128] normalised sums, then JQK_MAX_GROUP flags (some key was attended).
+template <int D>
+__device__ __forceinline__ void values_to_output(const float* yb, int n_group, const ValueSide& vs, int head, int n_cols,
+                                                 void* out, int out_dtype, size_t qrow0) {
+  const float* inv = vs.inv_rows + (size_t)head * 128 * D;
+  for (int e = threadIdx.x; e < n_group * D; e += DEC_THREADS) {
+    const int h = e / D, i = e % D;
+    float a = 0.f;
+#pragma unroll 8
+    for (int cc = 0; cc < n_cols; ++cc) a = fmaf(yb[h * 128 + cc], __ldg(inv + (size_t)cc * D + i), a);
+    const bool some = yb[JQK_MAX_GROUP * 128 + h] != 0.f;
+    if (vs.center && some) a += vs.center[(size_t)head * D + i];
+    store_out(out, out_dtype, (qrow0 + h) * D + i, some ? a : 0.f);
+  }
+}
+
+// D = head_dim (64 or 128).  VQ: values are packed codes of a second compressor (v_pool is then the
+// uint32 code pool, `vs` its tables); the keys' tables then always come from the table kernel.
+template <int D, bool BUILD_IN_BLOCK, bool VQ>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
               const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
-              const uint32_t* __restrict__ k_pool, const __nv_bfloat16* __restrict__ v_pool,
-              void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status) {
+              const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
+              void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs) {
+  static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
+  DecodeSmemT<VQ>& sm = *reinterpret_cast<DecodeSmemT<VQ>*>(smem_raw);
+  const __nv_bfloat16* v_pool = reinterpret_cast<const __nv_bfloat16*>(v_pool_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
   const int group = n_q_heads / tb.n_heads;
@@ -294,6 +352,18 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const uint32_t* k_head = k_pool + (size_t)head * wpr * JQK_PAGE_TOKENS;
   const __nv_bfloat16* v_head = v_pool + (size_t)head * JQK_PAGE_TOKENS * D;
   const uint32_t k_page_bytes = (uint32_t)hd.n_words * JQK_PAGE_TOKENS * 4;
+  // packed values: pages of the value code pool, one head's block inside a page
+  const uint32_t* vq_head = nullptr;
+  size_t vq_page_words = 0;
+  uint32_t vq_page_bytes = 0;
+  int v_n_active = 0;
+  if constexpr (VQ) {
+    const HeadDesc vhd = load_desc(vs.desc, head);
+    vq_head = reinterpret_cast<const uint32_t*>(v_pool_raw) + (size_t)head * vs.wpr * JQK_PAGE_TOKENS;
+    vq_page_words = (size_t)vs.n_heads * vs.wpr * JQK_PAGE_TOKENS;
+    vq_page_bytes = (uint32_t)vhd.n_words * JQK_PAGE_TOKENS * 4;
+    v_n_active = vhd.n_active;
+  }
 
   // ---- this warp's run of tiles and its page ids ----
   const int tiles_total = (t_end - t_begin + TILE_TOK - 1) / TILE_TOK;
@@ -311,7 +381,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // Lane 0 starts the copies of a tile (pages pg_lo / pg_hi, -1 = absent).  K pages of tile r go to
   // K buffer r & 1, V pages to the single V buffer.  Buffers are refilled by the warp that read
   // them, in program order after its last read, so no "empty" barriers are needed.
-  TileStage& st = sm.stage[warp];
+  TileStageT<VQ>& st = sm.stage[warp];
   const uint64_t stream_policy = l2_evict_first_policy();
   auto issue_keys = [&](int r, int pg_lo, int pg_hi) {
     if (lane == 0) {
@@ -328,9 +398,15 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       uint64_t* bar = &sm.vfull[warp];
       const int t0 = t_begin + (tile_lo + r) * TILE_TOK;
       const bool ok0 = pg_lo >= 0, ok1 = pg_hi >= 0 && t0 + JQK_PAGE_TOKENS < t_end;
-      bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * V_PAGE_BYTES);
-      if (ok0) bulk_load_stream(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
-      if (ok1) bulk_load_stream(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
+      if constexpr (VQ) {
+        bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * vq_page_bytes);
+        if (ok0) bulk_load_stream(st.vq[0], vq_head + (size_t)pg_lo * vq_page_words, vq_page_bytes, bar, stream_policy);
+        if (ok1) bulk_load_stream(st.vq[1], vq_head + (size_t)pg_hi * vq_page_words, vq_page_bytes, bar, stream_policy);
+      } else {
+        bar_expect_tx(bar, ((ok0 ? 1u : 0u) + (ok1 ? 1u : 0u)) * V_PAGE_BYTES);
+        if (ok0) bulk_load_stream(st.v[0], v_head + (size_t)pg_lo * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
+        if (ok1) bulk_load_stream(st.v[1], v_head + (size_t)pg_hi * v_page_elems, V_PAGE_BYTES, bar, stream_policy);
+      }
     }
   };
   // the first copies go in flight before the tables exist, so HBM works during the prologue
@@ -349,6 +425,16 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];
   } else {
+    if constexpr (VQ) {
+      // value-side tables of this head (static per head: no query enters them), and a clean tile:
+      // rows of columns that carry no bits are never written by the dequantiser and must read as 0
+      for (int e = tid; e < JQK_MAX_COLS; e += DEC_THREADS)
+        sm.vmeta[e] = (e < v_n_active) ? (__ldg(vs.col_meta + (size_t)head * 128 + e) & 0x3FFF) : 0;
+      for (int e = tid; e < JQK_MAX_COLS * 16; e += DEC_THREADS)
+        sm.vcb[e] = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
+      uint4* z = reinterpret_cast<uint4*>(&st.v[0][0]);
+      for (int e = lane; e < (int)(sizeof(st.v) / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
+    }
     // the finished tables of this (sequence, head group) come from the table kernel
     if (tid == 0) {
       const TableRecord* rec = ws.tables + (size_t)seq * gridDim.y + blockIdx.y;
@@ -438,7 +524,28 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
-    if (any && t0 + TILE_TOK > t_end) {
+    if constexpr (VQ) {
+      // dequantise this lane's key into the tile: column after column, code -> bf16 centroid -> the
+      // key's slot of the column's row (dims-major, the layout the tensor-core product reads).  Keys
+      // past the end or on absent pages produce finite garbage that meets a zero weight.
+      if (any && landed) {
+        const uint32_t* vw = reinterpret_cast<const uint32_t*>(st.vq[lane >> 4]) + (lane & 15);
+        uint8_t* vt = st.v[lane >> 4];
+        const int ts = lane & 15;
+        const uint32_t off_a = (uint32_t)((ts >> 3) * 16 + (ts & 7) * 2);        // rows with (column >> 2) & 1 == 0
+        const uint32_t off_b = (uint32_t)(((ts >> 3) ^ 1) * 16 + (ts & 7) * 2);  // the swapped halves
+        int cur_w = -1;
+        uint32_t word = 0u;
+#pragma unroll 4
+        for (int cc = 0; cc < v_n_active; ++cc) {
+          const int m = sm.vmeta[cc];
+          const int bp = m >> 4, w = bp >> 5;
+          if (w != cur_w) { word = vw[w * JQK_PAGE_TOKENS]; cur_w = w; }   // warp-uniform
+          const uint32_t code = (word >> (bp & 31)) & ((1u << (m & 15)) - 1u);
+          *reinterpret_cast<__nv_bfloat16*>(vt + cc * 32 + (((cc >> 2) & 1) ? off_b : off_a)) = sm.vcb[cc * 16 + code];
+        }
+      }
+    } else if (any && t0 + TILE_TOK > t_end) {
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb) {
         const int n_valid = min(JQK_PAGE_TOKENS, max(0, t_end - (t0 + JQK_PAGE_TOKENS * kb)));
@@ -487,7 +594,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 
   // ---- combine the warps of this block (each warp reuses its own first stage) ---------------
   float* wacc = reinterpret_cast<float*>(&sm.stage[0]);  // warp w at w * WACC_STRIDE floats
-  constexpr int WACC_STRIDE = (int)(sizeof(TileStage) / sizeof(float));
+  constexpr int WACC_STRIDE = (int)(sizeof(TileStageT<VQ>) / sizeof(float));
+  float* yb = reinterpret_cast<float*>(&sm.pbuf[0][0][0][0]);  // packed values: normalised sums in the value basis
 #pragma unroll
   for (int h = 0; h < JQK_MAX_GROUP; ++h) l_run[h] = warp_sum(l_run[h]);
   if (lane == 0) {
@@ -526,11 +634,22 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     const size_t qrow = (size_t)seq * n_q_heads + qh0 + h;
     if (single) {
-      store_out(out, out_dtype, qrow * D + i, L > 0.f ? A / L : 0.f);
+      if constexpr (VQ) {
+        yb[h * 128 + i] = L > 0.f ? A / L : 0.f;
+        if (i == 0) yb[JQK_MAX_GROUP * 128 + h] = L > 0.f ? 1.f : 0.f;
+      } else {
+        store_out(out, out_dtype, qrow * D + i, L > 0.f ? A / L : 0.f);
+      }
     } else {
       const size_t pidx = qrow * ws.max_splits + split;
       ws.part_acc[pidx * JQK_MAX_DIM + i] = A;
       if (i == 0) { ws.part_m[pidx] = M; ws.part_l[pidx] = L; }
+    }
+  }
+  if constexpr (VQ) {
+    if (single) {
+      __syncthreads();
+      values_to_output<D>(yb, n_group, vs, head, v_n_active, out, out_dtype, (size_t)seq * n_q_heads + qh0);
     }
   }
   if (single) return;
@@ -614,11 +733,21 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       a4.x += o.x; a4.y += o.y; a4.z += o.z; a4.w += o.w;
     }
     const float L = sm.wl[0][mh];
-    const size_t o0 = ((size_t)seq * n_q_heads + qh0 + mh) * D + 4 * mi;
-    store_out(out, out_dtype, o0 + 0, L > 0.f ? a4.x / L : 0.f);
-    store_out(out, out_dtype, o0 + 1, L > 0.f ? a4.y / L : 0.f);
-    store_out(out, out_dtype, o0 + 2, L > 0.f ? a4.z / L : 0.f);
-    store_out(out, out_dtype, o0 + 3, L > 0.f ? a4.w / L : 0.f);
+    if constexpr (VQ) {
+      const float r = L > 0.f ? 1.f / L : 0.f;
+      *reinterpret_cast<float4*>(yb + mh * 128 + 4 * mi) = make_float4(a4.x * r, a4.y * r, a4.z * r, a4.w * r);
+      if (mi == 0) yb[JQK_MAX_GROUP * 128 + mh] = L > 0.f ? 1.f : 0.f;
+    } else {
+      const size_t o0 = ((size_t)seq * n_q_heads + qh0 + mh) * D + 4 * mi;
+      store_out(out, out_dtype, o0 + 0, L > 0.f ? a4.x / L : 0.f);
+      store_out(out, out_dtype, o0 + 1, L > 0.f ? a4.y / L : 0.f);
+      store_out(out, out_dtype, o0 + 2, L > 0.f ? a4.z / L : 0.f);
+      store_out(out, out_dtype, o0 + 3, L > 0.f ? a4.w / L : 0.f);
+    }
+  }
+  if constexpr (VQ) {
+    __syncthreads();
+    values_to_output<D>(yb, n_group, vs, head, v_n_active, out, out_dtype, (size_t)seq * n_q_heads + qh0);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
 }
@@ -719,14 +848,21 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_
   return 0;
 }
 
-extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
-                                     int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
-                                     int32_t tokens_per_split, const int32_t* page_table,
-                                     int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
-                                     const void* v_pool, void* out, int32_t out_dtype, void* workspace,
-                                     size_t workspace_bytes, int32_t* status, void* stream) {
+// One decode step; `v_tables` non-null: `v_pool` holds packed value codes of that compressor.
+static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_tables* v_tables, const void* q, int32_t n_seqs,
+                             int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                             int32_t tokens_per_split, const int32_t* page_table,
+                             int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                             const void* v_pool, void* out, int32_t out_dtype, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
+  if (v_tables) {
+    rc = check_tables(v_tables);
+    if (rc) return rc;
+    if (v_tables->n_heads != tables->n_heads || v_tables->d != tables->d)
+      return fail(JQK_E_LAYOUT, "key and value tables disagree on heads or head_dim");
+  }
   if (n_seqs < 0 || max_seq_len < 0) return fail(JQK_E_ARG, "negative size");
   if (n_seqs == 0) return 0;
   if (!q || !seq_lens || !out) return fail(JQK_E_ARG, "null q, seq_lens or out");
@@ -759,7 +895,7 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   cudaStream_t st = (cudaStream_t)stream;
   // One wave of blocks or less: every block builds its own tables (no second launch on the
   // critical path).  More: a table kernel builds them once per group and the blocks copy them.
-  const bool in_block = (long long)max_splits * tables->n_heads * qbl * n_seqs <= 148;
+  const bool in_block = !v_tables && (long long)max_splits * tables->n_heads * qbl * n_seqs <= 148;
   if (max_seq_len > 0 && !in_block) {
     JQK_SMEM_ONCE(decode_tables_kernel, sizeof(TableSmem), "decode tables smem attribute");
     decode_tables_kernel<<<dim3(tables->n_heads * qbl, n_seqs), TBL_BUILD_THREADS, sizeof(TableSmem), st>>>(
@@ -774,23 +910,54 @@ extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(DEC_THREADS);
-  cfg.dynamicSmemBytes = sizeof(DecodeSmem);
   cfg.stream = st;
   cfg.attrs = pdl_attr;
   cfg.numAttrs = 1;
-#define JQK_LAUNCH_DECODE(DIM, INB)                                                                              \
-  do {                                                                                                           \
-    JQK_SMEM_ONCE((decode_kernel<DIM, INB>), sizeof(DecodeSmem), "decode smem attribute");                       \
-    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB>, *tables, (const __nv_bfloat16*)q, n_q_heads,   \
-                                   seq_lens, tokens_per_split, page_table, page_table_stride, n_pages, k_pool,   \
-                                   (const __nv_bfloat16*)v_pool, out, out_dtype, ws, status),                    \
-                "decode launch");                                                                                \
+  ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+  if (v_tables)
+    vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
+                   v_tables->n_heads, v_tables->words_per_record};
+#define JQK_LAUNCH_DECODE(DIM, INB, VQQ)                                                                              \
+  do {                                                                                                                \
+    cfg.dynamicSmemBytes = sizeof(DecodeSmemT<VQQ>);                                                                  \
+    JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");                 \
+    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ>, *tables, (const __nv_bfloat16*)q, n_q_heads,   \
+                                   seq_lens, tokens_per_split, page_table, page_table_stride, n_pages, k_pool,        \
+                                   v_pool, out, out_dtype, ws, status, vs),                                           \
+                "decode launch");                                                                                     \
   } while (0)
-  if (tables->d == 128) { if (in_block) JQK_LAUNCH_DECODE(128, true); else JQK_LAUNCH_DECODE(128, false); }
-  else { if (in_block) JQK_LAUNCH_DECODE(64, true); else JQK_LAUNCH_DECODE(64, false); }
+  if (v_tables) {
+    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true); else JQK_LAUNCH_DECODE(64, false, true);
+  } else if (tables->d == 128) {
+    if (in_block) JQK_LAUNCH_DECODE(128, true, false); else JQK_LAUNCH_DECODE(128, false, false);
+  } else {
+    if (in_block) JQK_LAUNCH_DECODE(64, true, false); else JQK_LAUNCH_DECODE(64, false, false);
+  }
 #undef JQK_LAUNCH_DECODE
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
   return 0;
+}
+
+extern "C" int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t n_seqs,
+                                     int32_t n_q_heads, const int32_t* seq_lens, int32_t max_seq_len,
+                                     int32_t tokens_per_split, const int32_t* page_table,
+                                     int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
+                                     const void* v_pool, void* out, int32_t out_dtype, void* workspace,
+                                     size_t workspace_bytes, int32_t* status, void* stream) {
+  return decode_launch(tables, nullptr, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                       page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int32_t jqk_decode_attend_packed_values(const jqk_head_tables* tables, const jqk_head_tables* v_tables,
+                                                   const void* q, int32_t n_seqs, int32_t n_q_heads,
+                                                   const int32_t* seq_lens, int32_t max_seq_len, int32_t tokens_per_split,
+                                                   const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
+                                                   const uint32_t* k_pool, const uint32_t* v_code_pool, void* out,
+                                                   int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                                                   int32_t* status, void* stream) {
+  if (!v_tables) return fail(JQK_E_ARG, "null value tables");
+  return decode_launch(tables, v_tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                       page_table_stride, n_pages, k_pool, v_code_pool, out, out_dtype, workspace, workspace_bytes, status, stream);
 }
 
 extern "C" int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const void* q_host, void* q_pinned,

@@ -227,10 +227,23 @@ def split_for_lengths(lengths: list[int], n_q_heads: int, n_kv_heads: int) -> in
 def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int,
                   page_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                   out: torch.Tensor, workspace: DecodeWorkspace | None, status: torch.Tensor,
-                  tokens_per_split: int = 0) -> torch.Tensor:
-    """One decode step for one layer.  q bf16 (n_seqs, Hq, d); out fp32 or bf16 (n_seqs, Hq, d)."""
+                  tokens_per_split: int = 0, v_tables: HeadTables | None = None) -> torch.Tensor:
+    """One decode step for one layer.  q bf16 (n_seqs, Hq, d); out fp32 or bf16 (n_seqs, Hq, d).
+    With ``v_tables`` the value pool holds packed codes of that compressor (int32 storage)."""
     if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
+    if v_tables is not None:
+        if v_pool.dtype != torch.int32:
+            raise ValueError("a packed value pool is int32 storage")
+        if out.shape != q.shape or not out.is_contiguous():
+            raise ValueError("out must be contiguous with the shape of q")
+        ws_ptr, ws_bytes = (None, 0) if workspace is None else (workspace.buf.data_ptr(), workspace.buf.numel())
+        _native.check(_native.lib.jqk_decode_attend_packed_values(
+            tables.ref, v_tables.ref, q.data_ptr(), q.shape[0], q.shape[1], seq_lens.data_ptr(), int(max_seq_len),
+            int(tokens_per_split), page_table.data_ptr(), page_table.stride(0), int(k_pool.shape[0]),
+            k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), _native.torch_dtype_code(out.dtype),
+            ws_ptr, ws_bytes, status.data_ptr(), _stream_ptr(tables.device)))
+        return out
     if v_pool.dtype != torch.bfloat16:
         raise ValueError("v_pool must be bf16")
     if out.shape != q.shape or not out.is_contiguous():
@@ -250,14 +263,18 @@ class PagePool:
     allocated, the old contents copied over and the old tensors dropped, so page indices stay valid
     and only the base pointers change (``generation`` counts the moves)."""
 
-    def __init__(self, tables: HeadTables, n_pages: int, growth: float = 1.5) -> None:
+    def __init__(self, tables: HeadTables, n_pages: int, growth: float = 1.5, v_tables: HeadTables | None = None) -> None:
         self.tables = tables
+        self.v_tables = v_tables          # values as packed codes of this compressor instead of bf16
         self.growth = float(growth)
         n_pages = max(1, int(n_pages))
         self.k_pool = alloc_k_pool(tables, n_pages)
-        self.v_pool = alloc_v_pool(tables, n_pages)
+        self.v_pool = self._alloc_v(n_pages)
         self._free = list(range(n_pages - 1, -1, -1))   # pop() hands out ascending indices
         self.generation = 0
+
+    def _alloc_v(self, n_pages: int) -> torch.Tensor:
+        return alloc_v_pool(self.tables, n_pages) if self.v_tables is None else alloc_k_pool(self.v_tables, n_pages)
 
     @property
     def n_pages(self) -> int:
@@ -271,7 +288,7 @@ class PagePool:
         old = self.n_pages
         if n_pages <= old:
             return
-        k_new, v_new = alloc_k_pool(self.tables, n_pages), alloc_v_pool(self.tables, n_pages)
+        k_new, v_new = alloc_k_pool(self.tables, n_pages), self._alloc_v(n_pages)
         k_new[:old].copy_(self.k_pool)
         v_new[:old].copy_(self.v_pool)
         self.k_pool, self.v_pool = k_new, v_new
@@ -296,11 +313,16 @@ class PagedKVCache:
     ``decode`` runs the fused attention kernel; ``release`` returns a sequence's pages to the pool.
     ``max_lengths`` reserves pages up front (sequence after sequence, which is all the fixed-size
     workloads need); with ``n_seqs`` alone the cache starts empty and grows, and so does the pool.
+
+    With ``v_tables`` (the head tables of a value-side compressor, centred or not) the values are
+    stored as packed codes as well: ``prefill`` compresses them with the same kernel as the keys and
+    ``decode`` dequantises them tile by tile inside the attention kernel.
     """
 
     def __init__(self, tables: HeadTables, max_lengths: list[int] | None = None, *, n_seqs: int | None = None,
-                 pool: PagePool | None = None, initial_pages: int = 0) -> None:
+                 pool: PagePool | None = None, initial_pages: int = 0, v_tables: HeadTables | None = None) -> None:
         self.tables = tables
+        self.v_tables = v_tables if pool is None else pool.v_tables
         dev = tables.device
         if max_lengths is None:
             if n_seqs is None:
@@ -308,7 +330,7 @@ class PagedKVCache:
             max_lengths = [0] * int(n_seqs)
         n = len(max_lengths)
         counts = [pages_for(x) for x in max_lengths]
-        self.pool = pool if pool is not None else PagePool(tables, max(1, sum(counts), int(initial_pages)))
+        self.pool = pool if pool is not None else PagePool(tables, max(1, sum(counts), int(initial_pages)), v_tables=v_tables)
         self._pages: list[list[int]] = [self.pool.take(c) for c in counts]
         width = max(1, max(counts) if counts else 1)
         table = torch.zeros((max(1, n), width), dtype=torch.int32)
@@ -374,7 +396,7 @@ class PagedKVCache:
         n_tok = torch.tensor(lengths, dtype=torch.int32, device=dev)
         if max(lengths) > 0:
             compress_into(self.tables, keys, n_tok, max(lengths), self.page_table, self.k_pool, self.status, starts)
-            store_values_into(values.to(dev), n_tok, max(lengths), self.page_table, self.v_pool, self.status, starts)
+            self._store_values(values.to(dev), n_tok, max(lengths), starts)
         for s, n in enumerate(lengths):
             self.lengths[s] += n
         self.seq_lens[: len(self.lengths)] = torch.tensor(self.lengths, dtype=torch.int32, device=dev)
@@ -392,10 +414,18 @@ class PagedKVCache:
         if getattr(self, "_ones", None) is None or self._ones.numel() != n:
             self._ones = torch.ones(n, dtype=torch.int32, device=self.tables.device)
         compress_into(self.tables, keys, self._ones, 1, self.page_table, self.k_pool, self.status, self.seq_lens)
-        store_values_into(values, self._ones, 1, self.page_table, self.v_pool, self.status, self.seq_lens)
+        self._store_values(values, self._ones, 1, self.seq_lens)
         self.seq_lens[:n] += 1
         for s in range(n):
             self.lengths[s] += 1
+
+    def _store_values(self, values: torch.Tensor, n_tok: torch.Tensor, max_tokens: int, starts: torch.Tensor) -> None:
+        if self.v_tables is None:
+            store_values_into(values, n_tok, max_tokens, self.page_table, self.v_pool, self.status, starts)
+        else:
+            if values.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+                values = values.float()
+            compress_into(self.v_tables, values, n_tok, max_tokens, self.page_table, self.v_pool, self.status, starts)
 
     def _workspace(self, n_seqs: int, n_q_heads: int, max_splits: int) -> DecodeWorkspace:
         ws = self._ws
@@ -410,7 +440,7 @@ class PagedKVCache:
         ws = self._workspace(n_seqs, n_q_heads, max(1, -(-max_len // tps)))
         out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
         return decode_attend(self.tables, q, self.seq_lens, max_len, self.page_table, self.k_pool, self.v_pool,
-                             out, ws, self.status, tps)
+                             out, ws, self.status, tps, v_tables=self.v_tables)
 
     def _host_state_stale(self, hs: dict | None, key: tuple) -> bool:
         return (hs is None or hs["key"] != key or hs["lengths"] != self.lengths
@@ -430,6 +460,8 @@ class PagedKVCache:
         call of ``jqk_decode_attend_host`` instead (no capture; three enqueues and a wait)."""
         if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3 or not q_host.is_contiguous():
             raise ValueError("q_host must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor in host memory")
+        if self.v_tables is not None:
+            raise NotImplementedError("decode_host is wired for bf16 values; use decode() with packed values")
         if not use_graph:
             return self._decode_host_call(q_host, tokens_per_split)
         dev = self.tables.device

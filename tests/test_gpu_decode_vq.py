@@ -1,0 +1,119 @@
+"""Decode attention over packed values (keys and values both stored as per-coordinate codes).
+
+The oracle attends over the reference's reconstructions: keys from the K codes, values from the V
+codes through ``CenteredCompressor`` semantics (dequantise, inverse map, add the mean;
+experiments/stage1/toolkit/v_compressor_adapter.py:64-72).  The kernel multiplies bf16 centroids on
+the tensor cores, so the comparison is made twice: against the oracle with the value centroids
+rounded to bf16 like the kernel's (the arithmetic being checked) and against the exact fp32
+reconstruction (which adds the rounding itself; the reference keeps reconstructed values in the
+model's bf16 cache, which rounds as much).  Both within 2e-3 of the row maximum, as for bf16 values;
+measured 1e-5 .. 8e-5 and 1e-4 .. 1.3e-3."""
+
+import pytest
+import torch
+
+import jointqk_b200 as jq
+from jointqk_b200 import paged
+from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, second_moment, spectrum_keys
+from gpu_util import recon_from_codes
+from oracle import reference_port as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(H, N, k_bits, v_bits, v_method="v_eigen_waterfill", layer=11):
+    keys = torch.stack([spectrum_keys(N, config_seed(0, layer, h)) for h in range(H)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096], k_bits)
+    tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    g = torch.Generator().manual_seed(layer)
+    vals = torch.stack([spectrum_keys(N, config_seed(0, layer + 50, h), n_outliers=0) for h in range(H)]) \
+        + 0.3 * torch.randn(H, 1, 128, generator=g)
+    v_comps = []
+    for h in range(H):
+        sig = second_moment(vals[h, :4096])
+        mu = vals[h, :4096].double().mean(0).float()
+        v_comps.append(jq.build_v_compressor(v_method, cov_v_for_head=sig - torch.outer(mu, mu), head_dim=128, bits=v_bits,
+                                             seed=42 + h, mu_v_for_head=mu, max_bits=4))
+    v_tables = jq.HeadTables.from_compressors([c.inner for c in v_comps], device="cuda",
+                                              center=torch.stack([c.mu for c in v_comps]))
+    return keys, vals, comps, v_comps, tables, v_tables
+
+
+def _case(lens, hq, hkv, k_bits, v_bits, tps=0, v_method="v_eigen_waterfill"):
+    N = max(max(lens), 1)
+    keys, vals, comps, v_comps, tables, v_tables = _setup(hkv, max(N, 4096), k_bits, v_bits, v_method)
+    S = len(lens)
+    g = torch.Generator().manual_seed(99 + S)
+    q = torch.randn(S, hq, 128, generator=g).to(torch.bfloat16)
+    kb = torch.stack([keys.roll(7 * s, 1)[:, :N] for s in range(S)]).cuda()
+    vb = torch.stack([vals.roll(5 * s, 1)[:, :N] for s in range(S)]).to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, [max(n, 1) for n in lens], v_tables=v_tables)
+    cache.prefill(kb, vb.cuda(), lens)
+    out = cache.decode(q.cuda(), tokens_per_split=tps).cpu()
+    paged.check_status(cache.status)
+    pk = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(lens), cache.status)
+    pv = paged.PackedKeys(v_tables, cache.v_pool, cache.page_table, cache.seq_lens, list(lens), cache.status)
+    k_codes, v_codes = paged.unpack_codes(pk).cpu(), paged.unpack_codes(pv).cpu()
+    v_dec = paged.decompress(pv).cpu()
+    ref = torch.zeros(S, hq, 128)
+    ref16 = torch.zeros(S, hq, 128)
+    bad = tot = 0
+    for s, n in enumerate(lens):
+        if n == 0:
+            continue
+        k_hat = torch.stack([recon_from_codes(comps[h], k_codes[s, h, :n]) for h in range(hkv)]).unsqueeze(0)
+        v_hat, v_hat16 = [], []
+        for h in range(hkv):
+            c = v_comps[h]
+            want, want_codes = orc.centred_roundtrip(vb[s, h, :n], c.mu, c.inner.codebooks_padded, c.inner.forward_map,
+                                                     c.inner.inverse_map)
+            bad += int((v_codes[s, h, :n].long() != want_codes).sum())
+            tot += want_codes.numel()
+            xh = orc.dequantise(v_codes[s, h, :n].long(), c.inner.codebooks_padded)
+            v_hat.append(xh @ c.inner.inverse_map + c.mu)
+            v_hat16.append(xh.to(torch.bfloat16).float() @ c.inner.inverse_map + c.mu)
+            same = (v_codes[s, h, :n].long() == want_codes).all(-1)
+            assert (v_dec[s, h, :n][same] - want[same]).abs().max().item() < 1e-5 * float(want.abs().max())
+        ref[s] = orc.decode_attention(q[s:s + 1], k_hat, torch.stack(v_hat).unsqueeze(0))[0]
+        ref16[s] = orc.decode_attention(q[s:s + 1], k_hat, torch.stack(v_hat16).unsqueeze(0))[0]
+    scale = ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)
+    return out, ref, ref16, scale, bad / max(tot, 1)
+
+
+@pytest.mark.parametrize("lens,hq,hkv,kb,vbits,tps,method", [
+    ([1000, 37, 1, 16], 8, 2, 2.0, 3, 0, "v_eigen_waterfill"),
+    ([4096], 32, 8, 2.0, 3, 0, "v_eigen_waterfill"),
+    ([513, 0, 2048], 8, 2, 3.0, 2, 256, "v_eigen_waterfill"),
+    ([700, 300], 16, 2, 3.0, 3, 128, "v_eigen_uniform"),
+    ([1500, 900], 8, 2, 2.0, 4, 0, "v_random"),
+    ([6000, 5000], 32, 8, 2.0, 3, 128, "v_eigen_waterfill")])        # 696 blocks: several waves
+def test_packed_value_decode_matches_oracle(lens, hq, hkv, kb, vbits, tps, method):
+    out, ref, ref16, scale, v_rate = _case(lens, hq, hkv, kb, vbits, tps, method)
+    err16 = ((out - ref16).abs() / scale).max().item()
+    err = ((out - ref).abs() / scale).max().item()
+    print(f"packed V decode lens={lens} K {kb} bits V {vbits} bits ({method}) tps={tps}: rel err vs bf16-centroid oracle "
+          f"{err16:.2e}, vs exact reconstruction {err:.2e}, V code mismatch rate {v_rate:.2e}")
+    assert err16 < 2e-3 and err < 2e-3 and v_rate <= 1e-5
+    for s, n in enumerate(lens):
+        if n == 0:
+            assert float(out[s].abs().max()) == 0.0
+
+
+def test_packed_values_append_and_bytes():
+    """A generate loop over packed values: append one token at a time, then the same result as one
+    prefill; and the cache holds what the bit budgets say."""
+    keys, vals, comps, v_comps, tables, v_tables = _setup(2, 4096, 2.0, 3)
+    n0, steps = 200, 20
+    kb = keys[:, : n0 + steps].unsqueeze(0).cuda()
+    vb = vals[:, : n0 + steps].unsqueeze(0).to(torch.bfloat16).cuda()
+    a = paged.PagedKVCache(tables, n_seqs=1, v_tables=v_tables)
+    a.prefill(kb[:, :, :n0], vb[:, :, :n0])
+    for t in range(n0, n0 + steps):
+        a.append(kb[:, :, t:t + 1], vb[:, :, t:t + 1])
+    b = paged.PagedKVCache(tables, [n0 + steps], v_tables=v_tables)
+    b.prefill(kb, vb)
+    q = torch.randn(1, 8, 128, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    assert torch.equal(a.decode(q), b.decode(q))
+    assert a.v_pool.dtype == torch.int32 and a.v_pool.shape[2] == v_tables.words_per_record
+    assert v_tables.payload_bytes_per_key == 48.0 and tables.payload_bytes_per_key == 32.0
+    paged.check_status(a.status)
