@@ -868,6 +868,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         e2e_out[0] = caches[i % n_copies].decode_host(q_host, tps)   # the next token depends on this result
 
     e2e_ms, _, _ = timed_loop(e2e_step, e2e_steps, max(3, args.warmup), device, world)
+    # the same step with no copy commands: the kernel reads the query from page-locked host memory and
+    # writes the result there itself (an option of decode_host; reported beside the default)
+    for c in caches:
+        c.decode_host(q_host, tps, zero_copy=True)
+    e2e_zc_ms, _, _ = timed_loop(lambda i: caches[i % n_copies].decode_host(q_host, tps, zero_copy=True),
+                                 e2e_steps, max(3, args.warmup), device, world)
 
     alg = decode_algorithmic_bytes(tables)
     per_launch_ms = ms / args.steps
@@ -879,7 +885,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "data": "synthetic", "config": workload_config(world), "clocks": clocks,
         "e2e": {"value": world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": e2e_out[0].numel() * 4,
-                "steps": e2e_steps, "note": "host query in, pinned-host result out through PagedKVCache.decode_host (replayed graph of H2D copy, decode, D2H copy; stream wait per step)"},
+                "steps": e2e_steps, "value_zero_copy": world * e2e_steps / (e2e_zc_ms * 1e-3),
+                "note": "host query in, pinned-host result out through PagedKVCache.decode_host (replayed graph of H2D copy, decode, D2H copy; "
+                        "stream wait per step); value_zero_copy: the same step as a one-kernel graph that reads the query from and writes the "
+                        "result to page-locked host memory itself"},
         "gpu_launches": args.steps,
         "repeats": {"regions": len(region_list), "steps_per_region": args.steps, "ms_per_step_median": per_launch_ms,
                     "ms_per_step_min": ordered[0] / args.steps, "ms_per_step_max": ordered[-1] / args.steps},

@@ -446,14 +446,22 @@ class PagedKVCache:
         return (hs is None or hs["key"] != key or hs["lengths"] != self.lengths
                 or hs["generation"] != self.pool.generation or hs["table_ptr"] != self.page_table.data_ptr())
 
-    def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0, use_graph: bool = True) -> torch.Tensor:
+    def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0, use_graph: bool = True,
+                    zero_copy: bool = False) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
         pinned host tensor that the next call overwrites.
 
-        The copy of the query to the device, the decode launch and the copy of the result back are
+        Default: the query is copied to the device, the step runs on device buffers and the result is
+        copied back (three commands).  ``zero_copy=True``: the kernel itself moves the data across the
+        bus: the blocks read their query heads from the page-locked staging buffer when they build
+        their tables, and the block that finishes a head writes its result straight into the
+        page-locked output, so the step is one kernel with no copy commands around it.  On the
+        single-sequence shape that measured slower (49 us against 45 us per step: 144 blocks each
+        wait for their own reads across the bus before they can build tables), so it is an option for
+        hosts that want no copy engine involved, not the default.  Either way the commands are
         captured once as a CUDA graph (per batch shape, context length and split); every call stages
         the query in pinned memory, replays the graph and waits for it, so the host pays one graph
-        launch and one synchronisation per step instead of three enqueues.  The cache must not grow
+        launch and one synchronisation per step.  The cache must not grow
         between capture and replay: a call after ``prefill`` captures again.  The captured graph keeps
         its own reference to the split workspace it was recorded with, so a later ``decode`` that needs
         a larger workspace does not pull that memory from under it.  ``use_graph=False`` makes one
@@ -463,11 +471,11 @@ class PagedKVCache:
         if self.v_tables is not None:
             raise NotImplementedError("decode_host is wired for bf16 values; use decode() with packed values")
         if not use_graph:
-            return self._decode_host_call(q_host, tokens_per_split)
+            return self._decode_host_call(q_host, tokens_per_split, zero_copy)
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_step
-        key = (n_seqs, n_q_heads, d, int(tokens_per_split))
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split), bool(zero_copy))
         if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
@@ -482,6 +490,10 @@ class PagedKVCache:
                   "stream": torch.cuda.Stream(dev)}
 
             def enqueue() -> None:
+                if zero_copy:      # page-locked host memory is device-addressable: pass it as q and out
+                    decode_attend(self.tables, hs["q_pin"], self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
+                                  hs["pools"][1], hs["out_pin"], hs["ws"], self.status, tps)
+                    return
                 hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
                 decode_attend(self.tables, hs["q_dev"], self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
                               hs["pools"][1], hs["out_dev"], hs["ws"], self.status, tps)
@@ -501,7 +513,7 @@ class PagedKVCache:
         torch.cuda.current_stream(dev).synchronize()   # the graph is launched on the current stream
         return hs["out_pin"]
 
-    def _decode_host_call(self, q_host: torch.Tensor, tokens_per_split: int = 0) -> torch.Tensor:
+    def _decode_host_call(self, q_host: torch.Tensor, tokens_per_split: int = 0, zero_copy: bool = False) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
         pinned host tensor that the next call overwrites.
 
@@ -512,7 +524,7 @@ class PagedKVCache:
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_call
-        key = (n_seqs, n_q_heads, d, int(tokens_per_split))
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split), bool(zero_copy))
         if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
@@ -525,10 +537,10 @@ class PagedKVCache:
                   "out_pin": keep["out_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
                   "q_dev": keep["q_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
                   "out_dev": keep["out_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32, device=dev)}
-            hs["args"] = (self.tables.ref, hs["q_pin"].data_ptr(), hs["q_dev"].data_ptr(), n_seqs, n_q_heads,
+            hs["args"] = (self.tables.ref, hs["q_pin"].data_ptr(), None if zero_copy else hs["q_dev"].data_ptr(), n_seqs, n_q_heads,
                           self.seq_lens.data_ptr(), int(max_len), int(tps), self.page_table.data_ptr(),
                           self.page_table.stride(0), int(self.k_pool.shape[0]), self.k_pool.data_ptr(),
-                          self.v_pool.data_ptr(), hs["out_dev"].data_ptr(), hs["out_pin"].data_ptr(),
+                          self.v_pool.data_ptr(), None if zero_copy else hs["out_dev"].data_ptr(), hs["out_pin"].data_ptr(),
                           _native.DTYPE_F32, ws.buf.data_ptr(), ws.buf.numel(), self.status.data_ptr())
             self._host_call = hs
         a = hs["args"]

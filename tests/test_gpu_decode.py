@@ -164,8 +164,10 @@ def test_decode_from_host_buffers_equals_device_call():
         if rep == 2:
             cache.prefill(keys[:, 1500:1501].unsqueeze(0).cuda(), v[:, :, 1500:1501].cuda())   # append one token
         want = cache.decode(q.cuda()).cpu()
-        assert torch.equal(cache.decode_host(q).clone(), want)                    # replayed graph
-        assert torch.equal(cache.decode_host(q, use_graph=False).clone(), want)   # jqk_decode_attend_host
+        assert torch.equal(cache.decode_host(q).clone(), want)                    # replayed graph of H2D copy, decode, D2H copy
+        assert torch.equal(cache.decode_host(q, zero_copy=True).clone(), want)    # one-kernel graph, kernel reads / writes host memory
+        assert torch.equal(cache.decode_host(q, use_graph=False).clone(), want)   # jqk_decode_attend_host with device staging
+        assert torch.equal(cache.decode_host(q, use_graph=False, zero_copy=True).clone(), want)   # ... without
     paged.check_status(cache.status)
 
 
