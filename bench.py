@@ -874,6 +874,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         c.decode_host(q_host, tps, zero_copy=True)
     e2e_zc_ms, _, _ = timed_loop(lambda i: caches[i % n_copies].decode_host(q_host, tps, zero_copy=True),
                                  e2e_steps, max(3, args.warmup), device, world)
+    for c in caches:
+        c.decode_host(q_host, tps, zero_copy="out")
+    e2e_zo_ms, _, _ = timed_loop(lambda i: caches[i % n_copies].decode_host(q_host, tps, zero_copy="out"),
+                                 e2e_steps, max(3, args.warmup), device, world)
 
     alg = decode_algorithmic_bytes(tables)
     per_launch_ms = ms / args.steps
@@ -886,6 +890,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         "e2e": {"value": world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": e2e_out[0].numel() * 4,
                 "steps": e2e_steps, "value_zero_copy": world * e2e_steps / (e2e_zc_ms * 1e-3),
+                "value_zero_copy_out": world * e2e_steps / (e2e_zo_ms * 1e-3),
                 "note": "host query in, pinned-host result out through PagedKVCache.decode_host (replayed graph of H2D copy, decode, D2H copy; "
                         "stream wait per step); value_zero_copy: the same step as a one-kernel graph that reads the query from and writes the "
                         "result to page-locked host memory itself"},

@@ -239,9 +239,9 @@ int32_t jqk_decode_attend_packed_values(const jqk_head_tables* tables, const jqk
  *              transfer is asynchronous); may equal q_host if that is page-locked already
  *   q_dev      device staging for the query, same size
  *   out_dev    device staging for the result, [n_seqs][n_q_heads][d] of out_dtype
- *              q_dev = out_dev = NULL: no copy commands at all; the kernel reads the query from q_pinned and
- *              writes the result into out_host across the bus itself (both page-locked, hence
- *              device-addressable), which saves the two copies' launch gaps on a step this short
+ *              either may be NULL (page-locked host memory is device-addressable): without q_dev the
+ *              blocks read the query from q_pinned themselves, without out_dev the block that finishes a
+ *              head writes its result into out_host itself, and the matching copy command is not issued
  *   out_host   page-locked host memory of the same size; valid when the call returns
  * Everything else as in jqk_decode_attend.  h2d / d2h bytes per call: the sizes of q and out.
  */

@@ -970,28 +970,20 @@ extern "C" int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const v
   if (rc) return rc;
   if (n_seqs <= 0 || n_q_heads <= 0) return fail(JQK_E_ARG, "n_seqs and n_q_heads must be positive");
   if (!q_host || !q_pinned || !out_host) return fail(JQK_E_ARG, "null host buffer");
-  if ((q_dev == nullptr) != (out_dev == nullptr)) return fail(JQK_E_ARG, "q_dev and out_dev must both be given or both be null");
   if (out_dtype != JQK_DTYPE_F32 && out_dtype != JQK_DTYPE_BF16) return fail(JQK_E_ARG, "out dtype must be f32 or bf16");
   cudaStream_t st = (cudaStream_t)stream;
   const size_t n = (size_t)n_seqs * n_q_heads * tables->d;
   const size_t q_bytes = n * 2, out_bytes = n * (out_dtype == JQK_DTYPE_F32 ? 4 : 2);
   if (q_pinned != q_host) memcpy(q_pinned, q_host, q_bytes);
-  if (!q_dev) {
-    // No staging on the device: page-locked host memory is device-addressable, so the kernel reads the
-    // query from q_pinned and the block that finishes a head writes its result into out_host itself.
-    rc = jqk_decode_attend(tables, q_pinned, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
-                           page_table_stride, n_pages, k_pool, v_pool, out_host, out_dtype, workspace, workspace_bytes,
-                           status, stream);
-    if (rc) return rc;
-    JQK_CUDA_OK(cudaStreamSynchronize(st), "waiting for the decode step");
-    return 0;
-  }
-  JQK_CUDA_OK(cudaMemcpyAsync(q_dev, q_pinned, q_bytes, cudaMemcpyHostToDevice, st), "query copy to the device");
-  rc = jqk_decode_attend(tables, q_dev, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
-                         page_table_stride, n_pages, k_pool, v_pool, out_dev, out_dtype, workspace, workspace_bytes,
-                         status, stream);
+  // Page-locked host memory is device-addressable.  Without q_dev the blocks read the query from
+  // q_pinned themselves; without out_dev the block that finishes a head writes its result into
+  // out_host itself (posted writes across the bus, no copy command after the kernel).
+  if (q_dev) JQK_CUDA_OK(cudaMemcpyAsync(q_dev, q_pinned, q_bytes, cudaMemcpyHostToDevice, st), "query copy to the device");
+  rc = jqk_decode_attend(tables, q_dev ? q_dev : q_pinned, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split,
+                         page_table, page_table_stride, n_pages, k_pool, v_pool, out_dev ? out_dev : out_host, out_dtype,
+                         workspace, workspace_bytes, status, stream);
   if (rc) return rc;
-  JQK_CUDA_OK(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, st), "result copy to the host");
+  if (out_dev) JQK_CUDA_OK(cudaMemcpyAsync(out_host, out_dev, out_bytes, cudaMemcpyDeviceToHost, st), "result copy to the host");
   JQK_CUDA_OK(cudaStreamSynchronize(st), "waiting for the decode step");
   return 0;
 }

@@ -447,7 +447,7 @@ class PagedKVCache:
                 or hs["generation"] != self.pool.generation or hs["table_ptr"] != self.page_table.data_ptr())
 
     def decode_host(self, q_host: torch.Tensor, tokens_per_split: int = 0, use_graph: bool = True,
-                    zero_copy: bool = False) -> torch.Tensor:
+                    zero_copy: bool | str = False) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
         pinned host tensor that the next call overwrites.
 
@@ -455,10 +455,12 @@ class PagedKVCache:
         copied back (three commands).  ``zero_copy=True``: the kernel itself moves the data across the
         bus: the blocks read their query heads from the page-locked staging buffer when they build
         their tables, and the block that finishes a head writes its result straight into the
-        page-locked output, so the step is one kernel with no copy commands around it.  On the
-        single-sequence shape that measured slower (49 us against 45 us per step: 144 blocks each
-        wait for their own reads across the bus before they can build tables), so it is an option for
-        hosts that want no copy engine involved, not the default.  Either way the commands are
+        page-locked output, so the step is one kernel with no copy commands around it;
+        ``zero_copy="out"`` keeps the copy of the query and lets the kernel write the result.  On the
+        single-sequence shape the three variants measured within a few percent of one another (44 to
+        49 us per step, run-to-run spread included: the step is dominated by the graph launch and the
+        wake-up after the wait, not by the two small copies), so the options are for hosts that want
+        no copy engine involved, not a speed-up.  Either way the commands are
         captured once as a CUDA graph (per batch shape, context length and split); every call stages
         the query in pinned memory, replays the graph and waits for it, so the host pays one graph
         launch and one synchronisation per step.  The cache must not grow
@@ -475,7 +477,9 @@ class PagedKVCache:
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_step
-        key = (n_seqs, n_q_heads, d, int(tokens_per_split), bool(zero_copy))
+        if zero_copy not in (False, True, "out"):
+            raise ValueError("zero_copy is False, True or 'out'")
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split), str(zero_copy))
         if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
@@ -490,14 +494,15 @@ class PagedKVCache:
                   "stream": torch.cuda.Stream(dev)}
 
             def enqueue() -> None:
-                if zero_copy:      # page-locked host memory is device-addressable: pass it as q and out
-                    decode_attend(self.tables, hs["q_pin"], self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
-                                  hs["pools"][1], hs["out_pin"], hs["ws"], self.status, tps)
-                    return
-                hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
-                decode_attend(self.tables, hs["q_dev"], self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
-                              hs["pools"][1], hs["out_dev"], hs["ws"], self.status, tps)
-                hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
+                # page-locked host memory is device-addressable: it can stand in for q and / or out
+                q_arg = hs["q_pin"] if zero_copy is True else hs["q_dev"]
+                out_arg = hs["out_pin"] if zero_copy else hs["out_dev"]
+                if q_arg is hs["q_dev"]:
+                    hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
+                decode_attend(self.tables, q_arg, self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
+                              hs["pools"][1], out_arg, hs["ws"], self.status, tps)
+                if out_arg is hs["out_dev"]:
+                    hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
 
             hs["q_pin"].copy_(q_host)
             with torch.cuda.stream(hs["stream"]):
@@ -513,7 +518,7 @@ class PagedKVCache:
         torch.cuda.current_stream(dev).synchronize()   # the graph is launched on the current stream
         return hs["out_pin"]
 
-    def _decode_host_call(self, q_host: torch.Tensor, tokens_per_split: int = 0, zero_copy: bool = False) -> torch.Tensor:
+    def _decode_host_call(self, q_host: torch.Tensor, tokens_per_split: int = 0, zero_copy: bool | str = False) -> torch.Tensor:
         """One decode step from host memory: bf16 query (n_seqs, Hq, d) in, fp32 result out in a
         pinned host tensor that the next call overwrites.
 
@@ -524,7 +529,7 @@ class PagedKVCache:
         dev = self.tables.device
         n_seqs, n_q_heads, d = q_host.shape
         hs = self._host_call
-        key = (n_seqs, n_q_heads, d, int(tokens_per_split), bool(zero_copy))
+        key = (n_seqs, n_q_heads, d, int(tokens_per_split), str(zero_copy))
         if self._host_state_stale(hs, key):
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
@@ -537,7 +542,7 @@ class PagedKVCache:
                   "out_pin": keep["out_pin"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32).pin_memory(),
                   "q_dev": keep["q_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16, device=dev),
                   "out_dev": keep["out_dev"] if keep else torch.empty((n_seqs, n_q_heads, d), dtype=torch.float32, device=dev)}
-            hs["args"] = (self.tables.ref, hs["q_pin"].data_ptr(), None if zero_copy else hs["q_dev"].data_ptr(), n_seqs, n_q_heads,
+            hs["args"] = (self.tables.ref, hs["q_pin"].data_ptr(), None if zero_copy is True else hs["q_dev"].data_ptr(), n_seqs, n_q_heads,
                           self.seq_lens.data_ptr(), int(max_len), int(tps), self.page_table.data_ptr(),
                           self.page_table.stride(0), int(self.k_pool.shape[0]), self.k_pool.data_ptr(),
                           self.v_pool.data_ptr(), None if zero_copy else hs["out_dev"].data_ptr(), hs["out_pin"].data_ptr(),

@@ -166,6 +166,7 @@ def test_decode_from_host_buffers_equals_device_call():
         want = cache.decode(q.cuda()).cpu()
         assert torch.equal(cache.decode_host(q).clone(), want)                    # replayed graph of H2D copy, decode, D2H copy
         assert torch.equal(cache.decode_host(q, zero_copy=True).clone(), want)    # one-kernel graph, kernel reads / writes host memory
+        assert torch.equal(cache.decode_host(q, zero_copy="out").clone(), want)   # H2D copy, then the kernel writes the host result
         assert torch.equal(cache.decode_host(q, use_graph=False).clone(), want)   # jqk_decode_attend_host with device staging
         assert torch.equal(cache.decode_host(q, use_graph=False, zero_copy=True).clone(), want)   # ... without
     paged.check_status(cache.status)
