@@ -8,7 +8,6 @@
 //   idx = argmin_l |x_j - cb[j, l]|, first index on ties   (:156-157)
 //   xh  = cb[j, idx]; k_hat = xh @ inverse_map             (:158-164)
 // The argmin is evaluated through exact fp32 decision thresholds prepared on the host.
-#include <stdlib.h>
 
 #include "jqk_common.cuh"
 
@@ -148,6 +147,55 @@ compress_simt_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t se
     const int page = lookup_page(pa.page_table, pa.pt_stride, seq, tok / JQK_PAGE_TOKENS, pa.n_pages, pa.status);
     if (page < 0) continue;
     k_pool[(((size_t)page * tb.n_heads + head) * wpr + w) * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS)] = word;
+  }
+}
+
+// A handful of keys per sequence (the newest token of a generate loop): one block of 128 threads per
+// (key, head, sequence), thread = column.  The dot product runs over the dims in ascending order
+// with fused multiply-adds, the order of compress_simt_kernel's tile product, so both kernels give
+// the same bits; the record is assembled with shared-memory atomics.
+constexpr int TOKEN_KERNEL_MAX = 4;
+template <typename KT>
+__global__ void __launch_bounds__(128)
+compress_token_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t seq_stride, int64_t head_stride,
+                      int64_t token_stride, PagedArgs pa, uint32_t* __restrict__ k_pool) {
+  __shared__ float krow[JQK_MAX_DIM];
+  __shared__ uint32_t words[JQK_MAX_WORDS];
+  const int t = blockIdx.x, head = blockIdx.y, seq = blockIdx.z, tid = threadIdx.x;
+  const int n_tok = call_tokens(pa, seq);
+  if (t >= n_tok) return;
+  const HeadDesc hd = load_desc(tb.desc, head);
+  const int d = hd.d;
+  const KT* row = keys + (size_t)seq * seq_stride + (size_t)head * head_stride + (size_t)t * token_stride;
+  if (tid < JQK_MAX_DIM) {
+    float v = 0.f;
+    if (tid < d) {
+      v = to_f32<KT>(row[tid]);
+      if (tb.center) v -= tb.center[(size_t)head * d + tid];
+    }
+    krow[tid] = v;
+  }
+  if (tid < JQK_MAX_WORDS) words[tid] = 0u;
+  __syncthreads();
+  if (tid < hd.n_active) {
+    const float* w = tb.fwd_cols + (size_t)head * d * 128 + tid;
+    float x = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < d; ++i) x = fmaf(krow[i], __ldg(w + (size_t)i * 128), x);
+    const int m = tb.col_meta[(size_t)head * 128 + tid];
+    const float* th = tb.thresholds + ((size_t)head * 128 + tid) * 16;
+    const int n_thr = (1 << meta_width(m)) - 1;
+    uint32_t code = 0;
+    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const int bp = meta_bitpos(m);
+    atomicOr(&words[bp >> 5], code << (bp & 31));
+  }
+  __syncthreads();
+  if (tid < hd.n_words) {
+    const int tok = (pa.seq_starts ? pa.seq_starts[seq] : 0) + t;
+    const int page = lookup_page(pa.page_table, pa.pt_stride, seq, tok / JQK_PAGE_TOKENS, pa.n_pages, pa.status);
+    if (page >= 0)
+      k_pool[(((size_t)page * tb.n_heads + head) * tb.words_per_record + tid) * JQK_PAGE_TOKENS + (tok % JQK_PAGE_TOKENS)] = words[tid];
   }
 }
 
@@ -291,19 +339,30 @@ extern "C" int32_t jqk_compress_paged(const jqk_head_tables* tables, const void*
   if (!keys) return fail(JQK_E_ARG, "null keys");
   if (token_stride < tables->d) return fail(JQK_E_ARG, "token_stride %lld smaller than d", (long long)token_stride);
   cudaStream_t st = (cudaStream_t)stream;
+  PagedArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, max_tokens, status};
+  if (max_tokens <= TOKEN_KERNEL_MAX) {
+    // a few keys per sequence (the append of a generate loop): one small block per key and head
+    dim3 tgrid(max_tokens, tables->n_heads, n_seqs);
+    if (key_dtype == JQK_DTYPE_F32)
+      compress_token_kernel<float><<<tgrid, 128, 0, st>>>(*tables, (const float*)keys, seq_stride, head_stride, token_stride, pa, k_pool);
+    else if (key_dtype == JQK_DTYPE_BF16)
+      compress_token_kernel<__nv_bfloat16><<<tgrid, 128, 0, st>>>(*tables, (const __nv_bfloat16*)keys, seq_stride, head_stride, token_stride, pa, k_pool);
+    else if (key_dtype == JQK_DTYPE_F16)
+      compress_token_kernel<__half><<<tgrid, 128, 0, st>>>(*tables, (const __half*)keys, seq_stride, head_stride, token_stride, pa, k_pool);
+    else
+      return fail(JQK_E_ARG, "unknown key dtype %d", key_dtype);
+    JQK_CUDA_OK(cudaGetLastError(), "token compress launch");
+    return 0;
+  }
   {
     // bf16 keys of head_dim 128 go to the tensor-core kernel; everything else (fp32 / fp16 keys,
     // other head sizes, unaligned strides, fewer than 128 keys) stays on the exact fp32 kernel.
-    static const bool tc_off = getenv("JQK_DISABLE_TENSOR_CORE_COMPRESS") != nullptr;
-    if (!tc_off) {
-      const int32_t r = jqk_compress_tc_try(tables, keys, key_dtype, seq_stride, head_stride, token_stride, n_seqs,
-                                            n_tokens, seq_starts, max_tokens, page_table, page_table_stride, n_pages,
-                                            k_pool, status, st);
-      if (r != 1) return r;
-    }
+    const int32_t r = jqk_compress_tc_try(tables, keys, key_dtype, seq_stride, head_stride, token_stride, n_seqs,
+                                          n_tokens, seq_starts, max_tokens, page_table, page_table_stride, n_pages,
+                                          k_pool, status, st);
+    if (r != 1) return r;
   }
   dim3 grid((max_tokens + TILE_T - 1) / TILE_T, tables->n_heads, n_seqs);
-  PagedArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, max_tokens, status};
 #define JQK_LAUNCH_COMPRESS(KT)                                                                       \
   do {                                                                                                 \
     JQK_SMEM_ONCE(compress_simt_kernel<KT>, kTileSmem, "compress smem attribute");                      \

@@ -164,7 +164,7 @@ template <> struct DecodeSmemT<true> {
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
-  int32_t vmeta[JQK_MAX_COLS];                    // value columns: width | bit position << 4
+  alignas(16) int32_t vmeta[JQK_MAX_COLS];        // value columns: width | bit position << 4
   __nv_bfloat16 vcb[JQK_MAX_COLS * 16];           // value codebooks, bf16 (what the tensor-core product multiplies)
 };
 // A warp's stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
@@ -534,15 +534,26 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         const int ts = lane & 15;
         const uint32_t off_a = (uint32_t)((ts >> 3) * 16 + (ts & 7) * 2);        // rows with (column >> 2) & 1 == 0
         const uint32_t off_b = (uint32_t)(((ts >> 3) ^ 1) * 16 + (ts & 7) * 2);  // the swapped halves
-        int cur_w = -1;
-        uint32_t word = 0u;
-#pragma unroll 4
-        for (int cc = 0; cc < v_n_active; ++cc) {
-          const int m = sm.vmeta[cc];
-          const int bp = m >> 4, w = bp >> 5;
-          if (w != cur_w) { word = vw[w * JQK_PAGE_TOKENS]; cur_w = w; }   // warp-uniform
-          const uint32_t code = (word >> (bp & 31)) & ((1u << (m & 15)) - 1u);
-          *reinterpret_cast<__nv_bfloat16*>(vt + cc * 32 + (((cc >> 2) & 1) ? off_b : off_a)) = sm.vcb[cc * 16 + code];
+        // eight columns at a time, stage by stage (descriptors, record words, centroids, stores), so
+        // that the dependent shared-memory reads of the eight overlap and no load waits behind a store
+        const int n_pad = (v_n_active + 7) & ~7;   // descriptors past the last column are 0: code 0 of a zero row
+#pragma unroll 1
+        for (int c0 = 0; c0 < n_pad; c0 += 8) {
+          const int4 ma = *reinterpret_cast<const int4*>(&sm.vmeta[c0]);
+          const int4 mb = *reinterpret_cast<const int4*>(&sm.vmeta[c0 + 4]);
+          const int m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+          uint32_t wd[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) wd[i] = vw[(m[i] >> 9) * JQK_PAGE_TOKENS];   // bit position >> 5 = record word
+          __nv_bfloat16 val[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t code = (wd[i] >> ((m[i] >> 4) & 31)) & ((1u << (m[i] & 15)) - 1u);
+            val[i] = sm.vcb[(c0 + i) * 16 + code];
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i)   // (c0 + i) >> 2 is odd for i >= 4: those rows have their halves swapped
+            *reinterpret_cast<__nv_bfloat16*>(vt + (c0 + i) * 32 + (i >= 4 ? off_b : off_a)) = val[i];
         }
       }
     } else if (any && t0 + TILE_TOK > t_end) {

@@ -10,6 +10,8 @@
 // every 16-byte piece of a page block (8 key slots of one dim) is then written with one store, so a
 // warp writes 512 contiguous bytes.  Pages that are only partly covered (an append that starts or
 // ends inside a page) are written slot by slot, leaving the other slots as they were.
+#include <type_traits>
+
 #include "jqk_common.cuh"
 
 namespace jqk {
@@ -33,6 +35,10 @@ __device__ __forceinline__ void load8_as_bf16(const T* src, bool vec, __nv_bfloa
   if constexpr (sizeof(T) == 2) {
     if (vec) {
       const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {   // already the pool's type: no conversion
+        *reinterpret_cast<uint4*>(out) = raw;
+        return;
+      }
       const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int i = 0; i < 8; ++i) out[i] = __float2bfloat16(to_f32<T>(e[i]));

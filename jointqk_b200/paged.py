@@ -419,6 +419,69 @@ class PagedKVCache:
         for s in range(n):
             self.lengths[s] += 1
 
+    def generate_step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
+        """One step of a generate loop as a single replayed CUDA graph: append the newest token of
+        every sequence (K compress, V store, lengths advanced on the device), then attend.
+
+        k_new / v_new (n_seqs, H, 1, d) and q bf16 (n_seqs, Hq, d) are copied into fixed staging
+        buffers (what a model's projection kernels would write into), so the captured launches see
+        stable addresses; the result is a device tensor that the next call overwrites.  The graph is
+        captured on first use and again whenever something it baked in changes: the page table or the
+        pools moved (growth), or the longest context crossed the split boundary the grid was sized
+        for (the capture rounds the context up to a whole number of splits, so that is every
+        ``tokens_per_split`` steps at most).  Pages are reserved on the host before the replay, which
+        only writes table entries in place."""
+        n = len(self.lengths)
+        dev = self.tables.device
+        if k_new.shape[0] != n or k_new.shape[2] != 1:
+            raise ValueError(f"generate_step takes one token for each of the {n} sequences")
+        for s_ in range(n):
+            self.reserve(s_, self.lengths[s_] + 1)
+        gs = getattr(self, "_gen_step", None)
+        new_max = max(self.lengths) + 1
+        if (gs is None or gs["generation"] != self.pool.generation or gs["table_ptr"] != self.page_table.data_ptr()
+                or gs["shape"] != (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) or new_max > gs["covered"]):
+            n_q_heads = q.shape[1]
+            tps = split_for_lengths([x + 1 for x in self.lengths], n_q_heads, self.tables.n_heads)
+            covered = -(-new_max // tps) * tps                     # the grid covers contexts up to here
+            ws = self._workspace(n, n_q_heads, covered // tps)
+            if getattr(self, "_ones", None) is None or self._ones.numel() != n:
+                self._ones = torch.ones(n, dtype=torch.int32, device=dev)
+            gs = {"generation": self.pool.generation, "table_ptr": self.page_table.data_ptr(), "covered": covered,
+                  "shape": (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype), "ws": ws,
+                  "pools": (self.k_pool, self.v_pool, self.page_table),
+                  "k": torch.empty_like(k_new, device=dev).contiguous(), "v": torch.empty_like(v_new, device=dev).contiguous(),
+                  "q": torch.empty_like(q, device=dev), "out": torch.empty(q.shape, dtype=torch.float32, device=dev),
+                  "stream": torch.cuda.Stream(dev)}
+
+            def enqueue() -> None:
+                compress_into(self.tables, gs["k"], self._ones, 1, self.page_table, self.k_pool, self.status, self.seq_lens)
+                self._store_values(gs["v"], self._ones, 1, self.seq_lens)
+                self.seq_lens[:n] += 1
+                decode_attend(self.tables, gs["q"], self.seq_lens, covered, self.page_table, self.k_pool, self.v_pool,
+                              gs["out"], ws, self.status, tps, v_tables=self.v_tables)
+
+            # the library's one-time set-up (shared-memory attributes) must happen outside a capture:
+            # run the step once for real on a scratch copy of the lengths, then restore them
+            saved = self.seq_lens.clone()
+            gs["k"].copy_(k_new); gs["v"].copy_(v_new); gs["q"].copy_(q)
+            with torch.cuda.stream(gs["stream"]):
+                gs["stream"].wait_stream(torch.cuda.current_stream(dev))
+                enqueue()
+                gs["stream"].synchronize()
+                self.seq_lens.copy_(saved)
+                gs["graph"] = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gs["graph"], stream=gs["stream"]):
+                    enqueue()
+            self._gen_step = gs
+        gs["k"].copy_(k_new, non_blocking=True)
+        gs["v"].copy_(v_new, non_blocking=True)
+        gs["q"].copy_(q, non_blocking=True)
+        gs["graph"].replay()
+        for s_ in range(n):
+            self.lengths[s_] += 1
+        return gs["out"]
+
     def _store_values(self, values: torch.Tensor, n_tok: torch.Tensor, max_tokens: int, starts: torch.Tensor) -> None:
         if self.v_tables is None:
             store_values_into(values, n_tok, max_tokens, self.page_table, self.v_pool, self.status, starts)

@@ -110,6 +110,33 @@ def test_generate_loop_append_equals_prefill():
     paged.check_status(cache.status)
 
 
+def test_generate_step_graph_equals_append_then_decode():
+    """generate_step (append + attend as one replayed graph, recaptured when the context crosses the
+    split boundary its grid covers or the pool moves) returns what append() followed by decode()
+    returns, step after step."""
+    H = 2
+    keys, comps, tables = _tables(H)
+    g = torch.Generator().manual_seed(12)
+    n0, steps = 370, 60                                                     # crosses the 384-key split boundary
+    v = torch.randn(2, H, n0 + steps, 128, generator=g).to(torch.bfloat16).cuda()
+    kk = torch.stack([keys[:, : n0 + steps], keys.flip(1)[:, : n0 + steps]]).cuda()
+    qs = torch.randn(steps, 2, 8, 128, generator=g).to(torch.bfloat16).cuda()
+    a = paged.PagedKVCache(tables, n_seqs=2, initial_pages=4)
+    b = paged.PagedKVCache(tables, n_seqs=2)
+    a.prefill(kk[:, :, :n0], v[:, :, :n0])
+    b.prefill(kk[:, :, :n0], v[:, :, :n0])
+    captures = set()
+    for i, t in enumerate(range(n0, n0 + steps)):
+        got = a.generate_step(kk[:, :, t:t + 1], v[:, :, t:t + 1], qs[i]).clone()
+        captures.add(id(a._gen_step["graph"]))
+        b.append(kk[:, :, t:t + 1], v[:, :, t:t + 1])
+        want = b.decode(qs[i])
+        assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item(), f"step {i}"   # the splits may differ
+    assert a.lengths == b.lengths == [n0 + steps] * 2 and a.seq_lens.tolist() == b.seq_lens.tolist()
+    assert 2 <= len(captures) <= 6                                           # recaptured, but not every step
+    paged.check_status(a.status)
+
+
 def test_overlong_length_is_clamped_flagged_and_leaves_the_workspace_clean():
     """A seq_lens entry above the max_seq_len the call was sized for: the kernel cuts the context to
     what its grid covers, sets JQK_STATUS_BAD_LENGTH, still merges, and the next call on the same
