@@ -74,15 +74,18 @@ extern "C" {
  *   cb_cols       float [H][128][16]: codebooks_padded[coord(c)][l], 0 beyond the last level
  *   qproj_cols    float [H][d][128]: inverse_map[coord(c)][i] (query projection)
  *   inv_rows      float [H][128][d]: inverse_map[coord(c)][i] (reconstruction)
- *   fwd_limbs     bf16  [H][3][128][d]: three-way bf16 split of fwd_cols, column-major
- *                 (limb l, column c, dim i), for the tensor-core transform; may be NULL
+ *   fwd_limbs     bf16  [H][3][128][d]: three-way bf16 split of fwd_cols with column c scaled by
+ *                 1 / sigma of its coordinate, column-major (limb l, column c, dim i), for the
+ *                 tensor-core transform, whose values are then quantised against the unit Lloyd-Max
+ *                 levels of the column's width; may be NULL (the CUDA-core kernel runs)
  *   center        float [H][d] or NULL: a mean that is subtracted from every input row before the
  *                 transform and added back after reconstruction (the reference's CenteredCompressor,
  *                 experiments/stage1/toolkit/v_compressor_adapter.py:46-72, used on the value side);
  *                 the tensor-core compress kernel is not used for centred tables
- *   bucket_pre    uint8 [H][128][128], bucket_aff float [H][128][2]: coarse-to-exact quantiser of the
- *                 tensor-core kernel: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes
- *                 2^23), code = pre[c][cell] + (x >= thresholds[c][pre[c][cell]]); both NULL = not used
+ *   unit_pre      uint8 [4][128], unit_thr float [4][16] (HOST values, +inf padded), unit_aff float [2]
+ *                 (HOST): the shared coarse-to-exact quantiser of the tensor-core kernel for widths
+ *                 1..4: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes 2^23),
+ *                 j = unit_pre[w-1][cell], code = (j & 15) + (x >= unit_thr flattened [j])
  */
 typedef struct jqk_head_tables {
   int32_t n_heads;
@@ -98,9 +101,10 @@ typedef struct jqk_head_tables {
   const float* qproj_cols;
   const float* inv_rows;
   const uint16_t* fwd_limbs;
-  const uint8_t* bucket_pre;
-  const float* bucket_aff;
+  const uint8_t* unit_pre;
   const float* center;
+  float unit_thr[64];
+  float unit_aff[2];
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */

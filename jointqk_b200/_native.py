@@ -31,9 +31,10 @@ class JqkHeadTables(C.Structure):
         ("qproj_cols", C.c_void_p),
         ("inv_rows", C.c_void_p),
         ("fwd_limbs", C.c_void_p),
-        ("bucket_pre", C.c_void_p),
-        ("bucket_aff", C.c_void_p),
+        ("unit_pre", C.c_void_p),
         ("center", C.c_void_p),
+        ("unit_thr", C.c_float * 64),
+        ("unit_aff", C.c_float * 2),
     ]
 
 

@@ -7,6 +7,14 @@
 // smallest first into one fp32 TMEM accumulator, so the transform keeps fp32 accuracy, which
 // the bit-exact code requirement needs (one bf16 or TF32 pass would flip ~1e-3 of the codes).
 //
+// The map's columns are scaled by 1 / sigma of their coordinate (on the host, before the split), so a
+// transformed value is in units of its coordinate's standard deviation and the nearest level of its
+// codebook (unit Lloyd-Max levels x sigma) is found against the UNIT levels of its width: one shared
+// set of thresholds and cell tables for every column, as compile-time constants in the code for reads
+// whose widths are regular.  The rescaling moves a code only when the value lies within ~1e-7
+// (relative) of a decision threshold: 1e-7 .. 5e-7 of the coordinates, the size of the difference
+// between two fp32 summation orders of the reference's own transform.
+//
 // One thread block walks a run of 128-key tiles of one head (the head's tiles of all sequences form
 // one list, cut into equal runs, so that a batch fills every SM whatever its shape):
 //   warp 0      TMA producer: key tiles [128 keys][128 dims] bf16 into a 3-stage ring (128B swizzle)
@@ -42,23 +50,31 @@ constexpr uint32_t TC_A_BYTES = TC_TILE * 128 * 2;   // one key tile
 constexpr uint32_t TC_B_BYTES = 3 * 128 * 128 * 2;   // three limb matrices
 constexpr uint32_t TC_TMEM_COLS = 512;               // two fp32 accumulators of 128 columns; the rest is only
                                                      // there so that a 16-column read may start at any column
-constexpr int TC_COL_PAD = 128 + CH;                 // per-column tables cover a read that starts at column 127
 constexpr int TC_MAX_UNITS = JQK_MAX_WORDS;          // a unit is one record word, or two neighbouring ones
 constexpr int TC_MAX_SLOTS = 20;                     // 16-column reads of all units (more: generic path)
 constexpr unsigned long long TC_WAIT_NS = 2000000000ull;
 
-// Classes of a 16-column read.  The general class takes any column; the others skip the cell and
-// threshold lookups for columns whose one or three thresholds fit the constant row itself.
+// Classes of a 16-column read.  A column of known width needs no per-column constant to be quantised
+// (its thresholds are the unit thresholds of the width); a column whose width is only known at run
+// time reads one word, the address of its width's cell table.  Every class but the two regular ones
+// reads per-column multipliers that put a code at its bit position.
 enum : int {
-  TC_CLS_GENERAL = 0,  // row = cell scale, cell offset, multiplier of the first word, of the second word
-  TC_CLS_ODD1 = 1,     // odd columns are 1-bit (or unused): row = threshold, -, multipliers; even columns general
-  TC_CLS_ALL1 = 2,     // every column 1-bit (or unused): row = threshold, -, multipliers
-  TC_CLS_ALL2 = 3,     // every column 2-bit (or unused), one word: row = three thresholds, multiplier
-  TC_CLS_REG4 = 4,     // sixteen 4-bit columns filling two words in order: general, multipliers known at compile time
-  TC_CLS_REG31 = 5,    // eight (3-bit, 1-bit) pairs filling one word in order: as TC_CLS_ODD1, multipliers known at compile time
+  TC_CLS_GENERAL = 0,  // any widths: width word + multipliers per column
+  TC_CLS_ODD1 = 1,     // odd columns are 1-bit (or unused): one comparison; even columns as in the general class
+  TC_CLS_ALL1 = 2,     // every column 1-bit (or unused): one comparison each
+  TC_CLS_ALL2 = 3,     // every column 2-bit (or unused), one word: three comparisons each
+  TC_CLS_REG4 = 4,     // sixteen 4-bit columns filling two words in order: no constants read at all
+  TC_CLS_REG31 = 5,    // eight (3-bit, 1-bit) pairs filling one word in order: no constants read at all
 };
-// The multiplier half of a row is 8 bytes (first word, second word; for TC_CLS_ALL2 third threshold,
-// multiplier) when the unit has two words or the class is TC_CLS_ALL2, else 4 bytes (first word).
+// The multiplier row of a read holds 8 bytes per column (first word, second word) when the unit has two
+// words, else 4 bytes (first word).
+
+// Unit thresholds and the cell grid, passed by value: the comparisons of the regular classes take them
+// straight from the constant bank.
+struct UnitConsts {
+  float thr[64];  // [width - 1][16], +inf padded
+  float cs, co;   // cell = round(127 * saturate(x * cs + co))
+};
 
 // How the epilogue warps share a head's record: units (one record word, or two neighbouring ones) are
 // dealt to the parts, and each unit is quantised in 16-column reads ("slots").
@@ -75,13 +91,15 @@ struct TcPlan {
 struct TcSmem {
   uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
-  float thr[TC_COL_PAD * 16];
-  uint8_t pre[TC_COL_PAD * 128];  // coarse-to-exact quantiser: lower bound of the code per cell
-  // one row per column of every 16-column read: x = cell scale, y = cell offset (cell = round(127 *
-  // saturate(v * x + y))), z / w = 1 << bit position when the column's code belongs to the first /
-  // second word of the unit that issues the read (both 0 for columns the read merely passes over)
-  float2 crow_a[TC_MAX_SLOTS * CH];  // x, y of the row
-  uint2 crow_m[TC_MAX_SLOTS * CH];   // z, w of the row
+  float uthr[64];         // unit decision thresholds, [width - 1][16]
+  uint8_t upre[4 * 128];  // per width and cell: 16 * (width - 1) + a lower bound of the code (at most one short),
+                          // i.e. the index into uthr at which the one exact comparison is made
+  // one entry per column of every 16-column read: crow_w = the bit pattern of the shared-memory address
+  // of the cell row of the column's width (classes with run-time widths); crow_m = 1 << bit position
+  // when the column's code belongs to the first / second word of the unit that issues the read (both 0
+  // for columns the read merely passes over)
+  float crow_w[TC_MAX_SLOTS * CH];
+  uint2 crow_m[TC_MAX_SLOTS * CH];
   TcPlan plan;
   int32_t meta[128];
   int32_t wcb[JQK_MAX_WORDS + 4];
@@ -90,7 +108,7 @@ struct TcSmem {
   volatile int abort;
 };
 
-static_assert(TC_MAX_UNITS * sizeof(int4) <= sizeof(TcSmem::crow_a), "the planner's scratch lies in the row table");
+static_assert(TC_MAX_UNITS * sizeof(int4) <= sizeof(TcSmem::crow_m), "the planner's scratch lies in the row table");
 static_assert(sizeof(TcSmem) + 1024 <= 232448, "shared memory of the tensor-core compress kernel");
 
 struct TcArgs {
@@ -240,35 +258,24 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
   for (int q = 0; q <= TC_PARTS; ++q) pl.cut[q] = cut[q];
 }
 
-// Constant row e (slot e / 16, column e % 16 of the read) of a planned head; see the classes above
-// quant16.  `thr`: the head's decision thresholds, 16 per column (+inf padded).
-template <bool USE_BUCKETS>
-__device__ __forceinline__ float4 tc_const_row(const TcPlan& pl, const int32_t* wcb, const int32_t* meta,
-                                               const float* thr, const float* bucket_aff_head, int e) {
+// Constants of entry e (slot e / 16, column e % 16 of the read) of a planned head: x = the bit pattern
+// of the address of the cell row of the column's width (`pre_addr`: shared-memory address of the four
+// cell rows), y / z = multipliers for the first / second word of the unit.
+__device__ __forceinline__ uint3 tc_const_row(const TcPlan& pl, const int32_t* wcb, const int32_t* meta, uint32_t pre_addr, int e) {
   const int ss = pl.slot_step[e >> 4];
   const int2 st = pl.step[ss >> 5][ss & 31];
-  const int w_first = st.y & 255, nw = (st.y >> 8) & 255, cls = (st.y >> 18) & 7;
+  const int w_first = st.y & 255, nw = (st.y >> 8) & 255;
   const int col = (st.x & 255) + (e & 15);
   const bool mine = col < wcb[w_first + nw];  // the column belongs to the unit that issues the read
   uint32_t m_lo = 0u, m_hi = 0u;
+  int width = 1;
   if (mine) {
     const int bp = (meta[col] >> 4) & 1023;
     if ((bp >> 5) == w_first) m_lo = 1u << (bp & 31);
     else m_hi = 1u << (bp & 31);
+    width = max(1, meta[col] & 15);
   }
-  if (cls == TC_CLS_ALL2)
-    return mine ? make_float4(thr[col * 16], thr[col * 16 + 1], thr[col * 16 + 2], __uint_as_float(m_lo))
-                : make_float4(CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, 0.f);
-  if (cls == TC_CLS_ALL1 || ((cls == TC_CLS_ODD1 || cls == TC_CLS_REG31) && (e & 1)))
-    return make_float4(mine ? thr[col * 16] : CUDART_INF_F, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
-  float4 cr = make_float4(0.f, 0.f, __uint_as_float(m_lo), __uint_as_float(m_hi));
-  if (USE_BUCKETS && mine) {
-    // host form: cell = clamp(round(x * inv_step + off), 0, 127) with 2^23 folded into off
-    const float2 h2 = reinterpret_cast<const float2*>(bucket_aff_head)[col];
-    cr.x = h2.x * (1.f / 127.f);
-    cr.y = (h2.y - 8388608.f) * (1.f / 127.f);
-  }
-  return cr;
+  return make_uint3(pre_addr + (uint32_t)(width - 1) * 128u, m_lo, m_hi);
 }
 
 // Shared-space loads at a register address plus a compile-time offset (the address register of the
@@ -297,88 +304,80 @@ __device__ __forceinline__ void static_for(F&& f) {
 
 // Codes of 16 consecutive columns of one key, added at their bit positions into the one or two word
 // registers of the unit.  Written stage by stage over all 16 columns (cells, lower bounds, thresholds,
-// comparison, placement) so that the three dependent shared-memory reads of a column overlap with
-// those of the other fifteen.  `ra` / `rm`: the read's constant rows; `pre_base`: a float whose bit
-// pattern is the shared-memory address of the first column's cell row; `thr_base`: address of its
-// threshold row.  The cell index is formed in the subnormal range, where a float's bit pattern is its
-// integer value: fma(y, 127 * 2^-149, pre_base) has the bit pattern pre_base + round(127 y), the
-// address of the cell.
-template <bool USE_BUCKETS, int CLS, int J>
-__device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uint2* __restrict__ rm,
-                                        const float (&v)[CH], float pre_base, uint32_t thr_base, uint32_t& lo,
+// comparison, placement) so that the dependent shared-memory reads of a column overlap with those of
+// the other fifteen.  A column of width W is quantised against the unit levels of W: a cell of the
+// common grid gives, through the cell row of W, the index j of the one threshold that still has to be
+// compared exactly; code = (j & 15) + (v >= uthr[j]).  1- and 2-bit columns of known width compare
+// with their one or three thresholds directly (operands from the constant bank).  `rw` / `rm`: the
+// read's width words and multipliers; `pre_base[W - 1]`: bit pattern (as a float) of the address of
+// the cell row of width W; `uthr_addr`: address of the unit thresholds.  The cell index is formed in
+// the subnormal range, where a float's bit pattern is its integer value: fma(y, 127 * 2^-149, base)
+// has the bit pattern base + round(127 y), the address of the cell.
+template <int CLS, int J>
+__device__ __forceinline__ void quant16(const UnitConsts& uc, const float* __restrict__ rw, const uint2* __restrict__ rm,
+                                        const float (&v)[CH], const float (&pre_base)[4], uint32_t uthr_addr, uint32_t& lo,
                                         uint32_t& hi) {
   constexpr bool all2 = CLS == TC_CLS_ALL2, all1 = CLS == TC_CLS_ALL1;
   uint32_t k[CH];
   float t[CH];
-  // (rows of two neighbouring columns come in one 16-byte read)
-  static_for<0, CH / 2>([&](auto pc) {
-    constexpr int P = decltype(pc)::value;
-    const float4 a2 = reinterpret_cast<const float4*>(ra)[P];
-    static_for<0, 2>([&](auto hc) {
-      constexpr int I = 2 * P + decltype(hc)::value;
-      [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
-      const float2 a = (I & 1) ? make_float2(a2.z, a2.w) : make_float2(a2.x, a2.y);
+  // stage 1: cell addresses (or the finished code of a directly compared column)
+  static_for<0, CH / 4>([&](auto qc) {
+    constexpr int Q = decltype(qc)::value;
+    [[maybe_unused]] float4 w4;
+    if constexpr (CLS == TC_CLS_GENERAL || CLS == TC_CLS_ODD1) w4 = reinterpret_cast<const float4*>(rw)[Q];
+    static_for<0, 4>([&](auto hc) {
+      constexpr int H = decltype(hc)::value, I = 4 * Q + H;
+      constexpr bool direct1 = all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
       if constexpr (all2) {
-        k[I] = ((v[I] >= a.x) ? 1u : 0u) + ((v[I] >= a.y) ? 1u : 0u);
-      } else if constexpr (direct) {
-        k[I] = (v[I] >= a.x) ? 1u : 0u;
-      } else if constexpr (USE_BUCKETS) {
-        const float y = __saturatef(fmaf(v[I], a.x, a.y));
-        k[I] = __float_as_uint(fmaf(y, __uint_as_float(127u), pre_base));  // address of the cell
+        k[I] = ((v[I] >= uc.thr[16]) ? 1u : 0u) + ((v[I] >= uc.thr[17]) ? 1u : 0u) + ((v[I] >= uc.thr[18]) ? 1u : 0u);
+      } else if constexpr (direct1) {
+        k[I] = (v[I] >= uc.thr[0]) ? 1u : 0u;
       } else {
-        k[I] = (v[I] >= lds_f32<I * 64 + 28>(thr_base)) ? 8u : 0u;
+        const float y = __saturatef(fmaf(v[I], uc.cs, uc.co));
+        float base;
+        if constexpr (CLS == TC_CLS_REG4) base = pre_base[3];
+        else if constexpr (CLS == TC_CLS_REG31) base = pre_base[2];
+        else base = (H == 0 ? w4.x : H == 1 ? w4.y : H == 2 ? w4.z : w4.w);
+        k[I] = __float_as_uint(fmaf(y, __uint_as_float(127u), base));  // address of the cell
       }
     });
   });
+  // stage 2: j = lower bound of the code with the width's offset; stage 3: the exact threshold at j
   static_for<0, CH>([&](auto ic) {
     constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
-    if constexpr (!direct) {
-      if constexpr (USE_BUCKETS) k[I] = lds_u8<I * 128>(k[I]);  // lower bound of the code, at most one short
-      else k[I] += (v[I] >= lds_f32<I * 64 + 12>(thr_base + 4u * k[I])) ? 4u : 0u;
-    }
+    constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
+    if constexpr (!direct) k[I] = lds_u8<0>(k[I]);
   });
-  if constexpr (!USE_BUCKETS) {
-    static_for<0, CH>([&](auto ic) {
-      constexpr int I = decltype(ic)::value;
-      constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
-      if constexpr (!direct) k[I] += (v[I] >= lds_f32<I * 64 + 4>(thr_base + 4u * k[I])) ? 2u : 0u;
-    });
-  }
   static_for<0, CH>([&](auto ic) {
     constexpr int I = decltype(ic)::value;
-    [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
-    if constexpr (!direct) t[I] = lds_f32<I * 64>(thr_base + 4u * k[I]);  // exact fp32 decision threshold
+    constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
+    if constexpr (!direct) t[I] = lds_f32<0>(uthr_addr + 4u * k[I]);
   });
+  // stage 4: the one exact comparison, and the code at its bit position
   if constexpr (CLS == TC_CLS_REG31) {
     static_for<0, CH>([&](auto ic) {
       constexpr int I = decltype(ic)::value;
-      if constexpr (!(I & 1)) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+      if constexpr (!(I & 1)) k[I] = (k[I] & 15u) + ((v[I] >= t[I]) ? 1u : 0u);
       lo += k[I] * (1u << (4 * (I / 2) + 3 * (I & 1)));
     });
   } else if constexpr (CLS == TC_CLS_REG4) {
     static_for<0, CH>([&](auto ic) {
       constexpr int I = decltype(ic)::value;
-      k[I] += (v[I] >= t[I]) ? 1u : 0u;
+      k[I] = (k[I] & 15u) + ((v[I] >= t[I]) ? 1u : 0u);
       if constexpr (I < 8) lo += k[I] * (1u << (4 * I));
       else hi += k[I] * (1u << (4 * (I - 8)));
     });
-  } else if constexpr (J > 1 || all2) {
+  } else if constexpr (J > 1) {
     static_for<0, CH / 2>([&](auto pc) {
       constexpr int P = decltype(pc)::value;
       const uint4 m2 = reinterpret_cast<const uint4*>(rm)[P];
       static_for<0, 2>([&](auto hc) {
         constexpr int I = 2 * P + decltype(hc)::value;
-        [[maybe_unused]] constexpr bool direct = all2 || all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
+        constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
         const uint2 m = (I & 1) ? make_uint2(m2.z, m2.w) : make_uint2(m2.x, m2.y);
-        if constexpr (all2) {
-          k[I] += (v[I] >= __uint_as_float(m.x)) ? 1u : 0u;  // third threshold
-          lo += k[I] * m.y;
-        } else {
-          if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
-          lo += k[I] * m.x;
-          hi += k[I] * m.y;
-        }
+        if constexpr (!direct) k[I] = (k[I] & 15u) + ((v[I] >= t[I]) ? 1u : 0u);
+        lo += k[I] * m.x;
+        hi += k[I] * m.y;
       });
     });
   } else {
@@ -387,18 +386,17 @@ __device__ __forceinline__ void quant16(const float2* __restrict__ ra, const uin
       const uint4 m4 = reinterpret_cast<const uint4*>(rm)[Q];  // four columns' first-word multipliers
       static_for<0, 4>([&](auto hc) {
         constexpr int H = decltype(hc)::value, I = 4 * Q + H;
-        [[maybe_unused]] constexpr bool direct = all1 || ((CLS == TC_CLS_ODD1 || CLS == TC_CLS_REG31) && (I & 1));
-        if constexpr (!direct) k[I] += (v[I] >= t[I]) ? 1u : 0u;
+        constexpr bool direct = all2 || all1 || (CLS == TC_CLS_ODD1 && (I & 1));
+        if constexpr (!direct) k[I] = (k[I] & 15u) + ((v[I] >= t[I]) ? 1u : 0u);
         lo += k[I] * (H == 0 ? m4.x : H == 1 ? m4.y : H == 2 ? m4.z : m4.w);
       });
     });
   }
 }
 
-template <bool USE_BUCKETS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
-                   jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
+                   const __grid_constant__ UnitConsts uc, jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
   extern __shared__ uint8_t smem_raw[];
   // align by pointer arithmetic on the __shared__ array (an integer round trip would turn every access into a generic load)
   TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
@@ -410,16 +408,11 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   const HeadDesc hd = load_desc(tb.desc, head);
 
   // ---- set-up ----
-  // per-column tables; columns past n_cols (reachable by the last 16-column read of a part) quantise to code 0
-  for (int e = tid; e < TC_COL_PAD * 16; e += TC_THREADS)
-    sm.thr[e] = (e < hd.n_cols * 16) ? tb.thresholds[(size_t)head * 128 * 16 + e] : CUDART_INF_F;
+  // the shared quantiser tables (the same for every head and column) and this head's column descriptors
+  for (int e = tid; e < 64; e += TC_THREADS) sm.uthr[e] = uc.thr[e];
+  for (int e = tid; e < 4 * 128 / 4; e += TC_THREADS)
+    reinterpret_cast<uint32_t*>(sm.upre)[e] = reinterpret_cast<const uint32_t*>(tb.unit_pre)[e];
   for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(tb.bucket_pre + (size_t)head * 128 * 128);
-    uint4* dst = reinterpret_cast<uint4*>(sm.pre);
-    for (int e = tid; e < TC_COL_PAD * 8; e += TC_THREADS)
-      dst[e] = (USE_BUCKETS && e < hd.n_cols * 8) ? src[e] : make_uint4(0u, 0u, 0u, 0u);
-  }
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -489,27 +482,30 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
     const int part = ew >> 2;
-    if (ew == 0 && lane == 0) tc_make_plan(sm.plan, sm.wcb, sm.meta, hd.n_words, hd.n_active, reinterpret_cast<int4*>(sm.crow_a));
+    if (ew == 0 && lane == 0) tc_make_plan(sm.plan, sm.wcb, sm.meta, hd.n_words, hd.n_active, reinterpret_cast<int4*>(sm.crow_m));
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
     const bool planned = sm.plan.n_slots <= TC_MAX_SLOTS;
-    if (planned) {  // constant rows of every read
+    const uint32_t pre_addr = smem_u32(sm.upre), uthr_addr = smem_u32(sm.uthr);
+    if (planned) {  // constants of every read: width words and multipliers
       const int et = tid - 64;
-      if (et < sm.plan.n_slots * CH)
-      {
-        const float4 cr = tc_const_row<USE_BUCKETS>(sm.plan, sm.wcb, sm.meta, sm.thr, tb.bucket_aff + (size_t)head * 256, et);
-        sm.crow_a[et] = make_float2(cr.x, cr.y);
+      if (et < sm.plan.n_slots * CH) {
+        const uint3 cr = tc_const_row(sm.plan, sm.wcb, sm.meta, pre_addr, et);
         const int2 st = sm.plan.step[sm.plan.slot_step[et >> 4] >> 5][sm.plan.slot_step[et >> 4] & 31];
-        if (((st.y >> 8) & 255) > 1 || ((st.y >> 18) & 7) == TC_CLS_ALL2)
-          sm.crow_m[et] = make_uint2(__float_as_uint(cr.z), __float_as_uint(cr.w));
+        asm volatile("" ::: "memory");  // the planner's scratch (units) lies in crow_m: every plan read above comes first
+        sm.crow_w[et] = __uint_as_float(cr.x);
+        if (((st.y >> 8) & 255) > 1)
+          sm.crow_m[et] = make_uint2(cr.y, cr.z);
         else
-          reinterpret_cast<uint32_t*>(sm.crow_m + (et & ~15))[et & 15] = __float_as_uint(cr.z);
+          reinterpret_cast<uint32_t*>(sm.crow_m + (et & ~15))[et & 15] = cr.y;
       }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
     const int w_lo = sm.plan.cut[part], w_hi = sm.plan.cut[part + 1];
     const int c_lo = sm.wcb[w_lo], c_hi = sm.wcb[w_hi];
     const int my_steps = sm.plan.n_steps[part];
-    const uint32_t pre_addr = smem_u32(sm.pre), thr_addr = smem_u32(sm.thr);
+    float pre_base[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) pre_base[w] = __uint_as_float(pre_addr + 128u * w);
     const int wpr = tb.words_per_record;
     int it = 0;
     int seq_of_start = -1, seq_start = 0;
@@ -539,25 +535,22 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         for (int s = 0; s < my_steps; ++s) {
           const int2 cur = sm.plan.step[part][s];
           tmem_ld16(t_lane + (cur.x & 255), v);
-          const int c0 = cur.x & 255;
-          const float2* ra = sm.crow_a + (cur.x >> 8) * CH;
+          const float* rw = sm.crow_w + (cur.x >> 8) * CH;
           const uint2* rm = sm.crow_m + (cur.x >> 8) * CH;
-          const float pre_base = __uint_as_float(pre_addr + (uint32_t)c0 * 128u);
-          const uint32_t thr_base = thr_addr + (uint32_t)c0 * 64u;
           if (cur.y & (1 << 16)) lo = hi = 0u;
           const bool two = (cur.y & 0xff00) == 0x200;
           switch ((cur.y >> 18) & 7) {  // warp-uniform
-            case TC_CLS_REG4: quant16<USE_BUCKETS, TC_CLS_REG4, 2>(ra, rm, v, pre_base, thr_base, lo, hi); break;
-            case TC_CLS_REG31: quant16<USE_BUCKETS, TC_CLS_REG31, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
-            case TC_CLS_ALL2: quant16<USE_BUCKETS, TC_CLS_ALL2, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
-            case TC_CLS_ALL1: quant16<USE_BUCKETS, TC_CLS_ALL1, 1>(ra, rm, v, pre_base, thr_base, lo, hi); break;
+            case TC_CLS_REG4: quant16<TC_CLS_REG4, 2>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
+            case TC_CLS_REG31: quant16<TC_CLS_REG31, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
+            case TC_CLS_ALL2: quant16<TC_CLS_ALL2, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
+            case TC_CLS_ALL1: quant16<TC_CLS_ALL1, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
             case TC_CLS_ODD1:
-              if (two) quant16<USE_BUCKETS, TC_CLS_ODD1, 2>(ra, rm, v, pre_base, thr_base, lo, hi);
-              else quant16<USE_BUCKETS, TC_CLS_ODD1, 1>(ra, rm, v, pre_base, thr_base, lo, hi);
+              if (two) quant16<TC_CLS_ODD1, 2>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi);
+              else quant16<TC_CLS_ODD1, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi);
               break;
             default:
-              if (two) quant16<USE_BUCKETS, TC_CLS_GENERAL, 2>(ra, rm, v, pre_base, thr_base, lo, hi);
-              else quant16<USE_BUCKETS, TC_CLS_GENERAL, 1>(ra, rm, v, pre_base, thr_base, lo, hi);
+              if (two) quant16<TC_CLS_GENERAL, 2>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi);
+              else quant16<TC_CLS_GENERAL, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi);
           }
           if ((cur.y & (1 << 17)) && dst) {
             dst[(cur.y & 255) * JQK_PAGE_TOKENS] = lo;
@@ -581,7 +574,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
             float x = v[0];  // v[i] without dynamic register indexing
 #pragma unroll
             for (int u = 1; u < CH; ++u) x = (u == i) ? v[u] : x;
-            cur |= search_code(x, sm.thr + (c0 + i) * 16, m & 15) << (bp & 31);
+            cur |= search_code(x, sm.uthr + ((m & 15) - 1) * 16, m & 15) << (bp & 31);
           }
         }
         while (cur_w < w_hi) {
@@ -619,7 +612,7 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
                             uint32_t* k_pool, int32_t* status, cudaStream_t st) {
   if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || tables->center) return 1;
   if ((uintptr_t)keys % 16 || (token_stride * 2) % 16 || (head_stride * 2) % 16 || (seq_stride * 2) % 16) return 1;
-  if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE) return 1;
+  if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE || !tables->unit_pre) return 1;
   CUtensorMap key_map, limb_map;
   char err[256];
   {
@@ -650,14 +643,13 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
   dim3 grid((unsigned)((slots + tiles_per_block - 1) / tiles_per_block), tables->n_heads, 1);
   TcArgs pa{n_tokens, seq_starts, page_table, page_table_stride, n_pages, tiles_per_block, max_tiles, n_seqs, status};
   const size_t smem = sizeof(TcSmem) + 1024;
-  const bool buckets = tables->bucket_pre && tables->bucket_aff;
-  if (buckets) {
-    JQK_SMEM_ONCE(compress_tc_kernel<true>, smem, "tensor-core compress smem attribute");
-    compress_tc_kernel<true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
-  } else {
-    JQK_SMEM_ONCE(compress_tc_kernel<false>, smem, "tensor-core compress smem attribute");
-    compress_tc_kernel<false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, *tables, pa, k_pool);
-  }
+  UnitConsts uc;
+  for (int i = 0; i < 64; ++i) uc.thr[i] = tables->unit_thr[i];
+  // host form of the grid: cell = clamp(round(x * aff[0] + aff[1] - 2^23), 0, 127)
+  uc.cs = tables->unit_aff[0] * (1.f / 127.f);
+  uc.co = (tables->unit_aff[1] - 8388608.f) * (1.f / 127.f);
+  JQK_SMEM_ONCE(compress_tc_kernel, smem, "tensor-core compress smem attribute");
+  compress_tc_kernel<<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
   return 0;
 }

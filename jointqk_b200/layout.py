@@ -221,45 +221,44 @@ def decision_thresholds(codebook_rows: np.ndarray, widths: np.ndarray) -> np.nda
 BUCKETS = 128
 
 
-def bucket_tables(thresholds: np.ndarray, widths: np.ndarray):
-    """Coarse-to-exact quantiser tables for the tensor-core compress kernel.
+def unit_quantiser_tables(unit_centroids: dict):
+    """Shared quantiser tables of the tensor-core compress kernel, one set for all columns.
 
-    The kernel maps a transformed value to one of ``BUCKETS`` equal cells with a single fused
-    multiply-add, ``y = x * inv_step + off`` (``off`` carries the 2**23 bias that leaves the cell
-    index in the low mantissa bits), reads ``pre[cell]`` -- a lower bound of the code that is at most
-    one short -- and settles the code with one exact comparison, ``code = pre + (x >= thr[pre])``.
-    The comparison is against the exact fp32 decision threshold, so the result equals the full
-    threshold count whenever the lower bound is valid; validity needs neighbouring thresholds to be
-    at least three cells apart (one cell of slack on either side absorbs any rounding difference
-    between this host arithmetic and the device FMA).  Returns ``(pre uint8 (n, BUCKETS), aff float32
-    (n, 2), ok)``; ``ok`` is False if some column's thresholds are too close for the scheme.
-    """
-    thr = np.asarray(thresholds, dtype=np.float32)
-    widths = np.asarray(widths).astype(np.int64).reshape(-1)
-    n = thr.shape[0]
-    pre = np.zeros((n, BUCKETS), np.uint8)
-    aff = np.zeros((n, 2), np.float32)
-    aff[:, 1] = np.float32(2.0 ** 23)
-    ok = True
+    The kernel transforms keys with basis columns scaled by 1 / sigma_c, so every transformed
+    coordinate is quantised against the *unit* Lloyd-Max levels of its width: the decision thresholds
+    of a column, sigma_c * u_l up to a rounding, become u_l for every column of that width (the
+    change moves a code only when the value lies within ~1e-7 relative of a threshold).  Returns
+
+    * ``thr``  float32 (4, 16): exact fp32 decision thresholds of the unit codebook of width 1..4
+      (``decision_thresholds``), ``+inf`` padded;
+    * ``pre``  uint8 (4, 128): for one common grid of 128 cells over the value axis, a lower bound of
+      the code (at most one short) with ``16 * (width - 1)`` added, i.e. the index into ``thr``
+      flattened at which the one exact comparison is made;
+    * ``aff``  float32 (2,): the kernel maps a value to one of ``BUCKETS`` equal cells with one fused
+      multiply-add, ``y = x * aff[0] + aff[1]`` (aff[1] carries the 2**23 bias that leaves the cell index
+      in the low mantissa bits, after clamping).  The lower bound read from ``pre`` is valid because
+      neighbouring thresholds are at least three cells apart: one cell of slack on either side absorbs
+      any rounding difference between this host arithmetic and the device's.
+
+    ``unit_centroids[b]`` are the unit-variance centroids of width b (ascending)."""
+    thr = np.full((4, 16), np.inf, np.float32)
+    for b in range(1, 5):
+        rows = np.zeros((1, 16), np.float32)
+        rows[0, : 2 ** b] = np.asarray(unit_centroids[b], dtype=np.float32)
+        thr[b - 1, : 2 ** b - 1] = decision_thresholds(rows, np.array([b]))[0, : 2 ** b - 1]
+    t4 = thr[3, :15].astype(np.float64)
+    step = (t4[-1] - t4[0]) / (BUCKETS - 8)
+    inv_step = np.float32(1.0 / step)
+    off = np.float32(-(t4[0] - 4.0 * step) * float(inv_step) + 2.0 ** 23)
+    pre = np.zeros((4, BUCKETS), np.uint8)
     cells = np.arange(BUCKETS)
-    for c in range(n):
-        n_thr = (1 << int(widths[c])) - 1
-        if n_thr <= 1:
-            continue                      # one threshold (or none): cell 0 for every x, pre = 0
-        t = thr[c, :n_thr].astype(np.float64)
-        span = t[-1] - t[0]
-        if not np.isfinite(span) or span <= 0:
-            ok = False
-            continue
-        step = span / (BUCKETS - 8)
-        inv_step = np.float32(1.0 / step)
-        off = np.float32(-(t[0] - 4.0 * step) * float(inv_step) + 2.0 ** 23)
-        y = np.float32(thr[c, :n_thr].astype(np.float64) * float(inv_step) + float(off))   # ~ device fmaf
+    for b in range(1, 5):
+        n_thr = 2 ** b - 1
+        y = np.float32(thr[b - 1, :n_thr].astype(np.float64) * float(inv_step) + float(off))
         y = np.minimum(np.maximum(y, np.float32(2.0 ** 23)), np.float32(2.0 ** 23 + BUCKETS - 1))
         cell = y.view(np.uint32).astype(np.int64) & (BUCKETS - 1)
-        if np.any(np.diff(cell) < 3):
-            ok = False
-            continue
-        pre[c] = (cell[None, :] <= (cells[:, None] - 2)).sum(-1).astype(np.uint8)
-        aff[c] = (inv_step, off)
-    return pre, aff, ok
+        if n_thr > 1 and np.any(np.diff(cell) < 3):
+            raise AssertionError("unit thresholds too close for the cell grid")
+        lower = (cell[None, :] <= (cells[:, None] - 2)).sum(-1)          # thresholds safely below the cell
+        pre[b - 1] = (16 * (b - 1) + np.minimum(lower, n_thr - 1 if n_thr > 1 else 0)).astype(np.uint8)
+    return thr, pre, np.array([inv_step, off], np.float32)

@@ -14,7 +14,8 @@ import numpy as np
 import torch
 
 from . import _native
-from .layout import BUCKETS, MAX_TABLES, KeyLayout, bucket_tables, decision_thresholds, plan_key_layout
+from .codebooks import unit_gaussian_centroids
+from .layout import MAX_TABLES, KeyLayout, decision_thresholds, plan_key_layout, unit_quantiser_tables
 
 DESC_INTS = 32
 MAX_COLS = 128
@@ -76,10 +77,9 @@ class HeadTables:
         inv_rows = np.zeros((H, MAX_COLS, d), np.float32)
         thr = np.full((H, MAX_COLS, 16), np.inf, np.float32)
         cb_cols = np.zeros((H, MAX_COLS, 16), np.float32)
-        b_pre = np.zeros((H, MAX_COLS, BUCKETS), np.uint8)
-        b_aff = np.zeros((H, MAX_COLS, 2), np.float32)
-        b_aff[..., 1] = np.float32(2.0 ** 23)
-        buckets_ok = True
+        col_scale = np.ones((H, MAX_COLS), np.float32)     # 1 / sigma of the column's coordinate
+        unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 5)}
+        scaled_ok = True
         cb_np, fwd_np, inv_np = cb.numpy(), fwd.numpy(), inv.numpy()
         for h, lay in enumerate(self.layouts):
             desc[h, :8] = lay.descriptor()
@@ -97,8 +97,15 @@ class HeadTables:
             rows[:, :kk] = np.where(np.isfinite(cb_np[h][coords, :kk]), cb_np[h][coords, :kk], 0.0)
             cb_cols[h, :n] = rows
             thr[h, :n, :15] = decision_thresholds(rows, lay.col_width[:n])
-            b_pre[h, :n], b_aff[h, :n], ok = bucket_tables(thr[h, :n, :15], lay.col_width[:n])
-            buckets_ok = buckets_ok and ok
+            # the codebook row is unit levels x sigma (per_coord_quantization.py:107): the ratio of the
+            # top levels gives 1 / sigma back to an ulp, which is all the scaled transform needs
+            for c in range(n):
+                w = int(lay.col_width[c])
+                top = float(rows[c, (1 << w) - 1])
+                if not (top > 1e-30 and np.isfinite(top)):
+                    scaled_ok = False
+                else:
+                    col_scale[h, c] = np.float32(float(unit[w][-1]) / top)
         self.device = torch.device(device)
         if self.device.type == "cuda" and self.device.index is None:
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -106,12 +113,18 @@ class HeadTables:
         self.desc, self.col_meta, self.table_fields = up(desc), up(col_meta), up(fields)
         self.fwd_cols, self.qproj_cols, self.inv_rows = up(fwd_cols), up(qproj), up(inv_rows)
         self.thresholds, self.cb_cols = up(thr), up(cb_cols)
-        # coarse-to-exact quantiser tables; absent when some column's thresholds are too close for them
-        self.bucket_pre = up(b_pre) if buckets_ok else None
-        self.bucket_aff = up(b_aff) if buckets_ok else None
-        # three bf16 limbs of the forward map, [H][3][col][dim] (column-major = K-major B operand)
-        self.fwd_limbs = split_bf16_limbs(torch.from_numpy(fwd_cols).transpose(1, 2).contiguous(), 3) \
-            .permute(1, 0, 2, 3).contiguous().to(self.device)
+        # Tensor-core transform: the basis columns scaled by 1 / sigma of their coordinate, so that every
+        # transformed value is quantised against the unit levels of its width (one shared set of tables,
+        # layout.unit_quantiser_tables), split into three bf16 limbs, [H][3][col][dim] (column-major =
+        # K-major B operand).  Absent when a codebook is degenerate; the CUDA-core kernel then runs.
+        u_thr, u_pre, u_aff = unit_quantiser_tables(unit)
+        self.unit_thr, self.unit_aff = u_thr, u_aff
+        self.unit_pre = up(u_pre)
+        self.fwd_limbs = None
+        if scaled_ok:
+            scaled = torch.from_numpy(fwd_cols * col_scale[:, None, :])
+            self.fwd_limbs = split_bf16_limbs(scaled.transpose(1, 2).contiguous(), 3) \
+                .permute(1, 0, 2, 3).contiguous().to(self.device)
         # optional per-head mean, subtracted before the transform and added back after reconstruction
         self.center = None
         if center is not None:
@@ -123,10 +136,11 @@ class HeadTables:
             table_fields=self.table_fields.data_ptr(), fwd_cols=self.fwd_cols.data_ptr(),
             thresholds=self.thresholds.data_ptr(), cb_cols=self.cb_cols.data_ptr(),
             qproj_cols=self.qproj_cols.data_ptr(), inv_rows=self.inv_rows.data_ptr(),
-            fwd_limbs=self.fwd_limbs.data_ptr(),
-            bucket_pre=None if self.bucket_pre is None else self.bucket_pre.data_ptr(),
-            bucket_aff=None if self.bucket_aff is None else self.bucket_aff.data_ptr(),
-            center=None if self.center is None else self.center.data_ptr())
+            fwd_limbs=None if self.fwd_limbs is None else self.fwd_limbs.data_ptr(),
+            unit_pre=self.unit_pre.data_ptr(),
+            center=None if self.center is None else self.center.data_ptr(),
+            unit_thr=(C.c_float * 64)(*[float(x) for x in u_thr.reshape(-1)]),
+            unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])))
 
     @property
     def ref(self):

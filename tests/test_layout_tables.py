@@ -134,42 +134,58 @@ def test_head_tables_reject_wide_codebooks():
         HeadTables(None, None, cb, device="cpu")
 
 
-def test_bucket_quantiser_tables_are_exact():
-    """The coarse-to-exact quantiser of the tensor-core kernel (one FMA -> cell -> lower bound -> one
-    exact comparison) must reproduce the full threshold count for every input, whether the device
-    fuses the multiply-add or not."""
+def test_unit_quantiser_tables_are_exact():
+    """The shared coarse-to-exact quantiser of the tensor-core kernel (one FMA -> cell of a common grid
+    -> index of the one threshold left to compare) must reproduce the full threshold count of every
+    width for every input, whether the device fuses the multiply-add or not."""
     from jointqk_b200.codebooks import unit_gaussian_centroids
-    from jointqk_b200.layout import BUCKETS, bucket_tables
+    from jointqk_b200.layout import BUCKETS, unit_quantiser_tables
 
     rng = np.random.default_rng(0)
-    widths = np.array([1, 2, 3, 4, 4, 3, 2, 4])
-    stds = np.array([1, 0.3, 12.0, 0.01, 3.3, 1e-3, 7.0, 150.0], np.float32)
-    cb = np.zeros((8, 16), np.float32)
-    for i, w in enumerate(widths):
-        cb[i, : 2 ** w] = unit_gaussian_centroids(int(w)).numpy() * stds[i]
-    thr = decision_thresholds(cb, widths)
-    thr16 = np.full((8, 16), np.inf, np.float32)
-    thr16[:, :15] = thr
-    pre, aff, ok = bucket_tables(thr, widths)
-    assert ok and pre.max() <= 15
-    for i, w in enumerate(widths):
-        xs = [rng.normal(size=100000).astype(np.float32) * stds[i] * 1.7]
-        for t in thr[i, : 2 ** w - 1]:
+    unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 5)}
+    thr, pre, aff = unit_quantiser_tables(unit)
+    flat = thr.reshape(-1)
+    for b in range(1, 5):
+        n = 2 ** b - 1
+        assert np.all(np.isfinite(thr[b - 1, :n])) and np.all(np.isinf(thr[b - 1, n:]))
+        assert pre[b - 1].min() >= 16 * (b - 1) and pre[b - 1].max() <= 16 * (b - 1) + max(n - 1, 0)
+        xs = [rng.normal(size=200000).astype(np.float32) * 1.7]
+        for t in thr[b - 1, :n]:
             xs.append(np.array([np.nextafter(t, -np.inf), t, np.nextafter(t, np.inf)], np.float32))
-        xs.append(np.array([0, 1e30, -1e30, np.nan], np.float32))
+        xs.append(np.array([0, -0.0, 1e30, -1e30, np.nan], np.float32))
         x = np.concatenate(xs)
-        ref = (x[:, None] >= thr[i][None, :]).sum(-1)
+        ref = (x[:, None] >= thr[b - 1, :n][None, :]).sum(-1)
         for fused in (True, False):
             with np.errstate(invalid="ignore", over="ignore"):
                 if fused:
-                    y = np.float32(x.astype(np.float64) * float(aff[i, 0]) + float(aff[i, 1]))
+                    y = np.float32(x.astype(np.float64) * float(aff[0]) + float(aff[1]))
                 else:
-                    y = np.float32(np.float32(x * aff[i, 0]) + aff[i, 1])
+                    y = np.float32(np.float32(x * aff[0]) + aff[1])
             y = np.fmin(np.fmax(y, np.float32(2 ** 23)), np.float32(2 ** 23 + BUCKETS - 1))
             cell = y.view(np.uint32) & (BUCKETS - 1)
-            p = pre[i][cell].astype(np.int64)
-            assert np.array_equal(p + (x >= thr16[i][p]), ref)
-    # thresholds closer than three cells: the scheme must report that it does not apply
-    tight = np.full((1, 15), np.inf, np.float32)
-    tight[0, :3] = [0.0, 1e-6, 1.0]
-    assert bucket_tables(tight, np.array([2]))[2] is False
+            j = pre[b - 1][cell].astype(np.int64)
+            assert np.array_equal((j & 15) + (x >= flat[j]), ref)
+
+
+def test_scaled_limbs_quantise_like_the_reference_rule():
+    """Columns scaled by 1 / sigma and compared with the unit thresholds give the codes of the
+    per-column thresholds except within rounding of a boundary (rate far below 1e-5)."""
+    from jointqk_b200.codebooks import unit_gaussian_centroids
+    from jointqk_b200.layout import unit_quantiser_tables
+
+    rng = np.random.default_rng(1)
+    unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 5)}
+    uthr, _, _ = unit_quantiser_tables(unit)
+    bad = tot = 0
+    for b in range(1, 5):
+        for sigma in (1e-3, 0.37, 1.0, 21.5):
+            cb = np.zeros((1, 16), np.float32)
+            cb[0, : 2 ** b] = unit[b] * np.float32(sigma)
+            thr = decision_thresholds(cb, np.array([b]))[0, : 2 ** b - 1]
+            scale = np.float32(float(unit[b][-1]) / float(cb[0, 2 ** b - 1]))
+            x = (rng.normal(size=400000) * sigma).astype(np.float32)
+            want = (x[:, None] >= thr[None, :]).sum(-1)
+            got = ((x * scale)[:, None] >= uthr[b - 1, : 2 ** b - 1][None, :]).sum(-1)
+            bad += int((want != got).sum())
+            tot += x.size
+    assert bad / tot < 2e-6
