@@ -659,26 +659,60 @@ def bench_generate_loop(device, tables, cache, hbm_gbs: float) -> dict:
     torch.cuda.synchronize(device)
     wall = time.perf_counter() - t0
     ms = e0.elapsed_time(e1) / steps
-    # the same step as one replayed CUDA graph (append + attend; PagedKVCache.generate_step)
-    more_k = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device)
-    more_v = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
-    for t in range(8):
-        cache.generate_step(more_k[:, :, t:t + 1], more_v[:, :, t:t + 1], q)
+    # the same step through PagedKVCache.generate_step: the four launches replayed as one CUDA graph
+    # (inputs staged), then the single launch that appends, attends and advances the lengths itself
+    def graph_loop(fused: bool):
+        more_k = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device)
+        more_v = torch.randn(1, H, steps + 8, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+        for t in range(8):
+            cache.generate_step(more_k[:, :, t:t + 1], more_v[:, :, t:t + 1], q, fused_append=fused)
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for t in range(8, 8 + steps):
+            cache.generate_step(more_k[:, :, t:t + 1], more_v[:, :, t:t + 1], q, fused_append=fused)
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / steps, (time.perf_counter() - t0) / steps * 1e3
+
+    ms_g4, wall_g4 = graph_loop(False)
+    ms_g, wall_g = graph_loop(True)
+    # the fused launch called directly, rows read in place (no staging copies, no graph): what a model
+    # whose projection kernels write k, v and q into fixed buffers pays per layer and step
+    n_direct = steps
+    rows_k = torch.randn(n_direct + 8, 1, H, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    rows_v = torch.randn(n_direct + 8, 1, H, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    cache.reserve(0, cache.lengths[0] + n_direct + 8)
+    covered = cache.lengths[0] + n_direct + 8
+    tps = paged.split_for_lengths([covered], N_Q_HEADS, H)
+    ws = paged.DecodeWorkspace(1, N_Q_HEADS, H, -(-covered // tps), device)
+    out = torch.empty(1, N_Q_HEADS, HEAD_DIM, device=device)
+
+    def direct(i):
+        paged.decode_append_attend(tables, q, rows_k[i], rows_v[i], cache.seq_lens, covered, cache.page_table,
+                                   cache.k_pool, cache.v_pool, out, ws, cache.status, tps)
+
+    for i in range(8):
+        direct(i)
     torch.cuda.synchronize(device)
-    t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for t in range(8, 8 + steps):
-        out = cache.generate_step(more_k[:, :, t:t + 1], more_v[:, :, t:t + 1], q)
+    for i in range(8, 8 + n_direct):
+        direct(i)
     e1.record()
     torch.cuda.synchronize(device)
-    wall_g = time.perf_counter() - t0
-    ms_g = e0.elapsed_time(e1) / steps
+    ms_d = e0.elapsed_time(e1) / n_direct
+    cache.lengths[0] += n_direct + 8
+    assert cache.seq_lens[0].item() == cache.lengths[0]
     paged.check_status(cache.status)
     return {"workload": "generate loop on the headline shape: append 1 token (K compress + V store + length), then decode, context %d -> %d"
-                        % (cache.lengths[0] - 2 * steps - 8, cache.lengths[0]),
-            "value": 1.0 / (ms_g * 1e-3), "unit": UNIT, "ms_per_step": ms_g, "wall_ms_per_step": wall_g / steps * 1e3,
-            "how": "PagedKVCache.generate_step: the four launches of a step replayed as one CUDA graph, inputs copied into fixed staging buffers",
+                        % (cache.lengths[0] - 4 * steps - 32, cache.lengths[0]),
+            "value": 1.0 / (ms_g * 1e-3), "unit": UNIT, "ms_per_step": ms_g, "wall_ms_per_step": wall_g,
+            "how": "PagedKVCache.generate_step: one launch per step (jqk_decode_append_attend appends the row, attends and advances the lengths), rows read in place",
+            "fused_launch_direct": {"ms_per_step": ms_d, "launches_per_step": 1,
+                                    "note": "back-to-back jqk_decode_append_attend launches reading the new rows in place, no graph"},
+            "graph_of_four_launches": {"ms_per_step": ms_g4, "wall_ms_per_step": wall_g4},
             "separate_launches": {"ms_per_step": ms, "wall_ms_per_step": wall / steps * 1e3, "launches_per_step": 4},
             "steps": steps}
 
@@ -1021,7 +1055,7 @@ def main() -> None:
     ap.add_argument("--workload", default="headline", choices=["headline", "batch64"],
                     help="headline: the single-layer context-32768 step (default, what the JSON contract names); "
                          "batch64: the 32-layer, 64-sequence decode config sharded by sequence over the ranks")
-    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "packed_values", "scale"],
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "packed_values", "generate", "scale"],
                     help="run only one of the secondary stages (or the three partitioned workloads) and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1036,6 +1070,10 @@ def main() -> None:
         dev = torch.device("cuda", local_rank)
         torch.cuda.set_device(dev)
         hbm, tf, kind = measured_peaks()
+        if args.stage == "generate":
+            tables, _comps, caches, _q, _keys = build_decode_workload(dev, 0, 1)
+            print(json.dumps(bench_generate_loop(dev, tables, caches[0], hbm)), flush=True)
+            return
         res = (bench_compress(dev, hbm, kind) if args.stage == "compress" else
                bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else
                bench_value_store(dev, hbm, kind) if args.stage == "values" else

@@ -215,6 +215,33 @@ int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t 
                           size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
+ * One step of a generate loop in one launch: append the newest token of every sequence, attend,
+ * advance the lengths.  Replaces the reference's Mode-B step, which compresses the new key into the
+ * cache entry (experiments/stage1/toolkit/jointqk_press.py:298-304) and then runs stock attention,
+ * and does the work of jqk_compress_paged + jqk_store_values_paged + jqk_decode_attend for that
+ * token in a single kernel:
+ *   - new_k / new_v: one row of d elements per (sequence, kv head), element (s, h, i) at
+ *     s * seq_stride + h * head_stride + i (strides in elements), dtypes k_dtype / v_dtype
+ *     (JQK_DTYPE_*);
+ *   - the row of sequence s goes to position seq_lens[s]; its page must already be in page_table;
+ *     the key's codes are bit-identical to those jqk_compress_paged writes for the same row;
+ *   - the step attends over seq_lens[s] + 1 keys; max_seq_len (grid and workspace sizing) must
+ *     cover that;
+ *   - when the launch is done seq_lens[s] has been advanced by one for every sequence, so the call
+ *     can be replayed from a CUDA graph without host work in between.
+ * bf16 value pool only (no packed values); tables without a centre.  Everything else as in
+ * jqk_decode_attend.
+ */
+int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, const void* new_k,
+                                 const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
+                                 int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride,
+                                 int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
+                                 int32_t tokens_per_split, const int32_t* page_table,
+                                 int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
+                                 void* out, int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                                 int32_t* status, void* stream);
+
+/*
  * jqk_decode_attend over packed values: the value pool holds codes of a second per-coordinate
  * compressor (`v_tables`, optionally centred) in the same paged record format as the keys, written
  * by jqk_compress_paged with those tables.  The kernel dequantises a tile of values into shared

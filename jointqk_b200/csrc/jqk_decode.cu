@@ -118,6 +118,7 @@ struct DecodeWs {
   float* part_acc;         // [n_seqs][n_q_heads][max_splits][128]
   unsigned int* counters;  // [n_seqs][n_kv_heads * q_blocks]
   int max_splits;
+  unsigned int* grid_ticket;  // one counter for the whole launch (append variant: who advances the lengths)
 };
 
 // Per-warp staging of one tile: the two V pages (dims-major, see the V page layout in the file
@@ -153,6 +154,11 @@ template <> struct DecodeSmemT<false> {
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
+  // the key and value row appended by this launch (blocks of the last split only)
+  float ap_k[JQK_MAX_DIM];
+  uint32_t ap_words[JQK_MAX_WORDS];
+  __nv_bfloat16 ap_v[JQK_MAX_DIM];
+  int ap_page, ap_last;
 };
 template <> struct DecodeSmemT<true> {
   struct { TableRecord rec; } t;     // the key tables always come from the table kernel
@@ -274,6 +280,26 @@ struct ValueSide {
   int n_heads, wpr;
 };
 
+// The newest token of every sequence, appended by the decode launch itself (k == nullptr: none).
+// Position seq_lens[s] takes the row; the launch attends over seq_lens[s] + 1 keys and its last
+// block to finish advances every length by one.
+struct AppendSide {
+  const void* k;            // [n_seqs][n_kv_heads][d] through the strides below (elements)
+  const void* v;
+  int k_dtype, v_dtype;     // JQK_DTYPE_* of k and of v
+  long long k_seq_stride, k_head_stride, v_seq_stride, v_head_stride;
+  uint32_t* k_pool;         // the pools again, writable
+  __nv_bfloat16* v_pool;
+  int32_t* seq_lens;        // the lengths again, writable
+  int n_seqs;
+};
+
+__device__ __forceinline__ float load_elem_f32(const void* p, int dtype, size_t i) {
+  if (dtype == JQK_DTYPE_F32) return reinterpret_cast<const float*>(p)[i];
+  if (dtype == JQK_DTYPE_F16) return __half2float(reinterpret_cast<const __half*>(p)[i]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
 // (sum_t p_t x_hat_t) / L in the value basis -> attention output: one 128 x d product per query head
 // with the value side's inverse map, plus the mean the values were centred with.  `yb`: shared,
 // [JQK_MAX_GROUP][128] normalised sums, then JQK_MAX_GROUP flags (some key was attended).
@@ -292,6 +318,56 @@ __device__ __forceinline__ void values_to_output(const float* yb, int n_group, c
   }
 }
 
+// The appended key of (seq, head): transformed and quantised exactly as compress_token_kernel does
+// (thread = column, the dims in ascending order with fused multiply-adds: the same bits), the value
+// row converted to bf16.  Both stay in shared memory for the warp whose tile holds the position;
+// with `write` they also go to their slot of the tail page.  Called by all threads of the block.
+template <int D>
+__device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __restrict__ fwd_cols,
+                                        const int32_t* __restrict__ col_meta, const float* __restrict__ thresholds,
+                                        int n_heads, int wpr, int n_active, int n_words, const void* k_row,
+                                        const void* v_row, int k_dtype, int v_dtype, uint32_t* k_pool, __nv_bfloat16* v_pool,
+                                        int head, int seq, bool write, int pos,
+                                        const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
+                                        int32_t* status) {
+  const int tid = threadIdx.x;
+  if (tid < D) {
+    sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
+  } else if (tid >= 128 && tid < 128 + D) {
+    sm.ap_v[tid - 128] = __float2bfloat16(load_elem_f32(v_row, v_dtype, tid - 128));
+  } else if (tid >= 256 && tid < 256 + JQK_MAX_WORDS) {
+    sm.ap_words[tid - 256] = 0u;
+  } else if (tid == DEC_THREADS - 1) {
+    sm.ap_page = lookup_page(page_table, pt_stride, seq, pos / JQK_PAGE_TOKENS, n_pages, status);
+  }
+  __syncthreads();
+  if (tid < n_active) {
+    const float* w = fwd_cols + (size_t)head * D * 128 + tid;
+    float x = 0.f;
+#pragma unroll 32
+    for (int i = 0; i < D; ++i) x = fmaf(sm.ap_k[i], __ldg(w + (size_t)i * 128), x);
+    const int m = col_meta[(size_t)head * 128 + tid];
+    const float* th = thresholds + ((size_t)head * 128 + tid) * 16;
+    const int n_thr = (1 << (m & 15)) - 1;
+    uint32_t code = 0;
+    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const int bp = (m >> 4) & 1023;
+    atomicOr(&sm.ap_words[bp >> 5], code << (bp & 31));
+  }
+  __syncthreads();
+  const int page = sm.ap_page;
+  if (write && page >= 0) {
+    const int slot = pos % JQK_PAGE_TOKENS;
+    if (tid < n_words) {
+      k_pool[(((size_t)page * n_heads + head) * wpr + tid) * JQK_PAGE_TOKENS + slot] = sm.ap_words[tid];
+    } else if (tid >= 128 && tid < 128 + D) {
+      const int i = tid - 128;
+      v_pool[((size_t)page * n_heads + head) * (size_t)(JQK_PAGE_TOKENS * D) + i * JQK_PAGE_TOKENS +
+                (((slot >> 3) ^ ((i >> 2) & 1)) * 8) + (slot & 7)] = sm.ap_v[i];
+    }
+  }
+}
+
 // D = head_dim (64 or 128).  VQ: values are packed codes of a second compressor (v_pool is then the
 // uint32 code pool, `vs` its tables); the keys' tables then always come from the table kernel.
 template <int D, bool BUILD_IN_BLOCK, bool VQ>
@@ -300,7 +376,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
               const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
               const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
-              void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs) {
+              void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs, AppendSide ap) {
   static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
@@ -321,6 +397,28 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // the workspace) is cut to what the grid covers and flagged; otherwise the ticket below would
   // never see its last block.
   int len = seq_lens[seq];
+  bool appending = false;
+  if constexpr (!VQ) appending = ap.k != nullptr;
+  if (appending) len += 1;  // this launch attends over the key it appends
+  // Append variant: every block of the launch passes here exactly once on its way out, all of its
+  // threads together.  Each has read its length by then, so the block that takes the last ticket
+  // may advance the lengths for the next launch.
+  auto leave = [&]() {
+    if constexpr (!VQ) {
+      if (!appending) return;
+      __syncthreads();
+      if (tid == 0) {
+        unsigned int prev;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(ws.grid_ticket) : "memory");
+        const bool last = prev == gridDim.x * gridDim.y * gridDim.z - 1u;
+        if (last) *ws.grid_ticket = 0u;
+        sm.ap_last = last ? 1 : 0;
+      }
+      __syncthreads();
+      if (sm.ap_last)
+        for (int s2 = tid; s2 < ap.n_seqs; s2 += DEC_THREADS) ap.seq_lens[s2] += 1;
+    }
+  };
   {
     const long long cap = (long long)gridDim.x * tokens_per_split;
     if (len > cap) {
@@ -335,9 +433,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if (split == 0)
       for (int e = tid; e < n_group * D; e += DEC_THREADS)
         store_out(out, out_dtype, ((size_t)seq * n_q_heads + qh0 + e / D) * D + e % D, 0.f);
+    leave();
     return;
   }
-  if (split >= n_splits) return;
+  if (split >= n_splits) { leave(); return; }
   // the table build's reads go out first: nothing a block does later is queued ahead of them
   TableLoads tloads;
   if constexpr (BUILD_IN_BLOCK)
@@ -417,6 +516,20 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if (n_my > 1) issue_keys(1, p2, p3);
   }
 
+  // the block whose split ends the context takes the appended row (every query block keeps its own
+  // copy in shared memory; the first one also writes it to the tail page)
+  int ap_pos = -1;
+  if constexpr (!VQ) {
+    if (appending && split == n_splits - 1) {
+      ap_pos = len - 1;
+      const size_t k_esz = ap.k_dtype == JQK_DTYPE_F32 ? 4 : 2, v_esz = ap.v_dtype == JQK_DTYPE_F32 ? 4 : 2;
+      append_row<D>(sm, tb.fwd_cols, tb.col_meta, tb.thresholds, tb.n_heads, tb.words_per_record, hd.n_active, hd.n_words,
+                    (const char*)ap.k + ((size_t)seq * ap.k_seq_stride + (size_t)head * ap.k_head_stride) * k_esz,
+                    (const char*)ap.v + ((size_t)seq * ap.v_seq_stride + (size_t)head * ap.v_head_stride) * v_esz,
+                    ap.k_dtype, ap.v_dtype, ap.k_pool, ap.v_pool, head, seq, qb == 0, ap_pos, page_table, pt_stride, n_pages, status);
+    }
+  }
+
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
@@ -481,6 +594,15 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
     bool landed = bar_wait(&sm.kfull[warp][r & 1], (r >> 1) & 1);
 
+    if constexpr (!VQ) {
+      if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {  // the page copy may predate the append: take the record from the block's own copy
+        const int slot = ap_pos - t0;
+        uint32_t* kd = reinterpret_cast<uint32_t*>(st.k[r & 1][slot >> 4]) + (slot & 15);
+        if (lane < n_words) kd[lane * JQK_PAGE_TOKENS] = sm.ap_words[lane];
+        __syncwarp();
+      }
+    }
+
     // ---- score this lane's key from the staged record words ----
     const int tok = t0 + lane;
     const bool lane_ok = landed && tok < t_end && ((lane < 16) ? page_lo : page_hi) >= 0;
@@ -522,6 +644,14 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
+    if constexpr (!VQ) {
+      if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {
+        const int ts = (ap_pos - t0) & 15;
+        unsigned char* vt = reinterpret_cast<unsigned char*>(st.v[(ap_pos - t0) >> 4]);
+        for (int d = lane; d < D; d += 32)
+          *reinterpret_cast<__nv_bfloat16*>(vt + d * 32 + (((ts >> 3) ^ ((d >> 2) & 1)) * 16) + (ts & 7) * 2) = sm.ap_v[d];
+      }
+    }
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
     if constexpr (VQ) {
@@ -663,7 +793,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       values_to_output<D>(yb, n_group, vs, head, v_n_active, out, out_dtype, (size_t)seq * n_q_heads + qh0);
     }
   }
-  if (single) return;
+  if (single) { leave(); return; }
 
   // ---- the last block of this (sequence, head group) to finish merges the splits ------------
   // Ticket with release/acquire at gpu scope: the barrier orders this block's partial results
@@ -677,7 +807,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     sm.is_last = (prev == (unsigned int)(n_splits - 1));
   }
   __syncthreads();
-  if (!sm.is_last) return;
+  if (!sm.is_last) { leave(); return; }
   // A thread owns four output dims of one head and every third split: it first puts its partial
   // rows in flight (MERGE_BATCH independent 16-byte loads), then one warp per head turns the
   // splits' (max, sum) pairs into one weight per split, so a single memory round trip covers both.
@@ -761,6 +891,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     values_to_output<D>(yb, n_group, vs, head, v_n_active, out, out_dtype, (size_t)seq * n_q_heads + qh0);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
+  leave();
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -780,7 +911,8 @@ extern "C" size_t jqk_decode_workspace_bytes(int32_t n_seqs, int32_t n_q_heads, 
   if (n_seqs <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_splits <= 0) return 0;
   const size_t rows = (size_t)n_seqs * n_q_heads * max_splits;
   const size_t groups = (size_t)n_seqs * n_kv_heads * q_blocks_for(n_q_heads, n_kv_heads);
-  size_t b = align_up(groups * sizeof(unsigned int), 256);
+  size_t b = 256;  // the launch-wide ticket of the append variant
+  b += align_up(groups * sizeof(unsigned int), 256);
   b += align_up(rows * sizeof(float), 256) * 2;
   b += align_up(rows * JQK_MAX_DIM * sizeof(float), 256);
   b += align_up(groups * sizeof(TableRecord), 256);
@@ -865,7 +997,7 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
                              int32_t tokens_per_split, const int32_t* page_table,
                              int32_t page_table_stride, int32_t n_pages, const uint32_t* k_pool,
                              const void* v_pool, void* out, int32_t out_dtype, void* workspace,
-                             size_t workspace_bytes, int32_t* status, void* stream) {
+                             size_t workspace_bytes, int32_t* status, void* stream, const AppendSide* append = nullptr) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
   if (v_tables) {
@@ -889,13 +1021,14 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
   if (max_splits > MAX_SPLITS) return fail(JQK_E_UNSUPPORTED, "%d key splits exceed %d: use a larger tokens_per_split", max_splits, MAX_SPLITS);
   const int qbl = q_blocks_for(n_q_heads, tables->n_heads);
-  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits};
+  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits, nullptr};
   {
     const size_t need = jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits);
     if (!workspace || workspace_bytes < need) return fail(JQK_E_WORKSPACE, "decode workspace needs %zu bytes, got %zu", need, workspace_bytes);
     if ((uintptr_t)workspace % 16) return fail(JQK_E_ARG, "workspace must be 16-byte aligned");
     const size_t rows = (size_t)n_seqs * n_q_heads * max_splits;
     char* p = (char*)workspace;
+    ws.grid_ticket = (unsigned int*)p; p += 256;
     ws.counters = (unsigned int*)p; p += align_up((size_t)n_seqs * tables->n_heads * qbl * sizeof(unsigned int), 256);
     ws.part_m = (float*)p; p += align_up(rows * sizeof(float), 256);
     ws.part_l = (float*)p; p += align_up(rows * sizeof(float), 256);
@@ -925,6 +1058,8 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   cfg.attrs = pdl_attr;
   cfg.numAttrs = 1;
   ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+  AppendSide ap{};
+  if (append) ap = *append;
   if (v_tables)
     vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
                    v_tables->n_heads, v_tables->words_per_record};
@@ -934,7 +1069,7 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
     JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");                 \
     JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ>, *tables, (const __nv_bfloat16*)q, n_q_heads,   \
                                    seq_lens, tokens_per_split, page_table, page_table_stride, n_pages, k_pool,        \
-                                   v_pool, out, out_dtype, ws, status, vs),                                           \
+                                   v_pool, out, out_dtype, ws, status, vs, ap),                                       \
                 "decode launch");                                                                                     \
   } while (0)
   if (v_tables) {
@@ -969,6 +1104,31 @@ extern "C" int32_t jqk_decode_attend_packed_values(const jqk_head_tables* tables
   if (!v_tables) return fail(JQK_E_ARG, "null value tables");
   return decode_launch(tables, v_tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
                        page_table_stride, n_pages, k_pool, v_code_pool, out, out_dtype, workspace, workspace_bytes, status, stream);
+}
+
+// One step of a generate loop in one launch: the newest key and value row of every sequence go to
+// position seq_lens[s] of its cache (compressed exactly as jqk_compress_paged would), the step
+// attends over seq_lens[s] + 1 keys, and seq_lens is advanced by one when the launch is done.
+extern "C" int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, const void* new_k,
+                                            const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
+                                            int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride,
+                                            int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
+                                            int32_t tokens_per_split, const int32_t* page_table,
+                                            int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
+                                            void* out, int32_t out_dtype, void* workspace, size_t workspace_bytes,
+                                            int32_t* status, void* stream) {
+  int32_t rc = check_tables(tables);
+  if (rc) return rc;
+  if (!new_k || !new_v) return fail(JQK_E_ARG, "null new_k or new_v");
+  for (int32_t dt : {k_dtype, v_dtype})
+    if (dt != JQK_DTYPE_F32 && dt != JQK_DTYPE_BF16 && dt != JQK_DTYPE_F16) return fail(JQK_E_ARG, "unknown dtype %d", dt);
+  if (tables->center) return fail(JQK_E_UNSUPPORTED, "centred tables are for values; keys are appended uncentred");
+  if (max_seq_len <= 0) return fail(JQK_E_ARG, "max_seq_len must cover the context after the append");
+  AppendSide ap{new_k, new_v, k_dtype, v_dtype, (long long)k_seq_stride, (long long)k_head_stride, (long long)v_seq_stride,
+                (long long)v_head_stride, k_pool, (__nv_bfloat16*)v_pool, seq_lens, n_seqs};
+  return decode_launch(tables, nullptr, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                       page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, workspace, workspace_bytes, status,
+                       stream, &ap);
 }
 
 extern "C" int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const void* q_host, void* q_pinned,
@@ -1057,7 +1217,7 @@ extern "C" int32_t jqk_decode_attend_static(const jqk_head_tables* tables, const
                 "this call needs %zu bytes of split scratch but the built-in array holds %d; use fewer splits "
                 "(larger tokens_per_split), a smaller batch, or jqk_decode_attend with a caller workspace",
                 need, (int)JQK_DECODE_STATIC_SCRATCH_BYTES);
-  if ((size_t)n_seqs * tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads) * sizeof(unsigned int) > 65536)
+  if (256 + (size_t)n_seqs * tables->n_heads * q_blocks_for(n_q_heads, tables->n_heads) * sizeof(unsigned int) > 65536)
     return fail(JQK_E_WORKSPACE, "too many (sequence, head group) pairs for the built-in ticket area");
   void* scratch = nullptr;
   rc = decode_static_scratch(&scratch, (cudaStream_t)stream);

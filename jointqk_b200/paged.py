@@ -257,6 +257,43 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
     return out
 
 
+def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                         seq_lens: torch.Tensor, max_seq_len: int, page_table: torch.Tensor, k_pool: torch.Tensor,
+                         v_pool: torch.Tensor, out: torch.Tensor, workspace: DecodeWorkspace, status: torch.Tensor,
+                         tokens_per_split: int = 0) -> torch.Tensor:
+    """One generate step in one launch: the rows k_new / v_new (n_seqs, H, 1, d) or (n_seqs, H, d) go
+    to position ``seq_lens[s]`` of every sequence (pages already in the table), the step attends
+    over ``seq_lens[s] + 1`` keys (``max_seq_len`` covers that) and ``seq_lens`` is advanced on the
+    device.  bf16 value pool only."""
+    if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
+        raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
+    if v_pool.dtype != torch.bfloat16:
+        raise ValueError("the fused append writes a bf16 value pool")
+    if out.shape != q.shape or not out.is_contiguous():
+        raise ValueError("out must be contiguous with the shape of q")
+    if k_new.dim() == 4:
+        if k_new.shape[2] != 1 or v_new.shape[2] != 1:
+            raise ValueError("one new token per sequence")
+        k_new, v_new = k_new[:, :, 0], v_new[:, :, 0]
+    n, h, d = k_new.shape
+    if (n, h, d) != (q.shape[0], tables.n_heads, tables.d) or v_new.shape != k_new.shape:
+        raise ValueError(f"k_new / v_new must be ({q.shape[0]}, {tables.n_heads}, {tables.d}) rows")
+    ok = (torch.float32, torch.bfloat16, torch.float16)
+    if k_new.dtype not in ok or v_new.dtype not in ok:
+        raise ValueError("k_new and v_new must be fp32, bf16 or fp16")
+    if k_new.stride(2) != 1 or v_new.stride(2) != 1:
+        raise ValueError("rows must be contiguous in their last dimension")
+    if seq_lens.dtype != torch.int32:
+        raise ValueError("seq_lens must be int32")
+    _native.check(_native.lib.jqk_decode_append_attend(
+        tables.ref, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), _native.torch_dtype_code(k_new.dtype),
+        _native.torch_dtype_code(v_new.dtype), k_new.stride(0), k_new.stride(1), v_new.stride(0), v_new.stride(1), n, q.shape[1], seq_lens.data_ptr(),
+        int(max_seq_len), int(tokens_per_split), page_table.data_ptr(), page_table.stride(0), int(k_pool.shape[0]),
+        k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), _native.torch_dtype_code(out.dtype),
+        workspace.buf.data_ptr(), workspace.buf.numel(), status.data_ptr(), _stream_ptr(tables.device)))
+    return out
+
+
 class PagePool:
     """Physical pages of one layer (packed K and bf16 V side by side, one index space) with a free
     list.  ``take`` hands out pages; when the list runs dry the pool grows: larger tensors are
@@ -366,6 +403,7 @@ class PagedKVCache:
         need = pages_for(n_tokens) - len(self._pages[seq])
         if need <= 0:
             return
+        self._gen_budget = 0
         have = len(self._pages[seq])
         new = self.pool.take(need)
         self._pages[seq].extend(new)
@@ -379,6 +417,7 @@ class PagedKVCache:
 
     def release(self, seq: int) -> None:
         """Forget sequence ``seq`` and return its pages to the pool."""
+        self._gen_budget = 0
         self.pool.give_back(self._pages[seq])
         self._pages[seq] = []
         self.lengths[seq] = 0
@@ -419,28 +458,49 @@ class PagedKVCache:
         for s in range(n):
             self.lengths[s] += 1
 
-    def generate_step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor) -> torch.Tensor:
-        """One step of a generate loop as a single replayed CUDA graph: append the newest token of
-        every sequence (K compress, V store, lengths advanced on the device), then attend.
+    RESERVE_AHEAD = 64   # tokens of page capacity the fused generate step keeps ahead of the context
 
-        k_new / v_new (n_seqs, H, 1, d) and q bf16 (n_seqs, Hq, d) are copied into fixed staging
-        buffers (what a model's projection kernels would write into), so the captured launches see
-        stable addresses; the result is a device tensor that the next call overwrites.  The graph is
-        captured on first use and again whenever something it baked in changes: the page table or the
-        pools moved (growth), or the longest context crossed the split boundary the grid was sized
-        for (the capture rounds the context up to a whole number of splits, so that is every
-        ``tokens_per_split`` steps at most).  Pages are reserved on the host before the replay, which
-        only writes table entries in place."""
+    def generate_step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor,
+                      fused_append: bool = True) -> torch.Tensor:
+        """One step of a generate loop: append the newest token of every sequence (K compress, V store,
+        lengths advanced on the device), then attend.  With a bf16 value pool that is one kernel
+        launch, which reads the rows in place (``jqk_decode_append_attend``).  ``fused_append=False``,
+        and always with packed values: the separate compress, store, length and decode launches,
+        replayed as one CUDA graph.
+
+        k_new / v_new (n_seqs, H, 1, d), q bf16 (n_seqs, Hq, d); the result is a device tensor that
+        the next call overwrites.  Pages are reserved on the host before the launch, which only
+        writes table entries in place.  In the graph form the inputs are first copied into fixed
+        staging buffers, so that the captured launches see stable addresses; the graph is captured on
+        first use and again whenever something it baked in changes: the page table or the pools moved
+        (growth), or the longest context crossed the split boundary the grid was sized for (the split
+        set-up rounds the context up to a whole number of splits, so that is every
+        ``tokens_per_split`` steps at most)."""
         n = len(self.lengths)
         dev = self.tables.device
+        gs = getattr(self, "_gen_step", None)
+        # Fast path of the fused step: while no sequence needs a page and the context stays inside
+        # what the grid was sized for, a step is one library call and nothing else on the host.
+        if (fused_append and gs is not None and gs["fused"] and getattr(self, "_gen_budget", 0) > 0
+                and gs["generation"] == self.pool.generation and gs["lengths_after"] == self.lengths
+                and gs["shape"] == (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) and q.is_contiguous()):
+            self._gen_budget -= 1
+            decode_append_attend(self.tables, q, k_new, v_new, self.seq_lens, gs["covered"], self.page_table, self.k_pool,
+                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"])
+            for s_ in range(n):
+                self.lengths[s_] += 1
+            gs["lengths_after"] = list(self.lengths)
+            return gs["out"]
         if k_new.shape[0] != n or k_new.shape[2] != 1:
             raise ValueError(f"generate_step takes one token for each of the {n} sequences")
-        for s_ in range(n):
-            self.reserve(s_, self.lengths[s_] + 1)
+        for s_ in range(n):   # pages a few steps ahead, so that the host touches the table once in a while only
+            self.reserve(s_, self.lengths[s_] + (self.RESERVE_AHEAD if fused_append and self.v_tables is None else 1))
         gs = getattr(self, "_gen_step", None)
         new_max = max(self.lengths) + 1
+        fused = self.v_tables is None and bool(fused_append)
         if (gs is None or gs["generation"] != self.pool.generation or gs["table_ptr"] != self.page_table.data_ptr()
-                or gs["shape"] != (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) or new_max > gs["covered"]):
+                or gs["shape"] != (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) or new_max > gs["covered"]
+                or gs["fused"] != fused):
             n_q_heads = q.shape[1]
             tps = split_for_lengths([x + 1 for x in self.lengths], n_q_heads, self.tables.n_heads)
             covered = -(-new_max // tps) * tps                     # the grid covers contexts up to here
@@ -448,38 +508,50 @@ class PagedKVCache:
             if getattr(self, "_ones", None) is None or self._ones.numel() != n:
                 self._ones = torch.ones(n, dtype=torch.int32, device=dev)
             gs = {"generation": self.pool.generation, "table_ptr": self.page_table.data_ptr(), "covered": covered,
-                  "shape": (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype), "ws": ws,
-                  "pools": (self.k_pool, self.v_pool, self.page_table),
-                  "k": torch.empty_like(k_new, device=dev).contiguous(), "v": torch.empty_like(v_new, device=dev).contiguous(),
-                  "q": torch.empty_like(q, device=dev), "out": torch.empty(q.shape, dtype=torch.float32, device=dev),
-                  "stream": torch.cuda.Stream(dev)}
+                  "shape": (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype), "ws": ws, "tps": tps,
+                  "fused": fused, "pools": (self.k_pool, self.v_pool, self.page_table),
+                  "out": torch.empty(q.shape, dtype=torch.float32, device=dev)}
+            if not fused:
+                gs.update({"k": torch.empty_like(k_new, device=dev).contiguous(), "v": torch.empty_like(v_new, device=dev).contiguous(),
+                           "q": torch.empty_like(q, device=dev), "stream": torch.cuda.Stream(dev)})
 
-            def enqueue() -> None:
-                compress_into(self.tables, gs["k"], self._ones, 1, self.page_table, self.k_pool, self.status, self.seq_lens)
-                self._store_values(gs["v"], self._ones, 1, self.seq_lens)
-                self.seq_lens[:n] += 1
-                decode_attend(self.tables, gs["q"], self.seq_lens, covered, self.page_table, self.k_pool, self.v_pool,
-                              gs["out"], ws, self.status, tps, v_tables=self.v_tables)
+                def enqueue() -> None:
+                    compress_into(self.tables, gs["k"], self._ones, 1, self.page_table, self.k_pool, self.status, self.seq_lens)
+                    self._store_values(gs["v"], self._ones, 1, self.seq_lens)
+                    self.seq_lens[:n] += 1
+                    decode_attend(self.tables, gs["q"], self.seq_lens, covered, self.page_table, self.k_pool, self.v_pool,
+                                  gs["out"], ws, self.status, tps, v_tables=self.v_tables)
 
-            # the library's one-time set-up (shared-memory attributes) must happen outside a capture:
-            # run the step once for real on a scratch copy of the lengths, then restore them
-            saved = self.seq_lens.clone()
-            gs["k"].copy_(k_new); gs["v"].copy_(v_new); gs["q"].copy_(q)
-            with torch.cuda.stream(gs["stream"]):
-                gs["stream"].wait_stream(torch.cuda.current_stream(dev))
-                enqueue()
-                gs["stream"].synchronize()
-                self.seq_lens.copy_(saved)
-                gs["graph"] = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gs["graph"], stream=gs["stream"]):
+                # the library's one-time set-up (shared-memory attributes) must happen outside a capture:
+                # run the step once for real on a scratch copy of the lengths, then restore them
+                saved = self.seq_lens.clone()
+                gs["k"].copy_(k_new); gs["v"].copy_(v_new); gs["q"].copy_(q)
+                with torch.cuda.stream(gs["stream"]):
+                    gs["stream"].wait_stream(torch.cuda.current_stream(dev))
                     enqueue()
+                    gs["stream"].synchronize()
+                    self.seq_lens.copy_(saved)
+                    gs["graph"] = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gs["graph"], stream=gs["stream"]):
+                        enqueue()
             self._gen_step = gs
-        gs["k"].copy_(k_new, non_blocking=True)
-        gs["v"].copy_(v_new, non_blocking=True)
-        gs["q"].copy_(q, non_blocking=True)
-        gs["graph"].replay()
+        if fused:
+            # one launch on the caller's stream: the kernel reads the rows where they are, appends them,
+            # attends and advances the lengths; there is nothing to stage and nothing to capture
+            decode_append_attend(self.tables, q if q.is_contiguous() else q.contiguous(), k_new, v_new, self.seq_lens,
+                                 gs["covered"], self.page_table, self.k_pool, self.v_pool, gs["out"], gs["ws"],
+                                 self.status, gs["tps"])
+        else:
+            gs["k"].copy_(k_new, non_blocking=True)
+            gs["v"].copy_(v_new, non_blocking=True)
+            gs["q"].copy_(q, non_blocking=True)
+            gs["graph"].replay()
         for s_ in range(n):
             self.lengths[s_] += 1
+        gs["lengths_after"] = list(self.lengths)
+        # steps that need neither a page nor a larger grid
+        self._gen_budget = min(min(len(pg) * PAGE_TOKENS - ln for pg, ln in zip(self._pages, self.lengths)),
+                               gs["covered"] - max(self.lengths)) if n else 0
         return gs["out"]
 
     def _store_values(self, values: torch.Tensor, n_tok: torch.Tensor, max_tokens: int, starts: torch.Tensor) -> None:

@@ -111,7 +111,7 @@ def test_generate_loop_append_equals_prefill():
 
 
 def test_generate_step_graph_equals_append_then_decode():
-    """generate_step (append + attend as one replayed graph, recaptured when the context crosses the
+    """generate_step in its graph form (append + attend as one replayed graph, recaptured when the context crosses the
     split boundary its grid covers or the pool moves) returns what append() followed by decode()
     returns, step after step."""
     H = 2
@@ -127,7 +127,7 @@ def test_generate_step_graph_equals_append_then_decode():
     b.prefill(kk[:, :, :n0], v[:, :, :n0])
     captures = set()
     for i, t in enumerate(range(n0, n0 + steps)):
-        got = a.generate_step(kk[:, :, t:t + 1], v[:, :, t:t + 1], qs[i]).clone()
+        got = a.generate_step(kk[:, :, t:t + 1], v[:, :, t:t + 1], qs[i], fused_append=False).clone()
         captures.add(id(a._gen_step["graph"]))
         b.append(kk[:, :, t:t + 1], v[:, :, t:t + 1])
         want = b.decode(qs[i])
@@ -135,6 +135,50 @@ def test_generate_step_graph_equals_append_then_decode():
     assert a.lengths == b.lengths == [n0 + steps] * 2 and a.seq_lens.tolist() == b.seq_lens.tolist()
     assert 2 <= len(captures) <= 6                                           # recaptured, but not every step
     paged.check_status(a.status)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_append_step_equals_the_separate_launches_bit_for_bit(dtype):
+    """jqk_decode_append_attend (one launch: append, attend, advance the lengths) against the
+    graph of compress + store + length + decode launches on ragged sequences that cross page and
+    split boundaries: the same output bits every step, the same codes and value rows in the pages,
+    the same lengths; and the codes are the oracle's codes of the appended keys."""
+    H = 2
+    keys, comps, tables = _tables(H)
+    g = torch.Generator().manual_seed(21)
+    n0, steps = [370, 29, 1], 70
+    total = max(n0) + steps
+    v = torch.randn(3, H, total, 128, generator=g).to(torch.bfloat16).cuda()
+    kk = torch.stack([keys[:, :total], keys.flip(1)[:, :total], keys[:, 100:100 + total]]).cuda()
+    qs = torch.randn(steps, 3, 8, 128, generator=g).to(torch.bfloat16).cuda()
+    caches = [paged.PagedKVCache(tables, [n + steps for n in n0]) for _ in range(2)]
+    for c in caches:
+        c.prefill(kk[:, :, :max(n0)], v[:, :, :max(n0)], lengths=n0)
+    new_k = torch.stack([torch.stack([kk[s, :, n0[s] + i] for s in range(3)]) for i in range(steps)]).to(dtype)   # (steps, 3, H, d)
+    new_v = torch.stack([torch.stack([v[s, :, n0[s] + i] for s in range(3)]) for i in range(steps)]).to(dtype)
+    for i in range(steps):
+        got = caches[0].generate_step(new_k[i].unsqueeze(2), new_v[i].unsqueeze(2), qs[i]).clone()
+        want = caches[1].generate_step(new_k[i].unsqueeze(2), new_v[i].unsqueeze(2), qs[i], fused_append=False).clone()
+        assert torch.equal(got, want), f"step {i}: {(got - want).abs().max().item()}"
+    a, b = caches
+    assert a._gen_step["fused"] and not b._gen_step["fused"]
+    assert a.lengths == b.lengths == [n + steps for n in n0]
+    assert a.seq_lens.tolist() == b.seq_lens.tolist() == a.lengths
+    for c in caches:
+        paged.check_status(c.status)
+    for s in range(3):
+        pk = [paged.PackedKeys(c.tables, c.k_pool, c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
+              for c in caches]
+        ca, cb = paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])
+        assert torch.equal(ca, cb)
+        assert torch.equal(_v_reference(a.v_pool, a.page_table, s, a.lengths, H, 128),
+                           _v_reference(b.v_pool, b.page_table, s, b.lengths, H, 128))
+        # the appended keys against the oracle's codes (fp32 transform, first-minimum ties)
+        rows = new_k[:, s].float().cpu().to(torch.bfloat16 if dtype == torch.bfloat16 else torch.float32).float()   # (steps, H, d)
+        for h in range(H):
+            want_codes = orc.nearest_codes(orc.transform(rows[:, h], comps[h].forward_map), comps[h].codebooks_padded)
+            got_codes = ca[0, h, n0[s]:, :].cpu()
+            assert (got_codes.long() != want_codes.long()).float().mean().item() <= 1e-4
 
 
 def test_overlong_length_is_clamped_flagged_and_leaves_the_workspace_clean():
