@@ -181,6 +181,50 @@ def test_fused_append_step_equals_the_separate_launches_bit_for_bit(dtype):
             assert (got_codes.long() != want_codes.long()).float().mean().item() <= 1e-4
 
 
+def test_fused_append_on_a_grid_of_several_waves():
+    """The append launch when the grid exceeds one wave of blocks (tables from the table kernel,
+    blocks that start after others have finished): ragged sequences, 180 blocks, three steps in a
+    row on one workspace.  Lengths advance once per launch, the appended rows land in the pages, the
+    outputs equal a plain decode over the grown cache."""
+    H, n_seqs, tps = 2, 3, 384
+    keys, comps, tables = _tables(H)
+    g = torch.Generator().manual_seed(31)
+    n0 = [384 * 30 - 2, 5000, 17]
+    total = max(n0) + 8
+    reps = -(-total // keys.shape[1])
+    kk = torch.stack([keys.repeat(1, reps, 1)[:, :total].roll(7 * s, 1) for s in range(n_seqs)]).cuda()
+    v = torch.randn(n_seqs, H, total, 128, generator=g).to(torch.bfloat16).cuda()
+    fused = paged.PagedKVCache(tables, [n + 8 for n in n0])
+    plain = paged.PagedKVCache(tables, [n + 8 for n in n0])
+    for c in (fused, plain):
+        c.prefill(kk[:, :, :max(n0)], v[:, :, :max(n0)], lengths=n0)
+    covered = 384 * 30 + 384
+    assert -(-covered // tps) * H * n_seqs > 148
+    ws = paged.DecodeWorkspace(n_seqs, 8, H, -(-covered // tps), "cuda")
+    out = torch.empty(n_seqs, 8, 128, device="cuda")
+    for i in range(3):
+        q = torch.randn(n_seqs, 8, 128, generator=g).to(torch.bfloat16).cuda()
+        k_new = torch.stack([kk[s, :, n0[s] + i] for s in range(n_seqs)])
+        v_new = torch.stack([v[s, :, n0[s] + i] for s in range(n_seqs)])
+        for s in range(n_seqs):
+            fused.reserve(s, n0[s] + i + 1)
+        got = paged.decode_append_attend(tables, q, k_new, v_new, fused.seq_lens, covered, fused.page_table, fused.k_pool,
+                                         fused.v_pool, out, ws, fused.status, tps).clone()
+        for s in range(n_seqs):
+            fused.lengths[s] += 1
+        assert fused.seq_lens.tolist() == fused.lengths
+        plain.append(k_new.unsqueeze(2), v_new.unsqueeze(2))
+        want = plain.decode(q, tokens_per_split=tps)
+        assert torch.equal(got, want), f"step {i}: {(got - want).abs().max().item()}"
+    paged.check_status(fused.status)
+    for s in range(n_seqs):
+        pk = [paged.PackedKeys(c.tables, c.k_pool, c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
+              for c in (fused, plain)]
+        assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1]))
+        assert torch.equal(_v_reference(fused.v_pool, fused.page_table, s, fused.lengths, H, 128),
+                           _v_reference(plain.v_pool, plain.page_table, s, plain.lengths, H, 128))
+
+
 def test_overlong_length_is_clamped_flagged_and_leaves_the_workspace_clean():
     """A seq_lens entry above the max_seq_len the call was sized for: the kernel cuts the context to
     what its grid covers, sets JQK_STATUS_BAD_LENGTH, still merges, and the next call on the same
