@@ -229,17 +229,22 @@ int32_t jqk_decode_attend(const jqk_head_tables* tables, const void* q, int32_t 
  *     cover that;
  *   - when the launch is done seq_lens[s] has been advanced by one for every sequence, so the call
  *     can be replayed from a CUDA graph without host work in between.
+ *   - flags: JQK_APPEND_OWN_KEY_EXACT scores the appended key from its exact values in this step
+ *     and from its codes in every later one, which is what the reference's Mode B does (its hook
+ *     compresses a decode key after the attention of the step that produced it); without the flag
+ *     the new key is scored from its codes like every other key.
  * bf16 value pool only (no packed values); tables without a centre.  Everything else as in
  * jqk_decode_attend.
  */
+#define JQK_APPEND_OWN_KEY_EXACT 1
 int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, const void* new_k,
                                  const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
                                  int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride,
                                  int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
                                  int32_t tokens_per_split, const int32_t* page_table,
                                  int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
-                                 void* out, int32_t out_dtype, void* workspace, size_t workspace_bytes,
-                                 int32_t* status, void* stream);
+                                 void* out, int32_t out_dtype, int32_t flags, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
  * jqk_decode_attend over packed values: the value pool holds codes of a second per-coordinate

@@ -158,6 +158,7 @@ template <> struct DecodeSmemT<false> {
   float ap_k[JQK_MAX_DIM];
   uint32_t ap_words[JQK_MAX_WORDS];
   __nv_bfloat16 ap_v[JQK_MAX_DIM];
+  float ap_dot[JQK_MAX_GROUP];   // q_h . k_new, exact
   int ap_page, ap_last;
 };
 template <> struct DecodeSmemT<true> {
@@ -292,6 +293,7 @@ struct AppendSide {
   __nv_bfloat16* v_pool;
   int32_t* seq_lens;        // the lengths again, writable
   int n_seqs;
+  int own_key_exact;        // score the appended key from its exact values in this step (its codes serve later steps)
 };
 
 __device__ __forceinline__ float load_elem_f32(const void* p, int dtype, size_t i) {
@@ -329,7 +331,7 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
                                         const void* v_row, int k_dtype, int v_dtype, uint32_t* k_pool, __nv_bfloat16* v_pool,
                                         int head, int seq, bool write, int pos,
                                         const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
-                                        int32_t* status) {
+                                        int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group) {
   const int tid = threadIdx.x;
   if (tid < D) {
     sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
@@ -353,6 +355,14 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
     for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
     const int bp = (m >> 4) & 1023;
     atomicOr(&sm.ap_words[bp >> 5], code << (bp & 31));
+  } else if (q_rows && tid >= 256) {   // the exact scores of the new key: one warp per query head of the group
+    const int h = (tid - 256) >> 5, lane = tid & 31;
+    if (h < n_group) {
+      float dot = 0.f;
+      for (int i = lane; i < D; i += 32) dot = fmaf(__bfloat162float(q_rows[(size_t)h * D + i]), sm.ap_k[i], dot);
+      dot = warp_sum(dot);
+      if (lane == 0) sm.ap_dot[h] = dot;
+    }
   }
   __syncthreads();
   const int page = sm.ap_page;
@@ -526,7 +536,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       append_row<D>(sm, tb.fwd_cols, tb.col_meta, tb.thresholds, tb.n_heads, tb.words_per_record, hd.n_active, hd.n_words,
                     (const char*)ap.k + ((size_t)seq * ap.k_seq_stride + (size_t)head * ap.k_head_stride) * k_esz,
                     (const char*)ap.v + ((size_t)seq * ap.v_seq_stride + (size_t)head * ap.v_head_stride) * v_esz,
-                    ap.k_dtype, ap.v_dtype, ap.k_pool, ap.v_pool, head, seq, qb == 0, ap_pos, page_table, pt_stride, n_pages, status);
+                    ap.k_dtype, ap.v_dtype, ap.k_pool, ap.v_pool, head, seq, qb == 0, ap_pos, page_table, pt_stride, n_pages, status,
+                    ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group);
     }
   }
 
@@ -614,6 +625,16 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if (!lane_ok) {
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) ia[h] = INT_MIN;
+    }
+    if constexpr (!VQ) {
+      // the appended key attends with its exact values in the step that appends it (the reference
+      // compresses a decode key after the step that produced it, jointqk_press.py:298-304)
+      if (ap.own_key_exact && tok == ap_pos && lane_ok) {
+        const float f = kLog2e / sqrtf((float)D);
+#pragma unroll
+        for (int h = 0; h < JQK_MAX_GROUP; ++h)
+          if (sc[h] > 0.f) ia[h] = __float2int_rn(fminf(fmaxf(sm.ap_dot[h] * f / sc[h], -2147483520.f), 2147483520.f));
+      }
     }
 
     // ---- online softmax: the tile maximum is an integer reduction (scores are scale * integer);
@@ -1115,17 +1136,19 @@ extern "C" int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const
                                             int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
                                             int32_t tokens_per_split, const int32_t* page_table,
                                             int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
-                                            void* out, int32_t out_dtype, void* workspace, size_t workspace_bytes,
-                                            int32_t* status, void* stream) {
+                                            void* out, int32_t out_dtype, int32_t flags, void* workspace,
+                                            size_t workspace_bytes, int32_t* status, void* stream) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
   if (!new_k || !new_v) return fail(JQK_E_ARG, "null new_k or new_v");
+  if (flags & ~JQK_APPEND_OWN_KEY_EXACT) return fail(JQK_E_ARG, "unknown flags 0x%x", flags);
   for (int32_t dt : {k_dtype, v_dtype})
     if (dt != JQK_DTYPE_F32 && dt != JQK_DTYPE_BF16 && dt != JQK_DTYPE_F16) return fail(JQK_E_ARG, "unknown dtype %d", dt);
   if (tables->center) return fail(JQK_E_UNSUPPORTED, "centred tables are for values; keys are appended uncentred");
   if (max_seq_len <= 0) return fail(JQK_E_ARG, "max_seq_len must cover the context after the append");
   AppendSide ap{new_k, new_v, k_dtype, v_dtype, (long long)k_seq_stride, (long long)k_head_stride, (long long)v_seq_stride,
-                (long long)v_head_stride, k_pool, (__nv_bfloat16*)v_pool, seq_lens, n_seqs};
+                (long long)v_head_stride, k_pool, (__nv_bfloat16*)v_pool, seq_lens, n_seqs,
+                (flags & JQK_APPEND_OWN_KEY_EXACT) ? 1 : 0};
   return decode_launch(tables, nullptr, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
                        page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, workspace, workspace_bytes, status,
                        stream, &ap);

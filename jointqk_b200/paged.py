@@ -260,11 +260,12 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
 def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                          seq_lens: torch.Tensor, max_seq_len: int, page_table: torch.Tensor, k_pool: torch.Tensor,
                          v_pool: torch.Tensor, out: torch.Tensor, workspace: DecodeWorkspace, status: torch.Tensor,
-                         tokens_per_split: int = 0) -> torch.Tensor:
+                         tokens_per_split: int = 0, own_key_exact: bool = False) -> torch.Tensor:
     """One generate step in one launch: the rows k_new / v_new (n_seqs, H, 1, d) or (n_seqs, H, d) go
     to position ``seq_lens[s]`` of every sequence (pages already in the table), the step attends
     over ``seq_lens[s] + 1`` keys (``max_seq_len`` covers that) and ``seq_lens`` is advanced on the
-    device.  bf16 value pool only."""
+    device.  bf16 value pool only.  ``own_key_exact``: the new key is scored from its exact values in
+    this step (and from its codes afterwards), the semantics of the reference's Mode B."""
     if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
     if v_pool.dtype != torch.bfloat16:
@@ -290,7 +291,8 @@ def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tenso
         _native.torch_dtype_code(v_new.dtype), k_new.stride(0), k_new.stride(1), v_new.stride(0), v_new.stride(1), n, q.shape[1], seq_lens.data_ptr(),
         int(max_seq_len), int(tokens_per_split), page_table.data_ptr(), page_table.stride(0), int(k_pool.shape[0]),
         k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), _native.torch_dtype_code(out.dtype),
-        workspace.buf.data_ptr(), workspace.buf.numel(), status.data_ptr(), _stream_ptr(tables.device)))
+        1 if own_key_exact else 0, workspace.buf.data_ptr(), workspace.buf.numel(), status.data_ptr(),
+        _stream_ptr(tables.device)))
     return out
 
 
@@ -461,12 +463,13 @@ class PagedKVCache:
     RESERVE_AHEAD = 64   # tokens of page capacity the fused generate step keeps ahead of the context
 
     def generate_step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor,
-                      fused_append: bool = True) -> torch.Tensor:
+                      fused_append: bool = True, own_key_exact: bool = False) -> torch.Tensor:
         """One step of a generate loop: append the newest token of every sequence (K compress, V store,
         lengths advanced on the device), then attend.  With a bf16 value pool that is one kernel
         launch, which reads the rows in place (``jqk_decode_append_attend``).  ``fused_append=False``,
         and always with packed values: the separate compress, store, length and decode launches,
-        replayed as one CUDA graph.
+        replayed as one CUDA graph.  ``own_key_exact`` (fused launch only): the new key attends with
+        its exact values in this step, as in the reference's Mode B.
 
         k_new / v_new (n_seqs, H, 1, d), q bf16 (n_seqs, Hq, d); the result is a device tensor that
         the next call overwrites.  Pages are reserved on the host before the launch, which only
@@ -486,7 +489,7 @@ class PagedKVCache:
                 and gs["shape"] == (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) and q.is_contiguous()):
             self._gen_budget -= 1
             decode_append_attend(self.tables, q, k_new, v_new, self.seq_lens, gs["covered"], self.page_table, self.k_pool,
-                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"])
+                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"], own_key_exact)
             for s_ in range(n):
                 self.lengths[s_] += 1
             gs["lengths_after"] = list(self.lengths)
@@ -498,6 +501,8 @@ class PagedKVCache:
         gs = getattr(self, "_gen_step", None)
         new_max = max(self.lengths) + 1
         fused = self.v_tables is None and bool(fused_append)
+        if own_key_exact and not fused:
+            raise ValueError("own_key_exact needs the fused append launch (bf16 values, fused_append=True)")
         if (gs is None or gs["generation"] != self.pool.generation or gs["table_ptr"] != self.page_table.data_ptr()
                 or gs["shape"] != (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) or new_max > gs["covered"]
                 or gs["fused"] != fused):
@@ -540,7 +545,7 @@ class PagedKVCache:
             # attends and advances the lengths; there is nothing to stage and nothing to capture
             decode_append_attend(self.tables, q if q.is_contiguous() else q.contiguous(), k_new, v_new, self.seq_lens,
                                  gs["covered"], self.page_table, self.k_pool, self.v_pool, gs["out"], gs["ws"],
-                                 self.status, gs["tps"])
+                                 self.status, gs["tps"], own_key_exact)
         else:
             gs["k"].copy_(k_new, non_blocking=True)
             gs["v"].copy_(v_new, non_blocking=True)

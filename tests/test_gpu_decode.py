@@ -172,6 +172,37 @@ def test_decode_from_host_buffers_equals_device_call():
     paged.check_status(cache.status)
 
 
+def test_appended_key_attends_exactly_in_its_own_step():
+    """Mode B of the reference compresses a decode key after the step that produced it
+    (jointqk_press.py:298-304): in that step attention sees the exact key, later steps see its
+    reconstruction.  jqk_decode_append_attend with JQK_APPEND_OWN_KEY_EXACT against the oracle's
+    attention over [reconstructed history, exact new key]; the retrieval-style query makes the new
+    key carry most of the weight, so the choice is visible in the output."""
+    H, n0, steps = 2, 700, 5
+    keys, comps, sig, tables = _setup(H, 2048, 2.0, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(17)
+    v = torch.randn(1, H, n0 + steps, 128, generator=g).to(torch.bfloat16)
+    cache = paged.PagedKVCache(tables, [n0 + steps])
+    cache.prefill(keys[:, :n0].unsqueeze(0).cuda(), v[:, :, :n0].cuda())
+    for i in range(steps):
+        k_new = keys[:, n0 + i].unsqueeze(0)                                     # (1, H, d) bf16
+        v_new = v[:, :, n0 + i]
+        q = (k_new.float().repeat_interleave(4, 1) * 0.6 + 0.3 * torch.randn(1, 8, 128, generator=g)).to(torch.bfloat16)
+        got = cache.generate_step(k_new.unsqueeze(2).cuda(), v_new.unsqueeze(2).cuda(), q.cuda(), own_key_exact=True).cpu()
+        packed = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(cache.lengths), cache.status)
+        k_hat = _k_hat_from_packed(packed, comps)                               # (1, H, n0+i+1, d), the new key compressed
+        k_own = k_hat.clone()
+        k_own[:, :, -1] = k_new.float()
+        ref_own = orc.decode_attention(q, k_own, v[:, :, :n0 + i + 1])
+        ref_codes = orc.decode_attention(q, k_hat, v[:, :, :n0 + i + 1])
+        scale = ref_own.abs().amax(-1, keepdim=True).clamp_min(1e-6)
+        err = ((got - ref_own).abs() / scale).max().item()
+        gap = ((ref_codes - ref_own).abs() / scale).max().item()
+        assert err < OUT_TOL, (i, err)
+        assert gap > 2 * OUT_TOL and gap > 4 * err, (gap, err)                    # the two semantics differ measurably here
+    paged.check_status(cache.status)
+
+
 def test_decode_split_invariance_at_context_32768():
     """Full-context property: the result does not depend on how the keys are split over blocks."""
     H, N = 8, 32768
