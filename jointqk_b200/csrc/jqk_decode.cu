@@ -380,7 +380,7 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
 
 // D = head_dim (64 or 128).  VQ: values are packed codes of a second compressor (v_pool is then the
 // uint32 code pool, `vs` its tables); the keys' tables then always come from the table kernel.
-template <int D, bool BUILD_IN_BLOCK, bool VQ>
+template <int D, bool BUILD_IN_BLOCK, bool VQ, bool APPEND>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
@@ -388,6 +388,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
               const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs, AppendSide ap) {
   static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
+  static_assert(!(VQ && APPEND), "the append variant writes a bf16 value pool");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -407,15 +408,12 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // the workspace) is cut to what the grid covers and flagged; otherwise the ticket below would
   // never see its last block.
   int len = seq_lens[seq];
-  bool appending = false;
-  if constexpr (!VQ) appending = ap.k != nullptr;
-  if (appending) len += 1;  // this launch attends over the key it appends
+  if constexpr (APPEND) len += 1;  // this launch attends over the key it appends
   // Append variant: every block of the launch passes here exactly once on its way out, all of its
   // threads together.  Each has read its length by then, so the block that takes the last ticket
   // may advance the lengths for the next launch.
   auto leave = [&]() {
-    if constexpr (!VQ) {
-      if (!appending) return;
+    if constexpr (APPEND) {
       __syncthreads();
       if (tid == 0) {
         unsigned int prev;
@@ -529,8 +527,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // the block whose split ends the context takes the appended row (every query block keeps its own
   // copy in shared memory; the first one also writes it to the tail page)
   int ap_pos = -1;
-  if constexpr (!VQ) {
-    if (appending && split == n_splits - 1) {
+  if constexpr (APPEND) {
+    if (split == n_splits - 1) {
       ap_pos = len - 1;
       const size_t k_esz = ap.k_dtype == JQK_DTYPE_F32 ? 4 : 2, v_esz = ap.v_dtype == JQK_DTYPE_F32 ? 4 : 2;
       append_row<D>(sm, tb.fwd_cols, tb.col_meta, tb.thresholds, tb.n_heads, tb.words_per_record, hd.n_active, hd.n_words,
@@ -605,7 +603,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     const int page_hi = __shfl_sync(0xffffffffu, pg_cur, ((r & 15) << 1) | 1);
     bool landed = bar_wait(&sm.kfull[warp][r & 1], (r >> 1) & 1);
 
-    if constexpr (!VQ) {
+    if constexpr (APPEND) {
       if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {  // the page copy may predate the append: take the record from the block's own copy
         const int slot = ap_pos - t0;
         uint32_t* kd = reinterpret_cast<uint32_t*>(st.k[r & 1][slot >> 4]) + (slot & 15);
@@ -626,7 +624,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) ia[h] = INT_MIN;
     }
-    if constexpr (!VQ) {
+    if constexpr (APPEND) {
       // the appended key attends with its exact values in the step that appends it (the reference
       // compresses a decode key after the step that produced it, jointqk_press.py:298-304)
       if (ap.own_key_exact && tok == ap_pos && lane_ok) {
@@ -665,7 +663,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
-    if constexpr (!VQ) {
+    if constexpr (APPEND) {
       if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {
         const int ts = (ap_pos - t0) & 15;
         unsigned char* vt = reinterpret_cast<unsigned char*>(st.v[(ap_pos - t0) >> 4]);
@@ -1084,21 +1082,27 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   if (v_tables)
     vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
                    v_tables->n_heads, v_tables->words_per_record};
-#define JQK_LAUNCH_DECODE(DIM, INB, VQQ)                                                                              \
+#define JQK_LAUNCH_DECODE(DIM, INB, VQQ, APP)                                                                         \
   do {                                                                                                                \
     cfg.dynamicSmemBytes = sizeof(DecodeSmemT<VQQ>);                                                                  \
-    JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");                 \
-    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ>, *tables, (const __nv_bfloat16*)q, n_q_heads,   \
-                                   seq_lens, tokens_per_split, page_table, page_table_stride, n_pages, k_pool,        \
-                                   v_pool, out, out_dtype, ws, status, vs, ap),                                       \
+    JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ, APP>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");            \
+    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ, APP>, *tables, (const __nv_bfloat16*)q,         \
+                                   n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride, n_pages,     \
+                                   k_pool, v_pool, out, out_dtype, ws, status, vs, ap),                               \
                 "decode launch");                                                                                     \
   } while (0)
   if (v_tables) {
-    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true); else JQK_LAUNCH_DECODE(64, false, true);
+    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false); else JQK_LAUNCH_DECODE(64, false, true, false);
+  } else if (append) {
+    if (tables->d == 128) {
+      if (in_block) JQK_LAUNCH_DECODE(128, true, false, true); else JQK_LAUNCH_DECODE(128, false, false, true);
+    } else {
+      if (in_block) JQK_LAUNCH_DECODE(64, true, false, true); else JQK_LAUNCH_DECODE(64, false, false, true);
+    }
   } else if (tables->d == 128) {
-    if (in_block) JQK_LAUNCH_DECODE(128, true, false); else JQK_LAUNCH_DECODE(128, false, false);
+    if (in_block) JQK_LAUNCH_DECODE(128, true, false, false); else JQK_LAUNCH_DECODE(128, false, false, false);
   } else {
-    if (in_block) JQK_LAUNCH_DECODE(64, true, false); else JQK_LAUNCH_DECODE(64, false, false);
+    if (in_block) JQK_LAUNCH_DECODE(64, true, false, false); else JQK_LAUNCH_DECODE(64, false, false, false);
   }
 #undef JQK_LAUNCH_DECODE
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");
