@@ -21,7 +21,9 @@ tensors.  Here a model keeps its keys packed for the whole generation:
   (layer 0 at full precision by default, as ``layer0_full_precision`` in the reference's runs).
 
 Limits, checked and raised: one prefill per sequence batch (no chunked prefill: earlier exact keys
-are not kept), no beam reordering, no cropping.
+are not kept), no beam reordering, no cropping.  Not checked: a decode step attends over every
+cached position of its sequence, so the sequences of a batch must be unpadded (prompts of equal
+length, or one sequence at a time); a padding mask is honoured by the stock prefill path only.
 """
 
 from __future__ import annotations
