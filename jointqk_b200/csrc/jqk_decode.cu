@@ -119,6 +119,7 @@ struct DecodeWs {
   unsigned int* counters;  // [n_seqs][n_kv_heads * q_blocks]
   int max_splits;
   unsigned int* grid_ticket;  // one counter for the whole launch (append variant: who advances the lengths)
+  int late_wait;              // the kernel right before this one on the stream is this call's table kernel
 };
 
 // Per-warp staging of one tile: the two V pages (dims-major, see the V page layout in the file
@@ -256,6 +257,8 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   const int q_blocks = (group + JQK_MAX_GROUP - 1) / JQK_MAX_GROUP;
   const int head = blockIdx.x / q_blocks, qb = blockIdx.x % q_blocks, seq = blockIdx.y;
   const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
+  // the decode launch that follows may start (its blocks wait for these records where they need them)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const HeadDesc hd = load_desc(tb.desc, head);
   {
     const TableLoads ld = issue_table_loads(tb, head, hd.d, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d,
@@ -402,7 +405,13 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const int seq = blockIdx.z, split = blockIdx.x;
   // Launched as a programmatic dependent: everything up to here overlaps the tail of the previous
   // kernel on the stream; nothing in memory is read or written before that kernel has completed.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // One exception: when the previous kernel is this call's own table kernel (ws.late_wait), it
+  // writes nothing but the table records, and everything older on the stream was complete before it
+  // started; the block then waits only where it needs the records, and its lengths, page ids and
+  // first page copies run beside the table build.
+  bool waited = true;
+  if constexpr (!BUILD_IN_BLOCK) waited = !ws.late_wait;
+  if (waited) asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // A context longer than the call was sized for (max_seq_len on the host side fixed the grid and
   // the workspace) is cut to what the grid covers and flagged; otherwise the ticket below would
@@ -558,6 +567,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       for (int e = lane; e < (int)(sizeof(st.v) / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
     }
     // the finished tables of this (sequence, head group) come from the table kernel
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (tid == 0) {
       const TableRecord* rec = ws.tables + (size_t)seq * gridDim.y + blockIdx.y;
       const uint32_t lut_bytes = (uint32_t)hd.n_tables * 128u;
@@ -1040,7 +1050,7 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   const int max_splits = max_seq_len > 0 ? (max_seq_len + tokens_per_split - 1) / tokens_per_split : 1;
   if (max_splits > MAX_SPLITS) return fail(JQK_E_UNSUPPORTED, "%d key splits exceed %d: use a larger tokens_per_split", max_splits, MAX_SPLITS);
   const int qbl = q_blocks_for(n_q_heads, tables->n_heads);
-  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits, nullptr};
+  DecodeWs ws{nullptr, nullptr, nullptr, nullptr, nullptr, max_splits, nullptr, 0};
   {
     const size_t need = jqk_decode_workspace_bytes(n_seqs, n_q_heads, tables->n_heads, max_splits);
     if (!workspace || workspace_bytes < need) return fail(JQK_E_WORKSPACE, "decode workspace needs %zu bytes, got %zu", need, workspace_bytes);
@@ -1064,6 +1074,7 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
     decode_tables_kernel<<<dim3(tables->n_heads * qbl, n_seqs), TBL_BUILD_THREADS, sizeof(TableSmem), st>>>(
         *tables, (const __nv_bfloat16*)q, n_q_heads, ws.tables);
     JQK_CUDA_OK(cudaGetLastError(), "decode tables launch");
+    ws.late_wait = 1;
   }
   // Programmatic dependent launch: the blocks may become resident while the previous kernel on the
   // stream drains; they wait for it to complete (griddepcontrol.wait) before they touch memory.
