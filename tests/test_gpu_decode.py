@@ -172,7 +172,8 @@ def test_decode_from_host_buffers_equals_device_call():
     paged.check_status(cache.status)
 
 
-def test_appended_key_attends_exactly_in_its_own_step():
+@pytest.mark.parametrize("hq", [8, 16])
+def test_appended_key_attends_exactly_in_its_own_step(hq):
     """Mode B of the reference compresses a decode key after the step that produced it
     (jointqk_press.py:298-304): in that step attention sees the exact key, later steps see its
     reconstruction.  jqk_decode_append_attend with JQK_APPEND_OWN_KEY_EXACT against the oracle's
@@ -187,7 +188,7 @@ def test_appended_key_attends_exactly_in_its_own_step():
     for i in range(steps):
         k_new = keys[:, n0 + i].unsqueeze(0)                                     # (1, H, d) bf16
         v_new = v[:, :, n0 + i]
-        q = (k_new.float().repeat_interleave(4, 1) * 0.6 + 0.3 * torch.randn(1, 8, 128, generator=g)).to(torch.bfloat16)
+        q = (k_new.float().repeat_interleave(hq // H, 1) * 0.6 + 0.3 * torch.randn(1, hq, 128, generator=g)).to(torch.bfloat16)
         got = cache.generate_step(k_new.unsqueeze(2).cuda(), v_new.unsqueeze(2).cuda(), q.cuda(), own_key_exact=True).cpu()
         packed = paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(cache.lengths), cache.status)
         k_hat = _k_hat_from_packed(packed, comps)                               # (1, H, n0+i+1, d), the new key compressed

@@ -137,12 +137,13 @@ def test_generate_step_graph_equals_append_then_decode():
     paged.check_status(a.status)
 
 
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_fused_append_step_equals_the_separate_launches_bit_for_bit(dtype):
+@pytest.mark.parametrize("dtype,hq", [(torch.bfloat16, 8), (torch.float32, 8), (torch.bfloat16, 16)])
+def test_fused_append_step_equals_the_separate_launches_bit_for_bit(dtype, hq):
     """jqk_decode_append_attend (one launch: append, attend, advance the lengths) against the
     graph of compress + store + length + decode launches on ragged sequences that cross page and
     split boundaries: the same output bits every step, the same codes and value rows in the pages,
-    the same lengths; and the codes are the oracle's codes of the appended keys."""
+    the same lengths; and the codes are the oracle's codes of the appended keys.  16 query heads over
+    2 kv heads make two query blocks per head: both keep a copy of the new row, one writes it."""
     H = 2
     keys, comps, tables = _tables(H)
     g = torch.Generator().manual_seed(21)
@@ -150,7 +151,7 @@ def test_fused_append_step_equals_the_separate_launches_bit_for_bit(dtype):
     total = max(n0) + steps
     v = torch.randn(3, H, total, 128, generator=g).to(torch.bfloat16).cuda()
     kk = torch.stack([keys[:, :total], keys.flip(1)[:, :total], keys[:, 100:100 + total]]).cuda()
-    qs = torch.randn(steps, 3, 8, 128, generator=g).to(torch.bfloat16).cuda()
+    qs = torch.randn(steps, 3, hq, 128, generator=g).to(torch.bfloat16).cuda()
     caches = [paged.PagedKVCache(tables, [n + steps for n in n0]) for _ in range(2)]
     for c in caches:
         c.prefill(kk[:, :, :max(n0)], v[:, :, :max(n0)], lengths=n0)
