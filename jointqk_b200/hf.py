@@ -34,6 +34,7 @@ from .compressor import PerCoordCompressor
 from .moments import KeyPathMoments
 from .paged import PagedKVCache
 from .tables import HeadTables
+from .v_compressor import build_v_compressor
 
 ATTN_NAME = "jointqk_paged"
 # The reference's Mode-B hook compresses a decode key after the attention of the step that produced
@@ -59,13 +60,14 @@ def _layer_base():
 class _Capture:
     """Moment accumulation during ``calibrate``: the attention function feeds it q and k of a layer."""
 
-    def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, d: int, device) -> None:
-        self.moments = KeyPathMoments(n_layers, n_q_heads, n_kv_heads, d, device=device)
+    def __init__(self, n_layers: int, n_q_heads: int, n_kv_heads: int, d: int, device, with_values: bool) -> None:
+        self.moments = KeyPathMoments(n_layers, n_q_heads, n_kv_heads, d, device=device, with_values=with_values)
 
-    def add(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor) -> None:
+    def add(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
         # (B, H, S, d): one (H, S, d) chunk per sequence, the layout of the moment kernel
+        bf = lambda t: t.to(torch.bfloat16).contiguous()
         for b in range(q.shape[0]):
-            self.moments.update(layer_idx, q[b].to(torch.bfloat16).contiguous(), k[b].to(torch.bfloat16).contiguous())
+            self.moments.update(layer_idx, bf(q[b]), bf(k[b]), bf(v[b]) if self.moments.with_values else None)
 
 
 _STATE = {"capture": None, "registered": False}
@@ -86,7 +88,7 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
     _, _, _, sdpa_attention = _transformers()
     cap = _STATE["capture"]
     if cap is not None:
-        cap.add(module.layer_idx, query, key[..., -query.shape[2]:, :])
+        cap.add(module.layer_idx, query, key[..., -query.shape[2]:, :], value[..., -query.shape[2]:, :])
     layer = getattr(module, "_jqk_layer", None)
     pending = layer.take_pending() if layer is not None else None
     if pending is None:
@@ -97,7 +99,8 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
         raise NotImplementedError("the packed decode scores with 1/sqrt(head_dim)")
     k_new, v_new = pending
     q = query[:, :, 0].to(torch.bfloat16).contiguous()
-    out = layer.paged.generate_step(k_new, v_new, q, own_key_exact=OWN_KEY_EXACT)   # (B, Hq, d) fp32, one launch
+    # (B, Hq, d) fp32; one launch with bf16 values, the separate launches with packed values
+    out = layer.paged.generate_step(k_new, v_new, q, own_key_exact=OWN_KEY_EXACT and layer.v_tables is None)
     return out.to(query.dtype).unsqueeze(1), None
 
 
@@ -109,16 +112,16 @@ def make_paged_layer_class():
         is_sliding = False
         is_compileable = False
 
-        def __init__(self, tables: HeadTables) -> None:
+        def __init__(self, tables: HeadTables, v_tables: HeadTables | None = None) -> None:
             super().__init__()
-            self.tables = tables
+            self.tables, self.v_tables = tables, v_tables
             self.paged: PagedKVCache | None = None
             self.cumulative_length = 0
             self._pending = None
 
         def lazy_initialization(self, key_states: torch.Tensor, value_states: torch.Tensor) -> None:
             self.dtype, self.device = key_states.dtype, key_states.device
-            self.paged = PagedKVCache(self.tables, n_seqs=key_states.shape[0])
+            self.paged = PagedKVCache(self.tables, n_seqs=key_states.shape[0], v_tables=self.v_tables)
             self.is_initialized = True
 
         def update(self, key_states: torch.Tensor, value_states: torch.Tensor, *args, **kwargs):
@@ -175,13 +178,15 @@ def set_attention(model) -> None:
 
 
 @torch.no_grad()
-def calibrate(model, prompts: list[torch.Tensor]) -> KeyPathMoments:
-    """Second moments of the post-RoPE queries and keys of every layer over ``prompts`` (each a
-    (B, S) tensor of token ids on the model's device), through the model's own forward."""
+def calibrate(model, prompts: list[torch.Tensor], with_values: bool = False) -> KeyPathMoments:
+    """Second moments of the post-RoPE queries and keys of every layer (and, ``with_values``, first
+    and second moments of the values) over ``prompts`` (each a (B, S) tensor of token ids on the
+    model's device), through the model's own forward."""
     cfg = model.config
     d = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
     set_attention(model)
-    cap = _Capture(cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads, d, next(model.parameters()).device)
+    cap = _Capture(cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads, d, next(model.parameters()).device,
+                   with_values)
     _STATE["capture"] = cap
     try:
         for ids in prompts:
@@ -191,16 +196,21 @@ def calibrate(model, prompts: list[torch.Tensor]) -> KeyPathMoments:
     return cap.moments
 
 
-def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_precision: bool = True, eps: float = 1e-4):
+def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_precision: bool = True, eps: float = 1e-4,
+                v_bits: int | None = None):
     """Fit one compressor per (layer, kv head) from the calibration moments (symmetrised Σ_Q Σ_K
     basis, water-fill at ``k_bits`` average, at most 4 bits per coordinate), attach a packed cache
-    layer to every attention module and return the ``Cache`` to pass as ``past_key_values``."""
+    layer to every attention module and return the ``Cache`` to pass as ``past_key_values``.
+    ``v_bits``: values are packed as well (eigenbasis of Cov[V], water-fill, mean-centred: the
+    reference's ``v_eigen_waterfill``); the moments must then have been taken ``with_values``.  A
+    decode step then takes the separate append and attend launches, and the new token's key and
+    value are compressed before it attends (the reference compresses them after)."""
     cache_utils, _, _, _ = _transformers()
     set_attention(model)
     layer_cls = make_paged_layer_class()
     stats = moments.finalize()
     device = next(model.parameters()).device
-    layers, comps_by_layer = [], {}
+    layers, comps_by_layer, v_comps_by_layer = [], {}, {}
     mods = attention_modules(model)
     for m in mods:
         L = m.layer_idx
@@ -211,9 +221,21 @@ def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_preci
         comps = [PerCoordCompressor.fit(stats["sigma_q"][L, h].cpu(), stats["sigma_k"][L, h].cpu(), float(k_bits),
                                         max_bits=4, basis="r_sym", eps=eps) for h in range(stats["sigma_k"].shape[1])]
         comps_by_layer[L] = comps
-        layer = layer_cls(HeadTables.from_compressors(comps, device=device))
+        v_tables = None
+        if v_bits is not None:
+            if "cov_v" not in stats:
+                raise ValueError("v_bits needs moments taken with_values=True")
+            d = stats["cov_v"].shape[-1]
+            v_comps = [build_v_compressor("v_eigen_waterfill", cov_v_for_head=stats["cov_v"][L, h].cpu(), head_dim=d,
+                                          bits=int(v_bits), seed=42, mu_v_for_head=stats["mu_v"][L, h].cpu(), max_bits=4)
+                       for h in range(stats["cov_v"].shape[1])]
+            v_comps_by_layer[L] = v_comps
+            v_tables = HeadTables.from_compressors([c.inner for c in v_comps], device=device,
+                                                   center=torch.stack([c.mu for c in v_comps]))
+        layer = layer_cls(HeadTables.from_compressors(comps, device=device), v_tables)
         layers.append(layer)
         m._jqk_layer = layer
     cache = cache_utils.Cache(layers=layers)
     cache.jqk_compressors = comps_by_layer
+    cache.jqk_v_compressors = v_comps_by_layer
     return cache

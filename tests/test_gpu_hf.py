@@ -91,3 +91,65 @@ def test_llama_decodes_over_the_packed_cache_like_the_reference_flow():
     assert torch.allclose(got[0], want[0], atol=1e-5 * scale)        # prefill sees exact keys in both
     assert err < 2e-2                                               # bf16 logits resolve 4e-3; 16-bit tables, bf16 weights in P.V
     assert effect > 2 * err
+
+
+@torch.no_grad()
+def test_llama_decodes_with_keys_and_values_packed():
+    """K at 2 bits and V at 3 bits, the reference's usual pairing: values calibrated through the
+    model's forward (first and second moments), packed by the centred eigenbasis compressor, and the
+    decode step attends over both code pools.  Checked against the same model over a dense cache
+    whose keys and values are the oracle's reconstructions, the new token's included (with packed
+    values the step compresses the new row before it attends)."""
+    from transformers import cache_utils
+    from transformers.cache_utils import DynamicLayer
+
+    from jointqk_b200 import hf, paged
+
+    model = _model()
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 512, (2, 256), generator=g).cuda() for _ in range(4)]
+    moments = hf.calibrate(model, prompts, with_values=True)
+    cache = hf.build_cache(model, moments, k_bits=2.0, v_bits=3)
+    ids = torch.randint(0, 512, (2, 40), generator=g).cuda()
+    forced = torch.randint(0, 512, (2, 6), generator=g).cuda()
+
+    def run(past):
+        out = [model(input_ids=ids, past_key_values=past, use_cache=True).logits[:, -1].float()]
+        for t in range(forced.shape[1]):
+            out.append(model(input_ids=forced[:, t:t + 1], past_key_values=past, use_cache=True).logits[:, -1].float())
+        return torch.stack(out)
+
+    got = run(cache)
+    for L in (1, 2):
+        assert cache.layers[L].paged.v_tables is not None and cache.layers[L].paged.lengths == [46, 46]
+        paged.check_status(cache.layers[L].paged.status)
+
+    def oracle_layer(kc, vc):
+        class OracleLayer(DynamicLayer):
+            def update(self, key_states, value_states, *args, **kwargs):
+                if not self.is_initialized:
+                    self.lazy_initialization(key_states, value_states)
+                rk = torch.stack([torch.stack([orc.roundtrip(key_states[b, h].float().cpu(), kc[h].codebooks_padded, kc[h].forward_map,
+                                                             kc[h].inverse_map)[0] for h in range(key_states.shape[1])])
+                                  for b in range(key_states.shape[0])]).to(key_states)
+                rv = torch.stack([torch.stack([orc.centred_roundtrip(value_states[b, h].float().cpu(), vc[h].mu, vc[h].inner.codebooks_padded,
+                                                                     vc[h].inner.forward_map, vc[h].inner.inverse_map)[0]
+                                               for h in range(value_states.shape[1])])
+                                  for b in range(value_states.shape[0])]).to(value_states)
+                first = self.keys.numel() == 0
+                self.keys = torch.cat([self.keys, rk], dim=-2)
+                self.values = torch.cat([self.values, rv], dim=-2)
+                # prefill attends over the exact rows (the pages are filled behind it), a step over the stored ones
+                return (key_states, value_states) if first else (self.keys, self.values)
+        return OracleLayer()
+
+    for m in hf.attention_modules(model):
+        m._jqk_layer = None
+    want = run(cache_utils.Cache(layers=[DynamicLayer()] + [oracle_layer(cache.jqk_compressors[L], cache.jqk_v_compressors[L])
+                                                             for L in (1, 2)]))
+    plain = run(cache_utils.DynamicCache())
+    scale = want.abs().max().item()
+    err = (got - want).abs().max().item() / scale
+    effect = (plain - want).abs().max().item() / scale
+    print(f"logits, K 2 bits + V 3 bits: packed vs reference flow {err:.3e}, compression effect {effect:.3e}")
+    assert err < 2e-2 and effect > 2 * err

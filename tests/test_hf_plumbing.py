@@ -12,7 +12,7 @@ transformers = pytest.importorskip("transformers")
 class DensePaged:
     """What the cache layer needs of PagedKVCache, kept dense and exact."""
 
-    def __init__(self, tables, n_seqs):
+    def __init__(self, tables, n_seqs, v_tables=None):
         self.k = self.v = None
         self.steps = 0
 
