@@ -7,6 +7,7 @@ dequantised floats in the HF cache, experiments/stage1/toolkit/jointqk_press.py:
 
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 
 import torch
@@ -382,6 +383,7 @@ class PagedKVCache:
         self._ws: DecodeWorkspace | None = None
         self._host_step: dict | None = None
         self._host_call: dict | None = None
+        self._epoch = 0      # bumped whenever lengths or pages change: cached host-step state compares one integer
 
     # the pools belong to the PagePool (they move when it grows)
     @property
@@ -406,6 +408,7 @@ class PagedKVCache:
         if need <= 0:
             return
         self._gen_budget = 0
+        self._epoch += 1
         have = len(self._pages[seq])
         new = self.pool.take(need)
         self._pages[seq].extend(new)
@@ -420,6 +423,7 @@ class PagedKVCache:
     def release(self, seq: int) -> None:
         """Forget sequence ``seq`` and return its pages to the pool."""
         self._gen_budget = 0
+        self._epoch += 1
         self.pool.give_back(self._pages[seq])
         self._pages[seq] = []
         self.lengths[seq] = 0
@@ -440,6 +444,7 @@ class PagedKVCache:
             self._store_values(values.to(dev), n_tok, max(lengths), starts)
         for s, n in enumerate(lengths):
             self.lengths[s] += n
+        self._epoch += 1
         self.seq_lens[: len(self.lengths)] = torch.tensor(self.lengths, dtype=torch.int32, device=dev)
 
     def append(self, keys: torch.Tensor, values: torch.Tensor) -> None:
@@ -459,6 +464,7 @@ class PagedKVCache:
         self.seq_lens[:n] += 1
         for s in range(n):
             self.lengths[s] += 1
+        self._epoch += 1
 
     RESERVE_AHEAD = 64   # tokens of page capacity the fused generate step keeps ahead of the context
 
@@ -492,6 +498,7 @@ class PagedKVCache:
                                  self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"], own_key_exact)
             for s_ in range(n):
                 self.lengths[s_] += 1
+            self._epoch += 1
             gs["lengths_after"] = list(self.lengths)
             return gs["out"]
         if k_new.shape[0] != n or k_new.shape[2] != 1:
@@ -553,6 +560,7 @@ class PagedKVCache:
             gs["graph"].replay()
         for s_ in range(n):
             self.lengths[s_] += 1
+        self._epoch += 1
         gs["lengths_after"] = list(self.lengths)
         # steps that need neither a page nor a larger grid
         self._gen_budget = min(min(len(pg) * PAGE_TOKENS - ln for pg, ln in zip(self._pages, self.lengths)),
@@ -608,6 +616,17 @@ class PagedKVCache:
         its own reference to the split workspace it was recorded with, so a later ``decode`` that needs
         a larger workspace does not pull that memory from under it.  ``use_graph=False`` makes one
         call of ``jqk_decode_attend_host`` instead (no capture; three enqueues and a wait)."""
+        hs = self._host_step
+        # Steady state: the same shape on an unchanged cache.  Two integer comparisons, a copy of the
+        # query into the staging buffer, one graph launch, one stream wait.
+        if (use_graph and hs is not None and hs["epoch"] == self._epoch and hs["generation"] == self.pool.generation
+                and hs["fast_key"] == (q_host.shape, tokens_per_split, zero_copy) and q_host.dtype is torch.bfloat16
+                and q_host.device.type == "cpu" and q_host.is_contiguous()):
+            if q_host.data_ptr() != hs["q_pin_ptr"]:
+                ctypes.memmove(hs["q_pin_ptr"], q_host.data_ptr(), hs["q_bytes"])
+            hs["graph"].replay()
+            torch.cuda.current_stream(hs["device"]).synchronize()
+            return hs["out_pin"]
         if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3 or not q_host.is_contiguous():
             raise ValueError("q_host must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor in host memory")
         if self.v_tables is not None:
@@ -624,7 +643,8 @@ class PagedKVCache:
             max_len = max(self.lengths) if self.lengths else 0
             tps = tokens_per_split or split_for_lengths(self.lengths[:n_seqs], n_q_heads, self.tables.n_heads)
             hs = {"key": key, "lengths": list(self.lengths), "generation": self.pool.generation,
-                  "table_ptr": self.page_table.data_ptr(),
+                  "table_ptr": self.page_table.data_ptr(), "epoch": self._epoch, "device": dev,
+                  "fast_key": (q_host.shape, tokens_per_split, zero_copy),
                   "ws": self._workspace(n_seqs, n_q_heads, max(1, -(-max_len // tps))),
                   "pools": (self.k_pool, self.v_pool, self.page_table),
                   "q_pin": torch.empty((n_seqs, n_q_heads, d), dtype=torch.bfloat16).pin_memory(),
@@ -644,6 +664,7 @@ class PagedKVCache:
                 if out_arg is hs["out_dev"]:
                     hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
 
+            hs["q_pin_ptr"], hs["q_bytes"] = hs["q_pin"].data_ptr(), hs["q_pin"].numel() * 2
             hs["q_pin"].copy_(q_host)
             with torch.cuda.stream(hs["stream"]):
                 enqueue()                      # first call outside capture: one-time set-up of the library
