@@ -70,7 +70,7 @@ class _Capture:
             self.moments.update(layer_idx, bf(q[b]), bf(k[b]), bf(v[b]) if self.moments.with_values else None)
 
 
-_STATE = {"capture": None, "registered": False}
+_STATE = {"capture": None, "registered": False, "layer_class": None}
 
 
 def register() -> None:
@@ -105,7 +105,9 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
 
 
 def make_paged_layer_class():
-    """The cache layer class (built lazily so that importing this module does not import transformers)."""
+    """The cache layer class (built on first use so that importing this module does not import transformers)."""
+    if _STATE["layer_class"] is not None:
+        return _STATE["layer_class"]
     base = _layer_base()
 
     class PagedCacheLayer(base):
@@ -163,6 +165,7 @@ def make_paged_layer_class():
         def prefetch(self) -> None:
             pass
 
+    _STATE["layer_class"] = PagedCacheLayer
     return PagedCacheLayer
 
 
