@@ -417,6 +417,13 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // the workspace) is cut to what the grid covers and flagged; otherwise the ticket below would
   // never see its last block.
   int len = seq_lens[seq];
+  // The table build's reads go out at once, in the same round trip as the length: nothing a block
+  // does later is queued ahead of them (a block that turns out to have no keys has read in vain).
+  const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
+  const int qh0 = head * group + g0;
+  TableLoads tloads;
+  if constexpr (BUILD_IN_BLOCK)
+    tloads = issue_table_loads(tb, head, D, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
   if constexpr (APPEND) len += 1;  // this launch attends over the key it appends
   // Append variant: every block of the launch passes here exactly once on its way out, all of its
   // threads together.  Each has read its length by then, so the block that takes the last ticket
@@ -444,8 +451,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
   }
   const int n_splits = (len + tokens_per_split - 1) / tokens_per_split;
-  const int g0 = qb * JQK_MAX_GROUP, n_group = min(JQK_MAX_GROUP, group - g0);
-  const int qh0 = head * group + g0;
   if (len <= 0) {  // empty context: defined output (zeros), written by split 0
     if (split == 0)
       for (int e = tid; e < n_group * D; e += DEC_THREADS)
@@ -454,10 +459,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     return;
   }
   if (split >= n_splits) { leave(); return; }
-  // the table build's reads go out first: nothing a block does later is queued ahead of them
-  TableLoads tloads;
-  if constexpr (BUILD_IN_BLOCK)
-    tloads = issue_table_loads(tb, head, D, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
   const HeadDesc hd = load_desc(tb.desc, head);
   const int t_begin = split * tokens_per_split;
   const int t_end = min(len, t_begin + tokens_per_split);
