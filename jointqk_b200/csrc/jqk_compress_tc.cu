@@ -173,89 +173,112 @@ __device__ __forceinline__ uint32_t search_code(float x, const float* __restrict
 }
 
 
-// Run by one thread.  `wcb[w]` is the first column of record word w (n_words + 1 entries, shared
-// memory), `units` a scratch of TC_MAX_UNITS int4.
+// Run by one whole warp (a single thread took 9 us over it, which every launch paid before its first
+// tile could leave).  `wcb[w]` is the first column of record word w (n_words + 1 entries, shared
+// memory), `units` a scratch of TC_MAX_UNITS int4 in shared memory.  Lane 0 lists the units, the
+// lanes classify one 16-column read each, then all lanes deal the units to the parts in step (the
+// same decisions in every lane; lane 0 writes).
 __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta, int n_words, int n_active, int4* units) {
+  const int lane = threadIdx.x & 31;
   // Units: every record word on its own, or together with its neighbour where that saves a
   // 16-column read (two 4-bit words hold 16 columns) or one of the two has no column.
   int n_units = 0, n_slots = 0;
-  for (int w = 0; w < n_words;) {
-    const int ca = wcb[w + 1] - wcb[w];
-    int nw = 1;
-    if (w + 1 < n_words) {
-      const int cb = wcb[w + 2] - wcb[w + 1];
-      if (ca == 0 || cb == 0 || (ca + cb + CH - 1) / CH < (ca + CH - 1) / CH + (cb + CH - 1) / CH) nw = 2;
+  if (lane == 0) {
+    for (int w = 0; w < n_words;) {
+      const int ca = wcb[w + 1] - wcb[w];
+      int nw = 1;
+      if (w + 1 < n_words) {
+        const int cb = wcb[w + 2] - wcb[w + 1];
+        if (ca == 0 || cb == 0 || (ca + cb + CH - 1) / CH < (ca + CH - 1) / CH + (cb + CH - 1) / CH) nw = 2;
+      }
+      // (a unit without columns still writes its zero words: one read that places nothing)
+      const int reads = max(1, (wcb[w + nw] - wcb[w] + CH - 1) / CH);
+      units[n_units] = make_int4(w | (nw << 8), wcb[w], reads, n_slots);
+      n_slots += reads;
+      ++n_units;
+      w += nw;
     }
-    // (a unit without columns still writes its zero words: one read that places nothing)
-    const int reads = max(1, (wcb[w + nw] - wcb[w] + CH - 1) / CH);
-    units[n_units] = make_int4(w | (nw << 8), wcb[w], reads, n_slots);
-    n_slots += reads;
-    ++n_units;
-    w += nw;
+    pl.n_slots = n_slots;
   }
-  pl.n_slots = n_slots;
-  // units to parts: largest first, each to the part with the least work so far
-  int load[TC_PARTS];
+  n_units = __shfl_sync(0xffffffffu, n_units, 0);
+  n_slots = __shfl_sync(0xffffffffu, n_slots, 0);
+  __syncwarp();
+  const bool planned = n_slots <= TC_MAX_SLOTS;   // at most 20: one read per lane
+  // class of read `lane` from the widths of its columns (columns past the unit count as unused)
+  int my_cls = TC_CLS_GENERAL;
+  if (planned && lane < n_slots) {
+    int4 un = units[0];
+    for (int u = 1; u < n_units; ++u) {
+      const int4 cand = units[u];
+      if (cand.w <= lane) un = cand;
+    }
+    const int r = lane - un.w;
+    const int c_end = wcb[(un.x & 255) + (un.x >> 8)];
+    const bool one_word = (un.x >> 8) == 1;
+    const bool full = un.y + r * CH + CH <= c_end;
+    bool all1 = true, all2 = true, odd1 = true, reg4 = !one_word && full, reg31 = one_word && full;
+#pragma unroll 4
+    for (int i = 0; i < CH; ++i) {
+      const int col = un.y + r * CH + i;
+      const int mt = (col < c_end) ? meta[col] : 0;
+      const int width = mt & 15, bp = (mt >> 4) & 1023;
+      all1 = all1 && (width == 0 || width == 1);
+      all2 = all2 && (width == 0 || width == 2);
+      if (i & 1) odd1 = odd1 && (width == 0 || width == 1);
+      reg4 = reg4 && width == 4 && bp == 32 * (un.x & 255) + 4 * i;
+      reg31 = reg31 && width == ((i & 1) ? 1 : 3) && bp == 32 * (un.x & 255) + 4 * (i / 2) + 3 * (i & 1);
+    }
+    my_cls = reg4 ? TC_CLS_REG4 : reg31 ? TC_CLS_REG31 : (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
+           : odd1 ? TC_CLS_ODD1 : TC_CLS_GENERAL;
+  }
+  // units to parts: largest first (ties: the earlier unit), each to the part with the least work so far
+  int load[TC_PARTS], n_steps[TC_PARTS];
 #pragma unroll
-  for (int q = 0; q < TC_PARTS; ++q) { load[q] = 0; pl.n_steps[q] = 0; }
-  uint32_t taken = 0;
-  for (int k = 0; k < n_units && n_slots <= TC_MAX_SLOTS; ++k) {
-    int best = -1, best_reads = -1;
-    for (int u = 0; u < n_units; ++u)
-      if (!((taken >> u) & 1u) && units[u].z > best_reads) { best = u; best_reads = units[u].z; }
-    taken |= 1u << best;
+  for (int q = 0; q < TC_PARTS; ++q) { load[q] = 0; n_steps[q] = 0; }
+  const int4 mine = (lane < n_units) ? units[lane] : make_int4(0, 0, 0, 0);
+  bool taken = lane >= n_units;
+  for (int k = 0; k < n_units && planned; ++k) {
+    const int key = taken ? -1 : ((mine.z << 5) | (31 - lane));
+    const int best_key = __reduce_max_sync(0xffffffffu, key);
+    const int best = 31 - (best_key & 31);
+    if (lane == best) taken = true;
+    const int un_x = __shfl_sync(0xffffffffu, mine.x, best), un_y = __shfl_sync(0xffffffffu, mine.y, best);
+    const int un_z = __shfl_sync(0xffffffffu, mine.z, best), un_w = __shfl_sync(0xffffffffu, mine.w, best);
     int q_min = 0;
 #pragma unroll
     for (int q = 1; q < TC_PARTS; ++q)
       if (load[q] < load[q_min]) q_min = q;
+    int pos = 0;
 #pragma unroll
     for (int q = 0; q < TC_PARTS; ++q)
-      if (q == q_min) load[q] += best_reads * CH + 4;
-    const int4 un = units[best];
-    int pos = pl.n_steps[q_min];
-    const int c_end = wcb[(un.x & 255) + (un.x >> 8)];
-    for (int r = 0; r < un.z; ++r) {
-      // class of the read from the widths of its columns (columns past the unit count as unused)
-      bool all1 = true, all2 = true, odd1 = true;
-      for (int i = 0; i < CH; ++i) {
-        const int col = un.y + r * CH + i;
-        const int width = (col < c_end) ? (meta[col] & 15) : 0;
-        all1 = all1 && (width == 0 || width == 1);
-        all2 = all2 && (width == 0 || width == 2);
-        if (i & 1) odd1 = odd1 && (width == 0 || width == 1);
+      if (q == q_min) { load[q] += un_z * CH + 4; pos = n_steps[q]; n_steps[q] += un_z; }
+    for (int r = 0; r < un_z; ++r) {
+      const int cls = __shfl_sync(0xffffffffu, my_cls, un_w + r);
+      if (lane == 0) {
+        pl.slot_step[un_w + r] = q_min * 32 + pos + r;
+        pl.step[q_min][pos + r] = make_int2((un_y + r * CH) | ((un_w + r) << 8),
+                                            un_x | ((r == 0) << 16) | ((r == un_z - 1) << 17) | (cls << 18));
       }
-      const bool one_word = (un.x >> 8) == 1;
-      bool reg4 = !one_word && un.y + r * CH + CH <= c_end;
-      for (int i = 0; reg4 && i < CH; ++i) {
-        const int mt = meta[un.y + r * CH + i];
-        reg4 = (mt & 15) == 4 && ((mt >> 4) & 1023) == 32 * (un.x & 255) + 4 * i;
-      }
-      bool reg31 = one_word && un.y + r * CH + CH <= c_end;
-      for (int i = 0; reg31 && i < CH; ++i) {
-        const int mt = meta[un.y + r * CH + i];
-        reg31 = (mt & 15) == ((i & 1) ? 1 : 3) && ((mt >> 4) & 1023) == 32 * (un.x & 255) + 4 * (i / 2) + 3 * (i & 1);
-      }
-      const int cls = reg4 ? TC_CLS_REG4 : reg31 ? TC_CLS_REG31 : (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
-                    : odd1 ? TC_CLS_ODD1 : TC_CLS_GENERAL;
-      pl.slot_step[un.w + r] = q_min * 32 + pos;
-      pl.step[q_min][pos++] = make_int2((un.y + r * CH) | ((un.w + r) << 8),
-                                        un.x | ((r == 0) << 16) | ((r == un.z - 1) << 17) | (cls << 18));
     }
-    pl.n_steps[q_min] = pos;
   }
-  // generic path: word ranges cut where the column counts are closest to even
-  int cut[TC_PARTS + 1];
-  cut[0] = 0; cut[TC_PARTS] = n_words;
+  if (lane == 0) {
 #pragma unroll
-  for (int q = 1; q < TC_PARTS; ++q) {
-    const int target = (n_active * q + TC_PARTS / 2) / TC_PARTS;
-    int w = cut[q - 1];
-    while (w < n_words && wcb[w] < target) ++w;
-    if (w > cut[q - 1] && w < n_words && target - wcb[w - 1] < wcb[w] - target) --w;
-    cut[q] = max(w, cut[q - 1]);
+    for (int q = 0; q < TC_PARTS; ++q) pl.n_steps[q] = planned ? n_steps[q] : 0;
+    // generic path: word ranges cut where the column counts are closest to even
+    int cut[TC_PARTS + 1];
+    cut[0] = 0; cut[TC_PARTS] = n_words;
+#pragma unroll
+    for (int q = 1; q < TC_PARTS; ++q) {
+      const int target = (n_active * q + TC_PARTS / 2) / TC_PARTS;
+      int w = cut[q - 1];
+      while (w < n_words && wcb[w] < target) ++w;
+      if (w > cut[q - 1] && w < n_words && target - wcb[w - 1] < wcb[w] - target) --w;
+      cut[q] = max(w, cut[q - 1]);
+    }
+#pragma unroll
+    for (int q = 0; q <= TC_PARTS; ++q) pl.cut[q] = cut[q];
   }
-#pragma unroll
-  for (int q = 0; q <= TC_PARTS; ++q) pl.cut[q] = cut[q];
+  __syncwarp();
 }
 
 // Constants of entry e (slot e / 16, column e % 16 of the read) of a planned head: x = the bit pattern
@@ -482,7 +505,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     const int ew = warp - 2;
     const int row = 32 * (warp & 3) + lane;          // TMEM lane = key inside the tile
     const int part = ew >> 2;
-    if (ew == 0 && lane == 0) tc_make_plan(sm.plan, sm.wcb, sm.meta, hd.n_words, hd.n_active, reinterpret_cast<int4*>(sm.crow_m));
+    if (ew == 0) tc_make_plan(sm.plan, sm.wcb, sm.meta, hd.n_words, hd.n_active, reinterpret_cast<int4*>(sm.crow_m));
     asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_WARPS * 32) : "memory");
     const bool planned = sm.plan.n_slots <= TC_MAX_SLOTS;
     const uint32_t pre_addr = smem_u32(sm.upre), uthr_addr = smem_u32(sm.uthr);
