@@ -264,11 +264,13 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
   if (lane == 0) {
 #pragma unroll
     for (int q = 0; q < TC_PARTS; ++q) pl.n_steps[q] = planned ? n_steps[q] : 0;
-    // generic path: word ranges cut where the column counts are closest to even
+    // generic path only: word ranges cut where the column counts are closest to even
     int cut[TC_PARTS + 1];
-    cut[0] = 0; cut[TC_PARTS] = n_words;
 #pragma unroll
-    for (int q = 1; q < TC_PARTS; ++q) {
+    for (int q = 0; q < TC_PARTS; ++q) cut[q] = 0;
+    cut[TC_PARTS] = n_words;
+#pragma unroll
+    for (int q = 1; q < TC_PARTS && !planned; ++q) {
       const int target = (n_active * q + TC_PARTS / 2) / TC_PARTS;
       int w = cut[q - 1];
       while (w < n_words && wcb[w] < target) ++w;
