@@ -1,0 +1,101 @@
+"""Seeded sweeps over shapes that the hand-picked cases do not enumerate: ragged and empty
+sequences, lengths on and around page (16), tile (32) and block (384) boundaries, group sizes that do
+and do not fill a query block, head sizes 64 and 128, every bit budget, small and default splits.
+
+* decode attention against fp32 attention over the reconstruction of the same codes (the decompress
+  kernel has its own parity tests against the oracle), tolerance as in test_gpu_decode.py;
+* the one-launch generate step against the graph of separate launches: same outputs, same codes in
+  the pages, same lengths, for bf16 / fp16 / fp32 rows and pools that have to grow."""
+
+import random
+
+import pytest
+import torch
+
+import jointqk_b200 as jq
+from jointqk_b200 import paged
+from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+pytestmark = pytest.mark.gpu
+
+EDGE_LENGTHS = [0, 1, 15, 16, 17, 31, 33, 383, 384, 385]
+_TABLES = {}
+
+
+def _tables(H, b, d=128):
+    key = (H, b, d)
+    if key not in _TABLES:
+        keys = torch.stack([spectrum_keys(8192, config_seed(0, 5, h), d=d) for h in range(H)])
+        comps, _ = fit_sigma_k_heads(keys[:, :4096], b)
+        _TABLES[key] = (keys, jq.HeadTables.from_compressors(comps, device="cuda"))
+    return _TABLES[key]
+
+
+def test_decode_over_random_shapes():
+    rng = random.Random(3)
+    worst = 0.0
+    for it in range(60):
+        d = rng.choice([128, 128, 128, 64])
+        H, g = rng.choice([1, 2, 4, 8]), rng.choice([1, 2, 4, 5, 8])
+        b = rng.choice([1.0, 2.0, 2.5, 3.0, 4.0])
+        lens = [rng.choice(EDGE_LENGTHS + [rng.randint(2, 8000)]) for _ in range(rng.randint(1, 6))]
+        tps = rng.choice([0, 0, 32, 128, 384, 1024])
+        keys, tables = _tables(H, b, d)
+        N = max(max(lens), 1)
+        gen = torch.Generator().manual_seed(it)
+        kk = torch.stack([keys[:, :N].roll(3 * s, 1) for s in range(len(lens))]).cuda()
+        v = torch.randn(len(lens), H, N, d, generator=gen).to(torch.bfloat16).cuda()
+        q = torch.randn(len(lens), H * g, d, generator=gen).to(torch.bfloat16).cuda()
+        cache = paged.PagedKVCache(tables, [max(n, 1) for n in lens])
+        cache.prefill(kk, v, lens)
+        out = cache.decode(q, tokens_per_split=tps)
+        paged.check_status(cache.status)
+        k_hat = paged.decompress(paged.PackedKeys(tables, cache.k_pool, cache.page_table, cache.seq_lens, list(lens), cache.status))
+        for s, n in enumerate(lens):
+            if n == 0:
+                assert out[s].abs().max().item() == 0.0
+                continue
+            kh = k_hat[s, :, :n].repeat_interleave(g, 0)
+            vv = v[s, :, :n].float().repeat_interleave(g, 0)
+            w = (torch.einsum("hd,htd->ht", q[s].float(), kh) / d ** 0.5).softmax(-1)
+            ref = torch.einsum("ht,htd->hd", w, vv)
+            err = ((out[s] - ref).abs() / ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)).max().item()
+            worst = max(worst, err)
+            assert err < 2e-3, (it, d, H, g, b, lens, tps, s, err)
+    print(f"decode over 60 random shapes: worst relative error {worst:.2e}")
+
+
+def test_fused_generate_step_over_random_shapes():
+    rng = random.Random(7)
+    for it in range(40):
+        H, g = rng.choice([1, 2, 4]), rng.choice([1, 2, 4, 8])
+        b = rng.choice([1.0, 2.0, 2.5, 3.0, 4.0])
+        n0 = [rng.choice(EDGE_LENGTHS + [rng.randint(2, 3000)]) for _ in range(rng.randint(1, 4))]
+        steps = rng.randint(1, 40)
+        dtype = rng.choice([torch.bfloat16, torch.float32, torch.float16])
+        keys, tables = _tables(H, b)
+        total = max(n0) + steps
+        gen = torch.Generator().manual_seed(it)
+        kk = torch.stack([keys[:, :total].roll(3 * s, 1) for s in range(len(n0))]).cuda()
+        v = torch.randn(len(n0), H, total, 128, generator=gen).to(torch.bfloat16).cuda()
+        fused = paged.PagedKVCache(tables, n_seqs=len(n0), initial_pages=rng.choice([1, 8, 64]))   # has to grow
+        plain = paged.PagedKVCache(tables, n_seqs=len(n0))
+        for cache in (fused, plain):
+            if max(n0) > 0:
+                cache.prefill(kk[:, :, :max(n0)], v[:, :, :max(n0)], lengths=n0)
+        for i in range(steps):
+            q = torch.randn(len(n0), H * g, 128, generator=gen).to(torch.bfloat16).cuda()
+            kn = torch.stack([kk[s, :, n0[s] + i] for s in range(len(n0))]).to(dtype).unsqueeze(2)
+            vn = torch.stack([v[s, :, n0[s] + i] for s in range(len(n0))]).to(dtype).unsqueeze(2)
+            got = fused.generate_step(kn, vn, q).clone()
+            want = plain.generate_step(kn, vn, q, fused_append=False)
+            # the two caches may size their grids differently (pages reserved ahead), so the splits,
+            # and with them the last bits of the merge, may differ
+            assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item(), (it, i)
+        assert fused.seq_lens.tolist() == fused.lengths == plain.lengths == [n + steps for n in n0]
+        for s in range(len(n0)):
+            pk = [paged.PackedKeys(c.tables, c.k_pool, c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
+                  for c in (fused, plain)]
+            assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])), (it, s)
+        paged.check_status(fused.status)
+        paged.check_status(plain.status)
