@@ -5,7 +5,10 @@ and do not fill a query block, head sizes 64 and 128, every bit budget, small an
 * decode attention against fp32 attention over the reconstruction of the same codes (the decompress
   kernel has its own parity tests against the oracle), tolerance as in test_gpu_decode.py;
 * the one-launch generate step against the graph of separate launches: same outputs, same codes in
-  the pages, same lengths, for bf16 / fp16 / fp32 rows and pools that have to grow."""
+  the pages, same lengths, for bf16 / fp16 / fp32 rows and pools that have to grow;
+* the tensor-core compress kernel against the CUDA-core one over arbitrary allocations (widths drawn
+  per coordinate, sorted, or in blocks of eight), which drives the read planner through every class
+  and into its generic path: the two may only differ where a value sits on a decision threshold."""
 
 import random
 
@@ -99,3 +102,37 @@ def test_fused_generate_step_over_random_shapes():
             assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])), (it, s)
         paged.check_status(fused.status)
         paged.check_status(plain.status)
+
+
+def test_tensor_core_compress_over_random_allocations():
+    rng = random.Random(5)
+    H, T = 2, 2048
+    keys = torch.stack([spectrum_keys(T, config_seed(0, 2, h)) for h in range(H)]).to(torch.bfloat16)
+    base, _ = fit_sigma_k_heads(keys.float(), 2.5)
+    differ = total = 0
+    for it in range(60):
+        comps = []
+        for c in base:
+            mode = rng.choice(["iid", "sorted", "blocks"])
+            if mode == "iid":
+                bits = torch.tensor(rng.choices([0, 1, 2, 3, 4], weights=[rng.random() for _ in range(5)], k=128))
+            elif mode == "sorted":
+                cuts = sorted(rng.randint(0, 128) for _ in range(4))
+                bits = torch.tensor([4] * cuts[0] + [3] * (cuts[1] - cuts[0]) + [2] * (cuts[2] - cuts[1])
+                                    + [1] * (cuts[3] - cuts[2]) + [0] * (128 - cuts[3]))
+            else:
+                bits = torch.tensor(sum([[rng.choice([0, 1, 2, 3, 4])] * 8 for _ in range(16)], []))
+            if int(bits.sum()) == 0:
+                bits[0] = 1
+            comps.append(jq.PerCoordCompressor(bits, c.stds, c.forward_map, c.inverse_map))
+        tables = jq.HeadTables.from_compressors(comps, device="cuda")
+        n = rng.choice([T, 1000, 129, 128, 17])
+        on_tensor_cores = paged.compress(tables, keys[:, :n].unsqueeze(0).cuda())            # bf16 keys
+        on_cuda_cores = paged.compress(tables, keys[:, :n].float().unsqueeze(0).cuda())      # the same values in fp32
+        a, b = paged.unpack_codes(on_tensor_cores), paged.unpack_codes(on_cuda_cores)
+        differ += int((a != b).sum())
+        total += a.numel()
+        assert (a.int() - b.int()).abs().max().item() <= 1, it          # a threshold tie moves a code by one level
+        paged.check_status(on_tensor_cores.status)
+    print(f"tensor-core vs CUDA-core codes over 60 allocations: {differ} of {total} differ")
+    assert differ <= 1e-5 * total + 2
