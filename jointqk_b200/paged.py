@@ -629,8 +629,8 @@ class PagedKVCache:
             return hs["out_pin"]
         if q_host.device.type != "cpu" or q_host.dtype != torch.bfloat16 or q_host.dim() != 3 or not q_host.is_contiguous():
             raise ValueError("q_host must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor in host memory")
-        if self.v_tables is not None:
-            raise NotImplementedError("decode_host is wired for bf16 values; use decode() with packed values")
+        if self.v_tables is not None and not use_graph:
+            raise NotImplementedError("with packed values decode_host takes the graph form (jqk_decode_attend_host is wired for bf16 values)")
         if not use_graph:
             return self._decode_host_call(q_host, tokens_per_split, zero_copy)
         dev = self.tables.device
@@ -660,7 +660,7 @@ class PagedKVCache:
                 if q_arg is hs["q_dev"]:
                     hs["q_dev"].copy_(hs["q_pin"], non_blocking=True)
                 decode_attend(self.tables, q_arg, self.seq_lens, max_len, hs["pools"][2], hs["pools"][0],
-                              hs["pools"][1], out_arg, hs["ws"], self.status, tps)
+                              hs["pools"][1], out_arg, hs["ws"], self.status, tps, v_tables=self.v_tables)
                 if out_arg is hs["out_dev"]:
                     hs["out_pin"].copy_(hs["out_dev"], non_blocking=True)
 

@@ -117,3 +117,20 @@ def test_packed_values_append_and_bytes():
     assert a.v_pool.dtype == torch.int32 and a.v_pool.shape[2] == v_tables.words_per_record
     assert v_tables.payload_bytes_per_key == 48.0 and tables.payload_bytes_per_key == 32.0
     paged.check_status(a.status)
+
+
+def test_decode_from_host_buffers_with_packed_values():
+    """decode_host (replayed graph of H2D copy, decode over packed keys and values, D2H copy) returns
+    what decode() returns."""
+    keys, vals, comps, v_comps, tables, v_tables = _setup(2, 4096, 2.0, 3)
+    cache = paged.PagedKVCache(tables, [3000], v_tables=v_tables)
+    cache.prefill(keys[:, :3000].unsqueeze(0).cuda(), vals[:, :3000].to(torch.bfloat16).unsqueeze(0).cuda())
+    g = torch.Generator().manual_seed(4)
+    for _ in range(2):
+        q = torch.randn(1, 8, 128, generator=g).to(torch.bfloat16)
+        want = cache.decode(q.cuda()).cpu()
+        assert torch.equal(cache.decode_host(q).clone(), want)
+        assert torch.equal(cache.decode_host(q, zero_copy="out").clone(), want)
+    with pytest.raises(NotImplementedError):
+        cache.decode_host(q, use_graph=False)
+    paged.check_status(cache.status)
