@@ -15,14 +15,15 @@ transformers = pytest.importorskip("transformers")
 from oracle import reference_port as orc  # noqa: E402
 
 
-def _model():
-    from transformers import LlamaConfig, LlamaForCausalLM
+def _model(family="llama"):
+    """Random weights, the attention shapes of the two families the reference evaluates."""
+    import transformers as tf
 
     torch.manual_seed(1234)
-    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=3,
-                      num_attention_heads=4, num_key_value_heads=2, head_dim=128, max_position_embeddings=1024,
-                      rope_theta=10000.0)
-    return LlamaForCausalLM(cfg).to(device="cuda", dtype=torch.bfloat16).eval()
+    kw = dict(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, max_position_embeddings=1024)
+    model = tf.LlamaForCausalLM(tf.LlamaConfig(**kw)) if family == "llama" else tf.Qwen3ForCausalLM(tf.Qwen3Config(**kw))
+    return model.to(device="cuda", dtype=torch.bfloat16).eval()
 
 
 def _oracle_layer_class(comps):
@@ -46,12 +47,13 @@ def _oracle_layer_class(comps):
 
 
 @torch.no_grad()
-def test_llama_decodes_over_the_packed_cache_like_the_reference_flow():
+@pytest.mark.parametrize("family", ["llama", "qwen3"])
+def test_model_decodes_over_the_packed_cache_like_the_reference_flow(family):
     from transformers import cache_utils
 
     from jointqk_b200 import hf, paged
 
-    model = _model()
+    model = _model(family)
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, 512, (2, 256), generator=g).cuda() for _ in range(4)]
     moments = hf.calibrate(model, prompts)
@@ -87,10 +89,12 @@ def test_llama_decodes_over_the_packed_cache_like_the_reference_flow():
     scale = want.abs().max().item()
     err = (got - want).abs().max().item() / scale
     effect = (plain - want).abs().max().item() / scale
-    print(f"logits: packed vs reference flow {err:.3e}, compression effect {effect:.3e}")
+    mean_err = (got - want).abs().mean().item() / scale
+    mean_effect = (plain - want).abs().mean().item() / scale
+    print(f"logits: packed vs reference flow {err:.3e} (mean {mean_err:.3e}), compression effect {effect:.3e} (mean {mean_effect:.3e})")
     assert torch.allclose(got[0], want[0], atol=1e-5 * scale)        # prefill sees exact keys in both
     assert err < 2e-2                                               # bf16 logits resolve 4e-3; 16-bit tables, bf16 weights in P.V
-    assert effect > 2 * err
+    assert mean_effect > 2 * mean_err                                # the comparison is not vacuous (means: a bf16 ulp is coarse for maxima)
 
 
 @torch.no_grad()

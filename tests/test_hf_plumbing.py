@@ -29,17 +29,27 @@ class DensePaged:
         return torch.einsum("bht,bhtd->bhd", s.softmax(-1), vv)
 
 
+def _tiny(family: str):
+    """The two model families the reference evaluates (Llama-3.1 and Qwen3 attention), at toy size."""
+    import transformers as tf
+
+    kw = dict(vocab_size=128, hidden_size=256, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, max_position_embeddings=256)
+    if family == "llama":
+        return tf.LlamaForCausalLM(tf.LlamaConfig(**kw)).eval()
+    return tf.Qwen3ForCausalLM(tf.Qwen3Config(**kw)).eval()
+
+
 @torch.no_grad()
-def test_cache_layer_and_attention_function_under_generate(monkeypatch):
-    from transformers import LlamaConfig, LlamaForCausalLM, cache_utils
+@pytest.mark.parametrize("family", ["llama", "qwen3"])
+def test_cache_layer_and_attention_function_under_generate(monkeypatch, family):
+    from transformers import cache_utils
 
     from jointqk_b200 import hf
 
     monkeypatch.setattr(hf, "PagedKVCache", DensePaged)
     torch.manual_seed(0)
-    cfg = LlamaConfig(vocab_size=128, hidden_size=256, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
-                      num_key_value_heads=2, head_dim=64, max_position_embeddings=256)
-    model = LlamaForCausalLM(cfg).eval()
+    model = _tiny(family)
     ids = torch.randint(0, 128, (2, 24))
     kw = dict(max_new_tokens=6, do_sample=False, output_logits=True, return_dict_in_generate=True, pad_token_id=0,
               attention_mask=torch.ones_like(ids))
