@@ -81,7 +81,9 @@ extern "C" {
  *   center        float [H][d] or NULL: a mean that is subtracted from every input row before the
  *                 transform and added back after reconstruction (the reference's CenteredCompressor,
  *                 experiments/stage1/toolkit/v_compressor_adapter.py:46-72, used on the value side);
- *                 the tensor-core compress kernel is not used for centred tables
+ *   center_cols   float [H][128] or NULL: center @ (the scaled basis that fwd_limbs holds), column c;
+ *                 with it the tensor-core compress kernel serves centred tables as well (it
+ *                 transforms the raw rows and subtracts this constant from every column)
  *   unit_pre      uint8 [4][128], unit_thr float [4][16] (HOST values, +inf padded), unit_aff float [2]
  *                 (HOST): the shared coarse-to-exact quantiser of the tensor-core kernel for widths
  *                 1..4: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes 2^23),
@@ -103,6 +105,7 @@ typedef struct jqk_head_tables {
   const uint16_t* fwd_limbs;
   const uint8_t* unit_pre;
   const float* center;
+  const float* center_cols;
   float unit_thr[64];
   float unit_aff[2];
 } jqk_head_tables;

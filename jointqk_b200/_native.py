@@ -33,6 +33,7 @@ class JqkHeadTables(C.Structure):
         ("fwd_limbs", C.c_void_p),
         ("unit_pre", C.c_void_p),
         ("center", C.c_void_p),
+        ("center_cols", C.c_void_p),
         ("unit_thr", C.c_float * 64),
         ("unit_aff", C.c_float * 2),
     ]

@@ -91,6 +91,7 @@ struct TcPlan {
 struct TcSmem {
   uint8_t a[TC_STAGES][TC_A_BYTES];  // [k half][128 keys][64 dims], 128B swizzle
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
+  float c0[128];          // centred tables: the mean in column space, subtracted from every transformed value
   float uthr[64];         // unit decision thresholds, [width - 1][16]
   uint8_t upre[4 * 128];  // per width and cell: 16 * (width - 1) + a lower bound of the code (at most one short),
                           // i.e. the index into uthr at which the one exact comparison is made
@@ -419,6 +420,7 @@ __device__ __forceinline__ void quant16(const UnitConsts& uc, const float* __res
   }
 }
 
+template <bool CENTERED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
                    const __grid_constant__ UnitConsts uc, jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
@@ -438,6 +440,8 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   for (int e = tid; e < 4 * 128 / 4; e += TC_THREADS)
     reinterpret_cast<uint32_t*>(sm.upre)[e] = reinterpret_cast<const uint32_t*>(tb.unit_pre)[e];
   for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
+  if constexpr (CENTERED)
+    for (int e = tid; e < 128; e += TC_THREADS) sm.c0[e] = tb.center_cols[(size_t)head * 128 + e];
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -560,6 +564,11 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         for (int s = 0; s < my_steps; ++s) {
           const int2 cur = sm.plan.step[part][s];
           tmem_ld16(t_lane + (cur.x & 255), v);
+          if constexpr (CENTERED) {
+            const float* cc = sm.c0 + (cur.x & 255);   // the same address in every lane: one broadcast read each
+#pragma unroll
+            for (int i = 0; i < CH; ++i) v[i] -= (((cur.x & 255) + i) < 128) ? cc[i] : 0.f;
+          }
           const float* rw = sm.crow_w + (cur.x >> 8) * CH;
           const uint2* rm = sm.crow_m + (cur.x >> 8) * CH;
           if (cur.y & (1 << 16)) lo = hi = 0u;
@@ -588,6 +597,10 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         for (int c0 = c_lo; c0 < c_hi; c0 += CH) {
           float v[CH];
           tmem_ld16(t_lane + c0, v);
+          if constexpr (CENTERED) {
+#pragma unroll
+            for (int i = 0; i < CH; ++i) v[i] -= (c0 + i < 128) ? sm.c0[c0 + i] : 0.f;
+          }
           for (int i = 0; i < CH && c0 + i < c_hi; ++i) {
             const int m = sm.meta[c0 + i];
             const int bp = (m >> 4) & 1023;
@@ -635,7 +648,7 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
                             const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
                             const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
                             uint32_t* k_pool, int32_t* status, cudaStream_t st) {
-  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || tables->center) return 1;
+  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || (tables->center && !tables->center_cols)) return 1;
   if ((uintptr_t)keys % 16 || (token_stride * 2) % 16 || (head_stride * 2) % 16 || (seq_stride * 2) % 16) return 1;
   if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE || !tables->unit_pre) return 1;
   CUtensorMap key_map, limb_map;
@@ -673,8 +686,12 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
   // host form of the grid: cell = clamp(round(x * aff[0] + aff[1] - 2^23), 0, 127)
   uc.cs = tables->unit_aff[0] * (1.f / 127.f);
   uc.co = (tables->unit_aff[1] - 8388608.f) * (1.f / 127.f);
-  JQK_SMEM_ONCE(compress_tc_kernel, smem, "tensor-core compress smem attribute");
-  compress_tc_kernel<<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  JQK_SMEM_ONCE(compress_tc_kernel<false>, smem, "tensor-core compress smem attribute");
+  JQK_SMEM_ONCE(compress_tc_kernel<true>, smem, "tensor-core compress smem attribute");
+  if (tables->center)
+    compress_tc_kernel<true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  else
+    compress_tc_kernel<false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
   return 0;
 }

@@ -126,10 +126,15 @@ class HeadTables:
             self.fwd_limbs = split_bf16_limbs(scaled.transpose(1, 2).contiguous(), 3) \
                 .permute(1, 0, 2, 3).contiguous().to(self.device)
         # optional per-head mean, subtracted before the transform and added back after reconstruction
-        self.center = None
+        self.center = self.center_cols = None
         if center is not None:
             c = center.detach().float().cpu().reshape(H, d).contiguous()
             self.center = c.to(self.device)
+            if self.fwd_limbs is not None:
+                # the mean in column space, through exactly the basis the tensor cores multiply by (the
+                # sum of the three limbs), in fp64: transform(raw row) - this = transform(row - mean)
+                basis = self.fwd_limbs.float().cpu().double().sum(1)                # [H][col][dim]
+                self.center_cols = torch.einsum("hd,hcd->hc", c.double(), basis).float().contiguous().to(self.device)
         self.struct = _native.JqkHeadTables(
             n_heads=H, d=d, words_per_record=self.words_per_record, reserved=0,
             desc=self.desc.data_ptr(), col_meta=self.col_meta.data_ptr(),
@@ -139,6 +144,7 @@ class HeadTables:
             fwd_limbs=None if self.fwd_limbs is None else self.fwd_limbs.data_ptr(),
             unit_pre=self.unit_pre.data_ptr(),
             center=None if self.center is None else self.center.data_ptr(),
+            center_cols=None if self.center_cols is None else self.center_cols.data_ptr(),
             unit_thr=(C.c_float * 64)(*[float(x) for x in u_thr.reshape(-1)]),
             unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])))
 
