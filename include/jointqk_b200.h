@@ -250,6 +250,20 @@ int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, c
                                  size_t workspace_bytes, int32_t* status, void* stream);
 
 /*
+ * jqk_decode_append_attend with the values stored as packed codes (see
+ * jqk_decode_attend_packed_values): the new value row has its mean subtracted in fp32 and is
+ * compressed through `v_tables` exactly as jqk_compress_paged would, into `v_code_pool`.  The flag
+ * JQK_APPEND_OWN_KEY_EXACT applies to the key only; the new value is read from its codes.
+ */
+int32_t jqk_decode_append_attend_packed_values(
+    const jqk_head_tables* tables, const jqk_head_tables* v_tables, const void* q, const void* new_k, const void* new_v,
+    int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride, int64_t k_head_stride, int64_t v_seq_stride,
+    int64_t v_head_stride, int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
+    int32_t tokens_per_split, const int32_t* page_table, int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool,
+    uint32_t* v_code_pool, void* out, int32_t out_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
+    int32_t* status, void* stream);
+
+/*
  * jqk_decode_attend over packed values: the value pool holds codes of a second per-coordinate
  * compressor (`v_tables`, optionally centred) in the same paged record format as the keys, written
  * by jqk_compress_paged with those tables.  The kernel dequantises a tile of values into shared

@@ -71,6 +71,11 @@ SIGNATURES = {
         C.POINTER(JqkHeadTables), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64,
         C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "jqk_decode_append_attend_packed_values": (C.c_int32, [
+        C.POINTER(JqkHeadTables), C.POINTER(JqkHeadTables), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+        C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+        C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t,
+        C.c_void_p, C.c_void_p]),
     "jqk_decode_attend_static": (C.c_int32, [
         C.POINTER(JqkHeadTables), C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
         C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,

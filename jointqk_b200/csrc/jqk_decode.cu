@@ -172,6 +172,12 @@ template <> struct DecodeSmemT<true> {
   float wm[DEC_WARPS][JQK_MAX_GROUP];
   float wl[DEC_WARPS][JQK_MAX_GROUP];
   int is_last;
+  // the row appended by this launch (blocks of the last split only): the key's and the value's codes
+  float ap_k[JQK_MAX_DIM];       // the key row, then the centred value row
+  uint32_t ap_words[JQK_MAX_WORDS];
+  uint32_t apv_words[JQK_MAX_WORDS];
+  float ap_dot[JQK_MAX_GROUP];
+  int ap_page, ap_last;
   alignas(16) int32_t vmeta[JQK_MAX_COLS];        // value columns: width | bit position << 4
   __nv_bfloat16 vcb[JQK_MAX_COLS * 16];           // value codebooks, bf16 (what the tensor-core product multiplies)
 };
@@ -282,6 +288,8 @@ struct ValueSide {
   const float* inv_rows;    // [H][128][d]
   const float* center;      // [H][d] or null
   int n_heads, wpr;
+  const float* fwd_cols;    // [H][d][128]  (append variant: the new value row is compressed in the kernel)
+  const float* thresholds;  // [H][128][16]
 };
 
 // The newest token of every sequence, appended by the decode launch itself (k == nullptr: none).
@@ -381,6 +389,80 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
   }
 }
 
+// One row of D values in shared memory (`row`) -> its record words in `words` (zeroed by the caller),
+// with the arithmetic of compress_token_kernel: thread = column, dims in ascending order.
+template <int D>
+__device__ __forceinline__ void quantise_row(const float* row, uint32_t* words, const float* __restrict__ fwd_cols,
+                                             const int32_t* __restrict__ col_meta, const float* __restrict__ thresholds,
+                                             int head, int n_active) {
+  const int tid = threadIdx.x;
+  if (tid < n_active) {
+    const float* w = fwd_cols + (size_t)head * D * 128 + tid;
+    float x = 0.f;
+#pragma unroll 32
+    for (int i = 0; i < D; ++i) x = fmaf(row[i], __ldg(w + (size_t)i * 128), x);
+    const int m = col_meta[(size_t)head * 128 + tid];
+    const float* th = thresholds + ((size_t)head * 128 + tid) * 16;
+    const int n_thr = (1 << (m & 15)) - 1;
+    uint32_t code = 0;
+    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const int bp = (m >> 4) & 1023;
+    atomicOr(&words[bp >> 5], code << (bp & 31));
+  }
+}
+
+// The append with packed values: the key as in append_row, then the value row (mean subtracted in
+// fp32, as the reference's wrapper does before its transform) through the value side's tables; both
+// records stay in shared memory and, with `write`, go to the tail pages of the two code pools.
+template <int D>
+__device__ __noinline__ void append_row_packed(DecodeSmemT<true>& sm, const float* __restrict__ k_fwd,
+                                               const int32_t* __restrict__ k_meta, const float* __restrict__ k_thr,
+                                               int n_heads, int k_wpr, int k_active, int k_words,
+                                               const float* __restrict__ v_fwd, const int32_t* __restrict__ v_meta,
+                                               const float* __restrict__ v_thr, const float* __restrict__ v_center,
+                                               int v_wpr, int v_active, int v_words, const void* k_row, const void* v_row,
+                                               int k_dtype, int v_dtype, uint32_t* k_pool, uint32_t* v_pool, int head, int seq,
+                                               bool write, int pos, const int32_t* __restrict__ page_table, int pt_stride,
+                                               int n_pages, int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group) {
+  const int tid = threadIdx.x;
+  if (tid < D) {
+    sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
+  } else if (tid >= 256 && tid < 256 + JQK_MAX_WORDS) {
+    sm.ap_words[tid - 256] = 0u;
+    sm.apv_words[tid - 256] = 0u;
+  } else if (tid == DEC_THREADS - 1) {
+    sm.ap_page = lookup_page(page_table, pt_stride, seq, pos / JQK_PAGE_TOKENS, n_pages, status);
+  }
+  __syncthreads();
+  quantise_row<D>(sm.ap_k, sm.ap_words, k_fwd, k_meta, k_thr, head, k_active);
+  if (q_rows && tid >= 256) {
+    const int h = (tid - 256) >> 5, lane = tid & 31;
+    if (h < n_group) {
+      float dot = 0.f;
+      for (int i = lane; i < D; i += 32) dot = fmaf(__bfloat162float(q_rows[(size_t)h * D + i]), sm.ap_k[i], dot);
+      dot = warp_sum(dot);
+      if (lane == 0) sm.ap_dot[h] = dot;
+    }
+  }
+  __syncthreads();
+  if (tid < D) {
+    float v = load_elem_f32(v_row, v_dtype, tid);
+    if (v_center) v -= v_center[(size_t)head * D + tid];
+    sm.ap_k[tid] = v;
+  }
+  __syncthreads();
+  quantise_row<D>(sm.ap_k, sm.apv_words, v_fwd, v_meta, v_thr, head, v_active);
+  __syncthreads();
+  const int page = sm.ap_page;
+  if (write && page >= 0) {
+    const int slot = pos % JQK_PAGE_TOKENS;
+    if (tid < k_words)
+      k_pool[(((size_t)page * n_heads + head) * k_wpr + tid) * JQK_PAGE_TOKENS + slot] = sm.ap_words[tid];
+    else if (tid >= 128 && tid < 128 + v_words)
+      v_pool[(((size_t)page * n_heads + head) * v_wpr + (tid - 128)) * JQK_PAGE_TOKENS + slot] = sm.apv_words[tid - 128];
+  }
+}
+
 // D = head_dim (64 or 128).  VQ: values are packed codes of a second compressor (v_pool is then the
 // uint32 code pool, `vs` its tables); the keys' tables then always come from the table kernel.
 template <int D, bool BUILD_IN_BLOCK, bool VQ, bool APPEND>
@@ -391,7 +473,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
               const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs, AppendSide ap) {
   static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
-  static_assert(!(VQ && APPEND), "the append variant writes a bf16 value pool");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -537,7 +618,21 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // the block whose split ends the context takes the appended row (every query block keeps its own
   // copy in shared memory; the first one also writes it to the tail page)
   int ap_pos = -1;
-  if constexpr (APPEND) {
+  if constexpr (APPEND && VQ) {
+    if (split == n_splits - 1) {
+      ap_pos = len - 1;
+      const HeadDesc vhd2 = load_desc(vs.desc, head);
+      const size_t k_esz = ap.k_dtype == JQK_DTYPE_F32 ? 4 : 2, v_esz = ap.v_dtype == JQK_DTYPE_F32 ? 4 : 2;
+      append_row_packed<D>(sm, tb.fwd_cols, tb.col_meta, tb.thresholds, tb.n_heads, tb.words_per_record, hd.n_active, hd.n_words,
+                           vs.fwd_cols, vs.col_meta, vs.thresholds, vs.center, vs.wpr, vhd2.n_active, vhd2.n_words,
+                           (const char*)ap.k + ((size_t)seq * ap.k_seq_stride + (size_t)head * ap.k_head_stride) * k_esz,
+                           (const char*)ap.v + ((size_t)seq * ap.v_seq_stride + (size_t)head * ap.v_head_stride) * v_esz,
+                           ap.k_dtype, ap.v_dtype, ap.k_pool, reinterpret_cast<uint32_t*>(ap.v_pool), head, seq, qb == 0, ap_pos,
+                           page_table, pt_stride, n_pages, status,
+                           ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group);
+    }
+  }
+  if constexpr (APPEND && !VQ) {
     if (split == n_splits - 1) {
       ap_pos = len - 1;
       const size_t k_esz = ap.k_dtype == JQK_DTYPE_F32 ? 4 : 2, v_esz = ap.v_dtype == JQK_DTYPE_F32 ? 4 : 2;
@@ -674,7 +769,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     landed = bar_wait(&sm.vfull[warp], r & 1) && landed;
     if (!landed && lane == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
-    if constexpr (APPEND) {
+    if constexpr (APPEND && !VQ) {
       if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {
         const int ts = (ap_pos - t0) & 15;
         unsigned char* vt = reinterpret_cast<unsigned char*>(st.v[(ap_pos - t0) >> 4]);
@@ -684,6 +779,14 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     // keys past the end of the split inside a page that is present: their V columns may hold
     // anything (stale or never written), and 0 x NaN must not reach the accumulators
+    if constexpr (VQ && APPEND) {
+      if (ap_pos >= t0 && ap_pos < t0 + TILE_TOK) {   // the appended value's codes from the block's own copy
+        const int slot = ap_pos - t0;
+        uint32_t* vd = reinterpret_cast<uint32_t*>(st.vq[slot >> 4]) + (slot & 15);
+        if (lane < (int)(vq_page_bytes / (JQK_PAGE_TOKENS * 4))) vd[lane * JQK_PAGE_TOKENS] = sm.apv_words[lane];
+        __syncwarp();
+      }
+    }
     if constexpr (VQ) {
       // dequantise this lane's key into the tile: column after column, code -> bf16 centroid -> the
       // key's slot of the column's row (dims-major, the layout the tensor-core product reads).  Keys
@@ -1088,12 +1191,12 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   cfg.stream = st;
   cfg.attrs = pdl_attr;
   cfg.numAttrs = 1;
-  ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0};
+  ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr};
   AppendSide ap{};
   if (append) ap = *append;
   if (v_tables)
     vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
-                   v_tables->n_heads, v_tables->words_per_record};
+                   v_tables->n_heads, v_tables->words_per_record, v_tables->fwd_cols, v_tables->thresholds};
 #define JQK_LAUNCH_DECODE(DIM, INB, VQQ, APP)                                                                         \
   do {                                                                                                                \
     cfg.dynamicSmemBytes = sizeof(DecodeSmemT<VQQ>);                                                                  \
@@ -1103,7 +1206,9 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
                                    k_pool, v_pool, out, out_dtype, ws, status, vs, ap),                               \
                 "decode launch");                                                                                     \
   } while (0)
-  if (v_tables) {
+  if (v_tables && append) {
+    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, true); else JQK_LAUNCH_DECODE(64, false, true, true);
+  } else if (v_tables) {
     if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false); else JQK_LAUNCH_DECODE(64, false, true, false);
   } else if (append) {
     if (tables->d == 128) {
@@ -1146,14 +1251,13 @@ extern "C" int32_t jqk_decode_attend_packed_values(const jqk_head_tables* tables
 // One step of a generate loop in one launch: the newest key and value row of every sequence go to
 // position seq_lens[s] of its cache (compressed exactly as jqk_compress_paged would), the step
 // attends over seq_lens[s] + 1 keys, and seq_lens is advanced by one when the launch is done.
-extern "C" int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, const void* new_k,
-                                            const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
-                                            int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride,
-                                            int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
-                                            int32_t tokens_per_split, const int32_t* page_table,
-                                            int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
-                                            void* out, int32_t out_dtype, int32_t flags, void* workspace,
-                                            size_t workspace_bytes, int32_t* status, void* stream) {
+static int32_t append_attend(const jqk_head_tables* tables, const jqk_head_tables* v_tables, const void* q,
+                             const void* new_k, const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
+                             int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride, int32_t n_seqs,
+                             int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len, int32_t tokens_per_split,
+                             const int32_t* page_table, int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool,
+                             void* v_pool, void* out, int32_t out_dtype, int32_t flags, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
   if (!new_k || !new_v) return fail(JQK_E_ARG, "null new_k or new_v");
@@ -1165,9 +1269,37 @@ extern "C" int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const
   AppendSide ap{new_k, new_v, k_dtype, v_dtype, (long long)k_seq_stride, (long long)k_head_stride, (long long)v_seq_stride,
                 (long long)v_head_stride, k_pool, (__nv_bfloat16*)v_pool, seq_lens, n_seqs,
                 (flags & JQK_APPEND_OWN_KEY_EXACT) ? 1 : 0};
-  return decode_launch(tables, nullptr, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+  return decode_launch(tables, v_tables, q, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
                        page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, workspace, workspace_bytes, status,
                        stream, &ap);
+}
+
+extern "C" int32_t jqk_decode_append_attend(const jqk_head_tables* tables, const void* q, const void* new_k,
+                                            const void* new_v, int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride,
+                                            int64_t k_head_stride, int64_t v_seq_stride, int64_t v_head_stride,
+                                            int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
+                                            int32_t tokens_per_split, const int32_t* page_table,
+                                            int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool, void* v_pool,
+                                            void* out, int32_t out_dtype, int32_t flags, void* workspace,
+                                            size_t workspace_bytes, int32_t* status, void* stream) {
+  return append_attend(tables, nullptr, q, new_k, new_v, k_dtype, v_dtype, k_seq_stride, k_head_stride, v_seq_stride,
+                       v_head_stride, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                       page_table_stride, n_pages, k_pool, v_pool, out, out_dtype, flags, workspace, workspace_bytes, status,
+                       stream);
+}
+
+extern "C" int32_t jqk_decode_append_attend_packed_values(
+    const jqk_head_tables* tables, const jqk_head_tables* v_tables, const void* q, const void* new_k, const void* new_v,
+    int32_t k_dtype, int32_t v_dtype, int64_t k_seq_stride, int64_t k_head_stride, int64_t v_seq_stride,
+    int64_t v_head_stride, int32_t n_seqs, int32_t n_q_heads, int32_t* seq_lens, int32_t max_seq_len,
+    int32_t tokens_per_split, const int32_t* page_table, int32_t page_table_stride, int32_t n_pages, uint32_t* k_pool,
+    uint32_t* v_code_pool, void* out, int32_t out_dtype, int32_t flags, void* workspace, size_t workspace_bytes,
+    int32_t* status, void* stream) {
+  if (!v_tables) return fail(JQK_E_ARG, "null value tables");
+  return append_attend(tables, v_tables, q, new_k, new_v, k_dtype, v_dtype, k_seq_stride, k_head_stride, v_seq_stride,
+                       v_head_stride, n_seqs, n_q_heads, seq_lens, max_seq_len, tokens_per_split, page_table,
+                       page_table_stride, n_pages, k_pool, v_code_pool, out, out_dtype, flags, workspace, workspace_bytes,
+                       status, stream);
 }
 
 extern "C" int32_t jqk_decode_attend_host(const jqk_head_tables* tables, const void* q_host, void* q_pinned,

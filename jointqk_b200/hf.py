@@ -99,8 +99,7 @@ def paged_attention_forward(module, query, key, value, attention_mask, dropout: 
         raise NotImplementedError("the packed decode scores with 1/sqrt(head_dim)")
     k_new, v_new = pending
     q = query[:, :, 0].to(torch.bfloat16).contiguous()
-    # (B, Hq, d) fp32; one launch with bf16 values, the separate launches with packed values
-    out = layer.paged.generate_step(k_new, v_new, q, own_key_exact=OWN_KEY_EXACT and layer.v_tables is None)
+    out = layer.paged.generate_step(k_new, v_new, q, own_key_exact=OWN_KEY_EXACT)   # (B, Hq, d) fp32, one launch
     return out.to(query.dtype).unsqueeze(1), None
 
 
@@ -205,9 +204,9 @@ def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_preci
     basis, water-fill at ``k_bits`` average, at most 4 bits per coordinate), attach a packed cache
     layer to every attention module and return the ``Cache`` to pass as ``past_key_values``.
     ``v_bits``: values are packed as well (eigenbasis of Cov[V], water-fill, mean-centred: the
-    reference's ``v_eigen_waterfill``); the moments must then have been taken ``with_values``.  A
-    decode step then takes the separate append and attend launches, and the new token's key and
-    value are compressed before it attends (the reference compresses them after)."""
+    reference's ``v_eigen_waterfill``); the moments must then have been taken ``with_values``.  The
+    new token's value is then read from its codes in its own step already (the reference compresses
+    it after that step); its key follows ``OWN_KEY_EXACT`` as with bf16 values."""
     cache_utils, _, _, _ = _transformers()
     set_attention(model)
     layer_cls = make_paged_layer_class()

@@ -261,16 +261,17 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
 def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                          seq_lens: torch.Tensor, max_seq_len: int, page_table: torch.Tensor, k_pool: torch.Tensor,
                          v_pool: torch.Tensor, out: torch.Tensor, workspace: DecodeWorkspace, status: torch.Tensor,
-                         tokens_per_split: int = 0, own_key_exact: bool = False) -> torch.Tensor:
+                         tokens_per_split: int = 0, own_key_exact: bool = False,
+                         v_tables: HeadTables | None = None) -> torch.Tensor:
     """One generate step in one launch: the rows k_new / v_new (n_seqs, H, 1, d) or (n_seqs, H, d) go
     to position ``seq_lens[s]`` of every sequence (pages already in the table), the step attends
     over ``seq_lens[s] + 1`` keys (``max_seq_len`` covers that) and ``seq_lens`` is advanced on the
-    device.  bf16 value pool only.  ``own_key_exact``: the new key is scored from its exact values in
+    device.  With ``v_tables`` the value row is packed as well.  ``own_key_exact``: the new key is scored from its exact values in
     this step (and from its codes afterwards), the semantics of the reference's Mode B."""
     if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
-    if v_pool.dtype != torch.bfloat16:
-        raise ValueError("the fused append writes a bf16 value pool")
+    if v_pool.dtype != (torch.bfloat16 if v_tables is None else torch.int32):
+        raise ValueError("the value pool is bf16, or int32 storage of packed codes when v_tables is given")
     if out.shape != q.shape or not out.is_contiguous():
         raise ValueError("out must be contiguous with the shape of q")
     if k_new.dim() == 4:
@@ -287,8 +288,10 @@ def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tenso
         raise ValueError("rows must be contiguous in their last dimension")
     if seq_lens.dtype != torch.int32:
         raise ValueError("seq_lens must be int32")
-    _native.check(_native.lib.jqk_decode_append_attend(
-        tables.ref, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), _native.torch_dtype_code(k_new.dtype),
+    fn = _native.lib.jqk_decode_append_attend if v_tables is None else _native.lib.jqk_decode_append_attend_packed_values
+    head = (tables.ref,) if v_tables is None else (tables.ref, v_tables.ref)
+    _native.check(fn(
+        *head, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), _native.torch_dtype_code(k_new.dtype),
         _native.torch_dtype_code(v_new.dtype), k_new.stride(0), k_new.stride(1), v_new.stride(0), v_new.stride(1), n, q.shape[1], seq_lens.data_ptr(),
         int(max_seq_len), int(tokens_per_split), page_table.data_ptr(), page_table.stride(0), int(k_pool.shape[0]),
         k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), _native.torch_dtype_code(out.dtype),
@@ -471,10 +474,9 @@ class PagedKVCache:
     def generate_step(self, k_new: torch.Tensor, v_new: torch.Tensor, q: torch.Tensor,
                       fused_append: bool = True, own_key_exact: bool = False) -> torch.Tensor:
         """One step of a generate loop: append the newest token of every sequence (K compress, V store,
-        lengths advanced on the device), then attend.  With a bf16 value pool that is one kernel
-        launch, which reads the rows in place (``jqk_decode_append_attend``).  ``fused_append=False``,
-        and always with packed values: the separate compress, store, length and decode launches,
-        replayed as one CUDA graph.  ``own_key_exact`` (fused launch only): the new key attends with
+        lengths advanced on the device), then attend.  That is one kernel launch, which reads the rows
+        in place (``jqk_decode_append_attend``, or its packed-values form).  ``fused_append=False``:
+        the separate compress, store, length and decode launches, replayed as one CUDA graph.  ``own_key_exact`` (fused launch only): the new key attends with
         its exact values in this step, as in the reference's Mode B.
 
         k_new / v_new (n_seqs, H, 1, d), q bf16 (n_seqs, Hq, d); the result is a device tensor that
@@ -495,7 +497,7 @@ class PagedKVCache:
                 and gs["shape"] == (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) and q.is_contiguous()):
             self._gen_budget -= 1
             decode_append_attend(self.tables, q, k_new, v_new, self.seq_lens, gs["covered"], self.page_table, self.k_pool,
-                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"], own_key_exact)
+                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"], own_key_exact, self.v_tables)
             for s_ in range(n):
                 self.lengths[s_] += 1
             self._epoch += 1
@@ -504,12 +506,12 @@ class PagedKVCache:
         if k_new.shape[0] != n or k_new.shape[2] != 1:
             raise ValueError(f"generate_step takes one token for each of the {n} sequences")
         for s_ in range(n):   # pages a few steps ahead, so that the host touches the table once in a while only
-            self.reserve(s_, self.lengths[s_] + (self.RESERVE_AHEAD if fused_append and self.v_tables is None else 1))
+            self.reserve(s_, self.lengths[s_] + (self.RESERVE_AHEAD if fused_append else 1))
         gs = getattr(self, "_gen_step", None)
         new_max = max(self.lengths) + 1
-        fused = self.v_tables is None and bool(fused_append)
+        fused = bool(fused_append)
         if own_key_exact and not fused:
-            raise ValueError("own_key_exact needs the fused append launch (bf16 values, fused_append=True)")
+            raise ValueError("own_key_exact needs the fused append launch (fused_append=True)")
         if (gs is None or gs["generation"] != self.pool.generation or gs["table_ptr"] != self.page_table.data_ptr()
                 or gs["shape"] != (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) or new_max > gs["covered"]
                 or gs["fused"] != fused):
@@ -552,7 +554,7 @@ class PagedKVCache:
             # attends and advances the lengths; there is nothing to stage and nothing to capture
             decode_append_attend(self.tables, q if q.is_contiguous() else q.contiguous(), k_new, v_new, self.seq_lens,
                                  gs["covered"], self.page_table, self.k_pool, self.v_pool, gs["out"], gs["ws"],
-                                 self.status, gs["tps"], own_key_exact)
+                                 self.status, gs["tps"], own_key_exact, self.v_tables)
         else:
             gs["k"].copy_(k_new, non_blocking=True)
             gs["v"].copy_(v_new, non_blocking=True)

@@ -134,3 +134,36 @@ def test_decode_from_host_buffers_with_packed_values():
     with pytest.raises(NotImplementedError):
         cache.decode_host(q, use_graph=False)
     paged.check_status(cache.status)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_append_with_packed_values_equals_the_separate_launches(dtype):
+    """jqk_decode_append_attend_packed_values against the graph of compress (K), compress (V, centred),
+    length and decode launches: same outputs, same key and value codes in the pages, same lengths,
+    over ragged sequences that cross page and split boundaries."""
+    keys, vals, comps, v_comps, tables, v_tables = _setup(2, 4096, 2.0, 3)
+    n0, steps = [370, 29, 1], 50
+    total = max(n0) + steps
+    g = torch.Generator().manual_seed(11)
+    kk = torch.stack([keys[:, :total].roll(5 * s, 1) for s in range(3)]).cuda()
+    vv = torch.stack([vals[:, :total].roll(9 * s, 1) for s in range(3)]).to(torch.bfloat16).cuda()
+    qs = torch.randn(steps, 3, 8, 128, generator=g).to(torch.bfloat16).cuda()
+    caches = [paged.PagedKVCache(tables, [n + steps for n in n0], v_tables=v_tables) for _ in range(2)]
+    for c in caches:
+        c.prefill(kk[:, :, :max(n0)], vv[:, :, :max(n0)], lengths=n0)
+    for i in range(steps):
+        kn = torch.stack([kk[s, :, n0[s] + i] for s in range(3)]).to(dtype).unsqueeze(2)
+        vn = torch.stack([vv[s, :, n0[s] + i] for s in range(3)]).to(dtype).unsqueeze(2)
+        got = caches[0].generate_step(kn, vn, qs[i]).clone()
+        want = caches[1].generate_step(kn, vn, qs[i], fused_append=False)
+        assert torch.equal(got, want), f"step {i}: {(got - want).abs().max().item()}"
+    a, b = caches
+    assert a._gen_step["fused"] and not b._gen_step["fused"]
+    assert a.seq_lens.tolist() == b.seq_lens.tolist() == a.lengths == [n + steps for n in n0]
+    for s in range(3):
+        for t, pool in ((tables, "k_pool"), (v_tables, "v_pool")):
+            pk = [paged.PackedKeys(t, getattr(c, pool), c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
+                  for c in caches]
+            assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])), (s, pool)
+    for c in caches:
+        paged.check_status(c.status)
