@@ -68,9 +68,31 @@ def test_decode_over_random_shapes():
     print(f"decode over 60 random shapes: worst relative error {worst:.2e}")
 
 
-def test_fused_generate_step_over_random_shapes():
-    rng = random.Random(7)
-    for it in range(40):
+_V_TABLES = {}
+
+
+def _v_tables(H):
+    """Value-side tables (eigenbasis of the covariance, 3 bits, mean-centred) for H heads."""
+    if H not in _V_TABLES:
+        from jointqk_b200.synthetic import second_moment
+
+        g = torch.Generator().manual_seed(40 + H)
+        vals = torch.stack([spectrum_keys(4096, config_seed(0, 60, h), n_outliers=0) for h in range(H)]) \
+            + 0.3 * torch.randn(H, 1, 128, generator=g)
+        comps = []
+        for h in range(H):
+            mu = vals[h].double().mean(0).float()
+            comps.append(jq.build_v_compressor("v_eigen_waterfill", cov_v_for_head=second_moment(vals[h]) - torch.outer(mu, mu),
+                                               head_dim=128, bits=3, seed=42 + h, mu_v_for_head=mu, max_bits=4))
+        _V_TABLES[H] = jq.HeadTables.from_compressors([c.inner for c in comps], device="cuda",
+                                                      center=torch.stack([c.mu for c in comps]))
+    return _V_TABLES[H]
+
+
+@pytest.mark.parametrize("packed_values", [False, True])
+def test_fused_generate_step_over_random_shapes(packed_values):
+    rng = random.Random(7 + packed_values)
+    for it in range(20 if packed_values else 40):
         H, g = rng.choice([1, 2, 4]), rng.choice([1, 2, 4, 8])
         b = rng.choice([1.0, 2.0, 2.5, 3.0, 4.0])
         n0 = [rng.choice(EDGE_LENGTHS + [rng.randint(2, 3000)]) for _ in range(rng.randint(1, 4))]
@@ -81,8 +103,9 @@ def test_fused_generate_step_over_random_shapes():
         gen = torch.Generator().manual_seed(it)
         kk = torch.stack([keys[:, :total].roll(3 * s, 1) for s in range(len(n0))]).cuda()
         v = torch.randn(len(n0), H, total, 128, generator=gen).to(torch.bfloat16).cuda()
-        fused = paged.PagedKVCache(tables, n_seqs=len(n0), initial_pages=rng.choice([1, 8, 64]))   # has to grow
-        plain = paged.PagedKVCache(tables, n_seqs=len(n0))
+        vt = _v_tables(H) if packed_values else None
+        fused = paged.PagedKVCache(tables, n_seqs=len(n0), initial_pages=rng.choice([1, 8, 64]), v_tables=vt)   # has to grow
+        plain = paged.PagedKVCache(tables, n_seqs=len(n0), v_tables=vt)
         for cache in (fused, plain):
             if max(n0) > 0:
                 cache.prefill(kk[:, :, :max(n0)], v[:, :, :max(n0)], lengths=n0)
@@ -97,9 +120,10 @@ def test_fused_generate_step_over_random_shapes():
             assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item(), (it, i)
         assert fused.seq_lens.tolist() == fused.lengths == plain.lengths == [n + steps for n in n0]
         for s in range(len(n0)):
-            pk = [paged.PackedKeys(c.tables, c.k_pool, c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
-                  for c in (fused, plain)]
-            assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])), (it, s)
+            for t, pool in ((tables, "k_pool"),) + (((vt, "v_pool"),) if packed_values else ()):
+                pk = [paged.PackedKeys(t, getattr(c, pool), c.page_table[s:s + 1], c.seq_lens[s:s + 1], [c.lengths[s]], c.status)
+                      for c in (fused, plain)]
+                assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1])), (it, s, pool)
         paged.check_status(fused.status)
         paged.check_status(plain.status)
 
