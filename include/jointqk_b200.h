@@ -38,6 +38,7 @@ extern "C" {
 #define JQK_MAX_DIM 128        /* head_dim: multiple of 16, at most 128 */
 #define JQK_MAX_COLS 128       /* coordinates that carry >0 bits, padded to 16 */
 #define JQK_MAX_WORDS 16       /* uint32 words per record */
+#define JQK_MAX_WIDE 16        /* columns of 5..8 bits per head */
 #define JQK_MAX_TABLES 208     /* lookups per record (see jqk_head_tables.table_fields) */
 #define JQK_DESC_INTS 32       /* int32 per head in jqk_head_tables.desc */
 #define JQK_MAX_GROUP 4        /* q heads scored together by one thread block */
@@ -84,6 +85,13 @@ extern "C" {
  *   center_cols   float [H][128] or NULL: center @ (the scaled basis that fwd_limbs holds), column c;
  *                 with it the tensor-core compress kernel serves centred tables as well (it
  *                 transforms the raw rows and subtracts this constant from every column)
+ *   wide_thr / wide_cb  float [H][JQK_MAX_WIDE][256] or NULL: decision thresholds (+inf padded) and levels
+ *                 of the columns that carry 5..8 bits (what the reference's cap of 8 gives outlier
+ *                 channels, per_coord_quantization.py:365-379); such a column takes one byte of the
+ *                 record, its rows here are indexed by column - desc[30] (desc[31] = how many).  They
+ *                 are written, read back and reconstructed by jqk_compress_paged / jqk_decompress_paged
+ *                 / jqk_unpack_codes on the CUDA cores; the score and decode entry points, whose lookup
+ *                 tables cover 0..4 bits, return JQK_E_UNSUPPORTED for tables with n_wide > 0
  *   unit_pre      uint8 [4][128], unit_thr float [4][16] (HOST values, +inf padded), unit_aff float [2]
  *                 (HOST): the shared coarse-to-exact quantiser of the tensor-core kernel for widths
  *                 1..4: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes 2^23),
@@ -93,7 +101,7 @@ typedef struct jqk_head_tables {
   int32_t n_heads;
   int32_t d;
   int32_t words_per_record; /* K pool stride in words: max n_words over the heads */
-  int32_t reserved;
+  int32_t n_wide;           /* largest number of 5..8-bit columns of a head (0: every code has at most 4 bits) */
   const int32_t* desc;
   const int32_t* col_meta;
   const int32_t* table_fields;
@@ -108,6 +116,8 @@ typedef struct jqk_head_tables {
   const float* center_cols;
   float unit_thr[64];
   float unit_aff[2];
+  const float* wide_thr;
+  const float* wide_cb;
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */

@@ -21,7 +21,7 @@ class JqkHeadTables(C.Structure):
         ("n_heads", C.c_int32),
         ("d", C.c_int32),
         ("words_per_record", C.c_int32),
-        ("reserved", C.c_int32),
+        ("n_wide", C.c_int32),
         ("desc", C.c_void_p),
         ("col_meta", C.c_void_p),
         ("table_fields", C.c_void_p),
@@ -36,6 +36,8 @@ class JqkHeadTables(C.Structure):
         ("center_cols", C.c_void_p),
         ("unit_thr", C.c_float * 64),
         ("unit_aff", C.c_float * 2),
+        ("wide_thr", C.c_void_p),
+        ("wide_cb", C.c_void_p),
     ]
 
 

@@ -65,7 +65,18 @@ class PerCoordCompressor:
 
     @property
     def packable(self) -> bool:
-        """True when every coordinate carries at most 4 bits, i.e. the packed GPU format can store it."""
+        """True when the packed GPU format can store the codes: at most 8 bits per coordinate and at
+        most 16 coordinates above 4 bits (those take a byte each).  The reference's default cap of 8
+        (per_coord_quantization.py:367) fits."""
+        if not self.bits_int.numel():
+            return True
+        return int(self.bits_int.max()) <= 8 and int((self.bits_int > 4).sum()) <= 16
+
+    @property
+    def decodable(self) -> bool:
+        """True when the decode and score kernels can read the codes through their lookup tables: at
+        most 4 bits per coordinate.  Wider allocations compress, unpack and reconstruct on the GPU and
+        are scored from their reconstruction; packed decode attention needs ``max_bits=4``."""
         return int(self.bits_int.max()) <= 4 if self.bits_int.numel() else True
 
     def _build_codebooks(self) -> None:
@@ -103,10 +114,10 @@ class PerCoordCompressor:
         dev = _cuda_device(device)
         if not self.packable:
             raise ValueError(
-                f"this compressor gives a coordinate {int(self.bits_int.max())} bits; the packed GPU format stores "
-                "0..4 bits per coordinate.  Fit it with max_bits=4 (PerCoordCompressor.fit(..., max_bits=4) or "
-                "build_method_compressor(..., max_bits=4)); that is a different allocation from the reference's "
-                "cap of 8 and costs retrieval quality where outlier channels want more than 4 bits")
+                f"this compressor gives a coordinate {int(self.bits_int.max())} bits and "
+                f"{int((self.bits_int > 4).sum())} coordinates more than 4; the packed GPU format stores 0..8 bits per "
+                "coordinate with at most 16 coordinates above 4 bits.  Fit it with a lower cap "
+                "(PerCoordCompressor.fit(..., max_bits=...) or build_method_compressor(..., max_bits=...))")
         if self._tables is None or self._tables.device != dev:
             self._tables = HeadTables.from_compressors([self], device=dev)
         return self._tables

@@ -18,6 +18,15 @@ int32_t check_tables(const jqk_head_tables* t) {
   if (!t->desc || !t->col_meta || !t->table_fields || !t->fwd_cols || !t->thresholds || !t->cb_cols ||
       !t->qproj_cols || !t->inv_rows)
     return fail(JQK_E_ARG, "head tables hold a null pointer");
+  if (t->n_wide < 0 || t->n_wide > JQK_MAX_WIDE) return fail(JQK_E_LAYOUT, "n_wide %d outside 0..%d", t->n_wide, JQK_MAX_WIDE);
+  if (t->n_wide > 0 && (!t->wide_thr || !t->wide_cb)) return fail(JQK_E_ARG, "tables with wide columns need wide_thr and wide_cb");
+  return 0;
+}
+
+// The lookup tables of the score and decode kernels cover 0..4 bits per coordinate.
+int32_t check_narrow(const jqk_head_tables* t, const char* what) {
+  if (t && t->n_wide > 0)
+    return fail(JQK_E_UNSUPPORTED, "%s takes tables with at most 4 bits per coordinate; these hold %d wider column(s)", what, t->n_wide);
   return 0;
 }
 

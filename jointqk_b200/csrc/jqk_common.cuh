@@ -52,12 +52,14 @@ inline int32_t cuda_fail(cudaError_t e, const char* what) {
 
 // Validates the table struct against the limits the kernels are written for.
 int32_t check_tables(const jqk_head_tables* t);
+int32_t check_narrow(const jqk_head_tables* t, const char* what);
 
 // ---------------------------------------------------------------------------------------
 // Device helpers
 // ---------------------------------------------------------------------------------------
 struct HeadDesc {
   int d, n_cols, n_active, n_words, n_a_words, n_c_words, n_tables, payload_bits;
+  int wide_first, n_wide;   // columns of 5..8 bits: wide_first .. wide_first + n_wide - 1
 };
 
 __device__ __forceinline__ HeadDesc load_desc(const int32_t* desc, int head) {
@@ -65,6 +67,7 @@ __device__ __forceinline__ HeadDesc load_desc(const int32_t* desc, int head) {
   HeadDesc h;
   h.d = p[0]; h.n_cols = p[1]; h.n_active = p[2]; h.n_words = p[3];
   h.n_a_words = p[4]; h.n_c_words = p[5]; h.n_tables = p[6]; h.payload_bits = p[7];
+  h.wide_first = p[30]; h.n_wide = p[31];
   return h;
 }
 
@@ -95,6 +98,22 @@ __device__ __forceinline__ int lookup_page(const int32_t* page_table, int pt_str
     return -1;
   }
   return p;
+}
+
+// code = #{l : x >= thr[l]} over the 2^width - 1 sorted thresholds of a column.  Narrow columns
+// (width <= 4) count through their 16-entry row; a wide column (5..8 bits) searches its 256-entry
+// row, which gives the same count in 8 steps.
+__device__ __forceinline__ uint32_t threshold_code(float x, int width, const float* __restrict__ narrow_row,
+                                                   const float* __restrict__ wide_row) {
+  uint32_t code = 0;
+  if (width <= 4) {
+    const int n_thr = (1 << width) - 1;
+    for (int l = 0; l < n_thr; ++l) code += (x >= narrow_row[l]) ? 1u : 0u;
+  } else {
+    for (int step = (1 << width) >> 1; step >= 1; step >>= 1)
+      code += (x >= wide_row[code + step - 1]) ? (uint32_t)step : 0u;
+  }
+  return code;
 }
 
 __device__ __forceinline__ float warp_max(float v) {

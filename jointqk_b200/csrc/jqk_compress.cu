@@ -137,10 +137,8 @@ compress_simt_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t se
       const int m = meta[c];
       const int width = meta_width(m);
       const float x = xs[t * XS_STRIDE + c];
-      const float* th = thr + c * 16;
-      const int n_thr = (1 << width) - 1;
-      uint32_t code = 0;
-      for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+      const float* wide_row = width > 4 ? tb.wide_thr + ((size_t)head * JQK_MAX_WIDE + (c - hd.wide_first)) * 256 : nullptr;
+      const uint32_t code = threshold_code(x, width, thr + c * 16, wide_row);
       word |= code << (meta_bitpos(m) - 32 * w);
     }
     const int tok = seq_start + t0 + t;
@@ -183,10 +181,9 @@ compress_token_kernel(jqk_head_tables tb, const KT* __restrict__ keys, int64_t s
 #pragma unroll 8
     for (int i = 0; i < d; ++i) x = fmaf(krow[i], __ldg(w + (size_t)i * 128), x);
     const int m = tb.col_meta[(size_t)head * 128 + tid];
-    const float* th = tb.thresholds + ((size_t)head * 128 + tid) * 16;
-    const int n_thr = (1 << meta_width(m)) - 1;
-    uint32_t code = 0;
-    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const int width = meta_width(m);
+    const float* wide_row = width > 4 ? tb.wide_thr + ((size_t)head * JQK_MAX_WIDE + (tid - hd.wide_first)) * 256 : nullptr;
+    const uint32_t code = threshold_code(x, width, tb.thresholds + ((size_t)head * 128 + tid) * 16, wide_row);
     const int bp = meta_bitpos(m);
     atomicOr(&words[bp >> 5], code << (bp & 31));
   }
@@ -232,7 +229,9 @@ decompress_simt_kernel(jqk_head_tables tb, PagedArgs pa, const uint32_t* __restr
       const int page = lookup_page(pa.page_table, pa.pt_stride, seq, tok / JQK_PAGE_TOKENS, pa.n_pages, pa.status);
       if (page >= 0) {
         const size_t rec = ((size_t)page * tb.n_heads + head) * wpr * JQK_PAGE_TOKENS;
-        v = cb[c * 16 + fetch_code(k_pool, rec, tok % JQK_PAGE_TOKENS, meta[c])];
+        const uint32_t code = fetch_code(k_pool, rec, tok % JQK_PAGE_TOKENS, meta[c]);
+        v = meta_width(meta[c]) > 4 ? tb.wide_cb[((size_t)head * JQK_MAX_WIDE + (c - hd.wide_first)) * 256 + code]
+                                    : cb[c * 16 + code];
       }
     }
     xs[t * XS_STRIDE + c] = v;

@@ -648,7 +648,7 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
                             const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
                             const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
                             uint32_t* k_pool, int32_t* status, cudaStream_t st) {
-  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || (tables->center && !tables->center_cols)) return 1;
+  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || tables->n_wide > 0 || (tables->center && !tables->center_cols)) return 1;
   if ((uintptr_t)keys % 16 || (token_stride * 2) % 16 || (head_stride * 2) % 16 || (seq_stride * 2) % 16) return 1;
   if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE || !tables->unit_pre) return 1;
   CUtensorMap key_map, limb_map;

@@ -1106,6 +1106,7 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_
                                    float* scores, int32_t* status, void* stream) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
+  if ((rc = check_narrow(tables, "jqk_score_paged"))) return rc;
   if (n_seqs < 0 || n_queries < 0 || max_tokens < 0) return fail(JQK_E_ARG, "negative size");
   if (n_seqs == 0 || n_queries == 0 || max_tokens == 0) return 0;
   if (!q || !seq_lens || !page_table || !k_pool || !scores) return fail(JQK_E_ARG, "null pointer argument");
@@ -1133,9 +1134,11 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
                              size_t workspace_bytes, int32_t* status, void* stream, const AppendSide* append = nullptr) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
+  if ((rc = check_narrow(tables, "decode attention"))) return rc;
   if (v_tables) {
     rc = check_tables(v_tables);
     if (rc) return rc;
+    if ((rc = check_narrow(v_tables, "decode attention over packed values"))) return rc;
     if (v_tables->n_heads != tables->n_heads || v_tables->d != tables->d)
       return fail(JQK_E_LAYOUT, "key and value tables disagree on heads or head_dim");
   }

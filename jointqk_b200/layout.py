@@ -42,7 +42,9 @@ from dataclasses import dataclass, field
 import numpy as np
 
 PAGE_TOKENS = 16
-MAX_CODE_BITS = 4
+MAX_CODE_BITS = 4       # widths the lookup tables of the decode kernels take
+MAX_STORED_BITS = 8     # widths a record can hold: 5..8-bit codes take a byte each ("wide" columns)
+MAX_WIDE = 16           # wide columns per head
 MAX_WORDS = 16          # 128 coordinates x 4 bits
 MAX_TABLES = 208        # (MAX_WORDS + 1 shared word) * 12 rounded up to a multiple of 8
 TABLE_FIELDS = 4        # a lookup combines at most four coordinates (1,1,1,1)
@@ -68,6 +70,8 @@ class KeyLayout:
     payload_bits: int                # sum of bits
     waste_bits: int                  # pad bits inside slots / bytes (not word rounding)
     word_col_begin: np.ndarray = field(default=None)  # (n_words + 1,) first column of each word
+    n_wide: int = 0                  # columns of 5..8 bits, one byte each, in whole words between the A and C regions
+    wide_first: int = 0              # column index of the first of them
 
     @property
     def record_bytes(self) -> int:
@@ -85,15 +89,23 @@ class KeyLayout:
 
 
 def plan_key_layout(bits) -> KeyLayout:
-    """Compose slots and bytes from a per-coordinate bit allocation (values 0..4)."""
+    """Compose slots and bytes from a per-coordinate bit allocation (values 0..8).
+
+    Coordinates of 5..8 bits ("wide", what the reference's cap of 8 gives outlier channels,
+    per_coord_quantization.py:365-379) take one byte each, four to a word, in whole words between
+    the A region and the C region; the two regions then share no word.  Such a record can be
+    written, read back and reconstructed; the decode kernels' lookup tables cover 0..4 bits only."""
     bits = np.asarray(bits).astype(np.int64).reshape(-1)
     d = int(bits.shape[0])
     if d % 16 != 0 or d > 128:
         raise ValueError(f"head_dim must be a multiple of 16 and at most 128, got {d}")
-    if bits.min() < 0 or bits.max() > MAX_CODE_BITS:
+    if bits.min() < 0 or bits.max() > MAX_STORED_BITS:
         raise ValueError(
-            f"the packed GPU path stores 0..{MAX_CODE_BITS} bits per coordinate, got range "
+            f"the packed GPU path stores 0..{MAX_STORED_BITS} bits per coordinate, got range "
             f"[{int(bits.min())}, {int(bits.max())}]")
+    wide = [int(j) for j in np.nonzero(bits > MAX_CODE_BITS)[0]]
+    if len(wide) > MAX_WIDE:
+        raise ValueError(f"{len(wide)} coordinates carry more than {MAX_CODE_BITS} bits; a record holds at most {MAX_WIDE} such")
     by_width = {w: [int(j) for j in np.nonzero(bits == w)[0]] for w in (1, 2, 3, 4)}
     l4, l3, l2, l1 = by_width[4], by_width[3], by_width[2], by_width[1]
 
@@ -127,11 +139,12 @@ def plan_key_layout(bits) -> KeyLayout:
         a_slots.append(slot)
 
     n_a, n_c = len(a_slots), len(c_bytes)
-    n_words = max(1, -(-(4 * n_a + 8 * n_c) // 32))
-    if n_words > MAX_WORDS:
-        raise ValueError("record exceeds 16 words")
     n_a_words = -(-n_a // 8)
     n_c_words = -(-n_c // 4)
+    n_w_words = -(-len(wide) // 4)
+    n_words = max(1, -(-(4 * n_a + 8 * n_c) // 32)) if not wide else n_a_words + n_w_words + n_c_words
+    if n_words > MAX_WORDS:
+        raise ValueError("record exceeds 16 words")
     n_tables = 8 * n_a_words + 12 * n_c_words
     rec_bytes = 4 * n_words
 
@@ -143,6 +156,9 @@ def plan_key_layout(bits) -> KeyLayout:
             table_fields[s, f] = len(cols) | (w << 8) | (shift << 12)
             cols.append((j, w, 4 * s + shift))
             shift += w
+    wide_first = len(cols)
+    for i, j in enumerate(wide):                       # one byte each, from the first word after the A region
+        cols.append((j, int(bits[j]), 32 * n_a_words + 8 * i))
     for i in range(n_c - 1, -1, -1):                   # ascending physical byte
         phys_byte = rec_bytes - 1 - i
         iw, pb = (n_words - 1) - phys_byte // 4, phys_byte % 4
@@ -172,10 +188,11 @@ def plan_key_layout(bits) -> KeyLayout:
         d=d, bits=bits.astype(np.int32), n_cols=n_cols, n_active=n_active, col_coord=col_coord,
         col_width=col_width, col_bitpos=col_bitpos, n_words=n_words, n_a_words=n_a_words,
         n_c_words=n_c_words, n_tables=n_tables, table_fields=table_fields[:max(n_tables, 1)],
-        payload_bits=payload, waste_bits=4 * n_a + 8 * n_c - payload, word_col_begin=word_col_begin)
+        payload_bits=payload, waste_bits=4 * n_a + 8 * n_c + 8 * len(wide) - payload, word_col_begin=word_col_begin,
+        n_wide=len(wide), wide_first=wide_first)
 
 
-def decision_thresholds(codebook_rows: np.ndarray, widths: np.ndarray) -> np.ndarray:
+def decision_thresholds(codebook_rows: np.ndarray, widths: np.ndarray, max_levels: int = 16) -> np.ndarray:
     """Exact fp32 decision thresholds of the reference's nearest-centroid rule.
 
     The reference picks ``argmin_l |x - cb[l]|`` in fp32 with the first index winning ties
@@ -186,18 +203,20 @@ def decision_thresholds(codebook_rows: np.ndarray, widths: np.ndarray) -> np.nda
     makes ``code = #{l : x >= thr[l]}`` reproduce the reference code for every finite ``x``
     whose distances to the centroids are distinguishable in fp32.
 
-    ``codebook_rows``: (n, 16) fp32 ascending centroids (unused tail arbitrary);
-    ``widths``: (n,) code widths.  Returns (n, 15) fp32, unused entries ``+inf``.
+    ``codebook_rows``: (n, L) fp32 ascending centroids (unused tail arbitrary), L = ``max_levels``
+    (16, or 256 for the wide columns); ``widths``: (n,) code widths.  Returns (n, L - 1) fp32,
+    unused entries ``+inf``.
     """
+    L = int(max_levels)
     cb = np.asarray(codebook_rows, dtype=np.float32)
     widths = np.asarray(widths).astype(np.int64).reshape(-1)
     n = cb.shape[0]
     levels = (1 << widths)[:, None]                           # (n, 1)
-    valid = np.arange(15)[None, :] < (levels - 1)             # (n, 15)
-    if cb.shape[1] < 16:
-        cb = np.concatenate([cb, np.zeros((n, 16 - cb.shape[1]), np.float32)], axis=1)
-    a = np.where(valid, cb[:, :15], np.float32(0.0)).astype(np.float32)
-    b = np.where(valid, cb[:, 1:16], np.float32(1.0)).astype(np.float32)
+    valid = np.arange(L - 1)[None, :] < (levels - 1)          # (n, L - 1)
+    if cb.shape[1] < L:
+        cb = np.concatenate([cb, np.zeros((n, L - cb.shape[1]), np.float32)], axis=1)
+    a = np.where(valid, cb[:, :L - 1], np.float32(0.0)).astype(np.float32)
+    b = np.where(valid, cb[:, 1:L], np.float32(1.0)).astype(np.float32)
 
     def to_ord(x: np.ndarray) -> np.ndarray:                  # monotone int64 key of fp32 values
         u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.int64)

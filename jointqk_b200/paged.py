@@ -194,6 +194,18 @@ def score(packed: PackedKeys, q: torch.Tensor, decode_tables: bool = False) -> t
     if q.shape[1] % t.n_heads:
         raise ValueError(f"Cannot group {q.shape[1]} query heads into {t.n_heads} KV heads evenly.")
     q = q.contiguous()
+    if t.n_wide:
+        # columns above 4 bits are outside the lookup tables: score against the reconstruction (fp32 on
+        # the device), which is what the reference's metric does (eval.py:20-21)
+        if decode_tables:
+            t.require_narrow("scoring through the decode tables")
+        k_hat = decompress(packed)                                            # (n_seqs, H, T, d)
+        g = q.shape[1] // t.n_heads
+        qg = q.float().to(t.device).view(packed.n_seqs, t.n_heads, g, q.shape[2], t.d)
+        s = torch.einsum("shgqd,shtd->shgqt", qg, k_hat) / t.d ** 0.5
+        s = s.reshape(packed.n_seqs, q.shape[1], q.shape[2], packed.max_tokens)
+        pos = torch.arange(packed.max_tokens, device=t.device)
+        return s.masked_fill(pos[None, None, None, :] >= packed.n_tokens.view(-1, 1, 1, 1), 0.0)
     out = torch.zeros((packed.n_seqs, q.shape[1], q.shape[2], packed.max_tokens), dtype=torch.float32, device=t.device)
     if out.numel():
         _native.check(_native.lib.jqk_score_paged(
@@ -233,7 +245,9 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
     With ``v_tables`` the value pool holds packed codes of that compressor (int32 storage)."""
     if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
+    tables.require_narrow("decode attention")
     if v_tables is not None:
+        v_tables.require_narrow("decode attention over packed values")
         if v_pool.dtype != torch.int32:
             raise ValueError("a packed value pool is int32 storage")
         if out.shape != q.shape or not out.is_contiguous():

@@ -15,7 +15,7 @@ import torch
 
 from . import _native
 from .codebooks import unit_gaussian_centroids
-from .layout import MAX_TABLES, KeyLayout, decision_thresholds, plan_key_layout, unit_quantiser_tables
+from .layout import MAX_TABLES, MAX_WIDE, KeyLayout, decision_thresholds, plan_key_layout, unit_quantiser_tables
 
 DESC_INTS = 32
 MAX_COLS = 128
@@ -54,9 +54,9 @@ class HeadTables:
         lengths = torch.isfinite(cb).sum(-1)                       # (H, d)
         if not bool(((lengths & (lengths - 1)) == 0).all()) or int(lengths.min()) < 1:
             raise ValueError("each codebook row must hold a power-of-two number of finite levels")
-        if int(lengths.max()) > 16:
+        if int(lengths.max()) > 256:
             raise ValueError(
-                f"the packed GPU path stores at most 4 bits per coordinate; a codebook row has "
+                f"the packed GPU path stores at most 8 bits per coordinate; a codebook row has "
                 f"{int(lengths.max())} levels")
         bits = torch.log2(lengths.float()).round().long()
         zero_rows = cb[..., 0][bits == 0]
@@ -77,6 +77,10 @@ class HeadTables:
         inv_rows = np.zeros((H, MAX_COLS, d), np.float32)
         thr = np.full((H, MAX_COLS, 16), np.inf, np.float32)
         cb_cols = np.zeros((H, MAX_COLS, 16), np.float32)
+        # columns of 5..8 bits: their own 256-entry rows, indexed by column - wide_first
+        self.n_wide = max(l.n_wide for l in self.layouts)
+        wide_thr = np.full((H, MAX_WIDE, 256), np.inf, np.float32)
+        wide_cb = np.zeros((H, MAX_WIDE, 256), np.float32)
         col_scale = np.ones((H, MAX_COLS), np.float32)     # 1 / sigma of the column's coordinate
         unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 5)}
         scaled_ok = True
@@ -84,6 +88,7 @@ class HeadTables:
         for h, lay in enumerate(self.layouts):
             desc[h, :8] = lay.descriptor()
             desc[h, 8:8 + lay.n_words + 1] = lay.word_col_begin
+            desc[h, 30], desc[h, 31] = lay.wide_first, lay.n_wide
             n = lay.n_active
             coords = lay.col_coord[:n]
             col_meta[h, :n] = lay.col_width[:n] | (lay.col_bitpos[:n] << 4) | (coords << 16)
@@ -95,12 +100,24 @@ class HeadTables:
             rows = np.zeros((n, 16), np.float32)
             kk = min(K, 16)
             rows[:, :kk] = np.where(np.isfinite(cb_np[h][coords, :kk]), cb_np[h][coords, :kk], 0.0)
+            narrow = lay.col_width[:n] <= 4
+            rows[~narrow] = 0.0
             cb_cols[h, :n] = rows
-            thr[h, :n, :15] = decision_thresholds(rows, lay.col_width[:n])
+            thr[h, :n, :15] = decision_thresholds(rows, np.where(narrow, lay.col_width[:n], 0))
+            if lay.n_wide:
+                wc = np.arange(lay.wide_first, lay.wide_first + lay.n_wide)
+                wrows = np.zeros((lay.n_wide, 256), np.float32)
+                kw = min(K, 256)
+                wrows[:, :kw] = np.where(np.isfinite(cb_np[h][coords[wc], :kw]), cb_np[h][coords[wc], :kw], 0.0)
+                wide_cb[h, :lay.n_wide] = wrows
+                wide_thr[h, :lay.n_wide, :255] = decision_thresholds(wrows, lay.col_width[wc], max_levels=256)
             # the codebook row is unit levels x sigma (per_coord_quantization.py:107): the ratio of the
             # top levels gives 1 / sigma back to an ulp, which is all the scaled transform needs
             for c in range(n):
                 w = int(lay.col_width[c])
+                if w > 4:            # wide columns never reach the tensor-core kernel
+                    scaled_ok = False
+                    continue
                 top = float(rows[c, (1 << w) - 1])
                 if not (top > 1e-30 and np.isfinite(top)):
                     scaled_ok = False
@@ -113,6 +130,9 @@ class HeadTables:
         self.desc, self.col_meta, self.table_fields = up(desc), up(col_meta), up(fields)
         self.fwd_cols, self.qproj_cols, self.inv_rows = up(fwd_cols), up(qproj), up(inv_rows)
         self.thresholds, self.cb_cols = up(thr), up(cb_cols)
+        self.wide_thr = self.wide_cb = None
+        if self.n_wide:
+            self.wide_thr, self.wide_cb = up(wide_thr), up(wide_cb)
         # Tensor-core transform: the basis columns scaled by 1 / sigma of their coordinate, so that every
         # transformed value is quantised against the unit levels of its width (one shared set of tables,
         # layout.unit_quantiser_tables), split into three bf16 limbs, [H][3][col][dim] (column-major =
@@ -136,7 +156,7 @@ class HeadTables:
                 basis = self.fwd_limbs.float().cpu().double().sum(1)                # [H][col][dim]
                 self.center_cols = torch.einsum("hd,hcd->hc", c.double(), basis).float().contiguous().to(self.device)
         self.struct = _native.JqkHeadTables(
-            n_heads=H, d=d, words_per_record=self.words_per_record, reserved=0,
+            n_heads=H, d=d, words_per_record=self.words_per_record, n_wide=self.n_wide,
             desc=self.desc.data_ptr(), col_meta=self.col_meta.data_ptr(),
             table_fields=self.table_fields.data_ptr(), fwd_cols=self.fwd_cols.data_ptr(),
             thresholds=self.thresholds.data_ptr(), cb_cols=self.cb_cols.data_ptr(),
@@ -146,11 +166,22 @@ class HeadTables:
             center=None if self.center is None else self.center.data_ptr(),
             center_cols=None if self.center_cols is None else self.center_cols.data_ptr(),
             unit_thr=(C.c_float * 64)(*[float(x) for x in u_thr.reshape(-1)]),
-            unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])))
+            unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])),
+            wide_thr=None if self.wide_thr is None else self.wide_thr.data_ptr(),
+            wide_cb=None if self.wide_cb is None else self.wide_cb.data_ptr())
 
     @property
     def ref(self):
         return C.byref(self.struct)
+
+    def require_narrow(self, what: str) -> None:
+        """The lookup tables of the decode and score kernels cover 0..4 bits per coordinate."""
+        if self.n_wide:
+            raise ValueError(
+                f"{what} reads the codes through 16-entry lookup tables and takes at most 4 bits per coordinate; these "
+                f"tables hold {self.n_wide} wider column(s).  Fit with max_bits=4 for packed decode attention (a different "
+                "allocation from the reference's cap of 8, with a quality cost where outlier channels want more bits); "
+                "compress, unpack, decompress, roundtrip and the evaluation scores work at the reference's cap")
 
     @property
     def record_bytes(self) -> int:

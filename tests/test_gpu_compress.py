@@ -10,6 +10,7 @@ import jointqk_b200 as jq
 from jointqk_b200 import paged
 from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
 from gpu_util import code_mismatch, oracle_codes_and_recon
+from oracle import reference_port as orc
 
 pytestmark = pytest.mark.gpu
 MAX_RATE = 1e-5
@@ -44,6 +45,31 @@ def test_codes_and_roundtrip_against_reference_fixture(golden, which, codes_name
     row_ok = (codes.cpu() == _t(g[codes_name])).all(-1)
     err = (out.cpu() - ref)[row_ok].abs().max().item()
     assert err < 1e-5 * max(1.0, ref.abs().max().item()), err
+
+
+def test_reference_default_cap8_roundtrip_against_reference_fixture(golden):
+    """The reference's own recipe, cap of 8 bits per coordinate untouched
+    (build_method_compressor defaults, per_coord_quantization.py:365-379): outlier coordinates take a
+    byte each in the record.  Bits, stds and codebooks equal the fixture bit for bit; the GPU
+    roundtrip equals the reference's roundtrip except on rows where a code sits on a decision
+    threshold; the codes equal the oracle's."""
+    g = golden("compressor")
+    R = _t(g["R_sym"])
+    comp = jq.build_method_compressor("r_sym_waterfill", _t(g["sigma_q"]), _t(g["sigma_k"]), None, None, None, 2.0, None, 0,
+                                      128, R_sym=R)
+    assert torch.equal(comp.bits_int, _t(g["ref_bits_cap8"]).long()) and torch.equal(comp.codebooks_padded, _t(g["ref_codebooks_cap8"]))
+    assert int(comp.bits_int.max()) > 4 and comp.packable and not comp.decodable
+    keys = _t(g["keys"])
+    out = comp.roundtrip(keys.cuda()).cpu()
+    ref = _t(g["ref_roundtrip_cap8"])
+    bad_rows = ((out - ref).abs().amax(-1) > 1e-5 * max(1.0, ref.abs().max().item())).sum().item()
+    assert bad_rows <= 1, bad_rows
+    want = orc.nearest_codes(orc.transform(keys, comp.forward_map), comp.codebooks_padded)
+    bad, _ = code_mismatch(comp.codes(keys.cuda()), want.to(torch.uint8))
+    assert bad <= 1, bad
+    # the same through the token kernel (one key at a time) and the batched call
+    one = torch.cat([comp.roundtrip(keys[i:i + 1].cuda()).cpu() for i in range(8)])
+    assert ((one - ref[:8]).abs().amax(-1) > 1e-5 * max(1.0, ref.abs().max().item())).sum().item() == 0
 
 
 def test_roundtrip_accepts_cpu_tensors_and_leading_dims(golden):

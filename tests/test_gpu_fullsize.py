@@ -134,12 +134,19 @@ def test_parity_config_retention_cap4_beside_reference_cap8():
                           for h in range(H)]).unsqueeze(0)
     ret4 = orc.attention_metrics(q, keys.unsqueeze(0), k_hat4)["top1_match"]
     comps8, _ = fit_sigma_k_heads(keys, 2.0, max_bits=8)                 # the reference's default cap
-    assert not comps8[0].packable
-    with pytest.raises(ValueError, match="max_bits=4"):
-        comps8[0].roundtrip(keys[0, :16])
+    assert comps8[0].packable and not comps8[0].decodable
+    tables8 = jq.HeadTables.from_compressors(comps8, device="cuda")
+    packed8 = paged.compress(tables8, keys.cuda().unsqueeze(0))          # outlier coordinates: a byte each
+    s8 = paged.score(packed8, q.cuda()).cpu()
+    ret8_gpu = (s8.argmax(-1) == real.argmax(-1)).float().mean().item()
     k_hat8 = torch.stack([orc.roundtrip(keys[h], comps8[h].codebooks_padded, comps8[h].forward_map, comps8[h].inverse_map)[0]
                           for h in range(H)]).unsqueeze(0)
     ret8 = orc.attention_metrics(q, keys.unsqueeze(0), k_hat8)["top1_match"]
-    print(f"top-1 retention at 2.0 bits: gpu (cap 4) {ret_gpu:.4f}, oracle cap 4 {ret4:.4f}, oracle cap 8 (reference default) {ret8:.4f}")
+    assert ret8_gpu == ret8
+    assert jq.compute_attention_metrics(q, keys.unsqueeze(0), packed8)["top1_match"] == ret8
+    with pytest.raises(ValueError, match="max_bits=4"):                   # the decode tables stop at 4 bits
+        paged.PagedKVCache(tables8, [N]).decode(torch.zeros(1, H, 128, dtype=torch.bfloat16, device="cuda"))
+    print(f"top-1 retention at 2.0 bits: gpu (cap 4) {ret_gpu:.4f}, oracle cap 4 {ret4:.4f}; gpu (cap 8, reference default) "
+          f"{ret8_gpu:.4f}, oracle cap 8 {ret8:.4f}")
     assert ret_gpu == ret4
     assert ret8 > ret4                                                   # the cap costs retrieval quality on this spectrum

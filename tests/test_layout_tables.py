@@ -127,11 +127,40 @@ def test_kernel_model_scores_match_reference(golden):
         assert np.array_equal(s.argmax(-1), ref.argmax(-1))
 
 
-def test_head_tables_reject_wide_codebooks():
-    cb = torch.full((1, 16, 32), float("inf"))
-    cb[0, :, :32] = torch.arange(32.0)
-    with pytest.raises(ValueError, match="4 bits"):
+def test_head_tables_reject_codebooks_beyond_8_bits():
+    cb = torch.arange(512.0).expand(1, 16, 512).clone()
+    with pytest.raises(ValueError, match="8 bits"):
         HeadTables(None, None, cb, device="cpu")
+
+
+def test_layout_with_wide_columns():
+    """Coordinates of 5..8 bits take a byte each in whole words between the nibble region and the byte
+    region; packing and unpacking such records round-trips, and more than 16 wide coordinates are refused."""
+    from oracle import reference_port as orc
+
+    rng = np.random.default_rng(3)
+    for _ in range(20):
+        bits = rng.integers(0, 5, 128)
+        wide = rng.choice(128, size=rng.integers(1, 17), replace=False)
+        bits[wide] = rng.integers(5, 9, len(wide))
+        if bits.sum() > 400:
+            continue
+        lay = plan_key_layout(bits)
+        n = lay.n_active
+        assert lay.n_wide == len(wide) and n == int((bits > 0).sum())
+        wc = slice(lay.wide_first, lay.wide_first + lay.n_wide)
+        assert np.all(lay.col_width[wc] > 4) and np.all(lay.col_bitpos[wc] % 8 == 0)
+        assert np.all(np.delete(lay.col_width[:n], np.arange(lay.wide_first, lay.wide_first + lay.n_wide)) <= 4)
+        assert np.all(np.diff(lay.col_bitpos[:n]) >= lay.col_width[:n - 1])            # fields do not overlap
+        assert np.all(lay.col_bitpos[:n] // 32 == (lay.col_bitpos[:n] + lay.col_width[:n] - 1) // 32)   # nor straddle words
+        codes = np.stack([rng.integers(0, 1 << max(int(b), 0) if b else 1, 50) for b in bits], 1)      # (50, 128) coordinate order
+        rec = orc.pack_records(codes, lay.col_coord[:n], lay.col_width[:n], lay.col_bitpos[:n], lay.n_words)
+        back = orc.unpack_records(rec, lay.col_coord[:n], lay.col_width[:n], lay.col_bitpos[:n], 128)
+        assert np.array_equal(back, codes)
+    too_many = np.zeros(128, dtype=np.int64)
+    too_many[:17] = 5
+    with pytest.raises(ValueError, match="at most 16"):
+        plan_key_layout(too_many)
 
 
 def test_unit_quantiser_tables_are_exact():
@@ -189,3 +218,23 @@ def test_scaled_limbs_quantise_like_the_reference_rule():
             bad += int((want != got).sum())
             tot += x.size
     assert bad / tot < 2e-6
+
+
+def test_wide_decision_thresholds_reproduce_the_argmin():
+    """Thresholds of 5..8-bit codebooks (256-entry rows): counting them gives the reference's
+    first-minimum argmin over |x - level| in fp32, also for inputs right at the thresholds."""
+    from jointqk_b200.codebooks import unit_gaussian_centroids
+
+    rng = np.random.default_rng(11)
+    for bits, sigma in ((5, 3.7), (6, 0.21), (7, 41.0), (8, 1.3)):
+        levels = (unit_gaussian_centroids(bits) * float(np.float32(sigma))).numpy().astype(np.float32)
+        rows = np.zeros((1, 256), np.float32)
+        rows[0, :len(levels)] = levels
+        thr = decision_thresholds(rows, np.array([bits]), max_levels=256)[0]
+        n_thr = (1 << bits) - 1
+        assert np.all(np.isfinite(thr[:n_thr])) and np.all(np.isinf(thr[n_thr:])) and np.all(np.diff(thr[:n_thr]) >= 0)
+        x = np.concatenate([rng.normal(0, sigma, 20000).astype(np.float32), thr[:n_thr],
+                            np.nextafter(thr[:n_thr], np.float32(-np.inf)), np.nextafter(thr[:n_thr], np.float32(np.inf))])
+        want = np.abs(x[:, None] - levels[None, :]).argmin(1)                    # fp32, first minimum
+        got = (x[:, None] >= thr[None, :n_thr]).sum(1)
+        assert np.array_equal(got, want), bits
