@@ -38,7 +38,7 @@ extern "C" {
 #define JQK_MAX_DIM 128        /* head_dim: multiple of 16, at most 128 */
 #define JQK_MAX_COLS 128       /* coordinates that carry >0 bits, padded to 16 */
 #define JQK_MAX_WORDS 16       /* uint32 words per record */
-#define JQK_MAX_WIDE 16        /* columns of 5..8 bits per head */
+#define JQK_MAX_WIDE 32        /* columns of 5..8 bits per head */
 #define JQK_MAX_TABLES 208     /* lookups per record (see jqk_head_tables.table_fields) */
 #define JQK_DESC_INTS 32       /* int32 per head in jqk_head_tables.desc */
 #define JQK_MAX_GROUP 4        /* q heads scored together by one thread block */
@@ -90,8 +90,10 @@ extern "C" {
  *                 channels, per_coord_quantization.py:365-379); such a column takes one byte of the
  *                 record, its rows here are indexed by column - desc[30] (desc[31] = how many).  They
  *                 are written, read back and reconstructed by jqk_compress_paged / jqk_decompress_paged
- *                 / jqk_unpack_codes on the CUDA cores; the score and decode entry points, whose lookup
- *                 tables cover 0..4 bits, return JQK_E_UNSUPPORTED for tables with n_wide > 0
+ *                 / jqk_unpack_codes on the CUDA cores.  The score and decode entry points give a wide
+ *                 column a 256-entry lookup table (sixteen of the JQK_MAX_TABLES slots of 16 entries;
+ *                 desc n_tables counts them); tables whose lookups do not fit have decodable = 0 and
+ *                 get JQK_E_UNSUPPORTED there, as do packed-VALUE tables with wide columns
  *   unit_pre      uint8 [4][128], unit_thr float [4][16] (HOST values, +inf padded), unit_aff float [2]
  *                 (HOST): the shared coarse-to-exact quantiser of the tensor-core kernel for widths
  *                 1..4: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes 2^23),
@@ -118,6 +120,8 @@ typedef struct jqk_head_tables {
   float unit_aff[2];
   const float* wide_thr;
   const float* wide_cb;
+  int32_t decodable;        /* every head's lookup tables fit the decode kernels' table memory (JQK_MAX_TABLES slots) */
+  int32_t pad;
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */

@@ -66,11 +66,11 @@ class PerCoordCompressor:
     @property
     def packable(self) -> bool:
         """True when the packed GPU format can store the codes: at most 8 bits per coordinate and at
-        most 16 coordinates above 4 bits (those take a byte each).  The reference's default cap of 8
+        most 32 coordinates above 4 bits (those take a byte each).  The reference's default cap of 8
         (per_coord_quantization.py:367) fits."""
         if not self.bits_int.numel():
             return True
-        return int(self.bits_int.max()) <= 8 and int((self.bits_int > 4).sum()) <= 16
+        return int(self.bits_int.max()) <= 8 and int((self.bits_int > 4).sum()) <= 32
 
     @property
     def decodable(self) -> bool:
@@ -116,7 +116,7 @@ class PerCoordCompressor:
             raise ValueError(
                 f"this compressor gives a coordinate {int(self.bits_int.max())} bits and "
                 f"{int((self.bits_int > 4).sum())} coordinates more than 4; the packed GPU format stores 0..8 bits per "
-                "coordinate with at most 16 coordinates above 4 bits.  Fit it with a lower cap "
+                "coordinate with at most 32 coordinates above 4 bits.  Fit it with a lower cap "
                 "(PerCoordCompressor.fit(..., max_bits=...) or build_method_compressor(..., max_bits=...))")
         if self._tables is None or self._tables.device != dev:
             self._tables = HeadTables.from_compressors([self], device=dev)

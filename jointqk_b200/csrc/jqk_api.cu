@@ -23,10 +23,17 @@ int32_t check_tables(const jqk_head_tables* t) {
   return 0;
 }
 
-// The lookup tables of the score and decode kernels cover 0..4 bits per coordinate.
+// Paths that take 0..4 bits per coordinate only (packed values).
 int32_t check_narrow(const jqk_head_tables* t, const char* what) {
   if (t && t->n_wide > 0)
     return fail(JQK_E_UNSUPPORTED, "%s takes tables with at most 4 bits per coordinate; these hold %d wider column(s)", what, t->n_wide);
+  return 0;
+}
+
+// The score and decode kernels keep all lookup tables of a head in shared memory.
+int32_t check_decodable(const jqk_head_tables* t, const char* what) {
+  if (t && t->n_wide > 0 && !t->decodable)
+    return fail(JQK_E_UNSUPPORTED, "%s: the lookup tables of a head do not fit (%d columns above 4 bits take 16 table slots each)", what, t->n_wide);
   return 0;
 }
 

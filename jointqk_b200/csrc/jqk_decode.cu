@@ -72,8 +72,9 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
   const char* q_ptr = (const char*)q + q_elem0 * (q_dtype == JQK_DTYPE_F32 ? 4 : 2);
   {
     const TableLoads ld = issue_table_loads(tb, head, d, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
-    build_tables(sm, hd, ld);
+    build_tables(sm, hd, ld, hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr, tb.col_meta + (size_t)head * 128);
   }
+  const float* wide_cb = hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr;
   const float inv_sqrt_d = 1.0f / sqrtf((float)d);
   for (int tok = t_begin + threadIdx.x; tok < t_end; tok += blockDim.x) {
     const int page = lookup_page(page_table, pt_stride, seq, tok / JQK_PAGE_TOKENS, n_pages, status);
@@ -83,7 +84,11 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
     float sv[JQK_MAX_GROUP];
     if (table_mode) {  // the decode kernel's fixed-point tables
       int acc[JQK_MAX_GROUP];
-      score_record([kp](int w) { return __ldg(kp + w * JQK_PAGE_TOKENS); }, TableView{sm.lut, sm.dshift, sm.bias}, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
+      auto word = [kp](int w) { return __ldg(kp + w * JQK_PAGE_TOKENS); };
+      if (hd.n_wide)
+        score_record<true>(word, TableView{sm.lut, sm.dshift, sm.bias, sm.woff}, hd.n_a_words, hd.n_c_words, hd.n_words, acc, hd.n_wide);
+      else
+        score_record<false>(word, TableView{sm.lut, sm.dshift, sm.bias}, hd.n_a_words, hd.n_c_words, hd.n_words, acc);
 #pragma unroll
       for (int h = 0; h < JQK_MAX_GROUP; ++h) sv[h] = (float)acc[h] * sm.scale[h];
     } else {           // plain fp32: sum_c q'_c * cb[c][code_c], column after column
@@ -94,7 +99,8 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
         const int m = __ldg(meta + c);
         const int bp = (m >> 4) & 1023;
         const uint32_t word = __ldg(kp + (bp >> 5) * JQK_PAGE_TOKENS);
-        const float x = sm.cb[c * 16 + ((word >> (bp & 31)) & ((1u << (m & 15)) - 1u))];
+        const uint32_t code = (word >> (bp & 31)) & ((1u << (m & 15)) - 1u);
+        const float x = (m & 15) > 4 ? __ldg(wide_cb + (size_t)(c - hd.wide_first) * 256 + code) : sm.cb[c * 16 + code];
         const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[c]);
         sv[0] = fmaf(qp.x, x, sv[0]); sv[1] = fmaf(qp.y, x, sv[1]);
         sv[2] = fmaf(qp.z, x, sv[2]); sv[3] = fmaf(qp.w, x, sv[3]);
@@ -269,7 +275,7 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   {
     const TableLoads ld = issue_table_loads(tb, head, hd.d, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d,
                                             JQK_DTYPE_BF16, (size_t)hd.d, n_group);
-    build_tables(sm, hd, ld);
+    build_tables(sm, hd, ld, hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr, tb.col_meta + (size_t)head * 128);
   }
   TableRecord* rec = recs + (size_t)seq * gridDim.x + blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(sm.lut);
@@ -278,6 +284,7 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   if (threadIdx.x < TBL_WORDS) rec->dshift[threadIdx.x] = sm.dshift[threadIdx.x];
   if (threadIdx.x < JQK_MAX_GROUP) rec->scale[threadIdx.x] = sm.scale[threadIdx.x];
   if (threadIdx.x == 0) rec->bias = sm.bias;
+  if (threadIdx.x < JQK_MAX_WIDE) rec->woff[threadIdx.x] = sm.woff[threadIdx.x];
 }
 
 // What the kernel needs of the value-side tables when values are stored as packed codes.
@@ -342,7 +349,8 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
                                         const void* v_row, int k_dtype, int v_dtype, uint32_t* k_pool, __nv_bfloat16* v_pool,
                                         int head, int seq, bool write, int pos,
                                         const int32_t* __restrict__ page_table, int pt_stride, int n_pages,
-                                        int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group) {
+                                        int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group,
+                                        const float* __restrict__ wide_thr, int wide_first) {
   const int tid = threadIdx.x;
   if (tid < D) {
     sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
@@ -360,10 +368,8 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
 #pragma unroll 32
     for (int i = 0; i < D; ++i) x = fmaf(sm.ap_k[i], __ldg(w + (size_t)i * 128), x);
     const int m = col_meta[(size_t)head * 128 + tid];
-    const float* th = thresholds + ((size_t)head * 128 + tid) * 16;
-    const int n_thr = (1 << (m & 15)) - 1;
-    uint32_t code = 0;
-    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const float* wide_row = (m & 15) > 4 ? wide_thr + ((size_t)head * JQK_MAX_WIDE + (tid - wide_first)) * 256 : nullptr;
+    const uint32_t code = threshold_code(x, m & 15, thresholds + ((size_t)head * 128 + tid) * 16, wide_row);
     const int bp = (m >> 4) & 1023;
     atomicOr(&sm.ap_words[bp >> 5], code << (bp & 31));
   } else if (q_rows && tid >= 256) {   // the exact scores of the new key: one warp per query head of the group
@@ -465,7 +471,7 @@ __device__ __noinline__ void append_row_packed(DecodeSmemT<true>& sm, const floa
 
 // D = head_dim (64 or 128).  VQ: values are packed codes of a second compressor (v_pool is then the
 // uint32 code pool, `vs` its tables); the keys' tables then always come from the table kernel.
-template <int D, bool BUILD_IN_BLOCK, bool VQ, bool APPEND>
+template <int D, bool BUILD_IN_BLOCK, bool VQ, bool APPEND, bool WIDE = false>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_heads,
               const int32_t* __restrict__ seq_lens, int tokens_per_split,
@@ -473,6 +479,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
               const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs, AppendSide ap) {
   static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
+  static_assert(!(VQ && WIDE), "keys with byte-wide codes go with bf16 values");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -640,15 +647,18 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
                     (const char*)ap.k + ((size_t)seq * ap.k_seq_stride + (size_t)head * ap.k_head_stride) * k_esz,
                     (const char*)ap.v + ((size_t)seq * ap.v_seq_stride + (size_t)head * ap.v_head_stride) * v_esz,
                     ap.k_dtype, ap.v_dtype, ap.k_pool, ap.v_pool, head, seq, qb == 0, ap_pos, page_table, pt_stride, n_pages, status,
-                    ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group);
+                    ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group, tb.wide_thr, hd.wide_first);
     }
   }
 
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
-    build_tables(sm.t.build, hd, tloads);
-    tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias};
+    if constexpr (WIDE)
+      build_tables(sm.t.build, hd, tloads, tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256, tb.col_meta + (size_t)head * 128);
+    else
+      build_tables(sm.t.build, hd, tloads);
+    tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias, sm.t.build.woff};
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];
   } else {
@@ -675,7 +685,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     }
     __syncthreads();
     if (!bar_wait(&sm.tfull, 0) && tid == 0 && status) atomicOr(status, JQK_STATUS_WAIT_EXPIRED);
-    tview = TableView{sm.t.rec.lut, sm.t.rec.dshift, sm.t.rec.bias};
+    tview = TableView{sm.t.rec.lut, sm.t.rec.dshift, sm.t.rec.bias, sm.t.rec.woff};
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.rec.scale[h];
   }
@@ -724,7 +734,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     int ia[JQK_MAX_GROUP];
     {
       const uint32_t* kw = reinterpret_cast<const uint32_t*>(st.k[r & 1][lane >> 4]) + (lane & 15);
-      score_record([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, tview, n_a_words, n_c_words, n_words, ia);
+      score_record<WIDE>([kw](int w) { return kw[w * JQK_PAGE_TOKENS]; }, tview, n_a_words, n_c_words, n_words, ia, WIDE ? hd.n_wide : 0);
     }
     if (!lane_ok) {
 #pragma unroll
@@ -1106,7 +1116,7 @@ extern "C" int32_t jqk_score_paged(const jqk_head_tables* tables, int32_t table_
                                    float* scores, int32_t* status, void* stream) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
-  if ((rc = check_narrow(tables, "jqk_score_paged"))) return rc;
+  if ((rc = check_decodable(tables, "jqk_score_paged"))) return rc;
   if (n_seqs < 0 || n_queries < 0 || max_tokens < 0) return fail(JQK_E_ARG, "negative size");
   if (n_seqs == 0 || n_queries == 0 || max_tokens == 0) return 0;
   if (!q || !seq_lens || !page_table || !k_pool || !scores) return fail(JQK_E_ARG, "null pointer argument");
@@ -1134,7 +1144,8 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
                              size_t workspace_bytes, int32_t* status, void* stream, const AppendSide* append = nullptr) {
   int32_t rc = check_tables(tables);
   if (rc) return rc;
-  if ((rc = check_narrow(tables, "decode attention"))) return rc;
+  if ((rc = check_decodable(tables, "decode attention"))) return rc;
+  if (v_tables && (rc = check_narrow(tables, "decode attention over packed values (the keys)"))) return rc;
   if (v_tables) {
     rc = check_tables(v_tables);
     if (rc) return rc;
@@ -1200,29 +1211,37 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   if (v_tables)
     vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
                    v_tables->n_heads, v_tables->words_per_record, v_tables->fwd_cols, v_tables->thresholds};
-#define JQK_LAUNCH_DECODE(DIM, INB, VQQ, APP)                                                                         \
+#define JQK_LAUNCH_DECODE(DIM, INB, VQQ, APP, WID)                                                                    \
   do {                                                                                                                \
     cfg.dynamicSmemBytes = sizeof(DecodeSmemT<VQQ>);                                                                  \
-    JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ, APP>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");            \
-    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ, APP>, *tables, (const __nv_bfloat16*)q,         \
+    JQK_SMEM_ONCE((decode_kernel<DIM, INB, VQQ, APP, WID>), sizeof(DecodeSmemT<VQQ>), "decode smem attribute");       \
+    JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, decode_kernel<DIM, INB, VQQ, APP, WID>, *tables, (const __nv_bfloat16*)q,    \
                                    n_q_heads, seq_lens, tokens_per_split, page_table, page_table_stride, n_pages,     \
                                    k_pool, v_pool, out, out_dtype, ws, status, vs, ap),                               \
                 "decode launch");                                                                                     \
   } while (0)
+  const bool wide = tables->n_wide > 0;   // byte-wide codes: head_dim 128 and bf16 values only
+  if (wide && tables->d != 128) return fail(JQK_E_UNSUPPORTED, "codes above 4 bits are decoded for head_dim 128 only");
   if (v_tables && append) {
-    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, true); else JQK_LAUNCH_DECODE(64, false, true, true);
+    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, true, false); else JQK_LAUNCH_DECODE(64, false, true, true, false);
   } else if (v_tables) {
-    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false); else JQK_LAUNCH_DECODE(64, false, true, false);
+    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false, false); else JQK_LAUNCH_DECODE(64, false, true, false, false);
+  } else if (wide) {
+    if (append) {
+      if (in_block) JQK_LAUNCH_DECODE(128, true, false, true, true); else JQK_LAUNCH_DECODE(128, false, false, true, true);
+    } else {
+      if (in_block) JQK_LAUNCH_DECODE(128, true, false, false, true); else JQK_LAUNCH_DECODE(128, false, false, false, true);
+    }
   } else if (append) {
     if (tables->d == 128) {
-      if (in_block) JQK_LAUNCH_DECODE(128, true, false, true); else JQK_LAUNCH_DECODE(128, false, false, true);
+      if (in_block) JQK_LAUNCH_DECODE(128, true, false, true, false); else JQK_LAUNCH_DECODE(128, false, false, true, false);
     } else {
-      if (in_block) JQK_LAUNCH_DECODE(64, true, false, true); else JQK_LAUNCH_DECODE(64, false, false, true);
+      if (in_block) JQK_LAUNCH_DECODE(64, true, false, true, false); else JQK_LAUNCH_DECODE(64, false, false, true, false);
     }
   } else if (tables->d == 128) {
-    if (in_block) JQK_LAUNCH_DECODE(128, true, false, false); else JQK_LAUNCH_DECODE(128, false, false, false);
+    if (in_block) JQK_LAUNCH_DECODE(128, true, false, false, false); else JQK_LAUNCH_DECODE(128, false, false, false, false);
   } else {
-    if (in_block) JQK_LAUNCH_DECODE(64, true, false, false); else JQK_LAUNCH_DECODE(64, false, false, false);
+    if (in_block) JQK_LAUNCH_DECODE(64, true, false, false, false); else JQK_LAUNCH_DECODE(64, false, false, false, false);
   }
 #undef JQK_LAUNCH_DECODE
   JQK_CUDA_OK(cudaGetLastError(), "decode launch");

@@ -14,6 +14,10 @@
 // w, which is exact, and the final sum is in units of scale_h / 2^K_last.  K_w is the largest
 // shift that keeps every entry of every later-or-equal word inside 16 bits (capped at
 // TBL_MAX_SHIFT so that the 32-bit sums cannot overflow).
+//
+// Columns of 5..8 bits (a byte each, in whole words between the nibble and the byte region) get a
+// table of 2^width entries each (2 .. 16 slots of 16 entries), after the 16-entry ones; their words
+// are scanned first (they are the highest-variance coordinates), one lookup per column.
 #pragma once
 
 #include <math_constants.h>
@@ -39,6 +43,8 @@ struct TableSmem {
   int dshift[TBL_WORDS];                         // K_w - K_{w-1}
   unsigned int bias;                             // what the +32768 offsets of the low halves add up to
   int wcb[JQK_MAX_WORDS + 4];                    // first column of every physical record word
+  uint8_t woff[JQK_MAX_WIDE];                    // wide column i: first table slot of its 2^width-entry table,
+                                                 // counted from the end of the 16-entry tables
 };
 
 // Scan-order word of table t: nibble word t/8, or n_a_words + byte word.
@@ -118,7 +124,11 @@ __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& t
 // words: it sums the partial projections of its word's columns and bounds that word's tables by
 // itself, so only the word maxima cross warps (one barrier); every warp then derives all shifts
 // and the entries are quantised by all threads.
-__device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld) {
+// `wide_cb`: the 256-entry level rows of this head's wide columns (null when it has none),
+// `col_meta`: this head's column descriptors (read for the wide columns only).
+__device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld,
+                                             const float* __restrict__ wide_cb = nullptr,
+                                             const int32_t* __restrict__ col_meta = nullptr) {
   const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
   const int lane = tid & 31, warp = tid >> 5, n_warps = nthr >> 5;
@@ -154,12 +164,28 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       *reinterpret_cast<float4*>(sm.part[rg][4 * cg + k]) = make_float4(a[k][0], a[k][1], a[k][2], a[k][3]);
   }
   __syncthreads();
-  const int n_a_words = hd.n_a_words, n_scan_words = hd.n_a_words + hd.n_c_words;
+  const int n_wide = wide_cb ? hd.n_wide : 0, n_w_words = (n_wide + 3) >> 2;
+  const int n_a_words = hd.n_a_words, n_scan_words = n_w_words + hd.n_a_words + hd.n_c_words;
+  const int n_narrow_tables = 8 * hd.n_a_words + 12 * hd.n_c_words;
   // column bounds |q'_c| * max |level| reuse the raw-query staging, which the projection is done with
   float4* colb = reinterpret_cast<float4*>(&sm.qraw[0][0]);  // [JQK_MAX_COLS]
+  // slots of the wide columns' tables: exclusive prefix sum of 2^(width - 4)
+  if (n_wide && warp == 0) {
+    int slots = (lane < n_wide) ? (1 << ((__ldg(col_meta + hd.wide_first + lane) & 15) - 4)) : 0;
+    int incl = slots;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int other = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += other;
+    }
+    if (lane < n_wide) sm.woff[lane] = (uint8_t)(incl - slots);
+  }
   // ---- per warp and scan word: projected queries of the word's columns, bound of its tables ----
   for (int sw = warp; sw < n_scan_words; sw += n_warps) {
-    const int pw = (sw < n_a_words) ? sw : hd.n_words - 1 - (sw - n_a_words);  // physical word
+    // scan order: wide words (physical words n_a_words ..), nibble words (0 ..), byte words (from the end)
+    const bool is_wide = sw < n_w_words;
+    const int nw = sw - n_w_words;                                                // index among the narrow scan words
+    const int pw = is_wide ? n_a_words + sw : (nw < n_a_words) ? nw : hd.n_words - 1 - (nw - n_a_words);  // physical word
     const int c_first = sm.wcb[pw], n_c = sm.wcb[pw + 1] - c_first;            // <= 32 columns
     if (lane < n_c) {
       const int c = c_first + lane;
@@ -172,19 +198,26 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       *reinterpret_cast<float4*>(sm.qproj[c]) = s;
       // levels are sorted and padded with zeros: the largest magnitude of a row is its largest |level|
       float big = 0.f;
+      if (is_wide) {
+        const float* row = wide_cb + (size_t)(c - hd.wide_first) * 256;
+        big = fmaxf(fabsf(__ldg(row)), fabsf(__ldg(row + (1 << (__ldg(col_meta + c) & 15)) - 1)));
+      } else {
 #pragma unroll
-      for (int l4 = 0; l4 < 4; ++l4) {
-        const float4 lv = *reinterpret_cast<const float4*>(sm.cb + c * 16 + 4 * l4);
-        big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
+        for (int l4 = 0; l4 < 4; ++l4) {
+          const float4 lv = *reinterpret_cast<const float4*>(sm.cb + c * 16 + 4 * l4);
+          big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
+        }
       }
       colb[c] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
     }
     __syncwarp();
     // The fields of a table take their codes independently, so the largest |entry| of a table is at
-    // most the sum of its columns' bounds; lane k owns table k of the word.
-    const int t_first = (sw < n_a_words) ? 8 * sw : 8 * n_a_words + 12 * (sw - n_a_words);
-    const int n_t = (sw < n_a_words) ? 8 : 12;
+    // most the sum of its columns' bounds; lane k owns table k of the word.  (A wide word: one
+    // single-column table per column.)
+    const int t_first = (nw < n_a_words) ? 8 * nw : 8 * n_a_words + 12 * (nw - n_a_words);
+    const int n_t = is_wide ? 0 : (nw < n_a_words) ? 8 : 12;
     float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (is_wide && lane < n_c) m = colb[c_first + lane];
     if (lane < n_t) {
       const int4 f4 = *reinterpret_cast<const int4*>(sm.fields + (t_first + lane) * 4);
       const int fl[4] = {f4.x, f4.y, f4.z, f4.w};
@@ -225,7 +258,8 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     unsigned int term = 0u;
     if (lane < n_scan_words) {
       sm.dshift[lane] = kw - (lane ? prev : 0);
-      term = (unsigned int)((lane < n_a_words ? 8 : 12) * 32768) << (k_last - kw);
+      const int lookups = lane < n_w_words ? min(4, n_wide - 4 * lane) : (lane - n_w_words < n_a_words ? 8 : 12);
+      term = (unsigned int)(lookups * 32768) << (k_last - kw);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) term += __shfl_xor_sync(0xffffffffu, term, o);
@@ -241,10 +275,10 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     if (tid == h) sm.scale[h] = base * __int_as_float((127 - (n_scan_words ? k_last : 0)) << 23);  // base / 2^k_last
   }
   // ---- all threads: quantise the entries (every warp knows every word's shift) ----
-  const int n_entries = hd.n_tables * 16;
+  const int n_entries = n_narrow_tables * 16;
   for (int e0 = warp * 32; e0 < n_entries; e0 += nthr) {
     const int e = e0 + lane;  // n_entries is a multiple of 16: the second half-warp may be past the end
-    const int sw = table_word(min(e, n_entries - 1) >> 4, n_a_words);
+    const int sw = n_w_words + table_word(min(e, n_entries - 1) >> 4, n_a_words);
     const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, sw));
     if (e < n_entries) {
       float v[JQK_MAX_GROUP];
@@ -257,6 +291,21 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       const uint32_t q3 = __float_as_uint(fmaf(v[3], inv[3] * up, 12582912.f));
       // high half: signed value of the odd head; low half: value of the even head plus 32768
       sm.lut[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
+    }
+  }
+  // the tables of the wide columns: entry = q'_c * level, behind the 16-entry tables
+  for (int i = 0; i < n_wide; ++i) {
+    const int levels = 1 << (__ldg(col_meta + hd.wide_first + i) & 15);
+    const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, i >> 2));
+    const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[hd.wide_first + i]);
+    uint2* dst = sm.lut + n_entries + (int)sm.woff[i] * 16;
+    for (int e = tid; e < levels; e += nthr) {
+      const float lv = __ldg(wide_cb + (size_t)i * 256 + e);
+      const uint32_t q0 = __float_as_uint(fmaf(qp.x * lv, inv[0] * up, 12582912.f + 32768.f));
+      const uint32_t q1 = __float_as_uint(fmaf(qp.y * lv, inv[1] * up, 12582912.f));
+      const uint32_t q2 = __float_as_uint(fmaf(qp.z * lv, inv[2] * up, 12582912.f + 32768.f));
+      const uint32_t q3 = __float_as_uint(fmaf(qp.w * lv, inv[3] * up, 12582912.f));
+      dst[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
     }
   }
   __syncthreads();
@@ -295,6 +344,7 @@ struct TableView {
   const uint2* lut;
   const int* dshift;
   unsigned int bias;
+  const uint8_t* woff = nullptr;
 };
 
 // Finished tables of one (sequence, kv head, q-head block) in global memory: written by the table
@@ -304,21 +354,38 @@ struct TableRecord {
   int dshift[TBL_WORDS];
   float scale[JQK_MAX_GROUP];
   unsigned int bias;
-  unsigned int pad[27];
+  uint8_t woff[JQK_MAX_WIDE];
+  unsigned int pad[27 - JQK_MAX_WIDE / 4];
 };
 static_assert(sizeof(TableRecord) % 16 == 0 && offsetof(TableRecord, dshift) % 16 == 0, "bulk copies need 16-byte pieces");
 constexpr uint32_t TABLE_RECORD_META_BYTES = sizeof(TableRecord) - offsetof(TableRecord, dshift);  // 256
 
-template <typename WordFn>
+// WIDE: the record also holds `n_wide` byte-wide codes in the words after the nibble words; their
+// 256-entry tables lie behind the 16-entry ones and their words come first in the scan.
+template <bool WIDE = false, typename WordFn>
 __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, int n_a_words, int n_c_words,
-                                             int n_words, int (&out)[JQK_MAX_GROUP]) {
+                                             int n_words, int (&out)[JQK_MAX_GROUP], int n_wide = 0) {
   ScoreAcc acc;
   acc.clear();
   const char* lb = reinterpret_cast<const char*>(sm.lut);
+  const int* dshift = sm.dshift;
+  if constexpr (WIDE) {
+    const char* lw = lb + (size_t)(8 * n_a_words + 12 * n_c_words) * 128;
+    uint32_t x = 0;
+#pragma unroll 1
+    for (int i = 0; i < n_wide; ++i) {
+      if ((i & 3) == 0) {
+        x = word(n_a_words + (i >> 2));
+        acc.shift(dshift[i >> 2]);
+      }
+      acc.add(*reinterpret_cast<const uint2*>(lw + (int)sm.woff[i] * 128 + ((x >> (8 * (i & 3))) & 255u) * 8));
+    }
+    dshift += (n_wide + 3) >> 2;
+  }
 #pragma unroll 4
   for (int w = 0; w < n_a_words; ++w) {
     const uint32_t x = word(w);
-    acc.shift(sm.dshift[w]);
+    acc.shift(dshift[w]);
     const char* lw = lb + w * 1024;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -330,7 +397,7 @@ __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, i
 #pragma unroll 2
   for (int w = 0; w < n_c_words; ++w) {
     const uint32_t x = word(n_words - 1 - w);
-    acc.shift(sm.dshift[n_a_words + w]);
+    acc.shift(dshift[n_a_words + w]);
     const char* lw = lc + w * 1536;
 #pragma unroll
     for (int b = 0; b < 4; ++b) {

@@ -44,7 +44,7 @@ import numpy as np
 PAGE_TOKENS = 16
 MAX_CODE_BITS = 4       # widths the lookup tables of the decode kernels take
 MAX_STORED_BITS = 8     # widths a record can hold: 5..8-bit codes take a byte each ("wide" columns)
-MAX_WIDE = 16           # wide columns per head
+MAX_WIDE = 32           # wide columns per head
 MAX_WORDS = 16          # 128 coordinates x 4 bits
 MAX_TABLES = 208        # (MAX_WORDS + 1 shared word) * 12 rounded up to a multiple of 8
 TABLE_FIELDS = 4        # a lookup combines at most four coordinates (1,1,1,1)
@@ -72,6 +72,7 @@ class KeyLayout:
     word_col_begin: np.ndarray = field(default=None)  # (n_words + 1,) first column of each word
     n_wide: int = 0                  # columns of 5..8 bits, one byte each, in whole words between the A and C regions
     wide_first: int = 0              # column index of the first of them
+    decodable: bool = True           # the decode kernels' table memory holds all lookups (2^(width-4) table slots per wide column)
 
     @property
     def record_bytes(self) -> int:
@@ -184,10 +185,14 @@ def plan_key_layout(bits) -> KeyLayout:
         col_bitpos[n_active:] = 32 * n_words
     word_col_begin = np.searchsorted(col_bitpos[:n_active], 32 * np.arange(n_words + 1)).astype(np.int32)
     payload = int(bits.sum())
+    # a wide column's table of 2^width entries takes the room of 2 .. 16 of the 16-entry ones, behind them
+    n_tables_all = n_tables + sum(1 << (int(bits[j]) - 4) for j in wide)
+    decodable = n_tables_all <= MAX_TABLES
     return KeyLayout(
         d=d, bits=bits.astype(np.int32), n_cols=n_cols, n_active=n_active, col_coord=col_coord,
         col_width=col_width, col_bitpos=col_bitpos, n_words=n_words, n_a_words=n_a_words,
-        n_c_words=n_c_words, n_tables=n_tables, table_fields=table_fields[:max(n_tables, 1)],
+        n_c_words=n_c_words, n_tables=n_tables_all if decodable else n_tables, decodable=decodable,
+        table_fields=table_fields[:max(n_tables, 1)],
         payload_bits=payload, waste_bits=4 * n_a + 8 * n_c + 8 * len(wide) - payload, word_col_begin=word_col_begin,
         n_wide=len(wide), wide_first=wide_first)
 

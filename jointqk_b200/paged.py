@@ -194,11 +194,11 @@ def score(packed: PackedKeys, q: torch.Tensor, decode_tables: bool = False) -> t
     if q.shape[1] % t.n_heads:
         raise ValueError(f"Cannot group {q.shape[1]} query heads into {t.n_heads} KV heads evenly.")
     q = q.contiguous()
-    if t.n_wide:
-        # columns above 4 bits are outside the lookup tables: score against the reconstruction (fp32 on
-        # the device), which is what the reference's metric does (eval.py:20-21)
+    if not t.decodable:
+        # more wide columns than the score kernel has table memory for: score against the reconstruction
+        # (fp32 on the device), which is what the reference's metric does (eval.py:20-21)
         if decode_tables:
-            t.require_narrow("scoring through the decode tables")
+            t.require_decodable("scoring through the decode tables")
         k_hat = decompress(packed)                                            # (n_seqs, H, T, d)
         g = q.shape[1] // t.n_heads
         qg = q.float().to(t.device).view(packed.n_seqs, t.n_heads, g, q.shape[2], t.d)
@@ -245,8 +245,9 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
     With ``v_tables`` the value pool holds packed codes of that compressor (int32 storage)."""
     if q.dtype != torch.bfloat16 or q.dim() != 3 or not q.is_contiguous():
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
-    tables.require_narrow("decode attention")
+    tables.require_decodable("decode attention")
     if v_tables is not None:
+        tables.require_narrow("decode attention over packed values (the keys)")
         v_tables.require_narrow("decode attention over packed values")
         if v_pool.dtype != torch.int32:
             raise ValueError("a packed value pool is int32 storage")
@@ -286,6 +287,10 @@ def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tenso
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
     if v_pool.dtype != (torch.bfloat16 if v_tables is None else torch.int32):
         raise ValueError("the value pool is bf16, or int32 storage of packed codes when v_tables is given")
+    tables.require_decodable("decode attention")
+    if v_tables is not None:
+        tables.require_narrow("decode attention over packed values (the keys)")
+        v_tables.require_narrow("decode attention over packed values")
     if out.shape != q.shape or not out.is_contiguous():
         raise ValueError("out must be contiguous with the shape of q")
     if k_new.dim() == 4:

@@ -79,6 +79,7 @@ class HeadTables:
         cb_cols = np.zeros((H, MAX_COLS, 16), np.float32)
         # columns of 5..8 bits: their own 256-entry rows, indexed by column - wide_first
         self.n_wide = max(l.n_wide for l in self.layouts)
+        self.decodable = all(l.decodable for l in self.layouts)     # every head's lookups fit the decode kernels' table memory
         wide_thr = np.full((H, MAX_WIDE, 256), np.inf, np.float32)
         wide_cb = np.zeros((H, MAX_WIDE, 256), np.float32)
         col_scale = np.ones((H, MAX_COLS), np.float32)     # 1 / sigma of the column's coordinate
@@ -92,8 +93,8 @@ class HeadTables:
             n = lay.n_active
             coords = lay.col_coord[:n]
             col_meta[h, :n] = lay.col_width[:n] | (lay.col_bitpos[:n] << 4) | (coords << 16)
-            if lay.n_tables:
-                fields[h, :lay.n_tables] = lay.table_fields
+            if len(lay.table_fields):
+                fields[h, :len(lay.table_fields)] = lay.table_fields
             fwd_cols[h, :, :n] = fwd_np[h][:, coords]
             qproj[h, :, :n] = inv_np[h][coords, :].T
             inv_rows[h, :n, :] = inv_np[h][coords, :]
@@ -168,20 +169,28 @@ class HeadTables:
             unit_thr=(C.c_float * 64)(*[float(x) for x in u_thr.reshape(-1)]),
             unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])),
             wide_thr=None if self.wide_thr is None else self.wide_thr.data_ptr(),
-            wide_cb=None if self.wide_cb is None else self.wide_cb.data_ptr())
+            wide_cb=None if self.wide_cb is None else self.wide_cb.data_ptr(),
+            decodable=int(self.decodable), pad=0)
 
     @property
     def ref(self):
         return C.byref(self.struct)
 
     def require_narrow(self, what: str) -> None:
-        """The lookup tables of the decode and score kernels cover 0..4 bits per coordinate."""
+        """For the paths that take 0..4 bits per coordinate only (packed values, the tensor-core tables)."""
         if self.n_wide:
             raise ValueError(
-                f"{what} reads the codes through 16-entry lookup tables and takes at most 4 bits per coordinate; these "
-                f"tables hold {self.n_wide} wider column(s).  Fit with max_bits=4 for packed decode attention (a different "
-                "allocation from the reference's cap of 8, with a quality cost where outlier channels want more bits); "
-                "compress, unpack, decompress, roundtrip and the evaluation scores work at the reference's cap")
+                f"{what} takes at most 4 bits per coordinate; these tables hold {self.n_wide} wider column(s).  "
+                "Fit with max_bits=4")
+
+    def require_decodable(self, what: str) -> None:
+        """The decode and score kernels keep every lookup table of a head in shared memory: 208 slots of
+        16 entries, a column of 5..8 bits taking 16 of them."""
+        if not self.decodable:
+            raise ValueError(
+                f"{what}: the lookup tables of a head exceed the kernels' table memory ({self.n_wide} columns above 4 bits "
+                "take 16 table slots each).  Fit with a lower cap, e.g. max_bits=4, for packed decode attention; "
+                "compress, unpack, decompress, roundtrip and the evaluation scores work as they are")
 
     @property
     def record_bytes(self) -> int:

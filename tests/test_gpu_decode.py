@@ -204,6 +204,75 @@ def test_appended_key_attends_exactly_in_its_own_step(hq):
     paged.check_status(cache.status)
 
 
+def _wide_setup(H, N, b_avg, n_wide_extra=0):
+    """Reference-default allocation (cap 8) on the parity spectrum: the four outlier channels get 5..8
+    bits; ``n_wide_extra`` more coordinates are lifted to 8 bits to crowd the table memory."""
+    keys = torch.stack([spectrum_keys(N, config_seed(0, 0, h)) for h in range(H)])
+    comps, sig = fit_sigma_k_heads(keys, b_avg, max_bits=8)
+    if n_wide_extra:
+        lifted = []
+        for c in comps:
+            bits = c.bits_int.clone()
+            idx = (bits <= 4).nonzero().flatten()[:n_wide_extra]
+            bits[idx] = 8
+            lifted.append(jq.PerCoordCompressor(bits, c.stds, c.forward_map, c.inverse_map))
+        comps = lifted
+    return keys, comps, sig, jq.HeadTables.from_compressors(comps, device="cuda")
+
+
+@pytest.mark.parametrize("b_avg", [2.0, 2.5, 3.0])
+def test_codes_above_4_bits_scores_decode_and_generate(b_avg):
+    """The reference's default cap of 8: outlier coordinates carry 5..8-bit codes, a byte each in the
+    record and a 256-entry lookup table each in the kernels.  Table scores against the oracle's
+    logits, decode attention against the oracle, the one-launch generate step against append + decode."""
+    H, N = 4, 3000
+    keys, comps, sig, tables = _wide_setup(H, 4096, b_avg)
+    assert tables.n_wide >= 4 and tables.decodable
+    packed = paged.compress(tables, keys[:, :N].cuda().unsqueeze(0))
+    k_hat = _k_hat_from_packed(packed, comps)
+    want_codes = torch.stack([orc.nearest_codes(orc.transform(keys[h, :N], comps[h].forward_map), comps[h].codebooks_padded)
+                              for h in range(H)])
+    assert (paged.unpack_codes(packed)[0].cpu().long() != want_codes).float().mean().item() <= 1e-5
+    q = torch.stack([retrieval_queries(keys[h], sig[h], 64, config_seed(0, 0, h) + 7)[0] for h in range(H)]).unsqueeze(0)
+    ref = orc.logits(q, k_hat)
+    s32 = paged.score(packed, q.cuda()).cpu()
+    stab = paged.score(packed, q.cuda(), decode_tables=True).cpu()
+    assert score_rel_error(s32, ref) < 1e-5 and score_rel_error(stab, ref) < SCORE_TOL
+    g = torch.Generator().manual_seed(19)
+    v = torch.randn(1, H, N + 8, 128, generator=g).to(torch.bfloat16)
+    for tps in (0, 256):                                       # blocks build their tables / table kernel (48 blocks x 4 heads)
+        cache = paged.PagedKVCache(tables, [N + 8])
+        cache.prefill(keys[:, :N].unsqueeze(0).cuda(), v[:, :, :N].cuda())
+        qd = torch.randn(1, 4 * H, 128, generator=g).to(torch.bfloat16)
+        out = cache.decode(qd.cuda(), tokens_per_split=tps).cpu()
+        want = orc.decode_attention(qd, k_hat, v[:, :, :N])
+        err = ((out - want).abs() / want.abs().amax(-1, keepdim=True).clamp_min(1e-6)).max().item()
+        assert err < OUT_TOL, (tps, err)
+    plain = paged.PagedKVCache(tables, [N + 8])
+    plain.prefill(keys[:, :N].unsqueeze(0).cuda(), v[:, :, :N].cuda())
+    for i in range(8):                                         # the new key's wide codes come from the decode kernel itself
+        kn, vn = keys[:, N + i].unsqueeze(0).unsqueeze(2).cuda(), v[:, :, N + i:N + i + 1].cuda()
+        qd = torch.randn(1, 4 * H, 128, generator=g).to(torch.bfloat16).cuda()
+        got = cache.generate_step(kn, vn, qd).clone()
+        plain.append(kn, vn)
+        want = plain.decode(qd)
+        assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item(), i
+    pk = [paged.PackedKeys(tables, c.k_pool, c.page_table, c.seq_lens, list(c.lengths), c.status) for c in (cache, plain)]
+    assert torch.equal(paged.unpack_codes(pk[0]), paged.unpack_codes(pk[1]))
+    paged.check_status(cache.status)
+
+
+def test_too_many_wide_columns_for_the_table_memory_are_refused_by_decode_only():
+    keys, comps, sig, tables = _wide_setup(2, 4096, 2.0, n_wide_extra=12)       # sixteen 256-entry tables would take 256 of 208 slots
+    assert tables.n_wide >= 14 and not tables.decodable
+    packed = paged.compress(tables, keys[:, :500].cuda().unsqueeze(0))          # stored, read back, scored from the reconstruction
+    k_hat = _k_hat_from_packed(packed, comps)
+    q = torch.randn(1, 2, 8, 128)
+    assert score_rel_error(paged.score(packed, q.cuda()).cpu(), orc.logits(q, k_hat)) < 1e-5
+    with pytest.raises(ValueError, match="max_bits=4"):
+        paged.PagedKVCache(tables, [500]).decode(torch.zeros(1, 2, 128, dtype=torch.bfloat16, device="cuda"))
+
+
 def test_decode_split_invariance_at_context_32768():
     """Full-context property: the result does not depend on how the keys are split over blocks."""
     H, N = 8, 32768

@@ -144,8 +144,21 @@ def test_parity_config_retention_cap4_beside_reference_cap8():
     ret8 = orc.attention_metrics(q, keys.unsqueeze(0), k_hat8)["top1_match"]
     assert ret8_gpu == ret8
     assert jq.compute_attention_metrics(q, keys.unsqueeze(0), packed8)["top1_match"] == ret8
-    with pytest.raises(ValueError, match="max_bits=4"):                   # the decode tables stop at 4 bits
-        paged.PagedKVCache(tables8, [N]).decode(torch.zeros(1, H, 128, dtype=torch.bfloat16, device="cuda"))
+    # and decode attention over the cap-8 codes (a 256-entry lookup table per outlier coordinate)
+    assert tables8.n_wide > 0 and tables8.decodable
+    s8_tab = paged.score(packed8, q.cuda(), decode_tables=True).cpu()
+    assert (s8_tab - s8).abs().max().item() < 2e-3 * s8.abs().max().item()          # 16-bit fixed-point tables
+    assert (s8_tab.argmax(-1) == s8.argmax(-1)).float().mean().item() > 0.995    # near ties may resolve differently
+    g8 = torch.Generator().manual_seed(3)
+    v8 = torch.randn(1, H, N, 128, generator=g8).to(torch.bfloat16)
+    cache8 = paged.PagedKVCache(tables8, [N])
+    cache8.prefill(keys.unsqueeze(0).cuda(), v8.cuda())
+    qd = q[:, :, :4].reshape(1, H * 4, 128).to(torch.bfloat16)           # 4 query heads per kv head
+    out8 = cache8.decode(qd.cuda()).cpu()
+    ref8 = orc.decode_attention(qd, k_hat8, v8)
+    err8 = ((out8 - ref8).abs() / ref8.abs().amax(-1, keepdim=True).clamp_min(1e-6)).max().item()
+    assert err8 < 2e-3, err8
+    paged.check_status(cache8.status)
     print(f"top-1 retention at 2.0 bits: gpu (cap 4) {ret_gpu:.4f}, oracle cap 4 {ret4:.4f}; gpu (cap 8, reference default) "
           f"{ret8_gpu:.4f}, oracle cap 8 {ret8:.4f}")
     assert ret_gpu == ret4

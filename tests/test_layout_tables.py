@@ -135,13 +135,13 @@ def test_head_tables_reject_codebooks_beyond_8_bits():
 
 def test_layout_with_wide_columns():
     """Coordinates of 5..8 bits take a byte each in whole words between the nibble region and the byte
-    region; packing and unpacking such records round-trips, and more than 16 wide coordinates are refused."""
+    region; packing and unpacking such records round-trips, and more than 32 wide coordinates are refused."""
     from oracle import reference_port as orc
 
     rng = np.random.default_rng(3)
     for _ in range(20):
         bits = rng.integers(0, 5, 128)
-        wide = rng.choice(128, size=rng.integers(1, 17), replace=False)
+        wide = rng.choice(128, size=rng.integers(1, 33), replace=False)
         bits[wide] = rng.integers(5, 9, len(wide))
         if bits.sum() > 400:
             continue
@@ -158,8 +158,8 @@ def test_layout_with_wide_columns():
         back = orc.unpack_records(rec, lay.col_coord[:n], lay.col_width[:n], lay.col_bitpos[:n], 128)
         assert np.array_equal(back, codes)
     too_many = np.zeros(128, dtype=np.int64)
-    too_many[:17] = 5
-    with pytest.raises(ValueError, match="at most 16"):
+    too_many[:33] = 5
+    with pytest.raises(ValueError, match="at most 32"):
         plan_key_layout(too_many)
 
 
