@@ -91,9 +91,13 @@ extern "C" {
  *                 record, its rows here are indexed by column - desc[30] (desc[31] = how many).  They
  *                 are written, read back and reconstructed by jqk_compress_paged / jqk_decompress_paged
  *                 / jqk_unpack_codes on the CUDA cores.  The score and decode entry points give a wide
- *                 column a 256-entry lookup table (sixteen of the JQK_MAX_TABLES slots of 16 entries;
- *                 desc n_tables counts them); tables whose lookups do not fit have decodable = 0 and
- *                 get JQK_E_UNSUPPORTED there, as do packed-VALUE tables with wide columns
+ *                 column of w bits a lookup table of 2^w entries (2^(w-4) of the JQK_MAX_TABLES slots of
+ *                 16 entries, behind the 16-entry tables that desc n_tables counts); tables whose
+ *                 lookups do not fit the slots have decodable = 0 and get JQK_E_UNSUPPORTED there, as do
+ *                 packed-VALUE tables with wide columns
+ *   unit_wide_thr float [4][256] or NULL: unit decision thresholds of the widths 5..8 (+inf padded); with it
+ *                 (and fwd_limbs) the tensor-core compress kernel serves tables with wide columns: a wide
+ *                 column's code is found by binary search over the row of its width
  *   unit_pre      uint8 [4][128], unit_thr float [4][16] (HOST values, +inf padded), unit_aff float [2]
  *                 (HOST): the shared coarse-to-exact quantiser of the tensor-core kernel for widths
  *                 1..4: cell = low 7 bits of clamp(x * aff[0] + aff[1]) (aff[1] includes 2^23),
@@ -120,6 +124,7 @@ typedef struct jqk_head_tables {
   float unit_aff[2];
   const float* wide_thr;
   const float* wide_cb;
+  const float* unit_wide_thr;
   int32_t decodable;        /* every head's lookup tables fit the decode kernels' table memory (JQK_MAX_TABLES slots) */
   int32_t pad;
 } jqk_head_tables;

@@ -38,6 +38,7 @@ class JqkHeadTables(C.Structure):
         ("unit_aff", C.c_float * 2),
         ("wide_thr", C.c_void_p),
         ("wide_cb", C.c_void_p),
+        ("unit_wide_thr", C.c_void_p),
         ("decodable", C.c_int32),
         ("pad", C.c_int32),
     ]

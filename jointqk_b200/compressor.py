@@ -74,10 +74,16 @@ class PerCoordCompressor:
 
     @property
     def decodable(self) -> bool:
-        """True when the decode and score kernels can read the codes through their lookup tables: at
-        most 4 bits per coordinate.  Wider allocations compress, unpack and reconstruct on the GPU and
-        are scored from their reconstruction; packed decode attention needs ``max_bits=4``."""
-        return int(self.bits_int.max()) <= 4 if self.bits_int.numel() else True
+        """True when the decode and score kernels can read the codes through their lookup tables: the
+        tables of a head (16 entries per group of up to 4 bits, 2^width entries per coordinate of 5..8
+        bits) fit the kernels' table memory.  The reference's default allocation (cap 8) fits on the
+        configs of its evaluation; an object that does not fit still compresses, unpacks and
+        reconstructs on the GPU and is scored from its reconstruction."""
+        if not self.packable:
+            return False
+        from .layout import plan_key_layout
+
+        return plan_key_layout(self.bits_int.cpu().numpy()).decodable if self.bits_int.numel() else True
 
     def _build_codebooks(self) -> None:
         """(d, K_max) table: row j = unit Gaussian centroids(b_j) * float(std_j), +inf padded;
@@ -256,11 +262,11 @@ def build_method_compressor(method: str, sigma_q_for_head: torch.Tensor, sigma_k
     """Reference signature (:261-274) for the method on this path, ``r_sym_waterfill``.
 
     ``max_bits`` defaults to the reference's hard-coded 8 (:367), so the object built here has the
-    reference's bits, standard deviations and codebooks.  The packed GPU format stores at most 4
-    bits per coordinate: a compressor whose allocation goes above that (``.packable`` is False)
-    raises ``ValueError`` on its first ``compress`` / ``roundtrip``, with a message that says to
-    pass ``max_bits=4``.  That is a different allocation with a quality cost where outlier
-    channels want more than 4 bits, so it is never substituted silently.  Other method ids belong
+    reference's bits, standard deviations and codebooks.  The packed GPU format stores up to 8 bits
+    per coordinate (a byte each above 4 bits, at most 32 such coordinates per head) and the decode
+    kernels read them (``.packable``, ``.decodable``); ``max_bits=4`` is a different allocation
+    with a quality cost where outlier channels want more than 4 bits, so it is never substituted
+    silently.  Other method ids belong
     to ablations outside this build and raise ``ValueError`` like an unknown method does in the
     reference."""
     if method == "v3":

@@ -33,7 +33,7 @@ int32_t check_narrow(const jqk_head_tables* t, const char* what) {
 // The score and decode kernels keep all lookup tables of a head in shared memory.
 int32_t check_decodable(const jqk_head_tables* t, const char* what) {
   if (t && t->n_wide > 0 && !t->decodable)
-    return fail(JQK_E_UNSUPPORTED, "%s: the lookup tables of a head do not fit (%d columns above 4 bits take 16 table slots each)", what, t->n_wide);
+    return fail(JQK_E_UNSUPPORTED, "%s: the lookup tables of a head do not fit (%d columns above 4 bits take 2..16 table slots each)", what, t->n_wide);
   return 0;
 }
 

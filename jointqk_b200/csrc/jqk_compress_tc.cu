@@ -65,6 +65,7 @@ enum : int {
   TC_CLS_ALL2 = 3,     // every column 2-bit (or unused), one word: three comparisons each
   TC_CLS_REG4 = 4,     // sixteen 4-bit columns filling two words in order: no constants read at all
   TC_CLS_REG31 = 5,    // eight (3-bit, 1-bit) pairs filling one word in order: no constants read at all
+  TC_CLS_WIDE = 6,     // columns of 5..8 bits (a byte each): binary search over the unit thresholds of the width
 };
 // The multiplier row of a read holds 8 bytes per column (first word, second word) when the unit has two
 // words, else 4 bytes (first word).
@@ -93,6 +94,7 @@ struct TcSmem {
   uint8_t b[3][128 * 128 * 2];       // limb l: [k half][128 columns][64 dims], 128B swizzle
   float c0[128];          // centred tables: the mean in column space, subtracted from every transformed value
   float uthr[64];         // unit decision thresholds, [width - 1][16]
+  float uwide[4 * 256];   // unit decision thresholds of the widths 5..8, +inf padded rows (tables with wide columns)
   uint8_t upre[4 * 128];  // per width and cell: 16 * (width - 1) + a lower bound of the code (at most one short),
                           // i.e. the index into uthr at which the one exact comparison is made
   // one entry per column of every 16-column read: crow_w = the bit pattern of the shared-memory address
@@ -190,7 +192,9 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
       int nw = 1;
       if (w + 1 < n_words) {
         const int cb = wcb[w + 2] - wcb[w + 1];
-        if (ca == 0 || cb == 0 || (ca + cb + CH - 1) / CH < (ca + CH - 1) / CH + (cb + CH - 1) / CH) nw = 2;
+        // (a word of byte-wide codes never shares a unit with a word of narrow ones: their reads differ in kind)
+        const bool same_kind = ca == 0 || cb == 0 || ((meta[wcb[w]] & 15) > 4) == ((meta[wcb[w + 1]] & 15) > 4);
+        if (same_kind && (ca == 0 || cb == 0 || (ca + cb + CH - 1) / CH < (ca + CH - 1) / CH + (cb + CH - 1) / CH)) nw = 2;
       }
       // (a unit without columns still writes its zero words: one read that places nothing)
       const int reads = max(1, (wcb[w + nw] - wcb[w] + CH - 1) / CH);
@@ -217,19 +221,20 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
     const int c_end = wcb[(un.x & 255) + (un.x >> 8)];
     const bool one_word = (un.x >> 8) == 1;
     const bool full = un.y + r * CH + CH <= c_end;
-    bool all1 = true, all2 = true, odd1 = true, reg4 = !one_word && full, reg31 = one_word && full;
+    bool all1 = true, all2 = true, odd1 = true, reg4 = !one_word && full, reg31 = one_word && full, wide = false;
 #pragma unroll 4
     for (int i = 0; i < CH; ++i) {
       const int col = un.y + r * CH + i;
       const int mt = (col < c_end) ? meta[col] : 0;
       const int width = mt & 15, bp = (mt >> 4) & 1023;
+      wide = wide || width > 4;
       all1 = all1 && (width == 0 || width == 1);
       all2 = all2 && (width == 0 || width == 2);
       if (i & 1) odd1 = odd1 && (width == 0 || width == 1);
       reg4 = reg4 && width == 4 && bp == 32 * (un.x & 255) + 4 * i;
       reg31 = reg31 && width == ((i & 1) ? 1 : 3) && bp == 32 * (un.x & 255) + 4 * (i / 2) + 3 * (i & 1);
     }
-    my_cls = reg4 ? TC_CLS_REG4 : reg31 ? TC_CLS_REG31 : (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
+    my_cls = wide ? TC_CLS_WIDE : reg4 ? TC_CLS_REG4 : reg31 ? TC_CLS_REG31 : (all1 && one_word) ? TC_CLS_ALL1 : (all2 && one_word) ? TC_CLS_ALL2
            : odd1 ? TC_CLS_ODD1 : TC_CLS_GENERAL;
   }
   // units to parts: largest first (ties: the earlier unit), each to the part with the least work so far
@@ -286,8 +291,9 @@ __device__ void tc_make_plan(TcPlan& pl, const int32_t* wcb, const int32_t* meta
 
 // Constants of entry e (slot e / 16, column e % 16 of the read) of a planned head: x = the bit pattern
 // of the address of the cell row of the column's width (`pre_addr`: shared-memory address of the four
-// cell rows), y / z = multipliers for the first / second word of the unit.
-__device__ __forceinline__ uint3 tc_const_row(const TcPlan& pl, const int32_t* wcb, const int32_t* meta, uint32_t pre_addr, int e) {
+// cell rows; `uwide_addr`: of the threshold rows of the widths 5..8), y / z = multipliers for the first / second word of the unit.
+__device__ __forceinline__ uint3 tc_const_row(const TcPlan& pl, const int32_t* wcb, const int32_t* meta, uint32_t pre_addr,
+                                              uint32_t uwide_addr, int e) {
   const int ss = pl.slot_step[e >> 4];
   const int2 st = pl.step[ss >> 5][ss & 31];
   const int w_first = st.y & 255, nw = (st.y >> 8) & 255;
@@ -301,6 +307,8 @@ __device__ __forceinline__ uint3 tc_const_row(const TcPlan& pl, const int32_t* w
     else m_hi = 1u << (bp & 31);
     width = max(1, meta[col] & 15);
   }
+  // a read of byte-wide columns: the address of the threshold row of the column's width instead
+  if (((st.y >> 18) & 7) == TC_CLS_WIDE) return make_uint3(uwide_addr + (uint32_t)(max(width, 5) - 5) * 1024u, m_lo, m_hi);
   return make_uint3(pre_addr + (uint32_t)(width - 1) * 128u, m_lo, m_hi);
 }
 
@@ -420,7 +428,41 @@ __device__ __forceinline__ void quant16(const UnitConsts& uc, const float* __res
   }
 }
 
-template <bool CENTERED>
+// Codes of the byte-wide columns of one read (a unit of one or two words of four such columns: the
+// first eight columns of the read at most), by binary search over the +inf padded threshold row of
+// each column's width; `rw`: bit patterns of the rows' shared-memory addresses.  The eight searches
+// run side by side, a step of all of them before the next.
+template <int J>
+__device__ __forceinline__ void quant_wide(const float* __restrict__ rw, const uint2* __restrict__ rm, const float (&v)[CH],
+                                           uint32_t& lo, uint32_t& hi) {
+  constexpr int NW = 8;
+  uint32_t a[NW];
+  const float4 w0 = reinterpret_cast<const float4*>(rw)[0], w1 = reinterpret_cast<const float4*>(rw)[1];
+  a[0] = __float_as_uint(w0.x); a[1] = __float_as_uint(w0.y); a[2] = __float_as_uint(w0.z); a[3] = __float_as_uint(w0.w);
+  a[4] = __float_as_uint(w1.x); a[5] = __float_as_uint(w1.y); a[6] = __float_as_uint(w1.z); a[7] = __float_as_uint(w1.w);
+  static_for<0, 8>([&](auto sc) {
+    constexpr int STEP = 128 >> decltype(sc)::value;
+    static_for<0, NW>([&](auto ic) {
+      constexpr int I = decltype(ic)::value;
+      a[I] += (v[I] >= lds_f32<4 * (STEP - 1)>(a[I])) ? 4u * STEP : 0u;   // a = row address + 4 * code so far
+    });
+  });
+  static_for<0, NW>([&](auto ic) {
+    constexpr int I = decltype(ic)::value;
+    const uint32_t row = __float_as_uint(I < 4 ? (I == 0 ? w0.x : I == 1 ? w0.y : I == 2 ? w0.z : w0.w)
+                                                : (I == 4 ? w1.x : I == 5 ? w1.y : I == 6 ? w1.z : w1.w));
+    const uint32_t code = (a[I] - row) >> 2;
+    if constexpr (J > 1) {
+      const uint2 m = rm[I];
+      lo += code * m.x;
+      hi += code * m.y;
+    } else {
+      lo += code * reinterpret_cast<const uint32_t*>(rm)[I];
+    }
+  });
+}
+
+template <bool CENTERED, bool WIDE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap limb_map,
                    const __grid_constant__ UnitConsts uc, jqk_head_tables tb, TcArgs pa, uint32_t* __restrict__ k_pool) {
@@ -442,6 +484,8 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   for (int e = tid; e < 128; e += TC_THREADS) sm.meta[e] = tb.col_meta[(size_t)head * 128 + e];
   if constexpr (CENTERED)
     for (int e = tid; e < 128; e += TC_THREADS) sm.c0[e] = tb.center_cols[(size_t)head * 128 + e];
+  if constexpr (WIDE)
+    for (int e = tid; e < 4 * 256; e += TC_THREADS) sm.uwide[e] = tb.unit_wide_thr[e];
   for (int e = tid; e <= hd.n_words; e += TC_THREADS) sm.wcb[e] = tb.desc[(size_t)head * JQK_DESC_INTS + 8 + e];
   if (tid == 0) {
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
@@ -518,7 +562,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     if (planned) {  // constants of every read: width words and multipliers
       const int et = tid - 64;
       if (et < sm.plan.n_slots * CH) {
-        const uint3 cr = tc_const_row(sm.plan, sm.wcb, sm.meta, pre_addr, et);
+        const uint3 cr = tc_const_row(sm.plan, sm.wcb, sm.meta, pre_addr, smem_u32(sm.uwide), et);
         const int2 st = sm.plan.step[sm.plan.slot_step[et >> 4] >> 5][sm.plan.slot_step[et >> 4] & 31];
         asm volatile("" ::: "memory");  // the planner's scratch (units) lies in crow_m: every plan read above comes first
         sm.crow_w[et] = __uint_as_float(cr.x);
@@ -573,7 +617,11 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
           const uint2* rm = sm.crow_m + (cur.x >> 8) * CH;
           if (cur.y & (1 << 16)) lo = hi = 0u;
           const bool two = (cur.y & 0xff00) == 0x200;
-          switch ((cur.y >> 18) & 7) {  // warp-uniform
+          const int cls = (cur.y >> 18) & 7;  // warp-uniform
+          if (WIDE && cls == TC_CLS_WIDE) {
+            if (two) quant_wide<2>(rw, rm, v, lo, hi);
+            else quant_wide<1>(rw, rm, v, lo, hi);
+          } else switch (cls) {
             case TC_CLS_REG4: quant16<TC_CLS_REG4, 2>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
             case TC_CLS_REG31: quant16<TC_CLS_REG31, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
             case TC_CLS_ALL2: quant16<TC_CLS_ALL2, 1>(uc, rw, rm, v, pre_base, uthr_addr, lo, hi); break;
@@ -612,7 +660,9 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
             float x = v[0];  // v[i] without dynamic register indexing
 #pragma unroll
             for (int u = 1; u < CH; ++u) x = (u == i) ? v[u] : x;
-            cur |= search_code(x, sm.uthr + ((m & 15) - 1) * 16, m & 15) << (bp & 31);
+            const int wd = m & 15;
+            const float* thr_row = (WIDE && wd > 4) ? sm.uwide + (wd - 5) * 256 : sm.uthr + (wd - 1) * 16;
+            cur |= search_code(x, thr_row, wd) << (bp & 31);
           }
         }
         while (cur_w < w_hi) {
@@ -648,7 +698,9 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
                             const int32_t* n_tokens, const int32_t* seq_starts, int32_t max_tokens,
                             const int32_t* page_table, int32_t page_table_stride, int32_t n_pages,
                             uint32_t* k_pool, int32_t* status, cudaStream_t st) {
-  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || tables->n_wide > 0 || (tables->center && !tables->center_cols)) return 1;
+  if (key_dtype != JQK_DTYPE_BF16 || tables->d != 128 || !tables->fwd_limbs || (tables->n_wide > 0 && !tables->unit_wide_thr) ||
+      (tables->center && !tables->center_cols))
+    return 1;
   if ((uintptr_t)keys % 16 || (token_stride * 2) % 16 || (head_stride * 2) % 16 || (seq_stride * 2) % 16) return 1;
   if ((uintptr_t)tables->fwd_limbs % 16 || max_tokens < TC_TILE || !tables->unit_pre) return 1;
   CUtensorMap key_map, limb_map;
@@ -686,12 +738,19 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
   // host form of the grid: cell = clamp(round(x * aff[0] + aff[1] - 2^23), 0, 127)
   uc.cs = tables->unit_aff[0] * (1.f / 127.f);
   uc.co = (tables->unit_aff[1] - 8388608.f) * (1.f / 127.f);
-  JQK_SMEM_ONCE(compress_tc_kernel<false>, smem, "tensor-core compress smem attribute");
-  JQK_SMEM_ONCE(compress_tc_kernel<true>, smem, "tensor-core compress smem attribute");
-  if (tables->center)
-    compress_tc_kernel<true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  JQK_SMEM_ONCE((compress_tc_kernel<false, false>), smem, "tensor-core compress smem attribute");
+  JQK_SMEM_ONCE((compress_tc_kernel<true, false>), smem, "tensor-core compress smem attribute");
+  JQK_SMEM_ONCE((compress_tc_kernel<false, true>), smem, "tensor-core compress smem attribute");
+  JQK_SMEM_ONCE((compress_tc_kernel<true, true>), smem, "tensor-core compress smem attribute");
+  const bool wide = tables->n_wide > 0;
+  if (tables->center && wide)
+    compress_tc_kernel<true, true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  else if (tables->center)
+    compress_tc_kernel<true, false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  else if (wide)
+    compress_tc_kernel<false, true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
   else
-    compress_tc_kernel<false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+    compress_tc_kernel<false, false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
   return 0;
 }

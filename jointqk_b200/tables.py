@@ -83,7 +83,7 @@ class HeadTables:
         wide_thr = np.full((H, MAX_WIDE, 256), np.inf, np.float32)
         wide_cb = np.zeros((H, MAX_WIDE, 256), np.float32)
         col_scale = np.ones((H, MAX_COLS), np.float32)     # 1 / sigma of the column's coordinate
-        unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 5)}
+        unit = {b: unit_gaussian_centroids(b).numpy() for b in range(1, 9 if self.n_wide else 5)}
         scaled_ok = True
         cb_np, fwd_np, inv_np = cb.numpy(), fwd.numpy(), inv.numpy()
         for h, lay in enumerate(self.layouts):
@@ -116,10 +116,7 @@ class HeadTables:
             # top levels gives 1 / sigma back to an ulp, which is all the scaled transform needs
             for c in range(n):
                 w = int(lay.col_width[c])
-                if w > 4:            # wide columns never reach the tensor-core kernel
-                    scaled_ok = False
-                    continue
-                top = float(rows[c, (1 << w) - 1])
+                top = float(rows[c, (1 << w) - 1]) if w <= 4 else float(wide_cb[h, c - lay.wide_first, (1 << w) - 1])
                 if not (top > 1e-30 and np.isfinite(top)):
                     scaled_ok = False
                 else:
@@ -141,6 +138,16 @@ class HeadTables:
         u_thr, u_pre, u_aff = unit_quantiser_tables(unit)
         self.unit_thr, self.unit_aff = u_thr, u_aff
         self.unit_pre = up(u_pre)
+        # unit thresholds of the widths 5..8, a 256-entry row each (+inf padded): the tensor-core kernel
+        # finds a wide column's code by binary search over the row of its width
+        self.unit_wide_thr = None
+        if self.n_wide:
+            uw = np.full((4, 256), np.inf, np.float32)
+            for b in range(5, 9):
+                rows_b = np.zeros((1, 256), np.float32)
+                rows_b[0, : 2 ** b] = unit[b]
+                uw[b - 5, :255] = decision_thresholds(rows_b, np.array([b]), max_levels=256)[0]
+            self.unit_wide_thr = up(uw)
         self.fwd_limbs = None
         if scaled_ok:
             scaled = torch.from_numpy(fwd_cols * col_scale[:, None, :])
@@ -170,6 +177,7 @@ class HeadTables:
             unit_aff=(C.c_float * 2)(float(u_aff[0]), float(u_aff[1])),
             wide_thr=None if self.wide_thr is None else self.wide_thr.data_ptr(),
             wide_cb=None if self.wide_cb is None else self.wide_cb.data_ptr(),
+            unit_wide_thr=None if self.unit_wide_thr is None else self.unit_wide_thr.data_ptr(),
             decodable=int(self.decodable), pad=0)
 
     @property
@@ -185,11 +193,11 @@ class HeadTables:
 
     def require_decodable(self, what: str) -> None:
         """The decode and score kernels keep every lookup table of a head in shared memory: 208 slots of
-        16 entries, a column of 5..8 bits taking 16 of them."""
+        16 entries, a column of w = 5..8 bits taking 2^(w-4) of them."""
         if not self.decodable:
             raise ValueError(
                 f"{what}: the lookup tables of a head exceed the kernels' table memory ({self.n_wide} columns above 4 bits "
-                "take 16 table slots each).  Fit with a lower cap, e.g. max_bits=4, for packed decode attention; "
+                "take 2..16 table slots each).  Fit with a lower cap, e.g. max_bits=4, for packed decode attention; "
                 "compress, unpack, decompress, roundtrip and the evaluation scores work as they are")
 
     @property
