@@ -366,10 +366,103 @@ def bench_compress(device, hbm_gbs: float, peak_kind: str) -> dict:
     n_keys = T * N_KV_HEADS * B
     bytes_per_key = HEAD_DIM * 2 + tables.payload_bytes_per_key
     gbs = n_keys * bytes_per_key / (ms * 1e-3) / 1e9
-    return {"metric": "keys compressed/s", "value": n_keys / (ms * 1e-3), "ms_per_launch": ms,
-            "workload": "1 layer x 4 sequences x 8 kv heads x 131072 bf16 keys, 2.5 bits/coord, 16-token pages",
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
-                         "bytes_per_key": bytes_per_key, "peak_kind": peak_kind}}
+    res = {"metric": "keys compressed/s", "value": n_keys / (ms * 1e-3), "ms_per_launch": ms,
+           "workload": "1 layer x 4 sequences x 8 kv heads x 131072 bf16 keys, 2.5 bits/coord, 16-token pages",
+           "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_gbs, "unit": "GB/s", "frac": gbs / hbm_gbs,
+                        "bytes_per_key": bytes_per_key, "peak_kind": peak_kind}}
+    # the same keys at the reference's default cap of 8 bits (outlier coordinates: a byte each)
+    del k_pool
+    comps8, _ = fit_sigma_k_heads(keys[0, :, :4096].float().cpu(), 2.5, max_bits=8)
+    tables8 = jq.HeadTables.from_compressors(comps8, device=device)
+    k_pool8 = paged.alloc_k_pool(tables8, used)
+    run8 = lambda: paged.compress_into(tables8, keys, n_tok, T, page_table, k_pool8, status)
+    for _ in range(3):
+        run8()
+    torch.cuda.synchronize(device)
+    e0.record()
+    for _ in range(reps):
+        run8()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms8 = e0.elapsed_time(e1) / reps
+    bpk8 = HEAD_DIM * 2 + tables8.payload_bytes_per_key
+    res["reference_default_cap8"] = {"ms_per_launch": ms8, "value": n_keys / (ms8 * 1e-3), "byte_wide_columns": tables8.n_wide,
+                                     "words_per_record": tables8.words_per_record, "bytes_per_key": bpk8,
+                                     "frac": n_keys * bpk8 / (ms8 * 1e-3) / 1e9 / hbm_gbs}
+    paged.check_status(status)
+    return res
+
+
+def bench_reference_cap8(device, hbm_gbs: float, peak_kind: str) -> dict:
+    """The headline decode step, the generate step and the prompt's compression with the reference's
+    own allocation: the same 2.0 bits per coordinate, its default cap of 8 bits instead of 4
+    (per_coord_quantization.py:367), so the outlier coordinates carry byte-wide codes."""
+    import jointqk_b200 as jq
+    from jointqk_b200 import paged
+    from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
+
+    keys = torch.stack([spectrum_keys(CTX, config_seed(1, 0, h), device=device) for h in range(N_KV_HEADS)])
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), B_AVG, max_bits=8)
+    tables = jq.HeadTables.from_compressors(comps, device=device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(config_seed(1, 0, 0) + 7)
+    n_copies = 4
+    caches = []
+    for c in range(n_copies):
+        cache = paged.PagedKVCache(tables, [CTX])
+        v = torch.randn(1, N_KV_HEADS, CTX, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+        cache.prefill(keys.roll(c * 17, 1).unsqueeze(0), v)
+        caches.append(cache)
+    q = torch.randn(1, N_Q_HEADS, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    tps = paged.default_split(1, N_Q_HEADS, N_KV_HEADS, CTX)
+    ws = paged.DecodeWorkspace(1, N_Q_HEADS, N_KV_HEADS, -(-CTX // tps), device)
+    out = torch.empty((1, N_Q_HEADS, HEAD_DIM), dtype=torch.float32, device=device)
+
+    def step(i: int) -> None:
+        c = caches[i % n_copies]
+        paged.decode_attend(tables, q, c.seq_lens, CTX, c.page_table, c.k_pool, c.v_pool, out, ws, c.status, tps)
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for i in range(n_copies):
+            step(i)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(n_copies):
+                step(i)
+    prewarm(lambda _i: graph.replay(), device, 0.1)
+    reps = 100
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / (reps * n_copies)
+    paged.check_status(caches[0].status)
+    alg = decode_algorithmic_bytes(tables)["total"]
+    res = {"workload": "the headline decode step with the reference's default cap of 8 bits per coordinate "
+                       "(%d byte-wide columns per head at most, %d words per record)" % (tables.n_wide, tables.words_per_record),
+           "ms_per_step": ms, "value": 1.0 / (ms * 1e-3), "unit": UNIT,
+           "roofline": {"bound": "hbm", "achieved": alg / (ms * 1e-3) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                        "frac": alg / (ms * 1e-3) / 1e9 / hbm_gbs, "peak_kind": peak_kind}}
+    # the generate step (one launch: append, attend, advance)
+    steps = 128
+    new_k = torch.randn(1, N_KV_HEADS, steps + 8, HEAD_DIM, generator=gen, device=device)
+    new_v = torch.randn(1, N_KV_HEADS, steps + 8, HEAD_DIM, generator=gen, device=device).to(torch.bfloat16)
+    cache = caches[0]
+    for t in range(8):
+        cache.generate_step(new_k[:, :, t:t + 1], new_v[:, :, t:t + 1], q)
+    torch.cuda.synchronize(device)
+    e0.record()
+    for t in range(8, 8 + steps):
+        cache.generate_step(new_k[:, :, t:t + 1], new_v[:, :, t:t + 1], q)
+    e1.record()
+    torch.cuda.synchronize(device)
+    res["generate_step_ms"] = e0.elapsed_time(e1) / steps
+    paged.check_status(cache.status)
+    return res
 
 
 def bench_decode_batch(device, hbm_gbs: float, peak_kind: str) -> dict:
@@ -965,6 +1058,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             extra["calibration_moments"] = bench_moments(device, hbm_gbs, tflops, peak_kind)
             extra["decode_batch"] = bench_decode_batch(device, hbm_gbs, peak_kind)
             extra["decode_packed_values"] = bench_decode_packed_values(device, hbm_gbs, peak_kind)
+            extra["reference_default_cap8"] = bench_reference_cap8(device, hbm_gbs, peak_kind)
         del caches[:]
         torch.cuda.empty_cache()
         # the partitioned workloads run at every N: sequences, tokens and (sequence, head) units over the ranks
@@ -1055,7 +1149,7 @@ def main() -> None:
     ap.add_argument("--workload", default="headline", choices=["headline", "batch64"],
                     help="headline: the single-layer context-32768 step (default, what the JSON contract names); "
                          "batch64: the 32-layer, 64-sequence decode config sharded by sequence over the ranks")
-    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "packed_values", "generate", "scale"],
+    ap.add_argument("--stage", default="all", choices=["all", "compress", "moments", "decode_batch", "values", "packed_values", "generate", "cap8", "scale"],
                     help="run only one of the secondary stages (or the three partitioned workloads) and print its JSON")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1077,7 +1171,8 @@ def main() -> None:
         res = (bench_compress(dev, hbm, kind) if args.stage == "compress" else
                bench_decode_batch(dev, hbm, kind) if args.stage == "decode_batch" else
                bench_value_store(dev, hbm, kind) if args.stage == "values" else
-               bench_decode_packed_values(dev, hbm, kind) if args.stage == "packed_values" else bench_moments(dev, hbm, tf, kind))
+               bench_decode_packed_values(dev, hbm, kind) if args.stage == "packed_values" else
+               bench_reference_cap8(dev, hbm, kind) if args.stage == "cap8" else bench_moments(dev, hbm, tf, kind))
         print(json.dumps(res), flush=True)
         return
     if world > 1:

@@ -92,7 +92,7 @@ extern "C" {
  *                 are written, read back and reconstructed by jqk_compress_paged / jqk_decompress_paged
  *                 / jqk_unpack_codes on the CUDA cores.  The score and decode entry points give a wide
  *                 column of w bits a lookup table of 2^w entries (2^(w-4) of the JQK_MAX_TABLES slots of
- *                 16 entries, behind the 16-entry tables that desc n_tables counts); tables whose
+ *                 16 entries, behind the 16-entry tables; desc n_tables counts them all); tables whose
  *                 lookups do not fit the slots have decodable = 0 and get JQK_E_UNSUPPORTED there, as do
  *                 packed-VALUE tables with wide columns
  *   unit_wide_thr float [4][256] or NULL: unit decision thresholds of the widths 5..8 (+inf padded); with it

@@ -71,8 +71,13 @@ score_kernel(jqk_head_tables tb, int table_mode, const void* __restrict__ q, int
   const size_t q_elem0 = (((size_t)seq * n_q_heads + qh0) * n_queries + qi) * d;
   const char* q_ptr = (const char*)q + q_elem0 * (q_dtype == JQK_DTYPE_F32 ? 4 : 2);
   {
-    const TableLoads ld = issue_table_loads(tb, head, d, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
-    build_tables(sm, hd, ld, hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr, tb.col_meta + (size_t)head * 128);
+    if (tb.n_wide) {  // (the struct's count: the same in every block)
+      const TableLoads ld = issue_table_loads<true>(tb, head, d, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
+      build_tables<true>(sm, hd, ld, tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256);
+    } else {
+      const TableLoads ld = issue_table_loads(tb, head, d, q_ptr, q_dtype, (size_t)n_queries * d, n_group);
+      build_tables(sm, hd, ld);
+    }
   }
   const float* wide_cb = hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr;
   const float inv_sqrt_d = 1.0f / sqrtf((float)d);
@@ -273,9 +278,14 @@ decode_tables_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, in
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const HeadDesc hd = load_desc(tb.desc, head);
   {
-    const TableLoads ld = issue_table_loads(tb, head, hd.d, q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d,
-                                            JQK_DTYPE_BF16, (size_t)hd.d, n_group);
-    build_tables(sm, hd, ld, hd.n_wide ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr, tb.col_meta + (size_t)head * 128);
+    const __nv_bfloat16* qg = q + ((size_t)seq * n_q_heads + head * group + g0) * hd.d;
+    if (tb.n_wide) {
+      const TableLoads ld = issue_table_loads<true>(tb, head, hd.d, qg, JQK_DTYPE_BF16, (size_t)hd.d, n_group);
+      build_tables<true>(sm, hd, ld, tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256);
+    } else {
+      const TableLoads ld = issue_table_loads(tb, head, hd.d, qg, JQK_DTYPE_BF16, (size_t)hd.d, n_group);
+      build_tables(sm, hd, ld);
+    }
   }
   TableRecord* rec = recs + (size_t)seq * gridDim.x + blockIdx.x;
   const uint4* src = reinterpret_cast<const uint4*>(sm.lut);
@@ -511,7 +521,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const int qh0 = head * group + g0;
   TableLoads tloads;
   if constexpr (BUILD_IN_BLOCK)
-    tloads = issue_table_loads(tb, head, D, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
+    tloads = issue_table_loads<WIDE>(tb, head, D, q + ((size_t)seq * n_q_heads + qh0) * D, JQK_DTYPE_BF16, (size_t)D, n_group);
   if constexpr (APPEND) len += 1;  // this launch attends over the key it appends
   // Append variant: every block of the launch passes here exactly once on its way out, all of its
   // threads together.  Each has read its length by then, so the block that takes the last ticket
@@ -654,10 +664,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   float sc[JQK_MAX_GROUP];
   TableView tview;
   if constexpr (BUILD_IN_BLOCK) {
-    if constexpr (WIDE)
-      build_tables(sm.t.build, hd, tloads, tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256, tb.col_meta + (size_t)head * 128);
-    else
-      build_tables(sm.t.build, hd, tloads);
+    build_tables<WIDE>(sm.t.build, hd, tloads, WIDE ? tb.wide_cb + (size_t)head * JQK_MAX_WIDE * 256 : nullptr);
     tview = TableView{sm.t.build.lut, sm.t.build.dshift, sm.t.build.bias, sm.t.build.woff};
 #pragma unroll
     for (int h = 0; h < JQK_MAX_GROUP; ++h) sc[h] = sm.t.build.scale[h];

@@ -45,6 +45,7 @@ struct TableSmem {
   int wcb[JQK_MAX_WORDS + 4];                    // first column of every physical record word
   uint8_t woff[JQK_MAX_WIDE];                    // wide column i: first table slot of its 2^width-entry table,
                                                  // counted from the end of the 16-entry tables
+  uint8_t wwidth[JQK_MAX_WIDE];                  // wide column i: its code width (5..8)
 };
 
 // Scan-order word of table t: nibble word t/8, or n_a_words + byte word.
@@ -85,11 +86,16 @@ struct TableLoads {
   float4 cv[2];
   int4 fv;
   int wv;  // word_col_begin[tid] of the head descriptor (tid <= JQK_MAX_WORDS)
+  // tables with wide columns only: warp i holds the 256-entry level row of wide column i (zero beyond
+  // the column's levels), lane l the entries l + 32 u; and the descriptor of column tid
+  float wl[8];
+  int mv;
 };
 
 //   q_base + h * q_head_stride : the d values of query head h of the group (h < n_group)
 // Needs blockDim.x >= TBL_THREADS.  Codebooks and table composition are read at their full
 // per-head extent (both arrays are allocated at it), so the head descriptor is not needed yet.
+template <bool WIDE = false>
 __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& tb, int head, int d, const void* q_base,
                                                         int q_dtype, size_t q_head_stride, int n_group) {
   static_assert(JQK_MAX_GROUP * JQK_MAX_DIM <= 2 * TBL_THREADS && JQK_MAX_COLS * 4 <= 2 * TBL_THREADS &&
@@ -116,6 +122,13 @@ __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& t
   }
   ld.fv = (tid < JQK_MAX_TABLES) ? __ldg(f4 + tid) : make_int4(-1, -1, -1, -1);
   ld.wv = (tid <= JQK_MAX_WORDS) ? __ldg(tb.desc + (size_t)head * JQK_DESC_INTS + 8 + tid) : 0;
+  if constexpr (WIDE) {
+    // (the rows are allocated at their full extent for every head, so the head's count is not needed yet)
+    const float* row = tb.wide_cb + ((size_t)head * JQK_MAX_WIDE + (tid >> 5)) * 256 + (tid & 31);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) ld.wl[u] = (tid < 32 * JQK_MAX_WIDE) ? __ldg(row + 32 * u) : 0.f;
+    ld.mv = (tid < JQK_MAX_COLS) ? __ldg(tb.col_meta + (size_t)head * JQK_MAX_COLS + tid) : 0;
+  }
   return ld;
 }
 
@@ -124,11 +137,11 @@ __device__ __forceinline__ TableLoads issue_table_loads(const jqk_head_tables& t
 // words: it sums the partial projections of its word's columns and bounds that word's tables by
 // itself, so only the word maxima cross warps (one barrier); every warp then derives all shifts
 // and the entries are quantised by all threads.
-// `wide_cb`: the 256-entry level rows of this head's wide columns (null when it has none),
-// `col_meta`: this head's column descriptors (read for the wide columns only).
+// WIDE: the head may have wide columns; `wide_cb`: their 256-entry level rows.  The loads hold the
+// rows of the first (number of warps) wide columns; further ones are read here.
+template <bool WIDE = false>
 __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, const TableLoads& ld,
-                                             const float* __restrict__ wide_cb = nullptr,
-                                             const int32_t* __restrict__ col_meta = nullptr) {
+                                             const float* __restrict__ wide_cb = nullptr) {
   const int tid = threadIdx.x, nthr = blockDim.x;  // nthr >= TBL_THREADS
   const int cg = tid & 31, rg = (tid >> 5) & 7;  // columns 4*cg..4*cg+3, rows rg + 8*r
   const int lane = tid & 31, warp = tid >> 5, n_warps = nthr >> 5;
@@ -141,6 +154,10 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
   }
   if (tid < JQK_MAX_TABLES) reinterpret_cast<int4*>(sm.fields)[tid] = ld.fv;
   if (tid <= JQK_MAX_WORDS) sm.wcb[tid] = ld.wv;
+  if constexpr (WIDE) {
+    const int wi = tid - hd.wide_first;
+    if (tid < JQK_MAX_COLS && wi >= 0 && wi < hd.n_wide) sm.wwidth[wi] = (uint8_t)(ld.mv & 15);
+  }
   __syncthreads();
   if (projector) {
     float a[4][JQK_MAX_GROUP];
@@ -164,14 +181,14 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       *reinterpret_cast<float4*>(sm.part[rg][4 * cg + k]) = make_float4(a[k][0], a[k][1], a[k][2], a[k][3]);
   }
   __syncthreads();
-  const int n_wide = wide_cb ? hd.n_wide : 0, n_w_words = (n_wide + 3) >> 2;
+  const int n_wide = WIDE ? hd.n_wide : 0, n_w_words = (n_wide + 3) >> 2;
   const int n_a_words = hd.n_a_words, n_scan_words = n_w_words + hd.n_a_words + hd.n_c_words;
   const int n_narrow_tables = 8 * hd.n_a_words + 12 * hd.n_c_words;
   // column bounds |q'_c| * max |level| reuse the raw-query staging, which the projection is done with
   float4* colb = reinterpret_cast<float4*>(&sm.qraw[0][0]);  // [JQK_MAX_COLS]
   // slots of the wide columns' tables: exclusive prefix sum of 2^(width - 4)
   if (n_wide && warp == 0) {
-    int slots = (lane < n_wide) ? (1 << ((__ldg(col_meta + hd.wide_first + lane) & 15) - 4)) : 0;
+    int slots = (lane < n_wide) ? (1 << ((int)sm.wwidth[lane] - 4)) : 0;
     int incl = slots;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -180,6 +197,29 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     }
     if (lane < n_wide) sm.woff[lane] = (uint8_t)(incl - slots);
   }
+  // wide columns, a warp each: the projected query and the bound |q'_c| * max |level| (the row is
+  // zero beyond its levels, so its largest magnitude is that of the levels)
+  if constexpr (WIDE) {
+    for (int i = warp; i < n_wide; i += n_warps) {
+      float big = 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        big = fmaxf(big, fabsf(i < n_warps ? ld.wl[u] : __ldg(wide_cb + (size_t)i * 256 + lane + 32 * u)));
+      big = warp_max(big);
+      if (lane == 0) {
+        const int c = hd.wide_first + i;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const float4 p = *reinterpret_cast<const float4*>(sm.part[r][c]);
+          s.x += p.x; s.y += p.y; s.z += p.z; s.w += p.w;
+        }
+        *reinterpret_cast<float4*>(sm.qproj[c]) = s;
+        colb[c] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
+      }
+    }
+    if (n_wide) __syncthreads();   // (block-uniform)
+  }
   // ---- per warp and scan word: projected queries of the word's columns, bound of its tables ----
   for (int sw = warp; sw < n_scan_words; sw += n_warps) {
     // scan order: wide words (physical words n_a_words ..), nibble words (0 ..), byte words (from the end)
@@ -187,7 +227,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
     const int nw = sw - n_w_words;                                                // index among the narrow scan words
     const int pw = is_wide ? n_a_words + sw : (nw < n_a_words) ? nw : hd.n_words - 1 - (nw - n_a_words);  // physical word
     const int c_first = sm.wcb[pw], n_c = sm.wcb[pw + 1] - c_first;            // <= 32 columns
-    if (lane < n_c) {
+    if (lane < n_c && !is_wide) {
       const int c = c_first + lane;
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -198,15 +238,10 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       *reinterpret_cast<float4*>(sm.qproj[c]) = s;
       // levels are sorted and padded with zeros: the largest magnitude of a row is its largest |level|
       float big = 0.f;
-      if (is_wide) {
-        const float* row = wide_cb + (size_t)(c - hd.wide_first) * 256;
-        big = fmaxf(fabsf(__ldg(row)), fabsf(__ldg(row + (1 << (__ldg(col_meta + c) & 15)) - 1)));
-      } else {
 #pragma unroll
-        for (int l4 = 0; l4 < 4; ++l4) {
-          const float4 lv = *reinterpret_cast<const float4*>(sm.cb + c * 16 + 4 * l4);
-          big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
-        }
+      for (int l4 = 0; l4 < 4; ++l4) {
+        const float4 lv = *reinterpret_cast<const float4*>(sm.cb + c * 16 + 4 * l4);
+        big = fmaxf(fmaxf(big, fmaxf(fabsf(lv.x), fabsf(lv.y))), fmaxf(fabsf(lv.z), fabsf(lv.w)));
       }
       colb[c] = make_float4(fabsf(s.x) * big, fabsf(s.y) * big, fabsf(s.z) * big, fabsf(s.w) * big);
     }
@@ -293,19 +328,23 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       sm.lut[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
     }
   }
-  // the tables of the wide columns: entry = q'_c * level, behind the 16-entry tables
-  for (int i = 0; i < n_wide; ++i) {
-    const int levels = 1 << (__ldg(col_meta + hd.wide_first + i) & 15);
-    const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, i >> 2));
-    const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[hd.wide_first + i]);
-    uint2* dst = sm.lut + n_entries + (int)sm.woff[i] * 16;
-    for (int e = tid; e < levels; e += nthr) {
-      const float lv = __ldg(wide_cb + (size_t)i * 256 + e);
-      const uint32_t q0 = __float_as_uint(fmaf(qp.x * lv, inv[0] * up, 12582912.f + 32768.f));
-      const uint32_t q1 = __float_as_uint(fmaf(qp.y * lv, inv[1] * up, 12582912.f));
-      const uint32_t q2 = __float_as_uint(fmaf(qp.z * lv, inv[2] * up, 12582912.f + 32768.f));
-      const uint32_t q3 = __float_as_uint(fmaf(qp.w * lv, inv[3] * up, 12582912.f));
-      dst[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
+  // the tables of the wide columns: entry = q'_c * level, behind the 16-entry tables; a warp per column
+  if constexpr (WIDE) {
+    for (int i = warp; i < n_wide; i += n_warps) {
+      const int levels = 1 << (int)sm.wwidth[i];
+      const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, i >> 2));
+      const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[hd.wide_first + i]);
+      uint2* dst = sm.lut + n_entries + (int)sm.woff[i] * 16;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int e = lane + 32 * u;
+        const float lv = i < n_warps ? ld.wl[u] : __ldg(wide_cb + (size_t)i * 256 + e);
+        const uint32_t q0 = __float_as_uint(fmaf(qp.x * lv, inv[0] * up, 12582912.f + 32768.f));
+        const uint32_t q1 = __float_as_uint(fmaf(qp.y * lv, inv[1] * up, 12582912.f));
+        const uint32_t q2 = __float_as_uint(fmaf(qp.z * lv, inv[2] * up, 12582912.f + 32768.f));
+        const uint32_t q3 = __float_as_uint(fmaf(qp.w * lv, inv[3] * up, 12582912.f));
+        if (e < levels) dst[e] = make_uint2(__byte_perm(q0, q1, 0x5410), __byte_perm(q2, q3, 0x5410));
+      }
     }
   }
   __syncthreads();
@@ -371,14 +410,18 @@ __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, i
   const int* dshift = sm.dshift;
   if constexpr (WIDE) {
     const char* lw = lb + (size_t)(8 * n_a_words + 12 * n_c_words) * 128;
-    uint32_t x = 0;
+    const int n_w_words = (n_wide + 3) >> 2;
 #pragma unroll 1
-    for (int i = 0; i < n_wide; ++i) {
-      if ((i & 3) == 0) {
-        x = word(n_a_words + (i >> 2));
-        acc.shift(dshift[i >> 2]);
+    for (int j = 0; j < n_w_words; ++j) {
+      const uint32_t x = word(n_a_words + j);
+      const uint32_t wo = reinterpret_cast<const uint32_t*>(sm.woff)[j];  // table slots of the word's four columns
+      acc.shift(dshift[j]);
+      const int left = n_wide - 4 * j;  // (the last word may hold fewer than four columns)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t off = ((wo >> (8 * b)) & 255u) * 128u + ((x >> (8 * b)) & 255u) * 8u;
+        if (b < left) acc.add(*reinterpret_cast<const uint2*>(lw + off));
       }
-      acc.add(*reinterpret_cast<const uint2*>(lw + (int)sm.woff[i] * 128 + ((x >> (8 * (i & 3))) & 255u) * 8));
     }
     dshift += (n_wide + 3) >> 2;
   }
