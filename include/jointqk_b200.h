@@ -39,6 +39,7 @@ extern "C" {
 #define JQK_MAX_COLS 128       /* coordinates that carry >0 bits, padded to 16 */
 #define JQK_MAX_WORDS 16       /* uint32 words per record */
 #define JQK_MAX_WIDE 32        /* columns of 5..8 bits per head */
+#define JQK_MAX_VALUE_WIDE_LEVELS 6144 /* sum of 2^width over a head's wide columns that packed-VALUE decode holds */
 #define JQK_MAX_TABLES 208     /* lookups per record (see jqk_head_tables.table_fields) */
 #define JQK_DESC_INTS 32       /* int32 per head in jqk_head_tables.desc */
 #define JQK_MAX_GROUP 4        /* q heads scored together by one thread block */
@@ -93,8 +94,10 @@ extern "C" {
  *                 / jqk_unpack_codes on the CUDA cores.  The score and decode entry points give a wide
  *                 column of w bits a lookup table of 2^w entries (2^(w-4) of the JQK_MAX_TABLES slots of
  *                 16 entries, behind the 16-entry tables; desc n_tables counts them all); tables whose
- *                 lookups do not fit the slots have decodable = 0 and get JQK_E_UNSUPPORTED there, as do
- *                 packed-VALUE tables with wide columns
+ *                 lookups do not fit the slots have decodable = 0 and get JQK_E_UNSUPPORTED there.  As
+ *                 packed-VALUE tables (jqk_decode_attend_packed_values) the levels of a head's wide
+ *                 columns are held as they are, JQK_MAX_VALUE_WIDE_LEVELS entries at most
+ *                 (value_decodable)
  *   unit_wide_thr float [4][256] or NULL: unit decision thresholds of the widths 5..8 (+inf padded); with it
  *                 (and fwd_limbs) the tensor-core compress kernel serves tables with wide columns: a wide
  *                 column's code is found by binary search over the row of its width
@@ -126,7 +129,7 @@ typedef struct jqk_head_tables {
   const float* wide_cb;
   const float* unit_wide_thr;
   int32_t decodable;        /* every head's lookup tables fit the decode kernels' table memory (JQK_MAX_TABLES slots) */
-  int32_t pad;
+  int32_t value_decodable;  /* as VALUE tables: the levels of every head's wide columns fit (JQK_MAX_VALUE_WIDE_LEVELS) */
 } jqk_head_tables;
 
 /* Library version: major << 16 | minor. */

@@ -40,7 +40,7 @@ class JqkHeadTables(C.Structure):
         ("wide_cb", C.c_void_p),
         ("unit_wide_thr", C.c_void_p),
         ("decodable", C.c_int32),
-        ("pad", C.c_int32),
+        ("value_decodable", C.c_int32),
     ]
 
 

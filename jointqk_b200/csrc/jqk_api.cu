@@ -23,13 +23,6 @@ int32_t check_tables(const jqk_head_tables* t) {
   return 0;
 }
 
-// Paths that take 0..4 bits per coordinate only (packed values).
-int32_t check_narrow(const jqk_head_tables* t, const char* what) {
-  if (t && t->n_wide > 0)
-    return fail(JQK_E_UNSUPPORTED, "%s takes tables with at most 4 bits per coordinate; these hold %d wider column(s)", what, t->n_wide);
-  return 0;
-}
-
 // The score and decode kernels keep all lookup tables of a head in shared memory.
 int32_t check_decodable(const jqk_head_tables* t, const char* what) {
   if (t && t->n_wide > 0 && !t->decodable)

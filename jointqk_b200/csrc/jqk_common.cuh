@@ -52,7 +52,6 @@ inline int32_t cuda_fail(cudaError_t e, const char* what) {
 
 // Validates the table struct against the limits the kernels are written for.
 int32_t check_tables(const jqk_head_tables* t);
-int32_t check_narrow(const jqk_head_tables* t, const char* what);
 int32_t check_decodable(const jqk_head_tables* t, const char* what);
 
 // ---------------------------------------------------------------------------------------

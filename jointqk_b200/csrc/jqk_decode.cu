@@ -152,6 +152,7 @@ template <> struct alignas(128) TileStageT<true> {
   uint8_t vq[2][K_STAGE_STRIDE];     // the two pages of V codes of the current tile
 };
 
+constexpr int VQ_WIDE_ENTRIES = JQK_MAX_VALUE_WIDE_LEVELS;   // levels of all byte-wide value columns of a head that the block can hold
 template <bool VQ> struct DecodeSmemT;
 template <> struct DecodeSmemT<false> {
   union {            // the tables this block scores with:
@@ -189,8 +190,10 @@ template <> struct DecodeSmemT<true> {
   uint32_t apv_words[JQK_MAX_WORDS];
   float ap_dot[JQK_MAX_GROUP];
   int ap_page, ap_last;
-  alignas(16) int32_t vmeta[JQK_MAX_COLS];        // value columns: width | bit position << 4
-  __nv_bfloat16 vcb[JQK_MAX_COLS * 16];           // value codebooks, bf16 (what the tensor-core product multiplies)
+  alignas(16) int32_t vmeta[JQK_MAX_COLS];        // value columns: width | bit position << 4 | first entry of its levels in vcb << 14
+  // value codebooks, bf16 (what the tensor-core product multiplies): 16 entries per column, then
+  // the 2^width levels of each column of 5..8 bits, one column after the other
+  __nv_bfloat16 vcb[JQK_MAX_COLS * 16 + VQ_WIDE_ENTRIES];
 };
 // A warp's stage doubles as its output staging [JQK_MAX_GROUP][128] floats after the last tile.
 static_assert(sizeof(TileStageT<false>) >= sizeof(float) * JQK_MAX_GROUP * JQK_MAX_DIM, "stage too small for the partial output");
@@ -307,6 +310,8 @@ struct ValueSide {
   int n_heads, wpr;
   const float* fwd_cols;    // [H][d][128]  (append variant: the new value row is compressed in the kernel)
   const float* thresholds;  // [H][128][16]
+  const float* wide_cb;     // [H][JQK_MAX_WIDE][256] levels of the columns of 5..8 bits, or null
+  const float* wide_thr;    // [H][JQK_MAX_WIDE][256] their thresholds (append variant), or null
 };
 
 // The newest token of every sequence, appended by the decode launch itself (k == nullptr: none).
@@ -410,7 +415,7 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
 template <int D>
 __device__ __forceinline__ void quantise_row(const float* row, uint32_t* words, const float* __restrict__ fwd_cols,
                                              const int32_t* __restrict__ col_meta, const float* __restrict__ thresholds,
-                                             int head, int n_active) {
+                                             int head, int n_active, const float* __restrict__ wide_thr, int wide_first) {
   const int tid = threadIdx.x;
   if (tid < n_active) {
     const float* w = fwd_cols + (size_t)head * D * 128 + tid;
@@ -418,10 +423,8 @@ __device__ __forceinline__ void quantise_row(const float* row, uint32_t* words, 
 #pragma unroll 32
     for (int i = 0; i < D; ++i) x = fmaf(row[i], __ldg(w + (size_t)i * 128), x);
     const int m = col_meta[(size_t)head * 128 + tid];
-    const float* th = thresholds + ((size_t)head * 128 + tid) * 16;
-    const int n_thr = (1 << (m & 15)) - 1;
-    uint32_t code = 0;
-    for (int l = 0; l < n_thr; ++l) code += (x >= th[l]) ? 1u : 0u;
+    const float* wide_row = (m & 15) > 4 ? wide_thr + ((size_t)head * JQK_MAX_WIDE + (tid - wide_first)) * 256 : nullptr;
+    const uint32_t code = threshold_code(x, m & 15, thresholds + ((size_t)head * 128 + tid) * 16, wide_row);
     const int bp = (m >> 4) & 1023;
     atomicOr(&words[bp >> 5], code << (bp & 31));
   }
@@ -439,7 +442,9 @@ __device__ __noinline__ void append_row_packed(DecodeSmemT<true>& sm, const floa
                                                int v_wpr, int v_active, int v_words, const void* k_row, const void* v_row,
                                                int k_dtype, int v_dtype, uint32_t* k_pool, uint32_t* v_pool, int head, int seq,
                                                bool write, int pos, const int32_t* __restrict__ page_table, int pt_stride,
-                                               int n_pages, int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group) {
+                                               int n_pages, int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group,
+                                               const float* __restrict__ k_wide_thr, int k_wide_first,
+                                               const float* __restrict__ v_wide_thr, int v_wide_first) {
   const int tid = threadIdx.x;
   if (tid < D) {
     sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
@@ -450,7 +455,7 @@ __device__ __noinline__ void append_row_packed(DecodeSmemT<true>& sm, const floa
     sm.ap_page = lookup_page(page_table, pt_stride, seq, pos / JQK_PAGE_TOKENS, n_pages, status);
   }
   __syncthreads();
-  quantise_row<D>(sm.ap_k, sm.ap_words, k_fwd, k_meta, k_thr, head, k_active);
+  quantise_row<D>(sm.ap_k, sm.ap_words, k_fwd, k_meta, k_thr, head, k_active, k_wide_thr, k_wide_first);
   if (q_rows && tid >= 256) {
     const int h = (tid - 256) >> 5, lane = tid & 31;
     if (h < n_group) {
@@ -467,7 +472,7 @@ __device__ __noinline__ void append_row_packed(DecodeSmemT<true>& sm, const floa
     sm.ap_k[tid] = v;
   }
   __syncthreads();
-  quantise_row<D>(sm.ap_k, sm.apv_words, v_fwd, v_meta, v_thr, head, v_active);
+  quantise_row<D>(sm.ap_k, sm.apv_words, v_fwd, v_meta, v_thr, head, v_active, v_wide_thr, v_wide_first);
   __syncthreads();
   const int page = sm.ap_page;
   if (write && page >= 0) {
@@ -489,7 +494,6 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
               const uint32_t* __restrict__ k_pool, const void* __restrict__ v_pool_raw,
               void* __restrict__ out, int out_dtype, DecodeWs ws, int32_t* status, ValueSide vs, AppendSide ap) {
   static_assert(!(VQ && BUILD_IN_BLOCK), "packed values need the table kernel");
-  static_assert(!(VQ && WIDE), "keys with byte-wide codes go with bf16 values");
   constexpr int DT = D / 16;                       // 16-dim MMA tiles
   constexpr uint32_t V_PAGE_BYTES = JQK_PAGE_TOKENS * D * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -571,13 +575,15 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   const uint32_t* vq_head = nullptr;
   size_t vq_page_words = 0;
   uint32_t vq_page_bytes = 0;
-  int v_n_active = 0;
+  int v_n_active = 0, v_wide_first = 0, v_n_wide = 0;
   if constexpr (VQ) {
     const HeadDesc vhd = load_desc(vs.desc, head);
     vq_head = reinterpret_cast<const uint32_t*>(v_pool_raw) + (size_t)head * vs.wpr * JQK_PAGE_TOKENS;
     vq_page_words = (size_t)vs.n_heads * vs.wpr * JQK_PAGE_TOKENS;
     vq_page_bytes = (uint32_t)vhd.n_words * JQK_PAGE_TOKENS * 4;
     v_n_active = vhd.n_active;
+    v_wide_first = vhd.wide_first;
+    v_n_wide = vhd.n_wide;
   }
 
   // ---- this warp's run of tiles and its page ids ----
@@ -646,7 +652,8 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
                            (const char*)ap.v + ((size_t)seq * ap.v_seq_stride + (size_t)head * ap.v_head_stride) * v_esz,
                            ap.k_dtype, ap.v_dtype, ap.k_pool, reinterpret_cast<uint32_t*>(ap.v_pool), head, seq, qb == 0, ap_pos,
                            page_table, pt_stride, n_pages, status,
-                           ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group);
+                           ap.own_key_exact ? q + ((size_t)seq * n_q_heads + qh0) * D : nullptr, n_group,
+                           tb.wide_thr, hd.wide_first, vs.wide_thr, vhd2.wide_first);
     }
   }
   if constexpr (APPEND && !VQ) {
@@ -672,8 +679,23 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     if constexpr (VQ) {
       // value-side tables of this head (static per head: no query enters them), and a clean tile:
       // rows of columns that carry no bits are never written by the dequantiser and must read as 0
-      for (int e = tid; e < JQK_MAX_COLS; e += DEC_THREADS)
-        sm.vmeta[e] = (e < v_n_active) ? (__ldg(vs.col_meta + (size_t)head * 128 + e) & 0x3FFF) : 0;
+      const int32_t* vcm = vs.col_meta + (size_t)head * 128;
+      for (int e = tid; e < JQK_MAX_COLS; e += DEC_THREADS) {
+        // (a descriptor past the last column reads code 0 of its own, all-zero, row)
+        int m = (e < v_n_active) ? (__ldg(vcm + e) & 0x3FFF) : 0, base = e * 16;
+        if ((m & 15) > 4) {  // a byte-wide column: its levels follow those of the wide columns before it
+          base = JQK_MAX_COLS * 16;
+          for (int j = v_wide_first; j < e; ++j) base += 1 << (__ldg(vcm + j) & 15);
+        }
+        sm.vmeta[e] = m | (base << 14);
+      }
+      for (int i = warp; i < v_n_wide; i += DEC_WARPS) {  // a warp per byte-wide column: its 2^width levels
+        const int m = __ldg(vcm + v_wide_first + i) & 15;
+        int base = JQK_MAX_COLS * 16;
+        for (int j = 0; j < i; ++j) base += 1 << (__ldg(vcm + v_wide_first + j) & 15);
+        const float* row = vs.wide_cb + ((size_t)head * JQK_MAX_WIDE + i) * 256;
+        for (int l = lane; l < (1 << m); l += 32) sm.vcb[base + l] = __float2bfloat16(__ldg(row + l));
+      }
       for (int e = tid; e < JQK_MAX_COLS * 16; e += DEC_THREADS)
         sm.vcb[e] = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
       uint4* z = reinterpret_cast<uint4*>(&st.v[0][0]);
@@ -824,12 +846,12 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
           const int m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
           uint32_t wd[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) wd[i] = vw[(m[i] >> 9) * JQK_PAGE_TOKENS];   // bit position >> 5 = record word
+          for (int i = 0; i < 8; ++i) wd[i] = vw[((m[i] >> 9) & 31) * JQK_PAGE_TOKENS];   // bit position >> 5 = record word
           __nv_bfloat16 val[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             const uint32_t code = (wd[i] >> ((m[i] >> 4) & 31)) & ((1u << (m[i] & 15)) - 1u);
-            val[i] = sm.vcb[(c0 + i) * 16 + code];
+            val[i] = sm.vcb[(m[i] >> 14) + code];
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i)   // (c0 + i) >> 2 is odd for i >= 4: those rows have their halves swapped
@@ -1152,11 +1174,12 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   int32_t rc = check_tables(tables);
   if (rc) return rc;
   if ((rc = check_decodable(tables, "decode attention"))) return rc;
-  if (v_tables && (rc = check_narrow(tables, "decode attention over packed values (the keys)"))) return rc;
   if (v_tables) {
     rc = check_tables(v_tables);
     if (rc) return rc;
-    if ((rc = check_narrow(v_tables, "decode attention over packed values"))) return rc;
+    if (v_tables->n_wide > 0 && !v_tables->value_decodable)
+      return fail(JQK_E_UNSUPPORTED, "decode attention over packed values: the levels of a head's columns above 4 bits "
+                                     "exceed the %d entries the kernel holds", VQ_WIDE_ENTRIES);
     if (v_tables->n_heads != tables->n_heads || v_tables->d != tables->d)
       return fail(JQK_E_LAYOUT, "key and value tables disagree on heads or head_dim");
   }
@@ -1212,12 +1235,13 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
   cfg.stream = st;
   cfg.attrs = pdl_attr;
   cfg.numAttrs = 1;
-  ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr};
+  ValueSide vs{nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr};
   AppendSide ap{};
   if (append) ap = *append;
   if (v_tables)
     vs = ValueSide{v_tables->desc, v_tables->col_meta, v_tables->cb_cols, v_tables->inv_rows, v_tables->center,
-                   v_tables->n_heads, v_tables->words_per_record, v_tables->fwd_cols, v_tables->thresholds};
+                   v_tables->n_heads, v_tables->words_per_record, v_tables->fwd_cols, v_tables->thresholds,
+                   v_tables->wide_cb, v_tables->wide_thr};
 #define JQK_LAUNCH_DECODE(DIM, INB, VQQ, APP, WID)                                                                    \
   do {                                                                                                                \
     cfg.dynamicSmemBytes = sizeof(DecodeSmemT<VQQ>);                                                                  \
@@ -1227,12 +1251,18 @@ static int32_t decode_launch(const jqk_head_tables* tables, const jqk_head_table
                                    k_pool, v_pool, out, out_dtype, ws, status, vs, ap),                               \
                 "decode launch");                                                                                     \
   } while (0)
-  const bool wide = tables->n_wide > 0;   // byte-wide codes: head_dim 128 and bf16 values only
+  const bool wide = tables->n_wide > 0;   // byte-wide codes: head_dim 128 only
   if (wide && tables->d != 128) return fail(JQK_E_UNSUPPORTED, "codes above 4 bits are decoded for head_dim 128 only");
+  if (v_tables && v_tables->n_wide > 0 && tables->d != 128)
+    return fail(JQK_E_UNSUPPORTED, "value codes above 4 bits are decoded for head_dim 128 only");
   if (v_tables && append) {
-    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, true, false); else JQK_LAUNCH_DECODE(64, false, true, true, false);
+    if (wide) JQK_LAUNCH_DECODE(128, false, true, true, true);
+    else if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, true, false);
+    else JQK_LAUNCH_DECODE(64, false, true, true, false);
   } else if (v_tables) {
-    if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false, false); else JQK_LAUNCH_DECODE(64, false, true, false, false);
+    if (wide) JQK_LAUNCH_DECODE(128, false, true, false, true);
+    else if (tables->d == 128) JQK_LAUNCH_DECODE(128, false, true, false, false);
+    else JQK_LAUNCH_DECODE(64, false, true, false, false);
   } else if (wide) {
     if (append) {
       if (in_block) JQK_LAUNCH_DECODE(128, true, false, true, true); else JQK_LAUNCH_DECODE(128, false, false, true, true);

@@ -199,10 +199,11 @@ def calibrate(model, prompts: list[torch.Tensor], with_values: bool = False) -> 
 
 
 def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_precision: bool = True, eps: float = 1e-4,
-                v_bits: int | None = None):
+                v_bits: int | None = None, max_bits: int = 4):
     """Fit one compressor per (layer, kv head) from the calibration moments (symmetrised Σ_Q Σ_K
-    basis, water-fill at ``k_bits`` average, at most 4 bits per coordinate), attach a packed cache
-    layer to every attention module and return the ``Cache`` to pass as ``past_key_values``.
+    basis, water-fill at ``k_bits`` average, at most ``max_bits`` bits per coordinate: 8 is the
+    reference's own cap, storable while at most 32 coordinates of a head go above 4 bits), attach a
+    packed cache layer to every attention module and return the ``Cache`` to pass as ``past_key_values``.
     ``v_bits``: values are packed as well (eigenbasis of Cov[V], water-fill, mean-centred: the
     reference's ``v_eigen_waterfill``); the moments must then have been taken ``with_values``.  The
     new token's value is then read from its codes in its own step already (the reference compresses
@@ -221,7 +222,7 @@ def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_preci
             m._jqk_layer = None
             continue
         comps = [PerCoordCompressor.fit(stats["sigma_q"][L, h].cpu(), stats["sigma_k"][L, h].cpu(), float(k_bits),
-                                        max_bits=4, basis="r_sym", eps=eps) for h in range(stats["sigma_k"].shape[1])]
+                                        max_bits=int(max_bits), basis="r_sym", eps=eps) for h in range(stats["sigma_k"].shape[1])]
         comps_by_layer[L] = comps
         v_tables = None
         if v_bits is not None:
@@ -229,7 +230,7 @@ def build_cache(model, moments: KeyPathMoments, k_bits: float, layer0_full_preci
                 raise ValueError("v_bits needs moments taken with_values=True")
             d = stats["cov_v"].shape[-1]
             v_comps = [build_v_compressor("v_eigen_waterfill", cov_v_for_head=stats["cov_v"][L, h].cpu(), head_dim=d,
-                                          bits=int(v_bits), seed=42, mu_v_for_head=stats["mu_v"][L, h].cpu(), max_bits=4)
+                                          bits=int(v_bits), seed=42, mu_v_for_head=stats["mu_v"][L, h].cpu(), max_bits=int(max_bits))
                        for h in range(stats["cov_v"].shape[1])]
             v_comps_by_layer[L] = v_comps
             v_tables = HeadTables.from_compressors([c.inner for c in v_comps], device=device,

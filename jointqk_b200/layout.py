@@ -45,6 +45,7 @@ PAGE_TOKENS = 16
 MAX_CODE_BITS = 4       # widths the lookup tables of the decode kernels take
 MAX_STORED_BITS = 8     # widths a record can hold: 5..8-bit codes take a byte each ("wide" columns)
 MAX_WIDE = 32           # wide columns per head
+MAX_VALUE_WIDE_LEVELS = 6144   # sum of 2^width over a head's wide columns that decode over packed VALUES holds
 MAX_WORDS = 16          # 128 coordinates x 4 bits
 MAX_TABLES = 208        # (MAX_WORDS + 1 shared word) * 12 rounded up to a multiple of 8
 TABLE_FIELDS = 4        # a lookup combines at most four coordinates (1,1,1,1)

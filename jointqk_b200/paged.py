@@ -247,8 +247,7 @@ def decode_attend(tables: HeadTables, q: torch.Tensor, seq_lens: torch.Tensor, m
         raise ValueError("q must be a contiguous bf16 (n_seqs, n_q_heads, d) tensor")
     tables.require_decodable("decode attention")
     if v_tables is not None:
-        tables.require_narrow("decode attention over packed values (the keys)")
-        v_tables.require_narrow("decode attention over packed values")
+        v_tables.require_value_decodable("decode attention over packed values")
         if v_pool.dtype != torch.int32:
             raise ValueError("a packed value pool is int32 storage")
         if out.shape != q.shape or not out.is_contiguous():
@@ -289,8 +288,7 @@ def decode_append_attend(tables: HeadTables, q: torch.Tensor, k_new: torch.Tenso
         raise ValueError("the value pool is bf16, or int32 storage of packed codes when v_tables is given")
     tables.require_decodable("decode attention")
     if v_tables is not None:
-        tables.require_narrow("decode attention over packed values (the keys)")
-        v_tables.require_narrow("decode attention over packed values")
+        v_tables.require_value_decodable("decode attention over packed values")
     if out.shape != q.shape or not out.is_contiguous():
         raise ValueError("out must be contiguous with the shape of q")
     if k_new.dim() == 4:

@@ -42,7 +42,10 @@ class JointQKPressB200:
     compress_decode: bool = False
     eps: float = 1e-6
     compression_ratio: float = 0.0
-    max_bits: int = 4            # cap on bits per coordinate; the packed format stores 0..4 (the reference caps at 8)
+    # cap on bits per coordinate.  The reference hard-codes 8; the packed format holds that as long as at
+    # most 32 coordinates of a head go above 4 bits and the record stays within 512 bits (budgets up to
+    # about 3 bits per coordinate on the evaluated spectra).  4 is storable at every budget.
+    max_bits: int = 4
 
     _k_compressors: dict = field(default_factory=dict, init=False, repr=False)
     _v_compressors: dict = field(default_factory=dict, init=False, repr=False)

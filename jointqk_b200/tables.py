@@ -15,7 +15,7 @@ import torch
 
 from . import _native
 from .codebooks import unit_gaussian_centroids
-from .layout import MAX_TABLES, MAX_WIDE, KeyLayout, decision_thresholds, plan_key_layout, unit_quantiser_tables
+from .layout import MAX_TABLES, MAX_VALUE_WIDE_LEVELS, MAX_WIDE, KeyLayout, decision_thresholds, plan_key_layout, unit_quantiser_tables
 
 DESC_INTS = 32
 MAX_COLS = 128
@@ -80,6 +80,9 @@ class HeadTables:
         # columns of 5..8 bits: their own 256-entry rows, indexed by column - wide_first
         self.n_wide = max(l.n_wide for l in self.layouts)
         self.decodable = all(l.decodable for l in self.layouts)     # every head's lookups fit the decode kernels' table memory
+        # as value tables: the kernel holds the levels of a head's wide columns as they are
+        self.value_decodable = all(int(sum(1 << int(w) for w in l.col_width[l.wide_first:l.wide_first + l.n_wide]))
+                                   <= MAX_VALUE_WIDE_LEVELS for l in self.layouts)
         wide_thr = np.full((H, MAX_WIDE, 256), np.inf, np.float32)
         wide_cb = np.zeros((H, MAX_WIDE, 256), np.float32)
         col_scale = np.ones((H, MAX_COLS), np.float32)     # 1 / sigma of the column's coordinate
@@ -178,18 +181,18 @@ class HeadTables:
             wide_thr=None if self.wide_thr is None else self.wide_thr.data_ptr(),
             wide_cb=None if self.wide_cb is None else self.wide_cb.data_ptr(),
             unit_wide_thr=None if self.unit_wide_thr is None else self.unit_wide_thr.data_ptr(),
-            decodable=int(self.decodable), pad=0)
+            decodable=int(self.decodable), value_decodable=int(self.value_decodable))
 
     @property
     def ref(self):
         return C.byref(self.struct)
 
-    def require_narrow(self, what: str) -> None:
-        """For the paths that take 0..4 bits per coordinate only (packed values, the tensor-core tables)."""
-        if self.n_wide:
+    def require_value_decodable(self, what: str) -> None:
+        """Decode over packed values keeps the levels of a head's columns of 5..8 bits in shared memory."""
+        if not self.value_decodable:
             raise ValueError(
-                f"{what} takes at most 4 bits per coordinate; these tables hold {self.n_wide} wider column(s).  "
-                "Fit with max_bits=4")
+                f"{what}: the levels of a head's columns above 4 bits exceed the {MAX_VALUE_WIDE_LEVELS} entries the decode "
+                f"kernel holds ({self.n_wide} such columns).  Fit the values with a lower cap, e.g. max_bits=4 or 6")
 
     def require_decodable(self, what: str) -> None:
         """The decode and score kernels keep every lookup table of a head in shared memory: 208 slots of

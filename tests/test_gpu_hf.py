@@ -98,7 +98,8 @@ def test_model_decodes_over_the_packed_cache_like_the_reference_flow(family):
 
 
 @torch.no_grad()
-def test_llama_decodes_with_keys_and_values_packed():
+@pytest.mark.parametrize("cap", [4, 8])
+def test_llama_decodes_with_keys_and_values_packed(cap):
     """K at 2 bits and V at 3 bits, the reference's usual pairing: values calibrated through the
     model's forward (first and second moments), packed by the centred eigenbasis compressor, and the
     decode step attends over both code pools.  Checked against the same model over a dense cache
@@ -113,7 +114,7 @@ def test_llama_decodes_with_keys_and_values_packed():
     g = torch.Generator().manual_seed(6)
     prompts = [torch.randint(0, 512, (2, 256), generator=g).cuda() for _ in range(4)]
     moments = hf.calibrate(model, prompts, with_values=True)
-    cache = hf.build_cache(model, moments, k_bits=2.0, v_bits=3)
+    cache = hf.build_cache(model, moments, k_bits=2.0, v_bits=3, max_bits=cap)   # 8: the reference's own cap
     ids = torch.randint(0, 512, (2, 40), generator=g).cuda()
     forced = torch.randint(0, 512, (2, 6), generator=g).cuda()
 

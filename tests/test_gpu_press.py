@@ -39,10 +39,12 @@ def _calibration(tmp_path):
     return cca, vst, data
 
 
-def test_press_compressors_equal_offline_builders_and_the_oracle(tmp_path):
+@pytest.mark.parametrize("cap", [4, 8])
+def test_press_compressors_equal_offline_builders_and_the_oracle(tmp_path, cap):
+    """``cap`` 8 is what the reference's builders hard-code (per_coord_quantization.py:367)."""
     cca, vst, data = _calibration(tmp_path)
     press = jq.JointQKPressB200(cca_stats_path=str(tmp_path / "cca_stats.pt"), v_stats_path=str(tmp_path / "v_stats.pt"),
-                                v_method="v_eigen_waterfill", k_method="r_sym_waterfill", k_bits=2, v_bits=3, rank=64)
+                                v_method="v_eigen_waterfill", k_method="r_sym_waterfill", k_bits=2, v_bits=3, rank=64, max_bits=cap)
     press.post_init_from_model(FakeModel())
     press.post_init_from_model(FakeModel())                      # idempotent
     assert (0, 0) not in press._k_compressors and (1, 1) in press._k_compressors   # layer 0 stays full precision
@@ -50,11 +52,12 @@ def test_press_compressors_equal_offline_builders_and_the_oracle(tmp_path):
     k, v = data[LAYER][1][HEAD, :512], data[LAYER][2][HEAD, :512]
     off_k = jq.build_method_compressor("r_sym_waterfill", cca["sigma_q"][LAYER, HEAD], cca["sigma_k"][LAYER, HEAD],
                                        cca={"P_K": None, "P_K_inv": None, "rho": None}, b_avg=2.0, r=64, seed=42, head_dim=D,
-                                       R_sym=cca["R_sym"][LAYER, HEAD], max_bits=4)
+                                       R_sym=cca["R_sym"][LAYER, HEAD], max_bits=cap)
     off_v = jq.build_v_compressor("v_eigen_waterfill", cov_v_for_head=vst["cov_v"][LAYER, HEAD],
                                   mu_v_for_head=vst["mu_v"][LAYER, HEAD], head_dim=D, bits=3,
-                                  seed=42 + LAYER * 1000 + HEAD, max_bits=4)
+                                  seed=42 + LAYER * 1000 + HEAD, max_bits=cap)
     pk, pv = press._k_compressors[(LAYER, HEAD)], press._v_compressors[(LAYER, HEAD)]
+    assert (int(pk.bits_int.max()) > 4) == (cap == 8)
     k_diff = (off_k.roundtrip(k) - pk.roundtrip(k)).abs().max().item()
     v_diff = (off_v.roundtrip(v) - pv.roundtrip(v)).abs().max().item()
     print(f"K parity max-abs-diff: {k_diff:.2e}   V parity max-abs-diff: {v_diff:.2e}")
