@@ -30,6 +30,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <type_traits>
 #include <mutex>
 
 #include "jqk_sm100.cuh"
@@ -687,7 +688,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
           base = JQK_MAX_COLS * 16;
           for (int j = v_wide_first; j < e; ++j) base += 1 << (__ldg(vcm + j) & 15);
         }
-        sm.vmeta[e] = m | (base << 14);
+        sm.vmeta[e] = v_n_wide ? (m | (base << 14)) : m;
       }
       for (int i = warp; i < v_n_wide; i += DEC_WARPS) {  // a warp per byte-wide column: its 2^width levels
         const int m = __ldg(vcm + v_wide_first + i) & 15;
@@ -839,24 +840,32 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         // eight columns at a time, stage by stage (descriptors, record words, centroids, stores), so
         // that the dependent shared-memory reads of the eight overlap and no load waits behind a store
         const int n_pad = (v_n_active + 7) & ~7;   // descriptors past the last column are 0: code 0 of a zero row
+        // (two forms of the loop: with byte-wide columns a descriptor also carries where the column's
+        // levels start; without, the rows are 16 entries apart and the descriptor has 14 bits)
+        auto dequantise = [&](auto with_wide) {
+          constexpr bool VW = decltype(with_wide)::value;
 #pragma unroll 1
-        for (int c0 = 0; c0 < n_pad; c0 += 8) {
-          const int4 ma = *reinterpret_cast<const int4*>(&sm.vmeta[c0]);
-          const int4 mb = *reinterpret_cast<const int4*>(&sm.vmeta[c0 + 4]);
-          const int m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
-          uint32_t wd[8];
+          for (int c0 = 0; c0 < n_pad; c0 += 8) {
+            const int4 ma = *reinterpret_cast<const int4*>(&sm.vmeta[c0]);
+            const int4 mb = *reinterpret_cast<const int4*>(&sm.vmeta[c0 + 4]);
+            const int m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+            uint32_t wd[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) wd[i] = vw[((m[i] >> 9) & 31) * JQK_PAGE_TOKENS];   // bit position >> 5 = record word
-          __nv_bfloat16 val[8];
+            for (int i = 0; i < 8; ++i)   // bit position >> 5 = record word
+              wd[i] = vw[(VW ? ((m[i] >> 9) & 31) : (m[i] >> 9)) * JQK_PAGE_TOKENS];
+            __nv_bfloat16 val[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t code = (wd[i] >> ((m[i] >> 4) & 31)) & ((1u << (m[i] & 15)) - 1u);
-            val[i] = sm.vcb[(m[i] >> 14) + code];
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t code = (wd[i] >> ((m[i] >> 4) & 31)) & ((1u << (m[i] & 15)) - 1u);
+              val[i] = VW ? sm.vcb[(m[i] >> 14) + code] : sm.vcb[(c0 + i) * 16 + code];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i)   // (c0 + i) >> 2 is odd for i >= 4: those rows have their halves swapped
+              *reinterpret_cast<__nv_bfloat16*>(vt + (c0 + i) * 32 + (i >= 4 ? off_b : off_a)) = val[i];
           }
-#pragma unroll
-          for (int i = 0; i < 8; ++i)   // (c0 + i) >> 2 is odd for i >= 4: those rows have their halves swapped
-            *reinterpret_cast<__nv_bfloat16*>(vt + (c0 + i) * 32 + (i >= 4 ? off_b : off_a)) = val[i];
-        }
+        };
+        if (v_n_wide) dequantise(std::true_type{});
+        else dequantise(std::false_type{});
       }
     } else if (any && t0 + TILE_TOK > t_end) {
 #pragma unroll
