@@ -36,11 +36,14 @@ def _k_hat(packed, comps):
             for s in range(codes.shape[0])]
 
 
-def test_decode_step_context_32768_against_oracle():
+@pytest.mark.parametrize("cap", [4, 8])
+def test_decode_step_context_32768_against_oracle(cap):
+    """``cap`` 8: the reference's default cap per coordinate (byte-wide codes for the outlier channels)."""
     H, HQ, N = 8, 32, 32768
     keys = torch.stack([spectrum_keys(N, config_seed(1, 0, h), device="cuda") for h in range(H)])
-    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), 2.0)
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].cpu(), 2.0, max_bits=cap)
     tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    assert (tables.n_wide > 0) == (cap == 8)
     g = torch.Generator(device="cuda").manual_seed(config_seed(1, 0, 0) + 7)
     v = torch.randn(1, H, N, 128, generator=g, device="cuda").to(torch.bfloat16)
     q = torch.randn(1, HQ, 128, generator=g, device="cuda").to(torch.bfloat16)
@@ -60,16 +63,18 @@ def test_decode_step_context_32768_against_oracle():
     bad = sum(code_mismatch(codes[h], orc.roundtrip(keys[h].cpu(), comps[h].codebooks_padded, comps[h].forward_map,
                                                     comps[h].inverse_map)[1])[0] for h in range(H))
     rate = bad / (H * N * 128)
-    print(f"context 32768: output rel err {err:.2e}, table-score rel err {s_err:.2e}, code mismatch rate {rate:.2e}")
+    print(f"context 32768, cap {cap}: output rel err {err:.2e}, table-score rel err {s_err:.2e}, code mismatch rate {rate:.2e}")
     assert err < TOL and s_err < TOL and rate <= 1e-5
 
 
-def test_prefill_config_sequence_131072_codes_against_oracle():
+@pytest.mark.parametrize("cap", [4, 8])
+def test_prefill_config_sequence_131072_codes_against_oracle(cap):
     H, N = 8, 131072
     keys = torch.stack([spectrum_keys(N, config_seed(4, 0, h), 8, 20.0, device="cuda", dtype=torch.bfloat16)
                         for h in range(H)])
-    comps, _ = fit_sigma_k_heads(keys[:, :4096].float().cpu(), 2.5)
+    comps, _ = fit_sigma_k_heads(keys[:, :4096].float().cpu(), 2.5, max_bits=cap)
     tables = jq.HeadTables.from_compressors(comps, device="cuda")
+    assert tables.fwd_limbs is not None and (tables.n_wide > 0) == (cap == 8)
     packed = paged.compress(tables, keys.unsqueeze(0))                  # bf16, 131072 keys: the tensor-core kernel
     paged.check_status(packed.status)
     codes = paged.unpack_codes(packed)[0].cpu()
@@ -78,8 +83,10 @@ def test_prefill_config_sequence_131072_codes_against_oracle():
         _, ref_codes = orc.roundtrip(keys[h].cpu(), comps[h].codebooks_padded, comps[h].forward_map, comps[h].inverse_map)
         bad += code_mismatch(codes[h], ref_codes)[0]
     rate = bad / (H * N * 128)
-    print(f"8 heads x 131072 bf16 keys at 2.5 bits: {bad} mismatching codes, rate {rate:.2e}")
-    assert rate <= 1e-5
+    n_wide_coords = sum(int((c.bits_int > 4).sum()) for c in comps)
+    print(f"8 heads x 131072 bf16 keys at 2.5 bits, cap {cap}: {bad} mismatching codes, rate {rate:.2e}")
+    # (a byte-wide coordinate has 255 thresholds for a value to sit on within an fp32 rounding, not 15)
+    assert bad <= 1e-5 * H * N * 128 + 1e-4 * n_wide_coords * N
 
 
 def test_batch_shard_3bit_ragged_decode_against_oracle():
