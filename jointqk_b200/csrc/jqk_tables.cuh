@@ -43,7 +43,7 @@ struct TableSmem {
   int dshift[TBL_WORDS];                         // K_w - K_{w-1}
   unsigned int bias;                             // what the +32768 offsets of the low halves add up to
   int wcb[JQK_MAX_WORDS + 4];                    // first column of every physical record word
-  uint8_t woff[JQK_MAX_WIDE];                    // wide column i: first table slot of its 2^width-entry table,
+  alignas(8) uint16_t woff[JQK_MAX_WIDE];        // wide column i: byte offset of its 2^width-entry table,
                                                  // counted from the end of the 16-entry tables
   uint8_t wwidth[JQK_MAX_WIDE];                  // wide column i: its code width (5..8)
 };
@@ -195,7 +195,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       const int other = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += other;
     }
-    if (lane < n_wide) sm.woff[lane] = (uint8_t)(incl - slots);
+    if (lane < n_wide) sm.woff[lane] = (uint16_t)((incl - slots) * 128);
   }
   // wide columns, a warp each: the projected query and the bound |q'_c| * max |level| (the row is
   // zero beyond its levels, so its largest magnitude is that of the levels)
@@ -334,7 +334,7 @@ __device__ __forceinline__ void build_tables(TableSmem& sm, const HeadDesc& hd, 
       const int levels = 1 << (int)sm.wwidth[i];
       const float up = (float)(1 << __shfl_sync(0xffffffffu, kw, i >> 2));
       const float4 qp = *reinterpret_cast<const float4*>(sm.qproj[hd.wide_first + i]);
-      uint2* dst = sm.lut + n_entries + (int)sm.woff[i] * 16;
+      uint2* dst = sm.lut + n_entries + ((int)sm.woff[i] >> 3);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int e = lane + 32 * u;
@@ -383,7 +383,7 @@ struct TableView {
   const uint2* lut;
   const int* dshift;
   unsigned int bias;
-  const uint8_t* woff = nullptr;
+  const uint16_t* woff = nullptr;
 };
 
 // Finished tables of one (sequence, kv head, q-head block) in global memory: written by the table
@@ -393,8 +393,8 @@ struct TableRecord {
   int dshift[TBL_WORDS];
   float scale[JQK_MAX_GROUP];
   unsigned int bias;
-  uint8_t woff[JQK_MAX_WIDE];
-  unsigned int pad[27 - JQK_MAX_WIDE / 4];
+  alignas(8) uint16_t woff[JQK_MAX_WIDE];
+  unsigned int pad[26 - JQK_MAX_WIDE / 2];
 };
 static_assert(sizeof(TableRecord) % 16 == 0 && offsetof(TableRecord, dshift) % 16 == 0, "bulk copies need 16-byte pieces");
 constexpr uint32_t TABLE_RECORD_META_BYTES = sizeof(TableRecord) - offsetof(TableRecord, dshift);  // 256
@@ -410,18 +410,24 @@ __device__ __forceinline__ void score_record(WordFn word, const TableView& sm, i
   const int* dshift = sm.dshift;
   if constexpr (WIDE) {
     const char* lw = lb + (size_t)(8 * n_a_words + 12 * n_c_words) * 128;
-    const int n_w_words = (n_wide + 3) >> 2;
+    const int n_full = n_wide >> 2, rest = n_wide & 3;
 #pragma unroll 1
-    for (int j = 0; j < n_w_words; ++j) {
+    for (int j = 0; j < n_full; ++j) {
       const uint32_t x = word(n_a_words + j);
-      const uint32_t wo = reinterpret_cast<const uint32_t*>(sm.woff)[j];  // table slots of the word's four columns
+      const uint2 wo = reinterpret_cast<const uint2*>(sm.woff)[j];  // table offsets of the word's four columns
       acc.shift(dshift[j]);
-      const int left = n_wide - 4 * j;  // (the last word may hold fewer than four columns)
-#pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        const uint32_t off = ((wo >> (8 * b)) & 255u) * 128u + ((x >> (8 * b)) & 255u) * 8u;
-        if (b < left) acc.add(*reinterpret_cast<const uint2*>(lw + off));
-      }
+      acc.add(*reinterpret_cast<const uint2*>(lw + (wo.x & 0xffffu) + ((x << 3) & 0x7f8u)));
+      acc.add(*reinterpret_cast<const uint2*>(lw + (wo.x >> 16) + ((x >> 5) & 0x7f8u)));
+      acc.add(*reinterpret_cast<const uint2*>(lw + (wo.y & 0xffffu) + ((x >> 13) & 0x7f8u)));
+      acc.add(*reinterpret_cast<const uint2*>(lw + (wo.y >> 16) + ((x >> 21) & 0x7f8u)));
+    }
+    if (rest) {  // the last word holds one to three columns
+      const uint32_t x = word(n_a_words + n_full);
+      const uint2 wo = reinterpret_cast<const uint2*>(sm.woff)[n_full];
+      acc.shift(dshift[n_full]);
+      acc.add(*reinterpret_cast<const uint2*>(lw + (wo.x & 0xffffu) + ((x << 3) & 0x7f8u)));
+      if (rest > 1) acc.add(*reinterpret_cast<const uint2*>(lw + (wo.x >> 16) + ((x >> 5) & 0x7f8u)));
+      if (rest > 2) acc.add(*reinterpret_cast<const uint2*>(lw + (wo.y & 0xffffu) + ((x >> 13) & 0x7f8u)));
     }
     dshift += (n_wide + 3) >> 2;
   }
