@@ -132,8 +132,12 @@ typedef struct jqk_head_tables {
   int32_t value_decodable;  /* as VALUE tables: the levels of every head's wide columns fit (JQK_MAX_VALUE_WIDE_LEVELS) */
 } jqk_head_tables;
 
-/* Library version: major << 16 | minor. */
+/* Library version: major << 16 | minor.  The minor number changes whenever struct jqk_head_tables or
+ * an entry point's arguments change; a binding compares it, and the struct's size, with its own. */
+#define JQK_VERSION ((0 << 16) | 2)
 int32_t jqk_version(void);
+/* sizeof(struct jqk_head_tables) as the library was built. */
+size_t jqk_head_tables_bytes(void);
 
 /* Message for the last non-zero return on the calling thread ("" if none). */
 const char* jqk_last_error(void);

@@ -47,6 +47,7 @@ class JqkHeadTables(C.Structure):
 # name -> (restype, argtypes); this table is also what the symbol-export test checks.
 SIGNATURES = {
     "jqk_version": (C.c_int32, []),
+    "jqk_head_tables_bytes": (C.c_size_t, []),
     "jqk_last_error": (C.c_char_p, []),
     "jqk_compress_paged": (C.c_int32, [
         C.POINTER(JqkHeadTables), C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32,
@@ -101,6 +102,7 @@ SIGNATURES = {
 }
 
 DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
+ABI_VERSION = 2              # JQK_VERSION of include/jointqk_b200.h
 STATUS_BAD_PAGE, STATUS_WAIT_EXPIRED, STATUS_BAD_LENGTH = 1, 2, 4
 
 
@@ -119,6 +121,12 @@ def _load() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError here means the library is out of date
         fn.restype = res
         fn.argtypes = args
+    # a library built from other sources than this binding would read the tables struct wrongly
+    if lib.jqk_version() != ABI_VERSION or lib.jqk_head_tables_bytes() != C.sizeof(JqkHeadTables):
+        raise ImportError(
+            f"jointqk_b200: {path} has interface version {lib.jqk_version()} and a tables struct of "
+            f"{lib.jqk_head_tables_bytes()} bytes; this binding expects {ABI_VERSION} and {C.sizeof(JqkHeadTables)}.  "
+            "Rebuild it: python -m jointqk_b200.build --force")
     return lib
 
 

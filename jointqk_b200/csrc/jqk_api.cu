@@ -32,6 +32,8 @@ int32_t check_decodable(const jqk_head_tables* t, const char* what) {
 
 }  // namespace jqk
 
-extern "C" int32_t jqk_version(void) { return (0 << 16) | 1; }
+extern "C" int32_t jqk_version(void) { return JQK_VERSION; }
+
+extern "C" size_t jqk_head_tables_bytes(void) { return sizeof(jqk_head_tables); }
 
 extern "C" const char* jqk_last_error(void) { return jqk::error_buffer(); }

@@ -28,7 +28,8 @@ def test_library_exports_every_declared_symbol():
 def test_version_and_argument_errors_without_gpu():
     from jointqk_b200 import _native
 
-    assert _native.lib.jqk_version() >= 1
+    assert _native.lib.jqk_version() == _native.ABI_VERSION == 2
+    assert _native.lib.jqk_head_tables_bytes() == ctypes.sizeof(_native.JqkHeadTables)
     rc = _native.lib.jqk_moments_accumulate(None, None, 1, 10, 1280, 1280, 3, 2, 128, None, None, None, None, None, 0, None, 0, None)
     assert rc == -1 and b"GQA mismatch" in _native.lib.jqk_last_error()
     rc = _native.lib.jqk_compress_paged(None, None, 0, 0, 0, 0, 1, None, None, 1, None, 1, 1, None, None, None)
