@@ -203,6 +203,27 @@ int32_t jqk_unpack_codes(const jqk_head_tables* tables, int32_t n_seqs, const in
                          uint8_t* codes, int32_t* status, void* stream);
 
 /*
+ * Round trip without a packed record, for allocations the record does not hold (more than
+ * JQK_MAX_WIDE coordinates above 4 bits, or more than 32 * JQK_MAX_WORDS bits per key: what the
+ * reference's default cap of 8 gives from budgets of about 3.5 bits per coordinate on).  Replaces
+ * PerCoordCompressor.roundtrip (experiments/stage1/toolkit/per_coord_quantization.py:123-165) and,
+ * with `center`, CenteredCompressor.roundtrip (v_compressor_adapter.py:64-72) for such objects:
+ * x = (row - center) @ forward_map, code_j = #{l : x_j >= thresholds[j][l]}, x_hat_j =
+ * levels[j][code_j], out = x_hat @ inverse_map + center.
+ *   forward_maps / inverse_maps  float [H][d][d] row-major
+ *   thresholds  float [H][d][255] exact fp32 decision thresholds of coordinate j, +inf padded
+ *   levels      float [H][d][256] its levels (codebooks_padded row), 0 beyond the last
+ *   widths      int32 [H][d]      bits of coordinate j, 0..8
+ *   rows        [H][n_tokens][d] of `dtype` with the given strides in elements
+ *   out         float [H][n_tokens][d] or NULL;  codes  uint8 [H][n_tokens][d] or NULL
+ */
+int32_t jqk_roundtrip_dense(const float* forward_maps, const float* inverse_maps, const float* thresholds,
+                            const float* levels, const int32_t* widths, const float* center,
+                            int32_t n_heads, int32_t d, const void* rows, int32_t dtype,
+                            int64_t head_stride, int64_t token_stride, int64_t n_tokens, float* out,
+                            uint8_t* codes, void* stream);
+
+/*
  * Attention logits of queries against packed keys, q . k_hat / sqrt(d).  Replaces compute_attention_metrics' candidate logits
  * (experiments/stage1/toolkit/eval.py:21) with GQA grouping as in repeat_kv_states
  * (experiments/stage1/toolkit/metric_transform.py:21-27).

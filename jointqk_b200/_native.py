@@ -98,6 +98,9 @@ SIGNATURES = {
     "jqk_store_values_paged": (C.c_int32, [
         C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
         C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "jqk_roundtrip_dense": (C.c_int32, [
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+        C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "jqk_selftest_bounded_wait": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p]),
 }
 

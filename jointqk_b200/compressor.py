@@ -61,16 +61,27 @@ class PerCoordCompressor:
         self.inverse_map = inverse_map.float() if inverse_map is not None else None
         self._build_codebooks()
         self._tables: HeadTables | None = None
+        self._dense = None
+        self._packable: bool | None = None
         self.allocation = "given"          # how bits_per_coord was obtained (set by fit / the builders)
 
     @property
     def packable(self) -> bool:
-        """True when the packed GPU format can store the codes: at most 8 bits per coordinate and at
-        most 32 coordinates above 4 bits (those take a byte each).  The reference's default cap of 8
-        (per_coord_quantization.py:367) fits."""
-        if not self.bits_int.numel():
-            return True
-        return int(self.bits_int.max()) <= 8 and int((self.bits_int > 4).sum()) <= 32
+        """True when the packed GPU format can store the codes: at most 8 bits per coordinate, at
+        most 32 coordinates above 4 bits (those take a byte each) and at most 512 bits per record.
+        The reference's default cap of 8 (per_coord_quantization.py:367) fits up to budgets of about
+        3 bits per coordinate; beyond the format, ``roundtrip`` and ``codes`` run unpacked
+        (``dense.DenseTables``) and there is no cache to attend over."""
+        if self._packable is None:
+            from .layout import plan_key_layout
+
+            self._packable = True
+            if self.bits_int.numel():
+                try:
+                    plan_key_layout(self.bits_int.cpu().numpy())
+                except ValueError:
+                    self._packable = False
+        return self._packable
 
     @property
     def decodable(self) -> bool:
@@ -122,7 +133,8 @@ class PerCoordCompressor:
             raise ValueError(
                 f"this compressor gives a coordinate {int(self.bits_int.max())} bits and "
                 f"{int((self.bits_int > 4).sum())} coordinates more than 4; the packed GPU format stores 0..8 bits per "
-                "coordinate with at most 32 coordinates above 4 bits.  Fit it with a lower cap "
+                "coordinate with at most 32 coordinates above 4 bits and 512 bits per key.  roundtrip() and codes() "
+                "work without a record up to 8 bits per coordinate; for a packed cache fit it with a lower cap "
                 "(PerCoordCompressor.fit(..., max_bits=...) or build_method_compressor(..., max_bits=...))")
         if self._tables is None or self._tables.device != dev:
             self._tables = HeadTables.from_compressors([self], device=dev)
@@ -198,9 +210,29 @@ class PerCoordCompressor:
         out = paged.decompress(packed)            # (1, 1, N, d)
         return out.reshape(tuple(packed.leading_shape) + (self.d,))
 
+    def _unpacked(self, device: torch.device):
+        """Tables of the record-free path, for an allocation the packed format does not hold (None
+        when it does).  Above 8 bits per coordinate nothing on the GPU applies: ``head_tables`` raises."""
+        if self.packable:
+            return None
+        if int(self.bits_int.max()) > 8:
+            self.head_tables(device)          # raises with the explanation
+        from .dense import DenseTables
+
+        if self._dense is None or self._dense.device != device:
+            eye = torch.eye(self.d)
+            fwd = self.forward_map if self.forward_map is not None else eye
+            inv = self.inverse_map if self.inverse_map is not None else eye
+            self._dense = DenseTables(fwd.unsqueeze(0), inv.unsqueeze(0), self.codebooks_padded.unsqueeze(0), device)
+        return self._dense
+
     @torch.no_grad()
     def codes(self, states: torch.Tensor) -> torch.Tensor:
         """uint8 codes (..., d) the quantiser assigns (the reference's implicit argmin)."""
+        dense = self._unpacked(_cuda_device(states.device))
+        if dense is not None:
+            _, codes = dense.roundtrip(states.reshape(1, -1, self.d), want_out=False, want_codes=True)
+            return codes.reshape(tuple(states.shape[:-1]) + (self.d,)).to(states.device)
         packed = self.compress(states)
         return paged.unpack_codes(packed).reshape(tuple(states.shape[:-1]) + (self.d,)).to(states.device)
 
@@ -209,6 +241,10 @@ class PerCoordCompressor:
         """states (..., d) -> fp32 reconstruction of the same shape on ``states.device``."""
         if states.shape[-1] != self.d:
             raise ValueError(f"states last-dim {states.shape[-1]} != compressor.d {self.d}")
+        dense = self._unpacked(_cuda_device(states.device))
+        if dense is not None:
+            out, _ = dense.roundtrip(states.reshape(1, -1, self.d))
+            return out.reshape(tuple(states.shape)).to(states.device)
         return self.decompress(self.compress(states)).to(states.device)
 
 
@@ -225,17 +261,38 @@ def stack_per_head(comps: list[PerCoordCompressor]) -> tuple[torch.Tensor, torch
     return fwd, inv, cb
 
 
-_BATCHED_TABLES: dict[tuple, HeadTables] = {}
+_BATCHED_TABLES: dict[tuple, object] = {}
 
 
-def _tables_for(forward_maps, inverse_maps, codebooks, device) -> HeadTables:
+def _codebooks_packable(codebooks: torch.Tensor) -> bool:
+    """Whether every head's allocation, read off its (d, K) +inf padded codebook, fits the packed record."""
+    from .layout import plan_key_layout
+
+    lengths = torch.isfinite(codebooks.detach().float().cpu()).sum(-1)
+    if int(lengths.max()) > 256 or int(lengths.min()) < 1:
+        return True                       # not a case for the record-free path: HeadTables raises with the reason
+    bits = torch.log2(lengths.float()).round().long()
+    try:
+        for h in range(bits.shape[0]):
+            plan_key_layout(bits[h].numpy())
+    except ValueError:
+        return False
+    return True
+
+
+def _tables_for(forward_maps, inverse_maps, codebooks, device):
     key = (forward_maps.data_ptr(), inverse_maps.data_ptr(), codebooks.data_ptr(),
            forward_maps._version, inverse_maps._version, codebooks._version, str(device))
     hit = _BATCHED_TABLES.get(key)
     if hit is None:
         if len(_BATCHED_TABLES) > 256:
             _BATCHED_TABLES.clear()
-        hit = HeadTables(forward_maps, inverse_maps, codebooks, device=device)
+        if _codebooks_packable(codebooks):
+            hit = HeadTables(forward_maps, inverse_maps, codebooks, device=device)
+        else:
+            from .dense import DenseTables
+
+            hit = DenseTables(forward_maps, inverse_maps, codebooks, device)
         _BATCHED_TABLES[key] = hit
     return hit
 
@@ -247,10 +304,13 @@ def batched_roundtrip(states: torch.Tensor, forward_maps: torch.Tensor, inverse_
     (reference :176-216).  One compress launch and one decompress launch for the layer."""
     B, H, S, d = states.shape
     dev = _cuda_device(states.device)
-    tables = _tables_for(forward_maps, inverse_maps, codebooks, dev)
     x = states.to(dev)
     if x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         x = x.float()
+    tables = _tables_for(forward_maps, inverse_maps, codebooks, dev)
+    if not isinstance(tables, HeadTables):        # an allocation beyond the packed format: no record in between
+        out = torch.stack([tables.roundtrip(x[b])[0] for b in range(B)]) if B else x.float()
+        return out.to(states.dtype).to(states.device)
     packed = paged.compress(tables, x)
     return paged.decompress(packed).to(states.dtype).to(states.device)
 

@@ -33,6 +33,7 @@ class CenteredCompressor:
         self.inner = inner
         self.mu = mu                      # (d,) in original (un-rotated) coordinates
         self._tables: HeadTables | None = None
+        self._dense = None
 
     @property
     def d(self) -> int:
@@ -70,6 +71,16 @@ class CenteredCompressor:
 
     @torch.no_grad()
     def roundtrip(self, states: torch.Tensor) -> torch.Tensor:
+        if not self.inner.packable and int(self.inner.bits_int.max()) <= 8:
+            # beyond the packed record: the same arithmetic without one (jqk_roundtrip_dense)
+            from .dense import DenseTables
+
+            dev = _cuda_device(states.device)
+            if self._dense is None or self._dense.device != dev:
+                self._dense = DenseTables(self.inner.forward_map.unsqueeze(0), self.inner.inverse_map.unsqueeze(0),
+                                          self.inner.codebooks_padded.unsqueeze(0), dev, center=self.mu.reshape(1, -1))
+            out, _ = self._dense.roundtrip(states.reshape(1, -1, self.d))
+            return out.reshape(tuple(states.shape)).to(states.device)
         return self.decompress(self.compress(states)).to(states.device)
 
 

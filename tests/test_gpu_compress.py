@@ -302,3 +302,48 @@ def test_tensor_core_path_centred_rows_at_the_reference_cap():
         assert (out[0, h][same] - want[same]).abs().max().item() < 1e-5 * max(1.0, want.abs().max().item())
     print(f"centred cap-8 rows: {bad} code mismatches of {H * N * 128}")
     assert bad <= max(2, int(MAX_RATE * H * N * 128)), bad
+
+
+def test_allocations_beyond_the_record_roundtrip_without_one(golden):
+    """The reference's default cap of 8 at 4.0 bits per coordinate puts 40-odd coordinates above 4
+    bits and 600-odd bits in a key: more than the packed record holds.  ``roundtrip``, ``codes``,
+    ``batched_roundtrip`` and the centred wrapper then run through jqk_roundtrip_dense; codes and
+    reconstruction against the oracle, and the same codes as the packed path where both apply."""
+    H, N = 2, 3000
+    keys = torch.stack([spectrum_keys(N, config_seed(0, 0, h)) for h in range(H)])
+    comps, _ = fit_sigma_k_heads(keys, 4.0, max_bits=8)
+    assert not comps[0].packable and int((comps[0].bits_int > 4).sum()) > 32
+    with pytest.raises(ValueError, match="512 bits per key"):
+        comps[0].compress(keys[0].cuda())
+    bad = 0
+    for h in range(H):
+        c = comps[h]
+        want, want_codes = orc.roundtrip(keys[h], c.codebooks_padded, c.forward_map, c.inverse_map)
+        codes = c.codes(keys[h].cuda()).cpu()
+        out = c.roundtrip(keys[h].cuda()).cpu()
+        bad += int((codes.long() != want_codes).sum())
+        same = (codes.long() == want_codes).all(-1)
+        assert (out[same] - want[same]).abs().max().item() < 1e-5 * max(1.0, want.abs().max().item())
+        assert c.roundtrip(keys[h].to(torch.bfloat16)).device.type == "cpu"        # host rows in, host rows out
+    print(f"record-free roundtrip at 4.0 bits, cap 8: {bad} code mismatches of {H * N * 128}")
+    assert bad <= 1e-4 * H * N * 128
+    fwd, inv, cb = jq.stack_per_head(comps)
+    got = jq.batched_roundtrip(keys.unsqueeze(0).cuda(), fwd, inv, cb).cpu()[0]
+    for h in range(H):
+        assert torch.equal(got[h], comps[h].roundtrip(keys[h].cuda()).cpu())
+    # centred rows (the value side's wrapper)
+    mu = keys[0].mean(0) + 0.5
+    cc = jq.CenteredCompressor(comps[0], mu)
+    want, _ = orc.centred_roundtrip(keys[0] + 0.5, mu, comps[0].codebooks_padded, comps[0].forward_map, comps[0].inverse_map)
+    got = cc.roundtrip((keys[0] + 0.5).cuda()).cpu()
+    close = ((got - want).abs().amax(-1) < 1e-4 * float(want.abs().max())).float().mean().item()
+    assert close > 0.99
+    # where the record applies too, both paths assign the same codes (fp32 rows: the CUDA-core kernels)
+    from jointqk_b200.dense import DenseTables
+
+    small, _ = fit_sigma_k_heads(keys, 2.0, max_bits=8)
+    dense = DenseTables(small[0].forward_map.unsqueeze(0), small[0].inverse_map.unsqueeze(0),
+                        small[0].codebooks_padded.unsqueeze(0), torch.device("cuda", 0))
+    out_d, codes_d = dense.roundtrip(keys[:1].cuda(), want_codes=True)
+    assert small[0].packable and torch.equal(codes_d[0], small[0].codes(keys[0].cuda()))
+    assert torch.allclose(out_d[0], small[0].roundtrip(keys[0].cuda()), atol=1e-5 * float(keys.abs().max()))
