@@ -44,7 +44,8 @@ class JointQKPressB200:
     compression_ratio: float = 0.0
     # cap on bits per coordinate.  The reference hard-codes 8; the packed format holds that as long as at
     # most 32 coordinates of a head go above 4 bits and the record stays within 512 bits (budgets up to
-    # about 3 bits per coordinate on the evaluated spectra).  4 is storable at every budget.
+    # about 3 bits per coordinate on the evaluated spectra).  Beyond that the press still hands back the
+    # reference's reconstruction (made without a record) but keeps no paged cache.  4 packs at every budget.
     max_bits: int = 4
 
     _k_compressors: dict = field(default_factory=dict, init=False, repr=False)
@@ -99,7 +100,7 @@ class JointQKPressB200:
                         bits=int(self.v_bits), seed=42 + L * 1000 + h, max_bits=self.max_bits)
 
     # ---- device tables per layer ------------------------------------------------------------
-    def _layer_tables(self, layer_idx: int, comps: dict, store: dict, device) -> HeadTables:
+    def _layer_tables(self, layer_idx: int, comps: dict, store: dict, device):
         hit = store.get(layer_idx)
         if hit is None or hit.device != torch.device(device):
             heads = [comps[(layer_idx, h)] for h in range(self._n_kv_heads)]
@@ -108,10 +109,20 @@ class JointQKPressB200:
             if any(isinstance(c, CenteredCompressor) for c in heads):
                 center = torch.stack([c.mu.float().cpu() if isinstance(c, CenteredCompressor) else torch.zeros(c.d)
                                       for c in heads])
-            for c in inner:
-                if not c.packable:
-                    c.head_tables(device)          # raises with the explanation
-            hit = store[layer_idx] = HeadTables.from_compressors(inner, device=device, center=center)
+            if all(c.packable for c in inner):
+                hit = HeadTables.from_compressors(inner, device=device, center=center)
+            else:
+                # an allocation beyond the packed record (the reference's cap of 8 at 4 bits per
+                # coordinate, say): the reconstruction is made without one and no cache is kept
+                for c in inner:
+                    if int(c.bits_int.max()) > 8:
+                        c.head_tables(device)      # raises with the explanation
+                from .compressor import stack_per_head
+                from .dense import DenseTables
+
+                fwd, inv, cb = stack_per_head(inner)
+                hit = DenseTables(fwd, inv, cb, device, center=center)
+            store[layer_idx] = hit
         return hit
 
     def _skip(self, layer_idx: int) -> bool:
@@ -132,12 +143,20 @@ class JointQKPressB200:
         v_out = values
         if self.quantize_v:        # values: compress and reconstruct on the GPU, keep the reconstruction
             vt = self._layer_tables(L, self._v_compressors, self._v_tables, dev)
-            v_hat = paged.decompress(paged.compress(vt, v_dev if v_dev.dtype != torch.float64 else v_dev.float()))
+            v_in = v_dev if v_dev.dtype != torch.float64 else v_dev.float()
+            if isinstance(vt, HeadTables):
+                v_hat = paged.decompress(paged.compress(vt, v_in))
+            else:
+                v_hat = torch.stack([vt.roundtrip(v_in[b])[0] for b in range(B)])
             v_dev = v_hat.to(values.dtype)
             v_out = v_dev.to(values.device)
         k_out = keys
         if self.quantize_k:
             kt = self._layer_tables(L, self._k_compressors, self._k_tables, dev)
+            if not isinstance(kt, HeadTables):     # no record, so no paged cache: reconstruct and hand back
+                k_in = k_dev if k_dev.dtype != torch.float64 else k_dev.float()
+                k_hat = torch.stack([kt.roundtrip(k_in[b])[0] for b in range(B)])
+                return k_hat.to(keys.dtype).to(keys.device), v_out
             cache = self.caches.get(L)
             if cache is None or len(cache.lengths) != B:
                 cache = self.caches[L] = paged.PagedKVCache(kt, n_seqs=B)
@@ -181,7 +200,11 @@ class JointQKPressB200:
     @torch.no_grad()
     def decode(self, layer_idx: int, q: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
         """softmax(q . k_hat / sqrt(d)) @ V over the layer's paged cache: q bf16 (B, Hq, d)."""
-        cache = self.caches[int(layer_idx)]
+        cache = self.caches.get(int(layer_idx))
+        if cache is None:
+            raise RuntimeError(
+                f"layer {int(layer_idx)} has no paged cache: nothing was compressed yet, or its allocation is beyond the "
+                "packed record (more than 32 coordinates above 4 bits or 512 bits per key; see max_bits)")
         return cache.decode(q.to(cache.tables.device), out_dtype=out_dtype)
 
 

@@ -120,3 +120,32 @@ def test_forward_hook_prefill_then_mode_b_decode_steps(tmp_path):
     assert torch.equal(raw.keys, keys)
     k0, v0 = press_a.compress(SimpleNamespace(layer_idx=0), None, keys, vals, None, {})
     assert k0 is keys and v0 is vals                               # layer 0 passes through
+
+
+def test_press_with_the_reference_constructor_defaults_beyond_the_record(tmp_path):
+    """k_bits = 4 at the reference's cap of 8 (its constructor default and its hard-coded cap) puts
+    more coordinates above 4 bits than a record holds: the hook still swaps in the reference's
+    reconstruction, made on the GPU without a record; there is no paged cache to decode over."""
+    cca, vst, data = _calibration(tmp_path)
+    press = jq.JointQKPressB200(cca_stats_path=str(tmp_path / "cca_stats.pt"), v_stats_path=str(tmp_path / "v_stats.pt"),
+                                k_bits=4, v_bits=2, layer0_full_precision=False, max_bits=8)
+    press.post_init_from_model(FakeModel())
+    assert not press._k_compressors[(1, 0)].packable
+    S0, B = 200, 2
+    q_all, k_all, v_all = data[1]
+    keys = torch.stack([k_all[:, :S0], k_all.flip(1)[:, :S0]]).cuda()
+    vals = torch.stack([v_all[:, :S0], v_all.flip(1)[:, :S0]]).cuda()
+    layer = SimpleNamespace(keys=keys.clone(), values=vals.clone())
+    press.forward_hook(SimpleNamespace(layer_idx=1), (), {"hidden_states": torch.zeros(B, S0, 16),
+                                                          "past_key_values": SimpleNamespace(layers={1: layer}),
+                                                          "cache_position": torch.arange(S0)}, ("o", None))
+    for h in range(HKV):
+        kc, vc = press._k_compressors[(1, h)], press._v_compressors[(1, h)]
+        ref_k, _ = orc.roundtrip(keys[1, h].cpu(), kc.codebooks_padded, kc.forward_map, kc.inverse_map)
+        ref_v, _ = orc.centred_roundtrip(vals[1, h].cpu(), vc.mu, vc.inner.codebooks_padded, vc.inner.forward_map, vc.inner.inverse_map)
+        for got, ref in ((layer.keys[1, h].cpu(), ref_k), (layer.values[1, h].cpu(), ref_v)):
+            close = ((got - ref).abs().amax(-1) < 1e-4 * float(ref.abs().max())).float().mean().item()
+            assert close > 0.99
+    assert 1 not in press.caches
+    with pytest.raises(RuntimeError, match="no paged cache"):
+        press.decode(1, torch.zeros(B, HQ, D, dtype=torch.bfloat16))
