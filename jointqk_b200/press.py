@@ -45,8 +45,9 @@ class JointQKPressB200:
     # cap on bits per coordinate.  The reference hard-codes 8; the packed format holds that as long as at
     # most 32 coordinates of a head go above 4 bits and the record stays within 512 bits (budgets up to
     # about 3 bits per coordinate on the evaluated spectra).  Beyond that the press still hands back the
-    # reference's reconstruction (made without a record) but keeps no paged cache.  4 packs at every budget.
-    max_bits: int = 4
+    # reference's reconstruction (made without a record) but keeps no paged cache.  4 packs at every budget,
+    # with a different allocation than the reference's (a quality cost where outlier channels want more).
+    max_bits: int = 8
 
     _k_compressors: dict = field(default_factory=dict, init=False, repr=False)
     _v_compressors: dict = field(default_factory=dict, init=False, repr=False)
