@@ -354,6 +354,32 @@ __device__ __forceinline__ void values_to_output(const float* yb, int n_group, c
   }
 }
 
+// Code of column `col` of one row (`row`: D values in shared memory), with the arithmetic of
+// compress_token_kernel: the dims in ascending order with fused multiply-adds.  The column's
+// descriptor and threshold row are fetched ahead of the dot product, whose 128 reads of the basis go
+// out 64 at a time: the latency of a block that appends is a few memory round trips, not a dozen.
+template <int D>
+__device__ __forceinline__ uint32_t column_code(const float* row, const float* __restrict__ fwd_cols,
+                                                const int32_t* __restrict__ col_meta, const float* __restrict__ thresholds,
+                                                const float* __restrict__ wide_thr, int wide_first, int head, int col, int& m_out) {
+  const int m = __ldg(col_meta + (size_t)head * 128 + col);
+  const float4* th4 = reinterpret_cast<const float4*>(thresholds + ((size_t)head * 128 + col) * 16);
+  const float4 t0 = __ldg(th4), t1 = __ldg(th4 + 1), t2 = __ldg(th4 + 2), t3 = __ldg(th4 + 3);
+  const float* w = fwd_cols + (size_t)head * D * 128 + col;
+  float x = 0.f;
+#pragma unroll 64
+  for (int i = 0; i < D; ++i) x = fmaf(row[i], __ldg(w + (size_t)i * 128), x);
+  m_out = m;
+  const int width = m & 15;
+  if (width > 4) return threshold_code(x, width, nullptr, wide_thr + ((size_t)head * JQK_MAX_WIDE + (col - wide_first)) * 256);
+  // (+inf beyond the column's 2^width - 1 thresholds: counting all fifteen gives the same code)
+  const float th[15] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w, t2.x, t2.y, t2.z, t2.w, t3.x, t3.y, t3.z};
+  uint32_t code = 0;
+#pragma unroll
+  for (int l = 0; l < 15; ++l) code += (x >= th[l]) ? 1u : 0u;
+  return code;
+}
+
 // The appended key of (seq, head): transformed and quantised exactly as compress_token_kernel does
 // (thread = column, the dims in ascending order with fused multiply-adds: the same bits), the value
 // row converted to bf16.  Both stay in shared memory for the warp whose tile holds the position;
@@ -368,6 +394,7 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
                                         int32_t* status, const __nv_bfloat16* __restrict__ q_rows, int n_group,
                                         const float* __restrict__ wide_thr, int wide_first) {
   const int tid = threadIdx.x;
+  int m_col = 0;
   if (tid < D) {
     sm.ap_k[tid] = load_elem_f32(k_row, k_dtype, tid);
   } else if (tid >= 128 && tid < 128 + D) {
@@ -379,14 +406,8 @@ __device__ __noinline__ void append_row(DecodeSmemT<false>& sm, const float* __r
   }
   __syncthreads();
   if (tid < n_active) {
-    const float* w = fwd_cols + (size_t)head * D * 128 + tid;
-    float x = 0.f;
-#pragma unroll 32
-    for (int i = 0; i < D; ++i) x = fmaf(sm.ap_k[i], __ldg(w + (size_t)i * 128), x);
-    const int m = col_meta[(size_t)head * 128 + tid];
-    const float* wide_row = (m & 15) > 4 ? wide_thr + ((size_t)head * JQK_MAX_WIDE + (tid - wide_first)) * 256 : nullptr;
-    const uint32_t code = threshold_code(x, m & 15, thresholds + ((size_t)head * 128 + tid) * 16, wide_row);
-    const int bp = (m >> 4) & 1023;
+    const uint32_t code = column_code<D>(sm.ap_k, fwd_cols, col_meta, thresholds, wide_thr, wide_first, head, tid, m_col);
+    const int bp = (m_col >> 4) & 1023;
     atomicOr(&sm.ap_words[bp >> 5], code << (bp & 31));
   } else if (q_rows && tid >= 256) {   // the exact scores of the new key: one warp per query head of the group
     const int h = (tid - 256) >> 5, lane = tid & 31;
@@ -419,13 +440,8 @@ __device__ __forceinline__ void quantise_row(const float* row, uint32_t* words, 
                                              int head, int n_active, const float* __restrict__ wide_thr, int wide_first) {
   const int tid = threadIdx.x;
   if (tid < n_active) {
-    const float* w = fwd_cols + (size_t)head * D * 128 + tid;
-    float x = 0.f;
-#pragma unroll 32
-    for (int i = 0; i < D; ++i) x = fmaf(row[i], __ldg(w + (size_t)i * 128), x);
-    const int m = col_meta[(size_t)head * 128 + tid];
-    const float* wide_row = (m & 15) > 4 ? wide_thr + ((size_t)head * JQK_MAX_WIDE + (tid - wide_first)) * 256 : nullptr;
-    const uint32_t code = threshold_code(x, m & 15, thresholds + ((size_t)head * 128 + tid) * 16, wide_row);
+    int m;
+    const uint32_t code = column_code<D>(row, fwd_cols, col_meta, thresholds, wide_thr, wide_first, head, tid, m);
     const int bp = (m >> 4) & 1023;
     atomicOr(&words[bp >> 5], code << (bp & 31));
   }
@@ -531,19 +547,31 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   // Append variant: every block of the launch passes here exactly once on its way out, all of its
   // threads together.  Each has read its length by then, so the block that takes the last ticket
   // may advance the lengths for the next launch.
-  auto leave = [&]() {
+  // (The ticket is taken in two halves so that the merging block can put the atomic in flight before
+  // its merge and read the answer after it: its round trip is then off the step's critical path.)
+  [[maybe_unused]] unsigned int ticket_prev = 0u;
+  auto take_ticket = [&]() {   // after a barrier that all threads of the block have passed since reading their length
+    if constexpr (APPEND)
+      if (tid == 0)
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(ticket_prev) : "l"(ws.grid_ticket) : "memory");
+  };
+  auto finish_ticket = [&]() {
     if constexpr (APPEND) {
-      __syncthreads();
       if (tid == 0) {
-        unsigned int prev;
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(ws.grid_ticket) : "memory");
-        const bool last = prev == gridDim.x * gridDim.y * gridDim.z - 1u;
+        const bool last = ticket_prev == gridDim.x * gridDim.y * gridDim.z - 1u;
         if (last) *ws.grid_ticket = 0u;
         sm.ap_last = last ? 1 : 0;
       }
       __syncthreads();
       if (sm.ap_last)
         for (int s2 = tid; s2 < ap.n_seqs; s2 += DEC_THREADS) ap.seq_lens[s2] += 1;
+    }
+  };
+  auto leave = [&]() {
+    if constexpr (APPEND) {
+      __syncthreads();
+      take_ticket();
+      finish_ticket();
     }
   };
   {
@@ -989,6 +1017,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
   }
   __syncthreads();
   if (!sm.is_last) { leave(); return; }
+  take_ticket();
   // A thread owns four output dims of one head and every third split: it first puts its partial
   // rows in flight (MERGE_BATCH independent 16-byte loads), then one warp per head turns the
   // splits' (max, sum) pairs into one weight per split, so a single memory round trip covers both.
@@ -1072,7 +1101,7 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
     values_to_output<D>(yb, n_group, vs, head, v_n_active, out, out_dtype, (size_t)seq * n_q_heads + qh0);
   }
   if (tid == 0) *counter = 0u;  // ready for the next launch that shares this workspace
-  leave();
+  finish_ticket();
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
