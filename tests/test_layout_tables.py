@@ -238,3 +238,23 @@ def test_wide_decision_thresholds_reproduce_the_argmin():
         want = np.abs(x[:, None] - levels[None, :]).argmin(1)                    # fp32, first minimum
         got = (x[:, None] >= thr[None, :n_thr]).sum(1)
         assert np.array_equal(got, want), bits
+
+
+def test_packable_follows_the_record_limits():
+    """A compressor knows whether the packed record holds its allocation: at most 32 coordinates above
+    4 bits and 512 bits per key; beyond that ``roundtrip`` takes the record-free path (GPU tests)."""
+    import jointqk_b200 as jq
+    from jointqk_b200.compressor import _codebooks_packable
+
+    stds = torch.ones(128)
+    eye = torch.eye(128)
+    fits = jq.PerCoordCompressor(torch.tensor([8] * 4 + [2] * 100 + [0] * 24), stds, eye, eye)
+    too_many_wide = jq.PerCoordCompressor(torch.tensor([5] * 33 + [1] * 95), stds, eye, eye)
+    too_long = jq.PerCoordCompressor(torch.tensor([8] * 32 + [4] * 96), stds, eye, eye)        # 256 + 384 bits
+    assert fits.packable and fits.decodable
+    assert not too_many_wide.packable and not too_many_wide.decodable
+    assert not too_long.packable
+    _, _, cb = jq.stack_per_head([fits, fits])
+    assert _codebooks_packable(cb)
+    _, _, cb = jq.stack_per_head([fits, too_long])
+    assert not _codebooks_packable(cb)
