@@ -10,6 +10,7 @@ and do not fill a query block, head sizes 64 and 128, every bit budget, small an
   per coordinate, sorted, or in blocks of eight), which drives the read planner through every class
   and into its generic path: the two may only differ where a value sits on a decision threshold."""
 
+import os
 import random
 
 import pytest
@@ -23,6 +24,9 @@ from jointqk_b200.synthetic import config_seed, fit_sigma_k_heads, spectrum_keys
 pytestmark = pytest.mark.gpu
 
 EDGE_LENGTHS = [0, 1, 15, 16, 17, 31, 33, 383, 384, 385]
+# longer sweeps from other seeds: JQK_SOAK_SCALE=5 JQK_SOAK_SEED=100 python -m pytest tests/test_gpu_soak.py -m gpu
+SCALE = int(os.environ.get("JQK_SOAK_SCALE", "1"))
+SEED = int(os.environ.get("JQK_SOAK_SEED", "0"))
 _TABLES = {}
 
 
@@ -37,9 +41,9 @@ def _tables(H, b, d=128, cap=4):
 
 
 def test_decode_over_random_shapes():
-    rng = random.Random(3)
+    rng = random.Random(3 + SEED)
     worst = 0.0
-    for it in range(60):
+    for it in range(60 * SCALE):
         d = rng.choice([128, 128, 128, 64])
         H, g = rng.choice([1, 2, 4, 8]), rng.choice([1, 2, 4, 5, 8])
         b = rng.choice([1.0, 2.0, 2.5, 3.0, 4.0])
@@ -68,7 +72,7 @@ def test_decode_over_random_shapes():
             err = ((out[s] - ref).abs() / ref.abs().amax(-1, keepdim=True).clamp_min(1e-6)).max().item()
             worst = max(worst, err)
             assert err < 2e-3, (it, d, H, g, b, lens, tps, s, err)
-    print(f"decode over 60 random shapes: worst relative error {worst:.2e}")
+    print(f"decode over {60 * SCALE} random shapes: worst relative error {worst:.2e}")
 
 
 _V_TABLES = {}
@@ -94,8 +98,8 @@ def _v_tables(H, cap=4):
 
 @pytest.mark.parametrize("packed_values", [False, True])
 def test_fused_generate_step_over_random_shapes(packed_values):
-    rng = random.Random(7 + packed_values)
-    for it in range(20 if packed_values else 40):
+    rng = random.Random(7 + packed_values + SEED)
+    for it in range((20 if packed_values else 40) * SCALE):
         H, g = rng.choice([1, 2, 4]), rng.choice([1, 2, 4, 8])
         b = rng.choice([1.0, 2.0, 2.5, 3.0, 4.0])
         n0 = [rng.choice(EDGE_LENGTHS + [rng.randint(2, 3000)]) for _ in range(rng.randint(1, 4))]
@@ -133,12 +137,12 @@ def test_fused_generate_step_over_random_shapes(packed_values):
 
 
 def test_tensor_core_compress_over_random_allocations():
-    rng = random.Random(5)
+    rng = random.Random(5 + SEED)
     H, T = 2, 2048
     keys = torch.stack([spectrum_keys(T, config_seed(0, 2, h)) for h in range(H)]).to(torch.bfloat16)
     base, _ = fit_sigma_k_heads(keys.float(), 2.5)
     differ = total = wide_coords = wide_values = 0
-    for it in range(60):
+    for it in range(60 * SCALE):
         comps = []
         wide_coords = 0
         for c in base:
@@ -175,5 +179,5 @@ def test_tensor_core_compress_over_random_allocations():
         wide_values += wide_coords * n
         assert (a.int() - b.int()).abs().max().item() <= 1, it          # a threshold tie moves a code by one level
         paged.check_status(on_tensor_cores.status)
-    print(f"tensor-core vs CUDA-core codes over 60 allocations: {differ} of {total} differ")
+    print(f"tensor-core vs CUDA-core codes over {60 * SCALE} allocations: {differ} of {total} differ")
     assert differ <= 1e-5 * total + 1e-4 * wide_values + 2     # 255 thresholds to sit on instead of 15
