@@ -154,6 +154,9 @@ const char* jqk_last_error(void);
  *               destination of key t is slot (seq_starts+t) % 16 of logical page (seq_starts+t)/16
  *   max_tokens  largest n_tokens[] value (host), sizes the grid
  *   status      int32 device word, see JQK_STATUS_*
+ * The tensor-core kernel (bf16 keys, head_dim 128) is launched as a programmatic dependent: its
+ * set-up reads the tables' arrays while the previous kernel on the stream may still run, so that
+ * kernel must not be the one that writes them (tables are written once, by copies from the host).
  */
 int32_t jqk_compress_paged(const jqk_head_tables* tables, const void* keys, int32_t key_dtype,
                            int64_t seq_stride, int64_t head_stride, int64_t token_stride,

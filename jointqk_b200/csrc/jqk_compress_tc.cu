@@ -474,6 +474,11 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
   const int f_lo = blockIdx.x * pa.tiles_per_block;
   const int f_hi = min(pa.n_seqs * pa.max_tiles, f_lo + pa.tiles_per_block);
   if (f_lo >= f_hi) return;
+  // Launched as a programmatic dependent: the set-up below (the head's static tables, barriers,
+  // tensor memory, the limb matrices, the read plan) may overlap the tail of the previous kernel on
+  // the stream; every role waits for that kernel (griddepcontrol.wait) before it first touches what
+  // a call passes in or out: token counts, keys, page table, pages.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const HeadDesc hd = load_desc(tb.desc, head);
 
   // ---- set-up ----
@@ -504,6 +509,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
     // ================= TMA producer =================
     if (lane == 0) {
       tma_prefetch_desc(&key_map);
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       int issued = 0;
       for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); w.valid(); w.advance(), ++issued) {
         const int s = issued % TC_STAGES;
@@ -527,6 +533,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
         for (int kh = 0; kh < 2; ++kh)
           tma_load_2d(sm.b[l] + kh * (128 * 64 * 2), &limb_map, &sm.b_full, 64 * kh, (head * 3 + l) * 128);
       const uint32_t idesc = make_idesc_bf16(128, hd.n_cols, false, false);
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       bool ok = tc_wait(sm, &sm.b_full, 0, pa.status);
       int it = 0;
       for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); ok && w.valid(); w.advance(), ++it) {
@@ -580,6 +587,7 @@ compress_tc_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_con
 #pragma unroll
     for (int w = 0; w < 4; ++w) pre_base[w] = __uint_as_float(pre_addr + 128u * w);
     const int wpr = tb.words_per_record;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     int it = 0;
     int seq_of_start = -1, seq_start = 0;
     for (TileWalk w(f_lo, f_hi, pa.max_tiles, pa.n_tokens); w.valid(); w.advance(), ++it) {
@@ -743,14 +751,24 @@ int32_t jqk_compress_tc_try(const jqk_head_tables* tables, const void* keys, int
   JQK_SMEM_ONCE((compress_tc_kernel<false, true>), smem, "tensor-core compress smem attribute");
   JQK_SMEM_ONCE((compress_tc_kernel<true, true>), smem, "tensor-core compress smem attribute");
   const bool wide = tables->n_wide > 0;
-  if (tables->center && wide)
-    compress_tc_kernel<true, true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
-  else if (tables->center)
-    compress_tc_kernel<true, false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
-  else if (wide)
-    compress_tc_kernel<false, true><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
-  else
-    compress_tc_kernel<false, false><<<grid, TC_THREADS, smem, st>>>(key_map, limb_map, uc, *tables, pa, k_pool);
+  cudaLaunchAttribute pdl_attr[1];
+  pdl_attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl_attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = pdl_attr;
+  cfg.numAttrs = 1;
+#define JQK_LAUNCH_TC(CEN, WID)                                                                                   \
+  JQK_CUDA_OK(cudaLaunchKernelEx(&cfg, compress_tc_kernel<CEN, WID>, key_map, limb_map, uc, *tables, pa, k_pool), \
+              "tensor-core compress launch")
+  if (tables->center && wide) JQK_LAUNCH_TC(true, true);
+  else if (tables->center) JQK_LAUNCH_TC(true, false);
+  else if (wide) JQK_LAUNCH_TC(false, true);
+  else JQK_LAUNCH_TC(false, false);
+#undef JQK_LAUNCH_TC
   JQK_CUDA_OK(cudaGetLastError(), "tensor-core compress launch");
   return 0;
 }
