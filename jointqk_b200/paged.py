@@ -511,10 +511,17 @@ class PagedKVCache:
         # what the grid was sized for, a step is one library call and nothing else on the host.
         if (fused_append and gs is not None and gs["fused"] and getattr(self, "_gen_budget", 0) > 0
                 and gs["generation"] == self.pool.generation and gs["lengths_after"] == self.lengths
-                and gs["shape"] == (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype) and q.is_contiguous()):
+                and gs["shape"] == (tuple(k_new.shape), tuple(q.shape), k_new.dtype, v_new.dtype)
+                and gs["strides"] == (k_new.stride(), v_new.stride()) and q.is_contiguous()
+                and gs["table_ptr"] == self.page_table.data_ptr() and gs["lens_ptr"] == self.seq_lens.data_ptr()):
             self._gen_budget -= 1
-            decode_append_attend(self.tables, q, k_new, v_new, self.seq_lens, gs["covered"], self.page_table, self.k_pool,
-                                 self.v_pool, gs["out"], gs["ws"], self.status, gs["tps"], own_key_exact, self.v_tables)
+            # the call the slow path below made through decode_append_attend (which checked the
+            # arguments), with this step's three pointers, flag and stream put in
+            args = gs["args"]
+            args[gs["arg0"]], args[gs["arg0"] + 1], args[gs["arg0"] + 2] = q.data_ptr(), k_new.data_ptr(), v_new.data_ptr()
+            args[-5] = 1 if own_key_exact else 0
+            args[-1] = _stream_ptr(dev)
+            _native.check(gs["fn"](*args))
             for s_ in range(n):
                 self.lengths[s_] += 1
             self._epoch += 1
@@ -572,6 +579,19 @@ class PagedKVCache:
             decode_append_attend(self.tables, q if q.is_contiguous() else q.contiguous(), k_new, v_new, self.seq_lens,
                                  gs["covered"], self.page_table, self.k_pool, self.v_pool, gs["out"], gs["ws"],
                                  self.status, gs["tps"], own_key_exact, self.v_tables)
+            # the same call's argument list, kept for the steps that change nothing but the rows
+            vt = self.v_tables
+            head = [self.tables.ref] if vt is None else [self.tables.ref, vt.ref]
+            gs["fn"] = _native.lib.jqk_decode_append_attend if vt is None else _native.lib.jqk_decode_append_attend_packed_values
+            gs["arg0"] = len(head)
+            gs["strides"] = (k_new.stride(), v_new.stride())
+            gs["lens_ptr"] = self.seq_lens.data_ptr()
+            gs["args"] = head + [
+                0, 0, 0, _native.torch_dtype_code(k_new.dtype), _native.torch_dtype_code(v_new.dtype), k_new.stride(0),
+                k_new.stride(1), v_new.stride(0), v_new.stride(1), n, q.shape[1], self.seq_lens.data_ptr(), int(gs["covered"]),
+                int(gs["tps"]), self.page_table.data_ptr(), self.page_table.stride(0), int(self.k_pool.shape[0]),
+                self.k_pool.data_ptr(), self.v_pool.data_ptr(), gs["out"].data_ptr(), _native.torch_dtype_code(gs["out"].dtype),
+                0, gs["ws"].buf.data_ptr(), gs["ws"].buf.numel(), self.status.data_ptr(), 0]
         else:
             gs["k"].copy_(k_new, non_blocking=True)
             gs["v"].copy_(v_new, non_blocking=True)
