@@ -725,8 +725,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
         const float* row = vs.wide_cb + ((size_t)head * JQK_MAX_WIDE + i) * 256;
         for (int l = lane; l < (1 << m); l += 32) sm.vcb[base + l] = __float2bfloat16(__ldg(row + l));
       }
-      for (int e = tid; e < JQK_MAX_COLS * 16; e += DEC_THREADS)
-        sm.vcb[e] = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
+      for (int e = tid; e < JQK_MAX_COLS * 16; e += DEC_THREADS) {
+        const int c = e >> 4, l = e & 15;
+        sm.vcb[v_n_wide ? e : ((c >> 5) * 16 + l) * 32 + (c & 31)] = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
+      }
       uint4* z = reinterpret_cast<uint4*>(&st.v[0][0]);
       for (int e = lane; e < (int)(sizeof(st.v) / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -856,40 +858,45 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       }
     }
     if constexpr (VQ) {
-      // dequantise this lane's key into the tile: column after column, code -> bf16 centroid -> the
-      // key's slot of the column's row (dims-major, the layout the tensor-core product reads).  Keys
-      // past the end or on absent pages produce finite garbage that meets a zero weight.
+      // dequantise the tile: a lane owns columns (lane, lane + 32, ...) and walks the 16 keys of each
+      // page for them, so a column's word index, shift and mask are loop constants, its 16 record words
+      // arrive as four 16-byte reads (lanes whose columns share a word read the same bytes), sixteen
+      // independent code -> bf16 level reads follow, and the 16 levels leave as two 16-byte stores: one
+      // half-row each of the dims-major tile the tensor-core product reads (the halves of a row are
+      // swapped on every other group of four columns, which also spreads a warp's stores over all
+      // banks).  Keys past the end or on absent pages produce finite garbage that meets a zero weight.
       if (any && landed) {
-        const uint32_t* vw = reinterpret_cast<const uint32_t*>(st.vq[lane >> 4]) + (lane & 15);
-        uint8_t* vt = st.v[lane >> 4];
-        const int ts = lane & 15;
-        const uint32_t off_a = (uint32_t)((ts >> 3) * 16 + (ts & 7) * 2);        // rows with (column >> 2) & 1 == 0
-        const uint32_t off_b = (uint32_t)(((ts >> 3) ^ 1) * 16 + (ts & 7) * 2);  // the swapped halves
-        // eight columns at a time, stage by stage (descriptors, record words, centroids, stores), so
-        // that the dependent shared-memory reads of the eight overlap and no load waits behind a store
-        const int n_pad = (v_n_active + 7) & ~7;   // descriptors past the last column are 0: code 0 of a zero row
-        // (two forms of the loop: with byte-wide columns a descriptor also carries where the column's
-        // levels start; without, the rows are 16 entries apart and the descriptor has 14 bits)
+        // (two forms: with byte-wide columns a descriptor also carries where the column's levels
+        // start; without, the rows are 16 entries apart and the descriptor has 14 bits)
         auto dequantise = [&](auto with_wide) {
           constexpr bool VW = decltype(with_wide)::value;
+          const unsigned short* vcb16 = reinterpret_cast<const unsigned short*>(sm.vcb);
 #pragma unroll 1
-          for (int c0 = 0; c0 < n_pad; c0 += 8) {
-            const int4 ma = *reinterpret_cast<const int4*>(&sm.vmeta[c0]);
-            const int4 mb = *reinterpret_cast<const int4*>(&sm.vmeta[c0 + 4]);
-            const int m[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
-            uint32_t wd[8];
+          for (int c = lane; c < v_n_active; c += 32) {
+            const int m = sm.vmeta[c];
+            const int wi = VW ? ((m >> 9) & 31) : (m >> 9);       // bit position >> 5 = record word
+            const uint32_t sh = (m >> 4) & 31, mask = (1u << (m & 15)) - 1u;
+            // (without byte-wide columns the levels are stored lane-interleaved: level l of column
+            // lane + 32 k at [(16 k + l) * 32 + lane], so a warp's reads of random levels fall into
+            // the lanes' own banks, two lanes to a bank)
+            const unsigned short* row = vcb16 + (VW ? (m >> 14) : (c >> 5) * 512 + (c & 31));
+            constexpr int LP = VW ? 1 : 32;   // pitch of a column's levels
+            const uint32_t swap = (c >> 2) & 1;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)   // bit position >> 5 = record word
-              wd[i] = vw[(VW ? ((m[i] >> 9) & 31) : (m[i] >> 9)) * JQK_PAGE_TOKENS];
-            __nv_bfloat16 val[8];
+            for (int pg = 0; pg < 2; ++pg) {
+              const uint4* src = reinterpret_cast<const uint4*>(st.vq[pg] + wi * (JQK_PAGE_TOKENS * 4));
+              const uint4 w0 = src[0], w1 = src[1], w2 = src[2], w3 = src[3];
+              const uint32_t w[16] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w,
+                                      w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+              uint32_t lv[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const uint32_t code = (wd[i] >> ((m[i] >> 4) & 31)) & ((1u << (m[i] & 15)) - 1u);
-              val[i] = VW ? sm.vcb[(m[i] >> 14) + code] : sm.vcb[(c0 + i) * 16 + code];
+              for (int t = 0; t < 16; ++t) lv[t] = row[((w[t] >> sh) & mask) * LP];
+              uint8_t* dst = st.v[pg] + c * 32;
+              *reinterpret_cast<uint4*>(dst + (swap ? 16 : 0)) =
+                  make_uint4(lv[0] | (lv[1] << 16), lv[2] | (lv[3] << 16), lv[4] | (lv[5] << 16), lv[6] | (lv[7] << 16));
+              *reinterpret_cast<uint4*>(dst + (swap ? 0 : 16)) =
+                  make_uint4(lv[8] | (lv[9] << 16), lv[10] | (lv[11] << 16), lv[12] | (lv[13] << 16), lv[14] | (lv[15] << 16));
             }
-#pragma unroll
-            for (int i = 0; i < 8; ++i)   // (c0 + i) >> 2 is odd for i >= 4: those rows have their halves swapped
-              *reinterpret_cast<__nv_bfloat16*>(vt + (c0 + i) * 32 + (i >= 4 ? off_b : off_a)) = val[i];
           }
         };
         if (v_n_wide) dequantise(std::true_type{});
