@@ -95,8 +95,10 @@ def plan_key_layout(bits) -> KeyLayout:
 
     Coordinates of 5..8 bits ("wide", what the reference's cap of 8 gives outlier channels,
     per_coord_quantization.py:365-379) take one byte each, four to a word, in whole words between
-    the A region and the C region; the two regions then share no word.  Such a record can be
-    written, read back and reconstructed; the decode kernels' lookup tables cover 0..4 bits only."""
+    the A region and the C region; the two regions then share no word.  The decode kernels read a
+    wide column through a table of 2^width entries, 2^(width - 4) of their ``MAX_TABLES`` slots of 16
+    entries (``decodable``: the slots of all columns fit).  Raises ``ValueError`` when the record
+    does not hold the allocation: more than ``MAX_WIDE`` wide coordinates, or more than 16 words."""
     bits = np.asarray(bits).astype(np.int64).reshape(-1)
     d = int(bits.shape[0])
     if d % 16 != 0 or d > 128:
