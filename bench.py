@@ -1029,7 +1029,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     line = {
         "metric": METRIC, "value": world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_launch_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes, fp32 accumulate",
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes (fixed-point 16-bit lookup tables), fp32 accumulate",
         "data": "synthetic", "config": workload_config(world), "clocks": clocks,
         "e2e": {"value": world * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": e2e_out[0].numel() * 4,
@@ -1124,7 +1124,7 @@ def run_batch64(args, rank: int, local_rank: int, world: int) -> None:
         print(json.dumps({
             "metric": METRIC, "value": 64 * steps / (ms * 1e-3), "unit": "tokens/s (one 32-layer decode step per sequence)",
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": per_step_ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes, fp32 accumulate", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 q/V, 0-4 bit K codes (fixed-point 16-bit lookup tables), fp32 accumulate", "data": "synthetic",
             "config": {"workload": "decode, 32 layers, 64 sequences with context U{4096..65536} (%d keys in all), 32 q / 8 kv heads, "
                                    "head_dim 128, K packed at 3.0 bits/coord in 16-token pages, V bf16" % sum(lens_all),
                        "sharding": "by sequence, longest-processing-time over %d rank(s), no collective" % world,

@@ -1,5 +1,5 @@
-"""Packed record layout for per-coordinate codes of 0..4 bits (new in this build; the
-reference keeps dequantised floats and models no storage, per_coord_quantization.py:8).
+"""Packed record layout for per-coordinate codes of 0..4 bits, and of 5..8 bits as whole bytes
+(the reference keeps dequantised floats and models no storage, per_coord_quantization.py:8).
 
 One *record* holds the codes of one key.  Its bit string is ``32 * n_words`` long:
 
@@ -25,6 +25,12 @@ coordinates in the lookup.  Lookups are numbered by physical position:
 A word that is shared by the two regions is scanned by both loops; the lookups that fall
 on the other region's bytes get all-zero tables.
 
+* **Wide words** (only when some coordinate carries 5..8 bits, what the reference's default cap of
+  8 gives outlier channels, per_coord_quantization.py:365-379): such a coordinate takes one byte,
+  four to a word, in whole words between the A region and the C region, which then share no word.
+  The decode kernels give it a table of 2^width entries behind the 16-entry ones and scan these
+  words first.
+
 *Columns* are the coordinates with >0 bits listed in ascending physical bit position, padded
 with empty columns to a multiple of 16 (the tensor-core N granularity of the transform).
 The compress kernel quantises column after column and appends the codes to the record in
@@ -42,7 +48,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 PAGE_TOKENS = 16
-MAX_CODE_BITS = 4       # widths the lookup tables of the decode kernels take
+MAX_CODE_BITS = 4       # widths that share slots and 16-entry tables; wider codes take a byte each
 MAX_STORED_BITS = 8     # widths a record can hold: 5..8-bit codes take a byte each ("wide" columns)
 MAX_WIDE = 32           # wide columns per head
 MAX_VALUE_WIDE_LEVELS = 6144   # sum of 2^width over a head's wide columns that decode over packed VALUES holds
@@ -56,7 +62,7 @@ class KeyLayout:
     """Everything the kernels need to know about one head's record format."""
 
     d: int
-    bits: np.ndarray                 # (d,) int32, 0..4, coordinate order
+    bits: np.ndarray                 # (d,) int32, 0..8, coordinate order
     n_cols: int                      # active columns rounded up to a multiple of 16
     n_active: int                    # coordinates with >0 bits
     col_coord: np.ndarray            # (n_cols,) int32, -1 for padding columns
