@@ -153,7 +153,8 @@ template <> struct alignas(128) TileStageT<true> {
   uint8_t vq[2][K_STAGE_STRIDE];     // the two pages of V codes of the current tile
 };
 
-constexpr int VQ_WIDE_ENTRIES = JQK_MAX_VALUE_WIDE_LEVELS;   // levels of all byte-wide value columns of a head that the block can hold
+constexpr int VQ_WIDE_ENTRIES = JQK_MAX_VALUE_WIDE_LEVELS;
+static_assert(VQ_WIDE_ENTRIES >= JQK_MAX_COLS * 16, "the lane-interleaved level words of the narrow form use the wide levels' room");   // levels of all byte-wide value columns of a head that the block can hold
 template <bool VQ> struct DecodeSmemT;
 template <> struct DecodeSmemT<false> {
   union {            // the tables this block scores with:
@@ -727,7 +728,9 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
       }
       for (int e = tid; e < JQK_MAX_COLS * 16; e += DEC_THREADS) {
         const int c = e >> 4, l = e & 15;
-        sm.vcb[v_n_wide ? e : ((c >> 5) * 16 + l) * 32 + (c & 31)] = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
+        const __nv_bfloat16 lvl = __float2bfloat16(__ldg(vs.cb_cols + (size_t)head * 128 * 16 + e));
+        if (v_n_wide) sm.vcb[e] = lvl;
+        else reinterpret_cast<uint32_t*>(sm.vcb)[((c >> 5) * 16 + l) * 32 + (c & 31)] = (uint32_t)__bfloat16_as_ushort(lvl);
       }
       uint4* z = reinterpret_cast<uint4*>(&st.v[0][0]);
       for (int e = lane; e < (int)(sizeof(st.v) / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
@@ -876,11 +879,11 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
             const int m = sm.vmeta[c];
             const int wi = VW ? ((m >> 9) & 31) : (m >> 9);       // bit position >> 5 = record word
             const uint32_t sh = (m >> 4) & 31, mask = (1u << (m & 15)) - 1u;
-            // (without byte-wide columns the levels are stored lane-interleaved: level l of column
-            // lane + 32 k at [(16 k + l) * 32 + lane], so a warp's reads of random levels fall into
-            // the lanes' own banks, two lanes to a bank)
-            const unsigned short* row = vcb16 + (VW ? (m >> 14) : (c >> 5) * 512 + (c & 31));
-            constexpr int LP = VW ? 1 : 32;   // pitch of a column's levels
+            // (without byte-wide columns the levels are stored lane-interleaved, a 32-bit word each:
+            // level l of column lane + 32 k at word (16 k + l) * 32 + lane, so a warp's reads of random
+            // levels fall into the lanes' own banks; the words take the room of the wide levels)
+            const unsigned short* row = vcb16 + (m >> 14);
+            const uint32_t* row32 = reinterpret_cast<const uint32_t*>(sm.vcb) + (c >> 5) * 512 + (c & 31);
             const uint32_t swap = (c >> 2) & 1;
 #pragma unroll
             for (int pg = 0; pg < 2; ++pg) {
@@ -890,7 +893,10 @@ decode_kernel(jqk_head_tables tb, const __nv_bfloat16* __restrict__ q, int n_q_h
                                       w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
               uint32_t lv[16];
 #pragma unroll
-              for (int t = 0; t < 16; ++t) lv[t] = row[((w[t] >> sh) & mask) * LP];
+              for (int t = 0; t < 16; ++t) {
+                const uint32_t code = (w[t] >> sh) & mask;
+                lv[t] = VW ? (uint32_t)row[code] : row32[code * 32];
+              }
               uint8_t* dst = st.v[pg] + c * 32;
               *reinterpret_cast<uint4*>(dst + (swap ? 16 : 0)) =
                   make_uint4(lv[0] | (lv[1] << 16), lv[2] | (lv[3] << 16), lv[4] | (lv[5] << 16), lv[6] | (lv[7] << 16));
